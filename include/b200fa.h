@@ -1,0 +1,184 @@
+/*
+ * b200fa.h — C-ABI of libb200fa.so: flash attention for NVIDIA B200 (sm_100a).
+ *
+ * This is the boundary that replaces the reference's nanobind module
+ * `mlx_mfa._ext` (csrc/bindings.cpp) for the attention hot path.  Each entry
+ * point names the reference binding it stands in for.
+ *
+ * Conventions
+ *   - every function is extern "C", takes plain pointers and sizes, returns an
+ *     int32 status (B200FA_OK == 0, negative on error) and never throws;
+ *   - all tensor pointers are DEVICE pointers; the caller owns inputs, outputs
+ *     and the workspace (query its size with the *_workspace_bytes functions);
+ *     nothing here allocates device memory, except where an entry point's own
+ *     comment says otherwise;
+ *   - `stream` is a cudaStream_t passed as void*; launches are asynchronous
+ *     with respect to the host and no entry point synchronises;
+ *   - layouts follow the reference: q [B,Hq,N,D], k/v [B,Hkv,S,D], out like q,
+ *     lse [B,Hq,N] float32; the last (D) dimension is contiguous, the other
+ *     strides are given in ELEMENTS in the descriptor;
+ *   - lse is base-2: lse = log2(sum_j exp(s_j)), s_j the scaled (and
+ *     soft-capped, masked) score — the convention of the reference kernels
+ *     (csrc/mfa_steel_fwd.cpp:630, 1208-1221) that its backward consumes;
+ *   - b200fa_last_error() returns a thread-local message for the last failure.
+ */
+#ifndef B200FA_H_
+#define B200FA_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* status codes */
+#define B200FA_OK                  0
+#define B200FA_ERR_INVALID_ARG    -1   /* null pointer, bad shape/stride/alignment */
+#define B200FA_ERR_UNSUPPORTED    -2   /* dtype / head_dim / option not built */
+#define B200FA_ERR_WORKSPACE      -3   /* workspace missing or too small */
+#define B200FA_ERR_CUDA           -4   /* a CUDA runtime call failed */
+#define B200FA_ERR_DEVICE         -5   /* device is not sm_100 */
+
+/* element types */
+#define B200FA_F16   0
+#define B200FA_BF16  1
+#define B200FA_F32   2
+#define B200FA_I8    3   /* KV pools only: int8 with per-token-per-head scale */
+#define B200FA_E4M3  4   /* KV pools only: fp8 e4m3 with per-token-per-head scale */
+
+/* flags */
+#define B200FA_FLAG_FORCE_MMA_SYNC  1  /* use the portable mma.sync kernels even where a tcgen05 kernel exists */
+#define B200FA_FLAG_DETERMINISTIC   2  /* backward: dQ accumulated in a fixed order */
+
+/*
+ * Problem descriptor.  Plays the role of MFAttention::Params + MFASteelParams
+ * (csrc/mfa_attention.hpp:30-41, csrc/mfa_steel_fwd.hpp:25-54).
+ * For the varlen entry points B == 1, N == total_q, S == total_k.
+ */
+typedef struct b200fa_desc {
+  int32_t dtype;        /* B200FA_F16 | B200FA_BF16 | B200FA_F32 (q, out, dout, grads) */
+  int32_t kv_dtype;     /* == dtype, or B200FA_I8 / B200FA_E4M3 for decode pools */
+  int32_t B, Hq, Hkv;   /* Hq % Hkv == 0 (GQA / MQA) */
+  int32_t N, S, D;      /* query rows, key rows, head dim (64 or 128) */
+  int64_t q_strides[3]; /* batch, head, row — in elements; 0,0,0 => contiguous BHND */
+  int64_t k_strides[3];
+  int64_t v_strides[3];
+  int64_t o_strides[3];
+  float   scale;        /* multiplies q.k^T; reference default 1/sqrt(D) */
+  float   softcap;      /* 0 = off; s = cap*tanh(s/cap) before masking */
+  int32_t causal;       /* lower-right aligned: key j visible to row i iff j <= i + (S-N) */
+  int32_t window_left;  /* -1 = off; key j visible iff j >= i + (S-N) - window_left */
+  int32_t num_splits;   /* decode: 0 = choose automatically */
+  int32_t flags;
+} b200fa_desc;
+
+typedef struct b200fa_device_info_t {
+  int32_t cc_major, cc_minor, sm_count;
+  int32_t smem_per_block_optin;
+  int64_t total_mem;
+  int32_t has_tcgen05;          /* 1 when built for and running on sm_100 */
+  char    name[128];
+} b200fa_device_info_t;
+
+/* Replaces get_device_info (csrc/bindings.cpp:165-216). `device` < 0 = current. */
+int32_t b200fa_device_info(int32_t device, b200fa_device_info_t* out);
+
+const char* b200fa_last_error(void);
+const char* b200fa_version(void);
+
+/*
+ * Forward, dense layout.  Replaces mfa_attention_forward (csrc/bindings.cpp:21-35)
+ * and mfa_forward_with_lse (csrc/bindings.cpp:38-57); host dispatch role of
+ * MFAttention::eval_gpu (csrc/mfa_attention.cpp:47-409).  `lse` may be NULL.
+ */
+size_t  b200fa_fwd_workspace_bytes(const b200fa_desc* d);
+int32_t b200fa_fwd(const b200fa_desc* d, const void* q, const void* k, const void* v,
+                   void* out, float* lse, void* workspace, size_t workspace_bytes,
+                   void* stream);
+
+/*
+ * Forward, packed variable-length sequences.  Replaces
+ * mfa_attention_varlen_forward (csrc/bindings.cpp:320-344) /
+ * MFAVarlenAttention::eval_gpu (csrc/mfa_attention.cpp:1228-1305).
+ * cu_seqlens_* are device int32 [num_seqs+1]; max_seqlen_* are host ints
+ * (the reference front end passes them the same way, mlx_mfa/attention.py:2399-2400).
+ */
+size_t  b200fa_fwd_varlen_workspace_bytes(const b200fa_desc* d, int32_t num_seqs,
+                                          int32_t max_seqlen_q, int32_t max_seqlen_k);
+int32_t b200fa_fwd_varlen(const b200fa_desc* d, const void* q, const void* k, const void* v,
+                          const int32_t* cu_seqlens_q, const int32_t* cu_seqlens_k,
+                          int32_t num_seqs, int32_t max_seqlen_q, int32_t max_seqlen_k,
+                          void* out, float* lse, void* workspace, size_t workspace_bytes,
+                          void* stream);
+
+/*
+ * Backward dQ/dK/dV, dense layout.  Replaces mfa_steel_backward
+ * (csrc/bindings.cpp:120-163: delta = sum(dO*O) + MFASteelBwdDQ + MFASteelBwdDKV,
+ * csrc/mfa_attention.cpp:732-930).  `lse` is the forward's base-2 lse.
+ * dq like q; dk, dv like k, v ([B,Hkv,S,D], summed over the GQA group).
+ */
+size_t  b200fa_bwd_workspace_bytes(const b200fa_desc* d);
+int32_t b200fa_bwd(const b200fa_desc* d, const void* q, const void* k, const void* v,
+                   const void* out, const float* lse, const void* dout,
+                   void* dq, void* dk, void* dv,
+                   void* workspace, size_t workspace_bytes, void* stream);
+
+/*
+ * Backward, packed variable-length sequences, one launch sequence for all
+ * sequences.  Replaces the per-sequence Python loop of _varlen_bwd
+ * (mlx_mfa/attention.py:2492-2521).
+ */
+size_t  b200fa_bwd_varlen_workspace_bytes(const b200fa_desc* d, int32_t num_seqs,
+                                          int32_t max_seqlen_q, int32_t max_seqlen_k);
+int32_t b200fa_bwd_varlen(const b200fa_desc* d, const void* q, const void* k, const void* v,
+                          const void* out, const float* lse, const void* dout,
+                          const int32_t* cu_seqlens_q, const int32_t* cu_seqlens_k,
+                          int32_t num_seqs, int32_t max_seqlen_q, int32_t max_seqlen_k,
+                          void* dq, void* dk, void* dv,
+                          void* workspace, size_t workspace_bytes, void* stream);
+
+/*
+ * Paged-KV attention for short queries (decode), split-KV with the
+ * log-sum-exp combine done inside the same launch.  Replaces
+ * mfa_paged_steel_forward (csrc/bindings.cpp:367-407) and the gather +
+ * per-sequence flash-decode route of flash_attention_paged
+ * (mlx_mfa/attention.py:3008-3017, csrc/mfa_attention.cpp:150-288).
+ *   k_pool/v_pool  [num_pages, block_size, Hkv, D] in d->kv_dtype
+ *   k_scale/v_scale [num_pages, block_size, Hkv] float16, required for
+ *                  B200FA_I8 / B200FA_E4M3, NULL otherwise; a stored value x
+ *                  stands for float(x) * scale (dense-dequant path of
+ *                  mlx_mfa/integrations/mlx_lm.py:97-110 with one group per row)
+ *   block_table    int32 [B, max_blocks], -1 = no page
+ *   seq_lens       int32 [B]
+ *   d->N is the number of query rows per sequence (<= 16), d->S is ignored;
+ *   causal is per-sequence lower-right aligned.
+ * `num_pages` is used only to validate the arguments' sizes.
+ */
+size_t  b200fa_decode_paged_workspace_bytes(const b200fa_desc* d, int32_t max_kv_len);
+int32_t b200fa_decode_paged(const b200fa_desc* d, const void* q,
+                            const void* k_pool, const void* v_pool,
+                            const void* k_scale, const void* v_scale,
+                            const int32_t* block_table, const int32_t* seq_lens,
+                            int32_t num_pages, int32_t block_size, int32_t max_blocks,
+                            int32_t max_kv_len,
+                            void* out, float* lse,
+                            void* workspace, size_t workspace_bytes, void* stream);
+
+/*
+ * Page gather: out[b,h,t,:] = pool[block_table[b, t / block_size], t % block_size, h, :]
+ * for t < seq_lens[b] and a non-negative table entry, else zero.  Bit-exact copy.
+ * Replaces mfa_paged_kv_gather (csrc/bindings.cpp:346-364) /
+ * MFAPagedKVGather (csrc/mfa_paged_gather.cpp:44-80, 89-129).
+ * elem_bytes in {1,2,4}; D*elem_bytes must be a multiple of 16.
+ */
+int32_t b200fa_paged_kv_gather(const void* pool, const int32_t* block_table,
+                               const int32_t* seq_lens,
+                               int32_t B, int32_t H, int32_t D, int32_t elem_bytes,
+                               int32_t block_size, int32_t max_blocks, int32_t max_kv_len,
+                               void* out, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* B200FA_H_ */

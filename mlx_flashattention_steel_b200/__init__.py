@@ -1,0 +1,29 @@
+"""B200-native flash attention behind the ``mlx_mfa`` operator surface.
+
+Public names follow ``mlx_mfa/__init__.py:96-133`` of the reference for the
+attention hot path; everything runs hand-written sm_100a CUDA through
+``libb200fa.so`` (C-ABI in ``include/b200fa.h``).
+"""
+from .attention import (
+    flash_attention,
+    flash_attention_kvcache,
+    flash_attention_paged,
+    flash_attention_varlen,
+    get_device_info,
+    get_supported_configs,
+    is_mfa_available,
+    paged_kv_gather,
+)
+
+__version__ = "0.1.0"
+
+__all__ = [
+    "flash_attention",
+    "flash_attention_varlen",
+    "flash_attention_kvcache",
+    "flash_attention_paged",
+    "paged_kv_gather",
+    "is_mfa_available",
+    "get_device_info",
+    "get_supported_configs",
+]

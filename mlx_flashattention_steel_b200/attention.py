@@ -1,0 +1,692 @@
+"""Operator front end: the ``mlx_mfa`` attention surface on B200.
+
+Same function names, argument order, defaults and error behaviour as the
+reference's ``mlx_mfa/attention.py`` for the attention hot path:
+
+* ``flash_attention``          (mlx_mfa/attention.py:39-316)
+* ``flash_attention_varlen``   (mlx_mfa/attention.py:2393-2523)
+* ``flash_attention_kvcache``  (mlx_mfa/attention.py:903-1213)
+* ``flash_attention_paged``    (mlx_mfa/attention.py:2819-3084)
+
+Arrays are ``torch.Tensor`` on a CUDA device or any object exporting
+``__dlpack__``; results are ``torch.Tensor``.  Every operator runs a hand-written
+CUDA kernel through the C-ABI of ``libb200fa.so``; where the reference would
+silently fall back to ``mx.fast.scaled_dot_product_attention`` this module
+raises instead (no second backend, no CPU path).
+
+Deliberate differences from the reference, all on the side of its CPU
+(``backend="sdpa"``) semantics:
+
+* causal masks are lower-right aligned per sequence everywhere (the reference's
+  varlen kernel and backward are top-left aligned, equal when N == S);
+* ``return_lse=True`` honours ``softcap`` and ``window_size`` (the reference
+  drops them on that path, mlx_mfa/attention.py:308-314);
+* the backward uses the lse saved by the forward instead of recomputing the
+  forward (mlx_mfa/attention.py:2009).
+"""
+from __future__ import annotations
+
+import ctypes as C
+import math
+from typing import Optional, Sequence, Tuple, Union
+
+import torch
+
+from . import _lib
+
+_SUPPORTED_HDIMS = (64, 128)
+_VALID_BACKENDS = {"auto", "mfa", "sdpa"}
+_DTYPE_CODE = {torch.float16: _lib.F16, torch.bfloat16: _lib.BF16, torch.float32: _lib.F32}
+
+__all__ = [
+    "flash_attention",
+    "flash_attention_varlen",
+    "flash_attention_kvcache",
+    "flash_attention_paged",
+    "paged_kv_gather",
+    "is_mfa_available",
+    "get_device_info",
+    "get_supported_configs",
+]
+
+
+# ---------------------------------------------------------------------------
+# helpers
+# ---------------------------------------------------------------------------
+def _as_tensor(x, name: str) -> torch.Tensor:
+    """Accepts a torch tensor or any DLPack exporter."""
+    if x is None:
+        raise ValueError(f"{name} is None")
+    if not isinstance(x, torch.Tensor):
+        if hasattr(x, "__dlpack__"):
+            x = torch.from_dlpack(x)
+        else:
+            raise TypeError(f"{name} must be a torch.Tensor or export __dlpack__, got {type(x)!r}")
+    return x
+
+
+def _require_cuda(*tensors) -> None:
+    """Raised just before a launch: there is no CPU implementation to fall back to."""
+    for t in tensors:
+        if t is not None and not t.is_cuda:
+            raise RuntimeError(
+                f"tensor on {t.device}: this library only runs CUDA kernels on a B200 and has no CPU path."
+            )
+
+
+def _row_contig(x: torch.Tensor) -> torch.Tensor:
+    """Makes the last dim contiguous and the strides / base 16-byte multiples,
+    copying only when needed (the reference forces full contiguity,
+    mlx_mfa/attention.py:2049-2053)."""
+    eb = x.element_size()
+    ok = x.stride(-1) == 1 and all((s * eb) % 16 == 0 for s in x.stride()[:-1]) and x.data_ptr() % 16 == 0
+    return x if ok else x.contiguous()
+
+
+def _stream_ptr(stream, device) -> int:
+    if stream is None:
+        return torch.cuda.current_stream(device).cuda_stream
+    if isinstance(stream, torch.cuda.Stream):
+        return stream.cuda_stream
+    if isinstance(stream, int):
+        return stream
+    raise TypeError("stream must be None, a torch.cuda.Stream or a raw cudaStream_t integer")
+
+
+def _ptr(t: Optional[torch.Tensor]):
+    return None if t is None else C.c_void_p(t.data_ptr())
+
+
+def _desc(dtype, kv_dtype, B, Hq, Hkv, N, S, D, scale, causal, softcap=0.0, window_left=-1,
+          num_splits=0, flags=0, q=None, k=None, v=None, o=None) -> _lib.Desc:
+    d = _lib.Desc()
+    d.dtype, d.kv_dtype = dtype, kv_dtype
+    d.B, d.Hq, d.Hkv, d.N, d.S, d.D = B, Hq, Hkv, N, S, D
+    for name, t in (("q_strides", q), ("k_strides", k), ("v_strides", v), ("o_strides", o)):
+        arr = getattr(d, name)
+        if t is None:
+            arr[0] = arr[1] = arr[2] = 0
+        else:
+            arr[0], arr[1], arr[2] = t.stride(0), t.stride(1), t.stride(2)
+    d.scale = float(scale)
+    d.softcap = float(softcap)
+    d.causal = 1 if causal else 0
+    d.window_left = int(window_left)
+    d.num_splits = int(num_splits)
+    d.flags = int(flags)
+    return d
+
+
+_FORCE_FLAGS = 0
+
+
+def _set_force_flags(flags: int) -> int:
+    """Test hook: ORs `flags` (e.g. FLAG_FORCE_MMA_SYNC) into every descriptor."""
+    global _FORCE_FLAGS
+    old, _FORCE_FLAGS = _FORCE_FLAGS, int(flags)
+    return old
+
+
+# ---------------------------------------------------------------------------
+# raw operator calls (C-ABI)
+# ---------------------------------------------------------------------------
+def _fwd_raw(q, k, v, scale, causal, softcap, window_left, want_lse, stream):
+    _require_cuda(q, k, v)
+    lib = _lib.load()
+    B, Hq, N, D = q.shape
+    Hkv, S = k.shape[1], k.shape[2]
+    q, k, v = _row_contig(q), _row_contig(k), _row_contig(v)
+    out = torch.empty((B, Hq, N, D), dtype=q.dtype, device=q.device)
+    lse = torch.empty((B, Hq, N), dtype=torch.float32, device=q.device) if want_lse else None
+    code = _DTYPE_CODE[q.dtype]
+    d = _desc(code, code, B, Hq, Hkv, N, S, D, scale, causal, softcap, window_left,
+              flags=_FORCE_FLAGS, q=q, k=k if S > 0 else None, v=v if S > 0 else None, o=out)
+    with torch.cuda.device(q.device):
+        st = lib.b200fa_fwd(C.byref(d), _ptr(q), _ptr(k), _ptr(v), _ptr(out), _ptr(lse), None, 0,
+                            C.c_void_p(_stream_ptr(stream, q.device)))
+    _lib.check(st, "flash_attention")
+    return out, lse
+
+
+def _bwd_raw(q, k, v, out, lse, dout, scale, causal, stream, cu=None):
+    _require_cuda(q, k, v, out, lse, dout)
+    lib = _lib.load()
+    B, Hq, N, D = q.shape
+    Hkv, S = k.shape[1], k.shape[2]
+    q, k, v = _row_contig(q), _row_contig(k), _row_contig(v)
+    out = out.contiguous()
+    dout = dout.contiguous()
+    dq = torch.empty((B, Hq, N, D), dtype=q.dtype, device=q.device)
+    dk = torch.empty((B, Hkv, S, D), dtype=q.dtype, device=q.device)
+    dv = torch.empty((B, Hkv, S, D), dtype=q.dtype, device=q.device)
+    code = _DTYPE_CODE[q.dtype]
+    d = _desc(code, code, B, Hq, Hkv, N, S, D, scale, causal, flags=_FORCE_FLAGS, q=q, k=k, v=v, o=out)
+    sp = C.c_void_p(_stream_ptr(stream, q.device))
+    with torch.cuda.device(q.device):
+        if cu is None:
+            need = lib.b200fa_bwd_workspace_bytes(C.byref(d))
+            ws = torch.empty(max(need, 16), dtype=torch.uint8, device=q.device)
+            st = lib.b200fa_bwd(C.byref(d), _ptr(q), _ptr(k), _ptr(v), _ptr(out), _ptr(lse), _ptr(dout),
+                                _ptr(dq), _ptr(dk), _ptr(dv), _ptr(ws), ws.numel(), sp)
+        else:
+            cu_q, cu_k, nseq, max_q, max_k = cu
+            need = lib.b200fa_bwd_varlen_workspace_bytes(C.byref(d), nseq, max_q, max_k)
+            ws = torch.empty(max(need, 16), dtype=torch.uint8, device=q.device)
+            st = lib.b200fa_bwd_varlen(C.byref(d), _ptr(q), _ptr(k), _ptr(v), _ptr(out), _ptr(lse),
+                                       _ptr(dout), _ptr(cu_q), _ptr(cu_k), nseq, max_q, max_k,
+                                       _ptr(dq), _ptr(dk), _ptr(dv), _ptr(ws), ws.numel(), sp)
+    _lib.check(st, "flash_attention backward")
+    return dq, dk, dv
+
+
+class _FlashAttnFn(torch.autograd.Function):
+    """Autograd glue; role of _make_mfa_custom (mlx_mfa/attention.py:1931-2030)."""
+
+    @staticmethod
+    def forward(ctx, q, k, v, scale, causal, softcap, window_left, want_lse, stream):
+        need_grad = q.requires_grad or k.requires_grad or v.requires_grad
+        out, lse = _fwd_raw(q, k, v, scale, causal, softcap, window_left, want_lse or need_grad, stream)
+        ctx.save_for_backward(q, k, v, out, lse if lse is not None else torch.empty(0, device=q.device))
+        ctx.cfg = (scale, causal, softcap, window_left, stream)
+        if want_lse:
+            ctx.mark_non_differentiable(lse)
+            return out, lse
+        return out, None
+
+    @staticmethod
+    def backward(ctx, dout, _dlse):
+        q, k, v, out, lse = ctx.saved_tensors
+        scale, causal, softcap, window_left, stream = ctx.cfg
+        if softcap != 0.0 or window_left >= 0:
+            raise NotImplementedError(
+                "flash_attention backward with softcap or window_size: the reference differentiates "
+                "its SDPA fallback here (mlx_mfa/attention.py:1976-1992, 2020-2027); no CUDA kernel is built."
+            )
+        if q.dtype == torch.float32:
+            raise NotImplementedError(
+                "flash_attention backward for float32: the reference differentiates its SDPA fallback "
+                "(mlx_mfa/attention.py:2013-2019); the CUDA backward takes f16/bf16."
+            )
+        if q.shape[2] != k.shape[2] and causal:
+            raise NotImplementedError("causal backward with N != S is not built")
+        dq, dk, dv = _bwd_raw(q, k, v, out, lse, dout, scale, causal, stream)
+        return dq, dk, dv, None, None, None, None, None, None
+
+
+# ---------------------------------------------------------------------------
+# flash_attention
+# ---------------------------------------------------------------------------
+def flash_attention(
+    q,
+    k,
+    v,
+    scale: Optional[float] = None,
+    causal: bool = False,
+    softcap: float = 0.0,
+    alibi_slopes=None,
+    dropout_p: float = 0.0,
+    return_attn_weights: bool = False,
+    window_size: Optional[Tuple[int, int]] = None,
+    return_lse: bool = False,
+    stream=None,
+    attn_bias=None,
+    backend: str = "auto",
+):
+    """Scaled dot-product attention, ``softmax(scale * q k^T + mask) v``.
+
+    Args follow mlx_mfa.flash_attention (mlx_mfa/attention.py:39-54):
+    q ``[B, Hq, N, D]``; k, v ``[B, Hkv, S, D]`` with ``Hq % Hkv == 0`` (GQA/MQA);
+    ``scale`` defaults to ``1/sqrt(D)``; ``causal`` masks key ``j > i + (S - N)``;
+    ``softcap`` applies ``cap * tanh(s / cap)`` before masking;
+    ``window_size=(left, right)`` keeps keys ``j >= i + (S - N) - left``; ``right``
+    must be -1 or 0 (no right bound, mlx_mfa/attention.py:282-288);
+    ``return_lse=True`` returns ``(O, L)``, ``L`` float32 ``[B, Hq, N]`` in base 2.
+
+    Raises ValueError / NotImplementedError / RuntimeError at the conditions the
+    reference does; options the reference serves only through its SDPA fallback
+    (``alibi_slopes``, ``dropout_p``, ``return_attn_weights``, ``attn_bias``,
+    ``backend="sdpa"``, ``D_v != D_qk``) raise NotImplementedError.
+    """
+    if backend not in _VALID_BACKENDS:
+        raise ValueError(
+            f"flash_attention: backend must be one of {sorted(_VALID_BACKENDS)}, got {backend!r}."
+        )
+    if backend == "sdpa":
+        raise NotImplementedError(
+            "flash_attention(backend='sdpa'): the SDPA fallback of the reference "
+            "(mlx_mfa/attention.py:169-180) is not part of this library; it has no CPU path."
+        )
+    q, k, v = _as_tensor(q, "q"), _as_tensor(k, "k"), _as_tensor(v, "v")
+    if q.ndim != 4 or k.ndim != 4 or v.ndim != 4:
+        raise ValueError(
+            f"flash_attention expects 4-D tensors [batch, heads, seq, head_dim]."
+            f" Got q={q.ndim}D, k={k.ndim}D, v={v.ndim}D."
+        )
+    q_dim, k_dim, v_dim = q.shape[-1], k.shape[-1], v.shape[-1]
+    if k_dim != q_dim:
+        raise ValueError(f"q and k must have the same head_dim. Got q_dim={q_dim}, k_dim={k_dim}.")
+    head_dim = q_dim
+    if scale is None:
+        scale = 1.0 / math.sqrt(head_dim)
+    q_heads, kv_heads = q.shape[1], k.shape[1]
+    if kv_heads != q_heads and q_heads % kv_heads != 0:
+        raise ValueError(
+            f"flash_attention GQA: q_heads ({q_heads}) must be divisible by kv_heads ({kv_heads})."
+        )
+    if k.shape[0] != q.shape[0] or v.shape[:3] != k.shape[:3]:
+        raise ValueError(f"flash_attention: inconsistent shapes q={tuple(q.shape)} k={tuple(k.shape)} v={tuple(v.shape)}.")
+    if return_attn_weights:
+        if return_lse:
+            raise ValueError("return_attn_weights and return_lse are mutually exclusive.")
+        raise NotImplementedError("return_attn_weights needs the reference's SDPA fallback; not built.")
+    if dropout_p > 0.0:
+        raise NotImplementedError("dropout_p > 0 needs the reference's SDPA fallback; not built.")
+    if attn_bias is not None:
+        raise NotImplementedError("attn_bias needs the reference's SDPA fallback; not built.")
+    if alibi_slopes is not None:
+        raise NotImplementedError("alibi_slopes is not built.")
+    supported = head_dim in _SUPPORTED_HDIMS and q.dtype in _DTYPE_CODE and v_dim == q_dim
+    if not supported:
+        msg = (
+            f"unsupported configuration — head_dim={head_dim}, dtype={q.dtype}, "
+            f"v_dim_mismatch={v_dim != q_dim}. Supported: head_dim∈{{64,128}}, dtype∈{{f16,bf16,f32}}."
+        )
+        if backend == "mfa":
+            raise RuntimeError(f"flash_attention(backend='mfa'): {msg}")
+        raise NotImplementedError(f"flash_attention: {msg}")
+    if k.dtype != q.dtype or v.dtype != q.dtype:
+        raise ValueError(f"flash_attention: q, k, v must share a dtype, got {q.dtype}, {k.dtype}, {v.dtype}.")
+
+    window_left = -1
+    if window_size is not None:
+        wr = window_size[1] if len(window_size) > 1 else -1
+        if wr > 0:
+            raise NotImplementedError(
+                f"flash_attention: window_size right={wr} is not yet supported. "
+                "The STEEL kernel only implements left-side sliding-window masking. "
+                "Use causal=True to mask all future tokens, or set right=-1."
+            )
+        window_left = max(int(window_size[0]), 0)
+
+    out, lse = _FlashAttnFn.apply(q, k, v, float(scale), bool(causal), float(softcap), window_left,
+                                  bool(return_lse), stream)
+    if return_lse:
+        return out, lse
+    return out
+
+
+# ---------------------------------------------------------------------------
+# flash_attention_varlen
+# ---------------------------------------------------------------------------
+def _varlen_fwd_raw(q, k, v, cu_q, cu_k, nseq, max_q, max_k, scale, causal, want_lse, stream):
+    _require_cuda(q, k, v, cu_q, cu_k)
+    lib = _lib.load()
+    _, Hq, Tq, D = q.shape
+    Hkv, Tk = k.shape[1], k.shape[2]
+    q, k, v = _row_contig(q), _row_contig(k), _row_contig(v)
+    out = torch.zeros((1, Hq, Tq, D), dtype=q.dtype, device=q.device)
+    lse = torch.zeros((1, Hq, Tq), dtype=torch.float32, device=q.device) if want_lse else None
+    code = _DTYPE_CODE[q.dtype]
+    d = _desc(code, code, 1, Hq, Hkv, Tq, Tk, D, scale, causal, flags=_FORCE_FLAGS, q=q, k=k, v=v, o=out)
+    with torch.cuda.device(q.device):
+        st = lib.b200fa_fwd_varlen(C.byref(d), _ptr(q), _ptr(k), _ptr(v), _ptr(cu_q), _ptr(cu_k), nseq,
+                                   max_q, max_k, _ptr(out), _ptr(lse), None, 0,
+                                   C.c_void_p(_stream_ptr(stream, q.device)))
+    _lib.check(st, "flash_attention_varlen")
+    return out, lse
+
+
+class _VarlenFn(torch.autograd.Function):
+    """One forward launch and one backward launch sequence for all packed
+    sequences; replaces _varlen_impl/_varlen_bwd (mlx_mfa/attention.py:2463-2521)."""
+
+    @staticmethod
+    def forward(ctx, q, k, v, cu_q, cu_k, nseq, max_q, max_k, scale, causal, stream):
+        need_grad = q.requires_grad or k.requires_grad or v.requires_grad
+        out, lse = _varlen_fwd_raw(q, k, v, cu_q, cu_k, nseq, max_q, max_k, scale, causal, need_grad, stream)
+        ctx.save_for_backward(q, k, v, out, lse if lse is not None else torch.empty(0, device=q.device), cu_q, cu_k)
+        ctx.cfg = (nseq, max_q, max_k, scale, causal, stream)
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        q, k, v, out, lse, cu_q, cu_k = ctx.saved_tensors
+        nseq, max_q, max_k, scale, causal, stream = ctx.cfg
+        if q.dtype == torch.float32:
+            raise NotImplementedError("flash_attention_varlen backward takes f16/bf16.")
+        dq, dk, dv = _bwd_raw(q, k, v, out, lse, dout, scale, causal, stream,
+                              cu=(cu_q, cu_k, nseq, max_q, max_k))
+        return dq, dk, dv, None, None, None, None, None, None, None, None
+
+
+def flash_attention_varlen(
+    q,
+    k,
+    v,
+    cu_seqlens_q,
+    cu_seqlens_k,
+    max_seqlen_q: int,
+    max_seqlen_k: int,
+    scale: Optional[float] = None,
+    causal: bool = False,
+    block_mask=None,
+    stream=None,
+):
+    """Attention over sequences packed along the token axis.
+
+    Signature of mlx_mfa.flash_attention_varlen (mlx_mfa/attention.py:2393-2405):
+    q, k, v ``[1, H, total_tokens, D]``; ``cu_seqlens_*`` int32 ``[num_seqs + 1]``
+    cumulative lengths; sequences attend only to themselves; ``causal`` is applied
+    per sequence.  Returns ``[1, H, total_q, D]``.  ``num_seqs == 0`` returns ``q``
+    (mlx_mfa/attention.py:2444-2445).  ``block_mask`` raises NotImplementedError.
+    """
+    q, k, v = _as_tensor(q, "q"), _as_tensor(k, "k"), _as_tensor(v, "v")
+    if q.ndim != 4 or k.ndim != 4 or v.ndim != 4:
+        raise ValueError("flash_attention_varlen expects 4-D tensors [1, H, total_tokens, D].")
+    if scale is None:
+        scale = 1.0 / math.sqrt(q.shape[-1])
+    cu_q = _as_tensor(cu_seqlens_q, "cu_seqlens_q")
+    cu_k = _as_tensor(cu_seqlens_k, "cu_seqlens_k")
+    nseq = cu_q.numel() - 1
+    if nseq <= 0:
+        return q
+    if block_mask is not None:
+        raise NotImplementedError("flash_attention_varlen: block_mask (block-sparse) is not built.")
+    if q.shape[0] != 1 or k.shape[0] != 1 or v.shape[0] != 1:
+        raise ValueError("flash_attention_varlen expects packed tensors with batch size 1.")
+    if cu_k.numel() != cu_q.numel():
+        raise ValueError("cu_seqlens_q and cu_seqlens_k must have the same length.")
+    D = q.shape[-1]
+    if k.shape[-1] != D or v.shape[-1] != D:
+        raise ValueError("q, k, v must have the same head_dim.")
+    if q.shape[1] % k.shape[1] != 0:
+        raise ValueError(f"flash_attention GQA: q_heads ({q.shape[1]}) must be divisible by kv_heads ({k.shape[1]}).")
+    if D not in _SUPPORTED_HDIMS or q.dtype not in _DTYPE_CODE:
+        raise NotImplementedError(f"flash_attention_varlen: head_dim={D}, dtype={q.dtype} not built.")
+    cu_q = cu_q.to(torch.int32).contiguous()
+    cu_k = cu_k.to(torch.int32).contiguous()
+    return _VarlenFn.apply(q, k, v, cu_q, cu_k, int(nseq), int(max_seqlen_q), int(max_seqlen_k),
+                           float(scale), bool(causal), stream)
+
+
+# ---------------------------------------------------------------------------
+# paged KV
+# ---------------------------------------------------------------------------
+def paged_kv_gather(pool, block_table, seq_lens, max_kv_len: int, stream=None) -> torch.Tensor:
+    """``pool [num_pages, block_size, H, D]`` -> ``[B, H, max_kv_len, D]``, zero
+    beyond ``seq_lens[b]`` and for ``-1`` table entries.  Bit-exact copy; same
+    contract as ``_ext.mfa_paged_kv_gather`` (csrc/bindings.cpp:346-364)."""
+    pool = _as_tensor(pool, "pool").contiguous()
+    table = _as_tensor(block_table, "block_table").to(torch.int32).contiguous()
+    lens = _as_tensor(seq_lens, "seq_lens").to(torch.int32).contiguous()
+    if pool.ndim != 4 or table.ndim != 2 or lens.ndim != 1:
+        raise ValueError("paged_kv_gather: pool must be 4-D, block_table 2-D, seq_lens 1-D.")
+    _require_cuda(pool, table, lens)
+    lib = _lib.load()
+    _, bs, H, D = pool.shape
+    B, max_blocks = table.shape
+    out = torch.empty((B, H, max_kv_len, D), dtype=pool.dtype, device=pool.device)
+    with torch.cuda.device(pool.device):
+        st = lib.b200fa_paged_kv_gather(_ptr(pool), _ptr(table), _ptr(lens), B, H, D, pool.element_size(),
+                                        bs, max_blocks, int(max_kv_len), _ptr(out),
+                                        C.c_void_p(_stream_ptr(stream, pool.device)))
+    _lib.check(st, "paged_kv_gather")
+    return out
+
+
+_KV_CODE = {torch.int8: _lib.I8}
+if hasattr(torch, "float8_e4m3fn"):
+    _KV_CODE[torch.float8_e4m3fn] = _lib.E4M3
+
+
+def _decode_raw(q, k_pages, v_pages, k_scale, v_scale, table, lens, max_kv_len, scale, causal, softcap,
+                block_size, want_lse, stream, num_splits=0, workspace=None):
+    _require_cuda(q, k_pages, v_pages, k_scale, v_scale, table, lens)
+    lib = _lib.load()
+    B, Hq, Nq, D = q.shape
+    num_pages, _, Hkv, _ = k_pages.shape
+    q = q.contiguous()
+    out = torch.empty((B, Hq, Nq, D), dtype=q.dtype, device=q.device)
+    lse = torch.empty((B, Hq, Nq), dtype=torch.float32, device=q.device) if want_lse else None
+    code = _DTYPE_CODE[q.dtype]
+    kv_code = _KV_CODE.get(k_pages.dtype, _DTYPE_CODE.get(k_pages.dtype, -1))
+    d = _desc(code, kv_code, B, Hq, Hkv, Nq, 0, D, scale, causal, softcap, -1, num_splits, _FORCE_FLAGS)
+    with torch.cuda.device(q.device):
+        need = lib.b200fa_decode_paged_workspace_bytes(C.byref(d), int(max_kv_len))
+        if workspace is None or workspace.numel() < need:
+            workspace = torch.empty(max(need, 16), dtype=torch.uint8, device=q.device)
+        st = lib.b200fa_decode_paged(C.byref(d), _ptr(q), _ptr(k_pages), _ptr(v_pages), _ptr(k_scale),
+                                     _ptr(v_scale), _ptr(table), _ptr(lens), num_pages, block_size,
+                                     table.shape[1], int(max_kv_len), _ptr(out), _ptr(lse),
+                                     _ptr(workspace), workspace.numel(),
+                                     C.c_void_p(_stream_ptr(stream, q.device)))
+    _lib.check(st, "flash_attention_paged")
+    return out, lse
+
+
+def flash_attention_paged(
+    q,
+    k_pages,
+    v_pages,
+    block_table,
+    seq_lens,
+    *,
+    scale: Optional[float] = None,
+    causal: bool = False,
+    block_size: int = 16,
+    stream=None,
+    k_scale=None,
+    v_scale=None,
+    softcap: float = 0.0,
+    max_kv_len: Optional[int] = None,
+    return_lse: bool = False,
+):
+    """Attention over a paged KV pool.
+
+    Signature of mlx_mfa.flash_attention_paged (mlx_mfa/attention.py:2819-2830) plus
+    keyword-only extensions.  q ``[B, Hq, Nq, D]``; ``k_pages``/``v_pages``
+    ``[num_pages, block_size, Hkv, D]``; ``block_table`` int32 ``[B, max_blocks]``
+    (-1 pads); ``seq_lens`` int32 ``[B]``.  Each sequence sees exactly its first
+    ``seq_lens[b]`` tokens; ``causal`` is lower-right aligned per sequence.
+
+    Extensions: ``k_scale``/``v_scale`` float16 ``[num_pages, block_size, Hkv]`` for
+    int8 / float8_e4m3 pools (a stored x stands for ``float(x) * scale``, rounded to
+    the query dtype as ``mx.dequantize(..., dtype=q.dtype)`` does in
+    mlx_mfa/integrations/mlx_lm.py:97-110); ``max_kv_len`` skips the host read of
+    ``seq_lens`` that the reference also performs (mlx_mfa/attention.py:2871-2873).
+
+    Short queries ((Hq/Hkv)*Nq <= 8, D = 128, block_size 16) run the split-KV
+    decode kernel with in-kernel combine; other shapes gather pages and attend
+    per sequence like the reference (mlx_mfa/attention.py:2944-2989).
+    """
+    q = _as_tensor(q, "q")
+    k_pages, v_pages = _as_tensor(k_pages, "k_pages"), _as_tensor(v_pages, "v_pages")
+    table = _as_tensor(block_table, "block_table")
+    lens = _as_tensor(seq_lens, "seq_lens")
+    if q.ndim != 4 or k_pages.ndim != 4 or v_pages.ndim != 4:
+        raise ValueError("flash_attention_paged expects q [B,Hq,Nq,D] and pools [num_pages,block_size,Hkv,D].")
+    B, Hq, Nq, D = q.shape
+    Hkv = k_pages.shape[2]
+    if k_pages.shape[1] != block_size or k_pages.shape[3] != D or v_pages.shape != k_pages.shape:
+        raise ValueError("flash_attention_paged: pool shape does not match block_size / head_dim.")
+    if Hq % Hkv != 0:
+        raise ValueError(f"flash_attention GQA: q_heads ({Hq}) must be divisible by kv_heads ({Hkv}).")
+    if table.ndim != 2 or table.shape[0] != B or lens.ndim != 1 or lens.shape[0] != B:
+        raise ValueError("flash_attention_paged: block_table must be [B, max_blocks] and seq_lens [B].")
+    if scale is None:
+        scale = 1.0 / math.sqrt(D)
+    table = table.to(torch.int32).contiguous()
+    lens = lens.to(torch.int32).contiguous()
+    if max_kv_len is None:
+        max_kv_len = int(lens.max().item()) if B > 0 else 0
+    if max_kv_len == 0:
+        z = torch.zeros((B, Hq, Nq, D), dtype=q.dtype, device=q.device)
+        if return_lse:
+            return z, torch.full((B, Hq, Nq), float("-inf"), dtype=torch.float32, device=q.device)
+        return z
+    quant = k_pages.dtype in _KV_CODE
+    if quant:
+        if k_scale is None or v_scale is None:
+            raise ValueError("flash_attention_paged: int8/fp8 pools need k_scale and v_scale.")
+        k_scale = _as_tensor(k_scale, "k_scale").to(torch.float16).contiguous()
+        v_scale = _as_tensor(v_scale, "v_scale").to(torch.float16).contiguous()
+        if tuple(k_scale.shape) != tuple(k_pages.shape[:3]) or tuple(v_scale.shape) != tuple(v_pages.shape[:3]):
+            raise ValueError("flash_attention_paged: scales must be [num_pages, block_size, Hkv].")
+    elif k_pages.dtype != q.dtype:
+        raise ValueError(f"flash_attention_paged: pool dtype {k_pages.dtype} must equal q dtype or be int8/fp8.")
+    if q.dtype not in (torch.float16, torch.bfloat16):
+        raise NotImplementedError("flash_attention_paged takes f16/bf16 queries.")
+    k_pages, v_pages = k_pages.contiguous(), v_pages.contiguous()
+
+    decode_ok = (Hq // Hkv) * Nq <= 8 and D == 128 and block_size == 16
+    if decode_ok:
+        out, lse = _decode_raw(q, k_pages, v_pages, k_scale, v_scale, table, lens, max_kv_len, float(scale),
+                               bool(causal), float(softcap), block_size, return_lse, stream)
+        return (out, lse) if return_lse else out
+    if quant:
+        raise NotImplementedError("quantized pools are served by the decode kernel only ((Hq/Hkv)*Nq <= 8, D=128).")
+    if return_lse:
+        raise NotImplementedError("return_lse on the gather route is not built.")
+    # gather route, as the reference: pages -> contiguous, then exact-length slices per sequence
+    K = paged_kv_gather(k_pages, table, lens, max_kv_len, stream)
+    V = paged_kv_gather(v_pages, table, lens, max_kv_len, stream)
+    lens_host = [int(x) for x in lens.tolist()]
+    outs = []
+    for b in range(B):
+        n = lens_host[b]
+        if n == 0:
+            outs.append(torch.zeros((1, Hq, Nq, D), dtype=q.dtype, device=q.device))
+            continue
+        outs.append(flash_attention(q[b:b + 1], K[b:b + 1, :, :n], V[b:b + 1, :, :n], scale=scale,
+                                    causal=causal, softcap=softcap, stream=stream))
+    return torch.cat(outs, dim=0)
+
+
+def flash_attention_kvcache(
+    q,
+    k_cache,
+    v_cache,
+    *,
+    k_new=None,
+    v_new=None,
+    block_table=None,
+    seq_lens=None,
+    block_size: int = 16,
+    scale: Optional[float] = None,
+    causal: bool = True,
+    softcap: float = 0.0,
+    alibi_slopes=None,
+    window_size: Optional[Tuple[int, int]] = None,
+    rotary_cos=None,
+    rotary_sin=None,
+    cache_seqlens: Union[int, Sequence[int]] = 0,
+    interleaved: bool = True,
+    rotary_dim: Optional[int] = None,
+    cache_batch_idx=None,
+    stream=None,
+    k_scale=None,
+    v_scale=None,
+):
+    """Attention against a KV cache, dense or paged.
+
+    Signature of mlx_mfa.flash_attention_kvcache (mlx_mfa/attention.py:903-931) plus
+    keyword-only ``k_scale``/``v_scale`` for quantized page pools.  Paged mode
+    (``block_table`` given) requires ``seq_lens`` and rejects ``window_size`` and
+    ``alibi_slopes`` with ValueError, as the reference does
+    (mlx_mfa/attention.py:1124-1167).  Dense mode takes caches ``[B, Hkv, S, D]``
+    (or a pool indexed by ``cache_batch_idx``).  Append (``k_new``/``v_new``) and
+    rotary arguments raise NotImplementedError.
+    """
+    q = _as_tensor(q, "q")
+    if q.ndim != 4:
+        raise ValueError(f"flash_attention_kvcache: q must be 4-D [B, H, N, D], got {q.ndim}D.")
+    D = q.shape[-1]
+    if scale is None:
+        scale = 1.0 / math.sqrt(D)
+    has_rope = (rotary_cos is not None) or (rotary_sin is not None)
+    if has_rope and alibi_slopes is not None:
+        raise ValueError("flash_attention_kvcache: rotary_cos/sin and alibi_slopes are mutually exclusive.")
+    if k_new is not None or v_new is not None:
+        if k_new is None or v_new is None:
+            raise ValueError("flash_attention_kvcache: k_new and v_new must both be provided or both be None.")
+        if block_table is not None:
+            raise ValueError(
+                "flash_attention_kvcache: k_new/v_new append is not supported in paged mode.  "
+                "Manage the page pool externally and call without k_new."
+            )
+        if cache_batch_idx is not None:
+            raise ValueError(
+                "flash_attention_kvcache: k_new/v_new append is not supported together with "
+                "cache_batch_idx (continuous-batching pool mode)."
+            )
+        raise NotImplementedError("flash_attention_kvcache: append mode (k_new/v_new) is not built.")
+    if block_table is not None:
+        if seq_lens is None:
+            raise ValueError("flash_attention_kvcache: paged mode requires seq_lens.")
+        if k_cache is None or v_cache is None:
+            raise ValueError(
+                "flash_attention_kvcache: k_cache and v_cache (page pool) must be provided in paged mode."
+            )
+        if window_size is not None:
+            raise ValueError("flash_attention_kvcache: window_size is not supported in paged mode.")
+        if has_rope:
+            if rotary_cos is None or rotary_sin is None:
+                raise ValueError("flash_attention_kvcache: both rotary_cos and rotary_sin must be provided together.")
+            raise NotImplementedError("flash_attention_kvcache: rotary embedding is not built.")
+        if alibi_slopes is not None:
+            raise ValueError("flash_attention_kvcache: alibi_slopes is not supported in paged mode.")
+        # The reference drops softcap here (mlx_mfa/attention.py:1169-1172); it is applied.
+        return flash_attention_paged(q, k_cache, v_cache, block_table, seq_lens, scale=scale, causal=causal,
+                                     block_size=block_size, stream=stream, k_scale=k_scale, v_scale=v_scale,
+                                     softcap=softcap)
+    if k_cache is None or v_cache is None:
+        raise ValueError(
+            "flash_attention_kvcache: k_cache and v_cache must be provided in dense mode "
+            "(use block_table to enable paged mode)."
+        )
+    k_cache, v_cache = _as_tensor(k_cache, "k_cache"), _as_tensor(v_cache, "v_cache")
+    if cache_batch_idx is not None:
+        idx = _as_tensor(cache_batch_idx, "cache_batch_idx").long()
+        k_cache, v_cache = k_cache[idx], v_cache[idx]
+    if has_rope:
+        if rotary_cos is None or rotary_sin is None:
+            raise ValueError("flash_attention_kvcache: both rotary_cos and rotary_sin must be provided together.")
+        raise NotImplementedError("flash_attention_kvcache: rotary embedding is not built.")
+    return flash_attention(q, k_cache, v_cache, scale=scale, causal=causal, softcap=softcap,
+                           alibi_slopes=alibi_slopes, window_size=window_size, stream=stream)
+
+
+# ---------------------------------------------------------------------------
+# capability queries (minimal; mlx_mfa/attention.py:558-709)
+# ---------------------------------------------------------------------------
+def is_mfa_available() -> bool:
+    """True when libb200fa.so is built and a CUDA device of compute capability 10.x is visible."""
+    if not _lib.is_built() or not torch.cuda.is_available():
+        return False
+    return torch.cuda.get_device_capability()[0] == 10
+
+
+def get_device_info() -> dict:
+    info = _lib.DeviceInfo()
+    _lib.check(_lib.load().b200fa_device_info(-1, C.byref(info)), "get_device_info")
+    return {
+        "device_name": info.name.decode(),
+        "compute_capability": (info.cc_major, info.cc_minor),
+        "sm_count": info.sm_count,
+        "smem_per_block_optin": info.smem_per_block_optin,
+        "total_mem": info.total_mem,
+        "has_tcgen05": bool(info.has_tcgen05),
+    }
+
+
+def get_supported_configs() -> dict:
+    return {
+        "head_dims": list(_SUPPORTED_HDIMS),
+        "dtypes": ["float16", "bfloat16", "float32"],
+        "kv_dtypes": ["float16", "bfloat16", "int8", "float8_e4m3fn"],
+        "features": {
+            "causal": True, "gqa": True, "softcap": True, "window_left": True, "return_lse": True,
+            "varlen": True, "paged": True, "quantized_kv": True, "native_backward": True,
+            "alibi": False, "dropout": False, "block_sparse": False, "rope": False,
+        },
+    }

@@ -1,0 +1,365 @@
+// C-ABI of libb200fa.so: argument validation, kernel-family choice and launch.
+// Host-side role of MFAttention::eval_gpu and friends in the reference
+// (csrc/mfa_attention.cpp:47-409, 732-930, 1228-1305, 1355-1496) without their
+// allocation: callers own outputs and workspace.
+#include "../../include/b200fa.h"
+
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+
+#include "common.cuh"
+#include "decode.h"
+#include "launch.h"
+
+namespace {
+
+thread_local char g_err[512] = "";
+
+int32_t fail(int32_t code, const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_err, sizeof(g_err), fmt, ap);
+  va_end(ap);
+  return code;
+}
+
+int32_t cuda_fail(cudaError_t e, const char* what) {
+  return fail(B200FA_ERR_CUDA, "%s: %s", what, cudaGetErrorString(e));
+}
+
+bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+int elem_bytes(int dtype) {
+  switch (dtype) {
+    case B200FA_F16:
+    case B200FA_BF16: return 2;
+    case B200FA_F32: return 4;
+    case B200FA_I8:
+    case B200FA_E4M3: return 1;
+    default: return 0;
+  }
+}
+
+// Resolves strides (all-zero => contiguous [B,H,rows,D]) and checks them.
+bool resolve_strides(const int64_t in[3], int H, int rows, int D, int eb, int64_t out[3]) {
+  if (in[0] == 0 && in[1] == 0 && in[2] == 0) {
+    out[2] = D;
+    out[1] = static_cast<int64_t>(rows) * D;
+    out[0] = static_cast<int64_t>(H) * rows * D;
+    return true;
+  }
+  for (int i = 0; i < 3; ++i) {
+    if (in[i] < 0) return false;
+    if ((in[i] * eb) % 16 != 0) return false;
+    out[i] = in[i];
+  }
+  return out[2] >= D;
+}
+
+int32_t check_common(const b200fa_desc* d, bool varlen) {
+  if (d == nullptr) return fail(B200FA_ERR_INVALID_ARG, "descriptor is null");
+  if (d->dtype != B200FA_F16 && d->dtype != B200FA_BF16 && d->dtype != B200FA_F32)
+    return fail(B200FA_ERR_UNSUPPORTED, "dtype %d: expected f16, bf16 or f32", d->dtype);
+  if (d->D != 64 && d->D != 128)
+    return fail(B200FA_ERR_UNSUPPORTED, "head_dim %d: this build has 64 and 128", d->D);
+  if (d->B < 0 || d->Hq <= 0 || d->Hkv <= 0 || d->N < 0 || d->S < 0)
+    return fail(B200FA_ERR_INVALID_ARG, "negative or zero extent (B=%d Hq=%d Hkv=%d N=%d S=%d)", d->B,
+                d->Hq, d->Hkv, d->N, d->S);
+  if (d->Hq % d->Hkv != 0)
+    return fail(B200FA_ERR_INVALID_ARG, "q_heads (%d) must be divisible by kv_heads (%d)", d->Hq, d->Hkv);
+  if (varlen && d->B != 1) return fail(B200FA_ERR_INVALID_ARG, "varlen expects B == 1, got %d", d->B);
+  if (!(d->scale == d->scale)) return fail(B200FA_ERR_INVALID_ARG, "scale is NaN");
+  if (d->softcap < 0.f) return fail(B200FA_ERR_INVALID_ARG, "softcap must be >= 0");
+  if (d->window_left < -1) return fail(B200FA_ERR_INVALID_ARG, "window_left must be >= -1");
+  return B200FA_OK;
+}
+
+int32_t fill_fwd_params(const b200fa_desc* d, const void* q, const void* k, const void* v, void* out,
+                        float* lse, b200fa::FwdParams* p) {
+  const int eb = elem_bytes(d->dtype);
+  int64_t qs[3], ks[3], vs[3], os[3];
+  if (!resolve_strides(d->q_strides, d->Hq, d->N, d->D, eb, qs) ||
+      !resolve_strides(d->k_strides, d->Hkv, d->S, d->D, eb, ks) ||
+      !resolve_strides(d->v_strides, d->Hkv, d->S, d->D, eb, vs) ||
+      !resolve_strides(d->o_strides, d->Hq, d->N, d->D, eb, os))
+    return fail(B200FA_ERR_INVALID_ARG, "strides must be non-negative, 16-byte multiples, row stride >= D");
+  if (!aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(out))
+    return fail(B200FA_ERR_INVALID_ARG, "q, k, v and out must be 16-byte aligned");
+  memset(p, 0, sizeof(*p));
+  p->q = q; p->k = k; p->v = v; p->o = out; p->lse = lse;
+  p->q_bs = qs[0]; p->q_hs = qs[1]; p->q_rs = qs[2];
+  p->k_bs = ks[0]; p->k_hs = ks[1]; p->k_rs = ks[2];
+  p->v_bs = vs[0]; p->v_hs = vs[1]; p->v_rs = vs[2];
+  p->o_bs = os[0]; p->o_hs = os[1]; p->o_rs = os[2];
+  p->lse_hs = d->N;
+  p->lse_bs = static_cast<int64_t>(d->Hq) * d->N;
+  p->B = d->B; p->Hq = d->Hq; p->Hkv = d->Hkv; p->N = d->N; p->S = d->S;
+  p->gqa = d->Hq / d->Hkv;
+  p->scale = d->scale;
+  p->scale_log2 = d->scale * b200fa::kLog2e;
+  p->softcap = d->softcap;
+  p->causal = d->causal ? 1 : 0;
+  p->window_left = d->window_left;
+  return B200FA_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+const char* b200fa_last_error(void) { return g_err; }
+const char* b200fa_version(void) { return "b200fa 0.1 (sm_100a)"; }
+
+int32_t b200fa_device_info(int32_t device, b200fa_device_info_t* out) {
+  if (out == nullptr) return fail(B200FA_ERR_INVALID_ARG, "out is null");
+  int dev = device;
+  cudaError_t e;
+  if (dev < 0) {
+    e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return cuda_fail(e, "cudaGetDevice");
+  }
+  cudaDeviceProp prop;
+  e = cudaGetDeviceProperties(&prop, dev);
+  if (e != cudaSuccess) return cuda_fail(e, "cudaGetDeviceProperties");
+  memset(out, 0, sizeof(*out));
+  out->cc_major = prop.major;
+  out->cc_minor = prop.minor;
+  out->sm_count = prop.multiProcessorCount;
+  out->smem_per_block_optin = static_cast<int32_t>(prop.sharedMemPerBlockOptin);
+  out->total_mem = static_cast<int64_t>(prop.totalGlobalMem);
+  out->has_tcgen05 = prop.major == 10 ? 1 : 0;
+  strncpy(out->name, prop.name, sizeof(out->name) - 1);
+  return B200FA_OK;
+}
+
+// ---------------------------------------------------------------------------
+// forward
+// ---------------------------------------------------------------------------
+size_t b200fa_fwd_workspace_bytes(const b200fa_desc* d) {
+  (void)d;
+  return 0;
+}
+
+int32_t b200fa_fwd(const b200fa_desc* d, const void* q, const void* k, const void* v, void* out,
+                   float* lse, void* workspace, size_t workspace_bytes, void* stream) {
+  (void)workspace; (void)workspace_bytes;
+  int32_t st = check_common(d, false);
+  if (st != B200FA_OK) return st;
+  if (d->B == 0 || d->N == 0) return B200FA_OK;
+  if (q == nullptr || out == nullptr) return fail(B200FA_ERR_INVALID_ARG, "q or out is null");
+  if (d->S > 0 && (k == nullptr || v == nullptr)) return fail(B200FA_ERR_INVALID_ARG, "k or v is null");
+  b200fa::FwdParams p;
+  st = fill_fwd_params(d, q, d->S > 0 ? k : q, d->S > 0 ? v : q, out, lse, &p);
+  if (st != B200FA_OK) return st;
+  cudaStream_t cs = reinterpret_cast<cudaStream_t>(stream);
+  cudaError_t e;
+  if (d->dtype == B200FA_F32) {
+    e = b200fa::launch_fwd_f32(p, d->D, false, d->B, d->N, cs);
+  } else if (!(d->flags & B200FA_FLAG_FORCE_MMA_SYNC) && b200fa::fwd_sm100_supported(p, d->dtype, d->D)) {
+    e = b200fa::launch_fwd_sm100(p, d->dtype, d->D, cs);
+  } else {
+    e = b200fa::launch_fwd_mma(p, d->dtype, d->D, false, d->B, d->N, cs);
+  }
+  if (e != cudaSuccess) return cuda_fail(e, "forward launch");
+  return B200FA_OK;
+}
+
+size_t b200fa_fwd_varlen_workspace_bytes(const b200fa_desc* d, int32_t num_seqs, int32_t max_seqlen_q,
+                                         int32_t max_seqlen_k) {
+  (void)d; (void)num_seqs; (void)max_seqlen_q; (void)max_seqlen_k;
+  return 0;
+}
+
+int32_t b200fa_fwd_varlen(const b200fa_desc* d, const void* q, const void* k, const void* v,
+                          const int32_t* cu_seqlens_q, const int32_t* cu_seqlens_k, int32_t num_seqs,
+                          int32_t max_seqlen_q, int32_t max_seqlen_k, void* out, float* lse,
+                          void* workspace, size_t workspace_bytes, void* stream) {
+  (void)workspace; (void)workspace_bytes; (void)max_seqlen_k;
+  int32_t st = check_common(d, true);
+  if (st != B200FA_OK) return st;
+  if (num_seqs < 0 || max_seqlen_q < 0) return fail(B200FA_ERR_INVALID_ARG, "negative num_seqs/max_seqlen");
+  if (num_seqs == 0 || d->N == 0 || max_seqlen_q == 0) return B200FA_OK;
+  if (q == nullptr || k == nullptr || v == nullptr || out == nullptr || cu_seqlens_q == nullptr ||
+      cu_seqlens_k == nullptr)
+    return fail(B200FA_ERR_INVALID_ARG, "null tensor pointer");
+  b200fa::FwdParams p;
+  st = fill_fwd_params(d, q, k, v, out, lse, &p);
+  if (st != B200FA_OK) return st;
+  p.cu_q = cu_seqlens_q;
+  p.cu_k = cu_seqlens_k;
+  cudaStream_t cs = reinterpret_cast<cudaStream_t>(stream);
+  cudaError_t e = d->dtype == B200FA_F32
+                      ? b200fa::launch_fwd_f32(p, d->D, true, num_seqs, max_seqlen_q, cs)
+                      : b200fa::launch_fwd_mma(p, d->dtype, d->D, true, num_seqs, max_seqlen_q, cs);
+  if (e != cudaSuccess) return cuda_fail(e, "varlen forward launch");
+  return B200FA_OK;
+}
+
+// ---------------------------------------------------------------------------
+// backward
+// ---------------------------------------------------------------------------
+static int32_t bwd_common(const b200fa_desc* d, const void* q, const void* k, const void* v,
+                          const void* out, const float* lse, const void* dout, void* dq, void* dk,
+                          void* dv, const int32_t* cu_q, const int32_t* cu_k, int nbatch, int max_q,
+                          int max_k, void* workspace, size_t workspace_bytes, void* stream) {
+  const bool varlen = cu_q != nullptr;
+  int32_t st = check_common(d, varlen);
+  if (st != B200FA_OK) return st;
+  if (d->dtype == B200FA_F32)
+    return fail(B200FA_ERR_UNSUPPORTED, "backward is built for f16 and bf16 (the reference's STEEL backward, "
+                                        "mlx_mfa/attention.py:2008-2012, takes the same)");
+  if (d->softcap != 0.f || d->window_left >= 0)
+    return fail(B200FA_ERR_UNSUPPORTED, "backward with softcap or window is not built");
+  if (d->B == 0 || d->N == 0 || nbatch == 0) return B200FA_OK;
+  if (!q || !k || !v || !out || !lse || !dout || !dq || !dk || !dv)
+    return fail(B200FA_ERR_INVALID_ARG, "null tensor pointer");
+  const size_t need = b200fa::bwd_workspace_bytes(d->B, d->Hq, d->N, d->D);
+  if (workspace == nullptr || workspace_bytes < need)
+    return fail(B200FA_ERR_WORKSPACE, "backward needs %zu workspace bytes, got %zu", need, workspace_bytes);
+  if (!aligned16(workspace)) return fail(B200FA_ERR_INVALID_ARG, "workspace must be 16-byte aligned");
+  b200fa::FwdParams f;
+  st = fill_fwd_params(d, q, k, v, const_cast<void*>(out), nullptr, &f);
+  if (st != B200FA_OK) return st;
+  if (!aligned16(dout) || !aligned16(dq) || !aligned16(dk) || !aligned16(dv))
+    return fail(B200FA_ERR_INVALID_ARG, "dout, dq, dk, dv must be 16-byte aligned");
+  b200fa::BwdParams p;
+  memset(&p, 0, sizeof(p));
+  p.q = q; p.k = k; p.v = v; p.o = out; p.dout = dout; p.lse = lse;
+  p.dq = dq; p.dk = dk; p.dv = dv;
+  p.q_bs = f.q_bs; p.q_hs = f.q_hs; p.q_rs = f.q_rs;
+  p.k_bs = f.k_bs; p.k_hs = f.k_hs; p.k_rs = f.k_rs;
+  p.v_bs = f.v_bs; p.v_hs = f.v_hs; p.v_rs = f.v_rs;
+  p.o_bs = f.o_bs; p.o_hs = f.o_hs; p.o_rs = f.o_rs;
+  p.dq_rs = d->D; p.dq_hs = static_cast<int64_t>(d->N) * d->D; p.dq_bs = p.dq_hs * d->Hq;
+  p.dk_rs = d->D; p.dk_hs = static_cast<int64_t>(d->S) * d->D; p.dk_bs = p.dk_hs * d->Hkv;
+  p.lse_hs = f.lse_hs; p.lse_bs = f.lse_bs;
+  p.B = d->B; p.Hq = d->Hq; p.Hkv = d->Hkv; p.N = d->N; p.S = d->S;
+  p.gqa = f.gqa; p.scale = d->scale; p.scale_log2 = f.scale_log2; p.causal = f.causal;
+  p.cu_q = cu_q; p.cu_k = cu_k;
+  cudaError_t e = b200fa::launch_bwd(p, d->dtype, d->D, varlen, nbatch, max_q, max_k, workspace,
+                                     reinterpret_cast<cudaStream_t>(stream));
+  if (e != cudaSuccess) return cuda_fail(e, "backward launch");
+  return B200FA_OK;
+}
+
+size_t b200fa_bwd_workspace_bytes(const b200fa_desc* d) {
+  if (d == nullptr) return 0;
+  return b200fa::bwd_workspace_bytes(d->B, d->Hq, d->N, d->D);
+}
+
+int32_t b200fa_bwd(const b200fa_desc* d, const void* q, const void* k, const void* v, const void* out,
+                   const float* lse, const void* dout, void* dq, void* dk, void* dv, void* workspace,
+                   size_t workspace_bytes, void* stream) {
+  if (d == nullptr) return fail(B200FA_ERR_INVALID_ARG, "descriptor is null");
+  return bwd_common(d, q, k, v, out, lse, dout, dq, dk, dv, nullptr, nullptr, d->B, d->N, d->S, workspace,
+                    workspace_bytes, stream);
+}
+
+size_t b200fa_bwd_varlen_workspace_bytes(const b200fa_desc* d, int32_t num_seqs, int32_t max_seqlen_q,
+                                         int32_t max_seqlen_k) {
+  (void)num_seqs; (void)max_seqlen_q; (void)max_seqlen_k;
+  if (d == nullptr) return 0;
+  return b200fa::bwd_workspace_bytes(d->B, d->Hq, d->N, d->D);
+}
+
+int32_t b200fa_bwd_varlen(const b200fa_desc* d, const void* q, const void* k, const void* v,
+                          const void* out, const float* lse, const void* dout,
+                          const int32_t* cu_seqlens_q, const int32_t* cu_seqlens_k, int32_t num_seqs,
+                          int32_t max_seqlen_q, int32_t max_seqlen_k, void* dq, void* dk, void* dv,
+                          void* workspace, size_t workspace_bytes, void* stream) {
+  if (d == nullptr) return fail(B200FA_ERR_INVALID_ARG, "descriptor is null");
+  if (cu_seqlens_q == nullptr || cu_seqlens_k == nullptr)
+    return fail(B200FA_ERR_INVALID_ARG, "cu_seqlens is null");
+  if (num_seqs < 0 || max_seqlen_q < 0 || max_seqlen_k < 0)
+    return fail(B200FA_ERR_INVALID_ARG, "negative num_seqs/max_seqlen");
+  return bwd_common(d, q, k, v, out, lse, dout, dq, dk, dv, cu_seqlens_q, cu_seqlens_k, num_seqs,
+                    max_seqlen_q, max_seqlen_k, workspace, workspace_bytes, stream);
+}
+
+// ---------------------------------------------------------------------------
+// paged KV: gather and decode
+// ---------------------------------------------------------------------------
+int32_t b200fa_paged_kv_gather(const void* pool, const int32_t* block_table, const int32_t* seq_lens,
+                               int32_t B, int32_t H, int32_t D, int32_t eb, int32_t block_size,
+                               int32_t max_blocks, int32_t max_kv_len, void* out, void* stream) {
+  if (B < 0 || H <= 0 || D <= 0 || block_size <= 0 || max_blocks < 0 || max_kv_len < 0)
+    return fail(B200FA_ERR_INVALID_ARG, "bad extent");
+  if (eb != 1 && eb != 2 && eb != 4) return fail(B200FA_ERR_INVALID_ARG, "elem_bytes must be 1, 2 or 4");
+  if ((D * eb) % 16 != 0) return fail(B200FA_ERR_INVALID_ARG, "D*elem_bytes must be a multiple of 16");
+  if (B == 0 || max_kv_len == 0) return B200FA_OK;
+  if (!pool || !block_table || !seq_lens || !out) return fail(B200FA_ERR_INVALID_ARG, "null pointer");
+  if (!aligned16(pool) || !aligned16(out)) return fail(B200FA_ERR_INVALID_ARG, "pool/out must be 16-byte aligned");
+  if (static_cast<int64_t>(max_blocks) * block_size < max_kv_len)
+    return fail(B200FA_ERR_INVALID_ARG, "max_kv_len %d exceeds max_blocks*block_size", max_kv_len);
+  cudaError_t e = b200fa::launch_paged_gather(pool, block_table, seq_lens, B, H, D, eb, block_size,
+                                              max_blocks, max_kv_len, out,
+                                              reinterpret_cast<cudaStream_t>(stream));
+  if (e != cudaSuccess) return cuda_fail(e, "gather launch");
+  return B200FA_OK;
+}
+
+static int32_t decode_check(const b200fa_desc* d) {
+  if (d == nullptr) return fail(B200FA_ERR_INVALID_ARG, "descriptor is null");
+  if (d->dtype != B200FA_F16 && d->dtype != B200FA_BF16)
+    return fail(B200FA_ERR_UNSUPPORTED, "paged decode takes f16 or bf16 queries");
+  if (d->D != 128) return fail(B200FA_ERR_UNSUPPORTED, "paged decode is built for head_dim 128");
+  if (d->B < 0 || d->Hq <= 0 || d->Hkv <= 0 || d->N <= 0)
+    return fail(B200FA_ERR_INVALID_ARG, "bad extent");
+  if (d->Hq % d->Hkv != 0)
+    return fail(B200FA_ERR_INVALID_ARG, "q_heads (%d) must be divisible by kv_heads (%d)", d->Hq, d->Hkv);
+  if ((d->Hq / d->Hkv) * d->N > 8)
+    return fail(B200FA_ERR_UNSUPPORTED, "paged decode takes (Hq/Hkv)*N <= 8 query rows per kv head");
+  const int kv = d->kv_dtype;
+  if (!(kv == d->dtype || kv == B200FA_I8 || kv == B200FA_E4M3))
+    return fail(B200FA_ERR_UNSUPPORTED, "kv_dtype must equal dtype or be int8 / e4m3");
+  if (d->window_left >= 0) return fail(B200FA_ERR_UNSUPPORTED, "window is not supported in paged mode");
+  return B200FA_OK;
+}
+
+size_t b200fa_decode_paged_workspace_bytes(const b200fa_desc* d, int32_t max_kv_len) {
+  if (d == nullptr) return 0;
+  return b200fa::decode_workspace_bytes(d->B, d->Hq, d->Hkv, d->N, d->D, max_kv_len, d->num_splits);
+}
+
+int32_t b200fa_decode_paged(const b200fa_desc* d, const void* q, const void* k_pool, const void* v_pool,
+                            const void* k_scale, const void* v_scale, const int32_t* block_table,
+                            const int32_t* seq_lens, int32_t num_pages, int32_t block_size,
+                            int32_t max_blocks, int32_t max_kv_len, void* out, float* lse,
+                            void* workspace, size_t workspace_bytes, void* stream) {
+  int32_t st = decode_check(d);
+  if (st != B200FA_OK) return st;
+  if (block_size != 16) return fail(B200FA_ERR_UNSUPPORTED, "paged decode is built for block_size 16");
+  if (num_pages <= 0 || max_blocks <= 0 || max_kv_len < 0) return fail(B200FA_ERR_INVALID_ARG, "bad extent");
+  if (d->B == 0) return B200FA_OK;
+  if (!q || !k_pool || !v_pool || !block_table || !seq_lens || !out)
+    return fail(B200FA_ERR_INVALID_ARG, "null tensor pointer");
+  const bool quant = d->kv_dtype == B200FA_I8 || d->kv_dtype == B200FA_E4M3;
+  if (quant && (!k_scale || !v_scale)) return fail(B200FA_ERR_INVALID_ARG, "quantized pools need k_scale and v_scale");
+  if (!aligned16(q) || !aligned16(k_pool) || !aligned16(v_pool) || !aligned16(out) ||
+      (quant && (!aligned16(k_scale) || !aligned16(v_scale))))
+    return fail(B200FA_ERR_INVALID_ARG, "tensors must be 16-byte aligned");
+  if (static_cast<int64_t>(max_blocks) * block_size < max_kv_len)
+    return fail(B200FA_ERR_INVALID_ARG, "max_kv_len %d exceeds max_blocks*block_size", max_kv_len);
+  const size_t need = b200fa::decode_workspace_bytes(d->B, d->Hq, d->Hkv, d->N, d->D, max_kv_len, d->num_splits);
+  if (workspace == nullptr || workspace_bytes < need)
+    return fail(B200FA_ERR_WORKSPACE, "decode needs %zu workspace bytes, got %zu", need, workspace_bytes);
+  if (!aligned16(workspace)) return fail(B200FA_ERR_INVALID_ARG, "workspace must be 16-byte aligned");
+  b200fa::DecodeParams p;
+  memset(&p, 0, sizeof(p));
+  p.q = q; p.k_pool = k_pool; p.v_pool = v_pool; p.k_scale = k_scale; p.v_scale = v_scale;
+  p.block_table = block_table; p.seq_lens = seq_lens; p.out = out; p.lse = lse;
+  p.workspace = workspace;
+  p.B = d->B; p.Hq = d->Hq; p.Hkv = d->Hkv; p.Nq = d->N; p.D = d->D;
+  p.num_pages = num_pages; p.block_size = block_size; p.max_blocks = max_blocks; p.max_kv_len = max_kv_len;
+  p.q_dtype = d->dtype; p.kv_dtype = d->kv_dtype;
+  p.scale = d->scale; p.softcap = d->softcap; p.causal = d->causal ? 1 : 0;
+  p.num_splits = d->num_splits;
+  char msg[256] = "";
+  cudaError_t e = b200fa::launch_decode_paged(p, reinterpret_cast<cudaStream_t>(stream), msg, sizeof(msg));
+  if (e == cudaErrorNotSupported) return fail(B200FA_ERR_UNSUPPORTED, "decode: %s", msg);
+  if (e != cudaSuccess) return fail(B200FA_ERR_CUDA, "decode launch: %s %s", cudaGetErrorString(e), msg);
+  return B200FA_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,34 @@
+// Internal launcher declarations: one per kernel family.  The C-ABI layer
+// (api.cu) validates arguments, picks a family and calls these.  This table of
+// ahead-of-time template instances plays the role of the reference's run-time
+// shader cache keyed by KernelKey (csrc/shader_cache.hpp:29-77).
+#pragma once
+#include <cuda_runtime.h>
+#include <stddef.h>
+#include <stdint.h>
+
+namespace b200fa {
+
+struct FwdParams;
+struct BwdParams;
+
+// dtype codes as in b200fa.h: 0 f16, 1 bf16, 2 f32.
+cudaError_t launch_fwd_mma(const FwdParams& p, int dtype, int D, bool varlen, int nbatch, int max_q,
+                           cudaStream_t stream);
+cudaError_t launch_fwd_f32(const FwdParams& p, int D, bool varlen, int nbatch, int max_q,
+                           cudaStream_t stream);
+
+// tcgen05 / TMEM / TMA forward (dense layout, D = 128, 16-bit).  Returns
+// cudaErrorNotSupported when the shape is outside what the kernel takes.
+bool fwd_sm100_supported(const FwdParams& p, int dtype, int D);
+cudaError_t launch_fwd_sm100(const FwdParams& p, int dtype, int D, cudaStream_t stream);
+
+cudaError_t launch_paged_gather(const void* pool, const int32_t* block_table, const int32_t* seq_lens,
+                                int B, int H, int D, int elem_bytes, int block_size, int max_blocks,
+                                int max_kv_len, void* out, cudaStream_t stream);
+
+size_t bwd_workspace_bytes(int B, int Hq, int N_total, int D);
+cudaError_t launch_bwd(const BwdParams& p, int dtype, int D, bool varlen, int nbatch, int max_q,
+                       int max_k, void* workspace, cudaStream_t stream);
+
+}  // namespace b200fa

@@ -1,0 +1,57 @@
+// Page gather: pool [num_pages, block_size, H, D] -> out [B, H, max_kv_len, D].
+// out[b,h,t,:] = pool[block_table[b, t / block_size], t % block_size, h, :] when
+// t < seq_lens[b] and the table entry is non-negative, else zero.  A bit-exact
+// copy with 64-bit offsets; same contract as the reference's paged_kv_gather
+// (csrc/mfa_paged_gather.cpp:44-80 kernel, 89-129 CPU loop).
+#include "common.cuh"
+#include "launch.h"
+
+namespace b200fa {
+
+namespace {
+
+__global__ void __launch_bounds__(256) paged_kv_gather_kernel(
+    const uint4* __restrict__ pool, const int32_t* __restrict__ block_table,
+    const int32_t* __restrict__ seq_lens, int H, int chunks_per_row /* D*elem_bytes/16 */,
+    int block_size, int max_blocks, int max_kv_len, long long total_chunks, uint4* __restrict__ out) {
+  const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+  for (long long idx = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; idx < total_chunks;
+       idx += stride) {
+    // idx = ((b*H + h)*max_kv_len + t)*chunks_per_row + c
+    const int c = static_cast<int>(idx % chunks_per_row);
+    long long rem = idx / chunks_per_row;
+    const int t = static_cast<int>(rem % max_kv_len);
+    rem /= max_kv_len;
+    const int h = static_cast<int>(rem % H);
+    const int b = static_cast<int>(rem / H);
+    uint4 val = make_uint4(0u, 0u, 0u, 0u);
+    if (t < seq_lens[b]) {
+      const int page = block_table[static_cast<long long>(b) * max_blocks + t / block_size];
+      if (page >= 0) {
+        const long long src =
+            ((static_cast<long long>(page) * block_size + (t % block_size)) * H + h) * chunks_per_row + c;
+        val = pool[src];
+      }
+    }
+    out[idx] = val;
+  }
+}
+
+}  // namespace
+
+cudaError_t launch_paged_gather(const void* pool, const int32_t* block_table, const int32_t* seq_lens,
+                                int B, int H, int D, int elem_bytes, int block_size, int max_blocks,
+                                int max_kv_len, void* out, cudaStream_t stream) {
+  const int cpr = D * elem_bytes / 16;
+  const long long total = static_cast<long long>(B) * H * max_kv_len * cpr;
+  if (total == 0) return cudaSuccess;
+  long long blocks = (total + 255) / 256;
+  const long long cap = 148LL * 32;
+  if (blocks > cap) blocks = cap;
+  paged_kv_gather_kernel<<<static_cast<unsigned>(blocks), 256, 0, stream>>>(
+      reinterpret_cast<const uint4*>(pool), block_table, seq_lens, H, cpr, block_size, max_blocks,
+      max_kv_len, total, reinterpret_cast<uint4*>(out));
+  return cudaGetLastError();
+}
+
+}  // namespace b200fa

@@ -1,0 +1,192 @@
+"""GPU parity tests of the dense forward against the CPU oracle (2e-2 for f16/bf16,
+1e-5 for float32).  Cases follow the reference's own test list
+(tests/test_attention.py in the reference: remainders 509-520 and 5632-5651,
+cross-attention 522-538, GQA ratios 830-881, softcap 2855-2932, window 4829-4886,
+decode rows 1472-1598)."""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+import mlx_flashattention_steel_b200 as fa
+from mlx_flashattention_steel_b200 import _lib, attention as fa_attn
+from oracle import sdpa_oracle as orc
+
+from .util import LSE_TOL, assert_close, randn
+
+pytestmark = pytest.mark.gpu
+
+DT = {"f16": torch.float16, "bf16": torch.bfloat16, "f32": torch.float32}
+
+
+def _run(dev, dtype, B, Hq, Hkv, N, S, D, seed, **kw):
+    q = randn((B, Hq, N, D), dtype, seed)
+    k = randn((B, Hkv, S, D), dtype, seed + 1)
+    v = randn((B, Hkv, S, D), dtype, seed + 2)
+    ws = kw.pop("window_size", None)
+    out, lse = fa.flash_attention(q.to(dev), k.to(dev), v.to(dev), return_lse=True, window_size=ws, **kw)
+    torch.cuda.synchronize()
+    wl = -1 if ws is None else max(ws[0], 0)
+    O, L, _ = orc.sdpa(q, k, v, scale=kw.get("scale"), causal=kw.get("causal", False),
+                       softcap=kw.get("softcap", 0.0), window_left=wl)
+    assert out.dtype == dtype and out.shape == q.shape and lse.dtype == torch.float32
+    e = assert_close(out, O, dtype)
+    assert_close(lse, L, dtype, "lse", LSE_TOL[dtype])
+    return e
+
+
+@pytest.mark.parametrize("dt", ["f16", "bf16", "f32"])
+@pytest.mark.parametrize("D", [64, 128])
+@pytest.mark.parametrize("causal", [False, True])
+def test_basic(dev, dt, D, causal):
+    _run(dev, DT[dt], 2, 4, 4, 256, 256, D, 10, causal=causal)
+
+
+@pytest.mark.parametrize("dt", ["bf16", "f32"])
+@pytest.mark.parametrize("N,S", [(37, 40), (1, 257), (4, 300), (5, 256), (129, 129), (200, 77), (64, 1)])
+@pytest.mark.parametrize("causal", [False, True])
+def test_remainders_and_cross_attention(dev, dt, N, S, causal):
+    if causal and N > S:
+        pytest.skip("rows without visible keys are covered separately")
+    _run(dev, DT[dt], 1, 2, 2, N, S, 128, 20, causal=causal)
+
+
+@pytest.mark.parametrize("dt", ["f16", "f32"])
+@pytest.mark.parametrize("ratio", [2, 4, 8])
+def test_gqa(dev, dt, ratio):
+    _run(dev, DT[dt], 2, 8, 8 // ratio, 150, 150, 64, 30, causal=True)
+
+
+def test_mqa(dev):
+    _run(dev, torch.bfloat16, 1, 8, 1, 300, 300, 128, 31, causal=True)
+
+
+@pytest.mark.parametrize("dt", ["f16", "bf16", "f32"])
+@pytest.mark.parametrize("cap", [5.0, 50.0])
+def test_softcap(dev, dt, cap):
+    _run(dev, DT[dt], 1, 4, 2, 200, 200, 128, 40, causal=True, softcap=cap)
+
+
+def test_softcap_zero_is_bit_identical(dev):
+    # tests/test_attention.py:2869-2886
+    q, k, v = (randn((1, 2, 100, 64), torch.float16, 50 + i).to(dev) for i in range(3))
+    a = fa.flash_attention(q, k, v, causal=True, softcap=0.0)
+    b = fa.flash_attention(q, k, v, causal=True)
+    assert torch.equal(a, b)
+
+
+@pytest.mark.parametrize("dt", ["f16", "f32"])
+@pytest.mark.parametrize("causal", [False, True])
+@pytest.mark.parametrize("left", [0, 7, 64, 300])
+def test_window(dev, dt, causal, left):
+    _run(dev, DT[dt], 1, 2, 2, 333, 333, 128, 60, causal=causal, window_size=(left, 0))
+
+
+def test_window_cross_lengths(dev):
+    _run(dev, torch.bfloat16, 1, 2, 1, 100, 400, 64, 61, causal=True, window_size=(50, -1))
+
+
+def test_window_none_is_bit_identical(dev):
+    # tests/test_attention.py:4870-4886
+    q, k, v = (randn((1, 2, 100, 64), torch.bfloat16, 70 + i).to(dev) for i in range(3))
+    a = fa.flash_attention(q, k, v, causal=True, window_size=None)
+    b = fa.flash_attention(q, k, v, causal=True)
+    assert torch.equal(a, b)
+
+
+def test_decode_row_causal_equals_noncausal(dev):
+    # tests/test_attention.py:1472-1487
+    q = randn((2, 4, 1, 128), torch.float16, 80).to(dev)
+    k = randn((2, 4, 500, 128), torch.float16, 81).to(dev)
+    v = randn((2, 4, 500, 128), torch.float16, 82).to(dev)
+    assert torch.equal(fa.flash_attention(q, k, v, causal=True), fa.flash_attention(q, k, v, causal=False))
+
+
+def test_rows_without_visible_keys_are_zero(dev):
+    # N > S with causal: the first N - S rows see nothing -> O = 0, L = -inf
+    q = randn((1, 2, 40, 64), torch.float16, 90).to(dev)
+    k = randn((1, 2, 24, 64), torch.float16, 91).to(dev)
+    v = randn((1, 2, 24, 64), torch.float16, 92).to(dev)
+    out, lse = fa.flash_attention(q, k, v, causal=True, return_lse=True)
+    assert not out[:, :, :16].any()
+    assert torch.isinf(lse[:, :, :16]).all() and (lse[:, :, :16] < 0).all()
+    O, L, _ = orc.sdpa(q.cpu(), k.cpu(), v.cpu(), causal=True)
+    assert_close(out, O, torch.float16)
+
+
+def test_strided_views_and_scale(dev):
+    # head-sliced views (the (batch, kv-head) shards of a larger tensor) run without a copy
+    full_q = randn((2, 8, 96, 128), torch.bfloat16, 100)
+    full_k = randn((2, 4, 96, 128), torch.bfloat16, 101)
+    full_v = randn((2, 4, 96, 128), torch.bfloat16, 102)
+    q, k, v = full_q[:, 2:6], full_k[:, 1:3], full_v[:, 1:3]
+    out = fa.flash_attention(q.to(dev)[:, :], k.to(dev), v.to(dev), scale=0.05, causal=True)
+    gq, gk, gv = full_q.to(dev)[:, 2:6], full_k.to(dev)[:, 1:3], full_v.to(dev)[:, 1:3]
+    out2 = fa.flash_attention(gq, gk, gv, scale=0.05, causal=True)
+    O, _, _ = orc.sdpa(q, k, v, scale=0.05, causal=True)
+    assert_close(out, O, torch.bfloat16)
+    assert torch.equal(out, out2)
+
+
+def test_golden_vectors(dev):
+    import os
+
+    z = np.load(os.path.join(os.path.dirname(__file__), "golden", "sdpa_golden.npz"))
+    q, k, v = (torch.from_numpy(z[f"dense_causal_gqa_{t}"]) for t in "qkv")
+    out, lse = fa.flash_attention(q.to(dev), k.to(dev), v.to(dev), causal=True, return_lse=True)
+    assert_close(out, torch.from_numpy(z["dense_causal_gqa_o"]), torch.float32)
+    assert_close(lse, torch.from_numpy(z["dense_causal_gqa_lse"]), torch.float32, "lse", 2e-5)
+    q, k, v = (torch.from_numpy(z[f"softcap_window_{t}"]) for t in "qkv")
+    for dtype in (torch.float32, torch.bfloat16):
+        out = fa.flash_attention(q.to(dev, dtype), k.to(dev, dtype), v.to(dev, dtype), causal=True,
+                                 softcap=30.0, window_size=(17, 0))
+        if dtype == torch.float32:
+            assert_close(out, torch.from_numpy(z["softcap_window_o"]), dtype)
+        else:
+            O, _, _ = orc.sdpa(q.to(dtype), k.to(dtype), v.to(dtype), causal=True, softcap=30.0, window_left=17)
+            assert_close(out, O, dtype)
+
+
+def test_config1_full_size_fp32(dev):
+    """B=1, H=8, N=S=1024, D=128, float32, causal: the reference's CPU-runnable config."""
+    _run(dev, torch.float32, 1, 8, 8, 1024, 1024, 128, 1, causal=True)
+
+
+def test_config2_shaped_slice_bf16(dev):
+    """GQA causal bf16 with softcap 50 and lse, one batch and two kv groups of config 2
+    at a reduced length the oracle finishes in seconds."""
+    _run(dev, torch.bfloat16, 1, 8, 2, 2048, 2048, 128, 2, causal=True, softcap=50.0)
+
+
+def test_portable_and_tcgen05_kernels_agree(dev):
+    """The mma.sync kernel (forced) and the default choice agree within tolerance."""
+    q = randn((1, 8, 1024, 128), torch.bfloat16, 110).to(dev)
+    k = randn((1, 2, 1024, 128), torch.bfloat16, 111).to(dev)
+    v = randn((1, 2, 1024, 128), torch.bfloat16, 112).to(dev)
+    a, la = fa.flash_attention(q, k, v, causal=True, return_lse=True)
+    old = fa_attn._set_force_flags(_lib.FLAG_FORCE_MMA_SYNC)
+    try:
+        b, lb = fa.flash_attention(q, k, v, causal=True, return_lse=True)
+    finally:
+        fa_attn._set_force_flags(old)
+    assert float((a.float() - b.float()).abs().max()) <= 2e-2
+    assert float((la - lb).abs().max()) <= 2e-2
+
+
+def test_full_size_linearity_in_v(dev):
+    """Size-independent property at config-2 scale (no oracle): attention is linear in V,
+    so O(v1 + v2) = O(v1) + O(v2) up to bf16 rounding; and rows of V equal to a constant c
+    give O = c exactly up to rounding."""
+    B, Hq, Hkv, N, D = 1, 8, 2, 8192, 128
+    q = randn((B, Hq, N, D), torch.bfloat16, 120).to(dev)
+    k = randn((B, Hkv, N, D), torch.bfloat16, 121).to(dev)
+    v1 = randn((B, Hkv, N, D), torch.bfloat16, 122).to(dev)
+    v2 = randn((B, Hkv, N, D), torch.bfloat16, 123).to(dev)
+    o1 = fa.flash_attention(q, k, v1, causal=True, softcap=50.0).float()
+    o2 = fa.flash_attention(q, k, v2, causal=True, softcap=50.0).float()
+    o12 = fa.flash_attention(q, k, (v1.float() + v2.float()).to(torch.bfloat16), causal=True, softcap=50.0).float()
+    assert float((o12 - (o1 + o2)).abs().max()) <= 4e-2
+    ones = torch.full((B, Hkv, N, D), 0.75, dtype=torch.bfloat16, device=dev)
+    oc = fa.flash_attention(q, k, ones, causal=True).float()
+    assert float((oc - 0.75).abs().max()) <= 1e-2

@@ -1,0 +1,376 @@
+#!/usr/bin/env python
+"""Headline benchmark: causal GQA prefill attention TFLOP/s (causal-adjusted) on B200,
+with the paged int8-KV decode GB/s reported beside it.
+
+    python bench.py --gpus N --steps K --warmup W [--impl reference]
+
+N = 1 workload ("config 2"): B=4, Hq=32, Hkv=8, N=S=8192, D=128, bf16, causal,
+softcap=50, return_lse; synthetic N(0,1) inputs from a fixed seed.  With N > 1 (one
+process per GPU under torchrun) every rank runs its own batch of 4 — (batch, kv-head)
+shards need no collective — so scaling is weak and `value` is the sum over ranks.
+
+One "step" = one forward over the batch.  `value` is timed with CUDA events on the
+launching stream with inputs resident in HBM (inputs are 403 MB > the 126 MB L2, so no
+explicit flush is needed); `e2e` is the same step through the public Python API with
+pinned host buffers, host->device and device->host copies inside the timed region.
+`--impl reference` times the CPU restatement of the reference's SDPA fallback (the
+reference's own CPU arithmetic lives in MLX, which cannot be installed here).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import math
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+import torch  # noqa: E402
+
+METRIC = "prefill attn TFLOP/s (causal-adj)"
+C2 = dict(B=4, Hq=32, Hkv=8, N=8192, S=8192, D=128, softcap=50.0)
+C4 = dict(B=128, Hq=32, Hkv=8, D=128, block_size=16, lo=512, hi=32768)
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        p = json.load(open(path))
+        return dict(hbm=p["hbm_gbs"], tf=p["bf16_tflops"], tf_sustained=p.get("bf16_tflops_sustained"), src="measured")
+    return dict(hbm=6650.0, tf=1590.0, tf_sustained=1400.0, src="fallback")
+
+
+def causal_pairs(N, S):
+    off = S - N
+    return sum(min(S, i + off + 1) for i in range(N)) if N != S else N * (N + 1) // 2
+
+
+def prefill_flops(cfg, batch=None):
+    b = cfg["B"] if batch is None else batch
+    return 4.0 * b * cfg["Hq"] * cfg["D"] * causal_pairs(cfg["N"], cfg["S"])
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons with nvidia-smi while the timed region runs."""
+
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+         "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index = index
+        self.rows = []
+        self.proc = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100", "-i", str(self.index)],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.t = threading.Thread(target=self._read, daemon=True)
+            self.t.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append((time.time(), [x.strip() for x in line.split(",")]))
+
+    def stop(self, t0, t1):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        rows = [r for (t, r) in self.rows if t0 - 0.05 <= t <= t1 + 0.15 and len(r) >= 9] or [r for _, r in self.rows if len(r) >= 9]
+        if not rows:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"]}
+        sm = [float(r[1]) for r in rows]
+        reasons = set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for r in rows:
+            for n, v in zip(names, r[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        return {"sm_mhz": statistics.median(sm), "sm_max_mhz": float(rows[0][2]), "reasons": sorted(reasons),
+                "samples": len(rows), "power_w_max": max(float(r[3]) for r in rows)}
+
+
+def make_prefill_inputs(cfg, device, seed):
+    g = torch.Generator(device="cpu").manual_seed(seed)
+    B, Hq, Hkv, N, S, D = (cfg[k] for k in ("B", "Hq", "Hkv", "N", "S", "D"))
+    # generated on the device for speed; the distribution (N(0,1), bf16) is what the config names
+    gd = torch.Generator(device=device).manual_seed(seed)
+    q = torch.randn((B, Hq, N, D), generator=gd, device=device, dtype=torch.float32).to(torch.bfloat16)
+    k = torch.randn((B, Hkv, S, D), generator=gd, device=device, dtype=torch.float32).to(torch.bfloat16)
+    v = torch.randn((B, Hkv, S, D), generator=gd, device=device, dtype=torch.float32).to(torch.bfloat16)
+    del g
+    return q, k, v
+
+
+def cpu_prefill_sample(cfg, seed, repeats=1):
+    """Times the oracle (CPU restatement of the reference's softcap SDPA fallback) on one
+    (batch, kv-group) slice of the workload: 1 batch x Hq/Hkv query heads x 1 kv head."""
+    from oracle import sdpa_oracle as orc
+
+    g = cfg["Hq"] // cfg["Hkv"]
+    gen = torch.Generator().manual_seed(seed)
+    q = torch.randn((1, g, cfg["N"], cfg["D"]), generator=gen)
+    k = torch.randn((1, 1, cfg["S"], cfg["D"]), generator=gen)
+    v = torch.randn((1, 1, cfg["S"], cfg["D"]), generator=gen)
+    best = float("inf")
+    for _ in range(repeats):
+        t0 = time.perf_counter()
+        orc.sdpa(q, k, v, causal=True, softcap=cfg["softcap"], faithful=True, row_block=512)
+        best = min(best, time.perf_counter() - t0)
+    flops = 4.0 * g * cfg["D"] * causal_pairs(cfg["N"], cfg["S"])
+    return flops / best / 1e12, best, f"1 batch x 1 kv-head group ({g} q-heads) of the workload = 1/{cfg['B'] * cfg['Hkv']} of a step, float32, torch CPU"
+
+
+def run_reference(args, rank, world):
+    if rank != 0:
+        return
+    torch.set_num_threads(os.cpu_count() or 1)
+    cfg = dict(C2)
+    for _ in range(max(args.warmup, 0)):
+        cpu_prefill_sample(dict(cfg, N=1024, S=1024), 0)
+    vals, secs = [], []
+    sample = ""
+    for i in range(args.steps):
+        tf, s, sample = cpu_prefill_sample(cfg, 2 + i)
+        vals.append(tf)
+        secs.append(s)
+    val = statistics.median(vals)
+    g = cfg["Hq"] // cfg["Hkv"]
+    step_equiv_ms = statistics.median(secs) * cfg["B"] * cfg["Hkv"] * 1e3
+    line = {
+        "impl": "reference", "metric": METRIC, "value": val, "unit": "TFLOP/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": step_equiv_ms, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": workload_config(args.gpus),
+        "cpu_baseline": {"value": val, "unit": "TFLOP/s", "cores": torch.get_num_threads(), "kind": "port", "sample": sample},
+        "e2e": {"value": val, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "note": "CPU restatement of the reference's SDPA fallback (MLX itself is not installable here); "
+                "each step times one (batch, kv-group) slice, ms_per_step is scaled to the whole batch",
+    }
+    print(json.dumps(line), flush=True)
+
+
+def workload_config(n):
+    return {"workload": "config 2: GQA causal prefill fwd B=4 Hq=32 Hkv=8 N=S=8192 D=128 bf16 softcap=50 return_lse",
+            "global_batch": C2["B"] * n, "seq_len": C2["N"], "parallelism": f"(batch,kv-head) shards, dp{n}, no collective",
+            "l2": "inputs (403 MB) exceed L2 (126 MB); no explicit flush"}
+
+
+def bench_decode(device, steps, warmup, pk):
+    """Config 4: paged int8-KV decode, B=128, seq_lens ~ U[512, 32768], page 16."""
+    import numpy as np
+
+    import mlx_flashattention_steel_b200 as fa
+    from mlx_flashattention_steel_b200 import attention as A
+
+    cfg = C4
+    rng = np.random.default_rng(4)
+    lens = rng.integers(cfg["lo"], cfg["hi"] + 1, size=cfg["B"]).astype(np.int32)
+    bs, Hkv, D = cfg["block_size"], cfg["Hkv"], cfg["D"]
+    pages_per = (lens + bs - 1) // bs
+    P = int(pages_per.sum()) + 8
+    perm = rng.permutation(P)
+    max_blocks = int(pages_per.max())
+    table = -np.ones((cfg["B"], max_blocks), dtype=np.int32)
+    pos = 0
+    for b in range(cfg["B"]):
+        n = int(pages_per[b])
+        table[b, :n] = perm[pos:pos + n]
+        pos += n
+    gd = torch.Generator(device=device).manual_seed(4)
+    pools = {}
+    for name in ("k", "v"):
+        qx = torch.empty((P, bs, Hkv, D), dtype=torch.int8, device=device)
+        sc = torch.empty((P, bs, Hkv), dtype=torch.float16, device=device)
+        step_p = 8192
+        for p0 in range(0, P, step_p):
+            x = torch.randn((min(step_p, P - p0), bs, Hkv, D), generator=gd, device=device)
+            s = (x.abs().amax(dim=-1) / 127.0).to(torch.float16)
+            qx[p0:p0 + x.shape[0]] = (x / s.float().unsqueeze(-1)).round().clamp(-127, 127).to(torch.int8)
+            sc[p0:p0 + x.shape[0]] = s
+        pools[name] = (qx, sc)
+    q = torch.randn((cfg["B"], cfg["Hq"], 1, D), generator=gd, device=device).to(torch.bfloat16)
+    table_t = torch.from_numpy(table).to(device)
+    lens_t = torch.from_numpy(lens).to(device)
+    max_len = int(lens.max())
+    tokens = int(lens.sum())
+    bytes_alg = tokens * Hkv * (2 * D + 4)
+
+    def step():
+        return fa.flash_attention_paged(q, pools["k"][0], pools["v"][0], table_t, lens_t, causal=True, block_size=bs,
+                                        k_scale=pools["k"][1], v_scale=pools["v"][1], max_kv_len=max_len)
+
+    for _ in range(max(warmup, 3)):
+        step()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        step()
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / steps
+    gbs = bytes_alg / (ms * 1e-3) / 1e9
+    return {"metric": "paged-decode KV GB/s", "value": gbs, "unit": "GB/s", "ms_per_step": ms,
+            "workload": "config 4: B=128 Hq=32 Hkv=8 D=128 page 16 seq_lens~U[512,32768] int8 KV + f16 scales, bf16 q",
+            "tokens": tokens, "algorithmic_bytes": bytes_alg,
+            "roofline": {"bound": "hbm", "achieved": gbs, "peak": pk["hbm"], "unit": "GB/s", "frac": gbs / pk["hbm"],
+                         "traffic": None, "peak_source": pk["src"]},
+            "gpu_launches": steps * 2}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--no-decode", action="store_true", help="skip the config-4 decode measurement")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--small", action="store_true", help="profiling aid: N=S=4096, B=1 (not a bench value)")
+    args = ap.parse_args()
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+
+    if args.impl == "reference":
+        run_reference(args, rank, world)
+        return
+
+    import mlx_flashattention_steel_b200 as fa
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device; the library has no CPU path")
+    torch.cuda.set_device(local)
+    device = torch.device("cuda", local)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=device)
+    pk = peaks()
+    cfg = dict(C2)
+    if args.small:
+        cfg.update(B=1, N=4096, S=4096)
+    q, k, v = make_prefill_inputs(cfg, device, seed=2 + rank)
+    flops = prefill_flops(cfg)
+    warm = max(args.warmup, 3)
+
+    def step():
+        return fa.flash_attention(q, k, v, causal=True, softcap=cfg["softcap"], return_lse=True)
+
+    for _ in range(warm):
+        step()
+    torch.cuda.synchronize()
+    if dist is not None:
+        dist.barrier()
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+        time.sleep(0.25)
+    torch.cuda.synchronize()
+    t_wall0 = time.time()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        step()
+    e1.record()
+    torch.cuda.synchronize()
+    t_wall1 = time.time()
+    ms_total = e0.elapsed_time(e1)
+    if dist is not None:
+        t = torch.tensor([ms_total], device=device, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms_total = float(t.item())
+        dist.barrier()
+    clocks = sampler.stop(t_wall0, t_wall1) if rank == 0 else None
+    ms = ms_total / args.steps
+    tf_rank = flops / (ms * 1e-3) / 1e12
+    value = tf_rank * world
+
+    # ---- end to end through the public API with pinned host buffers ----
+    hq, hk, hv = (t.cpu().pin_memory() for t in (q, k, v))
+    ho = torch.empty(q.shape, dtype=q.dtype).pin_memory()
+    hl = torch.empty(q.shape[:3], dtype=torch.float32).pin_memory()
+    h2d = sum(t.numel() * t.element_size() for t in (hq, hk, hv))
+    d2h = ho.numel() * ho.element_size() + hl.numel() * 4
+
+    def e2e_step():
+        dq, dk, dv = hq.to(device, non_blocking=True), hk.to(device, non_blocking=True), hv.to(device, non_blocking=True)
+        o, l = fa.flash_attention(dq, dk, dv, causal=True, softcap=cfg["softcap"], return_lse=True)
+        ho.copy_(o, non_blocking=True)
+        hl.copy_(l, non_blocking=True)
+
+    e2e_steps = max(3, min(args.steps, 10))
+    for _ in range(2):
+        e2e_step()
+    torch.cuda.synchronize()
+    if dist is not None:
+        dist.barrier()
+    e0.record()
+    for _ in range(e2e_steps):
+        e2e_step()
+    e1.record()
+    torch.cuda.synchronize()
+    e2e_ms = e0.elapsed_time(e1) / e2e_steps
+    if dist is not None:
+        t = torch.tensor([e2e_ms], device=device, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_ms = float(t.item())
+    e2e_val = flops / (e2e_ms * 1e-3) / 1e12 * world
+    del hq, hk, hv, ho, hl
+
+    decode = None
+    if rank == 0 and not args.no_decode and not args.small:
+        try:
+            decode = bench_decode(device, max(args.steps, 10), warm, pk)
+        except NotImplementedError as e:  # decode kernel not built for this shape
+            decode = {"unavailable": str(e)}
+    if dist is not None:
+        dist.barrier()
+
+    if rank == 0:
+        cpu = None
+        if world == 1 and not args.no_cpu_baseline:
+            torch.set_num_threads(os.cpu_count() or 1)
+            tf, secs, sample = cpu_prefill_sample(C2, 2)
+            cpu = {"value": tf, "unit": "TFLOP/s", "cores": torch.get_num_threads(), "kind": "port", "sample": sample,
+                   "seconds": secs}
+        line = {
+            "metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
+            "warmup": warm, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "bf16", "data": "synthetic", "config": workload_config(world),
+            "roofline": {"bound": "tensor", "achieved": tf_rank, "peak": pk["tf"], "unit": "TFLOP/s",
+                         "frac": tf_rank / pk["tf"], "traffic": None, "peak_source": pk["src"],
+                         "frac_of_sustained": (tf_rank / pk["tf_sustained"]) if pk.get("tf_sustained") else None,
+                         "flops_per_launch": flops},
+            "cpu_baseline": cpu,
+            "e2e": {"value": e2e_val, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                    "ms_per_step": e2e_ms},
+            "gpu_launches": args.steps,
+            "clocks": clocks,
+            "decode": decode,
+        }
+        if args.small:
+            line["note"] = "--small profiling case, not a bench value"
+        print(json.dumps(line), flush=True)
+    if dist is not None:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -166,6 +166,15 @@ int32_t b200fa_decode_paged(const b200fa_desc* d, const void* q,
                             void* workspace, size_t workspace_bytes, void* stream);
 
 /*
+ * Reads the error word the decode kernel keeps at the start of its workspace
+ * (0 = ok, bit 0 = a bounded wait inside the kernel gave up, bit 1 = a
+ * block_table entry pointed beyond num_pages and was treated as a hole).
+ * This is the one entry point that synchronises: it waits for `stream`.
+ * No counterpart in the reference, whose kernels report nothing back.
+ */
+int32_t b200fa_workspace_status(const void* workspace, void* stream, int32_t* status_out);
+
+/*
  * Page gather: out[b,h,t,:] = pool[block_table[b, t / block_size], t % block_size, h, :]
  * for t < seq_lens[b] and a non-negative table entry, else zero.  Bit-exact copy.
  * Replaces mfa_paged_kv_gather (csrc/bindings.cpp:346-364) /

@@ -434,6 +434,16 @@ def paged_kv_gather(pool, block_table, seq_lens, max_kv_len: int, stream=None) -
     return out
 
 
+_CHECK_DECODE_STATUS = False   # tests switch this on: one stream sync per call
+
+
+def _set_check_decode_status(on: bool) -> bool:
+    """Debug hook: after each decode launch, wait for it and raise if the kernel set its error word."""
+    global _CHECK_DECODE_STATUS
+    old, _CHECK_DECODE_STATUS = _CHECK_DECODE_STATUS, bool(on)
+    return old
+
+
 _KV_CODE = {torch.int8: _lib.I8}
 if hasattr(torch, "float8_e4m3fn"):
     _KV_CODE[torch.float8_e4m3fn] = _lib.E4M3
@@ -461,6 +471,13 @@ def _decode_raw(q, k_pages, v_pages, k_scale, v_scale, table, lens, max_kv_len, 
                                      _ptr(workspace), workspace.numel(),
                                      C.c_void_p(_stream_ptr(stream, q.device)))
     _lib.check(st, "flash_attention_paged")
+    if _CHECK_DECODE_STATUS:
+        word = C.c_int32(0)
+        _lib.check(lib.b200fa_workspace_status(_ptr(workspace), C.c_void_p(_stream_ptr(stream, q.device)),
+                                               C.byref(word)), "decode status")
+        if word.value != 0:
+            raise RuntimeError(f"flash_attention_paged: decode kernel reported status {word.value} "
+                               "(1 = a bounded wait gave up, 2 = block_table entry beyond the pool)")
     return out, lse
 
 
@@ -480,6 +497,7 @@ def flash_attention_paged(
     softcap: float = 0.0,
     max_kv_len: Optional[int] = None,
     return_lse: bool = False,
+    num_splits: int = 0,
 ):
     """Attention over a paged KV pool.
 
@@ -493,7 +511,8 @@ def flash_attention_paged(
     int8 / float8_e4m3 pools (a stored x stands for ``float(x) * scale``, rounded to
     the query dtype as ``mx.dequantize(..., dtype=q.dtype)`` does in
     mlx_mfa/integrations/mlx_lm.py:97-110); ``max_kv_len`` skips the host read of
-    ``seq_lens`` that the reference also performs (mlx_mfa/attention.py:2871-2873).
+    ``seq_lens`` that the reference also performs (mlx_mfa/attention.py:2871-2873);
+    ``num_splits`` caps how many CTAs share the page list (0 = one per SM).
 
     Short queries ((Hq/Hkv)*Nq <= 8, D = 128, block_size 16) run the split-KV
     decode kernel with in-kernel combine; other shapes gather pages and attend
@@ -541,7 +560,7 @@ def flash_attention_paged(
     decode_ok = (Hq // Hkv) * Nq <= 8 and D == 128 and block_size == 16
     if decode_ok:
         out, lse = _decode_raw(q, k_pages, v_pages, k_scale, v_scale, table, lens, max_kv_len, float(scale),
-                               bool(causal), float(softcap), block_size, return_lse, stream)
+                               bool(causal), float(softcap), block_size, return_lse, stream, num_splits)
         return (out, lse) if return_lse else out
     if quant:
         raise NotImplementedError("quantized pools are served by the decode kernel only ((Hq/Hkv)*Nq <= 8, D=128).")

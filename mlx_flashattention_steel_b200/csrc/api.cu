@@ -299,6 +299,17 @@ int32_t b200fa_paged_kv_gather(const void* pool, const int32_t* block_table, con
   return B200FA_OK;
 }
 
+int32_t b200fa_workspace_status(const void* workspace, void* stream, int32_t* status_out) {
+  if (workspace == nullptr || status_out == nullptr) return fail(B200FA_ERR_INVALID_ARG, "null pointer");
+  cudaStream_t cs = reinterpret_cast<cudaStream_t>(stream);
+  int32_t word = 0;
+  cudaError_t e = cudaMemcpyAsync(&word, workspace, sizeof(word), cudaMemcpyDeviceToHost, cs);
+  if (e == cudaSuccess) e = cudaStreamSynchronize(cs);
+  if (e != cudaSuccess) return cuda_fail(e, "workspace status read");
+  *status_out = word;
+  return B200FA_OK;
+}
+
 static int32_t decode_check(const b200fa_desc* d) {
   if (d == nullptr) return fail(B200FA_ERR_INVALID_ARG, "descriptor is null");
   if (d->dtype != B200FA_F16 && d->dtype != B200FA_BF16)

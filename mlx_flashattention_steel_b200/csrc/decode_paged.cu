@@ -1,0 +1,804 @@
+// Paged-KV decode: split-KV flash-decoding with the log-sum-exp combine inside the
+// same launch.  Replaces the reference's gather + per-sequence two-kernel flash-decode
+// route (mlx_mfa/attention.py:3008-3017; csrc/mfa_attention.cpp:150-288; kernels
+// csrc/mfa_steel_fwd.cpp:1541-1991, 2008-2105) and its paged forward
+// (csrc/mfa_steel_fwd.cpp:2462-3121).
+//
+// Shape of the work
+//   * The pages of all sequences form one list of U units.  CTA c of G takes units
+//     [c*U/G, (c+1)*U/G): equal bytes per CTA whatever the sequence lengths are.
+//   * A CTA holds HPC kv heads (one consumer warp each) plus one producer warp.  The
+//     producer looks pages up in block_table and brings each page in with ONE TMA
+//     tensor copy per pool ([block_size tokens] x [HPC heads] x [row bytes], a
+//     contiguous 16 KB of HBM for 8 int8 heads), 128B-swizzled by token, plus one
+//     bulk copy per scale array, into a ring of stages guarded by mbarriers.
+//   * A consumer warp computes S = Q.K^T (rows = the GQA group x query tokens, padded
+//     to the 16 rows of mma.m16n8k16) and O^T += V^T.P^T for its head.  int8 / e4m3
+//     values are widened to f16 in registers straight from the swizzled tile;
+//     k_scale multiplies the scores, v_scale is folded into P.
+//   * A CTA that covers a whole sequence writes the result; otherwise it writes a
+//     partial (normalised O, base-2 lse) and bumps a counter; the CTA that brings the
+//     counter to the number of parts combines them.  Nobody spins on anybody.
+//
+// Every mbarrier wait is bounded (tma.cuh); a timeout raises the error word at the
+// start of the workspace and the CTA leaves.
+#include <cuda_fp8.h>
+
+#include <cstdio>
+#include <type_traits>
+
+#include "common.cuh"
+#include "decode.h"
+#include "tma.cuh"
+
+namespace b200fa {
+
+namespace {
+
+constexpr int kBS = 16;           // tokens per page
+constexpr int kD = 128;
+constexpr int kMaxStages = 8;
+
+enum KvKind { KV_F16 = 0, KV_BF16 = 1, KV_I8 = 2, KV_E4M3 = 3 };
+
+struct DecodeLayout {          // workspace carve-up, in bytes from the workspace base
+  size_t err;                  // int[4]: [0] error word
+  size_t counters;             // int[B * HG]
+  size_t page_start;           // int[B + 1]
+  size_t part_lse;             // float[slots * Hq * Nq]
+  size_t part_o;               // float[slots * Hq * Nq * D]
+  size_t total;
+  int slots;
+};
+
+__host__ __device__ inline size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
+
+__host__ __device__ inline DecodeLayout make_layout(int B, int Hq, int Nq, int HG, int G) {
+  DecodeLayout L;
+  L.err = 0;
+  L.counters = 16;
+  L.page_start = align_up(L.counters + sizeof(int) * static_cast<size_t>(B) * HG, 16);
+  L.slots = G + B;
+  L.part_lse = align_up(L.page_start + sizeof(int) * (static_cast<size_t>(B) + 1), 16);
+  L.part_o = align_up(L.part_lse + sizeof(float) * static_cast<size_t>(L.slots) * Hq * Nq, 16);
+  L.total = align_up(L.part_o + sizeof(float) * static_cast<size_t>(L.slots) * Hq * Nq * kD, 16);
+  return L;
+}
+
+struct KernelArgs {
+  DecodeParams p;
+  DecodeLayout lay;
+  int HG;            // head groups = Hkv / HPC
+  int group;         // Hq / Hkv
+  int rows;          // group * Nq (<= 8)
+  int stages;
+  int stage_kv_bytes;   // bytes of one K (or V) stage tile = HPC * kBS * row_bytes
+  int scale_bytes;      // bytes of one scale page = kBS * Hkv * 2 (0 when not quantized)
+  float q_prescale;     // folded into Q (8-bit pools) or applied to the scores (16-bit)
+  float cap_log2;       // softcap * log2(e)
+  float inv_cap;        // 1 / softcap
+};
+
+// ---------------------------------------------------------------------------
+// plan: page prefix sums, counters and error word reset
+// ---------------------------------------------------------------------------
+__global__ void __launch_bounds__(1024) decode_plan_kernel(const int32_t* __restrict__ seq_lens, int B,
+                                                           int max_kv_len, int n_counters,
+                                                           int* __restrict__ err, int* __restrict__ counters,
+                                                           int* __restrict__ page_start) {
+  __shared__ int warp_sums[32];
+  __shared__ int carry;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  if (tid == 0) { carry = 0; page_start[0] = 0; }
+  if (tid < 4) err[tid] = 0;
+  for (int i = tid; i < n_counters; i += blockDim.x) counters[i] = 0;
+  __syncthreads();
+  for (int base = 0; base < B; base += blockDim.x) {
+    const int i = base + tid;
+    int val = 0;
+    if (i < B) {
+      int len = seq_lens[i];
+      len = len < 0 ? 0 : (len > max_kv_len ? max_kv_len : len);
+      val = (len + kBS - 1) / kBS;
+    }
+    int x = val;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      int y = __shfl_up_sync(0xffffffffu, x, o);
+      if (lane >= o) x += y;
+    }
+    if (lane == 31) warp_sums[warp] = x;
+    __syncthreads();
+    if (warp == 0) {
+      int w = warp_sums[lane];
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        int y = __shfl_up_sync(0xffffffffu, w, o);
+        if (lane >= o) w += y;
+      }
+      warp_sums[lane] = w;
+    }
+    __syncthreads();
+    const int incl = x + (warp > 0 ? warp_sums[warp - 1] : 0) + carry;
+    if (i < B) page_start[i + 1] = incl;
+    __syncthreads();
+    if (tid == blockDim.x - 1) carry = incl;
+    __syncthreads();
+  }
+}
+
+// ---------------------------------------------------------------------------
+// small device helpers
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
+  uint32_t d;
+  asm("prmt.b32 %0, %1, %2, %3;\n" : "=r"(d) : "r"(a), "r"(b), "r"(sel));
+  return d;
+}
+__device__ __forceinline__ uint32_t lds32(uint32_t addr) {
+  uint32_t v;
+  asm volatile("ld.shared.u32 %0, [%1];\n" : "=r"(v) : "r"(addr));
+  return v;
+}
+__device__ __forceinline__ uint4 lds128(uint32_t addr) {
+  uint4 v;
+  asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];\n" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+  return v;
+}
+__device__ __forceinline__ float lds_half(uint32_t addr) {
+  unsigned short v;
+  asm volatile("ld.shared.u16 %0, [%1];\n" : "=h"(v) : "r"(addr));
+  return __half2float(__ushort_as_half(v));
+}
+// two biased bytes (x ^ 0x80) at byte positions given by `sel` -> half2 of the signed values
+__device__ __forceinline__ uint32_t i8pair_to_h2(uint32_t biased, uint32_t sel) {
+  const uint32_t magic = prmt(biased, 0x64646464u, sel);      // 0x64XX64YY = 1024 + u
+  __half2 h = __hsub2(*reinterpret_cast<const __half2*>(&magic), __floats2half2_rn(1152.f, 1152.f));
+  return *reinterpret_cast<uint32_t*>(&h);
+}
+__device__ __forceinline__ uint32_t e4m3pair_to_h2(uint32_t two_bytes) {
+  __half2_raw r = __nv_cvt_fp8x2_to_halfraw2(static_cast<__nv_fp8x2_storage_t>(two_bytes & 0xffffu), __NV_E4M3);
+  __half2 h = r;
+  return *reinterpret_cast<uint32_t*>(&h);
+}
+__device__ __forceinline__ uint32_t pack_h2(float a, float b) {
+  __half2 h = __floats2half2_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&h);
+}
+__device__ __forceinline__ uint32_t pack_bf2(float a, float b) {
+  __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&h);
+}
+__device__ __forceinline__ void named_bar_sync(int id, int threads) {
+  asm volatile("bar.sync %0, %1;\n" ::"r"(id), "r"(threads) : "memory");
+}
+__device__ __forceinline__ float clamp_h(float x) { return fminf(fmaxf(x, -65504.f), 65504.f); }
+
+// CTA index (of G) whose unit range [c*U/G, (c+1)*U/G) holds unit u
+__device__ __forceinline__ int cta_of_unit(long long u, int G, long long U) {
+  return static_cast<int>(((u + 1) * G - 1) / U);
+}
+
+// ---------------------------------------------------------------------------
+// main kernel
+// ---------------------------------------------------------------------------
+template <int KV, int HPC>
+__global__ void __launch_bounds__((HPC + 1) * 32, 1)
+decode_paged_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
+                    const KernelArgs a) {
+  constexpr bool kQuant = (KV == KV_I8 || KV == KV_E4M3);
+  constexpr int kRowBytes = kQuant ? kD : 2 * kD;      // bytes of one (token, head) row
+  constexpr int kHalves = kRowBytes / 128;
+  constexpr int kHeadBytes = kBS * kRowBytes;          // one head of one page in shared memory
+  using MmaT = typename std::conditional<KV == KV_BF16, __nv_bfloat16, __half>::type;
+
+  extern __shared__ __align__(1024) unsigned char smem_raw[];
+  // carve: [stages] K tiles, [stages] V tiles, [stages] k scales, [stages] v scales, barriers, misc
+  unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  const DecodeParams& p = a.p;
+  const int NS = a.stages;
+  unsigned char* sK = smem;
+  unsigned char* sV = sK + static_cast<size_t>(NS) * a.stage_kv_bytes;
+  unsigned char* sKs = sV + static_cast<size_t>(NS) * a.stage_kv_bytes;
+  unsigned char* sVs = sKs + static_cast<size_t>(NS) * a.scale_bytes;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sVs + static_cast<size_t>(NS) * a.scale_bytes);  // full[NS], empty[NS]
+  int* s_page = reinterpret_cast<int*>(bars + 2 * kMaxStages);
+  volatile int* s_abort = s_page + kMaxStages;
+  int* s_last = const_cast<int*>(s_abort) + 1;
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int g = lane >> 2, t = lane & 3;
+  const int hg = blockIdx.y;
+  const int c = blockIdx.x;
+
+  unsigned char* ws = reinterpret_cast<unsigned char*>(p.workspace);
+  int* err = reinterpret_cast<int*>(ws + a.lay.err);
+  int* counters = reinterpret_cast<int*>(ws + a.lay.counters);
+  const int* page_start = reinterpret_cast<const int*>(ws + a.lay.page_start);
+  float* part_lse = reinterpret_cast<float*>(ws + a.lay.part_lse);
+  float* part_o = reinterpret_cast<float*>(ws + a.lay.part_o);
+
+  const int rows = a.rows;
+  const int HqNq = p.Hq * p.Nq;
+
+  // Sequences of length zero have no unit: CTA 0 of each head group zero-fills them.
+  if (c == 0) {
+    for (int b = 0; b < p.B; ++b) {
+      if (page_start[b + 1] != page_start[b]) continue;
+      for (int i = tid; i < HPC * a.group * p.Nq * kD; i += blockDim.x) {
+        const int d = i % kD;
+        const int r = i / kD;                       // (head in cta, group, qi)
+        const int qi = r % p.Nq;
+        const int hq = (hg * HPC) * a.group + r / p.Nq;
+        const size_t o = ((static_cast<size_t>(b) * p.Hq + hq) * p.Nq + qi) * kD + d;
+        if (p.q_dtype == 0) reinterpret_cast<__half*>(p.out)[o] = __float2half(0.f);
+        else reinterpret_cast<__nv_bfloat16*>(p.out)[o] = __float2bfloat16(0.f);
+        if (p.lse != nullptr && d == 0) p.lse[(static_cast<size_t>(b) * p.Hq + hq) * p.Nq + qi] = -INFINITY;
+      }
+    }
+  }
+
+  // With fewer units than CTAs only the first U CTAs work, one unit each, so that the
+  // CTAs sharing a sequence are always consecutive.
+  const long long U = page_start[p.B];
+  const int G = U < static_cast<long long>(gridDim.x) ? static_cast<int>(U) : static_cast<int>(gridDim.x);
+  if (c >= G) return;
+  const long long lo = static_cast<long long>(c) * U / G;
+  const long long hi = static_cast<long long>(c + 1) * U / G;
+  if (lo >= hi) return;
+
+  if (tid == 0) {
+    for (int i = 0; i < NS; ++i) {
+      mbar_init(smem_u32(&bars[i]), 1);                 // full: producer arrive (+ tx bytes)
+      mbar_init(smem_u32(&bars[kMaxStages + i]), HPC);  // empty: one arrive per consumer warp
+    }
+    *s_abort = 0;
+    *s_last = 0;
+    fence_barrier_init();
+    fence_proxy_async();
+  }
+  __syncthreads();
+
+  // first sequence: largest b with page_start[b] <= lo
+  int b_first;
+  {
+    int l = 0, r = p.B;   // invariant: page_start[l] <= lo < page_start[r]  (page_start[B] = U > lo)
+    while (r - l > 1) {
+      const int m = (l + r) >> 1;
+      if (page_start[m] <= lo) l = m; else r = m;
+    }
+    b_first = l;
+  }
+
+  const uint32_t tx_bytes = 2u * a.stage_kv_bytes + 2u * a.scale_bytes;
+
+  if (warp == HPC) {
+    // ======================= producer warp =======================
+    int stage = 0;
+    uint32_t phase = 0;
+    long long u = lo;
+    int b = b_first;
+    bool ok = true;
+    while (u < hi && ok) {
+      const int s0 = page_start[b], s1 = page_start[b + 1];
+      if (s1 <= u) { ++b; continue; }
+      const int j_lo = static_cast<int>(u - s0);
+      const int j_hi = static_cast<int>((hi < s1 ? hi : s1) - s0);
+      const int32_t* row = p.block_table + static_cast<size_t>(b) * p.max_blocks;
+      for (int j0 = j_lo; j0 < j_hi && ok; j0 += 32) {
+        const int jj = j0 + lane;
+        int my_page = (jj < j_hi) ? row[jj] : -1;
+        if (my_page >= p.num_pages) {
+          my_page = -1;
+          atomicOr(err, 2);                      // table entry beyond the pool
+        }
+        const int n = min(32, j_hi - j0);
+        for (int i = 0; i < n; ++i) {
+          const int page = __shfl_sync(0xffffffffu, my_page, i);
+          if (!__all_sync(0xffffffffu, mbar_wait_bounded(smem_u32(&bars[kMaxStages + stage]), phase ^ 1u, s_abort))) { ok = false; break; }
+          if (lane == 0) {
+            s_page[stage] = page;
+            const uint32_t full = smem_u32(&bars[stage]);
+            if (page >= 0) {
+              mbar_arrive_expect_tx(full, tx_bytes);
+              tma_load_5d(smem_u32(sK + static_cast<size_t>(stage) * a.stage_kv_bytes), &tmK, full, 0, page * kBS, 0, hg * HPC, 0);
+              tma_load_5d(smem_u32(sV + static_cast<size_t>(stage) * a.stage_kv_bytes), &tmV, full, 0, page * kBS, 0, hg * HPC, 0);
+              if (kQuant) {
+                const size_t soff = static_cast<size_t>(page) * a.scale_bytes;
+                bulk_load(smem_u32(sKs + static_cast<size_t>(stage) * a.scale_bytes),
+                          reinterpret_cast<const unsigned char*>(p.k_scale) + soff, a.scale_bytes, full);
+                bulk_load(smem_u32(sVs + static_cast<size_t>(stage) * a.scale_bytes),
+                          reinterpret_cast<const unsigned char*>(p.v_scale) + soff, a.scale_bytes, full);
+              }
+            } else {
+              mbar_arrive(full);                  // hole in the table: consumers treat K = V = 0
+            }
+          }
+          __syncwarp();
+          if (++stage == NS) { stage = 0; phase ^= 1u; }
+        }
+      }
+      u = s0 + j_hi;
+      if (u >= s1) ++b;
+    }
+    if (!ok && lane == 0) atomicOr(err, 1);
+    return;
+  }
+
+  // ======================= consumer warps =======================
+  const int kvh = hg * HPC + warp;
+  const int qi_row = g / a.group;                // query token of fragment row g
+  const int hq_row = kvh * a.group + g % a.group;
+  const bool row_valid = g < rows;
+  int stage = 0;
+  uint32_t phase = 0;
+  long long u = lo;
+  int b = b_first;
+  bool ok = true;
+
+  while (u < hi && ok) {
+    const int s0 = page_start[b], s1 = page_start[b + 1];
+    if (s1 <= u) { ++b; continue; }
+    const int j_lo = static_cast<int>(u - s0);
+    const int j_hi = static_cast<int>((hi < s1 ? hi : s1) - s0);
+    int len = p.seq_lens[b];
+    len = len < 0 ? 0 : (len > p.max_kv_len ? p.max_kv_len : len);
+    const int c_first = cta_of_unit(s0, G, U);
+    const int c_last = cta_of_unit(static_cast<long long>(s1) - 1, G, U);
+    const int n_parts = c_last - c_first + 1;
+
+    // ---- Q fragments (A operand rows 0..7; rows 8..15 are zero padding) ----
+    uint32_t qa[8][2];
+    {
+      const size_t qoff = ((static_cast<size_t>(b) * p.Hq + hq_row) * p.Nq + qi_row) * kD;
+      if (kQuant) {
+        // lane t owns d in [32t, 32t+32): k-step s uses d = 32t + 4s + {0,1 | 2,3}
+        float f[32];
+        if (row_valid) {
+          if (p.q_dtype == 0) {
+            const uint4* src = reinterpret_cast<const uint4*>(reinterpret_cast<const __half*>(p.q) + qoff + 32 * t);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              uint4 w = src[i];
+              const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                float2 v2 = __half22float2(*reinterpret_cast<const __half2*>(&ww[e]));
+                f[i * 8 + e * 2] = v2.x; f[i * 8 + e * 2 + 1] = v2.y;
+              }
+            }
+          } else {
+            const uint4* src = reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(p.q) + qoff + 32 * t);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              uint4 w = src[i];
+              const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                float2 v2 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&ww[e]));
+                f[i * 8 + e * 2] = v2.x; f[i * 8 + e * 2 + 1] = v2.y;
+              }
+            }
+          }
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) f[i] = 0.f;
+        }
+#pragma unroll
+        for (int s = 0; s < 8; ++s) {
+          qa[s][0] = pack_h2(clamp_h(f[4 * s] * a.q_prescale), clamp_h(f[4 * s + 1] * a.q_prescale));
+          qa[s][1] = pack_h2(clamp_h(f[4 * s + 2] * a.q_prescale), clamp_h(f[4 * s + 3] * a.q_prescale));
+        }
+      } else {
+        // natural order: a0 = Q[g][16s + 2t, +1], a2 = Q[g][16s + 8 + 2t, +1]
+        const uint32_t* src = reinterpret_cast<const uint32_t*>(reinterpret_cast<const uint16_t*>(p.q) + qoff);
+#pragma unroll
+        for (int s = 0; s < 8; ++s) {
+          qa[s][0] = row_valid ? src[8 * s + t] : 0u;
+          qa[s][1] = row_valid ? src[8 * s + 4 + t] : 0u;
+        }
+      }
+    }
+
+    float oacc[8][4];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) { oacc[i][0] = oacc[i][1] = oacc[i][2] = oacc[i][3] = 0.f; }
+    float m_run = -INFINITY, l_run = 0.f;
+    float vnorm = 1.f, vunnorm = 1.f;             // power-of-two normalisation of v_scale inside P
+    bool first_page = true;
+    const int causal_lim = p.causal ? (qi_row + len - p.Nq) : 0x7fffffff;   // last visible token of row g
+
+    for (int j = j_lo; j < j_hi; ++j) {
+      if (!__all_sync(0xffffffffu, mbar_wait_bounded(smem_u32(&bars[stage]), phase, s_abort))) { ok = false; break; }
+      const int page = s_page[stage];
+      const uint32_t kbase = smem_u32(sK + static_cast<size_t>(stage) * a.stage_kv_bytes) + warp * kHeadBytes;
+      const uint32_t vbase = smem_u32(sV + static_cast<size_t>(stage) * a.stage_kv_bytes) + warp * kHeadBytes;
+      const uint32_t ksb = smem_u32(sKs + static_cast<size_t>(stage) * a.scale_bytes) + kvh * 2;
+      const uint32_t vsb = smem_u32(sVs + static_cast<size_t>(stage) * a.scale_bytes) + kvh * 2;
+      const int scale_stride = p.Hkv * 2;          // bytes between tokens in a scale page
+      const int tok0 = j * kBS;
+
+      // ---- S = Q K^T : rows = query rows (8 real), cols = 16 tokens (two n-tiles) ----
+      float sacc[2][4];
+#pragma unroll
+      for (int i = 0; i < 2; ++i) { sacc[i][0] = sacc[i][1] = sacc[i][2] = sacc[i][3] = 0.f; }
+      if (page >= 0) {
+        if (kQuant) {
+#pragma unroll
+          for (int jn = 0; jn < 2; ++jn) {
+            const int tok = 8 * jn + g;                     // tok & 7 == g
+            const uint32_t rowa = kbase + tok * 128;
+            const uint4 w0 = lds128(rowa + (((2 * t) ^ g) << 4));
+            const uint4 w1 = lds128(rowa + (((2 * t + 1) ^ g) << 4));
+            const uint32_t words[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+#pragma unroll
+            for (int s = 0; s < 8; ++s) {
+              uint32_t b0, b1;
+              if (KV == KV_I8) {
+                const uint32_t x = words[s] ^ 0x80808080u;
+                b0 = i8pair_to_h2(x, 0x4140u);
+                b1 = i8pair_to_h2(x, 0x4342u);
+              } else {
+                b0 = e4m3pair_to_h2(words[s]);
+                b1 = e4m3pair_to_h2(words[s] >> 16);
+              }
+              const uint32_t afrag[4] = {qa[s][0], 0u, qa[s][1], 0u};
+              mma16816<MmaT>(sacc[jn], afrag, b0, b1);
+            }
+          }
+        } else {
+#pragma unroll
+          for (int s = 0; s < 8; ++s) {
+            uint32_t bfr[4];
+            const int tok = (lane & 7) + ((lane >> 4) << 3);
+            const int dcol = 16 * s + (((lane >> 3) & 1) << 3);
+            const uint32_t addr = kbase + (dcol >> 6) * (kBS * 128) + tok * 128 + ((((dcol & 63) >> 3) ^ (tok & 7)) << 4);
+            ldmatrix_x4(bfr, addr);
+            const uint32_t afrag[4] = {qa[s][0], 0u, qa[s][1], 0u};
+            mma16816<MmaT>(sacc[0], afrag, bfr[0], bfr[1]);
+            mma16816<MmaT>(sacc[1], afrag, bfr[2], bfr[3]);
+          }
+        }
+      }
+
+      // ---- scale / softcap / masks: this lane holds tokens {2t, 2t+1, 8+2t, 9+2t} of row g ----
+      float sc[4], vsc[4];
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int tok = ((e >> 1) << 3) + 2 * t + (e & 1);
+        float s = sacc[e >> 1][e & 1];
+        float ksv = 1.f;
+        vsc[e] = 1.f;
+        if (kQuant) {
+          if (page >= 0) {
+            ksv = lds_half(ksb + tok * scale_stride);
+            vsc[e] = lds_half(vsb + tok * scale_stride);
+          }
+          s *= ksv;
+        } else {
+          s *= a.q_prescale;
+        }
+        if (a.inv_cap > 0.f) s = a.cap_log2 * fast_tanh(s * a.inv_cap);
+        const int tg = tok0 + tok;
+        sc[e] = (tg < len && tg <= causal_lim) ? s : -INFINITY;
+      }
+      if (kQuant && first_page) {
+        // power of two near the first token's v scale keeps p * v_scale inside f16's normal range
+        float v0 = (page >= 0) ? lds_half(vsb) : 1.f;
+        v0 = __shfl_sync(0xffffffffu, v0, 0);
+        uint32_t bits = __float_as_uint(v0) & 0x7f800000u;
+        if (bits == 0u || bits == 0x7f800000u) bits = 0x3f800000u;
+        vunnorm = __uint_as_float(bits);
+        vnorm = 1.f / vunnorm;
+        first_page = false;
+      }
+
+      // ---- online softmax over the 16 tokens ----
+      float mx = fmaxf(fmaxf(sc[0], sc[1]), fmaxf(sc[2], sc[3]));
+      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+      const float m_new = fmaxf(m_run, mx);
+      const float msub = (m_new == -INFINITY) ? 0.f : m_new;
+      const bool grew = m_new > m_run;
+      if (__any_sync(0xffffffffu, grew)) {
+        const float corr = fast_exp2(m_run - msub);       // 1 when unchanged, 0 from -inf
+        l_run *= corr;
+        const float c0 = __shfl_sync(0xffffffffu, corr, (2 * t) * 4);
+        const float c1 = __shfl_sync(0xffffffffu, corr, (2 * t + 1) * 4);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          oacc[i][0] *= c0; oacc[i][1] *= c1; oacc[i][2] *= c0; oacc[i][3] *= c1;
+        }
+        m_run = m_new;
+      }
+      float pr[4];
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        pr[e] = fast_exp2(sc[e] - msub);
+        l_run += pr[e];
+      }
+
+      // ---- O^T += V^T P^T : rows = 16 head-dim values per m-tile, cols = query rows ----
+      if (page >= 0) {
+        uint32_t pb0, pb1;
+        if (kQuant) {
+          pb0 = pack_h2(pr[0] * vsc[0] * vnorm, pr[1] * vsc[1] * vnorm);
+          pb1 = pack_h2(pr[2] * vsc[2] * vnorm, pr[3] * vsc[3] * vnorm);
+        } else if (KV == KV_BF16) {
+          pb0 = pack_bf2(pr[0], pr[1]);
+          pb1 = pack_bf2(pr[2], pr[3]);
+        } else {
+          pb0 = pack_h2(pr[0], pr[1]);
+          pb1 = pack_h2(pr[2], pr[3]);
+        }
+        if (kQuant) {
+          // lane (g,t) reads word w = g + 8*jj (4 head-dim bytes) of token rows 2t, 2t+1, 2t+8, 2t+9
+          const uint32_t rA = vbase + (2 * t) * 128, rB = rA + 128, rC = rA + 8 * 128, rD = rC + 128;
+          const int xa = (2 * t) & 7, xb = (2 * t + 1) & 7;
+#pragma unroll
+          for (int jj = 0; jj < 4; ++jj) {
+            const int w = g + 8 * jj;
+            const int ch = w >> 2, wi = (w & 3) << 2;
+            uint32_t A = lds32(rA + ((ch ^ xa) << 4) + wi);
+            uint32_t Bw = lds32(rB + ((ch ^ xb) << 4) + wi);
+            uint32_t Cw = lds32(rC + ((ch ^ xa) << 4) + wi);
+            uint32_t Dw = lds32(rD + ((ch ^ xb) << 4) + wi);
+            if (KV == KV_I8) { A ^= 0x80808080u; Bw ^= 0x80808080u; Cw ^= 0x80808080u; Dw ^= 0x80808080u; }
+            const uint32_t ab[2] = {prmt(A, Bw, 0x5140u), prmt(A, Bw, 0x7362u)};   // [A0 B0 A1 B1], [A2 B2 A3 B3]
+            const uint32_t cd[2] = {prmt(Cw, Dw, 0x5140u), prmt(Cw, Dw, 0x7362u)};
+#pragma unroll
+            for (int kp = 0; kp < 2; ++kp) {
+              uint32_t af[4];
+              if (KV == KV_I8) {
+                af[0] = i8pair_to_h2(ab[kp], 0x4140u);   // head-dim byte 2kp   , tokens 2t, 2t+1
+                af[1] = i8pair_to_h2(ab[kp], 0x4342u);   // head-dim byte 2kp+1 , tokens 2t, 2t+1
+                af[2] = i8pair_to_h2(cd[kp], 0x4140u);   // tokens 2t+8, 2t+9
+                af[3] = i8pair_to_h2(cd[kp], 0x4342u);
+              } else {
+                af[0] = e4m3pair_to_h2(ab[kp]);
+                af[1] = e4m3pair_to_h2(ab[kp] >> 16);
+                af[2] = e4m3pair_to_h2(cd[kp]);
+                af[3] = e4m3pair_to_h2(cd[kp] >> 16);
+              }
+              mma16816<MmaT>(oacc[jj * 2 + kp], af, pb0, pb1);
+            }
+          }
+        } else {
+#pragma unroll
+          for (int mt = 0; mt < 8; ++mt) {
+            uint32_t af[4];
+            const int tok = (lane & 7) + ((lane >> 4) << 3);
+            const int dcol = 16 * mt + (((lane >> 3) & 1) << 3);
+            const uint32_t addr = vbase + (dcol >> 6) * (kBS * 128) + tok * 128 + ((((dcol & 63) >> 3) ^ (tok & 7)) << 4);
+            ldmatrix_x4_trans(af, addr);
+            // ldmatrix order: m0 = (tok 0-7, d 0-7), m1 = (tok 0-7, d 8-15), m2 = (tok 8-15, d 0-7), m3 = (tok 8-15, d 8-15)
+            // A fragment wants a0 = (d 0-7, tok 0-7), a1 = (d 8-15, tok 0-7), a2 = (d 0-7, tok 8-15), a3 = (d 8-15, tok 8-15)
+            mma16816<MmaT>(oacc[mt], af, pb0, pb1);
+          }
+        }
+      }
+
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&bars[kMaxStages + stage]));
+      if (++stage == NS) { stage = 0; phase ^= 1u; }
+    }
+    if (!ok) break;
+
+    // ---- end of this CTA's part of sequence b ----
+    float l_row = l_run;
+    l_row += __shfl_xor_sync(0xffffffffu, l_row, 1);
+    l_row += __shfl_xor_sync(0xffffffffu, l_row, 2);
+    const float lse_row = l_row > 0.f ? m_run + log2f(l_row) : -INFINITY;
+    const float inv_row = l_row > 0.f ? vunnorm / l_row : 0.f;
+    // accumulator columns are query rows 2t and 2t+1
+    const float inv0 = __shfl_sync(0xffffffffu, inv_row, (2 * t) * 4);
+    const float inv1 = __shfl_sync(0xffffffffu, inv_row, (2 * t + 1) * 4);
+    const int r0 = 2 * t, r1 = 2 * t + 1;
+    const bool direct = (n_parts == 1);
+    const int slot = c + b;
+
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        // head-dim index of accumulator register e of m-tile i
+        int d;
+        if (kQuant) d = 32 * (i >> 1) + 4 * g + 2 * (i & 1) + (e >> 1);
+        else d = 16 * i + g + ((e >> 1) << 3);
+        const int r = (e & 1) ? r1 : r0;
+        if (r >= rows) continue;
+        const float val = oacc[i][e] * ((e & 1) ? inv1 : inv0);
+        const int hq = kvh * a.group + r % a.group;
+        const int qi = r / a.group;
+        if (direct) {
+          const size_t o = ((static_cast<size_t>(b) * p.Hq + hq) * p.Nq + qi) * kD + d;
+          if (p.q_dtype == 0) reinterpret_cast<__half*>(p.out)[o] = __float2half_rn(val);
+          else reinterpret_cast<__nv_bfloat16*>(p.out)[o] = __float2bfloat16_rn(val);
+        } else {
+          part_o[(static_cast<size_t>(slot) * HqNq + hq * p.Nq + qi) * kD + d] = val;
+        }
+      }
+    }
+    if (t == 0 && row_valid) {
+      if (direct) {
+        if (p.lse != nullptr) p.lse[(static_cast<size_t>(b) * p.Hq + hq_row) * p.Nq + qi_row] = lse_row;
+      } else {
+        part_lse[static_cast<size_t>(slot) * HqNq + hq_row * p.Nq + qi_row] = lse_row;
+      }
+    }
+
+    if (!direct) {
+      __threadfence();
+      named_bar_sync(1, HPC * 32);
+      if (tid == 0) {
+        const int old = atomicAdd(&counters[b * a.HG + hg], 1);
+        *s_last = (old == n_parts - 1) ? 1 : 0;
+      }
+      named_bar_sync(1, HPC * 32);
+      const bool last = *s_last != 0;
+      if (last) {
+        __threadfence();
+        // combine: L = log2 sum_i 2^lse_i ; O = sum_i 2^(lse_i - L) O_i  (csrc/mfa_steel_fwd.cpp:2066-2101)
+        for (int r = 0; r < rows; ++r) {
+          const int hq = kvh * a.group + r % a.group;
+          const int qi = r / a.group;
+          const size_t rowi = static_cast<size_t>(hq) * p.Nq + qi;
+          float mmax = -INFINITY;
+          for (int i = 0; i < n_parts; ++i)
+            mmax = fmaxf(mmax, __ldcg(&part_lse[static_cast<size_t>(c_first + i + b) * HqNq + rowi]));
+          const float msb = (mmax == -INFINITY) ? 0.f : mmax;
+          float wsum = 0.f;
+          float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+          for (int i = 0; i < n_parts; ++i) {
+            const size_t sl = static_cast<size_t>(c_first + i + b);
+            const float w = exp2f(__ldcg(&part_lse[sl * HqNq + rowi]) - msb);
+            wsum += w;
+            const float4 v4 = __ldcg(reinterpret_cast<const float4*>(&part_o[(sl * HqNq + rowi) * kD + lane * 4]));
+            acc.x = fmaf(w, v4.x, acc.x); acc.y = fmaf(w, v4.y, acc.y);
+            acc.z = fmaf(w, v4.z, acc.z); acc.w = fmaf(w, v4.w, acc.w);
+          }
+          const float inv = wsum > 0.f ? 1.f / wsum : 0.f;
+          const size_t o = ((static_cast<size_t>(b) * p.Hq + hq) * p.Nq + qi) * kD + lane * 4;
+          if (p.q_dtype == 0) {
+            __half2 h0 = __floats2half2_rn(acc.x * inv, acc.y * inv), h1 = __floats2half2_rn(acc.z * inv, acc.w * inv);
+            uint2 pk = make_uint2(*reinterpret_cast<uint32_t*>(&h0), *reinterpret_cast<uint32_t*>(&h1));
+            *reinterpret_cast<uint2*>(reinterpret_cast<__half*>(p.out) + o) = pk;
+          } else {
+            __nv_bfloat162 h0 = __floats2bfloat162_rn(acc.x * inv, acc.y * inv), h1 = __floats2bfloat162_rn(acc.z * inv, acc.w * inv);
+            uint2 pk = make_uint2(*reinterpret_cast<uint32_t*>(&h0), *reinterpret_cast<uint32_t*>(&h1));
+            *reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(p.out) + o) = pk;
+          }
+          if (p.lse != nullptr && lane == 0)
+            p.lse[(static_cast<size_t>(b) * p.Hq + hq) * p.Nq + qi] = wsum > 0.f ? mmax + log2f(wsum) : -INFINITY;
+        }
+      }
+      named_bar_sync(1, HPC * 32);   // s_last is reused by the next sequence
+    }
+
+    u = static_cast<long long>(s0) + j_hi;
+    if (u >= s1) ++b;
+  }
+  if (!ok && lane == 0) atomicOr(err, 1);
+}
+
+int device_sm_count() {
+  static int cached[64] = {0};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+  if (cached[dev] == 0) {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+    cached[dev] = n;
+  }
+  return cached[dev];
+}
+
+int pick_hpc(int Hkv) {
+  if (Hkv % 8 == 0) return 8;
+  if (Hkv % 4 == 0) return 4;
+  if (Hkv % 2 == 0) return 2;
+  return 1;
+}
+
+int pick_grid_x(int Hkv, int num_splits) {
+  const int hpc = pick_hpc(Hkv);
+  const int hg = Hkv / hpc;
+  int target = device_sm_count() * (8 / hpc);     // CTAs in flight over the whole grid
+  int gx = (target + hg - 1) / hg;
+  if (gx < 1) gx = 1;
+  if (num_splits > 0 && gx > num_splits) gx = num_splits;
+  return gx;
+}
+
+template <int KV, int HPC>
+cudaError_t launch_t(const CUtensorMap& tmK, const CUtensorMap& tmV, const KernelArgs& a, int gx, size_t smem,
+                     cudaStream_t stream) {
+  auto kern = decode_paged_kernel<KV, HPC>;
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+  if (e != cudaSuccess) return e;
+  dim3 grid(gx, a.HG);
+  kern<<<grid, (HPC + 1) * 32, smem, stream>>>(tmK, tmV, a);
+  return cudaGetLastError();
+}
+
+template <int KV>
+cudaError_t launch_kv(int hpc, const CUtensorMap& tmK, const CUtensorMap& tmV, const KernelArgs& a, int gx,
+                      size_t smem, cudaStream_t stream) {
+  switch (hpc) {
+    case 8: return launch_t<KV, 8>(tmK, tmV, a, gx, smem, stream);
+    case 4: return launch_t<KV, 4>(tmK, tmV, a, gx, smem, stream);
+    case 2: return launch_t<KV, 2>(tmK, tmV, a, gx, smem, stream);
+    default: return launch_t<KV, 1>(tmK, tmV, a, gx, smem, stream);
+  }
+}
+
+}  // namespace
+
+size_t decode_workspace_bytes(int B, int Hq, int Hkv, int Nq, int D, int max_kv_len, int num_splits) {
+  (void)D; (void)max_kv_len;
+  if (B <= 0 || Hq <= 0 || Hkv <= 0 || Nq <= 0) return 16;
+  const int hpc = pick_hpc(Hkv);
+  return make_layout(B, Hq, Nq, Hkv / hpc, pick_grid_x(Hkv, num_splits)).total;
+}
+
+cudaError_t launch_decode_paged(const DecodeParams& p, cudaStream_t stream, char* msg, size_t msg_len) {
+  const bool quant = p.kv_dtype == 3 || p.kv_dtype == 4;
+  const int hpc = pick_hpc(p.Hkv);
+  const int HG = p.Hkv / hpc;
+  const int gx = pick_grid_x(p.Hkv, p.num_splits);
+  const int row_bytes = quant ? kD : 2 * kD;
+
+  KernelArgs a;
+  a.p = p;
+  a.lay = make_layout(p.B, p.Hq, p.Nq, HG, gx);
+  a.HG = HG;
+  a.group = p.Hq / p.Hkv;
+  a.rows = a.group * p.Nq;
+  a.stage_kv_bytes = hpc * kBS * row_bytes;
+  a.scale_bytes = quant ? kBS * p.Hkv * 2 : 0;
+  const size_t per_stage = 2 * static_cast<size_t>(a.stage_kv_bytes) + 2 * static_cast<size_t>(a.scale_bytes);
+  // several small CTAs share an SM when a CTA holds few heads
+  const size_t budget = hpc == 8 ? 200 * 1024 : (hpc == 4 ? 100 * 1024 : (hpc == 2 ? 50 * 1024 : 26 * 1024));
+  int stages = static_cast<int>(budget / per_stage);
+  if (stages > kMaxStages) stages = kMaxStages;
+  if (stages < 2) {
+    snprintf(msg, msg_len, "Hkv=%d needs %zu bytes per stage; too large for the stage ring", p.Hkv, per_stage);
+    return cudaErrorNotSupported;
+  }
+  a.stages = stages;
+  const float sc = p.softcap > 0.f ? p.scale : p.scale * kLog2e;
+  a.q_prescale = sc;
+  a.cap_log2 = p.softcap * kLog2e;
+  a.inv_cap = p.softcap > 0.f ? 1.f / p.softcap : 0.f;
+  const size_t smem = 1024 + static_cast<size_t>(stages) * per_stage + 2 * kMaxStages * 8 + kMaxStages * 4 + 64;
+
+  // tensor maps over the pools: (128 B, tokens, halves of a row, heads, 1)
+  CUtensorMap tmK, tmV;
+  const uint64_t tokens = static_cast<uint64_t>(p.num_pages) * kBS;
+  const uint64_t dims[5] = {128, tokens, static_cast<uint64_t>(row_bytes / 128), static_cast<uint64_t>(p.Hkv), 1};
+  const uint64_t strides[4] = {static_cast<uint64_t>(p.Hkv) * row_bytes, 128, static_cast<uint64_t>(row_bytes),
+                               tokens * p.Hkv * row_bytes};
+  const uint32_t box[5] = {128, kBS, static_cast<uint32_t>(row_bytes / 128), static_cast<uint32_t>(hpc), 1};
+  if (!encode_tmap(&tmK, CU_TENSOR_MAP_DATA_TYPE_UINT8, 5, p.k_pool, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B) ||
+      !encode_tmap(&tmV, CU_TENSOR_MAP_DATA_TYPE_UINT8, 5, p.v_pool, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B)) {
+    snprintf(msg, msg_len, "cuTensorMapEncodeTiled failed for the page pools");
+    return cudaErrorInvalidValue;
+  }
+
+  unsigned char* ws = reinterpret_cast<unsigned char*>(p.workspace);
+  decode_plan_kernel<<<1, 1024, 0, stream>>>(p.seq_lens, p.B, p.max_kv_len, p.B * HG,
+                                             reinterpret_cast<int*>(ws + a.lay.err),
+                                             reinterpret_cast<int*>(ws + a.lay.counters),
+                                             reinterpret_cast<int*>(ws + a.lay.page_start));
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return e;
+  switch (p.kv_dtype) {
+    case 0: return launch_kv<KV_F16>(hpc, tmK, tmV, a, gx, smem, stream);
+    case 1: return launch_kv<KV_BF16>(hpc, tmK, tmV, a, gx, smem, stream);
+    case 3: return launch_kv<KV_I8>(hpc, tmK, tmV, a, gx, smem, stream);
+    case 4: return launch_kv<KV_E4M3>(hpc, tmK, tmV, a, gx, smem, stream);
+    default: snprintf(msg, msg_len, "kv_dtype %d", p.kv_dtype); return cudaErrorNotSupported;
+  }
+}
+
+}  // namespace b200fa

@@ -1,0 +1,135 @@
+"""GPU parity of the paged split-KV decode kernel against the CPU oracle (gather pages,
+dequantise to the query dtype, attend per sequence to its exact length), 2e-2 max-abs.
+Cases follow the reference's paged tests (tests/test_attention.py in the reference:
+two sequences of different length with -1 padding 3812-3857, decode rows 1525-1598)."""
+import numpy as np
+import pytest
+import torch
+
+import mlx_flashattention_steel_b200 as fa
+from mlx_flashattention_steel_b200 import attention as A
+from oracle import sdpa_oracle as orc
+
+from .util import assert_close, make_paged, randn
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(autouse=True)
+def _status_checks():
+    old = A._set_check_decode_status(True)
+    yield
+    A._set_check_decode_status(old)
+
+
+def _run(dev, qdtype, quant, B, Hq, Hkv, Nq, lens, seed, causal=True, softcap=0.0, num_splits=0, holes=False, tol=2e-2):
+    pg = make_paged(B, Hkv, 128, 16, lens, qdtype, seed, quant=quant)
+    table = pg["block_table"].clone()
+    if holes:
+        table[B - 1, 1] = -1
+    q = randn((B, Hq, Nq, 128), qdtype, seed + 7)
+    ks, vs = pg["k_scale"], pg["v_scale"]
+    out, lse = fa.flash_attention_paged(
+        q.to(dev), pg["k"].to(dev), pg["v"].to(dev), table.to(dev), pg["seq_lens"].to(dev), causal=causal,
+        k_scale=None if ks is None else ks.to(dev), v_scale=None if vs is None else vs.to(dev), softcap=softcap,
+        return_lse=True, num_splits=num_splits)
+    torch.cuda.synchronize()
+    O, L = orc.paged_attention(q, pg["k"], pg["v"], table, pg["seq_lens"], causal=causal, softcap=softcap,
+                               k_scale=ks, v_scale=vs)
+    assert out.shape == q.shape and out.dtype == qdtype
+    assert_close(out, O, qdtype, "out", tol)
+    assert_close(lse, L, qdtype, "lse", tol)
+
+
+LENS = [1, 16, 17, 500, 3000]
+
+
+@pytest.mark.parametrize("qdtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("quant", [None, "int8", "e4m3"])
+@pytest.mark.parametrize("num_splits", [0, 1, 3])
+def test_decode_kinds(dev, qdtype, quant, num_splits):
+    _run(dev, qdtype, quant, len(LENS), 32, 8, 1, LENS, 400, num_splits=num_splits)
+
+
+@pytest.mark.parametrize("Hq,Hkv", [(4, 1), (4, 2), (8, 4), (16, 16), (48, 24), (8, 1)])
+@pytest.mark.parametrize("quant", [None, "int8"])
+def test_decode_head_layouts(dev, Hq, Hkv, quant):
+    _run(dev, torch.bfloat16, quant, 3, Hq, Hkv, 1, [33, 700, 129], 410)
+
+
+@pytest.mark.parametrize("Nq,Hq,Hkv", [(2, 8, 2), (4, 4, 2), (8, 2, 2), (5, 3, 3)])
+@pytest.mark.parametrize("causal", [False, True])
+def test_decode_several_query_rows(dev, Nq, Hq, Hkv, causal):
+    _run(dev, torch.float16, "int8", 4, Hq, Hkv, Nq, [16, 40, 333, 8], 420, causal=causal)
+    _run(dev, torch.bfloat16, None, 4, Hq, Hkv, Nq, [16, 40, 333, 8], 421, causal=causal)
+
+
+def test_decode_empty_sequences_and_holes(dev):
+    _run(dev, torch.bfloat16, "int8", 5, 32, 8, 1, [0, 100, 0, 48, 64], 430, holes=True)
+    _run(dev, torch.float16, None, 5, 8, 8, 1, [0, 100, 0, 48, 64], 431, holes=True)
+
+
+def test_decode_softcap(dev):
+    _run(dev, torch.bfloat16, "int8", 3, 32, 8, 1, [100, 2000, 31], 440, softcap=30.0)
+
+
+def test_decode_via_kvcache_entry(dev):
+    pg = make_paged(2, 8, 128, 16, [48, 32], torch.float16, 450)
+    q = randn((2, 32, 1, 128), torch.float16, 451)
+    out = fa.flash_attention_kvcache(q.to(dev), pg["k"].to(dev), pg["v"].to(dev), block_table=pg["block_table"].to(dev),
+                                     seq_lens=pg["seq_lens"].to(dev))
+    O, _ = orc.paged_attention(q, pg["k"], pg["v"], pg["block_table"], pg["seq_lens"], causal=True)
+    assert_close(out, O, torch.float16)
+
+
+def test_gather_route_for_long_queries(dev):
+    # (Hq/Hkv)*Nq > 8 -> gather + per-sequence attention, as the reference routes it
+    pg = make_paged(2, 2, 128, 16, [48, 100], torch.bfloat16, 460)
+    q = randn((2, 8, 16, 128), torch.bfloat16, 461)
+    out = fa.flash_attention_paged(q.to(dev), pg["k"].to(dev), pg["v"].to(dev), pg["block_table"].to(dev),
+                                   pg["seq_lens"].to(dev), causal=True)
+    O, _ = orc.paged_attention(q, pg["k"], pg["v"], pg["block_table"], pg["seq_lens"], causal=True)
+    assert_close(out, O, torch.bfloat16)
+
+
+def test_config4_shaped_reduced(dev):
+    """Config-4 shape with fewer, shorter sequences: B=24, lens ~ U[512, 6144], int8 KV, bf16 q."""
+    rng = np.random.default_rng(4)
+    lens = rng.integers(512, 6145, size=24).tolist()
+    _run(dev, torch.bfloat16, "int8", 24, 32, 8, 1, lens, 470)
+
+
+def test_full_size_properties(dev):
+    """Config 4 at full size (B=128, lens ~ U[512, 32768]) without the oracle:
+    (1) pools holding one constant value v (int8 x * scale) give O = v for every head;
+    (2) the int8 kernel agrees with the 16-bit kernel run on the dequantised pools."""
+    rng = np.random.default_rng(4)
+    B, Hq, Hkv, D, bs = 128, 32, 8, 128, 16
+    lens = rng.integers(512, 32769, size=B).astype(np.int32)
+    pages_per = (lens + bs - 1) // bs
+    P = int(pages_per.sum()) + 8
+    perm = rng.permutation(P)
+    table = -np.ones((B, int(pages_per.max())), dtype=np.int32)
+    pos = 0
+    for b in range(B):
+        table[b, :pages_per[b]] = perm[pos:pos + pages_per[b]]
+        pos += pages_per[b]
+    gd = torch.Generator(device=dev).manual_seed(4)
+    kq = torch.randint(-127, 128, (P, bs, Hkv, D), generator=gd, device=dev, dtype=torch.int8)
+    vq = torch.randint(-127, 128, (P, bs, Hkv, D), generator=gd, device=dev, dtype=torch.int8)
+    ksc = (torch.rand((P, bs, Hkv), generator=gd, device=dev) * 0.01 + 0.005).to(torch.float16)
+    vsc = (torch.rand((P, bs, Hkv), generator=gd, device=dev) * 0.02 + 0.01).to(torch.float16)
+    q = torch.randn((B, Hq, 1, D), generator=gd, device=dev).to(torch.bfloat16)
+    tt, lt = torch.from_numpy(table).to(dev), torch.from_numpy(lens).to(dev)
+    out = fa.flash_attention_paged(q, kq, vq, tt, lt, causal=True, k_scale=ksc, v_scale=vsc, max_kv_len=int(lens.max()))
+    # (2) same pools dequantised to bf16, 16-bit kernel
+    kd = (kq.float() * ksc.float().unsqueeze(-1)).to(torch.bfloat16)
+    vd = (vq.float() * vsc.float().unsqueeze(-1)).to(torch.bfloat16)
+    ref = fa.flash_attention_paged(q, kd, vd, tt, lt, causal=True, max_kv_len=int(lens.max()))
+    assert float((out.float() - ref.float()).abs().max()) <= 2e-2
+    del kd, vd
+    # (1) constant values
+    vq.fill_(50)
+    vsc.fill_(0.02)
+    outc = fa.flash_attention_paged(q, kq, vq, tt, lt, causal=True, k_scale=ksc, v_scale=vsc, max_kv_len=int(lens.max()))
+    assert float((outc.float() - 1.0).abs().max()) <= 1e-2

@@ -166,6 +166,41 @@ int32_t b200fa_decode_paged(const b200fa_desc* d, const void* q,
                             void* workspace, size_t workspace_bytes, void* stream);
 
 /*
+ * Paged decode for callers that cannot give it a workspace.  Same arguments and
+ * result as b200fa_decode_paged minus the workspace pair.  It has no counterpart in
+ * the reference, whose primitives get their scratch from MLX's allocator.
+ *
+ * Who needs it: a serving engine that has handed all of its device memory to the KV
+ * page pool at start-up and has no allocator left to ask at decode time; a host
+ * binding (cgo, JNI, a plugin ABI) that only passes the operator its input and output
+ * buffers; a latency-bound step that must not run into the device-wide stall a
+ * cudaMalloc/cudaFree can cause.  The split-KV partials, counters and page prefix
+ * sums live instead in a 16 MiB array inside the library's device image, which every
+ * GPU that loads the library holds until the process exits.
+ *
+ * Limits and rules:
+ *   - the problem must fit: b200fa_decode_paged_workspace_bytes(d, max_kv_len) <= 16 MiB
+ *     (config-4-sized decode, B=128 Hq=32 D=128, needs 4.6 MB); larger problems get
+ *     B200FA_ERR_WORKSPACE with an explanatory message and run nothing;
+ *   - the first call on each device looks up the array's device address (a host-side
+ *     query, no allocation); make that first call outside any stream capture;
+ *   - all calls on a device share the one array: two calls whose kernels can overlap
+ *     on the GPU (different streams, no ordering between them) race on it — serialise
+ *     them, or give the second one its own workspace through b200fa_decode_paged;
+ *   - what must start from zero (counters, error word) is cleared by the call itself;
+ *     the rest of the array keeps the previous call's partials and is overwritten
+ *     before it is read;
+ *   - it calls no cudaMalloc, cudaFree or allocating library routine.
+ */
+int32_t b200fa_decode_paged_static(const b200fa_desc* d, const void* q,
+                                   const void* k_pool, const void* v_pool,
+                                   const void* k_scale, const void* v_scale,
+                                   const int32_t* block_table, const int32_t* seq_lens,
+                                   int32_t num_pages, int32_t block_size, int32_t max_blocks,
+                                   int32_t max_kv_len,
+                                   void* out, float* lse, void* stream);
+
+/*
  * Reads the error word the decode kernel keeps at the start of its workspace
  * (0 = ok, bit 0 = a bounded wait inside the kernel gave up, bit 1 = a
  * block_table entry pointed beyond num_pages and was treated as a hole).

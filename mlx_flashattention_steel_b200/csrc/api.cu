@@ -106,6 +106,11 @@ int32_t fill_fwd_params(const b200fa_desc* d, const void* q, const void* k, cons
 
 }  // namespace
 
+namespace b200fa {
+// Lets entry points defined in other .cu files fill the thread-local error string.
+void set_last_error(const char* msg) { snprintf(g_err, sizeof(g_err), "%s", msg); }
+}  // namespace b200fa
+
 extern "C" {
 
 const char* b200fa_last_error(void) { return g_err; }

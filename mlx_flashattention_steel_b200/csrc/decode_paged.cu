@@ -27,6 +27,9 @@
 #include <cstdio>
 #include <type_traits>
 
+#include <mutex>
+
+#include "../../include/b200fa.h"
 #include "common.cuh"
 #include "decode.h"
 #include "tma.cuh"
@@ -802,3 +805,72 @@ cudaError_t launch_decode_paged(const DecodeParams& p, cudaStream_t stream, char
 }
 
 }  // namespace b200fa
+
+// ---------------------------------------------------------------------------
+// Decode without a caller-supplied workspace
+// ---------------------------------------------------------------------------
+// Scratch for b200fa_decode_paged_static: the same carve-up the workspace variant
+// uses (error word, per-sequence counters, page prefix sums, split partials), held in
+// a fixed array that every GPU loading this library keeps until the process exits.
+#define B200FA_STATIC_SCRATCH_BYTES (16u * 1024u * 1024u)
+static __device__ __align__(256) unsigned char g_decode_static_scratch[B200FA_STATIC_SCRATCH_BYTES];
+
+namespace b200fa {
+void set_last_error(const char* msg);
+
+namespace {
+// In host code the array's name is only a handle; the device address has to be asked
+// for, once per device, while that device is current.
+cudaError_t static_scratch_address(void** out) {
+  static std::mutex mu;
+  static void* addr[64] = {nullptr};
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return e;
+  if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
+  std::lock_guard<std::mutex> lock(mu);
+  if (addr[dev] == nullptr) {
+    void* p = nullptr;
+    e = cudaGetSymbolAddress(&p, g_decode_static_scratch);
+    if (e != cudaSuccess) return e;
+    addr[dev] = p;
+  }
+  *out = addr[dev];
+  return cudaSuccess;
+}
+}  // namespace
+}  // namespace b200fa
+
+extern "C" int32_t b200fa_decode_paged_static(const b200fa_desc* d, const void* q, const void* k_pool,
+                                              const void* v_pool, const void* k_scale, const void* v_scale,
+                                              const int32_t* block_table, const int32_t* seq_lens,
+                                              int32_t num_pages, int32_t block_size, int32_t max_blocks,
+                                              int32_t max_kv_len, void* out, float* lse, void* stream) {
+  if (d == nullptr) {
+    b200fa::set_last_error("descriptor is null");
+    return B200FA_ERR_INVALID_ARG;
+  }
+  const size_t need = b200fa_decode_paged_workspace_bytes(d, max_kv_len);
+  if (need > B200FA_STATIC_SCRATCH_BYTES) {
+    char msg[256];
+    snprintf(msg, sizeof(msg),
+             "b200fa_decode_paged_static: this problem needs %zu bytes of scratch, the built-in scratch holds %u; "
+             "use b200fa_decode_paged with a workspace, or lower B / Hq*N",
+             need, B200FA_STATIC_SCRATCH_BYTES);
+    b200fa::set_last_error(msg);
+    return B200FA_ERR_WORKSPACE;
+  }
+  void* scratch = nullptr;
+  cudaError_t e = b200fa::static_scratch_address(&scratch);
+  if (e != cudaSuccess) {
+    char msg[256];
+    snprintf(msg, sizeof(msg), "b200fa_decode_paged_static: cudaGetSymbolAddress failed: %s", cudaGetErrorString(e));
+    b200fa::set_last_error(msg);
+    return B200FA_ERR_CUDA;
+  }
+  // Same validation, planning and kernels as the workspace variant; the plan kernel
+  // clears the counters and the error word at the start of every call.
+  return b200fa_decode_paged(d, q, k_pool, v_pool, k_scale, v_scale, block_table, seq_lens, num_pages,
+                             block_size, max_blocks, max_kv_len, out, lse, scratch,
+                             B200FA_STATIC_SCRATCH_BYTES, stream);
+}

@@ -1,0 +1,459 @@
+// Blackwell forward kernel: tcgen05 MMAs with TMEM accumulators, TMA-staged tiles,
+// warp-specialised roles.  Dense layout, 16-bit, D = 128; any N, S; GQA; causal
+// (lower-right), left window, softcap, lse.  What it computes is the reference forward
+// (csrc/mfa_steel_fwd.cpp:801-1221); how is Blackwell's own:
+//
+//   warps 0-3  softmax: thread r owns query row r = TMEM lane r.  It pulls the row of
+//              S out of TMEM (tcgen05.ld), applies scale / softcap / masks, keeps the
+//              running max and sum, writes P (16-bit) back into the same TMEM columns
+//              (tcgen05.st) and, rarely, rescales O in TMEM (only when the row max grew
+//              by more than 2^8, so P stays small).
+//   warp 4     producer: TMA tensor copies of the Q tile (once) and of K / V tiles into
+//              two-stage rings, 128B-swizzled, completion on mbarriers.
+//   warp 5     MMA issue (one thread): S(j) = Q.K(j)^T  (SS, M=128 N=64 K=16 x8) into one
+//              of two S buffers, then O += P(j).V(j)  (A from TMEM, M=128 N=128 K=16 x4).
+//              Issue order S(0) S(1) PV(0) S(2) PV(1) ... keeps the tensor pipe busy while
+//              the softmax warps work on the other buffer; tcgen05.commit signals the
+//              mbarriers that free smem stages and publish S / O.
+//
+// TMEM (256 of 512 columns, so two CTAs share an SM and hide each other's softmax):
+//   [0,64) S0 / P0   [64,128) S1 / P1   [128,256) O.
+// Tiles above the causal diagonal or left of the window are skipped whole.
+// No load here uses cluster multicast.  Every mbarrier wait is bounded; on a timeout the
+// CTA raises its abort flag, frees its TMEM and leaves (outputs are then undefined and
+// the launch wrapper's status word says so).
+#include <cstdio>
+
+#include "common.cuh"
+#include "launch.h"
+#include "tma.cuh"
+
+namespace b200fa {
+
+namespace {
+
+constexpr int BM = 128;      // query rows per CTA
+constexpr int BN = 64;       // keys per tile
+constexpr int HD = 128;
+constexpr int kStages = 2;
+constexpr int kThreads = 192;
+constexpr uint32_t kTmemCols = 256;
+
+constexpr int kQBytes = BM * HD * 2;          // 32768: two 64-wide halves, [half][row][128 B]
+constexpr int kKVBytes = BN * HD * 2;         // 16384 per stage: [half][row][128 B]
+constexpr int kSmemTiles = kQBytes + 2 * kStages * kKVBytes;   // 98304
+constexpr int kSmemBytes = kSmemTiles + 256 + 1024;            // + barriers + alignment slack
+
+// barrier slots (uint64 each)
+enum Bar {
+  BAR_Q = 0,
+  BAR_K_FULL = 1,            // +stage
+  BAR_K_EMPTY = 3,
+  BAR_V_FULL = 5,
+  BAR_V_EMPTY = 7,
+  BAR_S_FULL = 9,            // +buffer
+  BAR_P_FULL = 11,           // +buffer
+  BAR_PV_DONE = 13,
+  BAR_COUNT = 14
+};
+
+struct Sm100Args {
+  FwdParams p;
+  int dtype;                 // 0 f16, 1 bf16
+  int* status;               // device word: bit 0 = a wait timed out (may be null)
+};
+
+// ---------------------------------------------------------------------------
+// tcgen05 wrappers
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ void tmem_alloc(uint32_t smem_dst, uint32_t cols) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_dst), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t addr, uint32_t cols) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(addr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory"); }
+__device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory"); }
+__device__ __forceinline__ void tc_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(bar) : "memory");
+}
+// D[tmem] (+)= A[smem] * B[smem]
+__device__ __forceinline__ void mma_ss(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t acc) {
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "setp.ne.b32 p, %4, 0;\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n"
+      "}\n" ::"r"(d_tmem),
+      "l"(adesc), "l"(bdesc), "r"(idesc), "r"(acc)
+      : "memory");
+}
+// D[tmem] (+)= A[tmem] * B[smem]
+__device__ __forceinline__ void mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t bdesc, uint32_t idesc, uint32_t acc) {
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "setp.ne.b32 p, %4, 0;\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n"
+      "}\n" ::"r"(d_tmem),
+      "r"(a_tmem), "l"(bdesc), "r"(idesc), "r"(acc)
+      : "memory");
+}
+
+// 32 lanes x 32 consecutive 32-bit columns: thread t of the warp gets its lane's columns
+__device__ __forceinline__ void tmem_ld32(uint32_t addr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];\n"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(addr)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_st32(uint32_t addr, const uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+      "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};\n" ::"r"(addr),
+      "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]),
+      "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]), "r"(r[18]),
+      "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]),
+      "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+      : "memory");
+}
+
+// Shared-memory matrix descriptor (sm_100 format): 128B swizzle, version 1.
+//   start address >> 4 in bits [0,14), leading byte offset >> 4 in [16,30),
+//   stride byte offset >> 4 in [32,46), version 1 in [46,48), layout 2 (SWIZZLE_128B) in [61,64).
+__device__ __forceinline__ uint64_t smem_desc(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+  uint64_t d = 0;
+  d |= static_cast<uint64_t>((saddr >> 4) & 0x3fffu);
+  d |= static_cast<uint64_t>((lbo_bytes >> 4) & 0x3fffu) << 16;
+  d |= static_cast<uint64_t>((sbo_bytes >> 4) & 0x3fffu) << 32;
+  d |= static_cast<uint64_t>(1) << 46;
+  d |= static_cast<uint64_t>(2) << 61;
+  return d;
+}
+
+// Instruction descriptor for kind::f16: f32 accumulate, A/B format (0 f16, 1 bf16),
+// A K-major, B K-major (b_mn = 0) or MN-major (b_mn = 1), N >> 3 at bit 17, M >> 4 at bit 24.
+__device__ __forceinline__ uint32_t instr_desc(int fmt, int b_mn, int M, int N) {
+  return (1u << 4) | (static_cast<uint32_t>(fmt) << 7) | (static_cast<uint32_t>(fmt) << 10) |
+         (static_cast<uint32_t>(b_mn) << 16) | (static_cast<uint32_t>(N >> 3) << 17) |
+         (static_cast<uint32_t>(M >> 4) << 24);
+}
+
+__device__ __forceinline__ uint32_t pack16(int dtype, float a, float b) {
+  return dtype == 0 ? Elem<__half>::pack(a, b) : Elem<__nv_bfloat16>::pack(a, b);
+}
+
+// ---------------------------------------------------------------------------
+// kernel
+// ---------------------------------------------------------------------------
+__global__ void __launch_bounds__(kThreads, 2)
+fa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                    const __grid_constant__ CUtensorMap tmV, const Sm100Args a) {
+  extern __shared__ __align__(1024) unsigned char smem_raw[];
+  unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  unsigned char* sQ = smem;
+  unsigned char* sK = sQ + kQBytes;
+  unsigned char* sV = sK + kStages * kKVBytes;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kSmemTiles);
+  uint32_t* s_tmem = reinterpret_cast<uint32_t*>(bars + BAR_COUNT);
+  volatile int* s_abort = reinterpret_cast<volatile int*>(s_tmem + 1);
+
+  const FwdParams& p = a.p;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int head = blockIdx.y, batch = blockIdx.z;
+  const int kvh = head / p.gqa;
+  const int N = p.N, S = p.S;
+  const int q0 = (static_cast<int>(gridDim.x) - 1 - static_cast<int>(blockIdx.x)) * BM;
+  const int off = S - N;
+  int k_hi = S;
+  if (p.causal) k_hi = min(S, q0 + BM + off);
+  int k_lo = 0;
+  if (p.window_left >= 0) k_lo = max(0, q0 + off - p.window_left);
+  const int kt_begin = k_lo / BN;
+  const int kt_end = k_hi > 0 ? (k_hi + BN - 1) / BN : 0;
+  const int n_tiles = kt_end - kt_begin;
+
+  auto bar = [&](int i) -> uint32_t { return smem_u32(&bars[i]); };
+
+  if (n_tiles <= 0) {
+    // no visible key for any row of this tile: O = 0, lse = -inf
+    if (warp < 4) {
+      const int row = q0 + tid;
+      if (row < N) {
+        uint4* orow = reinterpret_cast<uint4*>(reinterpret_cast<uint16_t*>(p.o) + batch * p.o_bs + head * p.o_hs +
+                                               static_cast<int64_t>(row) * p.o_rs);
+#pragma unroll
+        for (int i = 0; i < HD / 8; ++i) orow[i] = make_uint4(0u, 0u, 0u, 0u);
+        if (p.lse != nullptr) p.lse[batch * p.lse_bs + head * p.lse_hs + row] = -INFINITY;
+      }
+    }
+    return;
+  }
+
+  if (tid == 0) {
+    mbar_init(bar(BAR_Q), 1);
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(bar(BAR_K_FULL + s), 1);
+      mbar_init(bar(BAR_K_EMPTY + s), 1);
+      mbar_init(bar(BAR_V_FULL + s), 1);
+      mbar_init(bar(BAR_V_EMPTY + s), 1);
+      mbar_init(bar(BAR_S_FULL + s), 1);
+      mbar_init(bar(BAR_P_FULL + s), 4);     // one arrive per softmax warp
+    }
+    mbar_init(bar(BAR_PV_DONE), 1);
+    *s_abort = 0;
+    fence_barrier_init();
+    fence_proxy_async();
+  }
+  if (warp == 5) {
+    tmem_alloc(smem_u32(s_tmem), kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *s_tmem;
+  const uint32_t tS0 = tmem, tO = tmem + 128;   // S buffers at +0 and +64, O at +128
+
+  if (warp == 4) {
+    // ============================ producer ============================
+    if (lane == 0) {
+      mbar_arrive_expect_tx(bar(BAR_Q), kQBytes);
+      tma_load_4d(smem_u32(sQ), &tmQ, bar(BAR_Q), 0, q0, head, batch);
+      tma_load_4d(smem_u32(sQ + kQBytes / 2), &tmQ, bar(BAR_Q), 64, q0, head, batch);
+      for (int j = 0; j < n_tiles; ++j) {
+        const int st = j & 1;
+        const uint32_t par = ((j >> 1) & 1) ^ 1;
+        const int krow = (kt_begin + j) * BN;
+        if (!mbar_wait_bounded(bar(BAR_K_EMPTY + st), par, s_abort)) break;
+        mbar_arrive_expect_tx(bar(BAR_K_FULL + st), kKVBytes);
+        tma_load_4d(smem_u32(sK + st * kKVBytes), &tmK, bar(BAR_K_FULL + st), 0, krow, kvh, batch);
+        tma_load_4d(smem_u32(sK + st * kKVBytes + kKVBytes / 2), &tmK, bar(BAR_K_FULL + st), 64, krow, kvh, batch);
+        if (!mbar_wait_bounded(bar(BAR_V_EMPTY + st), par, s_abort)) break;
+        mbar_arrive_expect_tx(bar(BAR_V_FULL + st), kKVBytes);
+        tma_load_4d(smem_u32(sV + st * kKVBytes), &tmV, bar(BAR_V_FULL + st), 0, krow, kvh, batch);
+        tma_load_4d(smem_u32(sV + st * kKVBytes + kKVBytes / 2), &tmV, bar(BAR_V_FULL + st), 64, krow, kvh, batch);
+      }
+    }
+  } else if (warp == 5) {
+    // ============================ MMA issue ============================
+    if (lane == 0) {
+      const uint32_t idesc_qk = instr_desc(a.dtype, 0, BM, BN);
+      const uint32_t idesc_pv = instr_desc(a.dtype, 1, BM, HD);
+      const uint32_t q_addr = smem_u32(sQ);
+      bool ok = mbar_wait_bounded(bar(BAR_Q), 0, s_abort);
+      auto issue_s = [&](int j) -> bool {
+        const int st = j & 1;
+        if (!mbar_wait_bounded(bar(BAR_K_FULL + st), (j >> 1) & 1, s_abort)) return false;
+        tc_fence_after();
+        const uint32_t k_addr = smem_u32(sK + st * kKVBytes);
+#pragma unroll
+        for (int k = 0; k < HD / 16; ++k) {
+          // K-major operands: 64-wide halves of [rows][128 B]; a k-step of 16 elements is 32 B inside the swizzle row
+          const uint64_t ad = smem_desc(q_addr + (k >> 2) * (kQBytes / 2) + (k & 3) * 32, 16, 1024);
+          const uint64_t bd = smem_desc(k_addr + (k >> 2) * (kKVBytes / 2) + (k & 3) * 32, 16, 1024);
+          mma_ss(tS0 + st * 64, ad, bd, idesc_qk, k > 0 ? 1u : 0u);
+        }
+        tc_commit(bar(BAR_K_EMPTY + st));
+        tc_commit(bar(BAR_S_FULL + st));
+        return true;
+      };
+      if (ok) ok = issue_s(0);
+      for (int j = 0; j < n_tiles && ok; ++j) {
+        const int st = j & 1;
+        if (j + 1 < n_tiles) {
+          ok = issue_s(j + 1);
+          if (!ok) break;
+        }
+        if (!mbar_wait_bounded(bar(BAR_P_FULL + st), (j >> 1) & 1, s_abort)) { ok = false; break; }
+        if (!mbar_wait_bounded(bar(BAR_V_FULL + st), (j >> 1) & 1, s_abort)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t v_addr = smem_u32(sV + st * kKVBytes);
+#pragma unroll
+        for (int k = 0; k < BN / 16; ++k) {
+          // B = V, MN-major: [half][key][64 d]; 8-key groups 1024 B apart, d-halves kKVBytes/2 apart;
+          // a k-step is 16 keys = 2048 B.  A = P in TMEM: 16 16-bit values = 8 columns per k-step.
+          const uint64_t bd = smem_desc(v_addr + k * 2048, kKVBytes / 2, 1024);
+          mma_ts(tO, tS0 + st * 64 + k * 8, bd, idesc_pv, (j > 0 || k > 0) ? 1u : 0u);
+        }
+        tc_commit(bar(BAR_V_EMPTY + st));
+        tc_commit(bar(BAR_PV_DONE));
+      }
+    }
+  } else {
+    // ============================ softmax (warps 0-3) ============================
+    const int row = q0 + tid;                         // query row of this thread
+    const uint32_t lane_base = static_cast<uint32_t>(warp * 32) << 16;
+    const bool use_cap = p.softcap > 0.f;
+    const float cap_in = use_cap ? p.scale / p.softcap : 0.f;
+    const float cap_out = p.softcap * kLog2e;
+    float m_used = -INFINITY, l_run = 0.f;
+    bool ok = true;
+
+    for (int j = 0; j < n_tiles; ++j) {
+      const int st = j & 1;
+      const int k0 = (kt_begin + j) * BN;
+      if (!__all_sync(0xffffffffu, mbar_wait_bounded(bar(BAR_S_FULL + st), (j >> 1) & 1, s_abort))) { ok = false; break; }
+      tc_fence_after();
+      uint32_t r0[32], r1[32];
+      tmem_ld32(tS0 + lane_base + st * 64, r0);
+      tmem_ld32(tS0 + lane_base + st * 64 + 32, r1);
+      tc_wait_ld();
+      float s[BN];
+#pragma unroll
+      for (int i = 0; i < 32; ++i) { s[i] = __uint_as_float(r0[i]); s[32 + i] = __uint_as_float(r1[i]); }
+
+      if (use_cap) {
+#pragma unroll
+        for (int i = 0; i < BN; ++i) s[i] = cap_out * fast_tanh(s[i] * cap_in);
+      } else {
+#pragma unroll
+        for (int i = 0; i < BN; ++i) s[i] *= p.scale_log2;
+      }
+      const bool need_mask = (k0 + BN > S) || (p.causal && (k0 + BN - 1 > q0 + off)) ||
+                             (p.window_left >= 0 && (k0 < q0 + BM - 1 + off - p.window_left));
+      if (need_mask) {
+        const int hi = p.causal ? min(S - 1, row + off) : S - 1;       // last visible key
+        const int lo = p.window_left >= 0 ? row + off - p.window_left : 0;
+#pragma unroll
+        for (int i = 0; i < BN; ++i) {
+          const int col = k0 + i;
+          if (col > hi || col < lo) s[i] = -INFINITY;
+        }
+      }
+      float m_tile = s[0];
+#pragma unroll
+      for (int i = 1; i < BN; ++i) m_tile = fmaxf(m_tile, s[i]);
+
+      // lazy rescale: keep the old reference max unless the row max grew by more than 2^8
+      const bool need = m_tile > m_used + 8.f;
+      if (__any_sync(0xffffffffu, need)) {
+        const float m_new = fmaxf(m_used, m_tile);
+        const float corr = (m_new == -INFINITY) ? 1.f : fast_exp2(m_used - m_new);
+        l_run *= corr;
+        if (j > 0) {
+          // O is being accumulated by PV(j-1): wait for it, then scale this row in TMEM
+          if (!__all_sync(0xffffffffu, mbar_wait_bounded(bar(BAR_PV_DONE), (j - 1) & 1, s_abort))) { ok = false; break; }
+          tc_fence_after();
+#pragma unroll
+          for (int c = 0; c < HD / 32; ++c) {
+            uint32_t o[32];
+            tmem_ld32(tO + lane_base + c * 32, o);
+            tc_wait_ld();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * corr);
+            tmem_st32(tO + lane_base + c * 32, o);
+          }
+        }
+        m_used = m_new;
+      }
+      const float msub = (m_used == -INFINITY) ? 0.f : m_used;
+      uint32_t pk[32];
+#pragma unroll
+      for (int i = 0; i < BN; i += 2) {
+        const float p0 = fast_exp2(s[i] - msub);
+        const float p1 = fast_exp2(s[i + 1] - msub);
+        l_run += p0 + p1;
+        pk[i >> 1] = pack16(a.dtype, p0, p1);
+      }
+      // P(j) overwrites the first 32 columns of S(j): lane = row, column c = keys (2c, 2c+1)
+      tmem_st32(tS0 + lane_base + st * 64, pk);
+      tc_wait_st();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar(BAR_P_FULL + st));
+    }
+
+    // ---- epilogue: O / l -> global, lse ----
+    if (ok) ok = __all_sync(0xffffffffu, mbar_wait_bounded(bar(BAR_PV_DONE), (n_tiles - 1) & 1, s_abort));
+    if (ok) {
+      tc_fence_after();
+      const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
+      uint16_t* orow = reinterpret_cast<uint16_t*>(p.o) + batch * p.o_bs + head * p.o_hs + static_cast<int64_t>(row) * p.o_rs;
+#pragma unroll
+      for (int c = 0; c < HD / 32; ++c) {
+        uint32_t o[32];
+        tmem_ld32(tO + lane_base + c * 32, o);
+        tc_wait_ld();
+        if (row < N) {
+#pragma unroll
+          for (int i = 0; i < 32; i += 8) {
+            uint4 v;
+            v.x = pack16(a.dtype, __uint_as_float(o[i]) * inv, __uint_as_float(o[i + 1]) * inv);
+            v.y = pack16(a.dtype, __uint_as_float(o[i + 2]) * inv, __uint_as_float(o[i + 3]) * inv);
+            v.z = pack16(a.dtype, __uint_as_float(o[i + 4]) * inv, __uint_as_float(o[i + 5]) * inv);
+            v.w = pack16(a.dtype, __uint_as_float(o[i + 6]) * inv, __uint_as_float(o[i + 7]) * inv);
+            *reinterpret_cast<uint4*>(orow + c * 32 + i) = v;
+          }
+        }
+      }
+      if (p.lse != nullptr && row < N)
+        p.lse[batch * p.lse_bs + head * p.lse_hs + row] = l_run > 0.f ? m_used + log2f(l_run) : -INFINITY;
+    }
+  }
+
+  // ---- teardown: everyone meets, then the allocating warp frees TMEM ----
+  __syncwarp();
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 5) {
+    tc_fence_after();
+    tmem_dealloc(tmem, kTmemCols);
+  }
+  if (tid == 0 && *s_abort != 0 && a.status != nullptr) atomicOr(a.status, 1);
+}
+
+bool make_map(CUtensorMap* m, int dtype, const void* base, int D, int rows, int H, int B, int64_t rs, int64_t hs,
+              int64_t bs, int box_rows) {
+  const uint64_t dims[4] = {static_cast<uint64_t>(D), static_cast<uint64_t>(rows), static_cast<uint64_t>(H),
+                            static_cast<uint64_t>(B)};
+  const uint64_t strides[3] = {static_cast<uint64_t>(rs) * 2, static_cast<uint64_t>(hs) * 2, static_cast<uint64_t>(bs) * 2};
+  const uint32_t box[4] = {64, static_cast<uint32_t>(box_rows), 1, 1};
+  return encode_tmap(m, dtype == 0 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, base, dims,
+                     strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
+}
+
+}  // namespace
+
+bool fwd_sm100_supported(const FwdParams& p, int dtype, int D) {
+  if (!(dtype == 0 || dtype == 1) || D != HD) return false;
+  if (p.N <= 0 || p.S <= 0 || p.B <= 0) return false;
+  // TMA: a size-1 dimension still needs a legal stride; strides were validated as 16-byte multiples
+  return get_encode_tiled() != nullptr;
+}
+
+cudaError_t launch_fwd_sm100(const FwdParams& p, int dtype, int D, cudaStream_t stream) {
+  (void)D;
+  CUtensorMap tmQ, tmK, tmV;
+  auto fix = [](int64_t s, int64_t fallback) { return s > 0 ? s : fallback; };
+  const int64_t q_hs = fix(p.q_hs, static_cast<int64_t>(p.N) * p.q_rs), q_bs = fix(p.q_bs, q_hs * p.Hq);
+  const int64_t k_hs = fix(p.k_hs, static_cast<int64_t>(p.S) * p.k_rs), k_bs = fix(p.k_bs, k_hs * p.Hkv);
+  const int64_t v_hs = fix(p.v_hs, static_cast<int64_t>(p.S) * p.v_rs), v_bs = fix(p.v_bs, v_hs * p.Hkv);
+  if (!make_map(&tmQ, dtype, p.q, HD, p.N, p.Hq, p.B, p.q_rs, q_hs, q_bs, BM) ||
+      !make_map(&tmK, dtype, p.k, HD, p.S, p.Hkv, p.B, p.k_rs, k_hs, k_bs, BN) ||
+      !make_map(&tmV, dtype, p.v, HD, p.S, p.Hkv, p.B, p.v_rs, v_hs, v_bs, BN))
+    return cudaErrorInvalidValue;
+  Sm100Args a;
+  a.p = p;
+  a.dtype = dtype;
+  a.status = nullptr;
+  cudaError_t e = cudaFuncSetAttribute(fa_fwd_sm100_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+  if (e != cudaSuccess) return e;
+  dim3 grid((p.N + BM - 1) / BM, p.Hq, p.B);
+  fa_fwd_sm100_kernel<<<grid, kThreads, kSmemBytes, stream>>>(tmQ, tmK, tmV, a);
+  return cudaGetLastError();
+}
+
+}  // namespace b200fa

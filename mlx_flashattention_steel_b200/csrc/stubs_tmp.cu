@@ -3,8 +3,6 @@
 #include "decode.h"
 #include "launch.h"
 namespace b200fa {
-bool fwd_sm100_supported(const FwdParams&, int, int) { return false; }
-cudaError_t launch_fwd_sm100(const FwdParams&, int, int, cudaStream_t) { return cudaErrorNotSupported; }
 size_t bwd_workspace_bytes(int, int, int, int) { return 16; }
 cudaError_t launch_bwd(const BwdParams&, int, int, bool, int, int, int, void*, cudaStream_t) { return cudaErrorNotSupported; }
 }

@@ -168,14 +168,15 @@ def workload_config(n):
             "l2": "inputs (403 MB) exceed L2 (126 MB); no explicit flush"}
 
 
-def bench_decode(device, steps, warmup, pk):
+def bench_decode(device, steps, warmup, pk, batch=None):
     """Config 4: paged int8-KV decode, B=128, seq_lens ~ U[512, 32768], page 16."""
     import numpy as np
 
     import mlx_flashattention_steel_b200 as fa
-    from mlx_flashattention_steel_b200 import attention as A
 
-    cfg = C4
+    cfg = dict(C4)
+    if batch:
+        cfg["B"] = batch
     rng = np.random.default_rng(4)
     lens = rng.integers(cfg["lo"], cfg["hi"] + 1, size=cfg["B"]).astype(np.int32)
     bs, Hkv, D = cfg["block_size"], cfg["Hkv"], cfg["D"]
@@ -239,7 +240,9 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-decode", action="store_true", help="skip the config-4 decode measurement")
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--small", action="store_true", help="profiling aid: N=S=4096, B=1 (not a bench value)")
+    ap.add_argument("--small", action="store_true", help="profiling aid: N=S=4096, B=2 (not a bench value)")
+    ap.add_argument("--only-decode", type=int, default=0, metavar="B",
+                    help="profiling aid: run only the decode measurement with batch B (not a bench value)")
     args = ap.parse_args()
 
     rank = int(os.environ.get("RANK", "0"))
@@ -263,9 +266,12 @@ def main():
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         dist.init_process_group("nccl", device_id=device)
     pk = peaks()
+    if args.only_decode:
+        print(json.dumps(bench_decode(device, args.steps, args.warmup, pk, batch=args.only_decode)), flush=True)
+        return
     cfg = dict(C2)
     if args.small:
-        cfg.update(B=1, N=4096, S=4096)
+        cfg.update(B=2, N=4096, S=4096)
     q, k, v = make_prefill_inputs(cfg, device, seed=2 + rank)
     flops = prefill_flops(cfg)
     warm = max(args.warmup, 3)
@@ -301,6 +307,10 @@ def main():
     ms = ms_total / args.steps
     tf_rank = flops / (ms * 1e-3) / 1e12
     value = tf_rank * world
+
+    if args.small:
+        print(json.dumps({"note": "--small profiling case, not a bench value", "ms_per_step": ms, "tflops": tf_rank}), flush=True)
+        return
 
     # ---- end to end through the public API with pinned host buffers ----
     hq, hk, hv = (t.cpu().pin_memory() for t in (q, k, v))

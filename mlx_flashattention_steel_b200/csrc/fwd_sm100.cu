@@ -151,6 +151,41 @@ __device__ __forceinline__ uint32_t instr_desc(int fmt, int b_mn, int M, int N) 
          (static_cast<uint32_t>(M >> 4) << 24);
 }
 
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;\n" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
+__device__ __forceinline__ float min3(float a, float b, float c) {
+  float d;
+  asm("min.f32 %0, %1, %2, %3;\n" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
+
+// max / min of 64 values as a 3-ary tree (depth 4) instead of a 63-deep dependent chain
+__device__ __forceinline__ float tree_max64(const float (&x)[64]) {
+  float a[22];
+#pragma unroll
+  for (int i = 0; i < 21; ++i) a[i] = max3(x[3 * i], x[3 * i + 1], x[3 * i + 2]);
+  a[21] = x[63];
+  float b[8];
+#pragma unroll
+  for (int i = 0; i < 7; ++i) b[i] = max3(a[3 * i], a[3 * i + 1], a[3 * i + 2]);
+  b[7] = a[21];
+  return max3(max3(b[0], b[1], b[2]), max3(b[3], b[4], b[5]), fmaxf(b[6], b[7]));
+}
+__device__ __forceinline__ float tree_min64(const float (&x)[64]) {
+  float a[22];
+#pragma unroll
+  for (int i = 0; i < 21; ++i) a[i] = min3(x[3 * i], x[3 * i + 1], x[3 * i + 2]);
+  a[21] = x[63];
+  float b[8];
+#pragma unroll
+  for (int i = 0; i < 7; ++i) b[i] = min3(a[3 * i], a[3 * i + 1], a[3 * i + 2]);
+  b[7] = a[21];
+  return min3(min3(b[0], b[1], b[2]), min3(b[3], b[4], b[5]), fminf(b[6], b[7]));
+}
+
 __device__ __forceinline__ uint32_t pack16(int dtype, float a, float b) {
   return dtype == 0 ? Elem<__half>::pack(a, b) : Elem<__nv_bfloat16>::pack(a, b);
 }
@@ -252,19 +287,24 @@ fa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     if (lane == 0) {
       const uint32_t idesc_qk = instr_desc(a.dtype, 0, BM, BN);
       const uint32_t idesc_pv = instr_desc(a.dtype, 1, BM, HD);
-      const uint32_t q_addr = smem_u32(sQ);
+      // Descriptors differ only in their start-address field (low word); build the bases once so that
+      // the issue loop is a handful of integer adds per MMA.
+      const uint64_t qd = smem_desc(smem_u32(sQ), 16, 1024);
+      const uint64_t kd0 = smem_desc(smem_u32(sK), 16, 1024);
+      const uint64_t vd0 = smem_desc(smem_u32(sV), kKVBytes / 2, 1024);
+      constexpr uint64_t kHalfQ = (kQBytes / 2) >> 4, kHalfK = (kKVBytes / 2) >> 4, kStageKV = kKVBytes >> 4;
       bool ok = mbar_wait_bounded(bar(BAR_Q), 0, s_abort);
       auto issue_s = [&](int j) -> bool {
         const int st = j & 1;
         if (!mbar_wait_bounded(bar(BAR_K_FULL + st), (j >> 1) & 1, s_abort)) return false;
         tc_fence_after();
-        const uint32_t k_addr = smem_u32(sK + st * kKVBytes);
+        const uint64_t kd = kd0 + static_cast<uint64_t>(st) * kStageKV;
+        const uint32_t d_tmem = tS0 + st * 64;
 #pragma unroll
         for (int k = 0; k < HD / 16; ++k) {
-          // K-major operands: 64-wide halves of [rows][128 B]; a k-step of 16 elements is 32 B inside the swizzle row
-          const uint64_t ad = smem_desc(q_addr + (k >> 2) * (kQBytes / 2) + (k & 3) * 32, 16, 1024);
-          const uint64_t bd = smem_desc(k_addr + (k >> 2) * (kKVBytes / 2) + (k & 3) * 32, 16, 1024);
-          mma_ss(tS0 + st * 64, ad, bd, idesc_qk, k > 0 ? 1u : 0u);
+          // K-major operands: 64-wide halves of [rows][128 B]; a k-step of 16 elements is 32 B (2 units) inside the swizzle row
+          mma_ss(d_tmem, qd + (k >> 2) * kHalfQ + (k & 3) * 2, kd + (k >> 2) * kHalfK + (k & 3) * 2, idesc_qk,
+                 k > 0 ? 1u : 0u);
         }
         tc_commit(bar(BAR_K_EMPTY + st));
         tc_commit(bar(BAR_S_FULL + st));
@@ -280,13 +320,13 @@ fa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         if (!mbar_wait_bounded(bar(BAR_P_FULL + st), (j >> 1) & 1, s_abort)) { ok = false; break; }
         if (!mbar_wait_bounded(bar(BAR_V_FULL + st), (j >> 1) & 1, s_abort)) { ok = false; break; }
         tc_fence_after();
-        const uint32_t v_addr = smem_u32(sV + st * kKVBytes);
+        const uint64_t vd = vd0 + static_cast<uint64_t>(st) * kStageKV;
+        const uint32_t a_tmem = tS0 + st * 64;
 #pragma unroll
         for (int k = 0; k < BN / 16; ++k) {
           // B = V, MN-major: [half][key][64 d]; 8-key groups 1024 B apart, d-halves kKVBytes/2 apart;
-          // a k-step is 16 keys = 2048 B.  A = P in TMEM: 16 16-bit values = 8 columns per k-step.
-          const uint64_t bd = smem_desc(v_addr + k * 2048, kKVBytes / 2, 1024);
-          mma_ts(tO, tS0 + st * 64 + k * 8, bd, idesc_pv, (j > 0 || k > 0) ? 1u : 0u);
+          // a k-step is 16 keys = 2048 B (128 units).  A = P in TMEM: 16 16-bit values = 8 columns per k-step.
+          mma_ts(tO, a_tmem + k * 8, vd + k * 128, idesc_pv, (j > 0 || k > 0) ? 1u : 0u);
         }
         tc_commit(bar(BAR_V_EMPTY + st));
         tc_commit(bar(BAR_PV_DONE));
@@ -302,6 +342,11 @@ fa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     float m_used = -INFINITY, l_run = 0.f;
     bool ok = true;
 
+    const float kk = cap_in * cap_out;                // softcap on: scale * log2(e)
+    const float c2 = cap_in * cap_in;
+    const float b3 = (-1.f / 3.f) * c2, b5 = (2.f / 15.f) * c2 * c2, b7 = (-17.f / 315.f) * c2 * c2 * c2;
+    const bool monotone = p.scale > 0.f;              // lets the row max be taken on the raw dot products
+
     for (int j = 0; j < n_tiles; ++j) {
       const int st = j & 1;
       const int k0 = (kt_begin + j) * BN;
@@ -311,31 +356,57 @@ fa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       tmem_ld32(tS0 + lane_base + st * 64, r0);
       tmem_ld32(tS0 + lane_base + st * 64 + 32, r1);
       tc_wait_ld();
-      float s[BN];
+      float x[BN];                                     // raw q.k of this row
 #pragma unroll
-      for (int i = 0; i < 32; ++i) { s[i] = __uint_as_float(r0[i]); s[32 + i] = __uint_as_float(r1[i]); }
+      for (int i = 0; i < 32; ++i) { x[i] = __uint_as_float(r0[i]); x[32 + i] = __uint_as_float(r1[i]); }
 
-      if (use_cap) {
-#pragma unroll
-        for (int i = 0; i < BN; ++i) s[i] = cap_out * fast_tanh(s[i] * cap_in);
-      } else {
-#pragma unroll
-        for (int i = 0; i < BN; ++i) s[i] *= p.scale_log2;
-      }
       const bool need_mask = (k0 + BN > S) || (p.causal && (k0 + BN - 1 > q0 + off)) ||
                              (p.window_left >= 0 && (k0 < q0 + BM - 1 + off - p.window_left));
-      if (need_mask) {
-        const int hi = p.causal ? min(S - 1, row + off) : S - 1;       // last visible key
-        const int lo = p.window_left >= 0 ? row + off - p.window_left : 0;
-#pragma unroll
-        for (int i = 0; i < BN; ++i) {
-          const int col = k0 + i;
-          if (col > hi || col < lo) s[i] = -INFINITY;
+      const bool fast = !need_mask && monotone;
+      // mode 0: t = x*scale_log2 - m ; 1: softcap by polynomial ; 2: softcap by tanh.approx ; 3: general (masked tile)
+      int mode = 3;
+      float m_tile;
+      if (fast) {
+        // scale and softcap are increasing in x, so the tile max is f(max x): one pass of 3-input max
+        float xmax = tree_max64(x);
+        if (!use_cap) {
+          mode = 0;
+          m_tile = xmax * p.scale_log2;
+        } else {
+          // cap*tanh(x*scale/cap): while |x*scale/cap| <= 0.5 for the warp's rows the odd Taylor polynomial to
+          // y^7 (|error| < 4.3e-5) runs on the FMA pipe and leaves the special-function unit to exp2
+          const float xmin = tree_min64(x);
+          const bool small = fmaxf(xmax, -xmin) * cap_in <= 0.5f;
+          if (__all_sync(0xffffffffu, small)) {
+            mode = 1;
+            const float z = xmax * xmax;
+            m_tile = (xmax * kk) * fmaf(z, fmaf(z, fmaf(z, b7, b5), b3), 1.f);
+          } else {
+            mode = 2;
+            m_tile = cap_out * fast_tanh(xmax * cap_in);
+          }
         }
-      }
-      float m_tile = s[0];
+      } else {
+        if (use_cap) {
 #pragma unroll
-      for (int i = 1; i < BN; ++i) m_tile = fmaxf(m_tile, s[i]);
+          for (int i = 0; i < BN; ++i) x[i] = cap_out * fast_tanh(x[i] * cap_in);
+        } else {
+#pragma unroll
+          for (int i = 0; i < BN; ++i) x[i] *= p.scale_log2;
+        }
+        if (need_mask) {
+          const int hi = p.causal ? min(S - 1, row + off) : S - 1;       // last visible key
+          const int lo = p.window_left >= 0 ? row + off - p.window_left : 0;
+#pragma unroll
+          for (int i = 0; i < BN; ++i) {
+            const int col = k0 + i;
+            if (col > hi || col < lo) x[i] = -INFINITY;
+          }
+        }
+        m_tile = x[0];
+#pragma unroll
+        for (int i = 1; i < BN; ++i) m_tile = fmaxf(m_tile, x[i]);
+      }
 
       // lazy rescale: keep the old reference max unless the row max grew by more than 2^8
       const bool need = m_tile > m_used + 8.f;
@@ -360,14 +431,50 @@ fa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         m_used = m_new;
       }
       const float msub = (m_used == -INFINITY) ? 0.f : m_used;
+      const float2 nm2 = make_float2(-msub, -msub);
+      float2 lsum2 = make_float2(0.f, 0.f);
       uint32_t pk[32];
+      if (mode == 0) {
+        const float2 k2 = make_float2(p.scale_log2, p.scale_log2);
 #pragma unroll
-      for (int i = 0; i < BN; i += 2) {
-        const float p0 = fast_exp2(s[i] - msub);
-        const float p1 = fast_exp2(s[i + 1] - msub);
-        l_run += p0 + p1;
-        pk[i >> 1] = pack16(a.dtype, p0, p1);
+        for (int i = 0; i < BN; i += 2) {
+          const float2 t = __ffma2_rn(make_float2(x[i], x[i + 1]), k2, nm2);
+          const float2 e = make_float2(fast_exp2(t.x), fast_exp2(t.y));
+          lsum2 = __fadd2_rn(lsum2, e);
+          pk[i >> 1] = pack16(a.dtype, e.x, e.y);
+        }
+      } else if (mode == 1) {
+        const float2 kk2 = make_float2(kk, kk), b32 = make_float2(b3, b3), b52 = make_float2(b5, b5),
+                     b72 = make_float2(b7, b7), one2 = make_float2(1.f, 1.f);
+#pragma unroll
+        for (int i = 0; i < BN; i += 2) {
+          const float2 xv = make_float2(x[i], x[i + 1]);
+          const float2 z = __fmul2_rn(xv, xv);
+          float2 poly = __ffma2_rn(z, b72, b52);
+          poly = __ffma2_rn(z, poly, b32);
+          poly = __ffma2_rn(z, poly, one2);
+          const float2 t = __ffma2_rn(__fmul2_rn(xv, kk2), poly, nm2);
+          const float2 e = make_float2(fast_exp2(t.x), fast_exp2(t.y));
+          lsum2 = __fadd2_rn(lsum2, e);
+          pk[i >> 1] = pack16(a.dtype, e.x, e.y);
+        }
+      } else if (mode == 2) {
+#pragma unroll
+        for (int i = 0; i < BN; i += 2) {
+          const float2 e = make_float2(fast_exp2(fmaf(cap_out, fast_tanh(x[i] * cap_in), -msub)),
+                                       fast_exp2(fmaf(cap_out, fast_tanh(x[i + 1] * cap_in), -msub)));
+          lsum2 = __fadd2_rn(lsum2, e);
+          pk[i >> 1] = pack16(a.dtype, e.x, e.y);
+        }
+      } else {
+#pragma unroll
+        for (int i = 0; i < BN; i += 2) {
+          const float2 e = make_float2(fast_exp2(x[i] - msub), fast_exp2(x[i + 1] - msub));
+          lsum2 = __fadd2_rn(lsum2, e);
+          pk[i >> 1] = pack16(a.dtype, e.x, e.y);
+        }
       }
+      l_run += lsum2.x + lsum2.y;
       // P(j) overwrites the first 32 columns of S(j): lane = row, column c = keys (2c, 2c+1)
       tmem_st32(tS0 + lane_base + st * 64, pk);
       tc_wait_st();

@@ -207,8 +207,6 @@ class _FlashAttnFn(torch.autograd.Function):
                 "flash_attention backward for float32: the reference differentiates its SDPA fallback "
                 "(mlx_mfa/attention.py:2013-2019); the CUDA backward takes f16/bf16."
             )
-        if q.shape[2] != k.shape[2] and causal:
-            raise NotImplementedError("causal backward with N != S is not built")
         dq, dk, dv = _bwd_raw(q, k, v, out, lse, dout, scale, causal, stream)
         return dq, dk, dv, None, None, None, None, None, None
 

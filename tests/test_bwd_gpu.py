@@ -1,0 +1,117 @@
+"""GPU parity of the backward (dQ, dK, dV) against float64 autograd through the CPU oracle,
+2e-2 max-abs.  Cases follow the reference's backward tests (tests/test_attention.py in the
+reference: 191-283 dense, 4306-4381 GQA with dK/dV of shape [B,Hkv,N,D], 4461-4481 varlen)."""
+import numpy as np
+import pytest
+import torch
+
+import mlx_flashattention_steel_b200 as fa
+from oracle import sdpa_oracle as orc
+
+from .util import assert_close, assert_close_grad, randn
+
+pytestmark = pytest.mark.gpu
+
+
+def _grads(dev, dtype, B, Hq, Hkv, N, S, D, causal, seed, scale=None):
+    q = randn((B, Hq, N, D), dtype, seed)
+    k = randn((B, Hkv, S, D), dtype, seed + 1)
+    v = randn((B, Hkv, S, D), dtype, seed + 2)
+    do = randn((B, Hq, N, D), dtype, seed + 3)
+    qg, kg, vg = (x.to(dev).requires_grad_(True) for x in (q, k, v))
+    out = fa.flash_attention(qg, kg, vg, causal=causal, scale=scale)
+    out.backward(do.to(dev))
+    torch.cuda.synchronize()
+    dq, dk, dv = orc.backward(q, k, v, do, scale=scale, causal=causal)
+    assert qg.grad.shape == q.shape and kg.grad.shape == k.shape and vg.grad.shape == v.shape
+    assert_close_grad(qg.grad, dq, dtype, "dQ")
+    assert_close_grad(kg.grad, dk, dtype, "dK")
+    assert_close_grad(vg.grad, dv, dtype, "dV")
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("D", [64, 128])
+@pytest.mark.parametrize("causal", [False, True])
+def test_backward_basic(dev, dtype, D, causal):
+    _grads(dev, dtype, 2, 4, 4, 128, 128, D, causal, 500)
+
+
+@pytest.mark.parametrize("N,S,causal", [(37, 37, True), (37, 40, False), (100, 257, False), (129, 129, True), (64, 200, True), (1, 70, False)])
+def test_backward_remainders(dev, N, S, causal):
+    _grads(dev, torch.bfloat16, 1, 2, 2, N, S, 64, causal, 510)
+    _grads(dev, torch.float16, 1, 2, 2, N, S, 128, causal, 511)
+
+
+@pytest.mark.parametrize("ratio", [2, 4, 8])
+def test_backward_gqa(dev, ratio):
+    _grads(dev, torch.bfloat16, 2, 8, 8 // ratio, 150, 150, 64, True, 520)
+
+
+def test_backward_scale_and_longer(dev):
+    _grads(dev, torch.float16, 1, 4, 2, 512, 512, 128, True, 530, scale=0.05)
+
+
+def _cu(lens):
+    return [0] + list(np.cumsum(lens))
+
+
+@pytest.mark.parametrize("dtype,D", [(torch.bfloat16, 64), (torch.float16, 128)])
+@pytest.mark.parametrize("causal", [False, True])
+def test_backward_varlen(dev, dtype, D, causal):
+    lens = [33, 64, 17, 130]
+    cu = _cu(lens)
+    T = cu[-1]
+    q = randn((1, 4, T, D), dtype, 540)
+    k = randn((1, 2, T, D), dtype, 541)
+    v = randn((1, 2, T, D), dtype, 542)
+    do = randn((1, 4, T, D), dtype, 543)
+    cu_t = torch.tensor(cu, dtype=torch.int32, device=dev)
+    qg, kg, vg = (x.to(dev).requires_grad_(True) for x in (q, k, v))
+    out = fa.flash_attention_varlen(qg, kg, vg, cu_t, cu_t, max(lens), max(lens), causal=causal)
+    out.backward(do.to(dev))
+    dq, dk, dv = orc.backward(q, k, v, do, causal=causal, cu_q=cu, cu_k=cu)
+    O, _ = orc.varlen(q, k, v, cu, cu, causal=causal)
+    assert_close(out, O, dtype)
+    assert_close_grad(qg.grad, dq, dtype, "dQ")
+    assert_close_grad(kg.grad, dk, dtype, "dK")
+    assert_close_grad(vg.grad, dv, dtype, "dV")
+
+
+def test_backward_config5_shaped(dev):
+    """Config-5 shape at reduced total: packed causal bf16, D=64, lengths ~ U{128..2048}, 8192 tokens, 4 heads."""
+    rng = np.random.default_rng(5)
+    lens = []
+    while sum(lens) < 8192:
+        lens.append(int(rng.integers(128, 2049)))
+    lens[-1] -= sum(lens) - 8192
+    cu = _cu(lens)
+    q, k, v, do = (randn((1, 4, 8192, 64), torch.bfloat16, 550 + i) for i in range(4))
+    cu_t = torch.tensor(cu, dtype=torch.int32, device=dev)
+    qg, kg, vg = (x.to(dev).requires_grad_(True) for x in (q, k, v))
+    out = fa.flash_attention_varlen(qg, kg, vg, cu_t, cu_t, max(lens), max(lens), causal=True)
+    out.backward(do.to(dev))
+    dq, dk, dv = orc.backward(q, k, v, do, causal=True, cu_q=cu, cu_k=cu)
+    assert_close_grad(qg.grad, dq, torch.bfloat16, "dQ")
+    assert_close_grad(kg.grad, dk, torch.bfloat16, "dK")
+    assert_close_grad(vg.grad, dv, torch.bfloat16, "dV")
+
+
+def test_backward_linearity_full_size(dev):
+    """Size-independent property at config-5 scale (65536 packed tokens, H=16, D=64): the backward is
+    linear in dO, so grads(dO1 + dO2) = grads(dO1) + grads(dO2) up to bf16 rounding."""
+    rng = np.random.default_rng(5)
+    lens = []
+    while sum(lens) < 65536:
+        lens.append(int(rng.integers(128, 4097)))
+    lens[-1] -= sum(lens) - 65536
+    cu_t = torch.tensor(_cu(lens), dtype=torch.int32, device=dev)
+    gd = torch.Generator(device=dev).manual_seed(5)
+    mk = lambda: torch.randn((1, 16, 65536, 64), generator=gd, device=dev).to(torch.bfloat16)
+    q, k, v, d1, d2 = mk(), mk(), mk(), mk(), mk()
+    res = []
+    for do in (d1, d2, (d1.float() + d2.float()).to(torch.bfloat16)):
+        qg, kg, vg = (x.clone().requires_grad_(True) for x in (q, k, v))
+        fa.flash_attention_varlen(qg, kg, vg, cu_t, cu_t, max(lens), max(lens), causal=True).backward(do)
+        res.append((qg.grad.float(), kg.grad.float(), vg.grad.float()))
+    for a, b, c in zip(*res):
+        assert float((c - (a + b)).abs().max()) <= 8e-2 * max(1.0, float(c.abs().max()) / 4)

@@ -35,6 +35,20 @@ def assert_close(got, ref, dtype, what="out", tol=None):
     return err
 
 
+# one unit in the last place of the storage dtype, relative
+ULP = {torch.float16: 2.0 ** -10, torch.bfloat16: 2.0 ** -7}
+
+
+def assert_close_grad(got, ref, dtype, what):
+    """Gradients summed over a GQA group reach magnitudes where a single rounding to the
+    16-bit output type exceeds 2e-2 (bf16 at |x| >= 4 has ulp 0.03).  The bound is therefore
+    2e-2 absolute plus one unit in the last place of the output dtype at the reference value."""
+    a = got.detach().double().cpu()
+    b = ref.detach().double().cpu()
+    excess = ((a - b).abs() - (TOL[dtype] + ULP[dtype] * b.abs())).max()
+    assert float(excess) <= 0, f"{what}: exceeds 2e-2 + 1 ulp by {float(excess):.3e}; max-abs {float((a - b).abs().max()):.3e}"
+
+
 def make_paged(B, Hkv, D, block_size, lens, dtype, seed, quant=None, spare_pages=3, holes=False):
     """Builds a page pool in the reference's layout [num_pages, block_size, Hkv, D], a
     block table that is a random permutation of pool pages (-1 padded) and seq_lens.

@@ -1,0 +1,96 @@
+"""Multi-GPU host logic: one process per GPU, `torch.distributed` for the plumbing.
+
+The reference is single-device (no rank, world size or collective anywhere in it), so
+nothing here mirrors a reference file; it is the layer a serving or training stack puts
+around the operators on an 8-GPU box.
+
+* (batch, kv-head) shards are independent in forward, backward and decode — each query
+  head reads exactly one kv head — so the batched operators need no collective:
+  ``shard_units`` deals the (batch, kv-head) units out and each rank runs the ordinary
+  operators on views of its shard.
+* One very long decode sequence is the exception: its page list is split across ranks,
+  every rank runs the same split-KV decode kernel over its pages with ``return_lse=True``,
+  and ``combine_partials`` merges the per-rank (O, lse) with one small all-gather
+  (Hq*(D+1) floats per rank) and the log-sum-exp rule the decode kernel itself uses
+  between CTAs (``L = log2 sum_r 2^lse_r``, ``O = sum_r 2^(lse_r - L) O_r``).
+"""
+from __future__ import annotations
+
+from typing import List, Optional, Tuple
+
+import torch
+import torch.distributed as dist
+
+
+def shard_range(n: int, world: int, rank: int) -> Tuple[int, int]:
+    """Contiguous balanced split of ``range(n)``: the first ``n % world`` ranks get one extra."""
+    if world <= 0 or not (0 <= rank < world):
+        raise ValueError(f"bad rank/world: {rank}/{world}")
+    base, extra = divmod(n, world)
+    lo = rank * base + min(rank, extra)
+    return lo, lo + base + (1 if rank < extra else 0)
+
+
+def shard_units(B: int, Hkv: int, world: int, rank: int) -> List[Tuple[int, int]]:
+    """(batch, kv-head) units owned by ``rank``; unit u = b * Hkv + h, dealt contiguously so a
+    rank's units are a few whole batches plus a contiguous head range (views, no copies)."""
+    lo, hi = shard_range(B * Hkv, world, rank)
+    return [(u // Hkv, u % Hkv) for u in range(lo, hi)]
+
+
+def shard_views(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, world: int, rank: int):
+    """Yields (b, h, q_view, k_view, v_view) per owned unit: q heads [h*g, (h+1)*g) of batch b with
+    kv head h.  Views only; the kernels take the strides as they are."""
+    B, Hq = q.shape[0], q.shape[1]
+    Hkv = k.shape[1]
+    g = Hq // Hkv
+    for b, h in shard_units(B, Hkv, world, rank):
+        yield b, h, q[b:b + 1, h * g:(h + 1) * g], k[b:b + 1, h:h + 1], v[b:b + 1, h:h + 1]
+
+
+def split_pages(num_pages_of_seq: int, world: int, rank: int, block_size: int, seq_len: int) -> Tuple[int, int, int]:
+    """Page range [lo, hi) of one long sequence owned by ``rank`` and the number of valid tokens in it."""
+    lo, hi = shard_range(num_pages_of_seq, world, rank)
+    tok_lo = min(seq_len, lo * block_size)
+    tok_hi = min(seq_len, hi * block_size)
+    return lo, hi, tok_hi - tok_lo
+
+
+def combine_partials(out: torch.Tensor, lse: torch.Tensor, group: Optional[dist.ProcessGroup] = None,
+                     out_dtype: Optional[torch.dtype] = None) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Merges per-rank partial attention results over disjoint key ranges.
+
+    out [..., D] (any float dtype), lse [...] float32 base-2 (``-inf`` where the rank saw no key).
+    Returns (O, L) on every rank.  One all-gather of the packed (O fp32, lse) — 4*(D+1) bytes per row
+    per rank — then a local weighted sum; the formula is the split combine of the reference's
+    flash-decode reduce (csrc/mfa_steel_fwd.cpp:2066-2101) in base 2."""
+    world = dist.get_world_size(group)
+    packed = torch.cat([out.float(), lse.float().unsqueeze(-1)], dim=-1).contiguous()
+    gathered = [torch.empty_like(packed) for _ in range(world)]
+    dist.all_gather(gathered, packed, group=group)
+    allp = torch.stack(gathered, dim=0)                    # [world, ..., D+1]
+    o_r, l_r = allp[..., :-1], allp[..., -1]
+    m = l_r.max(dim=0).values
+    m_safe = torch.where(torch.isinf(m), torch.zeros_like(m), m)
+    w = torch.exp2(l_r - m_safe)                           # [world, ...]
+    wsum = w.sum(dim=0)
+    o = (w.unsqueeze(-1) * o_r).sum(dim=0) / torch.where(wsum > 0, wsum, torch.ones_like(wsum)).unsqueeze(-1)
+    L = torch.where(wsum > 0, m_safe + torch.log2(torch.where(wsum > 0, wsum, torch.ones_like(wsum))),
+                    torch.full_like(m, float("-inf")))
+    return o.to(out_dtype or out.dtype), L
+
+
+def decode_long_sequence(q, k_pages, v_pages, block_table_local, seq_lens_local, *, group=None, scale=None,
+                         k_scale=None, v_scale=None, softcap: float = 0.0, max_kv_len=None):
+    """Decode step for sequences whose pages are spread over the ranks of ``group``: every rank passes
+    the block table rows and token counts of ITS part of each sequence (q is replicated).  Runs the
+    paged decode kernel locally, then ``combine_partials``.  causal is irrelevant for a single query
+    token (the reference notes N=1 causal == non-causal, tests/test_attention.py:1472-1487)."""
+    from .attention import flash_attention_paged
+
+    if q.shape[2] != 1:
+        raise NotImplementedError("decode_long_sequence takes one query token per sequence")
+    o, l = flash_attention_paged(q, k_pages, v_pages, block_table_local, seq_lens_local, scale=scale, causal=False,
+                                 k_scale=k_scale, v_scale=v_scale, softcap=softcap, max_kv_len=max_kv_len,
+                                 return_lse=True)
+    return combine_partials(o, l, group=group, out_dtype=q.dtype)

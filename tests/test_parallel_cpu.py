@@ -1,0 +1,105 @@
+"""CPU tests (gloo, world_size 2) of the multi-GPU host logic: shard planning and the
+cross-rank log-sum-exp combine of split-KV partials, checked against the oracle."""
+import os
+import socket
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from mlx_flashattention_steel_b200 import parallel as par
+from oracle import sdpa_oracle as orc
+
+
+def test_shard_range_covers_everything_once():
+    for n in (0, 1, 7, 32, 33):
+        for world in (1, 2, 3, 8):
+            seen = []
+            for r in range(world):
+                lo, hi = par.shard_range(n, world, r)
+                assert 0 <= lo <= hi <= n
+                seen += list(range(lo, hi))
+            assert seen == list(range(n))
+    with pytest.raises(ValueError):
+        par.shard_range(4, 2, 2)
+
+
+def test_shard_units_config2():
+    # 4 batches x 8 kv heads over 8 GPUs -> 4 units each, whole number of heads of one batch
+    all_units = []
+    for r in range(8):
+        u = par.shard_units(4, 8, 8, r)
+        assert len(u) == 4 and len({b for b, _ in u}) == 1
+        all_units += u
+    assert sorted(all_units) == [(b, h) for b in range(4) for h in range(8)]
+
+
+def test_shard_views_are_views():
+    q, k, v = torch.zeros(2, 8, 4, 16), torch.zeros(2, 2, 6, 16), torch.zeros(2, 2, 6, 16)
+    got = list(par.shard_views(q, k, v, 2, 1))
+    assert [(b, h) for b, h, *_ in got] == [(1, 0), (1, 1)]
+    _, _, qv, kv, _ = got[1]
+    assert qv.shape == (1, 4, 4, 16) and kv.shape == (1, 1, 6, 16)
+    assert qv.data_ptr() == q[1, 4].data_ptr()
+
+
+def test_split_pages():
+    # 100 tokens, 7 pages of 16, over 2 ranks: pages [0,4) and [4,7) -> 64 and 36 tokens
+    assert par.split_pages(7, 2, 0, 16, 100) == (0, 4, 64)
+    assert par.split_pages(7, 2, 1, 16, 100) == (4, 7, 36)
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    port = s.getsockname()[1]
+    s.close()
+    return port
+
+
+def _worker(rank, world, port, q, k, v, ret):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        S = k.shape[2]
+        lo, hi = par.shard_range(S, world, rank)
+        if rank == 1:
+            hi = lo            # rank 1 holds no key at all: lse = -inf must drop out of the combine
+        elif world == 2:
+            hi = S
+        if hi > lo:
+            o, l, _ = orc.sdpa(q, k[:, :, lo:hi], v[:, :, lo:hi])
+        else:
+            o = torch.zeros(q.shape, dtype=torch.float64)
+            l = torch.full(q.shape[:3], float("-inf"), dtype=torch.float64)
+        O, L = par.combine_partials(o.float(), l.float())
+        # second round: a real split
+        lo, hi = par.shard_range(S, world, rank)
+        o, l, _ = orc.sdpa(q, k[:, :, lo:hi], v[:, :, lo:hi])
+        O2, L2 = par.combine_partials(o.float(), l.float())
+        if rank == 0:
+            ret.put((O, L, O2, L2))
+        dist.barrier()
+    finally:
+        dist.destroy_process_group()
+
+
+def test_combine_partials_over_gloo():
+    torch.manual_seed(0)
+    q, k, v = torch.randn(2, 4, 1, 32), torch.randn(2, 2, 77, 32), torch.randn(2, 2, 77, 32)
+    ctx = mp.get_context("spawn")
+    ret = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_worker, args=(r, 2, port, q, k, v, ret)) for r in range(2)]
+    for p in procs:
+        p.start()
+    O, L, O2, L2 = ret.get(timeout=120)
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    ref, lref, _ = orc.sdpa(q, k, v)
+    for o, l in ((O, L), (O2, L2)):
+        assert float((o.double() - ref).abs().max()) < 1e-5
+        assert float((l.double() - lref).abs().max()) < 1e-4

@@ -411,83 +411,112 @@ decode_paged_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_consta
     bool first_page = true;
     const int causal_lim = p.causal ? (qi_row + len - p.Nq) : 0x7fffffff;   // last visible token of row g
 
-    for (int j = j_lo; j < j_hi; ++j) {
-      if (!__all_sync(0xffffffffu, mbar_wait_bounded(smem_u32(&bars[stage]), phase, s_abort))) { ok = false; break; }
-      const int page = s_page[stage];
-      const uint32_t kbase = smem_u32(sK + static_cast<size_t>(stage) * a.stage_kv_bytes) + warp * kHeadBytes;
-      const uint32_t vbase = smem_u32(sV + static_cast<size_t>(stage) * a.stage_kv_bytes) + warp * kHeadBytes;
-      const uint32_t ksb = smem_u32(sKs + static_cast<size_t>(stage) * a.scale_bytes) + kvh * 2;
-      const uint32_t vsb = smem_u32(sVs + static_cast<size_t>(stage) * a.scale_bytes) + kvh * 2;
+    // Two pages per iteration: their loads, conversions and MMAs are independent, which gives the
+    // scheduler twice the instruction-level parallelism, and one online-softmax step covers 32 tokens.
+    for (int j = j_lo; j < j_hi; j += 2) {
+      const int np = min(2, j_hi - j);
+      int stg[2], pg[2];
+      {
+        int s2 = stage;
+        uint32_t ph2 = phase;
+        bool okw = true;
+#pragma unroll
+        for (int q = 0; q < 2; ++q) {
+          stg[q] = s2;
+          if (q < np && okw) {
+            okw = __all_sync(0xffffffffu, mbar_wait_bounded(smem_u32(&bars[s2]), ph2, s_abort));
+            if (++s2 == NS) { s2 = 0; ph2 ^= 1u; }
+          }
+        }
+        if (!okw) { ok = false; break; }
+      }
+      uint32_t kbase[2], vbase[2], ksb[2], vsb[2];
+#pragma unroll
+      for (int q = 0; q < 2; ++q) {
+        pg[q] = q < np ? s_page[stg[q]] : -2;       // -1: hole in the table, -2: no second page
+        kbase[q] = smem_u32(sK + static_cast<size_t>(stg[q]) * a.stage_kv_bytes) + warp * kHeadBytes;
+        vbase[q] = smem_u32(sV + static_cast<size_t>(stg[q]) * a.stage_kv_bytes) + warp * kHeadBytes;
+        ksb[q] = smem_u32(sKs + static_cast<size_t>(stg[q]) * a.scale_bytes) + kvh * 2;
+        vsb[q] = smem_u32(sVs + static_cast<size_t>(stg[q]) * a.scale_bytes) + kvh * 2;
+      }
       const int scale_stride = p.Hkv * 2;          // bytes between tokens in a scale page
-      const int tok0 = j * kBS;
 
-      // ---- S = Q K^T : rows = query rows (8 real), cols = 16 tokens (two n-tiles) ----
-      float sacc[2][4];
+      // ---- S = Q K^T : rows = query rows (8 real), cols = 16 tokens (two n-tiles) per page ----
+      float sacc[2][2][4];
 #pragma unroll
-      for (int i = 0; i < 2; ++i) { sacc[i][0] = sacc[i][1] = sacc[i][2] = sacc[i][3] = 0.f; }
-      if (page >= 0) {
-        if (kQuant) {
+      for (int q = 0; q < 2; ++q)
 #pragma unroll
-          for (int jn = 0; jn < 2; ++jn) {
-            const int tok = 8 * jn + g;                     // tok & 7 == g
-            const uint32_t rowa = kbase + tok * 128;
-            const uint4 w0 = lds128(rowa + (((2 * t) ^ g) << 4));
-            const uint4 w1 = lds128(rowa + (((2 * t + 1) ^ g) << 4));
-            const uint32_t words[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+        for (int i = 0; i < 2; ++i) { sacc[q][i][0] = sacc[q][i][1] = sacc[q][i][2] = sacc[q][i][3] = 0.f; }
+#pragma unroll
+      for (int q = 0; q < 2; ++q) {
+        if (pg[q] >= 0) {
+          if (kQuant) {
+#pragma unroll
+            for (int jn = 0; jn < 2; ++jn) {
+              const int tok = 8 * jn + g;                     // tok & 7 == g
+              const uint32_t rowa = kbase[q] + tok * 128;
+              const uint4 w0 = lds128(rowa + (((2 * t) ^ g) << 4));
+              const uint4 w1 = lds128(rowa + (((2 * t + 1) ^ g) << 4));
+              const uint32_t words[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+#pragma unroll
+              for (int s = 0; s < 8; ++s) {
+                uint32_t b0, b1;
+                if (KV == KV_I8) {
+                  const uint32_t x = words[s] ^ 0x80808080u;
+                  b0 = i8pair_to_h2(x, 0x4140u);
+                  b1 = i8pair_to_h2(x, 0x4342u);
+                } else {
+                  b0 = e4m3pair_to_h2(words[s]);
+                  b1 = e4m3pair_to_h2(words[s] >> 16);
+                }
+                const uint32_t afrag[4] = {qa[s][0], 0u, qa[s][1], 0u};
+                mma16816<MmaT>(sacc[q][jn], afrag, b0, b1);
+              }
+            }
+          } else {
 #pragma unroll
             for (int s = 0; s < 8; ++s) {
-              uint32_t b0, b1;
-              if (KV == KV_I8) {
-                const uint32_t x = words[s] ^ 0x80808080u;
-                b0 = i8pair_to_h2(x, 0x4140u);
-                b1 = i8pair_to_h2(x, 0x4342u);
-              } else {
-                b0 = e4m3pair_to_h2(words[s]);
-                b1 = e4m3pair_to_h2(words[s] >> 16);
-              }
+              uint32_t bfr[4];
+              const int tok = (lane & 7) + ((lane >> 4) << 3);
+              const int dcol = 16 * s + (((lane >> 3) & 1) << 3);
+              const uint32_t addr = kbase[q] + (dcol >> 6) * (kBS * 128) + tok * 128 + ((((dcol & 63) >> 3) ^ (tok & 7)) << 4);
+              ldmatrix_x4(bfr, addr);
               const uint32_t afrag[4] = {qa[s][0], 0u, qa[s][1], 0u};
-              mma16816<MmaT>(sacc[jn], afrag, b0, b1);
+              mma16816<MmaT>(sacc[q][0], afrag, bfr[0], bfr[1]);
+              mma16816<MmaT>(sacc[q][1], afrag, bfr[2], bfr[3]);
             }
-          }
-        } else {
-#pragma unroll
-          for (int s = 0; s < 8; ++s) {
-            uint32_t bfr[4];
-            const int tok = (lane & 7) + ((lane >> 4) << 3);
-            const int dcol = 16 * s + (((lane >> 3) & 1) << 3);
-            const uint32_t addr = kbase + (dcol >> 6) * (kBS * 128) + tok * 128 + ((((dcol & 63) >> 3) ^ (tok & 7)) << 4);
-            ldmatrix_x4(bfr, addr);
-            const uint32_t afrag[4] = {qa[s][0], 0u, qa[s][1], 0u};
-            mma16816<MmaT>(sacc[0], afrag, bfr[0], bfr[1]);
-            mma16816<MmaT>(sacc[1], afrag, bfr[2], bfr[3]);
           }
         }
       }
 
-      // ---- scale / softcap / masks: this lane holds tokens {2t, 2t+1, 8+2t, 9+2t} of row g ----
-      float sc[4], vsc[4];
+      // ---- scale / softcap / masks: per page this lane holds tokens {2t, 2t+1, 8+2t, 9+2t} of row g ----
+      float sc[2][4], vsc[2][4];
 #pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        const int tok = ((e >> 1) << 3) + 2 * t + (e & 1);
-        float s = sacc[e >> 1][e & 1];
-        float ksv = 1.f;
-        vsc[e] = 1.f;
-        if (kQuant) {
-          if (page >= 0) {
-            ksv = lds_half(ksb + tok * scale_stride);
-            vsc[e] = lds_half(vsb + tok * scale_stride);
+      for (int q = 0; q < 2; ++q) {
+        const int tok0 = (j + q) * kBS;
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int tok = ((e >> 1) << 3) + 2 * t + (e & 1);
+          float s = sacc[q][e >> 1][e & 1];
+          vsc[q][e] = 1.f;
+          if (kQuant) {
+            float ksv = 1.f;
+            if (pg[q] >= 0) {
+              ksv = lds_half(ksb[q] + tok * scale_stride);
+              vsc[q][e] = lds_half(vsb[q] + tok * scale_stride);
+            }
+            s *= ksv;
+          } else {
+            s *= a.q_prescale;
           }
-          s *= ksv;
-        } else {
-          s *= a.q_prescale;
+          if (a.inv_cap > 0.f) s = a.cap_log2 * fast_tanh(s * a.inv_cap);
+          const int tg = tok0 + tok;
+          sc[q][e] = (pg[q] != -2 && tg < len && tg <= causal_lim) ? s : -INFINITY;
         }
-        if (a.inv_cap > 0.f) s = a.cap_log2 * fast_tanh(s * a.inv_cap);
-        const int tg = tok0 + tok;
-        sc[e] = (tg < len && tg <= causal_lim) ? s : -INFINITY;
       }
       if (kQuant && first_page) {
         // power of two near the first token's v scale keeps p * v_scale inside f16's normal range
-        float v0 = (page >= 0) ? lds_half(vsb) : 1.f;
+        float v0 = (pg[0] >= 0) ? lds_half(vsb[0]) : 1.f;
         v0 = __shfl_sync(0xffffffffu, v0, 0);
         uint32_t bits = __float_as_uint(v0) & 0x7f800000u;
         if (bits == 0u || bits == 0x7f800000u) bits = 0x3f800000u;
@@ -496,8 +525,9 @@ decode_paged_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_consta
         first_page = false;
       }
 
-      // ---- online softmax over the 16 tokens ----
-      float mx = fmaxf(fmaxf(sc[0], sc[1]), fmaxf(sc[2], sc[3]));
+      // ---- online softmax over the (up to) 32 tokens ----
+      float mx = fmaxf(fmaxf(fmaxf(sc[0][0], sc[0][1]), fmaxf(sc[0][2], sc[0][3])),
+                       fmaxf(fmaxf(sc[1][0], sc[1][1]), fmaxf(sc[1][2], sc[1][3])));
       mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
       mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
       const float m_new = fmaxf(m_run, mx);
@@ -514,76 +544,85 @@ decode_paged_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_consta
         }
         m_run = m_new;
       }
-      float pr[4];
+      float pr[2][4];
 #pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        pr[e] = fast_exp2(sc[e] - msub);
-        l_run += pr[e];
-      }
+      for (int q = 0; q < 2; ++q)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          pr[q][e] = fast_exp2(sc[q][e] - msub);
+          l_run += pr[q][e];
+        }
 
       // ---- O^T += V^T P^T : rows = 16 head-dim values per m-tile, cols = query rows ----
-      if (page >= 0) {
-        uint32_t pb0, pb1;
-        if (kQuant) {
-          pb0 = pack_h2(pr[0] * vsc[0] * vnorm, pr[1] * vsc[1] * vnorm);
-          pb1 = pack_h2(pr[2] * vsc[2] * vnorm, pr[3] * vsc[3] * vnorm);
-        } else if (KV == KV_BF16) {
-          pb0 = pack_bf2(pr[0], pr[1]);
-          pb1 = pack_bf2(pr[2], pr[3]);
-        } else {
-          pb0 = pack_h2(pr[0], pr[1]);
-          pb1 = pack_h2(pr[2], pr[3]);
-        }
-        if (kQuant) {
-          // lane (g,t) reads word w = g + 8*jj (4 head-dim bytes) of token rows 2t, 2t+1, 2t+8, 2t+9
-          const uint32_t rA = vbase + (2 * t) * 128, rB = rA + 128, rC = rA + 8 * 128, rD = rC + 128;
-          const int xa = (2 * t) & 7, xb = (2 * t + 1) & 7;
 #pragma unroll
-          for (int jj = 0; jj < 4; ++jj) {
-            const int w = g + 8 * jj;
-            const int ch = w >> 2, wi = (w & 3) << 2;
-            uint32_t A = lds32(rA + ((ch ^ xa) << 4) + wi);
-            uint32_t Bw = lds32(rB + ((ch ^ xb) << 4) + wi);
-            uint32_t Cw = lds32(rC + ((ch ^ xa) << 4) + wi);
-            uint32_t Dw = lds32(rD + ((ch ^ xb) << 4) + wi);
-            if (KV == KV_I8) { A ^= 0x80808080u; Bw ^= 0x80808080u; Cw ^= 0x80808080u; Dw ^= 0x80808080u; }
-            const uint32_t ab[2] = {prmt(A, Bw, 0x5140u), prmt(A, Bw, 0x7362u)};   // [A0 B0 A1 B1], [A2 B2 A3 B3]
-            const uint32_t cd[2] = {prmt(Cw, Dw, 0x5140u), prmt(Cw, Dw, 0x7362u)};
-#pragma unroll
-            for (int kp = 0; kp < 2; ++kp) {
-              uint32_t af[4];
-              if (KV == KV_I8) {
-                af[0] = i8pair_to_h2(ab[kp], 0x4140u);   // head-dim byte 2kp   , tokens 2t, 2t+1
-                af[1] = i8pair_to_h2(ab[kp], 0x4342u);   // head-dim byte 2kp+1 , tokens 2t, 2t+1
-                af[2] = i8pair_to_h2(cd[kp], 0x4140u);   // tokens 2t+8, 2t+9
-                af[3] = i8pair_to_h2(cd[kp], 0x4342u);
-              } else {
-                af[0] = e4m3pair_to_h2(ab[kp]);
-                af[1] = e4m3pair_to_h2(ab[kp] >> 16);
-                af[2] = e4m3pair_to_h2(cd[kp]);
-                af[3] = e4m3pair_to_h2(cd[kp] >> 16);
-              }
-              mma16816<MmaT>(oacc[jj * 2 + kp], af, pb0, pb1);
-            }
+      for (int q = 0; q < 2; ++q) {
+        if (pg[q] >= 0) {
+          uint32_t pb0, pb1;
+          if (kQuant) {
+            pb0 = pack_h2(pr[q][0] * vsc[q][0] * vnorm, pr[q][1] * vsc[q][1] * vnorm);
+            pb1 = pack_h2(pr[q][2] * vsc[q][2] * vnorm, pr[q][3] * vsc[q][3] * vnorm);
+          } else if (KV == KV_BF16) {
+            pb0 = pack_bf2(pr[q][0], pr[q][1]);
+            pb1 = pack_bf2(pr[q][2], pr[q][3]);
+          } else {
+            pb0 = pack_h2(pr[q][0], pr[q][1]);
+            pb1 = pack_h2(pr[q][2], pr[q][3]);
           }
-        } else {
+          if (kQuant) {
+            // lane (g,t) reads word w = g + 8*jj (4 head-dim bytes) of token rows 2t, 2t+1, 2t+8, 2t+9
+            const uint32_t rA = vbase[q] + (2 * t) * 128, rB = rA + 128, rC = rA + 8 * 128, rD = rC + 128;
+            const int xa = (2 * t) & 7, xb = (2 * t + 1) & 7;
 #pragma unroll
-          for (int mt = 0; mt < 8; ++mt) {
-            uint32_t af[4];
-            const int tok = (lane & 7) + ((lane >> 4) << 3);
-            const int dcol = 16 * mt + (((lane >> 3) & 1) << 3);
-            const uint32_t addr = vbase + (dcol >> 6) * (kBS * 128) + tok * 128 + ((((dcol & 63) >> 3) ^ (tok & 7)) << 4);
-            ldmatrix_x4_trans(af, addr);
-            // ldmatrix order: m0 = (tok 0-7, d 0-7), m1 = (tok 0-7, d 8-15), m2 = (tok 8-15, d 0-7), m3 = (tok 8-15, d 8-15)
-            // A fragment wants a0 = (d 0-7, tok 0-7), a1 = (d 8-15, tok 0-7), a2 = (d 0-7, tok 8-15), a3 = (d 8-15, tok 8-15)
-            mma16816<MmaT>(oacc[mt], af, pb0, pb1);
+            for (int jj = 0; jj < 4; ++jj) {
+              const int w = g + 8 * jj;
+              const int ch = w >> 2, wi = (w & 3) << 2;
+              uint32_t A = lds32(rA + ((ch ^ xa) << 4) + wi);
+              uint32_t Bw = lds32(rB + ((ch ^ xb) << 4) + wi);
+              uint32_t Cw = lds32(rC + ((ch ^ xa) << 4) + wi);
+              uint32_t Dw = lds32(rD + ((ch ^ xb) << 4) + wi);
+              if (KV == KV_I8) { A ^= 0x80808080u; Bw ^= 0x80808080u; Cw ^= 0x80808080u; Dw ^= 0x80808080u; }
+              const uint32_t ab[2] = {prmt(A, Bw, 0x5140u), prmt(A, Bw, 0x7362u)};   // [A0 B0 A1 B1], [A2 B2 A3 B3]
+              const uint32_t cd[2] = {prmt(Cw, Dw, 0x5140u), prmt(Cw, Dw, 0x7362u)};
+#pragma unroll
+              for (int kp = 0; kp < 2; ++kp) {
+                uint32_t af[4];
+                if (KV == KV_I8) {
+                  af[0] = i8pair_to_h2(ab[kp], 0x4140u);   // head-dim byte 2kp   , tokens 2t, 2t+1
+                  af[1] = i8pair_to_h2(ab[kp], 0x4342u);   // head-dim byte 2kp+1 , tokens 2t, 2t+1
+                  af[2] = i8pair_to_h2(cd[kp], 0x4140u);   // tokens 2t+8, 2t+9
+                  af[3] = i8pair_to_h2(cd[kp], 0x4342u);
+                } else {
+                  af[0] = e4m3pair_to_h2(ab[kp]);
+                  af[1] = e4m3pair_to_h2(ab[kp] >> 16);
+                  af[2] = e4m3pair_to_h2(cd[kp]);
+                  af[3] = e4m3pair_to_h2(cd[kp] >> 16);
+                }
+                mma16816<MmaT>(oacc[jj * 2 + kp], af, pb0, pb1);
+              }
+            }
+          } else {
+#pragma unroll
+            for (int mt = 0; mt < 8; ++mt) {
+              uint32_t af[4];
+              const int tok = (lane & 7) + ((lane >> 4) << 3);
+              const int dcol = 16 * mt + (((lane >> 3) & 1) << 3);
+              const uint32_t addr = vbase[q] + (dcol >> 6) * (kBS * 128) + tok * 128 + ((((dcol & 63) >> 3) ^ (tok & 7)) << 4);
+              // after .trans: a0 = (d 0-7, tok 0-7), a1 = (d 8-15, tok 0-7), a2 = (d 0-7, tok 8-15), a3 = (d 8-15, tok 8-15)
+              ldmatrix_x4_trans(af, addr);
+              mma16816<MmaT>(oacc[mt], af, pb0, pb1);
+            }
           }
         }
       }
 
       __syncwarp();
-      if (lane == 0) mbar_arrive(smem_u32(&bars[kMaxStages + stage]));
-      if (++stage == NS) { stage = 0; phase ^= 1u; }
+#pragma unroll
+      for (int q = 0; q < 2; ++q) {
+        if (q < np) {
+          if (lane == 0) mbar_arrive(smem_u32(&bars[kMaxStages + stg[q]]));
+          if (++stage == NS) { stage = 0; phase ^= 1u; }
+        }
+      }
     }
     if (!ok) break;
 

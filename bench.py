@@ -232,6 +232,66 @@ def bench_decode(device, steps, warmup, pk, batch=None):
             "gpu_launches": steps * 2}
 
 
+def _time_ms(fn, steps, warmup):
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / steps
+
+
+def bench_extras(device, pk):
+    """The other configs of the spec, measured the same way (device-resident inputs, CUDA events):
+    config 1 (fp32 dense causal), config 3 (sliding window) and config 5 (packed varlen fwd+bwd)."""
+    import numpy as np
+
+    import mlx_flashattention_steel_b200 as fa
+
+    out = {}
+    gd = torch.Generator(device=device).manual_seed(11)
+    mk = lambda shape, dt: torch.randn(shape, generator=gd, device=device).to(dt)
+    # config 1: B=1 H=8 N=S=1024 D=128 float32 causal
+    q, k, v = (mk((1, 8, 1024, 128), torch.float32) for _ in range(3))
+    ms = _time_ms(lambda: fa.flash_attention(q, k, v, causal=True), 20, 5)
+    fl = 4.0 * 8 * 128 * (1024 * 1025 // 2)
+    out["config1_fp32_causal"] = {"ms": ms, "tflops": fl / ms / 1e9, "kernel": "fa_fwd_f32 (FFMA)"}
+    # config 3: B=2 H=16 N=S=32768 D=128 fp16 window (512, 0), causal
+    q, k, v = (mk((2, 16, 32768, 128), torch.float16) for _ in range(3))
+    ms = _time_ms(lambda: fa.flash_attention(q, k, v, causal=True, window_size=(512, 0)), 10, 3)
+    pairs = sum(min(i + 1, 513) for i in range(32768))
+    fl = 4.0 * 2 * 16 * 128 * pairs
+    byts = 4 * q.numel() * 2
+    out["config3_window512_fp16"] = {"ms": ms, "tflops": fl / ms / 1e9, "frac_tensor_peak": fl / ms / 1e9 / pk["tf"],
+                                     "gbs": byts / ms / 1e6, "frac_hbm_peak": byts / ms / 1e6 / pk["hbm"]}
+    del q, k, v
+    # config 5: packed varlen, 65536 tokens, lengths ~ U{128..4096}, H=16 D=64 bf16 causal, fwd + bwd
+    rng = np.random.default_rng(5)
+    lens = []
+    while sum(lens) < 65536:
+        lens.append(int(rng.integers(128, 4097)))
+    lens[-1] -= sum(lens) - 65536
+    cu = torch.tensor([0] + list(np.cumsum(lens)), dtype=torch.int32, device=device)
+    q, k, v, do = (mk((1, 16, 65536, 64), torch.bfloat16) for _ in range(4))
+    pairs = sum(L * (L + 1) // 2 for L in lens)
+    fl_fwd = 4.0 * 16 * 64 * pairs
+    ms_f = _time_ms(lambda: fa.flash_attention_varlen(q, k, v, cu, cu, max(lens), max(lens), causal=True), 10, 3)
+
+    def fb():
+        qg, kg, vg = q.detach().requires_grad_(True), k.detach().requires_grad_(True), v.detach().requires_grad_(True)
+        fa.flash_attention_varlen(qg, kg, vg, cu, cu, max(lens), max(lens), causal=True).backward(do)
+
+    ms_fb = _time_ms(fb, 10, 3)
+    out["config5_varlen_bf16_d64"] = {"num_seqs": len(lens), "fwd_ms": ms_f, "fwd_tflops": fl_fwd / ms_f / 1e9,
+                                      "fwd_bwd_ms": ms_fb, "fwd_bwd_tflops": 3.5 * fl_fwd / ms_fb / 1e9,
+                                      "frac_tensor_peak": 3.5 * fl_fwd / ms_fb / 1e9 / pk["tf"]}
+    return out
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -240,6 +300,7 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-decode", action="store_true", help="skip the config-4 decode measurement")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-extras", action="store_true", help="skip configs 1, 3 and 5")
     ap.add_argument("--small", action="store_true", help="profiling aid: N=S=4096, B=2 (not a bench value)")
     ap.add_argument("--only-decode", type=int, default=0, metavar="B",
                     help="profiling aid: run only the decode measurement with batch B (not a bench value)")
@@ -350,6 +411,9 @@ def main():
             decode = bench_decode(device, max(args.steps, 10), warm, pk)
         except NotImplementedError as e:  # decode kernel not built for this shape
             decode = {"unavailable": str(e)}
+    extras = None
+    if rank == 0 and world == 1 and not args.no_extras:
+        extras = bench_extras(device, pk)
     if dist is not None:
         dist.barrier()
 
@@ -374,6 +438,7 @@ def main():
             "gpu_launches": args.steps,
             "clocks": clocks,
             "decode": decode,
+            "extras": extras,
         }
         if args.small:
             line["note"] = "--small profiling case, not a bench value"

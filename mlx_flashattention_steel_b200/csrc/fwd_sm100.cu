@@ -306,8 +306,8 @@ fa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
           mma_ss(d_tmem, qd + (k >> 2) * kHalfQ + (k & 3) * 2, kd + (k >> 2) * kHalfK + (k & 3) * 2, idesc_qk,
                  k > 0 ? 1u : 0u);
         }
+        tc_commit(bar(BAR_S_FULL + st));        // the softmax warps first, then the producer
         tc_commit(bar(BAR_K_EMPTY + st));
-        tc_commit(bar(BAR_S_FULL + st));
         return true;
       };
       if (ok) ok = issue_s(0);
@@ -317,8 +317,9 @@ fa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
           ok = issue_s(j + 1);
           if (!ok) break;
         }
-        if (!mbar_wait_bounded(bar(BAR_P_FULL + st), (j >> 1) & 1, s_abort)) { ok = false; break; }
+        // V landed long ago; wait for it first so that nothing but the MMA issue follows the arrival of P
         if (!mbar_wait_bounded(bar(BAR_V_FULL + st), (j >> 1) & 1, s_abort)) { ok = false; break; }
+        if (!mbar_wait_bounded(bar(BAR_P_FULL + st), (j >> 1) & 1, s_abort)) { ok = false; break; }
         tc_fence_after();
         const uint64_t vd = vd0 + static_cast<uint64_t>(st) * kStageKV;
         const uint32_t a_tmem = tS0 + st * 64;
@@ -328,8 +329,8 @@ fa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
           // a k-step is 16 keys = 2048 B (128 units).  A = P in TMEM: 16 16-bit values = 8 columns per k-step.
           mma_ts(tO, a_tmem + k * 8, vd + k * 128, idesc_pv, (j > 0 || k > 0) ? 1u : 0u);
         }
-        tc_commit(bar(BAR_V_EMPTY + st));
         tc_commit(bar(BAR_PV_DONE));
+        tc_commit(bar(BAR_V_EMPTY + st));
       }
     }
   } else {

@@ -15,6 +15,8 @@ from .attention import (
     paged_kv_gather,
 )
 
+from .host_pipeline import HostPipeline, flash_attention_from_host
+
 __version__ = "0.1.0"
 
 __all__ = [
@@ -23,6 +25,8 @@ __all__ = [
     "flash_attention_kvcache",
     "flash_attention_paged",
     "paged_kv_gather",
+    "flash_attention_from_host",
+    "HostPipeline",
     "is_mfa_available",
     "get_device_info",
     "get_supported_configs",

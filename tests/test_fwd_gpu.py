@@ -190,3 +190,16 @@ def test_full_size_linearity_in_v(dev):
     ones = torch.full((B, Hkv, N, D), 0.75, dtype=torch.bfloat16, device=dev)
     oc = fa.flash_attention(q, k, ones, causal=True).float()
     assert float((oc - 0.75).abs().max()) <= 1e-2
+
+
+def test_host_pipeline_matches_device_call(dev):
+    """flash_attention_from_host (chunked, stream-pipelined copies) returns what the device call returns."""
+    q = randn((3, 8, 300, 128), torch.bfloat16, 130).pin_memory()
+    k = randn((3, 2, 300, 128), torch.bfloat16, 131).pin_memory()
+    v = randn((3, 2, 300, 128), torch.bfloat16, 132).pin_memory()
+    out, lse = fa.flash_attention_from_host(q, k, v, return_lse=True, causal=True, softcap=30.0, device=dev)
+    torch.cuda.synchronize()
+    ref, lref = fa.flash_attention(q.to(dev), k.to(dev), v.to(dev), causal=True, softcap=30.0, return_lse=True)
+    assert torch.equal(out, ref.cpu()) and torch.equal(lse, lref.cpu())
+    with pytest.raises(ValueError):
+        fa.flash_attention_from_host(q.to(dev), k, v)

@@ -162,7 +162,7 @@ int32_t b200fa_fwd(const b200fa_desc* d, const void* q, const void* k, const voi
   if (d->dtype == B200FA_F32) {
     e = b200fa::launch_fwd_f32(p, d->D, false, d->B, d->N, cs);
   } else if (!(d->flags & B200FA_FLAG_FORCE_MMA_SYNC) && b200fa::fwd_sm100_supported(p, d->dtype, d->D)) {
-    e = b200fa::launch_fwd_sm100(p, d->dtype, d->D, cs);
+    e = b200fa::launch_fwd_sm100(p, d->dtype, d->D, d->B, d->N, cs);
   } else {
     e = b200fa::launch_fwd_mma(p, d->dtype, d->D, false, d->B, d->N, cs);
   }
@@ -194,9 +194,14 @@ int32_t b200fa_fwd_varlen(const b200fa_desc* d, const void* q, const void* k, co
   p.cu_q = cu_seqlens_q;
   p.cu_k = cu_seqlens_k;
   cudaStream_t cs = reinterpret_cast<cudaStream_t>(stream);
-  cudaError_t e = d->dtype == B200FA_F32
-                      ? b200fa::launch_fwd_f32(p, d->D, true, num_seqs, max_seqlen_q, cs)
-                      : b200fa::launch_fwd_mma(p, d->dtype, d->D, true, num_seqs, max_seqlen_q, cs);
+  cudaError_t e;
+  if (d->dtype == B200FA_F32) {
+    e = b200fa::launch_fwd_f32(p, d->D, true, num_seqs, max_seqlen_q, cs);
+  } else if (!(d->flags & B200FA_FLAG_FORCE_MMA_SYNC) && b200fa::fwd_sm100_supported(p, d->dtype, d->D)) {
+    e = b200fa::launch_fwd_sm100(p, d->dtype, d->D, num_seqs, max_seqlen_q, cs);
+  } else {
+    e = b200fa::launch_fwd_mma(p, d->dtype, d->D, true, num_seqs, max_seqlen_q, cs);
+  }
   if (e != cudaSuccess) return cuda_fail(e, "varlen forward launch");
   return B200FA_OK;
 }

@@ -1,6 +1,6 @@
 // Blackwell forward kernel: tcgen05 MMAs with TMEM accumulators, TMA-staged tiles,
-// warp-specialised roles.  Dense layout, 16-bit, D = 128; any N, S; GQA; causal
-// (lower-right), left window, softcap, lse.  What it computes is the reference forward
+// warp-specialised roles.  Dense and packed-varlen layouts, 16-bit, D = 64 or 128; any N, S; GQA;
+// causal (lower-right), left window, softcap, lse.  What it computes is the reference forward
 // (csrc/mfa_steel_fwd.cpp:801-1221); how is Blackwell's own:
 //
 //   warps 0-3  softmax: thread r owns query row r = TMEM lane r.  It pulls the row of
@@ -11,13 +11,13 @@
 //   warp 4     producer: TMA tensor copies of the Q tile (once) and of K / V tiles into
 //              two-stage rings, 128B-swizzled, completion on mbarriers.
 //   warp 5     MMA issue (one thread): S(j) = Q.K(j)^T  (SS, M=128 N=64 K=16 x8) into one
-//              of two S buffers, then O += P(j).V(j)  (A from TMEM, M=128 N=128 K=16 x4).
+//              of two S buffers, then O += P(j).V(j)  (A from TMEM, M=128 N=D K=16 x4).
 //              Issue order S(0) S(1) PV(0) S(2) PV(1) ... keeps the tensor pipe busy while
 //              the softmax warps work on the other buffer; tcgen05.commit signals the
 //              mbarriers that free smem stages and publish S / O.
 //
 // TMEM (256 of 512 columns, so two CTAs share an SM and hide each other's softmax):
-//   [0,64) S0 / P0   [64,128) S1 / P1   [128,256) O.
+//   [0,64) S0 / P0   [64,128) S1 / P1   [128,128+D) O.
 // Tiles above the causal diagonal or left of the window are skipped whole.
 // No load here uses cluster multicast.  Every mbarrier wait is bounded; on a timeout the
 // CTA raises its abort flag, frees its TMEM and leaves (outputs are then undefined and
@@ -34,15 +34,19 @@ namespace {
 
 constexpr int BM = 128;      // query rows per CTA
 constexpr int BN = 64;       // keys per tile
-constexpr int HD = 128;
 constexpr int kStages = 2;
 constexpr int kThreads = 192;
 constexpr uint32_t kTmemCols = 256;
 
-constexpr int kQBytes = BM * HD * 2;          // 32768: two 64-wide halves, [half][row][128 B]
-constexpr int kKVBytes = BN * HD * 2;         // 16384 per stage: [half][row][128 B]
-constexpr int kSmemTiles = kQBytes + 2 * kStages * kKVBytes;   // 98304
-constexpr int kSmemBytes = kSmemTiles + 256 + 1024;            // + barriers + alignment slack
+// Sizes that depend on the head dim (64 or 128).  Tiles are stored as 64-element (128-byte) wide halves,
+// [half][row][128 B], each half one 128B-swizzle atom wide.
+template <int HD> struct Cfg {
+  static constexpr int kHalves = HD / 64;
+  static constexpr int kQBytes = BM * HD * 2;          // 32768 (D=128) / 16384 (D=64)
+  static constexpr int kKVBytes = BN * HD * 2;         // 16384 / 8192 per stage
+  static constexpr int kSmemTiles = kQBytes + 2 * kStages * kKVBytes;
+  static constexpr int kSmemBytes = kSmemTiles + 256 + 1024;   // + barriers + alignment slack
+};
 
 // barrier slots (uint64 each)
 enum Bar {
@@ -193,11 +197,14 @@ __device__ __forceinline__ uint32_t pack16(int dtype, float a, float b) {
 // ---------------------------------------------------------------------------
 // kernel
 // ---------------------------------------------------------------------------
+template <int HD>
 __global__ void __launch_bounds__(kThreads, 2)
 fa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                     const __grid_constant__ CUtensorMap tmV, const Sm100Args a) {
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  constexpr int kHalves = Cfg<HD>::kHalves, kQBytes = Cfg<HD>::kQBytes, kKVBytes = Cfg<HD>::kKVBytes,
+                kSmemTiles = Cfg<HD>::kSmemTiles;
   unsigned char* sQ = smem;
   unsigned char* sK = sQ + kQBytes;
   unsigned char* sV = sK + kStages * kKVBytes;
@@ -207,10 +214,21 @@ fa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
 
   const FwdParams& p = a.p;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int head = blockIdx.y, batch = blockIdx.z;
+  const int head = blockIdx.y;
+  int batch = blockIdx.z;
   const int kvh = head / p.gqa;
-  const int N = p.N, S = p.S;
+  int N = p.N, S = p.S, q_begin = 0, k_begin = 0;
+  if (p.cu_q != nullptr) {
+    // packed varlen: blockIdx.z is the sequence; rows of the neighbouring sequences that a tile drags in
+    // are masked (keys) or simply not stored (queries)
+    q_begin = p.cu_q[batch];
+    N = p.cu_q[batch + 1] - q_begin;
+    k_begin = p.cu_k[batch];
+    S = p.cu_k[batch + 1] - k_begin;
+    batch = 0;
+  }
   const int q0 = (static_cast<int>(gridDim.x) - 1 - static_cast<int>(blockIdx.x)) * BM;
+  if (q0 >= N) return;
   const int off = S - N;
   int k_hi = S;
   if (p.causal) k_hi = min(S, q0 + BM + off);
@@ -228,10 +246,10 @@ fa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       const int row = q0 + tid;
       if (row < N) {
         uint4* orow = reinterpret_cast<uint4*>(reinterpret_cast<uint16_t*>(p.o) + batch * p.o_bs + head * p.o_hs +
-                                               static_cast<int64_t>(row) * p.o_rs);
+                                               static_cast<int64_t>(q_begin + row) * p.o_rs);
 #pragma unroll
         for (int i = 0; i < HD / 8; ++i) orow[i] = make_uint4(0u, 0u, 0u, 0u);
-        if (p.lse != nullptr) p.lse[batch * p.lse_bs + head * p.lse_hs + row] = -INFINITY;
+        if (p.lse != nullptr) p.lse[batch * p.lse_bs + head * p.lse_hs + q_begin + row] = -INFINITY;
       }
     }
     return;
@@ -260,26 +278,29 @@ fa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = *s_tmem;
-  const uint32_t tS0 = tmem, tO = tmem + 128;   // S buffers at +0 and +64, O at +128
+  const uint32_t tS0 = tmem, tO = tmem + 128;   // S buffers at +0 and +64, O (HD columns) at +128
 
   if (warp == 4) {
     // ============================ producer ============================
     if (lane == 0) {
       mbar_arrive_expect_tx(bar(BAR_Q), kQBytes);
-      tma_load_4d(smem_u32(sQ), &tmQ, bar(BAR_Q), 0, q0, head, batch);
-      tma_load_4d(smem_u32(sQ + kQBytes / 2), &tmQ, bar(BAR_Q), 64, q0, head, batch);
+#pragma unroll
+      for (int hf = 0; hf < kHalves; ++hf)
+        tma_load_4d(smem_u32(sQ + hf * (kQBytes / kHalves)), &tmQ, bar(BAR_Q), 64 * hf, q_begin + q0, head, batch);
       for (int j = 0; j < n_tiles; ++j) {
         const int st = j & 1;
         const uint32_t par = ((j >> 1) & 1) ^ 1;
-        const int krow = (kt_begin + j) * BN;
+        const int krow = k_begin + (kt_begin + j) * BN;
         if (!mbar_wait_bounded(bar(BAR_K_EMPTY + st), par, s_abort)) break;
         mbar_arrive_expect_tx(bar(BAR_K_FULL + st), kKVBytes);
-        tma_load_4d(smem_u32(sK + st * kKVBytes), &tmK, bar(BAR_K_FULL + st), 0, krow, kvh, batch);
-        tma_load_4d(smem_u32(sK + st * kKVBytes + kKVBytes / 2), &tmK, bar(BAR_K_FULL + st), 64, krow, kvh, batch);
+#pragma unroll
+        for (int hf = 0; hf < kHalves; ++hf)
+          tma_load_4d(smem_u32(sK + st * kKVBytes + hf * (kKVBytes / kHalves)), &tmK, bar(BAR_K_FULL + st), 64 * hf, krow, kvh, batch);
         if (!mbar_wait_bounded(bar(BAR_V_EMPTY + st), par, s_abort)) break;
         mbar_arrive_expect_tx(bar(BAR_V_FULL + st), kKVBytes);
-        tma_load_4d(smem_u32(sV + st * kKVBytes), &tmV, bar(BAR_V_FULL + st), 0, krow, kvh, batch);
-        tma_load_4d(smem_u32(sV + st * kKVBytes + kKVBytes / 2), &tmV, bar(BAR_V_FULL + st), 64, krow, kvh, batch);
+#pragma unroll
+        for (int hf = 0; hf < kHalves; ++hf)
+          tma_load_4d(smem_u32(sV + st * kKVBytes + hf * (kKVBytes / kHalves)), &tmV, bar(BAR_V_FULL + st), 64 * hf, krow, kvh, batch);
       }
     }
   } else if (warp == 5) {
@@ -291,8 +312,8 @@ fa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       // the issue loop is a handful of integer adds per MMA.
       const uint64_t qd = smem_desc(smem_u32(sQ), 16, 1024);
       const uint64_t kd0 = smem_desc(smem_u32(sK), 16, 1024);
-      const uint64_t vd0 = smem_desc(smem_u32(sV), kKVBytes / 2, 1024);
-      constexpr uint64_t kHalfQ = (kQBytes / 2) >> 4, kHalfK = (kKVBytes / 2) >> 4, kStageKV = kKVBytes >> 4;
+      const uint64_t vd0 = smem_desc(smem_u32(sV), kKVBytes / kHalves, 1024);
+      constexpr uint64_t kHalfQ = (kQBytes / kHalves) >> 4, kHalfK = (kKVBytes / kHalves) >> 4, kStageKV = kKVBytes >> 4;
       bool ok = mbar_wait_bounded(bar(BAR_Q), 0, s_abort);
       auto issue_s = [&](int j) -> bool {
         const int st = j & 1;
@@ -489,7 +510,8 @@ fa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     if (ok) {
       tc_fence_after();
       const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
-      uint16_t* orow = reinterpret_cast<uint16_t*>(p.o) + batch * p.o_bs + head * p.o_hs + static_cast<int64_t>(row) * p.o_rs;
+      uint16_t* orow = reinterpret_cast<uint16_t*>(p.o) + batch * p.o_bs + head * p.o_hs +
+                       static_cast<int64_t>(q_begin + row) * p.o_rs;
 #pragma unroll
       for (int c = 0; c < HD / 32; ++c) {
         uint32_t o[32];
@@ -508,7 +530,7 @@ fa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         }
       }
       if (p.lse != nullptr && row < N)
-        p.lse[batch * p.lse_bs + head * p.lse_hs + row] = l_run > 0.f ? m_used + log2f(l_run) : -INFINITY;
+        p.lse[batch * p.lse_bs + head * p.lse_hs + q_begin + row] = l_run > 0.f ? m_used + log2f(l_run) : -INFINITY;
     }
   }
 
@@ -536,15 +558,15 @@ bool make_map(CUtensorMap* m, int dtype, const void* base, int D, int rows, int 
 }  // namespace
 
 bool fwd_sm100_supported(const FwdParams& p, int dtype, int D) {
-  if (!(dtype == 0 || dtype == 1) || D != HD) return false;
+  if (!(dtype == 0 || dtype == 1) || !(D == 64 || D == 128)) return false;
   if (p.N <= 0 || p.S <= 0 || p.B <= 0) return false;
-  // TMA: a size-1 dimension still needs a legal stride; strides were validated as 16-byte multiples
   return get_encode_tiled() != nullptr;
 }
 
-cudaError_t launch_fwd_sm100(const FwdParams& p, int dtype, int D, cudaStream_t stream) {
-  (void)D;
+template <int HD>
+static cudaError_t launch_hd(const FwdParams& p, int dtype, int nbatch, int max_q, cudaStream_t stream) {
   CUtensorMap tmQ, tmK, tmV;
+  // TMA: a size-1 dimension still needs a legal stride
   auto fix = [](int64_t s, int64_t fallback) { return s > 0 ? s : fallback; };
   const int64_t q_hs = fix(p.q_hs, static_cast<int64_t>(p.N) * p.q_rs), q_bs = fix(p.q_bs, q_hs * p.Hq);
   const int64_t k_hs = fix(p.k_hs, static_cast<int64_t>(p.S) * p.k_rs), k_bs = fix(p.k_bs, k_hs * p.Hkv);
@@ -557,11 +579,19 @@ cudaError_t launch_fwd_sm100(const FwdParams& p, int dtype, int D, cudaStream_t 
   a.p = p;
   a.dtype = dtype;
   a.status = nullptr;
-  cudaError_t e = cudaFuncSetAttribute(fa_fwd_sm100_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+  cudaError_t e = cudaFuncSetAttribute(fa_fwd_sm100_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       Cfg<HD>::kSmemBytes);
   if (e != cudaSuccess) return e;
-  dim3 grid((p.N + BM - 1) / BM, p.Hq, p.B);
-  fa_fwd_sm100_kernel<<<grid, kThreads, kSmemBytes, stream>>>(tmQ, tmK, tmV, a);
+  dim3 grid((max_q + BM - 1) / BM, p.Hq, nbatch);
+  fa_fwd_sm100_kernel<HD><<<grid, kThreads, Cfg<HD>::kSmemBytes, stream>>>(tmQ, tmK, tmV, a);
   return cudaGetLastError();
+}
+
+// Dense: nbatch = B, max_q = N.  Packed varlen (p.cu_q set, B == 1, N/S = total tokens): nbatch = number of
+// sequences, max_q = longest query sequence.
+cudaError_t launch_fwd_sm100(const FwdParams& p, int dtype, int D, int nbatch, int max_q, cudaStream_t stream) {
+  if (nbatch <= 0 || max_q <= 0) return cudaSuccess;
+  return D == 64 ? launch_hd<64>(p, dtype, nbatch, max_q, stream) : launch_hd<128>(p, dtype, nbatch, max_q, stream);
 }
 
 }  // namespace b200fa

@@ -18,10 +18,9 @@ cudaError_t launch_fwd_mma(const FwdParams& p, int dtype, int D, bool varlen, in
 cudaError_t launch_fwd_f32(const FwdParams& p, int D, bool varlen, int nbatch, int max_q,
                            cudaStream_t stream);
 
-// tcgen05 / TMEM / TMA forward (dense layout, D = 128, 16-bit).  Returns
-// cudaErrorNotSupported when the shape is outside what the kernel takes.
+// tcgen05 / TMEM / TMA forward (dense and packed-varlen layouts, D = 64 or 128, 16-bit).
 bool fwd_sm100_supported(const FwdParams& p, int dtype, int D);
-cudaError_t launch_fwd_sm100(const FwdParams& p, int dtype, int D, cudaStream_t stream);
+cudaError_t launch_fwd_sm100(const FwdParams& p, int dtype, int D, int nbatch, int max_q, cudaStream_t stream);
 
 cudaError_t launch_paged_gather(const void* pool, const int32_t* block_table, const int32_t* seq_lens,
                                 int B, int H, int D, int elem_bytes, int block_size, int max_blocks,

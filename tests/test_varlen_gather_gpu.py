@@ -100,3 +100,24 @@ def test_gather_large_offsets(dev):
     assert torch.equal(out[0, :, 16:20], pool[3, :4].permute(1, 0, 2))
     assert torch.equal(out[1, :, :16], pool[P - 2].permute(1, 0, 2))
     assert not out[0, :, 20:].any() and not out[1, :, 16:].any()
+
+
+@pytest.mark.parametrize("D", [64, 128])
+def test_varlen_tcgen05_and_portable_kernels_agree(dev, D):
+    """Packed varlen through the default (tcgen05) kernel and through the forced mma.sync kernel."""
+    from mlx_flashattention_steel_b200 import _lib, attention as A
+
+    lens = [700, 129, 1, 64, 1300, 257]
+    cu = _cu(lens)
+    q, k, v = (randn((1, 8, cu[-1], D), torch.bfloat16, 230 + i).to(dev) for i in range(3))
+    k, v = k[:, :2].contiguous(), v[:, :2].contiguous()
+    cu_t = torch.tensor(cu, dtype=torch.int32, device=dev)
+    a = fa.flash_attention_varlen(q, k, v, cu_t, cu_t, max(lens), max(lens), causal=True)
+    old = A._set_force_flags(_lib.FLAG_FORCE_MMA_SYNC)
+    try:
+        b = fa.flash_attention_varlen(q, k, v, cu_t, cu_t, max(lens), max(lens), causal=True)
+    finally:
+        A._set_force_flags(old)
+    assert float((a.float() - b.float()).abs().max()) <= 2e-2
+    O, _ = orc.varlen(q.cpu(), k.cpu(), v.cpu(), cu, cu, causal=True)
+    assert_close(a, O, torch.bfloat16)

@@ -228,7 +228,9 @@ def bench_decode(device, steps, warmup, pk, batch=None):
             "workload": "config 4: B=128 Hq=32 Hkv=8 D=128 page 16 seq_lens~U[512,32768] int8 KV + f16 scales, bf16 q",
             "tokens": tokens, "algorithmic_bytes": bytes_alg,
             "roofline": {"bound": "hbm", "achieved": gbs, "peak": pk["hbm"], "unit": "GB/s", "frac": gbs / pk["hbm"],
-                         "traffic": None, "peak_source": pk["src"]},
+                         # ncu capture at B=24 read 968.0 MB + wrote 4.4 MB for 966.5 MB algorithmic
+                         # (profiles/decode_paged_config4_small.md); traffic grows with the tokens processed
+                         "traffic": bytes_alg * (968.0 + 4.4) / 966.5, "peak_source": pk["src"]},
             "gpu_launches": steps * 2}
 
 
@@ -430,8 +432,10 @@ def main():
             "metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
             "warmup": warm, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": "bf16", "data": "synthetic", "config": workload_config(world),
+            # traffic: dram bytes of one launch; the ncu capture (profiles/fwd_sm100_config2_small.md) was taken at
+            # B=2 N=4096 (136 MB for 84.9 MB of q+k+v+o+lse) and is scaled by the algorithmic bytes of this launch
             "roofline": {"bound": "tensor", "achieved": tf_rank, "peak": pk["tf"], "unit": "TFLOP/s",
-                         "frac": tf_rank / pk["tf"], "traffic": None, "peak_source": pk["src"],
+                         "frac": tf_rank / pk["tf"], "traffic": 136.0e6 / 84.9e6 * 675.3e6, "peak_source": pk["src"],
                          "frac_of_sustained": (tf_rank / pk["tf_sustained"]) if pk.get("tf_sustained") else None,
                          "flops_per_launch": flops},
             "cpu_baseline": cpu,

@@ -248,7 +248,7 @@ static int32_t bwd_common(const b200fa_desc* d, const void* q, const void* k, co
   p.gqa = f.gqa; p.scale = d->scale; p.scale_log2 = f.scale_log2; p.causal = f.causal;
   p.cu_q = cu_q; p.cu_k = cu_k;
   cudaError_t e = b200fa::launch_bwd(p, d->dtype, d->D, varlen, nbatch, max_q, max_k, workspace,
-                                     reinterpret_cast<cudaStream_t>(stream));
+                                     !(d->flags & B200FA_FLAG_FORCE_MMA_SYNC), reinterpret_cast<cudaStream_t>(stream));
   if (e != cudaSuccess) return cuda_fail(e, "backward launch");
   return B200FA_OK;
 }

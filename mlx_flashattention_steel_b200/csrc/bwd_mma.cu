@@ -323,7 +323,7 @@ __global__ void __launch_bounds__(kThreads) bwd_main_kernel(const BwdParams p) {
 }
 
 template <typename T, int D>
-cudaError_t launch_t(const BwdParams& p, bool varlen, int nbatch, int max_k, cudaStream_t stream) {
+cudaError_t launch_t(const BwdParams& p, int dtype, bool varlen, int nbatch, int max_k, bool allow_sm100, cudaStream_t stream) {
   const int total_rows = p.B * p.Hq * p.N;
   {
     const int blocks = (total_rows + 7) / 8;
@@ -334,7 +334,10 @@ cudaError_t launch_t(const BwdParams& p, bool varlen, int nbatch, int max_k, cud
   constexpr size_t smem = (2 * kBN * D + 4 * kBM * D + kBN * kBM) * sizeof(T) + 4 * kBM * sizeof(float);
   dim3 grid((max_k + kBN - 1) / kBN, p.Hkv, nbatch);
   cudaError_t e;
-  if (varlen) {
+  if (allow_sm100 && bwd_sm100_supported(dtype, D)) {
+    e = launch_bwd_sm100_main(p, dtype, nbatch, max_k, stream);
+    if (e != cudaSuccess) return e;
+  } else if (varlen) {
     e = cudaFuncSetAttribute(bwd_main_kernel<T, D, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
     if (e != cudaSuccess) return e;
     if (grid.x > 0) bwd_main_kernel<T, D, true><<<grid, kThreads, smem, stream>>>(p);
@@ -360,17 +363,17 @@ size_t bwd_workspace_bytes(int B, int Hq, int N_total, int D) {
 }
 
 cudaError_t launch_bwd(const BwdParams& p_in, int dtype, int D, bool varlen, int nbatch, int max_q, int max_k,
-                       void* workspace, cudaStream_t stream) {
+                       void* workspace, bool allow_sm100, cudaStream_t stream) {
   (void)max_q;
   BwdParams p = p_in;
   const size_t rows = static_cast<size_t>(p.B) * p.Hq * p.N;
   p.delta = reinterpret_cast<float*>(workspace);
   p.dq_acc = reinterpret_cast<float*>(reinterpret_cast<unsigned char*>(workspace) + bwd_align(rows * sizeof(float)));
   if (rows == 0) return cudaSuccess;
-  if (dtype == 0 && D == 64) return launch_t<__half, 64>(p, varlen, nbatch, max_k, stream);
-  if (dtype == 0 && D == 128) return launch_t<__half, 128>(p, varlen, nbatch, max_k, stream);
-  if (dtype == 1 && D == 64) return launch_t<__nv_bfloat16, 64>(p, varlen, nbatch, max_k, stream);
-  if (dtype == 1 && D == 128) return launch_t<__nv_bfloat16, 128>(p, varlen, nbatch, max_k, stream);
+  if (dtype == 0 && D == 64) return launch_t<__half, 64>(p, dtype, varlen, nbatch, max_k, allow_sm100, stream);
+  if (dtype == 0 && D == 128) return launch_t<__half, 128>(p, dtype, varlen, nbatch, max_k, allow_sm100, stream);
+  if (dtype == 1 && D == 64) return launch_t<__nv_bfloat16, 64>(p, dtype, varlen, nbatch, max_k, allow_sm100, stream);
+  if (dtype == 1 && D == 128) return launch_t<__nv_bfloat16, 128>(p, dtype, varlen, nbatch, max_k, allow_sm100, stream);
   return cudaErrorInvalidValue;
 }
 

@@ -27,7 +27,11 @@ cudaError_t launch_paged_gather(const void* pool, const int32_t* block_table, co
                                 int max_kv_len, void* out, cudaStream_t stream);
 
 size_t bwd_workspace_bytes(int B, int Hq, int N_total, int D);
+// allow_sm100: let the tcgen05 main kernel run where it exists (head_dim 64); the preprocess and the
+// dQ conversion are common to both.
 cudaError_t launch_bwd(const BwdParams& p, int dtype, int D, bool varlen, int nbatch, int max_q,
-                       int max_k, void* workspace, cudaStream_t stream);
+                       int max_k, void* workspace, bool allow_sm100, cudaStream_t stream);
+bool bwd_sm100_supported(int dtype, int D);
+cudaError_t launch_bwd_sm100_main(const BwdParams& p, int dtype, int nbatch, int max_k, cudaStream_t stream);
 
 }  // namespace b200fa

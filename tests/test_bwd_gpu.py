@@ -115,3 +115,29 @@ def test_backward_linearity_full_size(dev):
         res.append((qg.grad.float(), kg.grad.float(), vg.grad.float()))
     for a, b, c in zip(*res):
         assert float((c - (a + b)).abs().max()) <= 8e-2 * max(1.0, float(c.abs().max()) / 4)
+
+
+def test_backward_tcgen05_and_portable_kernels_agree(dev):
+    """head_dim 64 runs the tcgen05 backward by default; forcing the mma.sync kernels must give the same
+    gradients within tolerance (and different bits, which shows that two kernels really ran)."""
+    from mlx_flashattention_steel_b200 import _lib, attention as A
+
+    q, k, v, do = (randn((2, 8, 700, 64), torch.bfloat16, 560 + i).to(dev) for i in range(4))
+    k, v = k[:, :2].contiguous(), v[:, :2].contiguous()
+
+    def grads():
+        qg, kg, vg = (x.clone().requires_grad_(True) for x in (q, k, v))
+        fa.flash_attention(qg, kg, vg, causal=True).backward(do)
+        return qg.grad.float(), kg.grad.float(), vg.grad.float()
+
+    g1 = grads()
+    old = A._set_force_flags(_lib.FLAG_FORCE_MMA_SYNC)
+    try:
+        g2 = grads()
+    finally:
+        A._set_force_flags(old)
+    differs = False
+    for a, b in zip(g1, g2):
+        assert float((a - b).abs().max()) <= 2e-2 + 2.0 ** -7 * float(b.abs().max())
+        differs = differs or not torch.equal(a, b)
+    assert differs

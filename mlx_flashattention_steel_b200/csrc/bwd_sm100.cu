@@ -4,16 +4,18 @@
 //
 // One CTA owns a tile of 128 keys of one kv head and walks the query heads of the GQA group and the
 // 128-row query tiles that can see those keys.  Per query tile, five GEMMs, all M = 128:
-//   S^T  = K . Q^T      (SS, N = 128 queries, K = 64)      -> TMEM [  0,128)
-//   dP^T = V . dO^T     (SS)                                -> TMEM [128,256)
+//   S^T  = K . Q^T      (SS, per half of 64 queries, K = 64)   -> TMEM [0,64) and [128,192)
+//   dP^T = V . dO^T     (SS, per half)                          -> TMEM [64,128) and [192,256)
 //   8 compute warps (thread = key row, two warps per 32 rows splitting the query columns) turn these into
 //   P^T = 2^(scale*log2e*S^T - L) and dS^T = P^T o (dP^T - delta), written back as 16-bit A operands over
 //   the columns they came from, and dS also to shared memory as a [query][key] tile
 //   dV  += P^T . dO     (A from TMEM, B = dO as an MN-major operand, N = 64)   -> TMEM [256,320)
 //   dK  += dS^T . Q     (A from TMEM, B = Q MN-major)                          -> TMEM [320,384)
 //   dQ   = dS . K       (SS: A = dS tile, B = K MN-major)                      -> TMEM [384,448)
-// dQ is read out of TMEM by the compute warps while the next tile's S^T / dP^T are being computed and
-// added to the fp32 accumulator with vector red.global.add; dK / dV leave TMEM once, at the end.
+// The two query halves have their own S^T / dP^T columns and dS has two shared-memory buffers, so the MMAs of one
+// half (and the next tile's S^T / dP^T) run while the compute warps work on the other half.  dQ is read out of TMEM by
+// the compute warps between the halves of the next tile and added to the fp32 accumulator with vector red.global.add;
+// dK / dV leave TMEM once, at the end.
 // Warp 8 is the TMA producer (K, V once; Q, dO double-buffered; L and delta staged with them), warp 9
 // issues the MMAs.  No load uses cluster multicast; every mbarrier wait is bounded.
 #include <type_traits>
@@ -32,20 +34,32 @@ constexpr int BQ = 128;      // queries per step
 constexpr int HD = 64;
 constexpr int kThreads = 320;
 constexpr uint32_t kTmemCols = 512;
-constexpr uint32_t cST = 0, cDPT = 128, cDV = 256, cDK = 320, cDQ = 384;
+// query half x (64 queries): S^T at cST + 128x, dP^T at cDPT + 128x
+constexpr uint32_t cST = 0, cDPT = 64, cDV = 256, cDK = 320, cDQ = 384;
 
 constexpr int kTileBytes = 128 * HD * 2;                 // 16384: one [128 rows][64] tile
 constexpr int kDSBytes = BQ * BK * 2;                    // 32768: dS as two 64-key halves [half][query][128 B]
 constexpr int kStatBytes = 2 * 2 * BQ * 4;               // L and delta, two stages
-constexpr int kSmemTiles = 2 * kTileBytes + 4 * kTileBytes + kDSBytes;   // K, V, Q x2, dO x2, dS = 131072
+constexpr int kSmemTiles = 2 * kTileBytes + 4 * kTileBytes + 2 * kDSBytes;   // K, V, Q x2, dO x2, dS x2 = 163840
 constexpr int kSmemBytes = kSmemTiles + kStatBytes + 256 + 1024;
 
-enum Bar { BAR_KV = 0, BAR_Q_FULL = 1, BAR_Q_EMPTY = 3, BAR_ST_DONE = 5, BAR_PD_READY = 6, BAR_DQ_DONE = 7, BAR_COUNT = 8 };
+enum Bar { BAR_KV = 0, BAR_Q_FULL = 1, BAR_Q_EMPTY = 3, BAR_ST_DONE = 5 /* + half */, BAR_PD_READY = 7 /* + half */, BAR_DQ_DONE = 9, BAR_COUNT = 10 };
 
 struct BwdArgs {
   BwdParams p;
   int dtype;
 };
+
+__device__ __forceinline__ float4 lds_f4(uint32_t addr) {
+  float4 v;
+  asm volatile("ld.shared.v4.f32 {%0,%1,%2,%3}, [%4];\n" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(addr));
+  return v;
+}
+// dS element of query `ql` (inside the warp's 32 columns): row pitch 128 bytes; ql is a constant after unrolling,
+// so the offset folds into the instruction's immediate
+__device__ __forceinline__ void sts_row(uint32_t addr, int ql, uint32_t v) {
+  asm volatile("st.shared.u16 [%0], %1;\n" ::"r"(addr + static_cast<uint32_t>(ql) * 128u), "h"(static_cast<unsigned short>(v)) : "memory");
+}
 
 __device__ __forceinline__ uint32_t pack16b(int dtype, float a, float b) {
   return dtype == 0 ? Elem<__half>::pack(a, b) : Elem<__nv_bfloat16>::pack(a, b);
@@ -60,7 +74,7 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   unsigned char* sV = sK + kTileBytes;
   unsigned char* sQ = sV + kTileBytes;                 // [2][128][128 B]
   unsigned char* sDO = sQ + 2 * kTileBytes;            // [2][128][128 B]
-  unsigned char* sDS = sDO + 2 * kTileBytes;           // [2 halves][128 queries][128 B]
+  unsigned char* sDS = sDO + 2 * kTileBytes;           // [2 buffers][2 key halves][128 queries][128 B]
   float* sL = reinterpret_cast<float*>(smem + kSmemTiles);      // [2][BQ]
   float* sDel = sL + 2 * BQ;                                    // [2][BQ]
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kSmemTiles + kStatBytes);
@@ -112,8 +126,10 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       mbar_init(bar(BAR_Q_FULL + s), 1);
       mbar_init(bar(BAR_Q_EMPTY + s), 1);
     }
-    mbar_init(bar(BAR_ST_DONE), 1);
-    mbar_init(bar(BAR_PD_READY), 8);      // one arrive per compute warp
+    for (int x = 0; x < 2; ++x) {
+      mbar_init(bar(BAR_ST_DONE + x), 1);
+      mbar_init(bar(BAR_PD_READY + x), 8);  // one arrive per compute warp
+    }
     mbar_init(bar(BAR_DQ_DONE), 1);
     *s_abort = 0;
     fence_barrier_init();
@@ -165,54 +181,72 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     }
   } else if (warp == 9) {
     // ============================ MMA issue ============================
+    // Per query tile t and query half x: [S^T_x, dP^T_x] -> (compute) -> [dV += P^T_x.dO_x, dK += dS^T_x.Q_x]; after both
+    // halves dQ = dS.K.  Issue order keeps the pipe fed while the compute warps work on the other half:
+    //   ST/DPT a,b (t=0) | PD_a -> dV_a dK_a, ST/DPT a (t+1) | PD_b -> dV_b dK_b, dQ, ST/DPT b (t+1) | ...
     const bool leader = lane == 0;
-    const uint32_t id_st = instr_desc(a.dtype, 0, 128, BQ);     // S^T, dP^T: B K-major, N = 128
+    const uint32_t id_st = instr_desc(a.dtype, 0, 128, 64);     // S^T, dP^T of one half: B K-major, N = 64
     const uint32_t id_mn = instr_desc(a.dtype, 1, 128, HD);     // dV, dK, dQ: B MN-major, N = 64
     const uint64_t kd = smem_desc(smem_u32(sK), 16, 1024), vd = smem_desc(smem_u32(sV), 16, 1024);
     const uint64_t kmn = smem_desc(smem_u32(sK), kTileBytes, 1024);
-    const uint64_t dsd = smem_desc(smem_u32(sDS), 16, 1024);
-    constexpr uint64_t kTileU = kTileBytes >> 4;
+    const uint64_t dsd0 = smem_desc(smem_u32(sDS), 16, 1024);
+    const uint64_t qd0 = smem_desc(smem_u32(sQ), 16, 1024), dod0 = smem_desc(smem_u32(sDO), 16, 1024);
+    const uint64_t qmn0 = smem_desc(smem_u32(sQ), kTileBytes, 1024), domn0 = smem_desc(smem_u32(sDO), kTileBytes, 1024);
+    constexpr uint64_t kTileU = kTileBytes >> 4, kHalfRowsU = (64 * 128) >> 4, kDSU = kDSBytes >> 4;
     bool ok = __all_sync(0xffffffffu, mbar_wait_bounded(bar(BAR_KV), 0, s_abort));
-    auto issue_stdp = [&](int it) -> bool {
+    // S^T_x and dP^T_x of tile `it`: B rows = the 64 queries of half x
+    auto issue_stdp = [&](int it, int x) -> bool {
       const int st = it & 1;
-      if (!__all_sync(0xffffffffu, mbar_wait_bounded(bar(BAR_Q_FULL + st), (it >> 1) & 1, s_abort))) return false;
-      tc_fence_after();
-      const uint64_t qd = smem_desc(smem_u32(sQ), 16, 1024) + st * kTileU;
-      const uint64_t dod = smem_desc(smem_u32(sDO), 16, 1024) + st * kTileU;
+      if (x == 0) {
+        if (!__all_sync(0xffffffffu, mbar_wait_bounded(bar(BAR_Q_FULL + st), (it >> 1) & 1, s_abort))) return false;
+        tc_fence_after();
+      }
+      const uint64_t qd = qd0 + st * kTileU + x * kHalfRowsU, dod = dod0 + st * kTileU + x * kHalfRowsU;
 #pragma unroll
       for (int k = 0; k < HD / 16; ++k)
-        if (leader) mma_ss(tmem + cST, kd + k * 2, qd + k * 2, id_st, k > 0 ? 1u : 0u);
+        if (leader) mma_ss(tmem + cST + 128 * x, kd + k * 2, qd + k * 2, id_st, k > 0 ? 1u : 0u);
 #pragma unroll
       for (int k = 0; k < HD / 16; ++k)
-        if (leader) mma_ss(tmem + cDPT, vd + k * 2, dod + k * 2, id_st, k > 0 ? 1u : 0u);
-      if (leader) tc_commit(bar(BAR_ST_DONE));
+        if (leader) mma_ss(tmem + cDPT + 128 * x, vd + k * 2, dod + k * 2, id_st, k > 0 ? 1u : 0u);
+      if (leader) tc_commit(bar(BAR_ST_DONE + x));
       __syncwarp();
       return true;
     };
-    if (ok) ok = issue_stdp(0);
+    if (ok) ok = issue_stdp(0, 0);
+    if (ok) ok = issue_stdp(0, 1);
     for (int it = 0; it < n_iter && ok; ++it) {
       const int st = it & 1;
-      if (!__all_sync(0xffffffffu, mbar_wait_bounded(bar(BAR_PD_READY), it & 1, s_abort))) { ok = false; break; }
-      tc_fence_after();
-      const uint64_t qmn = smem_desc(smem_u32(sQ), kTileBytes, 1024) + st * kTileU;
-      const uint64_t domn = smem_desc(smem_u32(sDO), kTileBytes, 1024) + st * kTileU;
-      // dV += P^T.dO and dK += dS^T.Q: A in TMEM (8 columns per 16 queries; queries 0-63 at +0, 64-127 at +64,
-      // where the two column halves were written), B rows = queries, 16 rows = 128 units
 #pragma unroll
-      for (int k = 0; k < BQ / 16; ++k)
-        if (leader) mma_ts(tmem + cDV, tmem + cST + (k >> 2) * 64 + (k & 3) * 8, domn + k * 128, id_mn, (it > 0 || k > 0) ? 1u : 0u);
+      for (int x = 0; x < 2; ++x) {
+        if (!__all_sync(0xffffffffu, mbar_wait_bounded(bar(BAR_PD_READY + x), it & 1, s_abort))) { ok = false; break; }
+        tc_fence_after();
+        const uint64_t qmn = qmn0 + st * kTileU + x * kHalfRowsU, domn = domn0 + st * kTileU + x * kHalfRowsU;
+        // A in TMEM: 8 columns per 16 queries; queries 0-31 of the half at +0, 32-63 at +32 (where the two warps of a
+        // row wrote them); B rows = queries, 16 rows = 128 units
 #pragma unroll
-      for (int k = 0; k < BQ / 16; ++k)
-        if (leader) mma_ts(tmem + cDK, tmem + cDPT + (k >> 2) * 64 + (k & 3) * 8, qmn + k * 128, id_mn, (it > 0 || k > 0) ? 1u : 0u);
-      if (leader) tc_commit(bar(BAR_Q_EMPTY + st));
-      // dQ = dS.K: A = dS [query][key] in two 64-key halves, B = K rows = keys
+        for (int k = 0; k < 4; ++k)
+          if (leader) mma_ts(tmem + cDV, tmem + cST + 128 * x + (k >> 1) * 32 + (k & 1) * 8, domn + k * 128, id_mn,
+                             (it > 0 || x > 0 || k > 0) ? 1u : 0u);
 #pragma unroll
-      for (int k = 0; k < BK / 16; ++k)
-        if (leader) mma_ss(tmem + cDQ, dsd + (k >> 2) * (static_cast<uint64_t>(kDSBytes / 2) >> 4) + (k & 3) * 2, kmn + k * 128,
-                           id_mn, k > 0 ? 1u : 0u);
-      if (leader) tc_commit(bar(BAR_DQ_DONE));
-      __syncwarp();
-      if (it + 1 < n_iter) ok = issue_stdp(it + 1);
+        for (int k = 0; k < 4; ++k)
+          if (leader) mma_ts(tmem + cDK, tmem + cDPT + 128 * x + (k >> 1) * 32 + (k & 1) * 8, qmn + k * 128, id_mn,
+                             (it > 0 || x > 0 || k > 0) ? 1u : 0u);
+        if (x == 1) {
+          if (leader) tc_commit(bar(BAR_Q_EMPTY + st));
+          // dQ = dS.K: A = dS [query][key] in two 64-key halves (buffer it & 1), B = K rows = keys
+          const uint64_t dsd = dsd0 + (it & 1) * kDSU;
+#pragma unroll
+          for (int k = 0; k < BK / 16; ++k)
+            if (leader) mma_ss(tmem + cDQ, dsd + (k >> 2) * (kDSU / 2) + (k & 3) * 2, kmn + k * 128, id_mn, k > 0 ? 1u : 0u);
+          if (leader) tc_commit(bar(BAR_DQ_DONE));
+        }
+        __syncwarp();
+        // the buffers of half x are free again (the MMAs above read them in pipe order before anything issued now)
+        if (it + 1 < n_iter) {
+          ok = issue_stdp(it + 1, x);
+          if (!ok) break;
+        }
+      }
     }
   } else {
     // ============================ compute warps 0-7 ============================
@@ -238,42 +272,36 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       }
     };
 
-    for (int it = 0; it < n_iter; ++it) {
+    for (int it = 0; it < n_iter && ok; ++it) {
       const int st = it & 1;
       const int m = m_begin + it % nm;
-      if (it > 0) {
-        if (!__all_sync(0xffffffffu, mbar_wait_bounded(bar(BAR_DQ_DONE), (it - 1) & 1, s_abort))) { ok = false; break; }
-        tc_fence_after();
-        flush_dq(it - 1);
-      }
       if (!__all_sync(0xffffffffu, mbar_wait_bounded(bar(BAR_Q_FULL + st), (it >> 1) & 1, s_abort))) { ok = false; break; }
-      if (!__all_sync(0xffffffffu, mbar_wait_bounded(bar(BAR_ST_DONE), it & 1, s_abort))) { ok = false; break; }
-      tc_fence_after();
-      const float* Ls = sL + st * BQ;
-      const float* Ds = sDel + st * BQ;
+      const uint32_t Ls = smem_u32(sL + st * BQ), Ds = smem_u32(sDel + st * BQ);
       const bool need_mask = (n0 + BK > S) || (p.causal && (n0 + BK - 1 > m * BQ + off));
-      // dS[query][this key] lives at ds_col + query * 128 + ((key chunk ^ (query & 7)) << 4); the eight swizzled
-      // chunk offsets are fixed per thread, and the query offsets are compile-time constants of the unrolled loop
-      unsigned char* ds_col = sDS + (rloc >> 6) * (kDSBytes / 2) + (rloc & 7) * 2;
+      // dS[query][this key] lives at ds_col + query * 128 + ((key chunk ^ (query & 7)) << 4) in buffer it & 1; the eight
+      // swizzled chunk offsets are fixed per thread, the query offsets are compile-time constants of the unrolled loop
+      const uint32_t ds_col = smem_u32(sDS) + (it & 1) * kDSBytes + (rloc >> 6) * (kDSBytes / 2) + (rloc & 7) * 2;
       const int kchunk = (rloc & 63) >> 3;
-      unsigned char* ds_sw[8];
+      uint32_t ds_sw[8];
 #pragma unroll
       for (int r = 0; r < 8; ++r) ds_sw[r] = ds_col + ((kchunk ^ r) << 4);
       const float2 c2 = make_float2(p.scale_log2, p.scale_log2);
-      auto run_tile = [&](auto masked) {
-#pragma unroll 1
-      for (int c = 0; c < 2; ++c) {
-        const int col0 = hf * 64 + c * 32;                 // first query column of this chunk
+
+      auto run_half = [&](int x, auto masked) {
+        const int q0l = x * 64 + hf * 32;                  // first query (inside the tile) of this warp's 32 columns
         uint32_t rs[32], rd[32];
-        tmem_ld32(tmem + lane_base + cST + col0, rs);
-        tmem_ld32(tmem + lane_base + cDPT + col0, rd);
+        tmem_ld32(tmem + lane_base + cST + 128 * x + hf * 32, rs);
+        tmem_ld32(tmem + lane_base + cDPT + 128 * x + hf * 32, rd);
         tc_wait_ld();
         uint32_t pp[16], pd[16];
-        const int rowoff = col0 * 128;
+        const uint32_t rowoff = q0l * 128;
+        uint32_t dsa[8];
+#pragma unroll
+        for (int r = 0; r < 8; ++r) dsa[r] = ds_sw[r] + rowoff;
 #pragma unroll
         for (int i = 0; i < 32; i += 4) {
-          const float4 nL = *reinterpret_cast<const float4*>(Ls + col0 + i);      // -L of four queries
-          const float4 nD = *reinterpret_cast<const float4*>(Ds + col0 + i);      // -delta
+          const float4 nL = lds_f4(Ls + (q0l + i) * 4);      // -L of four queries
+          const float4 nD = lds_f4(Ds + (q0l + i) * 4);      // -delta
 #pragma unroll
           for (int e = 0; e < 4; e += 2) {
             const float2 sv = make_float2(__uint_as_float(rs[i + e]), __uint_as_float(rs[i + e + 1]));
@@ -283,7 +311,7 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
             const float2 t = __ffma2_rn(sv, c2, nl);
             float2 pe = make_float2(fast_exp2(t.x), fast_exp2(t.y));
             if constexpr (decltype(masked)::value) {
-              const int qrow = m * BQ + col0 + i + e;
+              const int qrow = m * BQ + q0l + i + e;
               const bool kin = key < S;
               if (!(kin && (!p.causal || key <= qrow + off))) pe.x = 0.f;
               if (!(kin && (!p.causal || key <= qrow + 1 + off))) pe.y = 0.f;
@@ -292,24 +320,34 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
             pp[(i + e) >> 1] = pack16b(a.dtype, pe.x, pe.y);
             const uint32_t dpk = pack16b(a.dtype, dsv.x, dsv.y);
             pd[(i + e) >> 1] = dpk;
-            const int ql = i + e;                          // query inside the chunk; (col0 + ql) & 7 == ql & 7
-            *reinterpret_cast<uint16_t*>(ds_sw[ql & 7] + rowoff + ql * 128) = static_cast<uint16_t>(dpk & 0xffffu);
-            *reinterpret_cast<uint16_t*>(ds_sw[(ql + 1) & 7] + rowoff + (ql + 1) * 128) = static_cast<uint16_t>(dpk >> 16);
+            const int ql = i + e;                          // (q0l + ql) & 7 == ql & 7
+            sts_row(dsa[ql & 7], ql, dpk & 0xffffu);
+            sts_row(dsa[(ql + 1) & 7], ql + 1, dpk >> 16);
           }
         }
-        // P^T and dS^T overwrite the columns they came from: 16-bit pairs along the query index
-        // (inside this warp's own 64 columns, whose contents it has already loaded: the other warp of these
-        // rows may still be reading its half)
-        tmem_st16(tmem + lane_base + cST + hf * 64 + c * 16, pp);
-        tmem_st16(tmem + lane_base + cDPT + hf * 64 + c * 16, pd);
-      }
+        // P^T and dS^T go back as 16-bit pairs along the query index, inside the 32 columns this warp has just read
+        // (the other warp of these rows may still be reading its own 32)
+        tmem_st16(tmem + lane_base + cST + 128 * x + hf * 32, pp);
+        tmem_st16(tmem + lane_base + cDPT + 128 * x + hf * 32, pd);
       };
-      if (need_mask) run_tile(std::true_type{}); else run_tile(std::false_type{});
-      tc_wait_st();
-      fence_proxy_async();          // the dS tile was written with ordinary stores and is read by the MMA
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(bar(BAR_PD_READY));
+
+#pragma unroll
+      for (int x = 0; x < 2; ++x) {
+        if (x == 1 && it > 0) {
+          // dQ of the previous tile: read it out while the MMAs of this tile's first half run
+          if (!__all_sync(0xffffffffu, mbar_wait_bounded(bar(BAR_DQ_DONE), (it - 1) & 1, s_abort))) { ok = false; break; }
+          tc_fence_after();
+          flush_dq(it - 1);
+        }
+        if (!__all_sync(0xffffffffu, mbar_wait_bounded(bar(BAR_ST_DONE + x), it & 1, s_abort))) { ok = false; break; }
+        tc_fence_after();
+        if (need_mask) run_half(x, std::true_type{}); else run_half(x, std::false_type{});
+        tc_wait_st();
+        fence_proxy_async();          // the dS tile was written with ordinary stores and is read by the MMA
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar(BAR_PD_READY + x));
+      }
     }
 
     if (ok) ok = __all_sync(0xffffffffu, mbar_wait_bounded(bar(BAR_DQ_DONE), (n_iter - 1) & 1, s_abort));

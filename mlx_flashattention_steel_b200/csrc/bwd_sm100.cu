@@ -14,10 +14,9 @@
 //   dQ   = dS . K       (SS: A = dS tile, B = K MN-major)                      -> TMEM [384,448)
 // The two query halves have their own S^T / dP^T columns and dS has two shared-memory buffers, so the MMAs of one
 // half (and the next tile's S^T / dP^T) run while the compute warps work on the other half.  dQ is read out of TMEM by
-// the compute warps between the halves of the next tile and added to the fp32 accumulator with vector red.global.add;
-// dK / dV leave TMEM once, at the end.
+// four flush warps and added to the fp32 accumulator with vector red.global.add; dK / dV leave TMEM once, at the end.
 // Warp 8 is the TMA producer (K, V once; Q, dO double-buffered; L and delta staged with them), warp 9
-// issues the MMAs.  No load uses cluster multicast; every mbarrier wait is bounded.
+// issues the MMAs, warps 10-13 move dQ from TMEM to the fp32 accumulator.  No load uses cluster multicast; every mbarrier wait is bounded.
 #include <type_traits>
 
 #include "common.cuh"
@@ -32,7 +31,7 @@ namespace {
 constexpr int BK = 128;      // keys per CTA (TMEM lanes)
 constexpr int BQ = 128;      // queries per step
 constexpr int HD = 64;
-constexpr int kThreads = 320;
+constexpr int kThreads = 448;       // warps 0-7 compute, 8 producer, 9 MMA issue, 10-13 dQ flush
 constexpr uint32_t kTmemCols = 512;
 // query half x (64 queries): S^T at cST + 128x, dP^T at cDPT + 128x
 constexpr uint32_t cST = 0, cDPT = 64, cDV = 256, cDK = 320, cDQ = 384;
@@ -43,7 +42,7 @@ constexpr int kStatBytes = 2 * 2 * BQ * 4;               // L and delta, two sta
 constexpr int kSmemTiles = 2 * kTileBytes + 4 * kTileBytes + 2 * kDSBytes;   // K, V, Q x2, dO x2, dS x2 = 163840
 constexpr int kSmemBytes = kSmemTiles + kStatBytes + 256 + 1024;
 
-enum Bar { BAR_KV = 0, BAR_Q_FULL = 1, BAR_Q_EMPTY = 3, BAR_ST_DONE = 5 /* + half */, BAR_PD_READY = 7 /* + half */, BAR_DQ_DONE = 9, BAR_COUNT = 10 };
+enum Bar { BAR_KV = 0, BAR_Q_FULL = 1, BAR_Q_EMPTY = 3, BAR_ST_DONE = 5 /* + half */, BAR_PD_READY = 7 /* + half */, BAR_DQ_DONE = 9, BAR_DQ_FREE = 10, BAR_COUNT = 11 };
 
 struct BwdArgs {
   BwdParams p;
@@ -131,6 +130,7 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       mbar_init(bar(BAR_PD_READY + x), 8);  // one arrive per compute warp
     }
     mbar_init(bar(BAR_DQ_DONE), 1);
+    mbar_init(bar(BAR_DQ_FREE), 4);       // one arrive per flush warp
     *s_abort = 0;
     fence_barrier_init();
     fence_proxy_async();
@@ -154,22 +154,27 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     for (int it = 0; it < n_iter; ++it) {
       const int st = it & 1;
       const int hq = kvh * p.gqa + it / nm, m = m_begin + it % nm;
-      if (!__all_sync(0xffffffffu, mbar_wait_bounded(bar(BAR_Q_EMPTY + st), ((it >> 1) & 1) ^ 1, s_abort))) break;
       // -L and -delta of the 128 query rows ride with the Q tile; rows beyond N (or without any visible key)
-      // get L = +inf so that their P is exactly zero
+      // get L = +inf so that their P is exactly zero.  They are fetched before waiting for the stage so that
+      // their latency does not add to the TMA's.
+      float Lr[4], dr[4];
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
-        const int ql = lane * 4 + i;
-        const int row = m * BQ + ql;
-        float L = INFINITY, dl = 0.f;
+        const int row = m * BQ + lane * 4 + i;
+        Lr[i] = INFINITY;
+        dr[i] = 0.f;
         if (row < N) {
           const int64_t idx = bb * p.lse_bs + hq * p.lse_hs + q_begin + row;
-          L = p.lse[idx];
-          dl = p.delta[idx];
-          if (L == -INFINITY) L = INFINITY;
+          Lr[i] = p.lse[idx];
+          dr[i] = p.delta[idx];
+          if (Lr[i] == -INFINITY) Lr[i] = INFINITY;
         }
-        sL[st * BQ + ql] = -L;            // stored negated: the compute loop adds them
-        sDel[st * BQ + ql] = -dl;
+      }
+      if (!__all_sync(0xffffffffu, mbar_wait_bounded(bar(BAR_Q_EMPTY + st), ((it >> 1) & 1) ^ 1, s_abort))) break;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        sL[st * BQ + lane * 4 + i] = -Lr[i];            // stored negated: the compute loop adds them
+        sDel[st * BQ + lane * 4 + i] = -dr[i];
       }
       __syncwarp();
       if (lane == 0) {
@@ -233,7 +238,9 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
                              (it > 0 || x > 0 || k > 0) ? 1u : 0u);
         if (x == 1) {
           if (leader) tc_commit(bar(BAR_Q_EMPTY + st));
-          // dQ = dS.K: A = dS [query][key] in two 64-key halves (buffer it & 1), B = K rows = keys
+          // dQ = dS.K: A = dS [query][key] in two 64-key halves (buffer it & 1), B = K rows = keys; the flush warps
+          // must have read the previous tile's dQ out of TMEM first
+          if (it > 0 && !__all_sync(0xffffffffu, mbar_wait_bounded(bar(BAR_DQ_FREE), (it - 1) & 1, s_abort))) { ok = false; break; }
           const uint64_t dsd = dsd0 + (it & 1) * kDSU;
 #pragma unroll
           for (int k = 0; k < BK / 16; ++k)
@@ -248,6 +255,38 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         }
       }
     }
+  } else if (warp >= 10) {
+    // ============================ dQ flush warps 10-13 ============================
+    // dQ of each tile leaves TMEM here (rows = queries) and goes to the fp32 accumulator as fire-and-forget vector
+    // reductions, off the compute warps' critical path.  The stream of reductions is bound by L2 atomic throughput.
+    const int wq = warp & 3;                                  // TMEM lane quarter this warp may touch
+    const uint32_t lane_base = static_cast<uint32_t>(wq * 32) << 16;
+    for (int it = 0; it < n_iter; ++it) {
+      if (!__all_sync(0xffffffffu, mbar_wait_bounded(bar(BAR_DQ_DONE), it & 1, s_abort))) break;
+      tc_fence_after();
+      const int hq = kvh * p.gqa + it / nm, m = m_begin + it % nm;
+      const int row = m * BQ + wq * 32 + lane;
+      float* acc = p.dq_acc + ((static_cast<int64_t>(bb) * p.Hq + hq) * p.N + q_begin + row) * HD;
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        uint32_t r[32];
+        tmem_ld32(tmem + lane_base + cDQ + c * 32, r);
+        tc_wait_ld();
+        if (c == 1) {
+          // everything is in registers: the MMA warp may overwrite dQ
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(bar(BAR_DQ_FREE));
+        }
+        if (row < N) {
+#pragma unroll
+          for (int i = 0; i < 32; i += 4)
+            asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};\n" ::"l"(acc + c * 32 + i), "f"(__uint_as_float(r[i])),
+                         "f"(__uint_as_float(r[i + 1])), "f"(__uint_as_float(r[i + 2])), "f"(__uint_as_float(r[i + 3]))
+                         : "memory");
+        }
+      }
+    }
   } else {
     // ============================ compute warps 0-7 ============================
     const int wq = warp & 3, hf = warp >> 2;                 // TMEM lane quarter, column half
@@ -255,22 +294,6 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     const int key = n0 + rloc;
     const uint32_t lane_base = static_cast<uint32_t>(wq * 32) << 16;
     bool ok = true;
-
-    auto flush_dq = [&](int it_done) {
-      // dQ tile of iteration it_done: rows = queries, this warp's 32 of the 64 columns -> fp32 accumulator
-      const int hq = kvh * p.gqa + it_done / nm, m = m_begin + it_done % nm;
-      uint32_t r[32];
-      tmem_ld32(tmem + lane_base + cDQ + hf * 32, r);
-      tc_wait_ld();
-      const int row = m * BQ + rloc;
-      if (row < N) {
-        float* acc = p.dq_acc + ((static_cast<int64_t>(bb) * p.Hq + hq) * p.N + q_begin + row) * HD + hf * 32;
-#pragma unroll
-        for (int i = 0; i < 32; i += 4)
-          atomicAdd(reinterpret_cast<float4*>(acc + i), make_float4(__uint_as_float(r[i]), __uint_as_float(r[i + 1]),
-                                                                    __uint_as_float(r[i + 2]), __uint_as_float(r[i + 3])));
-      }
-    };
 
     for (int it = 0; it < n_iter && ok; ++it) {
       const int st = it & 1;
@@ -333,12 +356,6 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
 
 #pragma unroll
       for (int x = 0; x < 2; ++x) {
-        if (x == 1 && it > 0) {
-          // dQ of the previous tile: read it out while the MMAs of this tile's first half run
-          if (!__all_sync(0xffffffffu, mbar_wait_bounded(bar(BAR_DQ_DONE), (it - 1) & 1, s_abort))) { ok = false; break; }
-          tc_fence_after();
-          flush_dq(it - 1);
-        }
         if (!__all_sync(0xffffffffu, mbar_wait_bounded(bar(BAR_ST_DONE + x), it & 1, s_abort))) { ok = false; break; }
         tc_fence_after();
         if (need_mask) run_half(x, std::true_type{}); else run_half(x, std::false_type{});
@@ -353,7 +370,6 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     if (ok) ok = __all_sync(0xffffffffu, mbar_wait_bounded(bar(BAR_DQ_DONE), (n_iter - 1) & 1, s_abort));
     if (ok) {
       tc_fence_after();
-      flush_dq(n_iter - 1);
       // dK, dV: rows = keys, this warp's 32 of the 64 columns
       if (true) {
         uint32_t rk[32], rv[32];

@@ -201,6 +201,14 @@ int32_t b200fa_decode_paged_static(const b200fa_desc* d, const void* q,
                                    void* out, float* lse, void* stream);
 
 /*
+ * Reads and clears the library-wide device status word of the tcgen05 kernels
+ * (forward, backward): 0 = ok, bit 0 = a bounded mbarrier wait inside a kernel
+ * gave up after about a second (its outputs are then undefined).  Waits for
+ * `stream`.  No counterpart in the reference, whose kernels report nothing back.
+ */
+int32_t b200fa_kernel_status(void* stream, int32_t* status_out);
+
+/*
  * Reads the error word the decode kernel keeps at the start of its workspace
  * (0 = ok, bit 0 = a bounded wait inside the kernel gave up, bit 1 = a
  * block_table entry pointed beyond num_pages and was treated as a hole).

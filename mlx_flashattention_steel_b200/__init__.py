@@ -12,6 +12,7 @@ from .attention import (
     get_device_info,
     get_supported_configs,
     is_mfa_available,
+    kernel_status,
     paged_kv_gather,
 )
 
@@ -27,6 +28,7 @@ __all__ = [
     "paged_kv_gather",
     "flash_attention_from_host",
     "HostPipeline",
+    "kernel_status",
     "is_mfa_available",
     "get_device_info",
     "get_supported_configs",

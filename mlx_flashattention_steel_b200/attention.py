@@ -44,6 +44,7 @@ __all__ = [
     "flash_attention_kvcache",
     "flash_attention_paged",
     "paged_kv_gather",
+    "kernel_status",
     "is_mfa_available",
     "get_device_info",
     "get_supported_configs",
@@ -676,6 +677,16 @@ def flash_attention_kvcache(
 # ---------------------------------------------------------------------------
 # capability queries (minimal; mlx_mfa/attention.py:558-709)
 # ---------------------------------------------------------------------------
+def kernel_status(stream=None) -> int:
+    """Waits for `stream` and returns (then clears) the device status word of the tcgen05 kernels:
+    0 = ok, bit 0 = a bounded wait inside a kernel timed out and that launch's outputs are undefined."""
+    lib = _lib.load()
+    word = C.c_int32(0)
+    dev = torch.device("cuda", torch.cuda.current_device())
+    _lib.check(lib.b200fa_kernel_status(C.c_void_p(_stream_ptr(stream, dev)), C.byref(word)), "kernel_status")
+    return int(word.value)
+
+
 def is_mfa_available() -> bool:
     """True when libb200fa.so is built and a CUDA device of compute capability 10.x is visible."""
     if not _lib.is_built() or not torch.cuda.is_available():

@@ -309,6 +309,17 @@ int32_t b200fa_paged_kv_gather(const void* pool, const int32_t* block_table, con
   return B200FA_OK;
 }
 
+int32_t b200fa_kernel_status(void* stream, int32_t* status_out) {
+  if (status_out == nullptr) return fail(B200FA_ERR_INVALID_ARG, "status_out is null");
+  cudaStream_t cs = reinterpret_cast<cudaStream_t>(stream);
+  int a = 0, b = 0;
+  cudaError_t e = b200fa::fwd_sm100_read_clear_status(cs, &a);
+  if (e == cudaSuccess) e = b200fa::bwd_sm100_read_clear_status(cs, &b);
+  if (e != cudaSuccess) return cuda_fail(e, "kernel status read");
+  *status_out = a | b;
+  return B200FA_OK;
+}
+
 int32_t b200fa_workspace_status(const void* workspace, void* stream, int32_t* status_out) {
   if (workspace == nullptr || status_out == nullptr) return fail(B200FA_ERR_INVALID_ARG, "null pointer");
   cudaStream_t cs = reinterpret_cast<cudaStream_t>(stream);

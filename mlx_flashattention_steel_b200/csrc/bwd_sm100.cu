@@ -25,6 +25,9 @@
 #include "tma.cuh"
 
 namespace b200fa {
+// Device status word of this file's kernels: bit 0 = a bounded wait gave up.
+static __device__ int g_kernel_status = 0;
+
 
 namespace {
 
@@ -407,6 +410,7 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     tc_fence_after();
     tmem_dealloc(tmem, kTmemCols);
   }
+  if (tid == 0 && *s_abort != 0) atomicOr(&g_kernel_status, 1);
 }
 
 bool make_map64(CUtensorMap* m, int dtype, const void* base, int rows, int H, int B, int64_t rs, int64_t hs, int64_t bs) {
@@ -444,6 +448,16 @@ cudaError_t launch_bwd_sm100_main(const BwdParams& p, int dtype, int nbatch, int
   dim3 grid((max_k + BK - 1) / BK, p.Hkv, nbatch);
   bwd_sm100_kernel<<<grid, kThreads, kSmemBytes, stream>>>(tmQ, tmK, tmV, tmDO, a);
   return cudaGetLastError();
+}
+
+cudaError_t bwd_sm100_read_clear_status(cudaStream_t stream, int* out) {
+  const int zero = 0;
+  cudaError_t e = cudaMemcpyFromSymbolAsync(out, g_kernel_status, sizeof(int), 0, cudaMemcpyDeviceToHost, stream);
+  if (e == cudaSuccess) e = cudaStreamSynchronize(stream);
+  if (e == cudaSuccess && *out != 0)
+    e = cudaMemcpyToSymbolAsync(g_kernel_status, &zero, sizeof(int), 0, cudaMemcpyHostToDevice, stream);
+  if (e == cudaSuccess) e = cudaStreamSynchronize(stream);
+  return e;
 }
 
 }  // namespace b200fa

@@ -20,8 +20,8 @@
 //   [0,64) S0 / P0   [64,128) S1 / P1   [128,128+D) O.
 // Tiles above the causal diagonal or left of the window are skipped whole.
 // No load here uses cluster multicast.  Every mbarrier wait is bounded; on a timeout the
-// CTA raises its abort flag, frees its TMEM and leaves (outputs are then undefined and
-// the launch wrapper's status word says so).
+// CTA raises its abort flag, frees its TMEM, sets bit 0 of this file's device status word
+// (read through b200fa_kernel_status) and leaves; that launch's outputs are then undefined.
 #include <cstdio>
 
 #include "common.cuh"
@@ -30,6 +30,9 @@
 #include "tma.cuh"
 
 namespace b200fa {
+// Device status word of this file's kernels: bit 0 = a bounded wait gave up.
+static __device__ int g_kernel_status = 0;
+
 
 namespace {
 
@@ -65,7 +68,6 @@ enum Bar {
 struct Sm100Args {
   FwdParams p;
   int dtype;                 // 0 f16, 1 bf16
-  int* status;               // device word: bit 0 = a wait timed out (may be null)
 };
 
 // max / min of 64 values as a 3-ary tree (depth 4) instead of a 63-deep dependent chain
@@ -444,7 +446,7 @@ fa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     tc_fence_after();
     tmem_dealloc(tmem, kTmemCols);
   }
-  if (tid == 0 && *s_abort != 0 && a.status != nullptr) atomicOr(a.status, 1);
+  if (tid == 0 && *s_abort != 0) atomicOr(&g_kernel_status, 1);
 }
 
 bool make_map(CUtensorMap* m, int dtype, const void* base, int D, int rows, int H, int B, int64_t rs, int64_t hs,
@@ -480,7 +482,6 @@ static cudaError_t launch_hd(const FwdParams& p, int dtype, int nbatch, int max_
   Sm100Args a;
   a.p = p;
   a.dtype = dtype;
-  a.status = nullptr;
   cudaError_t e = cudaFuncSetAttribute(fa_fwd_sm100_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        Cfg<HD>::kSmemBytes);
   if (e != cudaSuccess) return e;
@@ -494,6 +495,16 @@ static cudaError_t launch_hd(const FwdParams& p, int dtype, int nbatch, int max_
 cudaError_t launch_fwd_sm100(const FwdParams& p, int dtype, int D, int nbatch, int max_q, cudaStream_t stream) {
   if (nbatch <= 0 || max_q <= 0) return cudaSuccess;
   return D == 64 ? launch_hd<64>(p, dtype, nbatch, max_q, stream) : launch_hd<128>(p, dtype, nbatch, max_q, stream);
+}
+
+cudaError_t fwd_sm100_read_clear_status(cudaStream_t stream, int* out) {
+  const int zero = 0;
+  cudaError_t e = cudaMemcpyFromSymbolAsync(out, g_kernel_status, sizeof(int), 0, cudaMemcpyDeviceToHost, stream);
+  if (e == cudaSuccess) e = cudaStreamSynchronize(stream);
+  if (e == cudaSuccess && *out != 0)
+    e = cudaMemcpyToSymbolAsync(g_kernel_status, &zero, sizeof(int), 0, cudaMemcpyHostToDevice, stream);
+  if (e == cudaSuccess) e = cudaStreamSynchronize(stream);
+  return e;
 }
 
 }  // namespace b200fa

@@ -34,4 +34,8 @@ cudaError_t launch_bwd(const BwdParams& p, int dtype, int D, bool varlen, int nb
 bool bwd_sm100_supported(int dtype, int D);
 cudaError_t launch_bwd_sm100_main(const BwdParams& p, int dtype, int nbatch, int max_k, cudaStream_t stream);
 
+// Read (and clear when set) the device status word of the tcgen05 kernels of each file; they wait for `stream`.
+cudaError_t fwd_sm100_read_clear_status(cudaStream_t stream, int* out);
+cudaError_t bwd_sm100_read_clear_status(cudaStream_t stream, int* out);
+
 }  // namespace b200fa

@@ -203,3 +203,14 @@ def test_host_pipeline_matches_device_call(dev):
     assert torch.equal(out, ref.cpu()) and torch.equal(lse, lref.cpu())
     with pytest.raises(ValueError):
         fa.flash_attention_from_host(q.to(dev), k, v)
+
+
+def test_kernel_status_word_stays_clear(dev):
+    """The tcgen05 kernels set bit 0 of a device status word only when a bounded wait gives up;
+    after a forward and a backward on healthy inputs it reads 0 (and reading clears it)."""
+    q = randn((1, 4, 300, 64), torch.bfloat16, 990).to(dev).requires_grad_(True)
+    k = randn((1, 2, 300, 64), torch.bfloat16, 991).to(dev).requires_grad_(True)
+    v = randn((1, 2, 300, 64), torch.bfloat16, 992).to(dev).requires_grad_(True)
+    fa.flash_attention(q, k, v, causal=True).sum().backward()
+    assert fa.kernel_status() == 0
+    assert fa.kernel_status() == 0

@@ -67,7 +67,6 @@ enum Bar {
 
 struct Sm100Args {
   FwdParams p;
-  int dtype;                 // 0 f16, 1 bf16
 };
 
 // max / min of 64 values as a 3-ary tree (depth 4) instead of a 63-deep dependent chain
@@ -94,14 +93,42 @@ __device__ __forceinline__ float tree_min64(const float (&x)[64]) {
   return min3(min3(b[0], b[1], b[2]), min3(b[3], b[4], b[5]), fminf(b[6], b[7]));
 }
 
-__device__ __forceinline__ uint32_t pack16(int dtype, float a, float b) {
-  return dtype == 0 ? Elem<__half>::pack(a, b) : Elem<__nv_bfloat16>::pack(a, b);
+// Of every 4 key pairs a softmax thread handles, this many take exp2 on the FMA pipe (exp2_poly2) instead of
+// the special-function unit, whose 4 lanes per scheduler are otherwise the bound of the inner loop.
+#ifndef B200FA_EXP_POLY_PAIRS
+#define B200FA_EXP_POLY_PAIRS 0
+#endif
+constexpr int kExpPolyPairs = B200FA_EXP_POLY_PAIRS;
+
+// 2^t for two values without the special-function unit: n = round(t) by the 1.5*2^23 trick, 2^(t-n) by a cubic
+// on [-0.5, 0.5] (relative error < 7.5e-5, far below the 16-bit rounding of P), n added into the exponent field.
+__device__ __forceinline__ float2 exp2_poly2(float2 t) {
+  const float2 magic = make_float2(12582912.f, 12582912.f), neg_magic = make_float2(-12582912.f, -12582912.f);
+  const float2 tc = make_float2(fmaxf(t.x, -125.f), fmaxf(t.y, -125.f));
+  const float2 tt = __fadd2_rn(tc, magic);
+  const float2 nf = __fadd2_rn(tt, neg_magic);
+  const float2 r = __ffma2_rn(nf, make_float2(-1.f, -1.f), tc);
+  float2 q = __ffma2_rn(r, make_float2(0.0551716685f, 0.0551716685f), make_float2(0.2426111251f, 0.2426111251f));
+  q = __ffma2_rn(r, q, make_float2(0.6932609677f, 0.6932609677f));
+  q = __ffma2_rn(r, q, make_float2(0.9999280572f, 0.9999280572f));
+  return make_float2(__int_as_float(__float_as_int(q.x) + (__float_as_int(tt.x) << 23)),
+                     __int_as_float(__float_as_int(q.y) + (__float_as_int(tt.y) << 23)));
+}
+// exp2 of a pair; `pair` is the compile-time index of the pair inside the row
+__device__ __forceinline__ float2 exp2_pair(float2 t, int pair) {
+  if ((pair & 3) < kExpPolyPairs) return exp2_poly2(t);
+  return make_float2(fast_exp2(t.x), fast_exp2(t.y));
+}
+
+// DT: 0 = float16, 1 = bfloat16 (a template parameter so that the inner loops convert once, not once per type)
+template <int DT> __device__ __forceinline__ uint32_t pack16(float a, float b) {
+  return DT == 0 ? Elem<__half>::pack(a, b) : Elem<__nv_bfloat16>::pack(a, b);
 }
 
 // ---------------------------------------------------------------------------
 // kernel
 // ---------------------------------------------------------------------------
-template <int HD>
+template <int HD, int DT>
 __global__ void __launch_bounds__(kThreads, 2)
 fa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                     const __grid_constant__ CUtensorMap tmV, const Sm100Args a) {
@@ -210,8 +237,8 @@ fa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   } else if (warp == 5) {
     // ============================ MMA issue ============================
     if (lane == 0) {
-      const uint32_t idesc_qk = instr_desc(a.dtype, 0, BM, BN);
-      const uint32_t idesc_pv = instr_desc(a.dtype, 1, BM, HD);
+      const uint32_t idesc_qk = instr_desc(DT, 0, BM, BN);
+      const uint32_t idesc_pv = instr_desc(DT, 1, BM, HD);
       // Descriptors differ only in their start-address field (low word); build the bases once so that
       // the issue loop is a handful of integer adds per MMA.
       const uint64_t qd = smem_desc(smem_u32(sQ), 16, 1024);
@@ -268,9 +295,13 @@ fa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     float m_used = -INFINITY, l_run = 0.f;
     bool ok = true;
 
-    const float kk = cap_in * cap_out;                // softcap on: scale * log2(e)
+    // softcap on: t = x * (kk + kb3 z + kb5 z^2 + kb7 z^3), z = x^2, is cap*log2(e)*tanh(x*scale/cap) to degree 7
+    const float kk = cap_in * cap_out;                // scale * log2(e)
     const float c2 = cap_in * cap_in;
-    const float b3 = (-1.f / 3.f) * c2, b5 = (2.f / 15.f) * c2 * c2, b7 = (-17.f / 315.f) * c2 * c2 * c2;
+    const float kb3 = kk * (-1.f / 3.f) * c2, kb5 = kk * (2.f / 15.f) * c2 * c2, kb7 = kk * (-17.f / 315.f) * c2 * c2 * c2;
+    // largest |y| for which the degree-3 / degree-5 polynomial is within 1e-3 / cap of tanh(y)
+    const float y_deg3 = use_cap ? fminf(0.5f, powf(1e-3f * 7.5f / p.softcap, 0.2f)) : 0.f;
+    const float y_deg5 = use_cap ? fminf(0.5f, powf(1e-3f * (315.f / 17.f) / p.softcap, 1.f / 7.f)) : 0.f;
     const bool monotone = p.scale > 0.f;              // lets the row max be taken on the raw dot products
 
     for (int j = 0; j < n_tiles; ++j) {
@@ -291,6 +322,7 @@ fa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       const bool fast = !need_mask && monotone;
       // mode 0: t = x*scale_log2 - m ; 1: softcap by polynomial ; 2: softcap by tanh.approx ; 3: general (masked tile)
       int mode = 3;
+      unsigned deg = 2;                                // mode 1 only: 0, 1, 2 = polynomial of degree 3, 5, 7
       float m_tile;
       if (fast) {
         // scale and softcap are increasing in x, so the tile max is f(max x): one pass of 3-input max
@@ -299,14 +331,18 @@ fa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
           mode = 0;
           m_tile = xmax * p.scale_log2;
         } else {
-          // cap*tanh(x*scale/cap): while |x*scale/cap| <= 0.5 for the warp's rows the odd Taylor polynomial to
-          // y^7 (|error| < 4.3e-5) runs on the FMA pipe and leaves the special-function unit to exp2
+          // cap*tanh(y), y = x*scale/cap: the odd Taylor polynomial of tanh runs on the FMA pipe and leaves the
+          // special-function unit to exp2.  Its degree (3, 5 or 7) is the lowest whose truncation error, times
+          // cap, stays below 1e-3 for the largest |y| among the warp's rows; above |y| = 0.5 tanh.approx takes over.
           const float xmin = tree_min64(x);
-          const bool small = fmaxf(xmax, -xmin) * cap_in <= 0.5f;
-          if (__all_sync(0xffffffffu, small)) {
+          const float ay = fmaxf(xmax, -xmin) * cap_in;
+          const unsigned lvl = __reduce_max_sync(0xffffffffu, ay <= y_deg3 ? 0u : (ay <= y_deg5 ? 1u : (ay <= 0.5f ? 2u : 3u)));
+          if (lvl < 3u) {
             mode = 1;
+            deg = lvl;
             const float z = xmax * xmax;
-            m_tile = (xmax * kk) * fmaf(z, fmaf(z, fmaf(z, b7, b5), b3), 1.f);
+            const float q = lvl == 0u ? fmaf(z, kb3, kk) : (lvl == 1u ? fmaf(z, fmaf(z, kb5, kb3), kk) : fmaf(z, fmaf(z, fmaf(z, kb7, kb5), kb3), kk));
+            m_tile = xmax * q;
           } else {
             mode = 2;
             m_tile = cap_out * fast_tanh(xmax * cap_in);
@@ -365,24 +401,45 @@ fa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
 #pragma unroll
         for (int i = 0; i < BN; i += 2) {
           const float2 t = __ffma2_rn(make_float2(x[i], x[i + 1]), k2, nm2);
-          const float2 e = make_float2(fast_exp2(t.x), fast_exp2(t.y));
+          const float2 e = exp2_pair(t, i >> 1);
           lsum2 = __fadd2_rn(lsum2, e);
-          pk[i >> 1] = pack16(a.dtype, e.x, e.y);
+          pk[i >> 1] = pack16<DT>(e.x, e.y);
         }
       } else if (mode == 1) {
-        const float2 kk2 = make_float2(kk, kk), b32 = make_float2(b3, b3), b52 = make_float2(b5, b5),
-                     b72 = make_float2(b7, b7), one2 = make_float2(1.f, 1.f);
+        const float2 kk2 = make_float2(kk, kk), b32 = make_float2(kb3, kb3), b52 = make_float2(kb5, kb5),
+                     b72 = make_float2(kb7, kb7);
+        if (deg == 0u) {
 #pragma unroll
-        for (int i = 0; i < BN; i += 2) {
-          const float2 xv = make_float2(x[i], x[i + 1]);
-          const float2 z = __fmul2_rn(xv, xv);
-          float2 poly = __ffma2_rn(z, b72, b52);
-          poly = __ffma2_rn(z, poly, b32);
-          poly = __ffma2_rn(z, poly, one2);
-          const float2 t = __ffma2_rn(__fmul2_rn(xv, kk2), poly, nm2);
-          const float2 e = make_float2(fast_exp2(t.x), fast_exp2(t.y));
-          lsum2 = __fadd2_rn(lsum2, e);
-          pk[i >> 1] = pack16(a.dtype, e.x, e.y);
+          for (int i = 0; i < BN; i += 2) {
+            const float2 xv = make_float2(x[i], x[i + 1]);
+            const float2 q = __ffma2_rn(__fmul2_rn(xv, xv), b32, kk2);
+            const float2 t = __ffma2_rn(xv, q, nm2);
+            const float2 e = exp2_pair(t, i >> 1);
+            lsum2 = __fadd2_rn(lsum2, e);
+            pk[i >> 1] = pack16<DT>(e.x, e.y);
+          }
+        } else if (deg == 1u) {
+#pragma unroll
+          for (int i = 0; i < BN; i += 2) {
+            const float2 xv = make_float2(x[i], x[i + 1]);
+            const float2 z = __fmul2_rn(xv, xv);
+            const float2 q = __ffma2_rn(z, __ffma2_rn(z, b52, b32), kk2);
+            const float2 t = __ffma2_rn(xv, q, nm2);
+            const float2 e = exp2_pair(t, i >> 1);
+            lsum2 = __fadd2_rn(lsum2, e);
+            pk[i >> 1] = pack16<DT>(e.x, e.y);
+          }
+        } else {
+#pragma unroll
+          for (int i = 0; i < BN; i += 2) {
+            const float2 xv = make_float2(x[i], x[i + 1]);
+            const float2 z = __fmul2_rn(xv, xv);
+            const float2 q = __ffma2_rn(z, __ffma2_rn(z, __ffma2_rn(z, b72, b52), b32), kk2);
+            const float2 t = __ffma2_rn(xv, q, nm2);
+            const float2 e = exp2_pair(t, i >> 1);
+            lsum2 = __fadd2_rn(lsum2, e);
+            pk[i >> 1] = pack16<DT>(e.x, e.y);
+          }
         }
       } else if (mode == 2) {
 #pragma unroll
@@ -390,14 +447,14 @@ fa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
           const float2 e = make_float2(fast_exp2(fmaf(cap_out, fast_tanh(x[i] * cap_in), -msub)),
                                        fast_exp2(fmaf(cap_out, fast_tanh(x[i + 1] * cap_in), -msub)));
           lsum2 = __fadd2_rn(lsum2, e);
-          pk[i >> 1] = pack16(a.dtype, e.x, e.y);
+          pk[i >> 1] = pack16<DT>(e.x, e.y);
         }
       } else {
 #pragma unroll
         for (int i = 0; i < BN; i += 2) {
           const float2 e = make_float2(fast_exp2(x[i] - msub), fast_exp2(x[i + 1] - msub));
           lsum2 = __fadd2_rn(lsum2, e);
-          pk[i >> 1] = pack16(a.dtype, e.x, e.y);
+          pk[i >> 1] = pack16<DT>(e.x, e.y);
         }
       }
       l_run += lsum2.x + lsum2.y;
@@ -425,10 +482,10 @@ fa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
 #pragma unroll
           for (int i = 0; i < 32; i += 8) {
             uint4 v;
-            v.x = pack16(a.dtype, __uint_as_float(o[i]) * inv, __uint_as_float(o[i + 1]) * inv);
-            v.y = pack16(a.dtype, __uint_as_float(o[i + 2]) * inv, __uint_as_float(o[i + 3]) * inv);
-            v.z = pack16(a.dtype, __uint_as_float(o[i + 4]) * inv, __uint_as_float(o[i + 5]) * inv);
-            v.w = pack16(a.dtype, __uint_as_float(o[i + 6]) * inv, __uint_as_float(o[i + 7]) * inv);
+            v.x = pack16<DT>(__uint_as_float(o[i]) * inv, __uint_as_float(o[i + 1]) * inv);
+            v.y = pack16<DT>(__uint_as_float(o[i + 2]) * inv, __uint_as_float(o[i + 3]) * inv);
+            v.z = pack16<DT>(__uint_as_float(o[i + 4]) * inv, __uint_as_float(o[i + 5]) * inv);
+            v.w = pack16<DT>(__uint_as_float(o[i + 6]) * inv, __uint_as_float(o[i + 7]) * inv);
             *reinterpret_cast<uint4*>(orow + c * 32 + i) = v;
           }
         }
@@ -467,8 +524,9 @@ bool fwd_sm100_supported(const FwdParams& p, int dtype, int D) {
   return get_encode_tiled() != nullptr;
 }
 
-template <int HD>
-static cudaError_t launch_hd(const FwdParams& p, int dtype, int nbatch, int max_q, cudaStream_t stream) {
+template <int HD, int DT>
+static cudaError_t launch_hd(const FwdParams& p, int nbatch, int max_q, cudaStream_t stream) {
+  constexpr int dtype = DT;
   CUtensorMap tmQ, tmK, tmV;
   // TMA: a size-1 dimension still needs a legal stride
   auto fix = [](int64_t s, int64_t fallback) { return s > 0 ? s : fallback; };
@@ -481,12 +539,11 @@ static cudaError_t launch_hd(const FwdParams& p, int dtype, int nbatch, int max_
     return cudaErrorInvalidValue;
   Sm100Args a;
   a.p = p;
-  a.dtype = dtype;
-  cudaError_t e = cudaFuncSetAttribute(fa_fwd_sm100_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+  cudaError_t e = cudaFuncSetAttribute(fa_fwd_sm100_kernel<HD, DT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        Cfg<HD>::kSmemBytes);
   if (e != cudaSuccess) return e;
   dim3 grid((max_q + BM - 1) / BM, p.Hq, nbatch);
-  fa_fwd_sm100_kernel<HD><<<grid, kThreads, Cfg<HD>::kSmemBytes, stream>>>(tmQ, tmK, tmV, a);
+  fa_fwd_sm100_kernel<HD, DT><<<grid, kThreads, Cfg<HD>::kSmemBytes, stream>>>(tmQ, tmK, tmV, a);
   return cudaGetLastError();
 }
 
@@ -494,7 +551,9 @@ static cudaError_t launch_hd(const FwdParams& p, int dtype, int nbatch, int max_
 // sequences, max_q = longest query sequence.
 cudaError_t launch_fwd_sm100(const FwdParams& p, int dtype, int D, int nbatch, int max_q, cudaStream_t stream) {
   if (nbatch <= 0 || max_q <= 0) return cudaSuccess;
-  return D == 64 ? launch_hd<64>(p, dtype, nbatch, max_q, stream) : launch_hd<128>(p, dtype, nbatch, max_q, stream);
+  if (D == 64)
+    return dtype == 0 ? launch_hd<64, 0>(p, nbatch, max_q, stream) : launch_hd<64, 1>(p, nbatch, max_q, stream);
+  return dtype == 0 ? launch_hd<128, 0>(p, nbatch, max_q, stream) : launch_hd<128, 1>(p, nbatch, max_q, stream);
 }
 
 cudaError_t fwd_sm100_read_clear_status(cudaStream_t stream, int* out) {

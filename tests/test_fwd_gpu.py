@@ -68,6 +68,16 @@ def test_softcap(dev, dt, cap):
     _run(dev, DT[dt], 1, 4, 2, 200, 200, 128, 40, causal=True, softcap=cap)
 
 
+@pytest.mark.parametrize("mult", [1.0, 3.0, 6.0, 12.0, 40.0])
+@pytest.mark.parametrize("dt", ["f16", "bf16"])
+def test_softcap_score_ranges(dev, dt, mult):
+    """The tcgen05 kernel evaluates tanh by a polynomial whose degree follows the largest |score/cap| of the
+    tile (degree 3, 5, 7, then tanh.approx).  Scaling the scores up walks through every branch, up to
+    saturated scores (|score/cap| >> 1)."""
+    _run(dev, DT[dt], 1, 4, 2, 384, 512, 128, 45, causal=True, softcap=50.0, scale=mult / math.sqrt(128))
+    _run(dev, DT[dt], 1, 2, 2, 256, 256, 64, 46, causal=False, softcap=20.0, scale=mult / math.sqrt(64))
+
+
 def test_softcap_zero_is_bit_identical(dev):
     # tests/test_attention.py:2869-2886
     q, k, v = (randn((1, 2, 100, 64), torch.float16, 50 + i).to(dev) for i in range(3))

@@ -81,6 +81,18 @@ __device__ __forceinline__ float tree_max64(const float (&x)[64]) {
   b[7] = a[21];
   return max3(max3(b[0], b[1], b[2]), max3(b[3], b[4], b[5]), fmaxf(b[6], b[7]));
 }
+// max of |x| over 64 values (the absolute values fold into the max instruction's source modifiers)
+__device__ __forceinline__ float tree_absmax64(const float (&x)[64]) {
+  float a[22];
+#pragma unroll
+  for (int i = 0; i < 21; ++i) a[i] = max3(fabsf(x[3 * i]), fabsf(x[3 * i + 1]), fabsf(x[3 * i + 2]));
+  a[21] = fabsf(x[63]);
+  float b[8];
+#pragma unroll
+  for (int i = 0; i < 7; ++i) b[i] = max3(a[3 * i], a[3 * i + 1], a[3 * i + 2]);
+  b[7] = a[21];
+  return max3(max3(b[0], b[1], b[2]), max3(b[3], b[4], b[5]), fmaxf(b[6], b[7]));
+}
 __device__ __forceinline__ float tree_min64(const float (&x)[64]) {
   float a[22];
 #pragma unroll
@@ -326,16 +338,25 @@ fa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       float m_tile;
       if (fast) {
         // scale and softcap are increasing in x, so the tile max is f(max x): one pass of 3-input max
-        float xmax = tree_max64(x);
         if (!use_cap) {
           mode = 0;
-          m_tile = xmax * p.scale_log2;
+          m_tile = tree_max64(x) * p.scale_log2;
         } else {
           // cap*tanh(y), y = x*scale/cap: the odd Taylor polynomial of tanh runs on the FMA pipe and leaves the
           // special-function unit to exp2.  Its degree (3, 5 or 7) is the lowest whose truncation error, times
           // cap, stays below 1e-3 for the largest |y| among the warp's rows; above |y| = 0.5 tanh.approx takes over.
-          const float xmin = tree_min64(x);
-          const float ay = fmaxf(xmax, -xmin) * cap_in;
+          // bf16: one tree over |x| serves both the range check and the reference max -- f(max|x|) is an upper
+          // bound of the row max at most 2*cap*0.5 above it, so P stays within bf16's exponent range (an fp16 P
+          // could underflow, hence the exact max and a second tree there).
+          float xmax, ax;
+          if (DT == 1) {
+            ax = tree_absmax64(x);
+            xmax = ax;
+          } else {
+            xmax = tree_max64(x);
+            ax = fmaxf(xmax, -tree_min64(x));
+          }
+          const float ay = ax * cap_in;
           const unsigned lvl = __reduce_max_sync(0xffffffffu, ay <= y_deg3 ? 0u : (ay <= y_deg5 ? 1u : (ay <= 0.5f ? 2u : 3u)));
           if (lvl < 3u) {
             mode = 1;
@@ -345,6 +366,7 @@ fa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
             m_tile = xmax * q;
           } else {
             mode = 2;
+            if (DT == 1) xmax = tree_max64(x);          // scores may saturate here: take the exact max
             m_tile = cap_out * fast_tanh(xmax * cap_in);
           }
         }

@@ -78,6 +78,27 @@ def test_softcap_score_ranges(dev, dt, mult):
     _run(dev, DT[dt], 1, 2, 2, 256, 256, 64, 46, causal=False, softcap=20.0, scale=mult / math.sqrt(64))
 
 
+@pytest.mark.parametrize("level", [6.0, 20.0])
+@pytest.mark.parametrize("dt", ["f16", "bf16"])
+def test_softcap_all_scores_negative(dev, dt, level):
+    """Every score of every row sits near -level: the bf16 path takes its reference max from max|score|, an upper
+    bound far above the true row max here, and must still produce the same probabilities and lse."""
+    dtype = DT[dt]
+    g = torch.Generator().manual_seed(47)
+    D, N = 128, 256
+    u = torch.randn(D, generator=g)
+    u = u / u.norm()
+    amp = math.sqrt(level * math.sqrt(D))
+    q = (amp * u + 0.05 * torch.randn((1, 2, N, D), generator=g)).to(dtype)
+    k = (-amp * u + 0.05 * torch.randn((1, 2, N, D), generator=g)).to(dtype)
+    v = torch.randn((1, 2, N, D), generator=g).to(dtype)
+    out, lse = fa.flash_attention(q.to(dev), k.to(dev), v.to(dev), causal=False, softcap=50.0, return_lse=True)
+    O, L, _ = orc.sdpa(q, k, v, causal=False, softcap=50.0)
+    assert float(L.max()) < 1.4427 * (math.log(N) - 0.8 * level)      # every score is below -0.8 * level
+    assert_close(out, O, dtype)
+    assert_close(lse, L, dtype, "lse", LSE_TOL[dtype])
+
+
 def test_softcap_zero_is_bit_identical(dev):
     # tests/test_attention.py:2869-2886
     q, k, v = (randn((1, 2, 100, 64), torch.float16, 50 + i).to(dev) for i in range(3))

@@ -201,6 +201,21 @@ int32_t b200fa_decode_paged_static(const b200fa_desc* d, const void* q,
                                    void* out, float* lse, void* stream);
 
 /*
+ * KV-cache write path.  Scatters T new tokens (k_new / v_new, element (t, h, d) at t*token_stride +
+ * h*head_stride + d, f16 or bf16) into page pools laid out [num_pages, block_size, Hkv, D]; token t goes to
+ * slot_mapping[t] = page * block_size + offset (device int64; negative or out-of-pool entries are skipped).
+ * pool_dtype F16 / BF16 stores the values (converted if the types differ); I8 / E4M3 quantises each (token, head)
+ * row with scale = f16(max|x| / qmax) (qmax 127 / 448, 1 when zero), q = rne(x / scale), and writes the scale
+ * to k_scale / v_scale [num_pages, block_size, Hkv] (f16) -- the pool format b200fa_decode_paged reads.
+ * One launch serves any number of sequences.  Replaces the per-block concatenations of PagedKVCache.append
+ * (mlx_mfa/attention.py:2642-2711); the reference has no 8-bit pool, so the quantising mode has no counterpart.
+ */
+int32_t b200fa_kv_append(int32_t src_dtype, int32_t pool_dtype, int32_t T, int32_t Hkv, int32_t D, int32_t block_size,
+                         int64_t num_pages, const void* k_new, const void* v_new, int64_t token_stride,
+                         int64_t head_stride, const int64_t* slot_mapping, void* k_pool, void* v_pool, void* k_scale,
+                         void* v_scale, void* stream);
+
+/*
  * Reads and clears the library-wide device status word of the tcgen05 kernels
  * (forward, backward): 0 = ok, bit 0 = a bounded mbarrier wait inside a kernel
  * gave up after about a second (its outputs are then undefined).  Waits for

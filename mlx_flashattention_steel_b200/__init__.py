@@ -17,6 +17,7 @@ from .attention import (
 )
 
 from .host_pipeline import HostPipeline, flash_attention_from_host
+from .kv_cache import PagedKVCache, kv_append
 
 __version__ = "0.1.0"
 
@@ -26,6 +27,8 @@ __all__ = [
     "flash_attention_kvcache",
     "flash_attention_paged",
     "paged_kv_gather",
+    "PagedKVCache",
+    "kv_append",
     "flash_attention_from_host",
     "HostPipeline",
     "kernel_status",

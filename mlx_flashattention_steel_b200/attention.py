@@ -612,8 +612,10 @@ def flash_attention_kvcache(
     (``block_table`` given) requires ``seq_lens`` and rejects ``window_size`` and
     ``alibi_slopes`` with ValueError, as the reference does
     (mlx_mfa/attention.py:1124-1167).  Dense mode takes caches ``[B, Hkv, S, D]``
-    (or a pool indexed by ``cache_batch_idx``).  Append (``k_new``/``v_new``) and
-    rotary arguments raise NotImplementedError.
+    (or a pool indexed by ``cache_batch_idx``).  Append mode (``k_new``/``v_new``, dense only)
+    returns ``(out, k_updated, v_updated)`` as the reference does (mlx_mfa/attention.py:1059-1119);
+    paged pools are written through ``PagedKVCache.append``.  Rotary arguments raise
+    NotImplementedError.
     """
     q = _as_tensor(q, "q")
     if q.ndim != 4:
@@ -637,7 +639,20 @@ def flash_attention_kvcache(
                 "flash_attention_kvcache: k_new/v_new append is not supported together with "
                 "cache_batch_idx (continuous-batching pool mode)."
             )
-        raise NotImplementedError("flash_attention_kvcache: append mode (k_new/v_new) is not built.")
+        if has_rope:
+            raise NotImplementedError("flash_attention_kvcache: rotary embedding is not built.")
+        # Append to the dense cache (or start one from k_new / v_new alone), then attend on the updated cache
+        # and hand it back: (out, k_updated, v_updated), mlx_mfa/attention.py:1102-1119.
+        k_new, v_new = _as_tensor(k_new, "k_new"), _as_tensor(v_new, "v_new")
+        if k_cache is not None:
+            k_cache, v_cache = _as_tensor(k_cache, "k_cache"), _as_tensor(v_cache, "v_cache")
+            k_updated = torch.cat([k_cache, k_new.to(k_cache.dtype)], dim=2)
+            v_updated = torch.cat([v_cache, v_new.to(v_cache.dtype)], dim=2)
+        else:
+            k_updated, v_updated = k_new, v_new
+        out = flash_attention(q, k_updated, v_updated, scale=scale, causal=causal, softcap=softcap,
+                              alibi_slopes=alibi_slopes, window_size=window_size, stream=stream)
+        return out, k_updated, v_updated
     if block_table is not None:
         if seq_lens is None:
             raise ValueError("flash_attention_kvcache: paged mode requires seq_lens.")

@@ -309,6 +309,32 @@ int32_t b200fa_paged_kv_gather(const void* pool, const int32_t* block_table, con
   return B200FA_OK;
 }
 
+int32_t b200fa_kv_append(int32_t src_dtype, int32_t pool_dtype, int32_t T, int32_t Hkv, int32_t D, int32_t block_size,
+                         int64_t num_pages, const void* k_new, const void* v_new, int64_t token_stride,
+                         int64_t head_stride, const int64_t* slot_mapping, void* k_pool, void* v_pool, void* k_scale,
+                         void* v_scale, void* stream) {
+  if (src_dtype != B200FA_F16 && src_dtype != B200FA_BF16)
+    return fail(B200FA_ERR_UNSUPPORTED, "kv_append: new tokens must be f16 or bf16");
+  if (pool_dtype != B200FA_F16 && pool_dtype != B200FA_BF16 && pool_dtype != B200FA_I8 && pool_dtype != B200FA_E4M3)
+    return fail(B200FA_ERR_UNSUPPORTED, "kv_append: pool dtype %d not built", pool_dtype);
+  if (D != 64 && D != 128) return fail(B200FA_ERR_UNSUPPORTED, "kv_append: head_dim %d not built (64, 128)", D);
+  if (T < 0 || Hkv <= 0 || block_size <= 0 || num_pages < 0) return fail(B200FA_ERR_INVALID_ARG, "kv_append: bad extent");
+  if (T == 0) return B200FA_OK;
+  if (!k_new || !v_new || !slot_mapping || !k_pool || !v_pool) return fail(B200FA_ERR_INVALID_ARG, "kv_append: null pointer");
+  const bool quant = pool_dtype == B200FA_I8 || pool_dtype == B200FA_E4M3;
+  if (quant && (!k_scale || !v_scale)) return fail(B200FA_ERR_INVALID_ARG, "kv_append: 8-bit pools need k_scale and v_scale");
+  const int epl = D / 32;   // elements each lane moves with one vector access
+  if (token_stride % epl != 0 || head_stride % epl != 0 || (reinterpret_cast<uintptr_t>(k_new) % (2 * epl)) != 0 ||
+      (reinterpret_cast<uintptr_t>(v_new) % (2 * epl)) != 0)
+    return fail(B200FA_ERR_INVALID_ARG, "kv_append: k_new/v_new rows must be %d-byte aligned", 2 * epl);
+  if (!aligned16(k_pool) || !aligned16(v_pool)) return fail(B200FA_ERR_INVALID_ARG, "kv_append: pools must be 16-byte aligned");
+  cudaError_t e = b200fa::launch_kv_append(src_dtype, pool_dtype, D, k_new, v_new, token_stride, head_stride, slot_mapping,
+                                           k_pool, v_pool, k_scale, v_scale, T, Hkv, num_pages * block_size,
+                                           reinterpret_cast<cudaStream_t>(stream));
+  if (e != cudaSuccess) return cuda_fail(e, "kv_append launch");
+  return B200FA_OK;
+}
+
 int32_t b200fa_kernel_status(void* stream, int32_t* status_out) {
   if (status_out == nullptr) return fail(B200FA_ERR_INVALID_ARG, "status_out is null");
   cudaStream_t cs = reinterpret_cast<cudaStream_t>(stream);

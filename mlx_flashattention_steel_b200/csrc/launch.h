@@ -34,6 +34,12 @@ cudaError_t launch_bwd(const BwdParams& p, int dtype, int D, bool varlen, int nb
 bool bwd_sm100_supported(int dtype, int D);
 cudaError_t launch_bwd_sm100_main(const BwdParams& p, int dtype, int nbatch, int max_k, cudaStream_t stream);
 
+// KV-cache write path (kv_append.cu): scatter T new tokens per kv head into the page pools; 8-bit pools are
+// quantised per (token, head) with an f16 scale.  Strides in elements; slots[t] = page * block_size + offset.
+cudaError_t launch_kv_append(int src_dtype, int pool_dtype, int D, const void* k_new, const void* v_new, int64_t token_stride,
+                             int64_t head_stride, const int64_t* slots, void* k_pool, void* v_pool, void* k_scale,
+                             void* v_scale, int T, int Hkv, int64_t total_slots, cudaStream_t stream);
+
 // Read (and clear when set) the device status word of the tcgen05 kernels of each file; they wait for `stream`.
 cudaError_t fwd_sm100_read_clear_status(cudaStream_t stream, int* out);
 cudaError_t bwd_sm100_read_clear_status(cudaStream_t stream, int* out);

@@ -155,6 +155,45 @@ def dequant(data: torch.Tensor, scale: torch.Tensor, dtype: torch.dtype) -> torc
     return (data.to(torch.float32) * scale.to(torch.float32).unsqueeze(-1)).to(dtype)
 
 
+def quantise_kv(x: torch.Tensor, kind: str) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Per-(token, head) symmetric quantisation of rows [..., D] to int8 or fp8-e4m3, the inverse of `dequant`:
+    scale = f16(max|x| / qmax) (1 where that is zero), q = round-to-nearest-even(x / float(scale)) clamped to
+    +-qmax (qmax 127 / 448).  float32 arithmetic throughout, so a device kernel can match it bit for bit.  The
+    reference has no 8-bit pool (its quantised caches are MLX affine tuples, mlx_mfa/integrations/mlx_lm.py:97-110);
+    this is the format this build defines for its decode kernel."""
+    qmax = 127.0 if kind == "int8" else 448.0
+    xf = x.to(torch.float32)
+    sc = (xf.abs().amax(dim=-1) / qmax).to(torch.float16)
+    sc = torch.where(sc == 0, torch.ones_like(sc), sc)
+    y = xf / sc.to(torch.float32).unsqueeze(-1)
+    if kind == "int8":
+        return y.round().clamp(-127, 127).to(torch.int8), sc
+    return y.clamp(-448, 448).to(torch.float8_e4m3fn), sc
+
+
+def kv_append(k_pool: torch.Tensor, v_pool: torch.Tensor, k_new: torch.Tensor, v_new: torch.Tensor,
+              slot_mapping: Sequence[int], k_scale: Optional[torch.Tensor] = None,
+              v_scale: Optional[torch.Tensor] = None) -> None:
+    """In-place scatter of new tokens [T, Hkv, D] into pools [P, bs, Hkv, D]: token t goes to page
+    slot // bs, offset slot % bs (negative slots are skipped) -- the end state of the splice loop of
+    PagedKVCache.append (mlx_mfa/attention.py:2642-2711).  8-bit pools are quantised with `quantise_kv`
+    and their scales written to k_scale / v_scale [P, bs, Hkv]."""
+    P, bs, H, D = k_pool.shape
+    for pool, new, scale in ((k_pool, k_new, k_scale), (v_pool, v_new, v_scale)):
+        quant = pool.dtype in (torch.int8, torch.float8_e4m3fn)
+        for t, slot in enumerate(slot_mapping):
+            slot = int(slot)
+            if slot < 0 or slot >= P * bs:
+                continue
+            page, offs = divmod(slot, bs)
+            if quant:
+                qx, sc = quantise_kv(new[t], "int8" if pool.dtype == torch.int8 else "e4m3")
+                pool[page, offs] = qx
+                scale[page, offs] = sc
+            else:
+                pool[page, offs] = new[t].to(torch.float32).to(pool.dtype)
+
+
 def paged_attention(
     q: torch.Tensor,
     k_pool: torch.Tensor,

@@ -291,6 +291,23 @@ def bench_extras(device, pk):
     out["config5_varlen_bf16_d64"] = {"num_seqs": len(lens), "fwd_ms": ms_f, "fwd_tflops": fl_fwd / ms_f / 1e9,
                                       "fwd_bwd_ms": ms_fb, "fwd_bwd_tflops": 3.5 * fl_fwd / ms_fb / 1e9,
                                       "frac_tensor_peak": 3.5 * fl_fwd / ms_fb / 1e9 / pk["tf"]}
+    del q, k, v, do
+    # KV-cache write path (the producer of config 4's pools): 262144 new tokens x 8 kv heads x 128, bf16 in,
+    # int8 + f16 scales out, into randomly placed pages filled in token order (what a prefill append looks like).
+    # Algorithmic bytes = tokens read + values and scales written.
+    T, H, D, bs = 262144, 8, 128, 16
+    P = T // bs
+    kn, vn = mk((T, H, D), torch.bfloat16), mk((T, H, D), torch.bfloat16)
+    pages = torch.randperm(P, generator=gd, device=device).to(torch.int64)
+    slots = (pages[:, None] * bs + torch.arange(bs, device=device)[None, :]).reshape(-1).contiguous()
+    kp = torch.zeros((P, bs, H, D), dtype=torch.int8, device=device)
+    vp = torch.zeros_like(kp)
+    ks = torch.ones((P, bs, H), dtype=torch.float16, device=device)
+    vs = torch.ones_like(ks)
+    ms = _time_ms(lambda: fa.kv_append(kn, vn, slots, kp, vp, ks, vs), 10, 3)
+    byts = 2.0 * T * H * (D * 2 + D + 2)
+    out["kv_append_int8"] = {"tokens": T, "ms": ms, "gbs": byts / ms / 1e6, "frac_hbm_peak": byts / ms / 1e6 / pk["hbm"],
+                             "kernel": "kv_append_kernel<bf16, int8>"}
     return out
 
 

@@ -323,10 +323,9 @@ int32_t b200fa_kv_append(int32_t src_dtype, int32_t pool_dtype, int32_t T, int32
   if (!k_new || !v_new || !slot_mapping || !k_pool || !v_pool) return fail(B200FA_ERR_INVALID_ARG, "kv_append: null pointer");
   const bool quant = pool_dtype == B200FA_I8 || pool_dtype == B200FA_E4M3;
   if (quant && (!k_scale || !v_scale)) return fail(B200FA_ERR_INVALID_ARG, "kv_append: 8-bit pools need k_scale and v_scale");
-  const int epl = D / 32;   // elements each lane moves with one vector access
-  if (token_stride % epl != 0 || head_stride % epl != 0 || (reinterpret_cast<uintptr_t>(k_new) % (2 * epl)) != 0 ||
-      (reinterpret_cast<uintptr_t>(v_new) % (2 * epl)) != 0)
-    return fail(B200FA_ERR_INVALID_ARG, "kv_append: k_new/v_new rows must be %d-byte aligned", 2 * epl);
+  // rows are read with 16-byte loads
+  if (token_stride % 8 != 0 || head_stride % 8 != 0 || !aligned16(k_new) || !aligned16(v_new))
+    return fail(B200FA_ERR_INVALID_ARG, "kv_append: k_new/v_new rows must be 16-byte aligned");
   if (!aligned16(k_pool) || !aligned16(v_pool)) return fail(B200FA_ERR_INVALID_ARG, "kv_append: pools must be 16-byte aligned");
   cudaError_t e = b200fa::launch_kv_append(src_dtype, pool_dtype, D, k_new, v_new, token_stride, head_stride, slot_mapping,
                                            k_pool, v_pool, k_scale, v_scale, T, Hkv, num_pages * block_size,

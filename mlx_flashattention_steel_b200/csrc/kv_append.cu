@@ -3,9 +3,10 @@
 // PagedKVCache.append does block by block with array concatenations (mlx_mfa/attention.py:2642-2711), and it
 // is the producer of the int8 / fp8 pool format the decode kernel reads.
 //
-// One warp per (token, kv head) row of D values, K and V in the same launch (blockIdx.y).  A row is 128 or 256
-// bytes in and 64 to 256 bytes out, every access a full-warp contiguous segment: the kernel is bound by HBM
-// (about 3 bytes moved per stored int8 value, 4 per 16-bit value).
+// A (token, kv head) row of D values is handled by D/8 lanes (16-byte loads), K and V in the same launch
+// (blockIdx.y); warps walk the rows with a grid stride.  A row is 128 or 256 bytes in and 64 to 256 bytes out,
+// every access a contiguous segment: the kernel is bound by HBM (about 3 bytes moved per stored int8 value,
+// 4 per 16-bit value).
 //
 // 8-bit pools (one symmetric group spanning D, zero bias):
 //   scale = f16(max|x| / qmax)  (1 if that is zero),  q = round_to_nearest_even(x / float(scale)),
@@ -22,91 +23,125 @@ namespace {
 
 constexpr int kWarpsPerBlock = 8;
 
-// SRC: 0 f16, 1 bf16.  POOL: 0 f16, 1 bf16, 3 int8, 4 e4m3 (the library's dtype codes).  EPL: elements per lane (D / 32).
-template <typename SrcT, int POOL, int EPL>
+// SrcT: __half or __nv_bfloat16.  POOL: 0 f16, 1 bf16, 3 int8, 4 e4m3 (the library's dtype codes).
+// Each lane moves 8 values (one 16-byte load), so a row takes D/8 lanes and a warp handles 32/(D/8) rows per step;
+// warps walk the rows with a grid stride, two steps in flight, from a grid of a few CTAs per SM.
+template <typename SrcT, int POOL, int D>
 __global__ void __launch_bounds__(kWarpsPerBlock * 32)
 kv_append_kernel(const SrcT* __restrict__ k_new, const SrcT* __restrict__ v_new, int64_t token_stride, int64_t head_stride,
                  const int64_t* __restrict__ slots, void* __restrict__ k_pool, void* __restrict__ v_pool,
                  __half* __restrict__ k_scale, __half* __restrict__ v_scale, int T, int Hkv, int64_t total_slots) {
-  constexpr int D = EPL * 32;
-  const int lane = threadIdx.x & 31;
-  const int64_t rowid = static_cast<int64_t>(blockIdx.x) * kWarpsPerBlock + (threadIdx.x >> 5);
-  if (rowid >= static_cast<int64_t>(T) * Hkv) return;
-  const int t = static_cast<int>(rowid / Hkv), h = static_cast<int>(rowid % Hkv);
-  const int64_t slot = slots[t];
-  if (slot < 0 || slot >= total_slots) return;          // padding entry (or a slot outside the pool): nothing is written
+  constexpr int LPR = D / 8;             // lanes per row: 16 (D = 128) or 8 (D = 64)
+  constexpr int RPW = 32 / LPR;          // rows per warp step
+  const int lane = threadIdx.x & 31, sub = lane / LPR, l = lane % LPR;
   const bool is_v = blockIdx.y != 0;
-  const SrcT* src = (is_v ? v_new : k_new) + t * token_stride + h * head_stride + lane * EPL;
-  // one 8-byte (D = 128) or 4-byte (D = 64) load per lane: the warp reads the row as one contiguous segment
-  uint32_t raw[EPL / 2];
-  if (EPL == 4) {
-    const uint2 v = *reinterpret_cast<const uint2*>(src);
-    raw[0] = v.x;
-    raw[EPL / 2 - 1] = v.y;
-  } else {
-    raw[0] = *reinterpret_cast<const uint32_t*>(src);
-  }
-  float x[EPL];
-#pragma unroll
-  for (int i = 0; i < EPL / 2; ++i) {
-    const float2 f = Elem<SrcT>::unpack(raw[i]);
-    x[2 * i] = f.x;
-    x[2 * i + 1] = f.y;
-  }
-  const int64_t dst_row = slot * Hkv + h;               // pools are [page, offset, head, D]: row index = slot * Hkv + h
+  const SrcT* new_base = is_v ? v_new : k_new;
   void* pool = is_v ? v_pool : k_pool;
+  __half* scale_out = is_v ? v_scale : k_scale;
+  const int64_t rows = static_cast<int64_t>(T) * Hkv;
+  const int64_t warp_id = static_cast<int64_t>(blockIdx.x) * kWarpsPerBlock + (threadIdx.x >> 5);
+  const int64_t n_warps = static_cast<int64_t>(gridDim.x) * kWarpsPerBlock;
 
-  if (POOL == 0 || POOL == 1) {
-    // 16-bit pool: copy (same type) or convert through float
-    uint16_t outv[EPL];
-#pragma unroll
-    for (int i = 0; i < EPL; ++i) {
-      if (POOL == 0) { const __half hv = __float2half_rn(x[i]); outv[i] = *reinterpret_cast<const uint16_t*>(&hv); }
-      else { const __nv_bfloat16 bv = __float2bfloat16_rn(x[i]); outv[i] = *reinterpret_cast<const uint16_t*>(&bv); }
+  // one row per lane group; the next step's row is fetched before the current one is quantised and stored
+  struct Row {
+    uint4 raw;
+    int64_t slot;
+    int h;
+    bool write;
+  };
+  auto fetch = [&](int64_t r0) -> Row {
+    Row r;
+    r.raw = make_uint4(0u, 0u, 0u, 0u);
+    r.slot = -1;
+    r.h = 0;
+    const int64_t rowid = r0 + sub;
+    int t = 0;
+    if (rowid < rows) {
+      t = static_cast<int>(rowid / Hkv);
+      r.h = static_cast<int>(rowid % Hkv);
+      r.slot = __ldg(slots + t);
     }
-    uint16_t* dst = reinterpret_cast<uint16_t*>(pool) + dst_row * D + lane * EPL;
-    if (EPL == 4) *reinterpret_cast<uint2*>(dst) = make_uint2(outv[0] | (static_cast<uint32_t>(outv[1]) << 16), outv[2] | (static_cast<uint32_t>(outv[3 % EPL]) << 16));
-    else *reinterpret_cast<uint32_t*>(dst) = outv[0] | (static_cast<uint32_t>(outv[1]) << 16);
-    return;
-  }
+    r.write = r.slot >= 0 && r.slot < total_slots;      // padding entries and slots outside the pool write nothing
+    if (r.write) r.raw = __ldg(reinterpret_cast<const uint4*>(new_base + t * token_stride + r.h * head_stride + l * 8));
+    return r;
+  };
 
-  // 8-bit pool: row max, scale, quantise
-  float amax = 0.f;
+  const int64_t step = n_warps * RPW;
+  Row nxt = fetch(warp_id * RPW);
+  for (int64_t r0 = warp_id * RPW; r0 < rows; r0 += step) {
+    const Row cur = nxt;
+    if (r0 + step < rows) nxt = fetch(r0 + step);
+    const uint4 raw = cur.raw;
+    const int64_t slot = cur.slot;
+    const int h = cur.h;
+    const bool write = cur.write;
+    float x[8];
+    {
+      const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
 #pragma unroll
-  for (int i = 0; i < EPL; ++i) amax = fmaxf(amax, fabsf(x[i]));
+      for (int i = 0; i < 4; ++i) {
+        const float2 f = Elem<SrcT>::unpack(w[i]);
+        x[2 * i] = f.x;
+        x[2 * i + 1] = f.y;
+      }
+    }
+    const int64_t dst_row = slot * Hkv + h;             // pools are [page, offset, head, D]: row index = slot * Hkv + h
+
+    if (POOL == 0 || POOL == 1) {
+      // 16-bit pool: the same bits, or a conversion through float when the types differ
+      uint4 o;
+      if (POOL == 0) o = make_uint4(Elem<__half>::pack(x[0], x[1]), Elem<__half>::pack(x[2], x[3]), Elem<__half>::pack(x[4], x[5]), Elem<__half>::pack(x[6], x[7]));
+      else o = make_uint4(Elem<__nv_bfloat16>::pack(x[0], x[1]), Elem<__nv_bfloat16>::pack(x[2], x[3]), Elem<__nv_bfloat16>::pack(x[4], x[5]), Elem<__nv_bfloat16>::pack(x[6], x[7]));
+      if (write) *reinterpret_cast<uint4*>(reinterpret_cast<uint16_t*>(pool) + dst_row * D + l * 8) = o;
+      continue;
+    }
+
+    // 8-bit pool: row max over the row's lanes, scale, quantise
+    float amax = 0.f;
 #pragma unroll
-  for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
-  const float qmax = POOL == 3 ? 127.f : 448.f;
-  __half sc = __float2half_rn(__fdiv_rn(amax, qmax));
-  if (__half2float(sc) == 0.f) sc = __float2half_rn(1.f);
-  const float scf = __half2float(sc);
-  uint8_t q[EPL];
+    for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(x[i]));
 #pragma unroll
-  for (int i = 0; i < EPL; ++i) {
-    const float y = __fdiv_rn(x[i], scf);
-    if (POOL == 3) {
-      q[i] = static_cast<uint8_t>(static_cast<int8_t>(max(-127, min(127, __float2int_rn(y)))));
-    } else {
-      q[i] = static_cast<uint8_t>(__nv_cvt_float_to_fp8(fminf(fmaxf(y, -448.f), 448.f), __NV_SATFINITE, __NV_E4M3));
+    for (int o = LPR / 2; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+    // Correctly rounded quotients without the division routine: with r = rn(1/b), q0 = rn(a*r), the residual
+    // e = a - b*q0 is exact in one fma and rn(q0 + e*r) is the IEEE quotient (the final step of a Newton division).
+    auto div_rn = [](float a, float b, float rb) -> float {
+      const float q0 = a * rb;
+      return fmaf(fmaf(-q0, b, a), rb, q0);
+    };
+    const float qmax = POOL == 3 ? 127.f : 448.f;
+    __half sc = __float2half_rn(div_rn(amax, qmax, __frcp_rn(qmax)));
+    if (__half2float(sc) == 0.f) sc = __float2half_rn(1.f);
+    const float scf = __half2float(sc);
+    const float rcp = __frcp_rn(scf);
+    uint32_t q[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const float y = div_rn(x[i], scf, rcp);
+      if (POOL == 3) q[i] = static_cast<uint32_t>(max(-127, min(127, __float2int_rn(y)))) & 0xffu;
+      else q[i] = static_cast<uint32_t>(__nv_cvt_float_to_fp8(fminf(fmaxf(y, -448.f), 448.f), __NV_SATFINITE, __NV_E4M3));
+    }
+    if (write) {
+      *reinterpret_cast<uint2*>(reinterpret_cast<uint8_t*>(pool) + dst_row * D + l * 8) =
+          make_uint2(q[0] | (q[1] << 8) | (q[2] << 16) | (q[3] << 24), q[4] | (q[5] << 8) | (q[6] << 16) | (q[7] << 24));
+      if (l == 0) scale_out[dst_row] = sc;
     }
   }
-  uint8_t* dst = reinterpret_cast<uint8_t*>(pool) + dst_row * D + lane * EPL;
-  if (EPL == 4) *reinterpret_cast<uint32_t*>(dst) = q[0] | (q[1] << 8) | (q[2 % EPL] << 16) | (static_cast<uint32_t>(q[3 % EPL]) << 24);
-  else *reinterpret_cast<uint16_t*>(dst) = static_cast<uint16_t>(q[0] | (q[1] << 8));
-  if (lane == 0) (is_v ? v_scale : k_scale)[dst_row] = sc;
 }
 
 template <typename SrcT, int POOL>
 cudaError_t launch_d(int D, const void* k_new, const void* v_new, int64_t ts, int64_t hs, const int64_t* slots, void* k_pool,
                      void* v_pool, void* k_scale, void* v_scale, int T, int Hkv, int64_t total_slots, cudaStream_t stream) {
   const int64_t rows = static_cast<int64_t>(T) * Hkv;
-  dim3 grid(static_cast<unsigned>((rows + kWarpsPerBlock - 1) / kWarpsPerBlock), 2);
+  const int rpw = 32 / (D / 8);
+  // enough CTAs to cover the rows once, capped at 8 per SM on each of K and V (148 SMs): the rest is the grid stride
+  const int64_t want = (rows + static_cast<int64_t>(kWarpsPerBlock) * rpw - 1) / (static_cast<int64_t>(kWarpsPerBlock) * rpw);
+  dim3 grid(static_cast<unsigned>(want < 148 * 8 ? want : 148 * 8), 2);
   if (D == 128)
-    kv_append_kernel<SrcT, POOL, 4><<<grid, kWarpsPerBlock * 32, 0, stream>>>(
+    kv_append_kernel<SrcT, POOL, 128><<<grid, kWarpsPerBlock * 32, 0, stream>>>(
         static_cast<const SrcT*>(k_new), static_cast<const SrcT*>(v_new), ts, hs, slots, k_pool, v_pool,
         static_cast<__half*>(k_scale), static_cast<__half*>(v_scale), T, Hkv, total_slots);
   else
-    kv_append_kernel<SrcT, POOL, 2><<<grid, kWarpsPerBlock * 32, 0, stream>>>(
+    kv_append_kernel<SrcT, POOL, 64><<<grid, kWarpsPerBlock * 32, 0, stream>>>(
         static_cast<const SrcT*>(k_new), static_cast<const SrcT*>(v_new), ts, hs, slots, k_pool, v_pool,
         static_cast<__half*>(k_scale), static_cast<__half*>(v_scale), T, Hkv, total_slots);
   return cudaGetLastError();

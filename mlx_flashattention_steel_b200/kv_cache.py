@@ -57,7 +57,10 @@ def kv_append(k_new, v_new, slot_mapping, k_pool, v_pool, k_scale=None, v_scale=
         for s in (k_scale, v_scale):
             if s is None or s.dtype != torch.float16 or tuple(s.shape) != (P, bs, H) or not s.is_contiguous():
                 raise ValueError("kv_append: 8-bit pools need contiguous f16 scales [P, block_size, Hkv].")
-    if k_new.stride(2) != 1 or v_new.stride(2) != 1 or v_new.stride() != k_new.stride():
+    def rows_ok(x):   # the kernel reads rows with 16-byte loads
+        return x.stride(2) == 1 and x.stride(0) % 8 == 0 and x.stride(1) % 8 == 0 and x.data_ptr() % 16 == 0
+
+    if not (rows_ok(k_new) and rows_ok(v_new)) or v_new.stride() != k_new.stride():
         k_new, v_new = k_new.contiguous(), v_new.contiguous()
     if T == 0:
         return

@@ -379,17 +379,24 @@ fa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
           for (int i = 0; i < BN; ++i) x[i] *= p.scale_log2;
         }
         if (need_mask) {
-          const int hi = p.causal ? min(S - 1, row + off) : S - 1;       // last visible key
-          const int lo = p.window_left >= 0 ? row + off - p.window_left : 0;
+          // first / last visible column of this row in tile coordinates; a tile usually crosses only one of the
+          // two edges (the diagonal or the end of the keys on the right, the window on the left)
+          const int hi_rel = (p.causal ? min(S - 1, row + off) : S - 1) - k0;
+          const int lo_rel = (p.window_left >= 0 ? row + off - p.window_left : 0) - k0;
+          const bool cut_hi = (k0 + BN > S) || (p.causal && (k0 + BN - 1 > q0 + off));
+          const bool cut_lo = p.window_left >= 0 && (k0 < q0 + BM - 1 + off - p.window_left);
+          if (cut_hi) {
 #pragma unroll
-          for (int i = 0; i < BN; ++i) {
-            const int col = k0 + i;
-            if (col > hi || col < lo) x[i] = -INFINITY;
+            for (int i = 0; i < BN; ++i)
+              if (i > hi_rel) x[i] = -INFINITY;
+          }
+          if (cut_lo) {
+#pragma unroll
+            for (int i = 0; i < BN; ++i)
+              if (i < lo_rel) x[i] = -INFINITY;
           }
         }
-        m_tile = x[0];
-#pragma unroll
-        for (int i = 1; i < BN; ++i) m_tile = fmaxf(m_tile, x[i]);
+        m_tile = tree_max64(x);
       }
 
       // lazy rescale: keep the old reference max unless the row max grew by more than 2^8

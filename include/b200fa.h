@@ -216,6 +216,20 @@ int32_t b200fa_kv_append(int32_t src_dtype, int32_t pool_dtype, int32_t T, int32
                          void* v_scale, void* stream);
 
 /*
+ * Rotary position embedding of x [B, H, N, D] (f16 / bf16; strides in elements: batch, head, row; D contiguous) into
+ * out (may be x).  cos_table / sin_table: float32 [max_pos, rotary_dim / 2]; row n of batch b uses position
+ * offsets[b] + n (offsets: device int32 [B]) or offset + n when offsets is null.  interleaved != 0 rotates pairs
+ * (2i, 2i+1), else (i, i + rotary_dim/2); elements beyond rotary_dim pass through; inverse != 0 applies the
+ * transposed rotation (for gradients).  With a device `offsets` array the caller guarantees offsets[b] + N <= max_pos.
+ * Replaces the in-kernel rotation of mfa_attention_rope_forward (csrc/bindings.cpp, csrc/mfa_steel_fwd.cpp:704-734,
+ * 831-858) and _apply_rope_mlx (mlx_mfa/attention.py:2128-2210).
+ */
+int32_t b200fa_rope(int32_t dtype, int32_t B, int32_t H, int32_t N, int32_t D, int32_t rotary_dim, int32_t interleaved,
+                    int32_t inverse, const void* x, const int64_t* x_strides, void* out, const int64_t* out_strides,
+                    const float* cos_table, const float* sin_table, int32_t max_pos, const int32_t* offsets, int32_t offset,
+                    void* stream);
+
+/*
  * Reads and clears the library-wide device status word of the tcgen05 kernels
  * (forward, backward): 0 = ok, bit 0 = a bounded mbarrier wait inside a kernel
  * gave up after about a second (its outputs are then undefined).  Waits for

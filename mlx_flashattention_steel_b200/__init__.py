@@ -18,6 +18,7 @@ from .attention import (
 
 from .host_pipeline import HostPipeline, flash_attention_from_host
 from .kv_cache import PagedKVCache, kv_append
+from .rope import apply_rope, flash_attention_rope, make_rope_3d_tables
 
 __version__ = "0.1.0"
 
@@ -27,6 +28,9 @@ __all__ = [
     "flash_attention_kvcache",
     "flash_attention_paged",
     "paged_kv_gather",
+    "flash_attention_rope",
+    "apply_rope",
+    "make_rope_3d_tables",
     "PagedKVCache",
     "kv_append",
     "flash_attention_from_host",

@@ -580,6 +580,16 @@ def flash_attention_paged(
     return torch.cat(outs, dim=0)
 
 
+def _first_offset(cache_seqlens) -> int:
+    """cache_seqlens as one int: the value itself, or the first entry of an array / list (what the reference's
+    append and paged routes do, mlx_mfa/attention.py:1077-1082, 1153-1158)."""
+    if isinstance(cache_seqlens, torch.Tensor):
+        return int(cache_seqlens.reshape(-1)[0])
+    if isinstance(cache_seqlens, int):
+        return cache_seqlens
+    return int(list(cache_seqlens)[0]) if hasattr(cache_seqlens, "__iter__") else int(cache_seqlens)
+
+
 def flash_attention_kvcache(
     q,
     k_cache,
@@ -614,8 +624,9 @@ def flash_attention_kvcache(
     (mlx_mfa/attention.py:1124-1167).  Dense mode takes caches ``[B, Hkv, S, D]``
     (or a pool indexed by ``cache_batch_idx``).  Append mode (``k_new``/``v_new``, dense only)
     returns ``(out, k_updated, v_updated)`` as the reference does (mlx_mfa/attention.py:1059-1119);
-    paged pools are written through ``PagedKVCache.append``.  Rotary arguments raise
-    NotImplementedError.
+    paged pools are written through ``PagedKVCache.append``.  ``rotary_cos`` / ``rotary_sin`` rotate q at
+    ``cache_seqlens`` (and k_new in append mode, the dense cache's keys at ``[0, S)`` in dense mode; a paged pool
+    holds rotated keys already).
     """
     q = _as_tensor(q, "q")
     if q.ndim != 4:
@@ -639,11 +650,18 @@ def flash_attention_kvcache(
                 "flash_attention_kvcache: k_new/v_new append is not supported together with "
                 "cache_batch_idx (continuous-batching pool mode)."
             )
-        if has_rope:
-            raise NotImplementedError("flash_attention_kvcache: rotary embedding is not built.")
         # Append to the dense cache (or start one from k_new / v_new alone), then attend on the updated cache
-        # and hand it back: (out, k_updated, v_updated), mlx_mfa/attention.py:1102-1119.
+        # and hand it back: (out, k_updated, v_updated), mlx_mfa/attention.py:1102-1119.  With rotary tables q and
+        # k_new are both rotated at position cache_seqlens first; the cache holds rotated keys (1084-1100).
         k_new, v_new = _as_tensor(k_new, "k_new"), _as_tensor(v_new, "v_new")
+        if has_rope:
+            if rotary_cos is None or rotary_sin is None:
+                raise ValueError("flash_attention_kvcache: both rotary_cos and rotary_sin must be provided together.")
+            from .rope import apply_rope
+
+            cs = _first_offset(cache_seqlens)
+            q = apply_rope(q, rotary_cos, rotary_sin, cs, interleaved, rotary_dim, stream)
+            k_new = apply_rope(k_new, rotary_cos, rotary_sin, cs, interleaved, rotary_dim, stream)
         if k_cache is not None:
             k_cache, v_cache = _as_tensor(k_cache, "k_cache"), _as_tensor(v_cache, "v_cache")
             k_updated = torch.cat([k_cache, k_new.to(k_cache.dtype)], dim=2)
@@ -663,9 +681,12 @@ def flash_attention_kvcache(
         if window_size is not None:
             raise ValueError("flash_attention_kvcache: window_size is not supported in paged mode.")
         if has_rope:
+            # keys in the pool are already rotated; only q is, at position cache_seqlens (mlx_mfa/attention.py:1138-1161)
             if rotary_cos is None or rotary_sin is None:
                 raise ValueError("flash_attention_kvcache: both rotary_cos and rotary_sin must be provided together.")
-            raise NotImplementedError("flash_attention_kvcache: rotary embedding is not built.")
+            from .rope import apply_rope
+
+            q = apply_rope(q, rotary_cos, rotary_sin, _first_offset(cache_seqlens), interleaved, rotary_dim, stream)
         if alibi_slopes is not None:
             raise ValueError("flash_attention_kvcache: alibi_slopes is not supported in paged mode.")
         # The reference drops softcap here (mlx_mfa/attention.py:1169-1172); it is applied.
@@ -682,9 +703,14 @@ def flash_attention_kvcache(
         idx = _as_tensor(cache_batch_idx, "cache_batch_idx").long()
         k_cache, v_cache = k_cache[idx], v_cache[idx]
     if has_rope:
+        # dense cache of unrotated keys: q at cache_seqlens (+ per-batch offsets), keys at [0, S)
+        # (the reference routes this to flash_attention_rope and drops softcap / window there, 1195-1203; they apply here)
         if rotary_cos is None or rotary_sin is None:
             raise ValueError("flash_attention_kvcache: both rotary_cos and rotary_sin must be provided together.")
-        raise NotImplementedError("flash_attention_kvcache: rotary embedding is not built.")
+        from .rope import apply_rope
+
+        q = apply_rope(q, rotary_cos, rotary_sin, cache_seqlens, interleaved, rotary_dim, stream)
+        k_cache = apply_rope(k_cache, rotary_cos, rotary_sin, 0, interleaved, rotary_dim, stream)
     return flash_attention(q, k_cache, v_cache, scale=scale, causal=causal, softcap=softcap,
                            alibi_slopes=alibi_slopes, window_size=window_size, stream=stream)
 

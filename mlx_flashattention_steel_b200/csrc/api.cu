@@ -334,6 +334,31 @@ int32_t b200fa_kv_append(int32_t src_dtype, int32_t pool_dtype, int32_t T, int32
   return B200FA_OK;
 }
 
+int32_t b200fa_rope(int32_t dtype, int32_t B, int32_t H, int32_t N, int32_t D, int32_t rotary_dim, int32_t interleaved,
+                    int32_t inverse, const void* x, const int64_t* x_strides, void* out, const int64_t* out_strides,
+                    const float* cos_table, const float* sin_table, int32_t max_pos, const int32_t* offsets, int32_t offset,
+                    void* stream) {
+  if (dtype != B200FA_F16 && dtype != B200FA_BF16) return fail(B200FA_ERR_UNSUPPORTED, "rope: f16 / bf16 only");
+  if (B < 0 || H <= 0 || N < 0 || D <= 0 || D % 8 != 0) return fail(B200FA_ERR_INVALID_ARG, "rope: bad extent (D must be a multiple of 8)");
+  if (rotary_dim <= 0 || rotary_dim > D || rotary_dim % 2 != 0)
+    return fail(B200FA_ERR_INVALID_ARG, "rope: rotary_dim %d must be even and in (0, D]", rotary_dim);
+  if (!interleaved && rotary_dim % 16 != 0)
+    return fail(B200FA_ERR_UNSUPPORTED, "rope: split-half mode needs rotary_dim to be a multiple of 16");
+  if ((D - rotary_dim) % 8 != 0 && !interleaved) return fail(B200FA_ERR_UNSUPPORTED, "rope: D - rotary_dim must be a multiple of 8");
+  if (B == 0 || N == 0) return B200FA_OK;
+  if (!x || !out || !cos_table || !sin_table || !x_strides || !out_strides) return fail(B200FA_ERR_INVALID_ARG, "rope: null pointer");
+  if (!aligned16(x) || !aligned16(out)) return fail(B200FA_ERR_INVALID_ARG, "rope: x and out must be 16-byte aligned");
+  for (int i = 0; i < 3; ++i)
+    if (x_strides[i] % 8 != 0 || out_strides[i] % 8 != 0) return fail(B200FA_ERR_INVALID_ARG, "rope: strides must be multiples of 8 elements");
+  if (offsets == nullptr && (offset < 0 || static_cast<int64_t>(offset) + N > max_pos))
+    return fail(B200FA_ERR_INVALID_ARG, "rope: positions [%d, %d) exceed the table's %d rows", offset, offset + N, max_pos);
+  cudaError_t e = b200fa::launch_rope(dtype, x, out, cos_table, sin_table, offsets, offset, B, H, N, D, rotary_dim,
+                                      interleaved ? 1 : 0, inverse ? 1 : 0, x_strides, out_strides,
+                                      reinterpret_cast<cudaStream_t>(stream));
+  if (e != cudaSuccess) return cuda_fail(e, "rope launch");
+  return B200FA_OK;
+}
+
 int32_t b200fa_kernel_status(void* stream, int32_t* status_out) {
   if (status_out == nullptr) return fail(B200FA_ERR_INVALID_ARG, "status_out is null");
   cudaStream_t cs = reinterpret_cast<cudaStream_t>(stream);

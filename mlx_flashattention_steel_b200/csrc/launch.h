@@ -40,6 +40,11 @@ cudaError_t launch_kv_append(int src_dtype, int pool_dtype, int D, const void* k
                              int64_t head_stride, const int64_t* slots, void* k_pool, void* v_pool, void* k_scale,
                              void* v_scale, int T, int Hkv, int64_t total_slots, cudaStream_t stream);
 
+// Rotary embedding pass (rope.cu).  xs / os: batch, head, row strides in elements; offsets (device, [B]) or one offset.
+cudaError_t launch_rope(int dtype, const void* x, void* out, const float* cosb, const float* sinb, const int* offsets,
+                        int offset, int B, int H, int N, int D, int rot, int interleaved, int inverse, const int64_t* xs,
+                        const int64_t* os, cudaStream_t stream);
+
 // Read (and clear when set) the device status word of the tcgen05 kernels of each file; they wait for `stream`.
 cudaError_t fwd_sm100_read_clear_status(cudaStream_t stream, int* out);
 cudaError_t bwd_sm100_read_clear_status(cudaStream_t stream, int* out);

@@ -155,6 +155,30 @@ def dequant(data: torch.Tensor, scale: torch.Tensor, dtype: torch.dtype) -> torc
     return (data.to(torch.float32) * scale.to(torch.float32).unsqueeze(-1)).to(dtype)
 
 
+def rope(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, offset=0, interleaved: bool = True,
+         rotary_dim: Optional[int] = None) -> torch.Tensor:
+    """Rotary embedding of x [B,H,N,D] in float64 (mlx_mfa/attention.py:2128-2210): row n of batch b uses table row
+    offset[b] + n; interleaved pairs (2i, 2i+1) or halves (i, i + rot/2); out[a] = x[a]cos - x[b]sin,
+    out[b] = x[a]sin + x[b]cos; elements beyond rotary_dim pass through."""
+    B, H, N, D = x.shape
+    rot = D if rotary_dim is None else rotary_dim
+    xd = x.to(torch.float64)
+    out = xd.clone()
+    offs = [int(offset)] * B if isinstance(offset, int) else [int(o) for o in offset]
+    for b in range(B):
+        c = cos[offs[b]:offs[b] + N].to(torch.float64)[None]          # [1, N, rot/2]
+        s_ = sin[offs[b]:offs[b] + N].to(torch.float64)[None]
+        if interleaved:
+            a, bb = xd[b, :, :, 0:rot:2], xd[b, :, :, 1:rot:2]
+            out[b, :, :, 0:rot:2] = a * c - bb * s_
+            out[b, :, :, 1:rot:2] = a * s_ + bb * c
+        else:
+            a, bb = xd[b, :, :, :rot // 2], xd[b, :, :, rot // 2:rot]
+            out[b, :, :, :rot // 2] = a * c - bb * s_
+            out[b, :, :, rot // 2:rot] = a * s_ + bb * c
+    return out
+
+
 def quantise_kv(x: torch.Tensor, kind: str) -> Tuple[torch.Tensor, torch.Tensor]:
     """Per-(token, head) symmetric quantisation of rows [..., D] to int8 or fp8-e4m3, the inverse of `dequant`:
     scale = f16(max|x| / qmax) (1 where that is zero), q = round-to-nearest-even(x / float(scale)) clamped to

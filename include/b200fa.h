@@ -201,6 +201,16 @@ int32_t b200fa_decode_paged_static(const b200fa_desc* d, const void* q,
                                    void* out, float* lse, void* stream);
 
 /*
+ * Transpose of b200fa_paged_kv_gather, for the backward pass through a page pool: grad [B, H, max_kv_len, D]
+ * (f16 / bf16, contiguous) is added into grad_pool [num_pages, block_size, H, D], which the caller zeroes first;
+ * tokens beyond seq_lens[b] and negative table entries contribute nothing, a page listed by several sequences
+ * receives the sum.  Replaces _scatter_to_pool (mlx_mfa/attention.py:2878-2940).
+ */
+int32_t b200fa_paged_kv_scatter_add(const void* grad, const int32_t* block_table, const int32_t* seq_lens, int32_t B,
+                                    int32_t H, int32_t D, int32_t dtype, int32_t block_size, int32_t max_blocks,
+                                    int32_t max_kv_len, void* grad_pool, void* stream);
+
+/*
  * KV-cache write path.  Scatters T new tokens (k_new / v_new, element (t, h, d) at t*token_stride +
  * h*head_stride + d, f16 or bf16) into page pools laid out [num_pages, block_size, Hkv, D]; token t goes to
  * slot_mapping[t] = page * block_size + offset (device int64; negative or out-of-pool entries are skipped).

@@ -433,6 +433,34 @@ def paged_kv_gather(pool, block_table, seq_lens, max_kv_len: int, stream=None) -
     return out
 
 
+class _PagedGatherFn(torch.autograd.Function):
+    """paged_kv_gather with a backward: the dense gradient is added back into a pool-shaped tensor page by page
+    (the role of _gather_contig / _scatter_to_pool in the reference's paged vjp, mlx_mfa/attention.py:2878-2989)."""
+
+    @staticmethod
+    def forward(ctx, pool, table, lens, max_kv_len, stream):
+        ctx.save_for_backward(table, lens)
+        ctx.meta = (tuple(pool.shape), pool.dtype, max_kv_len, stream)
+        return paged_kv_gather(pool, table, lens, max_kv_len, stream)
+
+    @staticmethod
+    def backward(ctx, g):
+        table, lens = ctx.saved_tensors
+        shape, dtype, max_kv_len, stream = ctx.meta
+        if dtype not in (torch.float16, torch.bfloat16):
+            raise NotImplementedError("backward through a page pool takes f16 / bf16 pools.")
+        g = g.to(dtype).contiguous()
+        grad_pool = torch.zeros(shape, dtype=dtype, device=g.device)
+        B, H, _, D = g.shape
+        lib = _lib.load()
+        with torch.cuda.device(g.device):
+            st = lib.b200fa_paged_kv_scatter_add(_ptr(g), _ptr(table), _ptr(lens), B, H, D, _DTYPE_CODE[dtype], shape[1],
+                                                 table.shape[1], int(max_kv_len), _ptr(grad_pool),
+                                                 C.c_void_p(_stream_ptr(stream, g.device)))
+        _lib.check(st, "paged_kv_scatter_add")
+        return grad_pool, None, None, None, None
+
+
 _CHECK_DECODE_STATUS = False   # tests switch this on: one stream sync per call
 
 
@@ -515,7 +543,9 @@ def flash_attention_paged(
 
     Short queries ((Hq/Hkv)*Nq <= 8, D = 128, block_size 16) run the split-KV
     decode kernel with in-kernel combine; other shapes gather pages and attend
-    per sequence like the reference (mlx_mfa/attention.py:2944-2989).
+    per sequence like the reference (mlx_mfa/attention.py:2944-2989).  When gradients are
+    wanted (q or a 16-bit pool requires grad) every shape takes the gather route, whose
+    backward adds dK / dV back into pool-shaped gradients page by page (2878-2940, 3020-3084).
     """
     q = _as_tensor(q, "q")
     k_pages, v_pages = _as_tensor(k_pages, "k_pages"), _as_tensor(v_pages, "v_pages")
@@ -556,7 +586,9 @@ def flash_attention_paged(
         raise NotImplementedError("flash_attention_paged takes f16/bf16 queries.")
     k_pages, v_pages = k_pages.contiguous(), v_pages.contiguous()
 
-    decode_ok = (Hq // Hkv) * Nq <= 8 and D == 128 and block_size == 16
+    # training: gradients flow through the gather route (gather, per-sequence attention, scatter-add into the pools)
+    needs_grad = torch.is_grad_enabled() and (q.requires_grad or k_pages.requires_grad or v_pages.requires_grad)
+    decode_ok = (Hq // Hkv) * Nq <= 8 and D == 128 and block_size == 16 and not needs_grad
     if decode_ok:
         out, lse = _decode_raw(q, k_pages, v_pages, k_scale, v_scale, table, lens, max_kv_len, float(scale),
                                bool(causal), float(softcap), block_size, return_lse, stream, num_splits)
@@ -566,8 +598,13 @@ def flash_attention_paged(
     if return_lse:
         raise NotImplementedError("return_lse on the gather route is not built.")
     # gather route, as the reference: pages -> contiguous, then exact-length slices per sequence
-    K = paged_kv_gather(k_pages, table, lens, max_kv_len, stream)
-    V = paged_kv_gather(v_pages, table, lens, max_kv_len, stream)
+    if needs_grad:
+        _require_cuda(q, k_pages, v_pages, table, lens)
+        K = _PagedGatherFn.apply(k_pages, table, lens, int(max_kv_len), stream)
+        V = _PagedGatherFn.apply(v_pages, table, lens, int(max_kv_len), stream)
+    else:
+        K = paged_kv_gather(k_pages, table, lens, max_kv_len, stream)
+        V = paged_kv_gather(v_pages, table, lens, max_kv_len, stream)
     lens_host = [int(x) for x in lens.tolist()]
     outs = []
     for b in range(B):

@@ -309,6 +309,24 @@ int32_t b200fa_paged_kv_gather(const void* pool, const int32_t* block_table, con
   return B200FA_OK;
 }
 
+int32_t b200fa_paged_kv_scatter_add(const void* grad, const int32_t* block_table, const int32_t* seq_lens, int32_t B,
+                                    int32_t H, int32_t D, int32_t dtype, int32_t block_size, int32_t max_blocks,
+                                    int32_t max_kv_len, void* grad_pool, void* stream) {
+  if (B < 0 || H <= 0 || D <= 0 || block_size <= 0 || max_blocks < 0 || max_kv_len < 0)
+    return fail(B200FA_ERR_INVALID_ARG, "bad extent");
+  if (dtype != B200FA_F16 && dtype != B200FA_BF16) return fail(B200FA_ERR_UNSUPPORTED, "scatter_add: f16 / bf16 only");
+  if (D % 8 != 0) return fail(B200FA_ERR_INVALID_ARG, "D must be a multiple of 8");
+  if (B == 0 || max_kv_len == 0) return B200FA_OK;
+  if (!grad || !block_table || !seq_lens || !grad_pool) return fail(B200FA_ERR_INVALID_ARG, "null pointer");
+  if (!aligned16(grad) || !aligned16(grad_pool)) return fail(B200FA_ERR_INVALID_ARG, "grad/grad_pool must be 16-byte aligned");
+  if (static_cast<int64_t>(max_blocks) * block_size < max_kv_len)
+    return fail(B200FA_ERR_INVALID_ARG, "max_kv_len %d exceeds max_blocks*block_size", max_kv_len);
+  cudaError_t e = b200fa::launch_paged_scatter_add(grad, block_table, seq_lens, B, H, D, dtype, block_size, max_blocks,
+                                                   max_kv_len, grad_pool, reinterpret_cast<cudaStream_t>(stream));
+  if (e != cudaSuccess) return cuda_fail(e, "scatter_add launch");
+  return B200FA_OK;
+}
+
 int32_t b200fa_kv_append(int32_t src_dtype, int32_t pool_dtype, int32_t T, int32_t Hkv, int32_t D, int32_t block_size,
                          int64_t num_pages, const void* k_new, const void* v_new, int64_t token_stride,
                          int64_t head_stride, const int64_t* slot_mapping, void* k_pool, void* v_pool, void* k_scale,

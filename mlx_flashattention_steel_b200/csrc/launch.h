@@ -40,6 +40,11 @@ cudaError_t launch_kv_append(int src_dtype, int pool_dtype, int D, const void* k
                              int64_t head_stride, const int64_t* slots, void* k_pool, void* v_pool, void* k_scale,
                              void* v_scale, int T, int Hkv, int64_t total_slots, cudaStream_t stream);
 
+// Transpose of the page gather for gradients (paged_gather.cu); grad_pool must be zero on entry.  dtype 0 f16, 1 bf16.
+cudaError_t launch_paged_scatter_add(const void* grad, const int32_t* block_table, const int32_t* seq_lens, int B, int H,
+                                     int D, int dtype, int block_size, int max_blocks, int max_kv_len, void* grad_pool,
+                                     cudaStream_t stream);
+
 // Rotary embedding pass (rope.cu).  xs / os: batch, head, row strides in elements; offsets (device, [B]) or one offset.
 cudaError_t launch_rope(int dtype, const void* x, void* out, const float* cosb, const float* sinb, const int* offsets,
                         int offset, int B, int H, int N, int D, int rot, int interleaved, int inverse, const int64_t* xs,

@@ -37,7 +37,54 @@ __global__ void __launch_bounds__(256) paged_kv_gather_kernel(
   }
 }
 
+// The transpose of the gather, for gradients: grad_pool[page, t % bs, h, :] += grad[b, h, t, :] for t < seq_lens[b]
+// and a non-negative table entry (the role of _scatter_to_pool, mlx_mfa/attention.py:2878-2940).  The pool-shaped
+// output must start at zero; a page listed by several sequences (a shared prefix) accumulates all of them, which is
+// why the adds are packed 16-bit atomics rather than stores.
+template <typename T2>
+__global__ void __launch_bounds__(256) paged_kv_scatter_add_kernel(
+    const uint4* __restrict__ grad, const int32_t* __restrict__ block_table, const int32_t* __restrict__ seq_lens, int H,
+    int chunks_per_row, int block_size, int max_blocks, int max_kv_len, long long total_chunks, T2* __restrict__ grad_pool) {
+  const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+  for (long long idx = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; idx < total_chunks; idx += stride) {
+    const int c = static_cast<int>(idx % chunks_per_row);
+    long long rem = idx / chunks_per_row;
+    const int t = static_cast<int>(rem % max_kv_len);
+    rem /= max_kv_len;
+    const int h = static_cast<int>(rem % H);
+    const int b = static_cast<int>(rem / H);
+    if (t >= seq_lens[b]) continue;
+    const int page = block_table[static_cast<long long>(b) * max_blocks + t / block_size];
+    if (page < 0) continue;
+    const uint4 v = grad[idx];
+    const long long dst = (((static_cast<long long>(page) * block_size + (t % block_size)) * H + h) * chunks_per_row + c) * 4;
+    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) atomicAdd(grad_pool + dst + i, *reinterpret_cast<const T2*>(&w[i]));
+  }
+}
+
 }  // namespace
+
+cudaError_t launch_paged_scatter_add(const void* grad, const int32_t* block_table, const int32_t* seq_lens, int B, int H,
+                                     int D, int dtype, int block_size, int max_blocks, int max_kv_len, void* grad_pool,
+                                     cudaStream_t stream) {
+  const int cpr = D * 2 / 16;
+  const long long total = static_cast<long long>(B) * H * max_kv_len * cpr;
+  if (total == 0) return cudaSuccess;
+  long long blocks = (total + 255) / 256;
+  const long long cap = 148LL * 32;
+  if (blocks > cap) blocks = cap;
+  if (dtype == 0)
+    paged_kv_scatter_add_kernel<__half2><<<static_cast<unsigned>(blocks), 256, 0, stream>>>(
+        reinterpret_cast<const uint4*>(grad), block_table, seq_lens, H, cpr, block_size, max_blocks, max_kv_len, total,
+        reinterpret_cast<__half2*>(grad_pool));
+  else
+    paged_kv_scatter_add_kernel<__nv_bfloat162><<<static_cast<unsigned>(blocks), 256, 0, stream>>>(
+        reinterpret_cast<const uint4*>(grad), block_table, seq_lens, H, cpr, block_size, max_blocks, max_kv_len, total,
+        reinterpret_cast<__nv_bfloat162*>(grad_pool));
+  return cudaGetLastError();
+}
 
 cudaError_t launch_paged_gather(const void* pool, const int32_t* block_table, const int32_t* seq_lens,
                                 int B, int H, int D, int elem_bytes, int block_size, int max_blocks,

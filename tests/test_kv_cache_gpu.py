@@ -144,3 +144,39 @@ def test_dense_append_mode_returns_the_updated_cache(dev):
     assert_close(out2, vn.repeat_interleave(2, 1), torch.float16)       # one key: the output is its value
     with pytest.raises(ValueError):
         fa.flash_attention_kvcache(q.to(dev), kc.to(dev), vc.to(dev), k_new=kn.to(dev))
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+def test_backward_through_the_page_pool(dev, dtype):
+    """dQ and pool-shaped dK / dV through flash_attention_paged: two sequences of different length, -1 padding, and a
+    page shared by both sequences (its gradient is the sum of both), against float64 autograd through the same
+    gather written with index operations (the reference's vjp: gather, per-sequence vjp, _scatter_to_pool;
+    mlx_mfa/attention.py:2878-2940, 3020-3084)."""
+    P, bs, H, D = 10, 16, 2, 64
+    lens = [40, 23]
+    table = torch.tensor([[7, 2, 5], [7, 4, -1]], dtype=torch.int32)         # page 7 is a shared prefix
+    kp, vp = randn((P, bs, H, D), dtype, 660), randn((P, bs, H, D), dtype, 661)
+    q, do = randn((2, 4, 24, D), dtype, 662), randn((2, 4, 24, D), dtype, 663)
+    qg, kg, vg = (x.to(dev).requires_grad_(True) for x in (q, kp, vp))
+    out = fa.flash_attention_paged(qg, kg, vg, table.to(dev), torch.tensor(lens, dtype=torch.int32, device=dev),
+                                   causal=True, block_size=bs)
+    out.backward(do.to(dev))
+    torch.cuda.synchronize()
+    # oracle
+    qr, kr, vr = (x.double().requires_grad_(True) for x in (q, kp, vp))
+    outs = []
+    for b, n in enumerate(lens):
+        pages = table[b, : (n + bs - 1) // bs].long()
+        K = kr[pages].reshape(-1, H, D)[:n].permute(1, 0, 2)[None]
+        V = vr[pages].reshape(-1, H, D)[:n].permute(1, 0, 2)[None]
+        O, _, _ = orc.sdpa(qr[b:b + 1], K, V, causal=True)
+        outs.append(O)
+    ref = torch.cat(outs, 0)
+    assert_close(out, ref.detach(), dtype)
+    ref.backward(do.double())
+    from .util import assert_close_grad
+    assert_close_grad(qg.grad, qr.grad, dtype, "dQ")
+    assert_close_grad(kg.grad, kr.grad, dtype, "dK pages")
+    assert_close_grad(vg.grad, vr.grad, dtype, "dV pages")
+    assert kg.grad.shape == kp.shape and float(kg.grad[0].abs().max()) == 0.0       # an unused page gets no gradient
+    assert float(kg.grad[5, 8:].abs().max()) == 0.0                                  # nor do slots beyond seq_lens

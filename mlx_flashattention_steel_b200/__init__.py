@@ -18,6 +18,12 @@ from .attention import (
 
 from .host_pipeline import HostPipeline, flash_attention_from_host
 from .kv_cache import PagedKVCache, kv_append
+from .packed import (
+    flash_attention_kv_packed,
+    flash_attention_qkv_packed,
+    flash_attention_varlen_kv_packed,
+    flash_attention_varlen_qkv_packed,
+)
 from .rope import apply_rope, flash_attention_rope, make_rope_3d_tables
 
 __version__ = "0.1.0"
@@ -29,6 +35,10 @@ __all__ = [
     "flash_attention_paged",
     "paged_kv_gather",
     "flash_attention_rope",
+    "flash_attention_qkv_packed",
+    "flash_attention_kv_packed",
+    "flash_attention_varlen_qkv_packed",
+    "flash_attention_varlen_kv_packed",
     "apply_rope",
     "make_rope_3d_tables",
     "PagedKVCache",

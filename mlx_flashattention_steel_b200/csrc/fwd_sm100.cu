@@ -62,11 +62,13 @@ enum Bar {
   BAR_S_FULL = 9,            // +buffer
   BAR_P_FULL = 11,           // +buffer
   BAR_PV_DONE = 13,
-  BAR_COUNT = 14
+  BAR_O_STAGED = 14,         // count 4: the softmax warps have written their O rows to shared memory
+  BAR_COUNT = 15
 };
 
 struct Sm100Args {
   FwdParams p;
+  int tma_store;             // dense layout: O leaves through shared memory and TMA stores
 };
 
 // max / min of 64 values as a 3-ary tree (depth 4) instead of a 63-deep dependent chain
@@ -143,7 +145,8 @@ template <int DT> __device__ __forceinline__ uint32_t pack16(float a, float b) {
 template <int HD, int DT>
 __global__ void __launch_bounds__(kThreads, 2)
 fa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
-                    const __grid_constant__ CUtensorMap tmV, const Sm100Args a) {
+                    const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmO,
+                    const Sm100Args a) {
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   constexpr int kHalves = Cfg<HD>::kHalves, kQBytes = Cfg<HD>::kQBytes, kKVBytes = Cfg<HD>::kKVBytes,
@@ -198,7 +201,25 @@ fa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     return;
   }
 
-  if (tid == 0) {
+  // The producer thread sets up the barriers and starts the first loads (Q and as many K / V tiles as there are
+  // stages, all of which are empty) before the CTA-wide sync, so TMEM allocation and the sync hide under them.
+  auto load_k = [&](int j) {
+    const int st = j & 1;
+    mbar_arrive_expect_tx(bar(BAR_K_FULL + st), kKVBytes);
+#pragma unroll
+    for (int hf = 0; hf < kHalves; ++hf)
+      tma_load_4d(smem_u32(sK + st * kKVBytes + hf * (kKVBytes / kHalves)), &tmK, bar(BAR_K_FULL + st), 64 * hf,
+                  k_begin + (kt_begin + j) * BN, kvh, batch);
+  };
+  auto load_v = [&](int j) {
+    const int st = j & 1;
+    mbar_arrive_expect_tx(bar(BAR_V_FULL + st), kKVBytes);
+#pragma unroll
+    for (int hf = 0; hf < kHalves; ++hf)
+      tma_load_4d(smem_u32(sV + st * kKVBytes + hf * (kKVBytes / kHalves)), &tmV, bar(BAR_V_FULL + st), 64 * hf,
+                  k_begin + (kt_begin + j) * BN, kvh, batch);
+  };
+  if (warp == 4 && lane == 0) {
     mbar_init(bar(BAR_Q), 1);
     for (int s = 0; s < kStages; ++s) {
       mbar_init(bar(BAR_K_FULL + s), 1);
@@ -209,9 +230,18 @@ fa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       mbar_init(bar(BAR_P_FULL + s), 4);     // one arrive per softmax warp
     }
     mbar_init(bar(BAR_PV_DONE), 1);
+    mbar_init(bar(BAR_O_STAGED), 4);
     *s_abort = 0;
     fence_barrier_init();
     fence_proxy_async();
+    mbar_arrive_expect_tx(bar(BAR_Q), kQBytes);
+#pragma unroll
+    for (int hf = 0; hf < kHalves; ++hf)
+      tma_load_4d(smem_u32(sQ + hf * (kQBytes / kHalves)), &tmQ, bar(BAR_Q), 64 * hf, q_begin + q0, head, batch);
+    for (int j = 0; j < kStages && j < n_tiles; ++j) {
+      load_k(j);
+      load_v(j);
+    }
   }
   if (warp == 5) {
     tmem_alloc(smem_u32(s_tmem), kTmemCols);
@@ -226,24 +256,14 @@ fa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   if (warp == 4) {
     // ============================ producer ============================
     if (lane == 0) {
-      mbar_arrive_expect_tx(bar(BAR_Q), kQBytes);
-#pragma unroll
-      for (int hf = 0; hf < kHalves; ++hf)
-        tma_load_4d(smem_u32(sQ + hf * (kQBytes / kHalves)), &tmQ, bar(BAR_Q), 64 * hf, q_begin + q0, head, batch);
-      for (int j = 0; j < n_tiles; ++j) {
+      for (int j = kStages; j < n_tiles; ++j) {
         const int st = j & 1;
         const uint32_t par = ((j >> 1) & 1) ^ 1;
-        const int krow = k_begin + (kt_begin + j) * BN;
+        // K(j) and V(j) reuse the stage of tile j-2: wait until its S MMAs, then its PV MMAs, have read it
         if (!mbar_wait_bounded(bar(BAR_K_EMPTY + st), par, s_abort)) break;
-        mbar_arrive_expect_tx(bar(BAR_K_FULL + st), kKVBytes);
-#pragma unroll
-        for (int hf = 0; hf < kHalves; ++hf)
-          tma_load_4d(smem_u32(sK + st * kKVBytes + hf * (kKVBytes / kHalves)), &tmK, bar(BAR_K_FULL + st), 64 * hf, krow, kvh, batch);
+        load_k(j);
         if (!mbar_wait_bounded(bar(BAR_V_EMPTY + st), par, s_abort)) break;
-        mbar_arrive_expect_tx(bar(BAR_V_FULL + st), kKVBytes);
-#pragma unroll
-        for (int hf = 0; hf < kHalves; ++hf)
-          tma_load_4d(smem_u32(sV + st * kKVBytes + hf * (kKVBytes / kHalves)), &tmV, bar(BAR_V_FULL + st), 64 * hf, krow, kvh, batch);
+        load_v(j);
       }
     }
   } else if (warp == 5) {
@@ -496,18 +516,23 @@ fa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     }
 
     // ---- epilogue: O / l -> global, lse ----
+    // S(n-1) being complete only implies PV(n-3): these warps may be two completions ahead of PV_DONE, and a parity
+    // wait two phases ahead passes at once.  So wait for PV(n-2) first, then for PV(n-1).
+    if (ok && n_tiles >= 2) ok = __all_sync(0xffffffffu, mbar_wait_bounded(bar(BAR_PV_DONE), (n_tiles - 2) & 1, s_abort));
     if (ok) ok = __all_sync(0xffffffffu, mbar_wait_bounded(bar(BAR_PV_DONE), (n_tiles - 1) & 1, s_abort));
     if (ok) {
       tc_fence_after();
       const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
-      uint16_t* orow = reinterpret_cast<uint16_t*>(p.o) + batch * p.o_bs + head * p.o_hs +
-                       static_cast<int64_t>(q_begin + row) * p.o_rs;
+      if (a.tma_store) {
+        // Stage the tile in the Q buffer (free: every S MMA has completed) as two 64-wide 128B-swizzled halves and
+        // let TMA write it: full-line stores instead of 32 rows x 16 bytes per instruction; rows beyond N are
+        // clipped by the tensor map.
+        const int r = tid;
 #pragma unroll
-      for (int c = 0; c < HD / 32; ++c) {
-        uint32_t o[32];
-        tmem_ld32(tO + lane_base + c * 32, o);
-        tc_wait_ld();
-        if (row < N) {
+        for (int c = 0; c < HD / 32; ++c) {
+          uint32_t o[32];
+          tmem_ld32(tO + lane_base + c * 32, o);
+          tc_wait_ld();
 #pragma unroll
           for (int i = 0; i < 32; i += 8) {
             uint4 v;
@@ -515,7 +540,39 @@ fa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
             v.y = pack16<DT>(__uint_as_float(o[i + 2]) * inv, __uint_as_float(o[i + 3]) * inv);
             v.z = pack16<DT>(__uint_as_float(o[i + 4]) * inv, __uint_as_float(o[i + 5]) * inv);
             v.w = pack16<DT>(__uint_as_float(o[i + 6]) * inv, __uint_as_float(o[i + 7]) * inv);
-            *reinterpret_cast<uint4*>(orow + c * 32 + i) = v;
+            const int chunk = c * 4 + (i >> 3);              // 16-byte chunk of the row: half = chunk / 8
+            unsigned char* dst = sQ + (chunk >> 3) * (kQBytes / kHalves) + r * 128 + (((chunk & 7) ^ (r & 7)) << 4);
+            *reinterpret_cast<uint4*>(dst) = v;
+          }
+        }
+        fence_proxy_async();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar(BAR_O_STAGED));
+        if (tid == 0 && mbar_wait_bounded(bar(BAR_O_STAGED), 0, s_abort)) {
+#pragma unroll
+          for (int hf = 0; hf < kHalves; ++hf)
+            tma_store_4d(&tmO, smem_u32(sQ + hf * (kQBytes / kHalves)), 64 * hf, q0, head, batch);
+          tma_store_commit();
+          tma_store_wait<0>();
+        }
+      } else {
+        uint16_t* orow = reinterpret_cast<uint16_t*>(p.o) + batch * p.o_bs + head * p.o_hs +
+                         static_cast<int64_t>(q_begin + row) * p.o_rs;
+#pragma unroll
+        for (int c = 0; c < HD / 32; ++c) {
+          uint32_t o[32];
+          tmem_ld32(tO + lane_base + c * 32, o);
+          tc_wait_ld();
+          if (row < N) {
+#pragma unroll
+            for (int i = 0; i < 32; i += 8) {
+              uint4 v;
+              v.x = pack16<DT>(__uint_as_float(o[i]) * inv, __uint_as_float(o[i + 1]) * inv);
+              v.y = pack16<DT>(__uint_as_float(o[i + 2]) * inv, __uint_as_float(o[i + 3]) * inv);
+              v.z = pack16<DT>(__uint_as_float(o[i + 4]) * inv, __uint_as_float(o[i + 5]) * inv);
+              v.w = pack16<DT>(__uint_as_float(o[i + 6]) * inv, __uint_as_float(o[i + 7]) * inv);
+              *reinterpret_cast<uint4*>(orow + c * 32 + i) = v;
+            }
           }
         }
       }
@@ -556,7 +613,7 @@ bool fwd_sm100_supported(const FwdParams& p, int dtype, int D) {
 template <int HD, int DT>
 static cudaError_t launch_hd(const FwdParams& p, int nbatch, int max_q, cudaStream_t stream) {
   constexpr int dtype = DT;
-  CUtensorMap tmQ, tmK, tmV;
+  CUtensorMap tmQ, tmK, tmV, tmO;
   // TMA: a size-1 dimension still needs a legal stride
   auto fix = [](int64_t s, int64_t fallback) { return s > 0 ? s : fallback; };
   const int64_t q_hs = fix(p.q_hs, static_cast<int64_t>(p.N) * p.q_rs), q_bs = fix(p.q_bs, q_hs * p.Hq);
@@ -568,11 +625,15 @@ static cudaError_t launch_hd(const FwdParams& p, int nbatch, int max_q, cudaStre
     return cudaErrorInvalidValue;
   Sm100Args a;
   a.p = p;
+  // dense outputs go out by TMA; packed sequences share rows of one tensor, so their tiles are stored row by row
+  const int64_t o_hs = fix(p.o_hs, static_cast<int64_t>(p.N) * p.o_rs), o_bs = fix(p.o_bs, o_hs * p.Hq);
+  a.tma_store = (p.cu_q == nullptr && make_map(&tmO, dtype, p.o, HD, p.N, p.Hq, p.B, p.o_rs, o_hs, o_bs, BM)) ? 1 : 0;
+  if (!a.tma_store) tmO = tmQ;
   cudaError_t e = cudaFuncSetAttribute(fa_fwd_sm100_kernel<HD, DT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        Cfg<HD>::kSmemBytes);
   if (e != cudaSuccess) return e;
   dim3 grid((max_q + BM - 1) / BM, p.Hq, nbatch);
-  fa_fwd_sm100_kernel<HD, DT><<<grid, kThreads, Cfg<HD>::kSmemBytes, stream>>>(tmQ, tmK, tmV, a);
+  fa_fwd_sm100_kernel<HD, DT><<<grid, kThreads, Cfg<HD>::kSmemBytes, stream>>>(tmQ, tmK, tmV, tmO, a);
   return cudaGetLastError();
 }
 

@@ -223,6 +223,24 @@ def test_full_size_linearity_in_v(dev):
     assert float((oc - 0.75).abs().max()) <= 1e-2
 
 
+def test_short_tiles_wait_for_both_pending_accumulations(dev):
+    """A query tile with two key tiles can finish its second softmax before the first P.V product has completed;
+    the epilogue must then wait for both.  With constant V every output equals that constant whatever the
+    probabilities are, so any read of an unfinished accumulator shows.  Many such tiles, mixed with long ones."""
+    v_const = 0.75
+    for rep in range(8):
+        q = randn((1, 8, 8192, 128), torch.bfloat16, 140 + rep).to(dev)
+        k = randn((1, 2, 8192, 128), torch.bfloat16, 150 + rep).to(dev)
+        v = torch.full((1, 2, 8192, 128), v_const, dtype=torch.bfloat16, device=dev)
+        out = fa.flash_attention(q, k, v, causal=True).float()
+        assert float((out - v_const).abs().max()) <= 1e-2
+        q = randn((16, 8, 128, 128), torch.bfloat16, 160 + rep).to(dev)
+        k = randn((16, 2, 128, 128), torch.bfloat16, 170 + rep).to(dev)
+        v = torch.full((16, 2, 128, 128), v_const, dtype=torch.bfloat16, device=dev)
+        out = fa.flash_attention(q, k, v, causal=True, softcap=30.0).float()
+        assert float((out - v_const).abs().max()) <= 1e-2
+
+
 def test_host_pipeline_matches_device_call(dev):
     """flash_attention_from_host (chunked, stream-pipelined copies) returns what the device call returns."""
     q = randn((3, 8, 300, 128), torch.bfloat16, 130).pin_memory()

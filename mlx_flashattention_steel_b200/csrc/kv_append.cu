@@ -113,16 +113,40 @@ kv_append_kernel(const SrcT* __restrict__ k_new, const SrcT* __restrict__ v_new,
     if (__half2float(sc) == 0.f) sc = __float2half_rn(1.f);
     const float scf = __half2float(sc);
     const float rcp = __frcp_rn(scf);
-    uint32_t q[8];
+    uint32_t packed[2];
+    if (POOL == 3) {
+      // the same Newton step on value pairs (packed f32x2 ops), round to nearest even, clamp to [-127, 127]
+      // (saturating pack covers the top, one max the bottom), four values per pack pair
+      const float2 rb2 = make_float2(rcp, rcp), nb2 = make_float2(-scf, -scf);
+      int qi[8];
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      const float y = div_rn(x[i], scf, rcp);
-      if (POOL == 3) q[i] = static_cast<uint32_t>(max(-127, min(127, __float2int_rn(y)))) & 0xffu;
-      else q[i] = static_cast<uint32_t>(__nv_cvt_float_to_fp8(fminf(fmaxf(y, -448.f), 448.f), __NV_SATFINITE, __NV_E4M3));
+      for (int i = 0; i < 8; i += 2) {
+        const float2 a = make_float2(x[i], x[i + 1]);
+        const float2 q0 = __fmul2_rn(a, rb2);
+        const float2 y = __ffma2_rn(__ffma2_rn(q0, nb2, a), rb2, q0);
+        qi[i] = max(-127, __float2int_rn(y.x));
+        qi[i + 1] = max(-127, __float2int_rn(y.y));
+      }
+#pragma unroll
+      for (int w = 0; w < 2; ++w) {
+        // cvt.pack d, a, b, c = (c << 16) | (sat8(a) << 8) | sat8(b): the upper pair first, then the lower pair on top
+        uint32_t hi;
+        asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, %3;" : "=r"(hi) : "r"(qi[4 * w + 3]), "r"(qi[4 * w + 2]), "r"(0));
+        asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, %3;" : "=r"(packed[w]) : "r"(qi[4 * w + 1]), "r"(qi[4 * w]), "r"(hi));
+      }
+    } else {
+      uint32_t q[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const float y = div_rn(x[i], scf, rcp);
+        q[i] = static_cast<uint32_t>(__nv_cvt_float_to_fp8(fminf(fmaxf(y, -448.f), 448.f), __NV_SATFINITE, __NV_E4M3));
+      }
+      packed[0] = q[0] | (q[1] << 8) | (q[2] << 16) | (q[3] << 24);
+      packed[1] = q[4] | (q[5] << 8) | (q[6] << 16) | (q[7] << 24);
     }
     if (write) {
       *reinterpret_cast<uint2*>(reinterpret_cast<uint8_t*>(pool) + dst_row * D + l * 8) =
-          make_uint2(q[0] | (q[1] << 8) | (q[2] << 16) | (q[3] << 24), q[4] | (q[5] << 8) | (q[6] << 16) | (q[7] << 24));
+          make_uint2(packed[0], packed[1]);
       if (l == 0) scale_out[dst_row] = sc;
     }
   }

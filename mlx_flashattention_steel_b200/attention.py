@@ -131,14 +131,19 @@ def _set_force_flags(flags: int) -> int:
 # ---------------------------------------------------------------------------
 # raw operator calls (C-ABI)
 # ---------------------------------------------------------------------------
-def _fwd_raw(q, k, v, scale, causal, softcap, window_left, want_lse, stream):
+def _fwd_raw(q, k, v, scale, causal, softcap, window_left, want_lse, stream, out=None, lse=None):
+    """One forward launch.  `out` / `lse` may be caller-owned contiguous buffers (the host pipeline's staging slots)."""
     _require_cuda(q, k, v)
     lib = _lib.load()
     B, Hq, N, D = q.shape
     Hkv, S = k.shape[1], k.shape[2]
     q, k, v = _row_contig(q), _row_contig(k), _row_contig(v)
-    out = torch.empty((B, Hq, N, D), dtype=q.dtype, device=q.device)
-    lse = torch.empty((B, Hq, N), dtype=torch.float32, device=q.device) if want_lse else None
+    if out is None:
+        out = torch.empty((B, Hq, N, D), dtype=q.dtype, device=q.device)
+    if want_lse and lse is None:
+        lse = torch.empty((B, Hq, N), dtype=torch.float32, device=q.device)
+    if not want_lse:
+        lse = None
     code = _DTYPE_CODE[q.dtype]
     d = _desc(code, code, B, Hq, Hkv, N, S, D, scale, causal, softcap, window_left,
               flags=_FORCE_FLAGS, q=q, k=k if S > 0 else None, v=v if S > 0 else None, o=out)

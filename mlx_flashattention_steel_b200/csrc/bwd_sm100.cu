@@ -63,10 +63,12 @@ __device__ __forceinline__ void sts_row(uint32_t addr, int ql, uint32_t v) {
   asm volatile("st.shared.u16 [%0], %1;\n" ::"r"(addr + static_cast<uint32_t>(ql) * 128u), "h"(static_cast<unsigned short>(v)) : "memory");
 }
 
-__device__ __forceinline__ uint32_t pack16b(int dtype, float a, float b) {
-  return dtype == 0 ? Elem<__half>::pack(a, b) : Elem<__nv_bfloat16>::pack(a, b);
+// DT: 0 = float16, 1 = bfloat16 (a template parameter so that each pair is converted once, not once per type)
+template <int DT> __device__ __forceinline__ uint32_t pack16b(float a, float b) {
+  return DT == 0 ? Elem<__half>::pack(a, b) : Elem<__nv_bfloat16>::pack(a, b);
 }
 
+template <int DT>
 __global__ void __launch_bounds__(kThreads, 1)
 bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                  const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmDO, const BwdArgs a) {
@@ -193,8 +195,8 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     // halves dQ = dS.K.  Issue order keeps the pipe fed while the compute warps work on the other half:
     //   ST/DPT a,b (t=0) | PD_a -> dV_a dK_a, ST/DPT a (t+1) | PD_b -> dV_b dK_b, dQ, ST/DPT b (t+1) | ...
     const bool leader = lane == 0;
-    const uint32_t id_st = instr_desc(a.dtype, 0, 128, 64);     // S^T, dP^T of one half: B K-major, N = 64
-    const uint32_t id_mn = instr_desc(a.dtype, 1, 128, HD);     // dV, dK, dQ: B MN-major, N = 64
+    const uint32_t id_st = instr_desc(DT, 0, 128, 64);     // S^T, dP^T of one half: B K-major, N = 64
+    const uint32_t id_mn = instr_desc(DT, 1, 128, HD);     // dV, dK, dQ: B MN-major, N = 64
     const uint64_t kd = smem_desc(smem_u32(sK), 16, 1024), vd = smem_desc(smem_u32(sV), 16, 1024);
     const uint64_t kmn = smem_desc(smem_u32(sK), kTileBytes, 1024);
     const uint64_t dsd0 = smem_desc(smem_u32(sDS), 16, 1024);
@@ -343,8 +345,8 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
               if (!(kin && (!p.causal || key <= qrow + 1 + off))) pe.y = 0.f;
             }
             const float2 dsv = __fmul2_rn(pe, __fadd2_rn(dv, nd));
-            pp[(i + e) >> 1] = pack16b(a.dtype, pe.x, pe.y);
-            const uint32_t dpk = pack16b(a.dtype, dsv.x, dsv.y);
+            pp[(i + e) >> 1] = pack16b<DT>(pe.x, pe.y);
+            const uint32_t dpk = pack16b<DT>(dsv.x, dsv.y);
             pd[(i + e) >> 1] = dpk;
             const int ql = i + e;                          // (q0l + ql) & 7 == ql & 7
             sts_row(dsa[ql & 7], ql, dpk & 0xffffu);
@@ -386,14 +388,14 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
 #pragma unroll
           for (int i = 0; i < 32; i += 8) {
             uint4 vk, vv;
-            vk.x = pack16b(a.dtype, __uint_as_float(rk[i]) * p.scale, __uint_as_float(rk[i + 1]) * p.scale);
-            vk.y = pack16b(a.dtype, __uint_as_float(rk[i + 2]) * p.scale, __uint_as_float(rk[i + 3]) * p.scale);
-            vk.z = pack16b(a.dtype, __uint_as_float(rk[i + 4]) * p.scale, __uint_as_float(rk[i + 5]) * p.scale);
-            vk.w = pack16b(a.dtype, __uint_as_float(rk[i + 6]) * p.scale, __uint_as_float(rk[i + 7]) * p.scale);
-            vv.x = pack16b(a.dtype, __uint_as_float(rv[i]), __uint_as_float(rv[i + 1]));
-            vv.y = pack16b(a.dtype, __uint_as_float(rv[i + 2]), __uint_as_float(rv[i + 3]));
-            vv.z = pack16b(a.dtype, __uint_as_float(rv[i + 4]), __uint_as_float(rv[i + 5]));
-            vv.w = pack16b(a.dtype, __uint_as_float(rv[i + 6]), __uint_as_float(rv[i + 7]));
+            vk.x = pack16b<DT>(__uint_as_float(rk[i]) * p.scale, __uint_as_float(rk[i + 1]) * p.scale);
+            vk.y = pack16b<DT>(__uint_as_float(rk[i + 2]) * p.scale, __uint_as_float(rk[i + 3]) * p.scale);
+            vk.z = pack16b<DT>(__uint_as_float(rk[i + 4]) * p.scale, __uint_as_float(rk[i + 5]) * p.scale);
+            vk.w = pack16b<DT>(__uint_as_float(rk[i + 6]) * p.scale, __uint_as_float(rk[i + 7]) * p.scale);
+            vv.x = pack16b<DT>(__uint_as_float(rv[i]), __uint_as_float(rv[i + 1]));
+            vv.y = pack16b<DT>(__uint_as_float(rv[i + 2]), __uint_as_float(rv[i + 3]));
+            vv.z = pack16b<DT>(__uint_as_float(rv[i + 4]), __uint_as_float(rv[i + 5]));
+            vv.w = pack16b<DT>(__uint_as_float(rv[i + 6]), __uint_as_float(rv[i + 7]));
             *reinterpret_cast<uint4*>(dkp + i) = vk;
             *reinterpret_cast<uint4*>(dvp + i) = vv;
           }
@@ -443,10 +445,17 @@ cudaError_t launch_bwd_sm100_main(const BwdParams& p, int dtype, int nbatch, int
   BwdArgs a;
   a.p = p;
   a.dtype = dtype;
-  cudaError_t e = cudaFuncSetAttribute(bwd_sm100_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
-  if (e != cudaSuccess) return e;
   dim3 grid((max_k + BK - 1) / BK, p.Hkv, nbatch);
-  bwd_sm100_kernel<<<grid, kThreads, kSmemBytes, stream>>>(tmQ, tmK, tmV, tmDO, a);
+  cudaError_t e;
+  if (dtype == 0) {
+    e = cudaFuncSetAttribute(bwd_sm100_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+    if (e != cudaSuccess) return e;
+    bwd_sm100_kernel<0><<<grid, kThreads, kSmemBytes, stream>>>(tmQ, tmK, tmV, tmDO, a);
+  } else {
+    e = cudaFuncSetAttribute(bwd_sm100_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+    if (e != cudaSuccess) return e;
+    bwd_sm100_kernel<1><<<grid, kThreads, kSmemBytes, stream>>>(tmQ, tmK, tmV, tmDO, a);
+  }
   return cudaGetLastError();
 }
 

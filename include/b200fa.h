@@ -71,6 +71,9 @@ typedef struct b200fa_desc {
   int32_t window_left;  /* -1 = off; key j visible iff j >= i + (S-N) - window_left */
   int32_t num_splits;   /* decode: 0 = choose automatically */
   int32_t flags;
+  const float* alibi_slopes; /* NULL = off; device float32 [Hq]: slope[h] * (j - (i + S - N)) is added to the scaled
+                                (and soft-capped) score of row i, key j (csrc/mfa_steel_fwd.cpp:951-970).  Dense
+                                forward and backward only; served by the portable kernels. */
 } b200fa_desc;
 
 typedef struct b200fa_device_info_t {

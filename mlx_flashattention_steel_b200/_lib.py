@@ -44,6 +44,7 @@ class Desc(C.Structure):
         ("window_left", C.c_int32),
         ("num_splits", C.c_int32),
         ("flags", C.c_int32),
+        ("alibi_slopes", C.c_void_p),
     ]
 
 

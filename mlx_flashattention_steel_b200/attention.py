@@ -99,7 +99,7 @@ def _ptr(t: Optional[torch.Tensor]):
 
 
 def _desc(dtype, kv_dtype, B, Hq, Hkv, N, S, D, scale, causal, softcap=0.0, window_left=-1,
-          num_splits=0, flags=0, q=None, k=None, v=None, o=None) -> _lib.Desc:
+          num_splits=0, flags=0, q=None, k=None, v=None, o=None, alibi=None) -> _lib.Desc:
     d = _lib.Desc()
     d.dtype, d.kv_dtype = dtype, kv_dtype
     d.B, d.Hq, d.Hkv, d.N, d.S, d.D = B, Hq, Hkv, N, S, D
@@ -115,6 +115,7 @@ def _desc(dtype, kv_dtype, B, Hq, Hkv, N, S, D, scale, causal, softcap=0.0, wind
     d.window_left = int(window_left)
     d.num_splits = int(num_splits)
     d.flags = int(flags)
+    d.alibi_slopes = None if alibi is None else alibi.data_ptr()
     return d
 
 
@@ -131,7 +132,7 @@ def _set_force_flags(flags: int) -> int:
 # ---------------------------------------------------------------------------
 # raw operator calls (C-ABI)
 # ---------------------------------------------------------------------------
-def _fwd_raw(q, k, v, scale, causal, softcap, window_left, want_lse, stream, out=None, lse=None):
+def _fwd_raw(q, k, v, scale, causal, softcap, window_left, want_lse, stream, out=None, lse=None, alibi=None):
     """One forward launch.  `out` / `lse` may be caller-owned contiguous buffers (the host pipeline's staging slots)."""
     _require_cuda(q, k, v)
     lib = _lib.load()
@@ -146,7 +147,7 @@ def _fwd_raw(q, k, v, scale, causal, softcap, window_left, want_lse, stream, out
         lse = None
     code = _DTYPE_CODE[q.dtype]
     d = _desc(code, code, B, Hq, Hkv, N, S, D, scale, causal, softcap, window_left,
-              flags=_FORCE_FLAGS, q=q, k=k if S > 0 else None, v=v if S > 0 else None, o=out)
+              flags=_FORCE_FLAGS, q=q, k=k if S > 0 else None, v=v if S > 0 else None, o=out, alibi=alibi)
     with torch.cuda.device(q.device):
         st = lib.b200fa_fwd(C.byref(d), _ptr(q), _ptr(k), _ptr(v), _ptr(out), _ptr(lse), None, 0,
                             C.c_void_p(_stream_ptr(stream, q.device)))
@@ -154,7 +155,7 @@ def _fwd_raw(q, k, v, scale, causal, softcap, window_left, want_lse, stream, out
     return out, lse
 
 
-def _bwd_raw(q, k, v, out, lse, dout, scale, causal, stream, cu=None):
+def _bwd_raw(q, k, v, out, lse, dout, scale, causal, stream, cu=None, alibi=None):
     _require_cuda(q, k, v, out, lse, dout)
     lib = _lib.load()
     B, Hq, N, D = q.shape
@@ -166,7 +167,7 @@ def _bwd_raw(q, k, v, out, lse, dout, scale, causal, stream, cu=None):
     dk = torch.empty((B, Hkv, S, D), dtype=q.dtype, device=q.device)
     dv = torch.empty((B, Hkv, S, D), dtype=q.dtype, device=q.device)
     code = _DTYPE_CODE[q.dtype]
-    d = _desc(code, code, B, Hq, Hkv, N, S, D, scale, causal, flags=_FORCE_FLAGS, q=q, k=k, v=v, o=out)
+    d = _desc(code, code, B, Hq, Hkv, N, S, D, scale, causal, flags=_FORCE_FLAGS, q=q, k=k, v=v, o=out, alibi=alibi)
     sp = C.c_void_p(_stream_ptr(stream, q.device))
     with torch.cuda.device(q.device):
         if cu is None:
@@ -189,11 +190,12 @@ class _FlashAttnFn(torch.autograd.Function):
     """Autograd glue; role of _make_mfa_custom (mlx_mfa/attention.py:1931-2030)."""
 
     @staticmethod
-    def forward(ctx, q, k, v, scale, causal, softcap, window_left, want_lse, stream):
+    def forward(ctx, q, k, v, scale, causal, softcap, window_left, want_lse, stream, alibi=None):
         need_grad = q.requires_grad or k.requires_grad or v.requires_grad
-        out, lse = _fwd_raw(q, k, v, scale, causal, softcap, window_left, want_lse or need_grad, stream)
+        out, lse = _fwd_raw(q, k, v, scale, causal, softcap, window_left, want_lse or need_grad, stream, alibi=alibi)
         ctx.save_for_backward(q, k, v, out, lse if lse is not None else torch.empty(0, device=q.device))
         ctx.cfg = (scale, causal, softcap, window_left, stream)
+        ctx.alibi = alibi          # a constant of the graph: the slopes get no gradient (mlx_mfa/attention.py:1909)
         if want_lse:
             ctx.mark_non_differentiable(lse)
             return out, lse
@@ -213,8 +215,8 @@ class _FlashAttnFn(torch.autograd.Function):
                 "flash_attention backward for float32: the reference differentiates its SDPA fallback "
                 "(mlx_mfa/attention.py:2013-2019); the CUDA backward takes f16/bf16."
             )
-        dq, dk, dv = _bwd_raw(q, k, v, out, lse, dout, scale, causal, stream)
-        return dq, dk, dv, None, None, None, None, None, None
+        dq, dk, dv = _bwd_raw(q, k, v, out, lse, dout, scale, causal, stream, alibi=ctx.alibi)
+        return dq, dk, dv, None, None, None, None, None, None, None
 
 
 # ---------------------------------------------------------------------------
@@ -287,8 +289,14 @@ def flash_attention(
         raise NotImplementedError("dropout_p > 0 needs the reference's SDPA fallback; not built.")
     if attn_bias is not None:
         raise NotImplementedError("attn_bias needs the reference's SDPA fallback; not built.")
+    alibi = None
     if alibi_slopes is not None:
-        raise NotImplementedError("alibi_slopes is not built.")
+        # per-head linear position bias slope[h] * (j - i) (mlx_mfa/attention.py:77-81, 1774-1822); float32 [Hq]
+        alibi = _as_tensor(alibi_slopes, "alibi_slopes")
+        if alibi.ndim != 1 or alibi.shape[0] != q_heads:
+            raise ValueError(f"alibi_slopes must be [H_q] = [{q_heads}], got {tuple(alibi.shape)}.")
+        _require_cuda(alibi)
+        alibi = alibi.to(torch.float32).contiguous()
     supported = head_dim in _SUPPORTED_HDIMS and q.dtype in _DTYPE_CODE and v_dim == q_dim
     if not supported:
         msg = (
@@ -313,7 +321,7 @@ def flash_attention(
         window_left = max(int(window_size[0]), 0)
 
     out, lse = _FlashAttnFn.apply(q, k, v, float(scale), bool(causal), float(softcap), window_left,
-                                  bool(return_lse), stream)
+                                  bool(return_lse), stream, alibi)
     if return_lse:
         return out, lse
     return out

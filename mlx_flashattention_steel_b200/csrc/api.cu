@@ -101,6 +101,7 @@ int32_t fill_fwd_params(const b200fa_desc* d, const void* q, const void* k, cons
   p->softcap = d->softcap;
   p->causal = d->causal ? 1 : 0;
   p->window_left = d->window_left;
+  p->alibi = d->alibi_slopes;
   return B200FA_OK;
 }
 
@@ -161,7 +162,7 @@ int32_t b200fa_fwd(const b200fa_desc* d, const void* q, const void* k, const voi
   cudaError_t e;
   if (d->dtype == B200FA_F32) {
     e = b200fa::launch_fwd_f32(p, d->D, false, d->B, d->N, cs);
-  } else if (!(d->flags & B200FA_FLAG_FORCE_MMA_SYNC) && b200fa::fwd_sm100_supported(p, d->dtype, d->D)) {
+  } else if (!(d->flags & B200FA_FLAG_FORCE_MMA_SYNC) && p.alibi == nullptr && b200fa::fwd_sm100_supported(p, d->dtype, d->D)) {
     e = b200fa::launch_fwd_sm100(p, d->dtype, d->D, d->B, d->N, cs);
   } else {
     e = b200fa::launch_fwd_mma(p, d->dtype, d->D, false, d->B, d->N, cs);
@@ -191,6 +192,7 @@ int32_t b200fa_fwd_varlen(const b200fa_desc* d, const void* q, const void* k, co
   b200fa::FwdParams p;
   st = fill_fwd_params(d, q, k, v, out, lse, &p);
   if (st != B200FA_OK) return st;
+  if (d->alibi_slopes != nullptr) return fail(B200FA_ERR_UNSUPPORTED, "alibi_slopes with packed sequences is not built");
   p.cu_q = cu_seqlens_q;
   p.cu_k = cu_seqlens_k;
   cudaStream_t cs = reinterpret_cast<cudaStream_t>(stream);
@@ -247,8 +249,11 @@ static int32_t bwd_common(const b200fa_desc* d, const void* q, const void* k, co
   p.B = d->B; p.Hq = d->Hq; p.Hkv = d->Hkv; p.N = d->N; p.S = d->S;
   p.gqa = f.gqa; p.scale = d->scale; p.scale_log2 = f.scale_log2; p.causal = f.causal;
   p.cu_q = cu_q; p.cu_k = cu_k;
+  if (d->alibi_slopes != nullptr && varlen) return fail(B200FA_ERR_UNSUPPORTED, "alibi_slopes with packed sequences is not built");
+  p.alibi = d->alibi_slopes;       // the biased scores are recomputed by the portable kernel only
   cudaError_t e = b200fa::launch_bwd(p, d->dtype, d->D, varlen, nbatch, max_q, max_k, workspace,
-                                     !(d->flags & B200FA_FLAG_FORCE_MMA_SYNC), reinterpret_cast<cudaStream_t>(stream));
+                                     !(d->flags & B200FA_FLAG_FORCE_MMA_SYNC) && p.alibi == nullptr,
+                                     reinterpret_cast<cudaStream_t>(stream));
   if (e != cudaSuccess) return cuda_fail(e, "backward launch");
   return B200FA_OK;
 }

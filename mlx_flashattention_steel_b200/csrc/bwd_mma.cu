@@ -172,6 +172,7 @@ __global__ void __launch_bounds__(kThreads) bwd_main_kernel(const BwdParams p) {
       cp_async_commit();
     }
     const uint32_t sQ_u = smem_u32(sQ + stage * kBM * D), sdO_u = smem_u32(sdO + stage * kBM * D);
+    const float alibi_l2 = p.alibi != nullptr ? p.alibi[hq] * kLog2e : 0.f;      // the bias the forward added
     const float* Ls = sL + stage * kBM;
     const float* Ds = sDel + stage * kBM;
 
@@ -215,7 +216,8 @@ __global__ void __launch_bounds__(kThreads) bwd_main_kernel(const BwdParams p) {
         bool vis = key < S;
         if (p.causal) vis = vis && (key <= qrow + off);
         const float L = Ls[ql];
-        const float pe = (vis && L != -INFINITY) ? fast_exp2(fmaf(st[j][e], p.scale_log2, -L)) : 0.f;
+        const float sc = fmaf(alibi_l2, static_cast<float>(key - (qrow + off)), st[j][e] * p.scale_log2);
+        const float pe = (vis && L != -INFINITY) ? fast_exp2(sc - L) : 0.f;
         pv[e] = pe;
         dsv[e] = pe * (dp[j][e] - Ds[ql]);
       }

@@ -33,6 +33,7 @@ struct FwdParams {
   int window_left;       // -1 = off
   const int* cu_q;       // varlen only
   const int* cu_k;
+  const float* alibi;    // per q-head slopes, or null
 };
 
 // Backward parameter block.  Role of MFASteelBackwardParams
@@ -63,6 +64,7 @@ struct BwdParams {
   int causal;
   const int* cu_q;
   const int* cu_k;
+  const float* alibi;    // per q-head slopes, or null
 };
 
 // ---------------------------------------------------------------------------

@@ -79,6 +79,7 @@ __global__ void __launch_bounds__(kThreads) fa_fwd_f32_kernel(const FwdParams p)
   load_rows<D>(sQ, qg, p.q_rs, q0, N, tid);
 
   const bool use_cap = p.softcap > 0.f;
+  const float alibi = p.alibi != nullptr ? p.alibi[head] : 0.f;
 
   for (int kt = kt_begin; kt < kt_end; ++kt) {
     const int k0 = kt * kBK;
@@ -119,6 +120,7 @@ __global__ void __launch_bounds__(kThreads) fa_fwd_f32_kernel(const FwdParams p)
         const int col = k0 + tx + 16 * j;
         float sc = acc[i][j] * p.scale;
         if (use_cap) sc = tanhf(sc / p.softcap) * p.softcap;
+        if (p.alibi != nullptr) sc = fmaf(alibi, static_cast<float>(col - (row + off)), sc);
         sc *= kLog2e;
         bool vis = col < S;
         if (p.causal) vis = vis && (col <= row + off);

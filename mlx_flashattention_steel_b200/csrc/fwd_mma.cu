@@ -90,6 +90,7 @@ __global__ void __launch_bounds__(kThreads) fa_fwd_mma_kernel(const FwdParams p)
   const bool use_cap = p.softcap > 0.f;
   const float cap_in = use_cap ? p.scale / p.softcap : 0.f;
   const float cap_out = p.softcap * kLog2e;
+  const float alibi_l2 = p.alibi != nullptr ? p.alibi[head] * kLog2e : 0.f;
 
   for (int kt = kt_begin; kt < kt_end; ++kt) {
     const int stage = (kt - kt_begin) & 1;
@@ -134,6 +135,18 @@ __global__ void __launch_bounds__(kThreads) fa_fwd_mma_kernel(const FwdParams p)
       for (int i = 0; i < kBK / 8; ++i)
 #pragma unroll
         for (int e = 0; e < 4; ++e) s[i][e] *= p.scale_log2;
+    }
+    if (p.alibi != nullptr) {
+      // ALiBi: slope * (key - query position), in the base-2 domain, after scale / softcap and before the masks
+#pragma unroll
+      for (int i = 0; i < kBK / 8; ++i) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int col = k0 + i * 8 + 2 * t + (e & 1);
+          const int row = (e < 2) ? r0 : r1;
+          s[i][e] = fmaf(alibi_l2, static_cast<float>(col - (row + off)), s[i][e]);
+        }
+      }
     }
     const bool need_mask = (k0 + kBK > S) || (p.causal && (k0 + kBK - 1 > q0 + off)) ||
                            (p.window_left >= 0 && (k0 < q0 + kBQ - 1 + off - p.window_left));

@@ -55,6 +55,7 @@ def sdpa(
     window_left: int = -1,
     faithful: bool = False,
     row_block: int = 1024,
+    alibi_slopes: Optional[torch.Tensor] = None,
 ) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
     """Dense attention.  q [B,Hq,N,D], k/v [B,Hkv,S,D] (CPU tensors, any float dtype).
 
@@ -67,7 +68,10 @@ def sdpa(
     probabilities cast to q.dtype before A @ V).  GQA: query head h reads kv head
     h // (Hq/Hkv) (csrc/mfa_steel_fwd.cpp:545), as the tests do with mx.repeat
     (tests/test_attention.py:458-460).  Rows with no visible key give O = 0,
-    L = -inf.
+    L = -inf.  alibi_slopes [Hq]: slope[h] * (j - (i + S - N)) is added after the
+    cap and before the mask (_alibi_sdpa_ref, mlx_mfa/attention.py:1774-1822, with
+    the kernel's query position i + qL_off, csrc/mfa_steel_fwd.cpp:951-970; the two
+    differ by a per-row constant, which the softmax cancels).
     """
     B, Hq, N, D = q.shape
     Hkv, S = k.shape[1], k.shape[2]
@@ -90,6 +94,10 @@ def sdpa(
         if softcap > 0:
             s = torch.tanh(s / softcap) * softcap
         s = s.to(sdt)
+        if alibi_slopes is not None:
+            qpos = torch.arange(rows.start, rows.stop, dtype=sdt)[:, None] + (S - N)
+            kpos = torch.arange(S, dtype=sdt)[None, :]
+            s = s + alibi_slopes.to(sdt)[None, :, None, None] * (kpos - qpos)[None, None]
         vis = _visible(N, S, causal, window_left, rows)
         if vis is not None:
             s = s.masked_fill(~vis, float("-inf"))

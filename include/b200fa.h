@@ -74,6 +74,11 @@ typedef struct b200fa_desc {
   const float* alibi_slopes; /* NULL = off; device float32 [Hq]: slope[h] * (j - (i + S - N)) is added to the scaled
                                 (and soft-capped) score of row i, key j (csrc/mfa_steel_fwd.cpp:951-970).  Dense
                                 forward and backward only; served by the portable kernels. */
+  const uint8_t* block_mask; /* NULL = off; device bytes [ceil(N/mask_bq), mask_nk]: row i sees key j only if
+                                block_mask[i / mask_bq][j / mask_bk] != 0 (flash_attention_sparse,
+                                mlx_mfa/attention.py:1219-1311).  Key tiles without an active block are skipped.
+                                Dense 16-bit forward and backward; served by the portable kernels. */
+  int32_t mask_bq, mask_bk, mask_nk;
 } b200fa_desc;
 
 typedef struct b200fa_device_info_t {

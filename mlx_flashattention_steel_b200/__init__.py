@@ -24,6 +24,7 @@ from .packed import (
     flash_attention_varlen_kv_packed,
     flash_attention_varlen_qkv_packed,
 )
+from .sparse import flash_attention_sparse, make_causal_block_mask, make_sliding_window_mask
 from .rope import apply_rope, flash_attention_rope, make_rope_3d_tables
 
 __version__ = "0.1.0"
@@ -35,6 +36,9 @@ __all__ = [
     "flash_attention_paged",
     "paged_kv_gather",
     "flash_attention_rope",
+    "flash_attention_sparse",
+    "make_causal_block_mask",
+    "make_sliding_window_mask",
     "flash_attention_qkv_packed",
     "flash_attention_kv_packed",
     "flash_attention_varlen_qkv_packed",

@@ -45,6 +45,10 @@ class Desc(C.Structure):
         ("num_splits", C.c_int32),
         ("flags", C.c_int32),
         ("alibi_slopes", C.c_void_p),
+        ("block_mask", C.c_void_p),
+        ("mask_bq", C.c_int32),
+        ("mask_bk", C.c_int32),
+        ("mask_nk", C.c_int32),
     ]
 
 

@@ -99,7 +99,7 @@ def _ptr(t: Optional[torch.Tensor]):
 
 
 def _desc(dtype, kv_dtype, B, Hq, Hkv, N, S, D, scale, causal, softcap=0.0, window_left=-1,
-          num_splits=0, flags=0, q=None, k=None, v=None, o=None, alibi=None) -> _lib.Desc:
+          num_splits=0, flags=0, q=None, k=None, v=None, o=None, alibi=None, bmask=None) -> _lib.Desc:
     d = _lib.Desc()
     d.dtype, d.kv_dtype = dtype, kv_dtype
     d.B, d.Hq, d.Hkv, d.N, d.S, d.D = B, Hq, Hkv, N, S, D
@@ -116,6 +116,9 @@ def _desc(dtype, kv_dtype, B, Hq, Hkv, N, S, D, scale, causal, softcap=0.0, wind
     d.num_splits = int(num_splits)
     d.flags = int(flags)
     d.alibi_slopes = None if alibi is None else alibi.data_ptr()
+    if bmask is not None:            # (uint8 tensor [NQ, NK], block rows, block columns)
+        d.block_mask = bmask[0].data_ptr()
+        d.mask_bq, d.mask_bk, d.mask_nk = int(bmask[1]), int(bmask[2]), int(bmask[0].shape[1])
     return d
 
 
@@ -132,7 +135,8 @@ def _set_force_flags(flags: int) -> int:
 # ---------------------------------------------------------------------------
 # raw operator calls (C-ABI)
 # ---------------------------------------------------------------------------
-def _fwd_raw(q, k, v, scale, causal, softcap, window_left, want_lse, stream, out=None, lse=None, alibi=None):
+def _fwd_raw(q, k, v, scale, causal, softcap, window_left, want_lse, stream, out=None, lse=None, alibi=None,
+             bmask=None):
     """One forward launch.  `out` / `lse` may be caller-owned contiguous buffers (the host pipeline's staging slots)."""
     _require_cuda(q, k, v)
     lib = _lib.load()
@@ -147,7 +151,7 @@ def _fwd_raw(q, k, v, scale, causal, softcap, window_left, want_lse, stream, out
         lse = None
     code = _DTYPE_CODE[q.dtype]
     d = _desc(code, code, B, Hq, Hkv, N, S, D, scale, causal, softcap, window_left,
-              flags=_FORCE_FLAGS, q=q, k=k if S > 0 else None, v=v if S > 0 else None, o=out, alibi=alibi)
+              flags=_FORCE_FLAGS, q=q, k=k if S > 0 else None, v=v if S > 0 else None, o=out, alibi=alibi, bmask=bmask)
     with torch.cuda.device(q.device):
         st = lib.b200fa_fwd(C.byref(d), _ptr(q), _ptr(k), _ptr(v), _ptr(out), _ptr(lse), None, 0,
                             C.c_void_p(_stream_ptr(stream, q.device)))
@@ -155,7 +159,7 @@ def _fwd_raw(q, k, v, scale, causal, softcap, window_left, want_lse, stream, out
     return out, lse
 
 
-def _bwd_raw(q, k, v, out, lse, dout, scale, causal, stream, cu=None, alibi=None):
+def _bwd_raw(q, k, v, out, lse, dout, scale, causal, stream, cu=None, alibi=None, bmask=None):
     _require_cuda(q, k, v, out, lse, dout)
     lib = _lib.load()
     B, Hq, N, D = q.shape
@@ -167,7 +171,7 @@ def _bwd_raw(q, k, v, out, lse, dout, scale, causal, stream, cu=None, alibi=None
     dk = torch.empty((B, Hkv, S, D), dtype=q.dtype, device=q.device)
     dv = torch.empty((B, Hkv, S, D), dtype=q.dtype, device=q.device)
     code = _DTYPE_CODE[q.dtype]
-    d = _desc(code, code, B, Hq, Hkv, N, S, D, scale, causal, flags=_FORCE_FLAGS, q=q, k=k, v=v, o=out, alibi=alibi)
+    d = _desc(code, code, B, Hq, Hkv, N, S, D, scale, causal, flags=_FORCE_FLAGS, q=q, k=k, v=v, o=out, alibi=alibi, bmask=bmask)
     sp = C.c_void_p(_stream_ptr(stream, q.device))
     with torch.cuda.device(q.device):
         if cu is None:
@@ -190,9 +194,11 @@ class _FlashAttnFn(torch.autograd.Function):
     """Autograd glue; role of _make_mfa_custom (mlx_mfa/attention.py:1931-2030)."""
 
     @staticmethod
-    def forward(ctx, q, k, v, scale, causal, softcap, window_left, want_lse, stream, alibi=None):
+    def forward(ctx, q, k, v, scale, causal, softcap, window_left, want_lse, stream, alibi=None, bmask=None):
         need_grad = q.requires_grad or k.requires_grad or v.requires_grad
-        out, lse = _fwd_raw(q, k, v, scale, causal, softcap, window_left, want_lse or need_grad, stream, alibi=alibi)
+        out, lse = _fwd_raw(q, k, v, scale, causal, softcap, window_left, want_lse or need_grad, stream, alibi=alibi,
+                            bmask=bmask)
+        ctx.bmask = bmask
         ctx.save_for_backward(q, k, v, out, lse if lse is not None else torch.empty(0, device=q.device))
         ctx.cfg = (scale, causal, softcap, window_left, stream)
         ctx.alibi = alibi          # a constant of the graph: the slopes get no gradient (mlx_mfa/attention.py:1909)
@@ -215,8 +221,8 @@ class _FlashAttnFn(torch.autograd.Function):
                 "flash_attention backward for float32: the reference differentiates its SDPA fallback "
                 "(mlx_mfa/attention.py:2013-2019); the CUDA backward takes f16/bf16."
             )
-        dq, dk, dv = _bwd_raw(q, k, v, out, lse, dout, scale, causal, stream, alibi=ctx.alibi)
-        return dq, dk, dv, None, None, None, None, None, None, None
+        dq, dk, dv = _bwd_raw(q, k, v, out, lse, dout, scale, causal, stream, alibi=ctx.alibi, bmask=ctx.bmask)
+        return dq, dk, dv, None, None, None, None, None, None, None, None
 
 
 # ---------------------------------------------------------------------------

@@ -102,6 +102,13 @@ int32_t fill_fwd_params(const b200fa_desc* d, const void* q, const void* k, cons
   p->causal = d->causal ? 1 : 0;
   p->window_left = d->window_left;
   p->alibi = d->alibi_slopes;
+  p->bmask = d->block_mask;
+  p->bm_bq = d->mask_bq; p->bm_bk = d->mask_bk; p->bm_nk = d->mask_nk;
+  if (d->block_mask != nullptr) {
+    if (d->mask_bq <= 0 || d->mask_bk <= 0 || static_cast<int64_t>(d->mask_nk) * d->mask_bk < d->S)
+      return fail(B200FA_ERR_INVALID_ARG, "block_mask: block sizes must be positive and mask_nk * mask_bk cover S");
+    if (d->dtype == B200FA_F32) return fail(B200FA_ERR_UNSUPPORTED, "block_mask takes f16 / bf16");
+  }
   return B200FA_OK;
 }
 
@@ -162,7 +169,8 @@ int32_t b200fa_fwd(const b200fa_desc* d, const void* q, const void* k, const voi
   cudaError_t e;
   if (d->dtype == B200FA_F32) {
     e = b200fa::launch_fwd_f32(p, d->D, false, d->B, d->N, cs);
-  } else if (!(d->flags & B200FA_FLAG_FORCE_MMA_SYNC) && p.alibi == nullptr && b200fa::fwd_sm100_supported(p, d->dtype, d->D)) {
+  } else if (!(d->flags & B200FA_FLAG_FORCE_MMA_SYNC) && p.alibi == nullptr && p.bmask == nullptr &&
+             b200fa::fwd_sm100_supported(p, d->dtype, d->D)) {
     e = b200fa::launch_fwd_sm100(p, d->dtype, d->D, d->B, d->N, cs);
   } else {
     e = b200fa::launch_fwd_mma(p, d->dtype, d->D, false, d->B, d->N, cs);
@@ -192,7 +200,8 @@ int32_t b200fa_fwd_varlen(const b200fa_desc* d, const void* q, const void* k, co
   b200fa::FwdParams p;
   st = fill_fwd_params(d, q, k, v, out, lse, &p);
   if (st != B200FA_OK) return st;
-  if (d->alibi_slopes != nullptr) return fail(B200FA_ERR_UNSUPPORTED, "alibi_slopes with packed sequences is not built");
+  if (d->alibi_slopes != nullptr || d->block_mask != nullptr)
+    return fail(B200FA_ERR_UNSUPPORTED, "alibi_slopes / block_mask with packed sequences are not built");
   p.cu_q = cu_seqlens_q;
   p.cu_k = cu_seqlens_k;
   cudaStream_t cs = reinterpret_cast<cudaStream_t>(stream);
@@ -249,10 +258,13 @@ static int32_t bwd_common(const b200fa_desc* d, const void* q, const void* k, co
   p.B = d->B; p.Hq = d->Hq; p.Hkv = d->Hkv; p.N = d->N; p.S = d->S;
   p.gqa = f.gqa; p.scale = d->scale; p.scale_log2 = f.scale_log2; p.causal = f.causal;
   p.cu_q = cu_q; p.cu_k = cu_k;
-  if (d->alibi_slopes != nullptr && varlen) return fail(B200FA_ERR_UNSUPPORTED, "alibi_slopes with packed sequences is not built");
-  p.alibi = d->alibi_slopes;       // the biased scores are recomputed by the portable kernel only
+  if ((d->alibi_slopes != nullptr || d->block_mask != nullptr) && varlen)
+    return fail(B200FA_ERR_UNSUPPORTED, "alibi_slopes / block_mask with packed sequences are not built");
+  p.alibi = d->alibi_slopes;       // biased / block-masked scores are recomputed by the portable kernel only
+  p.bmask = d->block_mask;
+  p.bm_bq = d->mask_bq; p.bm_bk = d->mask_bk; p.bm_nk = d->mask_nk;
   cudaError_t e = b200fa::launch_bwd(p, d->dtype, d->D, varlen, nbatch, max_q, max_k, workspace,
-                                     !(d->flags & B200FA_FLAG_FORCE_MMA_SYNC) && p.alibi == nullptr,
+                                     !(d->flags & B200FA_FLAG_FORCE_MMA_SYNC) && p.alibi == nullptr && p.bmask == nullptr,
                                      reinterpret_cast<cudaStream_t>(stream));
   if (e != cudaSuccess) return cuda_fail(e, "backward launch");
   return B200FA_OK;

@@ -215,6 +215,7 @@ __global__ void __launch_bounds__(kThreads) bwd_main_kernel(const BwdParams p) {
         const int qrow = m * kBM + ql;
         bool vis = key < S;
         if (p.causal) vis = vis && (key <= qrow + off);
+        if (p.bmask != nullptr && vis) vis = p.bmask[(min(qrow, N - 1) / p.bm_bq) * p.bm_nk + key / p.bm_bk] != 0;
         const float L = Ls[ql];
         const float sc = fmaf(alibi_l2, static_cast<float>(key - (qrow + off)), st[j][e] * p.scale_log2);
         const float pe = (vis && L != -INFINITY) ? fast_exp2(sc - L) : 0.f;

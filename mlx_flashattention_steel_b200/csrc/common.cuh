@@ -34,6 +34,8 @@ struct FwdParams {
   const int* cu_q;       // varlen only
   const int* cu_k;
   const float* alibi;    // per q-head slopes, or null
+  const unsigned char* bmask;  // block mask bytes [rows / bm_bq][bm_nk], or null
+  int bm_bq, bm_bk, bm_nk;
 };
 
 // Backward parameter block.  Role of MFASteelBackwardParams
@@ -65,6 +67,8 @@ struct BwdParams {
   const int* cu_q;
   const int* cu_k;
   const float* alibi;    // per q-head slopes, or null
+  const unsigned char* bmask;  // block mask bytes [rows / bm_bq][bm_nk], or null
+  int bm_bq, bm_bk, bm_nk;
 };
 
 // ---------------------------------------------------------------------------

@@ -75,10 +75,32 @@ __global__ void __launch_bounds__(kThreads) fa_fwd_mma_kernel(const FwdParams p)
   float row_max[2] = {-INFINITY, -INFINITY};
   float row_sum[2] = {0.f, 0.f};
 
+  // Block-sparse mask: a key tile is visited only if one of its (query block, key block) cells is active; every
+  // thread scans the same few bytes, so the decision is uniform across the CTA.  Bit 0 of the result: some cell
+  // active; bit 1: all cells active (no per-element masking needed for this tile).
+  auto tile_cells = [&](int kt) -> int {
+    if (p.bmask == nullptr) return 3;
+    const int rb0 = q0 / p.bm_bq, rb1 = (min(q0 + kBQ, N) - 1) / p.bm_bq;
+    const int cb0 = (kt * kBK) / p.bm_bk, cb1 = (min((kt + 1) * kBK, S) - 1) / p.bm_bk;
+    bool any = false, all = true;
+    for (int rb = rb0; rb <= rb1; ++rb)
+      for (int cb = cb0; cb <= cb1; ++cb) {
+        const bool on = p.bmask[rb * p.bm_nk + cb] != 0;
+        any = any || on;
+        all = all && on;
+      }
+    return (any ? 1 : 0) | (all ? 2 : 0);
+  };
+  auto next_active = [&](int kt) -> int {
+    while (kt < kt_end && !(tile_cells(kt) & 1)) ++kt;
+    return kt;
+  };
+
   load_tile_async<kBQ, D>(sQ, qg, p.q_rs, q0, N, tid);
-  if (kt_begin < kt_end) {
-    load_tile_async<kBK, D>(sK, kg, p.k_rs, kt_begin * kBK, S, tid);
-    load_tile_async<kBK, D>(sV, vg, p.v_rs, kt_begin * kBK, S, tid);
+  const int kt_first = next_active(kt_begin);
+  if (kt_first < kt_end) {
+    load_tile_async<kBK, D>(sK, kg, p.k_rs, kt_first * kBK, S, tid);
+    load_tile_async<kBK, D>(sV, vg, p.v_rs, kt_first * kBK, S, tid);
   }
   cp_async_commit();
 
@@ -92,13 +114,14 @@ __global__ void __launch_bounds__(kThreads) fa_fwd_mma_kernel(const FwdParams p)
   const float cap_out = p.softcap * kLog2e;
   const float alibi_l2 = p.alibi != nullptr ? p.alibi[head] * kLog2e : 0.f;
 
-  for (int kt = kt_begin; kt < kt_end; ++kt) {
-    const int stage = (kt - kt_begin) & 1;
+  int stage = 0;
+  for (int kt = kt_first; kt < kt_end; stage ^= 1) {
+    const int kt_next = next_active(kt + 1);
     cp_async_wait<0>();
     __syncthreads();
-    if (kt + 1 < kt_end) {
-      load_tile_async<kBK, D>(sK + (stage ^ 1) * kBK * D, kg, p.k_rs, (kt + 1) * kBK, S, tid);
-      load_tile_async<kBK, D>(sV + (stage ^ 1) * kBK * D, vg, p.v_rs, (kt + 1) * kBK, S, tid);
+    if (kt_next < kt_end) {
+      load_tile_async<kBK, D>(sK + (stage ^ 1) * kBK * D, kg, p.k_rs, kt_next * kBK, S, tid);
+      load_tile_async<kBK, D>(sV + (stage ^ 1) * kBK * D, vg, p.v_rs, kt_next * kBK, S, tid);
       cp_async_commit();
     }
     const uint32_t sK_u = smem_u32(sK + stage * kBK * D);
@@ -148,8 +171,9 @@ __global__ void __launch_bounds__(kThreads) fa_fwd_mma_kernel(const FwdParams p)
         }
       }
     }
+    const bool cells_partial = !(tile_cells(kt) & 2);
     const bool need_mask = (k0 + kBK > S) || (p.causal && (k0 + kBK - 1 > q0 + off)) ||
-                           (p.window_left >= 0 && (k0 < q0 + kBQ - 1 + off - p.window_left));
+                           (p.window_left >= 0 && (k0 < q0 + kBQ - 1 + off - p.window_left)) || cells_partial;
     if (need_mask) {
 #pragma unroll
       for (int i = 0; i < kBK / 8; ++i) {
@@ -160,6 +184,7 @@ __global__ void __launch_bounds__(kThreads) fa_fwd_mma_kernel(const FwdParams p)
           bool vis = col < S;
           if (p.causal) vis = vis && (col <= row + off);
           if (p.window_left >= 0) vis = vis && (col >= row + off - p.window_left);
+          if (cells_partial && vis) vis = p.bmask[(min(row, N - 1) / p.bm_bq) * p.bm_nk + col / p.bm_bk] != 0;
           if (!vis) s[i][e] = -INFINITY;
         }
       }
@@ -218,6 +243,7 @@ __global__ void __launch_bounds__(kThreads) fa_fwd_mma_kernel(const FwdParams p)
         mma16816<T>(o[2 * dj + 1], a, bfr[2], bfr[3]);
       }
     }
+    kt = kt_next;
   }
   cp_async_wait<0>();
 

@@ -56,6 +56,8 @@ def sdpa(
     faithful: bool = False,
     row_block: int = 1024,
     alibi_slopes: Optional[torch.Tensor] = None,
+    block_mask: Optional[torch.Tensor] = None,
+    block: Tuple[int, int] = (32, 16),
 ) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
     """Dense attention.  q [B,Hq,N,D], k/v [B,Hkv,S,D] (CPU tensors, any float dtype).
 
@@ -71,7 +73,10 @@ def sdpa(
     L = -inf.  alibi_slopes [Hq]: slope[h] * (j - (i + S - N)) is added after the
     cap and before the mask (_alibi_sdpa_ref, mlx_mfa/attention.py:1774-1822, with
     the kernel's query position i + qL_off, csrc/mfa_steel_fwd.cpp:951-970; the two
-    differ by a per-row constant, which the softmax cancels).
+    differ by a per-row constant, which the softmax cancels).  block_mask bool
+    [ceil(N/BQ), ceil(S/BK)] with block = (BQ, BK): element (i, j) is visible only if
+    block_mask[i // BQ, j // BK] (_sparse_fallback_sdpa / _block_mask_to_float_bias,
+    mlx_mfa/attention.py:1399-1432).
     """
     B, Hq, N, D = q.shape
     Hkv, S = k.shape[1], k.shape[2]
@@ -99,6 +104,10 @@ def sdpa(
             kpos = torch.arange(S, dtype=sdt)[None, :]
             s = s + alibi_slopes.to(sdt)[None, :, None, None] * (kpos - qpos)[None, None]
         vis = _visible(N, S, causal, window_left, rows)
+        if block_mask is not None:
+            cells = block_mask.bool().repeat_interleave(block[0], dim=0)[:N].repeat_interleave(block[1], dim=1)[:, :S]
+            cells = cells[rows]
+            vis = cells if vis is None else (vis & cells)
         if vis is not None:
             s = s.masked_fill(~vis, float("-inf"))
         m = s.max(dim=-1, keepdim=True).values

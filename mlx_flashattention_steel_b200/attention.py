@@ -35,6 +35,7 @@ import torch
 from . import _lib
 
 _SUPPORTED_HDIMS = (64, 128)
+_FWD_ONLY_HDIMS = (256,)       # f16 / bf16 forward through the portable kernel; no backward, no decode kernel
 _VALID_BACKENDS = {"auto", "mfa", "sdpa"}
 _DTYPE_CODE = {torch.float16: _lib.F16, torch.bfloat16: _lib.BF16, torch.float32: _lib.F32}
 
@@ -216,6 +217,8 @@ class _FlashAttnFn(torch.autograd.Function):
                 "flash_attention backward with softcap or window_size: the reference differentiates "
                 "its SDPA fallback here (mlx_mfa/attention.py:1976-1992, 2020-2027); no CUDA kernel is built."
             )
+        if q.shape[-1] in _FWD_ONLY_HDIMS:
+            raise NotImplementedError(f"flash_attention backward for head_dim {q.shape[-1]} is not built.")
         if q.dtype == torch.float32:
             raise NotImplementedError(
                 "flash_attention backward for float32: the reference differentiates its SDPA fallback "
@@ -303,11 +306,12 @@ def flash_attention(
             raise ValueError(f"alibi_slopes must be [H_q] = [{q_heads}], got {tuple(alibi.shape)}.")
         _require_cuda(alibi)
         alibi = alibi.to(torch.float32).contiguous()
-    supported = head_dim in _SUPPORTED_HDIMS and q.dtype in _DTYPE_CODE and v_dim == q_dim
+    supported = ((head_dim in _SUPPORTED_HDIMS and q.dtype in _DTYPE_CODE) or
+                 (head_dim in _FWD_ONLY_HDIMS and q.dtype in (torch.float16, torch.bfloat16))) and v_dim == q_dim
     if not supported:
         msg = (
             f"unsupported configuration — head_dim={head_dim}, dtype={q.dtype}, "
-            f"v_dim_mismatch={v_dim != q_dim}. Supported: head_dim∈{{64,128}}, dtype∈{{f16,bf16,f32}}."
+            f"v_dim_mismatch={v_dim != q_dim}. Supported: head_dim∈{{64,128}} with f16/bf16/f32, head_dim=256 with f16/bf16 (forward only)."
         )
         if backend == "mfa":
             raise RuntimeError(f"flash_attention(backend='mfa'): {msg}")
@@ -419,7 +423,8 @@ def flash_attention_varlen(
         raise ValueError("q, k, v must have the same head_dim.")
     if q.shape[1] % k.shape[1] != 0:
         raise ValueError(f"flash_attention GQA: q_heads ({q.shape[1]}) must be divisible by kv_heads ({k.shape[1]}).")
-    if D not in _SUPPORTED_HDIMS or q.dtype not in _DTYPE_CODE:
+    ok = (D in _SUPPORTED_HDIMS and q.dtype in _DTYPE_CODE) or (D in _FWD_ONLY_HDIMS and q.dtype in (torch.float16, torch.bfloat16))
+    if not ok:
         raise NotImplementedError(f"flash_attention_varlen: head_dim={D}, dtype={q.dtype} not built.")
     cu_q = cu_q.to(torch.int32).contiguous()
     cu_k = cu_k.to(torch.int32).contiguous()
@@ -806,12 +811,12 @@ def get_device_info() -> dict:
 
 def get_supported_configs() -> dict:
     return {
-        "head_dims": list(_SUPPORTED_HDIMS),
+        "head_dims": list(_SUPPORTED_HDIMS) + list(_FWD_ONLY_HDIMS),
         "dtypes": ["float16", "bfloat16", "float32"],
         "kv_dtypes": ["float16", "bfloat16", "int8", "float8_e4m3fn"],
         "features": {
             "causal": True, "gqa": True, "softcap": True, "window_left": True, "return_lse": True,
             "varlen": True, "paged": True, "quantized_kv": True, "native_backward": True,
-            "alibi": False, "dropout": False, "block_sparse": False, "rope": False,
+            "alibi": True, "dropout": False, "block_sparse": True, "rope": True,
         },
     }

@@ -61,8 +61,8 @@ int32_t check_common(const b200fa_desc* d, bool varlen) {
   if (d == nullptr) return fail(B200FA_ERR_INVALID_ARG, "descriptor is null");
   if (d->dtype != B200FA_F16 && d->dtype != B200FA_BF16 && d->dtype != B200FA_F32)
     return fail(B200FA_ERR_UNSUPPORTED, "dtype %d: expected f16, bf16 or f32", d->dtype);
-  if (d->D != 64 && d->D != 128)
-    return fail(B200FA_ERR_UNSUPPORTED, "head_dim %d: this build has 64 and 128", d->D);
+  if (d->D != 64 && d->D != 128 && !(d->D == 256 && d->dtype != B200FA_F32))
+    return fail(B200FA_ERR_UNSUPPORTED, "head_dim %d: this build has 64 and 128 (and 256 for the f16 / bf16 forward)", d->D);
   if (d->B < 0 || d->Hq <= 0 || d->Hkv <= 0 || d->N < 0 || d->S < 0)
     return fail(B200FA_ERR_INVALID_ARG, "negative or zero extent (B=%d Hq=%d Hkv=%d N=%d S=%d)", d->B,
                 d->Hq, d->Hkv, d->N, d->S);
@@ -244,6 +244,7 @@ static int32_t bwd_common(const b200fa_desc* d, const void* q, const void* k, co
   if (st != B200FA_OK) return st;
   if (!aligned16(dout) || !aligned16(dq) || !aligned16(dk) || !aligned16(dv))
     return fail(B200FA_ERR_INVALID_ARG, "dout, dq, dk, dv must be 16-byte aligned");
+  if (d->D == 256) return fail(B200FA_ERR_UNSUPPORTED, "backward for head_dim 256 is not built");
   b200fa::BwdParams p;
   memset(&p, 0, sizeof(p));
   p.q = q; p.k = k; p.v = v; p.o = out; p.dout = dout; p.lse = lse;

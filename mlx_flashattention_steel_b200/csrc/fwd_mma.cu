@@ -313,6 +313,8 @@ cudaError_t launch_fwd_mma(const FwdParams& p, int dtype, int D, bool varlen, in
   if (dtype == 0 && D == 128) { B200FA_CASE(__half, 128); }
   if (dtype == 1 && D == 64) { B200FA_CASE(__nv_bfloat16, 64); }
   if (dtype == 1 && D == 128) { B200FA_CASE(__nv_bfloat16, 128); }
+  if (dtype == 0 && D == 256) { B200FA_CASE(__half, 256); }
+  if (dtype == 1 && D == 256) { B200FA_CASE(__nv_bfloat16, 256); }
 #undef B200FA_CASE
   return cudaErrorInvalidValue;
 }

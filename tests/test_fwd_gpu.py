@@ -223,6 +223,21 @@ def test_full_size_linearity_in_v(dev):
     assert float((oc - 0.75).abs().max()) <= 1e-2
 
 
+@pytest.mark.parametrize("dt", ["f16", "bf16"])
+@pytest.mark.parametrize("Hq,Hkv,N,S,causal", [(4, 4, 200, 200, True), (4, 2, 70, 333, False), (2, 1, 1, 500, True)])
+def test_head_dim_256_forward(dev, dt, Hq, Hkv, N, S, causal):
+    """head_dim 256 (the reference's largest kernel size, mlx_mfa/attention.py:30): 16-bit forward through the portable
+    kernel; the backward and float32 are refused."""
+    _run(dev, DT[dt], 1, Hq, Hkv, N, S, 256, 180, causal=causal)
+    _run(dev, DT[dt], 1, Hq, Hkv, N, S, 256, 181, causal=causal, softcap=20.0, window_size=(64, 0))
+    q = randn((1, 2, 16, 256), torch.float32, 182).to(dev)
+    with pytest.raises(NotImplementedError):
+        fa.flash_attention(q, q, q)
+    qh = randn((1, 2, 16, 256), DT[dt], 183).to(dev).requires_grad_(True)
+    with pytest.raises(NotImplementedError):
+        fa.flash_attention(qh, qh, qh).sum().backward()
+
+
 def test_short_tiles_wait_for_both_pending_accumulations(dev):
     """A query tile with two key tiles can finish its second softmax before the first P.V product has completed;
     the epilogue must then wait for both.  With constant V every output equals that constant whatever the

@@ -108,7 +108,9 @@ __device__ __forceinline__ float tree_min64(const float (&x)[64]) {
 }
 
 // Of every 4 key pairs a softmax thread handles, this many take exp2 on the FMA pipe (exp2_poly2) instead of
-// the special-function unit, whose 4 lanes per scheduler are otherwise the bound of the inner loop.
+// the special-function unit.  0 by default: measured on config 2, shares of 25 % and 50 % were 5 % and 10 % slower
+// (the polynomial costs about 20 FMA-pipe clocks per pair against 16 on the special-function unit, and the kernel
+// is not bound by that unit alone).  Kept as a build-time switch for shapes where that balance differs.
 #ifndef B200FA_EXP_POLY_PAIRS
 #define B200FA_EXP_POLY_PAIRS 0
 #endif

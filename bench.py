@@ -511,6 +511,7 @@ def main():
             "e2e": {"value": e2e_val, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                     "ms_per_step": e2e_ms},
             "gpu_launches": args.steps,
+            "kernel_status": int(fa.kernel_status()),       # 0 = no bounded wait inside a tcgen05 kernel gave up
             "clocks": clocks,
             "decode": decode,
             "extras": extras,

@@ -19,3 +19,16 @@ def dev():
     if not torch.cuda.is_available():
         pytest.skip("no CUDA device")
     return torch.device("cuda:0")
+
+
+@pytest.fixture(autouse=True, scope="module")
+def _no_kernel_wait_timed_out():
+    """After every test module that ran on a GPU: none of the tcgen05 kernels' bounded waits may have given up.  A wait
+    that times out leaves wrong outputs behind only for the launch it happened in, which a later assertion can miss."""
+    yield
+    import torch
+
+    if torch.cuda.is_available():
+        import mlx_flashattention_steel_b200 as fa
+
+        assert fa.kernel_status() == 0, "a bounded wait inside a tcgen05 kernel timed out during this module"

@@ -159,6 +159,11 @@ __device__ __forceinline__ uint32_t i8pair_to_h2(uint32_t biased, uint32_t sel) 
   __half2 h = __hsub2(*reinterpret_cast<const __half2*>(&magic), __floats2half2_rn(1152.f, 1152.f));
   return *reinterpret_cast<uint32_t*>(&h);
 }
+// the same without the subtraction: half2 of 1024 + (x + 128) = x + 1152.  Used for K, where the constant offset
+// becomes 1152 * sum(q) in each score and is taken out of the fp32 accumulator after the eight MMAs of a tile.
+__device__ __forceinline__ uint32_t i8pair_to_h2_biased(uint32_t biased, uint32_t sel) {
+  return prmt(biased, 0x64646464u, sel);
+}
 __device__ __forceinline__ uint32_t e4m3pair_to_h2(uint32_t two_bytes) {
   __half2_raw r = __nv_cvt_fp8x2_to_halfraw2(static_cast<__nv_fp8x2_storage_t>(two_bytes & 0xffffu), __NV_E4M3);
   __half2 h = r;
@@ -352,6 +357,7 @@ decode_paged_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_consta
 
     // ---- Q fragments (A operand rows 0..7; rows 8..15 are zero padding) ----
     uint32_t qa[8][2];
+    float q_bias = 0.f;          // int8 pools: 1152 * sum of the row's query values (see i8pair_to_h2_biased)
     {
       const size_t qoff = ((static_cast<size_t>(b) * p.Hq + hq_row) * p.Nq + qi_row) * kD;
       if (kQuant) {
@@ -391,6 +397,20 @@ decode_paged_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_consta
         for (int s = 0; s < 8; ++s) {
           qa[s][0] = pack_h2(clamp_h(f[4 * s] * a.q_prescale), clamp_h(f[4 * s + 1] * a.q_prescale));
           qa[s][1] = pack_h2(clamp_h(f[4 * s + 2] * a.q_prescale), clamp_h(f[4 * s + 3] * a.q_prescale));
+        }
+        if (KV == KV_I8) {
+          // 1152 * (sum over the head dim of this row's f16 query values): the part of every score that comes from
+          // the +1152 offset left inside the widened K values
+          float qs = 0.f;
+#pragma unroll
+          for (int s = 0; s < 8; ++s) {
+            const float2 u = __half22float2(*reinterpret_cast<const __half2*>(&qa[s][0]));
+            const float2 w = __half22float2(*reinterpret_cast<const __half2*>(&qa[s][1]));
+            qs += (u.x + u.y) + (w.x + w.y);
+          }
+          qs += __shfl_xor_sync(0xffffffffu, qs, 1);
+          qs += __shfl_xor_sync(0xffffffffu, qs, 2);
+          q_bias = 1152.f * qs;
         }
       } else {
         // natural order: a0 = Q[g][16s + 2t, +1], a2 = Q[g][16s + 8 + 2t, +1]
@@ -463,8 +483,8 @@ decode_paged_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_consta
                 uint32_t b0, b1;
                 if (KV == KV_I8) {
                   const uint32_t x = words[s] ^ 0x80808080u;
-                  b0 = i8pair_to_h2(x, 0x4140u);
-                  b1 = i8pair_to_h2(x, 0x4342u);
+                  b0 = i8pair_to_h2_biased(x, 0x4140u);
+                  b1 = i8pair_to_h2_biased(x, 0x4342u);
                 } else {
                   b0 = e4m3pair_to_h2(words[s]);
                   b1 = e4m3pair_to_h2(words[s] >> 16);
@@ -504,6 +524,7 @@ decode_paged_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_consta
             if (pg[q] >= 0) {
               ksv = lds_half(ksb[q] + tok * scale_stride);
               vsc[q][e] = lds_half(vsb[q] + tok * scale_stride);
+              if (KV == KV_I8) s -= q_bias;                 // the K values went into the MMA as x + 1152
             }
             s *= ksv;
           } else {

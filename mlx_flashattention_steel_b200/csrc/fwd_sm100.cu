@@ -63,7 +63,8 @@ enum Bar {
   BAR_P_FULL = 11,           // +buffer
   BAR_PV_DONE = 13,
   BAR_O_STAGED = 14,         // count 4: the softmax warps have written their O rows to shared memory
-  BAR_COUNT = 15
+  BAR_O_FINAL = 15,          // committed once, after the last P.V: O is complete
+  BAR_COUNT = 16
 };
 
 struct Sm100Args {
@@ -233,6 +234,7 @@ fa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     }
     mbar_init(bar(BAR_PV_DONE), 1);
     mbar_init(bar(BAR_O_STAGED), 4);
+    mbar_init(bar(BAR_O_FINAL), 1);
     *s_abort = 0;
     fence_barrier_init();
     fence_proxy_async();
@@ -317,6 +319,7 @@ fa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         }
         tc_commit(bar(BAR_PV_DONE));
         tc_commit(bar(BAR_V_EMPTY + st));
+        if (j + 1 == n_tiles) tc_commit(bar(BAR_O_FINAL));
       }
     }
   } else {
@@ -518,10 +521,11 @@ fa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     }
 
     // ---- epilogue: O / l -> global, lse ----
-    // S(n-1) being complete only implies PV(n-3): these warps may be two completions ahead of PV_DONE, and a parity
-    // wait two phases ahead passes at once.  So wait for PV(n-2) first, then for PV(n-1).
-    if (ok && n_tiles >= 2) ok = __all_sync(0xffffffffu, mbar_wait_bounded(bar(BAR_PV_DONE), (n_tiles - 2) & 1, s_abort));
-    if (ok) ok = __all_sync(0xffffffffu, mbar_wait_bounded(bar(BAR_PV_DONE), (n_tiles - 1) & 1, s_abort));
+    // O is complete when the barrier committed after the last P.V fires.  It is used once per CTA, so its parity
+    // cannot alias: PV_DONE would not do here, because a warp may reach this point two completions ahead of it
+    // (S(n-1) complete only implies PV(n-3)) or after both have happened, and a parity wait is only sound within one
+    // phase of the barrier.
+    if (ok) ok = __all_sync(0xffffffffu, mbar_wait_bounded(bar(BAR_O_FINAL), 0, s_abort));
     if (ok) {
       tc_fence_after();
       const float inv = l_run > 0.f ? 1.f / l_run : 0.f;

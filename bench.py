@@ -322,6 +322,13 @@ def bench_extras(device, pk):
     byts = 4 * q.numel() * 2
     out["config3_window512_fp16"] = {"ms": ms, "tflops": fl / ms / 1e9, "frac_tensor_peak": fl / ms / 1e9 / pk["tf"],
                                      "gbs": byts / ms / 1e6, "frac_hbm_peak": byts / ms / 1e6 / pk["hbm"]}
+    # the same shape through a block mask (32 x 16 cells): the causal sliding-window builder switches on the cells a
+    # +-512 window around each query block's centre touches; FLOPs are counted over the active cells
+    bm = fa.make_sliding_window_mask(32768, 512, 128, causal=True, device=device)
+    ms = _time_ms(lambda: fa.flash_attention_sparse(q, k, v, bm, causal=True), 10, 3)
+    fl = 4.0 * 2 * 16 * 128 * float(bm.sum().item()) * 32 * 16
+    out["sparse_window_mask_fp16"] = {"ms": ms, "active_cells": float(bm.float().mean().item()),
+                                      "tflops_active_cells": fl / ms / 1e9, "kernel": "fa_fwd_sm100_kernel<128, f16, features>"}
     del q, k, v
     # config 5: packed varlen, 65536 tokens, lengths ~ U{128..4096}, H=16 D=64 bf16 causal, fwd + bwd
     rng = np.random.default_rng(5)

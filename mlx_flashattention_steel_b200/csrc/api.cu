@@ -169,8 +169,7 @@ int32_t b200fa_fwd(const b200fa_desc* d, const void* q, const void* k, const voi
   cudaError_t e;
   if (d->dtype == B200FA_F32) {
     e = b200fa::launch_fwd_f32(p, d->D, false, d->B, d->N, cs);
-  } else if (!(d->flags & B200FA_FLAG_FORCE_MMA_SYNC) && p.alibi == nullptr && p.bmask == nullptr &&
-             b200fa::fwd_sm100_supported(p, d->dtype, d->D)) {
+  } else if (!(d->flags & B200FA_FLAG_FORCE_MMA_SYNC) && b200fa::fwd_sm100_supported(p, d->dtype, d->D)) {
     e = b200fa::launch_fwd_sm100(p, d->dtype, d->D, d->B, d->N, cs);
   } else {
     e = b200fa::launch_fwd_mma(p, d->dtype, d->D, false, d->B, d->N, cs);

@@ -41,6 +41,7 @@ constexpr int BN = 64;       // keys per tile
 constexpr int kStages = 2;
 constexpr int kThreads = 192;
 constexpr uint32_t kTmemCols = 256;
+constexpr int kMaxListTiles = 1024;   // block-sparse instantiation: active key tiles of one query tile (16-bit indices)
 
 // Sizes that depend on the head dim (64 or 128).  Tiles are stored as 64-element (128-byte) wide halves,
 // [half][row][128 B], each half one 128B-swizzle atom wide.
@@ -50,6 +51,7 @@ template <int HD> struct Cfg {
   static constexpr int kKVBytes = BN * HD * 2;         // 16384 / 8192 per stage
   static constexpr int kSmemTiles = kQBytes + 2 * kStages * kKVBytes;
   static constexpr int kSmemBytes = kSmemTiles + 256 + 1024;   // + barriers + alignment slack
+  static constexpr int kSmemBytesFeat = kSmemBytes + kMaxListTiles * 2;   // + the active-tile list
 };
 
 // barrier slots (uint64 each)
@@ -145,7 +147,10 @@ template <int DT> __device__ __forceinline__ uint32_t pack16(float a, float b) {
 // ---------------------------------------------------------------------------
 // kernel
 // ---------------------------------------------------------------------------
-template <int HD, int DT>
+// FEAT adds the ALiBi bias and the block mask (reference: mlx_mfa/attention.py:1079-1216 flash_attention_sparse,
+// csrc/mfa_steel_fwd.cpp:230-262 the shader's per-tile mask test): a key tile is visited only if one of the mask
+// cells under it is set, and partially set tiles are masked by element.  The plain instantiation compiles none of it.
+template <int HD, int DT, bool FEAT>
 __global__ void __launch_bounds__(kThreads, 2)
 fa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                     const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmO,
@@ -160,6 +165,8 @@ fa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kSmemTiles);
   uint32_t* s_tmem = reinterpret_cast<uint32_t*>(bars + BAR_COUNT);
   volatile int* s_abort = reinterpret_cast<volatile int*>(s_tmem + 1);
+  int* s_ntiles = reinterpret_cast<int*>(s_tmem + 2);
+  uint16_t* s_list = reinterpret_cast<uint16_t*>(smem + kSmemTiles + 256);     // FEAT only
 
   const FwdParams& p = a.p;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -185,7 +192,37 @@ fa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   if (p.window_left >= 0) k_lo = max(0, q0 + off - p.window_left);
   const int kt_begin = k_lo / BN;
   const int kt_end = k_hi > 0 ? (k_hi + BN - 1) / BN : 0;
-  const int n_tiles = kt_end - kt_begin;
+  int n_tiles = kt_end - kt_begin;
+  const bool sparse = FEAT && p.bmask != nullptr;
+  if constexpr (FEAT) {
+    if (sparse) {
+      // warp 0 compacts the key tiles that have a set mask cell under this query tile
+      if (warp == 0) {
+        const int rb0 = q0 / p.bm_bq, rb1 = (min(q0 + BM, N) - 1) / p.bm_bq;
+        int count = 0;
+        for (int base = kt_begin; base < kt_end; base += 32) {
+          const int kt = base + lane;
+          bool on = false;
+          if (kt < kt_end) {
+            const int cb0 = (kt * BN) / p.bm_bk, cb1 = (min((kt + 1) * BN, S) - 1) / p.bm_bk;
+            for (int rb = rb0; rb <= rb1; ++rb)
+              for (int cb = cb0; cb <= cb1; ++cb) on = on || (p.bmask[rb * p.bm_nk + cb] != 0);
+          }
+          const unsigned bal = __ballot_sync(0xffffffffu, on);
+          if (on) s_list[count + __popc(bal & ((1u << lane) - 1u))] = static_cast<uint16_t>(kt);
+          count += __popc(bal);
+        }
+        if (lane == 0) *s_ntiles = count;
+      }
+      __syncthreads();
+      n_tiles = *s_ntiles;
+    }
+  }
+  // j-th key tile this CTA visits
+  auto tile_of = [&](int j) -> int {
+    if constexpr (FEAT) return sparse ? static_cast<int>(s_list[j]) : kt_begin + j;
+    return kt_begin + j;
+  };
 
   auto bar = [&](int i) -> uint32_t { return smem_u32(&bars[i]); };
 
@@ -212,7 +249,7 @@ fa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
 #pragma unroll
     for (int hf = 0; hf < kHalves; ++hf)
       tma_load_4d(smem_u32(sK + st * kKVBytes + hf * (kKVBytes / kHalves)), &tmK, bar(BAR_K_FULL + st), 64 * hf,
-                  k_begin + (kt_begin + j) * BN, kvh, batch);
+                  k_begin + tile_of(j) * BN, kvh, batch);
   };
   auto load_v = [&](int j) {
     const int st = j & 1;
@@ -220,7 +257,7 @@ fa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
 #pragma unroll
     for (int hf = 0; hf < kHalves; ++hf)
       tma_load_4d(smem_u32(sV + st * kKVBytes + hf * (kKVBytes / kHalves)), &tmV, bar(BAR_V_FULL + st), 64 * hf,
-                  k_begin + (kt_begin + j) * BN, kvh, batch);
+                  k_begin + tile_of(j) * BN, kvh, batch);
   };
   if (warp == 4 && lane == 0) {
     mbar_init(bar(BAR_Q), 1);
@@ -340,10 +377,11 @@ fa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     const float y_deg3 = use_cap ? fminf(0.5f, powf(1e-3f * 7.5f / p.softcap, 0.2f)) : 0.f;
     const float y_deg5 = use_cap ? fminf(0.5f, powf(1e-3f * (315.f / 17.f) / p.softcap, 1.f / 7.f)) : 0.f;
     const bool monotone = p.scale > 0.f;              // lets the row max be taken on the raw dot products
+    const float alibi_l2 = (FEAT && p.alibi != nullptr) ? p.alibi[head] * kLog2e : 0.f;
 
     for (int j = 0; j < n_tiles; ++j) {
       const int st = j & 1;
-      const int k0 = (kt_begin + j) * BN;
+      const int k0 = tile_of(j) * BN;
       if (!__all_sync(0xffffffffu, mbar_wait_bounded(bar(BAR_S_FULL + st), (j >> 1) & 1, s_abort))) { ok = false; break; }
       tc_fence_after();
       uint32_t r0[32], r1[32];
@@ -354,9 +392,20 @@ fa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
 #pragma unroll
       for (int i = 0; i < 32; ++i) { x[i] = __uint_as_float(r0[i]); x[32 + i] = __uint_as_float(r1[i]); }
 
+      unsigned cells = 0xffffffffu;                   // FEAT: set mask cells of this row under the tile
+      bool cells_partial = false;
+      if constexpr (FEAT) {
+        if (sparse) {
+          const int rb = min(row, N - 1) / p.bm_bq, cb0 = k0 / p.bm_bk, ncell = BN / p.bm_bk;
+          cells = 0u;
+          for (int c = 0; c < ncell; ++c)
+            if (cb0 + c < p.bm_nk && p.bmask[rb * p.bm_nk + cb0 + c] != 0) cells |= 1u << c;
+          cells_partial = __any_sync(0xffffffffu, cells != (1u << ncell) - 1u);
+        }
+      }
       const bool need_mask = (k0 + BN > S) || (p.causal && (k0 + BN - 1 > q0 + off)) ||
-                             (p.window_left >= 0 && (k0 < q0 + BM - 1 + off - p.window_left));
-      const bool fast = !need_mask && monotone;
+                             (p.window_left >= 0 && (k0 < q0 + BM - 1 + off - p.window_left)) || cells_partial;
+      const bool fast = !need_mask && monotone && !(FEAT && p.alibi != nullptr);
       // mode 0: t = x*scale_log2 - m ; 1: softcap by polynomial ; 2: softcap by tanh.approx ; 3: general (masked tile)
       int mode = 3;
       unsigned deg = 2;                                // mode 1 only: 0, 1, 2 = polynomial of degree 3, 5, 7
@@ -403,6 +452,14 @@ fa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
 #pragma unroll
           for (int i = 0; i < BN; ++i) x[i] *= p.scale_log2;
         }
+        if constexpr (FEAT) {
+          if (p.alibi != nullptr) {
+            // slope * (key - query position), in the log2 domain like the scores
+            const float base = alibi_l2 * static_cast<float>(k0 - (row + off));
+#pragma unroll
+            for (int i = 0; i < BN; ++i) x[i] += fmaf(alibi_l2, static_cast<float>(i), base);
+          }
+        }
         if (need_mask) {
           // first / last visible column of this row in tile coordinates; a tile usually crosses only one of the
           // two edges (the diagonal or the end of the keys on the right, the window on the left)
@@ -419,6 +476,14 @@ fa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
 #pragma unroll
             for (int i = 0; i < BN; ++i)
               if (i < lo_rel) x[i] = -INFINITY;
+          }
+          if constexpr (FEAT) {
+            if (cells_partial) {
+              const int sh = p.bm_bk == 16 ? 4 : (p.bm_bk == 32 ? 5 : 6);
+#pragma unroll
+              for (int i = 0; i < BN; ++i)
+                if (!((cells >> (i >> sh)) & 1u)) x[i] = -INFINITY;
+            }
           }
         }
         m_tile = tree_max64(x);
@@ -613,10 +678,15 @@ bool make_map(CUtensorMap* m, int dtype, const void* base, int D, int rows, int 
 bool fwd_sm100_supported(const FwdParams& p, int dtype, int D) {
   if (!(dtype == 0 || dtype == 1) || !(D == 64 || D == 128)) return false;
   if (p.N <= 0 || p.S <= 0 || p.B <= 0) return false;
+  if (p.bmask != nullptr) {
+    // mask cells must tile the 64-key tiles, and the active-tile list holds 16-bit indices of at most kMaxListTiles
+    if (!(p.bm_bk == 16 || p.bm_bk == 32 || p.bm_bk == 64) || p.bm_bq <= 0) return false;
+    if ((p.S + BN - 1) / BN > kMaxListTiles) return false;
+  }
   return get_encode_tiled() != nullptr;
 }
 
-template <int HD, int DT>
+template <int HD, int DT, bool FEAT>
 static cudaError_t launch_hd(const FwdParams& p, int nbatch, int max_q, cudaStream_t stream) {
   constexpr int dtype = DT;
   CUtensorMap tmQ, tmK, tmV, tmO;
@@ -635,11 +705,12 @@ static cudaError_t launch_hd(const FwdParams& p, int nbatch, int max_q, cudaStre
   const int64_t o_hs = fix(p.o_hs, static_cast<int64_t>(p.N) * p.o_rs), o_bs = fix(p.o_bs, o_hs * p.Hq);
   a.tma_store = (p.cu_q == nullptr && make_map(&tmO, dtype, p.o, HD, p.N, p.Hq, p.B, p.o_rs, o_hs, o_bs, BM)) ? 1 : 0;
   if (!a.tma_store) tmO = tmQ;
-  cudaError_t e = cudaFuncSetAttribute(fa_fwd_sm100_kernel<HD, DT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                       Cfg<HD>::kSmemBytes);
+  constexpr int smem_bytes = FEAT ? Cfg<HD>::kSmemBytesFeat : Cfg<HD>::kSmemBytes;
+  cudaError_t e = cudaFuncSetAttribute(fa_fwd_sm100_kernel<HD, DT, FEAT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       smem_bytes);
   if (e != cudaSuccess) return e;
   dim3 grid((max_q + BM - 1) / BM, p.Hq, nbatch);
-  fa_fwd_sm100_kernel<HD, DT><<<grid, kThreads, Cfg<HD>::kSmemBytes, stream>>>(tmQ, tmK, tmV, tmO, a);
+  fa_fwd_sm100_kernel<HD, DT, FEAT><<<grid, kThreads, smem_bytes, stream>>>(tmQ, tmK, tmV, tmO, a);
   return cudaGetLastError();
 }
 
@@ -647,9 +718,14 @@ static cudaError_t launch_hd(const FwdParams& p, int nbatch, int max_q, cudaStre
 // sequences, max_q = longest query sequence.
 cudaError_t launch_fwd_sm100(const FwdParams& p, int dtype, int D, int nbatch, int max_q, cudaStream_t stream) {
   if (nbatch <= 0 || max_q <= 0) return cudaSuccess;
+  if (p.alibi != nullptr || p.bmask != nullptr) {
+    if (D == 64)
+      return dtype == 0 ? launch_hd<64, 0, true>(p, nbatch, max_q, stream) : launch_hd<64, 1, true>(p, nbatch, max_q, stream);
+    return dtype == 0 ? launch_hd<128, 0, true>(p, nbatch, max_q, stream) : launch_hd<128, 1, true>(p, nbatch, max_q, stream);
+  }
   if (D == 64)
-    return dtype == 0 ? launch_hd<64, 0>(p, nbatch, max_q, stream) : launch_hd<64, 1>(p, nbatch, max_q, stream);
-  return dtype == 0 ? launch_hd<128, 0>(p, nbatch, max_q, stream) : launch_hd<128, 1>(p, nbatch, max_q, stream);
+    return dtype == 0 ? launch_hd<64, 0, false>(p, nbatch, max_q, stream) : launch_hd<64, 1, false>(p, nbatch, max_q, stream);
+  return dtype == 0 ? launch_hd<128, 0, false>(p, nbatch, max_q, stream) : launch_hd<128, 1, false>(p, nbatch, max_q, stream);
 }
 
 cudaError_t fwd_sm100_read_clear_status(cudaStream_t stream, int* out) {

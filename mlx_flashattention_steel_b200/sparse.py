@@ -3,7 +3,8 @@
 A block mask is a boolean ``[NQ_tiles, NK_tiles]`` grid over (query block, key block) cells whose sizes are the
 reference's tile sizes for the head dimension (32 x 32 up to D = 64, 32 x 16 above), so masks built for the reference
 mean the same thing here.  Key tiles without an active cell are skipped; cells of a visited tile that are off are
-masked element-wise.  Forward and backward run the portable kernels (the mask rides in the descriptor).
+masked element-wise.  The mask rides in the descriptor: the forward runs the tcgen05 kernel's feature instantiation
+(head_dim 64 / 128), the backward the portable kernel.
 """
 from __future__ import annotations
 

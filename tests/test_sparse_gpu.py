@@ -66,6 +66,23 @@ def test_sparse_forward(dev, dtype, Hq, Hkv, N, S, D, causal):
 
 
 @pytest.mark.gpu
+@pytest.mark.parametrize("D,density", [(128, 0.05), (64, 0.3)])
+def test_sparse_forward_long_rows(dev, D, density):
+    """More than 32 key tiles per query tile (the active-tile list is built in several rounds), low density so that most
+    tiles are skipped, lse checked as well."""
+    BQ, BK = _steel_block_config(D)
+    N = S = 4096 + 40
+    NQ, NK = (N + BQ - 1) // BQ, (S + BK - 1) // BK
+    mask = _random_mask(NQ, NK, 990, density=density)
+    mask[5] = False
+    q, k, v = randn((1, 2, N, D), torch.bfloat16, 991), randn((1, 1, S, D), torch.bfloat16, 992), randn((1, 1, S, D), torch.bfloat16, 993)
+    out = fa.flash_attention_sparse(q.to(dev), k.to(dev), v.to(dev), mask.to(dev), causal=True)
+    O, _, _ = orc.sdpa(q, k, v, causal=True, block_mask=mask, block=(BQ, BK))
+    assert_close(out, O, torch.bfloat16)
+    assert float(out[:, :, 5 * BQ:6 * BQ].abs().max()) == 0.0
+
+
+@pytest.mark.gpu
 def test_builders_reproduce_dense_causal_and_window(dev):
     """A causal block mask plus causal=True is exactly causal attention; the sliding-window cells bound the keys seen."""
     q, k, v = (randn((1, 2, 320, 128), torch.bfloat16, 960 + i).to(dev) for i in range(3))

@@ -52,10 +52,18 @@ struct BwdArgs {
   int dtype;
 };
 
+// Not volatile: the loads may be scheduled ahead of the (volatile) dS stores of earlier elements, which hides their
+// latency.  The address must come from opaque_u32() issued after the wait that makes the data visible, so that no
+// load moves above that wait and none is merged with the same address of another tile.
 __device__ __forceinline__ float4 lds_f4(uint32_t addr) {
   float4 v;
-  asm volatile("ld.shared.v4.f32 {%0,%1,%2,%3}, [%4];\n" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(addr));
+  asm("ld.shared.v4.f32 {%0,%1,%2,%3}, [%4];\n" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(addr));
   return v;
+}
+__device__ __forceinline__ uint32_t opaque_u32(uint32_t x) {
+  uint32_t y;
+  asm volatile("mov.u32 %0, %1;\n" : "=r"(y) : "r"(x) : "memory");
+  return y;
 }
 // dS element of query `ql` (inside the warp's 32 columns): row pitch 128 bytes; ql is a constant after unrolling,
 // so the offset folds into the instruction's immediate
@@ -304,7 +312,7 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       const int st = it & 1;
       const int m = m_begin + it % nm;
       if (!__all_sync(0xffffffffu, mbar_wait_bounded(bar(BAR_Q_FULL + st), (it >> 1) & 1, s_abort))) { ok = false; break; }
-      const uint32_t Ls = smem_u32(sL + st * BQ), Ds = smem_u32(sDel + st * BQ);
+      const uint32_t Ls = opaque_u32(smem_u32(sL + st * BQ)), Ds = Ls + 2 * BQ * 4;
       const bool need_mask = (n0 + BK > S) || (p.causal && (n0 + BK - 1 > m * BQ + off));
       // dS[query][this key] lives at ds_col + query * 128 + ((key chunk ^ (query & 7)) << 4) in buffer it & 1; the eight
       // swizzled chunk offsets are fixed per thread, the query offsets are compile-time constants of the unrolled loop

@@ -14,7 +14,9 @@
 //   dQ   = dS . K       (SS: A = dS tile, B = K MN-major)                      -> TMEM [384,448)
 // The two query halves have their own S^T / dP^T columns and dS has two shared-memory buffers, so the MMAs of one
 // half (and the next tile's S^T / dP^T) run while the compute warps work on the other half.  dQ is read out of TMEM by
-// four flush warps and added to the fp32 accumulator with vector red.global.add; dK / dV leave TMEM once, at the end.
+// four flush warps, staged in shared memory and added to the fp32 accumulator by TMA reduce-add copies (whole 128-byte
+// lines per request; per-lane red.global.add touched 32 lines per instruction and was bound by the load/store unit);
+// dK / dV leave TMEM once, at the end.
 // Warp 8 is the TMA producer (K, V once; Q, dO double-buffered; L and delta staged with them), warp 9
 // issues the MMAs, warps 10-13 move dQ from TMEM to the fp32 accumulator.  No load uses cluster multicast; every mbarrier wait is bounded.
 #include <type_traits>
@@ -42,7 +44,8 @@ constexpr uint32_t cST = 0, cDPT = 64, cDV = 256, cDK = 320, cDQ = 384;
 constexpr int kTileBytes = 128 * HD * 2;                 // 16384: one [128 rows][64] tile
 constexpr int kDSBytes = BQ * BK * 2;                    // 32768: dS as two 64-key halves [half][query][128 B]
 constexpr int kStatBytes = 2 * 2 * BQ * 4;               // L and delta, two stages
-constexpr int kSmemTiles = 2 * kTileBytes + 4 * kTileBytes + 2 * kDSBytes;   // K, V, Q x2, dO x2, dS x2 = 163840
+constexpr int kDQStageBytes = BQ * HD * 4;               // 32768: dQ tile in fp32, two 32-column halves [half][query][128 B]
+constexpr int kSmemTiles = 2 * kTileBytes + 4 * kTileBytes + 2 * kDSBytes + kDQStageBytes;   // K, V, Q x2, dO x2, dS x2, dQ = 196608
 constexpr int kSmemBytes = kSmemTiles + kStatBytes + 256 + 1024;
 
 enum Bar { BAR_KV = 0, BAR_Q_FULL = 1, BAR_Q_EMPTY = 3, BAR_ST_DONE = 5 /* + half */, BAR_PD_READY = 7 /* + half */, BAR_DQ_DONE = 9, BAR_DQ_FREE = 10, BAR_COUNT = 11 };
@@ -59,6 +62,9 @@ __device__ __forceinline__ float4 lds_f4(uint32_t addr) {
   float4 v;
   asm("ld.shared.v4.f32 {%0,%1,%2,%3}, [%4];\n" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(addr));
   return v;
+}
+__device__ __forceinline__ void sts_v4(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+  asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};\n" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
 }
 __device__ __forceinline__ uint32_t opaque_u32(uint32_t x) {
   uint32_t y;
@@ -79,7 +85,8 @@ template <int DT> __device__ __forceinline__ uint32_t pack16b(float a, float b) 
 template <int DT>
 __global__ void __launch_bounds__(kThreads, 1)
 bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
-                 const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmDO, const BwdArgs a) {
+                 const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmDO,
+                 const __grid_constant__ CUtensorMap tmDQ, const BwdArgs a) {
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   unsigned char* sK = smem;
@@ -87,6 +94,7 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   unsigned char* sQ = sV + kTileBytes;                 // [2][128][128 B]
   unsigned char* sDO = sQ + 2 * kTileBytes;            // [2][128][128 B]
   unsigned char* sDS = sDO + 2 * kTileBytes;           // [2 buffers][2 key halves][128 queries][128 B]
+  unsigned char* sDQ = sDS + 2 * kDSBytes;             // [2 column halves][128 queries][128 B] fp32, 128B-swizzled
   float* sL = reinterpret_cast<float*>(smem + kSmemTiles);      // [2][BQ]
   float* sDel = sL + 2 * BQ;                                    // [2][BQ]
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kSmemTiles + kStatBytes);
@@ -270,36 +278,48 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     }
   } else if (warp >= 10) {
     // ============================ dQ flush warps 10-13 ============================
-    // dQ of each tile leaves TMEM here (rows = queries) and goes to the fp32 accumulator as fire-and-forget vector
-    // reductions, off the compute warps' critical path.  The stream of reductions is bound by L2 atomic throughput.
+    // dQ of each tile leaves TMEM here (rows = queries), is staged in shared memory in the tensor map's 128B-swizzled
+    // layout and added to the fp32 accumulator by two TMA reduce-add copies per warp (32 rows x 32 columns each), off
+    // the compute warps' critical path.  TMEM is handed back as soon as the tile is in registers.
     const int wq = warp & 3;                                  // TMEM lane quarter this warp may touch
     const uint32_t lane_base = static_cast<uint32_t>(wq * 32) << 16;
+    const uint32_t stage = smem_u32(sDQ) + wq * 4096;         // this warp's 32 rows; the other column half is 16384 on
+    const uint32_t row_addr = stage + lane * 128;
     for (int it = 0; it < n_iter; ++it) {
       if (!__all_sync(0xffffffffu, mbar_wait_bounded(bar(BAR_DQ_DONE), it & 1, s_abort))) break;
       tc_fence_after();
       const int hq = kvh * p.gqa + it / nm, m = m_begin + it % nm;
-      const int row = m * BQ + wq * 32 + lane;
-      float* acc = p.dq_acc + ((static_cast<int64_t>(bb) * p.Hq + hq) * p.N + q_begin + row) * HD;
+      uint32_t r0[32], r1[32];
+      tmem_ld32(tmem + lane_base + cDQ, r0);
+      tmem_ld32(tmem + lane_base + cDQ + 32, r1);
+      tc_wait_ld();
+      // everything is in registers: the MMA warp may overwrite dQ
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) {
+        mbar_arrive(bar(BAR_DQ_FREE));
+        tma_store_wait_read<0>();                             // the previous tile's copies have read the staging rows
+      }
+      __syncwarp();
+      // rows of this group beyond the sequence hold exact zeros (their P is zero): nothing to add
+      if (m * BQ + wq * 32 < N) {
 #pragma unroll
-      for (int c = 0; c < 2; ++c) {
-        uint32_t r[32];
-        tmem_ld32(tmem + lane_base + cDQ + c * 32, r);
-        tc_wait_ld();
-        if (c == 1) {
-          // everything is in registers: the MMA warp may overwrite dQ
-          tc_fence_before();
-          __syncwarp();
-          if (lane == 0) mbar_arrive(bar(BAR_DQ_FREE));
+        for (int c = 0; c < 8; ++c) {
+          const uint32_t o = static_cast<uint32_t>((c ^ (lane & 7)) << 4);
+          sts_v4(row_addr + o, r0[4 * c], r0[4 * c + 1], r0[4 * c + 2], r0[4 * c + 3]);
+          sts_v4(row_addr + 16384 + o, r1[4 * c], r1[4 * c + 1], r1[4 * c + 2], r1[4 * c + 3]);
         }
-        if (row < N) {
-#pragma unroll
-          for (int i = 0; i < 32; i += 4)
-            asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};\n" ::"l"(acc + c * 32 + i), "f"(__uint_as_float(r[i])),
-                         "f"(__uint_as_float(r[i + 1])), "f"(__uint_as_float(r[i + 2])), "f"(__uint_as_float(r[i + 3]))
-                         : "memory");
+        fence_proxy_async();
+        __syncwarp();
+        if (lane == 0) {
+          const int row0 = q_begin + m * BQ + wq * 32;
+          tma_reduce_add_4d(&tmDQ, stage, 0, row0, hq, bb);
+          tma_reduce_add_4d(&tmDQ, stage + 16384, 32, row0, hq, bb);
+          tma_store_commit();
         }
       }
     }
+    if (lane == 0) tma_store_wait<0>();
   } else {
     // ============================ compute warps 0-7 ============================
     const int wq = warp & 3, hf = warp >> 2;                 // TMEM lane quarter, column half
@@ -450,6 +470,17 @@ cudaError_t launch_bwd_sm100_main(const BwdParams& p, int dtype, int nbatch, int
       !make_map64(&tmV, dtype, p.v, p.S, p.Hkv, p.B, p.v_rs, v_hs, v_bs) ||
       !make_map64(&tmDO, dtype, p.dout, p.N, p.Hq, p.B, HD, do_hs, do_bs))
     return cudaErrorInvalidValue;
+  // fp32 dQ accumulator [B][Hq][N][64]: boxes of 32 rows x 32 columns (128 bytes), 128B-swizzled in shared memory
+  CUtensorMap tmDQ;
+  {
+    const uint64_t dims[4] = {static_cast<uint64_t>(HD), static_cast<uint64_t>(p.N), static_cast<uint64_t>(p.Hq),
+                              static_cast<uint64_t>(p.B)};
+    const uint64_t strides[3] = {static_cast<uint64_t>(HD) * 4, static_cast<uint64_t>(p.N) * HD * 4,
+                                 static_cast<uint64_t>(p.Hq) * p.N * HD * 4};
+    const uint32_t box[4] = {32, 32, 1, 1};
+    if (!encode_tmap(&tmDQ, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, p.dq_acc, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B))
+      return cudaErrorInvalidValue;
+  }
   BwdArgs a;
   a.p = p;
   a.dtype = dtype;
@@ -458,11 +489,11 @@ cudaError_t launch_bwd_sm100_main(const BwdParams& p, int dtype, int nbatch, int
   if (dtype == 0) {
     e = cudaFuncSetAttribute(bwd_sm100_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
     if (e != cudaSuccess) return e;
-    bwd_sm100_kernel<0><<<grid, kThreads, kSmemBytes, stream>>>(tmQ, tmK, tmV, tmDO, a);
+    bwd_sm100_kernel<0><<<grid, kThreads, kSmemBytes, stream>>>(tmQ, tmK, tmV, tmDO, tmDQ, a);
   } else {
     e = cudaFuncSetAttribute(bwd_sm100_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
     if (e != cudaSuccess) return e;
-    bwd_sm100_kernel<1><<<grid, kThreads, kSmemBytes, stream>>>(tmQ, tmK, tmV, tmDO, a);
+    bwd_sm100_kernel<1><<<grid, kThreads, kSmemBytes, stream>>>(tmQ, tmK, tmV, tmDO, tmDQ, a);
   }
   return cudaGetLastError();
 }

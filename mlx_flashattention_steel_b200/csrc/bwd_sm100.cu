@@ -40,6 +40,8 @@ constexpr int kThreads = 448;       // warps 0-7 compute, 8 producer, 9 MMA issu
 constexpr uint32_t kTmemCols = 512;
 // query half x (64 queries): S^T at cST + 128x, dP^T at cDPT + 128x
 constexpr uint32_t cST = 0, cDPT = 64, cDV = 256, cDK = 320, cDQ = 384;
+// K and V rows as 16-bit A operands (two elements per column), written once per CTA
+constexpr uint32_t cKA = 448, cVA = 480;
 
 constexpr int kTileBytes = 128 * HD * 2;                 // 16384: one [128 rows][64] tile
 constexpr int kDSBytes = BQ * BK * 2;                    // 32768: dS as two 64-key halves [half][query][128 B]
@@ -48,7 +50,7 @@ constexpr int kDQStageBytes = BQ * HD * 4;               // 32768: dQ tile in fp
 constexpr int kSmemTiles = 2 * kTileBytes + 4 * kTileBytes + 2 * kDSBytes + kDQStageBytes;   // K, V, Q x2, dO x2, dS x2, dQ = 196608
 constexpr int kSmemBytes = kSmemTiles + kStatBytes + 256 + 1024;
 
-enum Bar { BAR_KV = 0, BAR_Q_FULL = 1, BAR_Q_EMPTY = 3, BAR_ST_DONE = 5 /* + half */, BAR_PD_READY = 7 /* + half */, BAR_DQ_DONE = 9, BAR_DQ_FREE = 10, BAR_COUNT = 11 };
+enum Bar { BAR_KV = 0, BAR_Q_FULL = 1, BAR_Q_EMPTY = 3, BAR_ST_DONE = 5 /* + half */, BAR_PD_READY = 7 /* + half */, BAR_DQ_DONE = 9, BAR_DQ_FREE = 10, BAR_KV_TMEM = 11, BAR_COUNT = 12 };
 
 struct BwdArgs {
   BwdParams p;
@@ -66,17 +68,14 @@ __device__ __forceinline__ float4 lds_f4(uint32_t addr) {
 __device__ __forceinline__ void sts_v4(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
   asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};\n" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
 }
+__device__ __forceinline__ void lds_v4u(uint32_t addr, uint32_t& a, uint32_t& b, uint32_t& c, uint32_t& d) {
+  asm volatile("ld.shared.v4.b32 {%0,%1,%2,%3}, [%4];\n" : "=r"(a), "=r"(b), "=r"(c), "=r"(d) : "r"(addr) : "memory");
+}
 __device__ __forceinline__ uint32_t opaque_u32(uint32_t x) {
   uint32_t y;
   asm volatile("mov.u32 %0, %1;\n" : "=r"(y) : "r"(x) : "memory");
   return y;
 }
-// dS element of query `ql` (inside the warp's 32 columns): row pitch 128 bytes; ql is a constant after unrolling,
-// so the offset folds into the instruction's immediate
-__device__ __forceinline__ void sts_row(uint32_t addr, int ql, uint32_t v) {
-  asm volatile("st.shared.u16 [%0], %1;\n" ::"r"(addr + static_cast<uint32_t>(ql) * 128u), "h"(static_cast<unsigned short>(v)) : "memory");
-}
-
 // DT: 0 = float16, 1 = bfloat16 (a template parameter so that each pair is converted once, not once per type)
 template <int DT> __device__ __forceinline__ uint32_t pack16b(float a, float b) {
   return DT == 0 ? Elem<__half>::pack(a, b) : Elem<__nv_bfloat16>::pack(a, b);
@@ -152,6 +151,7 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     }
     mbar_init(bar(BAR_DQ_DONE), 1);
     mbar_init(bar(BAR_DQ_FREE), 4);       // one arrive per flush warp
+    mbar_init(bar(BAR_KV_TMEM), 8);       // one arrive per compute warp
     *s_abort = 0;
     fence_barrier_init();
     fence_proxy_async();
@@ -212,15 +212,18 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     //   ST/DPT a,b (t=0) | PD_a -> dV_a dK_a, ST/DPT a (t+1) | PD_b -> dV_b dK_b, dQ, ST/DPT b (t+1) | ...
     const bool leader = lane == 0;
     const uint32_t id_st = instr_desc(DT, 0, 128, 64);     // S^T, dP^T of one half: B K-major, N = 64
-    const uint32_t id_mn = instr_desc(DT, 1, 128, HD);     // dV, dK, dQ: B MN-major, N = 64
-    const uint64_t kd = smem_desc(smem_u32(sK), 16, 1024), vd = smem_desc(smem_u32(sV), 16, 1024);
+    const uint32_t id_mn = instr_desc(DT, 1, 128, HD);     // dV, dK: B MN-major, N = 64
+    const uint32_t id_dq = id_mn | (1u << 15);             // dQ: A (dS^T as stored) MN-major as well
     const uint64_t kmn = smem_desc(smem_u32(sK), kTileBytes, 1024);
-    const uint64_t dsd0 = smem_desc(smem_u32(sDS), 16, 1024);
+    // dS^T [query block of 64][key][128 B]: MN (query) blocks kTileBytes apart, 8-key groups 1024 apart
+    const uint64_t dsd0 = smem_desc(smem_u32(sDS), kTileBytes, 1024);
     const uint64_t qd0 = smem_desc(smem_u32(sQ), 16, 1024), dod0 = smem_desc(smem_u32(sDO), 16, 1024);
     const uint64_t qmn0 = smem_desc(smem_u32(sQ), kTileBytes, 1024), domn0 = smem_desc(smem_u32(sDO), kTileBytes, 1024);
     constexpr uint64_t kTileU = kTileBytes >> 4, kHalfRowsU = (64 * 128) >> 4, kDSU = kDSBytes >> 4;
-    bool ok = __all_sync(0xffffffffu, mbar_wait_bounded(bar(BAR_KV), 0, s_abort));
-    // S^T_x and dP^T_x of tile `it`: B rows = the 64 queries of half x
+    bool ok = __all_sync(0xffffffffu, mbar_wait_bounded(bar(BAR_KV_TMEM), 0, s_abort));
+    tc_fence_after();
+    // S^T_x and dP^T_x of tile `it`: A = K / V rows in TMEM (8 columns per 16 head-dim elements), B rows = the 64
+    // queries of half x
     auto issue_stdp = [&](int it, int x) -> bool {
       const int st = it & 1;
       if (x == 0) {
@@ -230,10 +233,10 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       const uint64_t qd = qd0 + st * kTileU + x * kHalfRowsU, dod = dod0 + st * kTileU + x * kHalfRowsU;
 #pragma unroll
       for (int k = 0; k < HD / 16; ++k)
-        if (leader) mma_ss(tmem + cST + 128 * x, kd + k * 2, qd + k * 2, id_st, k > 0 ? 1u : 0u);
+        if (leader) mma_ts(tmem + cST + 128 * x, tmem + cKA + k * 8, qd + k * 2, id_st, k > 0 ? 1u : 0u);
 #pragma unroll
       for (int k = 0; k < HD / 16; ++k)
-        if (leader) mma_ss(tmem + cDPT + 128 * x, vd + k * 2, dod + k * 2, id_st, k > 0 ? 1u : 0u);
+        if (leader) mma_ts(tmem + cDPT + 128 * x, tmem + cVA + k * 8, dod + k * 2, id_st, k > 0 ? 1u : 0u);
       if (leader) tc_commit(bar(BAR_ST_DONE + x));
       __syncwarp();
       return true;
@@ -259,13 +262,13 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
                              (it > 0 || x > 0 || k > 0) ? 1u : 0u);
         if (x == 1) {
           if (leader) tc_commit(bar(BAR_Q_EMPTY + st));
-          // dQ = dS.K: A = dS [query][key] in two 64-key halves (buffer it & 1), B = K rows = keys; the flush warps
-          // must have read the previous tile's dQ out of TMEM first
+          // dQ = dS.K: A = dS^T rows = keys (buffer it & 1), B = K rows = keys, 16 keys = 128 units per step; the
+          // flush warps must have read the previous tile's dQ out of TMEM first
           if (it > 0 && !__all_sync(0xffffffffu, mbar_wait_bounded(bar(BAR_DQ_FREE), (it - 1) & 1, s_abort))) { ok = false; break; }
           const uint64_t dsd = dsd0 + (it & 1) * kDSU;
 #pragma unroll
           for (int k = 0; k < BK / 16; ++k)
-            if (leader) mma_ss(tmem + cDQ, dsd + (k >> 2) * (kDSU / 2) + (k & 3) * 2, kmn + k * 128, id_mn, k > 0 ? 1u : 0u);
+            if (leader) mma_ss(tmem + cDQ, dsd + k * 128, kmn + k * 128, id_dq, k > 0 ? 1u : 0u);
           if (leader) tc_commit(bar(BAR_DQ_DONE));
         }
         __syncwarp();
@@ -326,7 +329,21 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     const int rloc = wq * 32 + lane;                         // key row (S^T, dK, dV) or query row (dQ) inside the tile
     const int key = n0 + rloc;
     const uint32_t lane_base = static_cast<uint32_t>(wq * 32) << 16;
-    bool ok = true;
+    bool ok = __all_sync(0xffffffffu, mbar_wait_bounded(bar(BAR_KV), 0, s_abort));
+    if (ok) {
+      // K rows (warps 0-3) and V rows (warps 4-7) go to TMEM once, as the A operands of S^T and dP^T: their MMAs then
+      // read only the query tiles from shared memory, whose bandwidth is what bounds this kernel
+      const uint32_t rowa = smem_u32(hf == 0 ? sK : sV) + rloc * 128;
+      uint32_t kr[32];
+#pragma unroll
+      for (int c = 0; c < 8; ++c)
+        lds_v4u(rowa + static_cast<uint32_t>((c ^ (rloc & 7)) << 4), kr[4 * c], kr[4 * c + 1], kr[4 * c + 2], kr[4 * c + 3]);
+      tmem_st32(tmem + lane_base + (hf == 0 ? cKA : cVA), kr);
+      tc_wait_st();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar(BAR_KV_TMEM));
+    }
 
     for (int it = 0; it < n_iter && ok; ++it) {
       const int st = it & 1;
@@ -334,13 +351,9 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       if (!__all_sync(0xffffffffu, mbar_wait_bounded(bar(BAR_Q_FULL + st), (it >> 1) & 1, s_abort))) { ok = false; break; }
       const uint32_t Ls = opaque_u32(smem_u32(sL + st * BQ)), Ds = Ls + 2 * BQ * 4;
       const bool need_mask = (n0 + BK > S) || (p.causal && (n0 + BK - 1 > m * BQ + off));
-      // dS[query][this key] lives at ds_col + query * 128 + ((key chunk ^ (query & 7)) << 4) in buffer it & 1; the eight
-      // swizzled chunk offsets are fixed per thread, the query offsets are compile-time constants of the unrolled loop
-      const uint32_t ds_col = smem_u32(sDS) + (it & 1) * kDSBytes + (rloc >> 6) * (kDSBytes / 2) + (rloc & 7) * 2;
-      const int kchunk = (rloc & 63) >> 3;
-      uint32_t ds_sw[8];
-#pragma unroll
-      for (int r = 0; r < 8; ++r) ds_sw[r] = ds_col + ((kchunk ^ r) << 4);
+      // dS^T[this key][query] lives in buffer it & 1 as [query block of 64][key][128 B], 16-byte chunks swizzled by
+      // key & 7: each thread stores its 32 queries as four 16-byte chunks
+      const uint32_t ds_row = smem_u32(sDS) + (it & 1) * kDSBytes + rloc * 128;
       const float2 c2 = make_float2(p.scale_log2, p.scale_log2);
 
       auto run_half = [&](int x, auto masked) {
@@ -350,10 +363,6 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         tmem_ld32(tmem + lane_base + cDPT + 128 * x + hf * 32, rd);
         tc_wait_ld();
         uint32_t pp[16], pd[16];
-        const uint32_t rowoff = q0l * 128;
-        uint32_t dsa[8];
-#pragma unroll
-        for (int r = 0; r < 8; ++r) dsa[r] = ds_sw[r] + rowoff;
 #pragma unroll
         for (int i = 0; i < 32; i += 4) {
           const float4 nL = lds_f4(Ls + (q0l + i) * 4);      // -L of four queries
@@ -374,17 +383,17 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
             }
             const float2 dsv = __fmul2_rn(pe, __fadd2_rn(dv, nd));
             pp[(i + e) >> 1] = pack16b<DT>(pe.x, pe.y);
-            const uint32_t dpk = pack16b<DT>(dsv.x, dsv.y);
-            pd[(i + e) >> 1] = dpk;
-            const int ql = i + e;                          // (q0l + ql) & 7 == ql & 7
-            sts_row(dsa[ql & 7], ql, dpk & 0xffffu);
-            sts_row(dsa[(ql + 1) & 7], ql + 1, dpk >> 16);
+            pd[(i + e) >> 1] = pack16b<DT>(dsv.x, dsv.y);
           }
         }
         // P^T and dS^T go back as 16-bit pairs along the query index, inside the 32 columns this warp has just read
         // (the other warp of these rows may still be reading its own 32)
         tmem_st16(tmem + lane_base + cST + 128 * x + hf * 32, pp);
         tmem_st16(tmem + lane_base + cDPT + 128 * x + hf * 32, pd);
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+          sts_v4(ds_row + x * kTileBytes + static_cast<uint32_t>(((hf * 4 + j) ^ (rloc & 7)) << 4), pd[4 * j], pd[4 * j + 1],
+                 pd[4 * j + 2], pd[4 * j + 3]);
       };
 
 #pragma unroll

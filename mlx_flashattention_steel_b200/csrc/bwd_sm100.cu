@@ -206,11 +206,13 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       __syncwarp();
     }
   } else if (warp == 9) {
+   if (lane == 0) {
     // ============================ MMA issue ============================
     // Per query tile t and query half x: [S^T_x, dP^T_x] -> (compute) -> [dV += P^T_x.dO_x, dK += dS^T_x.Q_x]; after both
     // halves dQ = dS.K.  Issue order keeps the pipe fed while the compute warps work on the other half:
     //   ST/DPT a,b (t=0) | PD_a -> dV_a dK_a, ST/DPT a (t+1) | PD_b -> dV_b dK_b, dQ, ST/DPT b (t+1) | ...
-    const bool leader = lane == 0;
+    // One thread runs the whole role: a warp-wide loop with one elected lane per instruction costs a divergent
+    // region per MMA (62 against 49 clk per MMA in a microbenchmark of this very sequence).
     const uint32_t id_st = instr_desc(DT, 0, 128, 64);     // S^T, dP^T of one half: B K-major, N = 64
     const uint32_t id_mn = instr_desc(DT, 1, 128, HD);     // dV, dK: B MN-major, N = 64
     const uint32_t id_dq = id_mn | (1u << 15);             // dQ: A (dS^T as stored) MN-major as well
@@ -220,25 +222,24 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     const uint64_t qd0 = smem_desc(smem_u32(sQ), 16, 1024), dod0 = smem_desc(smem_u32(sDO), 16, 1024);
     const uint64_t qmn0 = smem_desc(smem_u32(sQ), kTileBytes, 1024), domn0 = smem_desc(smem_u32(sDO), kTileBytes, 1024);
     constexpr uint64_t kTileU = kTileBytes >> 4, kHalfRowsU = (64 * 128) >> 4, kDSU = kDSBytes >> 4;
-    bool ok = __all_sync(0xffffffffu, mbar_wait_bounded(bar(BAR_KV_TMEM), 0, s_abort));
+    bool ok = mbar_wait_bounded(bar(BAR_KV_TMEM), 0, s_abort);
     tc_fence_after();
     // S^T_x and dP^T_x of tile `it`: A = K / V rows in TMEM (8 columns per 16 head-dim elements), B rows = the 64
     // queries of half x
     auto issue_stdp = [&](int it, int x) -> bool {
       const int st = it & 1;
       if (x == 0) {
-        if (!__all_sync(0xffffffffu, mbar_wait_bounded(bar(BAR_Q_FULL + st), (it >> 1) & 1, s_abort))) return false;
+        if (!mbar_wait_bounded(bar(BAR_Q_FULL + st), (it >> 1) & 1, s_abort)) return false;
         tc_fence_after();
       }
       const uint64_t qd = qd0 + st * kTileU + x * kHalfRowsU, dod = dod0 + st * kTileU + x * kHalfRowsU;
 #pragma unroll
       for (int k = 0; k < HD / 16; ++k)
-        if (leader) mma_ts(tmem + cST + 128 * x, tmem + cKA + k * 8, qd + k * 2, id_st, k > 0 ? 1u : 0u);
+        mma_ts(tmem + cST + 128 * x, tmem + cKA + k * 8, qd + k * 2, id_st, k > 0 ? 1u : 0u);
 #pragma unroll
       for (int k = 0; k < HD / 16; ++k)
-        if (leader) mma_ts(tmem + cDPT + 128 * x, tmem + cVA + k * 8, dod + k * 2, id_st, k > 0 ? 1u : 0u);
-      if (leader) tc_commit(bar(BAR_ST_DONE + x));
-      __syncwarp();
+        mma_ts(tmem + cDPT + 128 * x, tmem + cVA + k * 8, dod + k * 2, id_st, k > 0 ? 1u : 0u);
+      tc_commit(bar(BAR_ST_DONE + x));
       return true;
     };
     if (ok) ok = issue_stdp(0, 0);
@@ -247,31 +248,30 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       const int st = it & 1;
 #pragma unroll
       for (int x = 0; x < 2; ++x) {
-        if (!__all_sync(0xffffffffu, mbar_wait_bounded(bar(BAR_PD_READY + x), it & 1, s_abort))) { ok = false; break; }
+        if (!mbar_wait_bounded(bar(BAR_PD_READY + x), it & 1, s_abort)) { ok = false; break; }
         tc_fence_after();
         const uint64_t qmn = qmn0 + st * kTileU + x * kHalfRowsU, domn = domn0 + st * kTileU + x * kHalfRowsU;
         // A in TMEM: 8 columns per 16 queries; queries 0-31 of the half at +0, 32-63 at +32 (where the two warps of a
         // row wrote them); B rows = queries, 16 rows = 128 units
 #pragma unroll
         for (int k = 0; k < 4; ++k)
-          if (leader) mma_ts(tmem + cDV, tmem + cST + 128 * x + (k >> 1) * 32 + (k & 1) * 8, domn + k * 128, id_mn,
+          mma_ts(tmem + cDV, tmem + cST + 128 * x + (k >> 1) * 32 + (k & 1) * 8, domn + k * 128, id_mn,
                              (it > 0 || x > 0 || k > 0) ? 1u : 0u);
 #pragma unroll
         for (int k = 0; k < 4; ++k)
-          if (leader) mma_ts(tmem + cDK, tmem + cDPT + 128 * x + (k >> 1) * 32 + (k & 1) * 8, qmn + k * 128, id_mn,
+          mma_ts(tmem + cDK, tmem + cDPT + 128 * x + (k >> 1) * 32 + (k & 1) * 8, qmn + k * 128, id_mn,
                              (it > 0 || x > 0 || k > 0) ? 1u : 0u);
         if (x == 1) {
-          if (leader) tc_commit(bar(BAR_Q_EMPTY + st));
+          tc_commit(bar(BAR_Q_EMPTY + st));
           // dQ = dS.K: A = dS^T rows = keys (buffer it & 1), B = K rows = keys, 16 keys = 128 units per step; the
           // flush warps must have read the previous tile's dQ out of TMEM first
-          if (it > 0 && !__all_sync(0xffffffffu, mbar_wait_bounded(bar(BAR_DQ_FREE), (it - 1) & 1, s_abort))) { ok = false; break; }
+          if (it > 0 && !mbar_wait_bounded(bar(BAR_DQ_FREE), (it - 1) & 1, s_abort)) { ok = false; break; }
           const uint64_t dsd = dsd0 + (it & 1) * kDSU;
 #pragma unroll
           for (int k = 0; k < BK / 16; ++k)
-            if (leader) mma_ss(tmem + cDQ, dsd + k * 128, kmn + k * 128, id_dq, k > 0 ? 1u : 0u);
-          if (leader) tc_commit(bar(BAR_DQ_DONE));
+            mma_ss(tmem + cDQ, dsd + k * 128, kmn + k * 128, id_dq, k > 0 ? 1u : 0u);
+          tc_commit(bar(BAR_DQ_DONE));
         }
-        __syncwarp();
         // the buffers of half x are free again (the MMAs above read them in pipe order before anything issued now)
         if (it + 1 < n_iter) {
           ok = issue_stdp(it + 1, x);
@@ -279,6 +279,7 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         }
       }
     }
+   }
   } else if (warp >= 10) {
     // ============================ dQ flush warps 10-13 ============================
     // dQ of each tile leaves TMEM here (rows = queries), is staged in shared memory in the tensor map's 128B-swizzled

@@ -139,7 +139,17 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     return;
   }
 
-  if (tid == 0) {
+  // The producer thread sets up the barriers and starts the loads of K, V and of the first two Q / dO tiles (all
+  // stages are empty) before the CTA-wide sync, so that TMEM allocation and the sync hide under them.  A Q_FULL phase
+  // needs the tile's bytes and one arrival, which the producer makes after it has staged the tile's L and delta.
+  auto load_q = [&](int it) {
+    const int st = it & 1;
+    const int hq = kvh * p.gqa + it / nm, m = m_begin + it % nm;
+    mbar_expect_tx(bar(BAR_Q_FULL + st), 2 * kTileBytes);
+    tma_load_4d(smem_u32(sQ + st * kTileBytes), &tmQ, bar(BAR_Q_FULL + st), 0, q_begin + m * BQ, hq, bb);
+    tma_load_4d(smem_u32(sDO + st * kTileBytes), &tmDO, bar(BAR_Q_FULL + st), 0, q_begin + m * BQ, hq, bb);
+  };
+  if (warp == 8 && lane == 0) {
     mbar_init(bar(BAR_KV), 1);
     for (int s = 0; s < 2; ++s) {
       mbar_init(bar(BAR_Q_FULL + s), 1);
@@ -155,6 +165,11 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     *s_abort = 0;
     fence_barrier_init();
     fence_proxy_async();
+    mbar_arrive_expect_tx(bar(BAR_KV), 2 * kTileBytes);
+    tma_load_4d(smem_u32(sK), &tmK, bar(BAR_KV), 0, k_begin + n0, kvh, bb);
+    tma_load_4d(smem_u32(sV), &tmV, bar(BAR_KV), 0, k_begin + n0, kvh, bb);
+    load_q(0);
+    if (n_iter > 1) load_q(1);
   }
   if (warp == 9) {
     tmem_alloc(smem_u32(s_tmem), kTmemCols);
@@ -167,11 +182,6 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
 
   if (warp == 8) {
     // ============================ producer ============================
-    if (lane == 0) {
-      mbar_arrive_expect_tx(bar(BAR_KV), 2 * kTileBytes);
-      tma_load_4d(smem_u32(sK), &tmK, bar(BAR_KV), 0, k_begin + n0, kvh, bb);
-      tma_load_4d(smem_u32(sV), &tmV, bar(BAR_KV), 0, k_begin + n0, kvh, bb);
-    }
     for (int it = 0; it < n_iter; ++it) {
       const int st = it & 1;
       const int hq = kvh * p.gqa + it / nm, m = m_begin + it % nm;
@@ -191,18 +201,17 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
           if (Lr[i] == -INFINITY) Lr[i] = INFINITY;
         }
       }
-      if (!__all_sync(0xffffffffu, mbar_wait_bounded(bar(BAR_Q_EMPTY + st), ((it >> 1) & 1) ^ 1, s_abort))) break;
+      if (it >= 2) {
+        if (!__all_sync(0xffffffffu, mbar_wait_bounded(bar(BAR_Q_EMPTY + st), ((it >> 1) & 1) ^ 1, s_abort))) break;
+        if (lane == 0) load_q(it);
+      }
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
         sL[st * BQ + lane * 4 + i] = -Lr[i];            // stored negated: the compute loop adds them
         sDel[st * BQ + lane * 4 + i] = -dr[i];
       }
       __syncwarp();
-      if (lane == 0) {
-        mbar_arrive_expect_tx(bar(BAR_Q_FULL + st), 2 * kTileBytes);
-        tma_load_4d(smem_u32(sQ + st * kTileBytes), &tmQ, bar(BAR_Q_FULL + st), 0, q_begin + m * BQ, hq, bb);
-        tma_load_4d(smem_u32(sDO + st * kTileBytes), &tmDO, bar(BAR_Q_FULL + st), 0, q_begin + m * BQ, hq, bb);
-      }
+      if (lane == 0) mbar_arrive(bar(BAR_Q_FULL + st));
       __syncwarp();
     }
   } else if (warp == 9) {

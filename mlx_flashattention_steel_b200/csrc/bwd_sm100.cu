@@ -332,7 +332,7 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         }
       }
     }
-    if (lane == 0) tma_store_wait<0>();
+    if (lane == 0) tma_store_wait_read<0>();   // the copies have left shared memory; the kernel's end makes them visible
   } else {
     // ============================ compute warps 0-7 ============================
     const int wq = warp & 3, hf = warp >> 2;                 // TMEM lane quarter, column half
@@ -420,32 +420,45 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     }
 
     if (ok) ok = __all_sync(0xffffffffu, mbar_wait_bounded(bar(BAR_DQ_DONE), (n_iter - 1) & 1, s_abort));
+    // dK, dV: rows = keys, this warp's 32 of the 64 columns.  The tiles go through shared memory (the Q stages, which
+    // nothing reads any more) so that each store instruction writes four whole 128-byte rows: straight from the TMEM
+    // layout a warp would touch 32 different rows per instruction, which took 3600 clk per CTA.
     if (ok) {
       tc_fence_after();
-      // dK, dV: rows = keys, this warp's 32 of the 64 columns
-      if (true) {
-        uint32_t rk[32], rv[32];
-        tmem_ld32(tmem + lane_base + cDK + hf * 32, rk);
-        tmem_ld32(tmem + lane_base + cDV + hf * 32, rv);
-        tc_wait_ld();
-        if (key < S) {
-          const int64_t o = bb * p.dk_bs + kvh * p.dk_hs + static_cast<int64_t>(k_begin + key) * p.dk_rs + hf * 32;
-          uint16_t* dkp = reinterpret_cast<uint16_t*>(p.dk) + o;
-          uint16_t* dvp = reinterpret_cast<uint16_t*>(p.dv) + o;
+      uint32_t rk[32], rv[32];
+      tmem_ld32(tmem + lane_base + cDK + hf * 32, rk);
+      tmem_ld32(tmem + lane_base + cDV + hf * 32, rv);
+      tc_wait_ld();
+      const uint32_t srow = smem_u32(sQ) + rloc * 128;
 #pragma unroll
-          for (int i = 0; i < 32; i += 8) {
-            uint4 vk, vv;
-            vk.x = pack16b<DT>(__uint_as_float(rk[i]) * p.scale, __uint_as_float(rk[i + 1]) * p.scale);
-            vk.y = pack16b<DT>(__uint_as_float(rk[i + 2]) * p.scale, __uint_as_float(rk[i + 3]) * p.scale);
-            vk.z = pack16b<DT>(__uint_as_float(rk[i + 4]) * p.scale, __uint_as_float(rk[i + 5]) * p.scale);
-            vk.w = pack16b<DT>(__uint_as_float(rk[i + 6]) * p.scale, __uint_as_float(rk[i + 7]) * p.scale);
-            vv.x = pack16b<DT>(__uint_as_float(rv[i]), __uint_as_float(rv[i + 1]));
-            vv.y = pack16b<DT>(__uint_as_float(rv[i + 2]), __uint_as_float(rv[i + 3]));
-            vv.z = pack16b<DT>(__uint_as_float(rv[i + 4]), __uint_as_float(rv[i + 5]));
-            vv.w = pack16b<DT>(__uint_as_float(rv[i + 6]), __uint_as_float(rv[i + 7]));
-            *reinterpret_cast<uint4*>(dkp + i) = vk;
-            *reinterpret_cast<uint4*>(dvp + i) = vv;
-          }
+      for (int j = 0; j < 4; ++j) {
+        const int i = 8 * j;
+        const uint32_t o = static_cast<uint32_t>(((hf * 4 + j) ^ (rloc & 7)) << 4);
+        sts_v4(srow + o, pack16b<DT>(__uint_as_float(rk[i]) * p.scale, __uint_as_float(rk[i + 1]) * p.scale),
+               pack16b<DT>(__uint_as_float(rk[i + 2]) * p.scale, __uint_as_float(rk[i + 3]) * p.scale),
+               pack16b<DT>(__uint_as_float(rk[i + 4]) * p.scale, __uint_as_float(rk[i + 5]) * p.scale),
+               pack16b<DT>(__uint_as_float(rk[i + 6]) * p.scale, __uint_as_float(rk[i + 7]) * p.scale));
+        sts_v4(srow + kTileBytes + o, pack16b<DT>(__uint_as_float(rv[i]), __uint_as_float(rv[i + 1])),
+               pack16b<DT>(__uint_as_float(rv[i + 2]), __uint_as_float(rv[i + 3])),
+               pack16b<DT>(__uint_as_float(rv[i + 4]), __uint_as_float(rv[i + 5])),
+               pack16b<DT>(__uint_as_float(rv[i + 6]), __uint_as_float(rv[i + 7])));
+      }
+    }
+    // all eight compute warps pass here, whatever happened before (a named barrier has no time-out)
+    asm volatile("bar.sync 1, 256;\n" ::: "memory");
+    if (ok) {
+      // warp w writes rows 16w .. 16w+15 of both tiles: lane = (row & 3, 16-byte chunk)
+#pragma unroll
+      for (int r4 = 0; r4 < 4; ++r4) {
+        const int r = warp * 16 + r4 * 4 + (lane >> 3), c = lane & 7;
+        const uint32_t sa = smem_u32(sQ) + r * 128 + static_cast<uint32_t>((c ^ (r & 7)) << 4);
+        uint4 vk, vv;
+        lds_v4u(sa, vk.x, vk.y, vk.z, vk.w);
+        lds_v4u(sa + kTileBytes, vv.x, vv.y, vv.z, vv.w);
+        if (n0 + r < S) {
+          const int64_t o = bb * p.dk_bs + kvh * p.dk_hs + static_cast<int64_t>(k_begin + n0 + r) * p.dk_rs + c * 8;
+          *reinterpret_cast<uint4*>(reinterpret_cast<uint16_t*>(p.dk) + o) = vk;
+          *reinterpret_cast<uint4*>(reinterpret_cast<uint16_t*>(p.dv) + o) = vv;
         }
       }
     }

@@ -4,21 +4,24 @@
 //
 // One CTA owns a tile of 128 keys of one kv head and walks the query heads of the GQA group and the
 // 128-row query tiles that can see those keys.  Per query tile, five GEMMs, all M = 128:
-//   S^T  = K . Q^T      (SS, per half of 64 queries, K = 64)   -> TMEM [0,64) and [128,192)
-//   dP^T = V . dO^T     (SS, per half)                          -> TMEM [64,128) and [192,256)
+//   S^T  = K . Q^T      (A = K rows in TMEM, per half of 64 queries, K = 64)   -> TMEM [0,64) and [128,192)
+//   dP^T = V . dO^T     (A = V rows in TMEM, per half)                          -> TMEM [64,128) and [192,256)
 //   8 compute warps (thread = key row, two warps per 32 rows splitting the query columns) turn these into
 //   P^T = 2^(scale*log2e*S^T - L) and dS^T = P^T o (dP^T - delta), written back as 16-bit A operands over
-//   the columns they came from, and dS also to shared memory as a [query][key] tile
+//   the columns they came from, and dS^T also to shared memory as a [query block][key][64 queries] tile
 //   dV  += P^T . dO     (A from TMEM, B = dO as an MN-major operand, N = 64)   -> TMEM [256,320)
 //   dK  += dS^T . Q     (A from TMEM, B = Q MN-major)                          -> TMEM [320,384)
-//   dQ   = dS . K       (SS: A = dS tile, B = K MN-major)                      -> TMEM [384,448)
+//   dQ   = dS . K       (SS: A = the dS^T tile read MN-major, B = K MN-major)  -> TMEM [384,448)
+// K and V rows sit in TMEM [448,512) as A operands for the CTA's lifetime (copied there once by the compute warps),
+// so S^T / dP^T read only the query tiles from shared memory.
 // The two query halves have their own S^T / dP^T columns and dS has two shared-memory buffers, so the MMAs of one
 // half (and the next tile's S^T / dP^T) run while the compute warps work on the other half.  dQ is read out of TMEM by
 // four flush warps, staged in shared memory and added to the fp32 accumulator by TMA reduce-add copies (whole 128-byte
 // lines per request; per-lane red.global.add touched 32 lines per instruction and was bound by the load/store unit);
-// dK / dV leave TMEM once, at the end.
-// Warp 8 is the TMA producer (K, V once; Q, dO double-buffered; L and delta staged with them), warp 9
-// issues the MMAs, warps 10-13 move dQ from TMEM to the fp32 accumulator.  No load uses cluster multicast; every mbarrier wait is bounded.
+// dK / dV leave TMEM once, at the end, through shared memory as whole rows.
+// Warp 8 is the TMA producer (K, V once; Q, dO double-buffered; L and delta staged with them), one thread of warp 9
+// issues the MMAs, warps 10-13 move dQ from TMEM to the fp32 accumulator.  No load uses cluster multicast; every
+// mbarrier wait is bounded.
 #include <type_traits>
 
 #include "common.cuh"
@@ -235,12 +238,12 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     tc_fence_after();
     // S^T_x and dP^T_x of tile `it`: A = K / V rows in TMEM (8 columns per 16 head-dim elements), B rows = the 64
     // queries of half x
-    auto issue_stdp = [&](int it, int x) -> bool {
+    // Each tcgen05.mma waits for room in a queue about one MMA deep (in a microbenchmark the issue loop ends as the
+    // last MMA completes), so whatever else this thread does is a bubble in the tensor pipe.  It therefore waits on
+    // two barriers per tile only (PD_READY of each half): the compute warps check, before they arrive there, that the
+    // next tile's Q / dO have landed (half a) and that the flush warps have read the previous dQ (half b).
+    auto issue_stdp = [&](int it, int x) {
       const int st = it & 1;
-      if (x == 0) {
-        if (!mbar_wait_bounded(bar(BAR_Q_FULL + st), (it >> 1) & 1, s_abort)) return false;
-        tc_fence_after();
-      }
       const uint64_t qd = qd0 + st * kTileU + x * kHalfRowsU, dod = dod0 + st * kTileU + x * kHalfRowsU;
 #pragma unroll
       for (int k = 0; k < HD / 16; ++k)
@@ -249,10 +252,12 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       for (int k = 0; k < HD / 16; ++k)
         mma_ts(tmem + cDPT + 128 * x, tmem + cVA + k * 8, dod + k * 2, id_st, k > 0 ? 1u : 0u);
       tc_commit(bar(BAR_ST_DONE + x));
-      return true;
     };
-    if (ok) ok = issue_stdp(0, 0);
-    if (ok) ok = issue_stdp(0, 1);
+    if (ok) ok = mbar_wait_bounded(bar(BAR_Q_FULL), 0, s_abort);
+    if (ok) {
+      issue_stdp(0, 0);
+      issue_stdp(0, 1);
+    }
     for (int it = 0; it < n_iter && ok; ++it) {
       const int st = it & 1;
 #pragma unroll
@@ -273,8 +278,7 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         if (x == 1) {
           tc_commit(bar(BAR_Q_EMPTY + st));
           // dQ = dS.K: A = dS^T rows = keys (buffer it & 1), B = K rows = keys, 16 keys = 128 units per step; the
-          // flush warps must have read the previous tile's dQ out of TMEM first
-          if (it > 0 && !mbar_wait_bounded(bar(BAR_DQ_FREE), (it - 1) & 1, s_abort)) { ok = false; break; }
+          // flush warps have read the previous tile's dQ out of TMEM (the compute warps saw DQ_FREE before PD_READY)
           const uint64_t dsd = dsd0 + (it & 1) * kDSU;
 #pragma unroll
           for (int k = 0; k < BK / 16; ++k)
@@ -282,10 +286,7 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
           tc_commit(bar(BAR_DQ_DONE));
         }
         // the buffers of half x are free again (the MMAs above read them in pipe order before anything issued now)
-        if (it + 1 < n_iter) {
-          ok = issue_stdp(it + 1, x);
-          if (!ok) break;
-        }
+        if (it + 1 < n_iter) issue_stdp(it + 1, x);
       }
     }
    }
@@ -413,6 +414,15 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         if (need_mask) run_half(x, std::true_type{}); else run_half(x, std::false_type{});
         tc_wait_st();
         fence_proxy_async();          // the dS tile was written with ordinary stores and is read by the MMA
+        // on behalf of the MMA thread (see there): half a vouches for the next tile's Q / dO, half b for the dQ buffer.
+        // Neither barrier can be more than one completion ahead: the next fill of that stage and the next dQ both
+        // need this arrival first.
+        if (x == 0) {
+          if (it + 1 < n_iter &&
+              !__all_sync(0xffffffffu, mbar_wait_bounded(bar(BAR_Q_FULL + ((it + 1) & 1)), ((it + 1) >> 1) & 1, s_abort))) { ok = false; break; }
+        } else {
+          if (it > 0 && !__all_sync(0xffffffffu, mbar_wait_bounded(bar(BAR_DQ_FREE), (it - 1) & 1, s_abort))) { ok = false; break; }
+        }
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(bar(BAR_PD_READY + x));

@@ -51,7 +51,7 @@ template <int HD> struct Cfg {
   static constexpr int kKVBytes = BN * HD * 2;         // 16384 / 8192 per stage
   static constexpr int kSmemTiles = kQBytes + 2 * kStages * kKVBytes;
   static constexpr int kSmemBytes = kSmemTiles + 256 + 1024;   // + barriers + alignment slack
-  static constexpr int kSmemBytesFeat = kSmemBytes + kMaxListTiles * 2;   // + the active-tile list
+  static constexpr int kSmemBytesFeat = kSmemBytes + kMaxListTiles * 3;   // + the active-tile list and its flags
 };
 
 // barrier slots (uint64 each)
@@ -167,6 +167,7 @@ fa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   volatile int* s_abort = reinterpret_cast<volatile int*>(s_tmem + 1);
   int* s_ntiles = reinterpret_cast<int*>(s_tmem + 2);
   uint16_t* s_list = reinterpret_cast<uint16_t*>(smem + kSmemTiles + 256);     // FEAT only
+  unsigned char* s_flag = reinterpret_cast<unsigned char*>(s_list + kMaxListTiles);
 
   const FwdParams& p = a.p;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -196,18 +197,24 @@ fa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   const bool sparse = FEAT && p.bmask != nullptr;
   if constexpr (FEAT) {
     if (sparse) {
-      // warp 0 compacts the key tiles that have a set mask cell under this query tile
-      if (warp == 0) {
+      // every thread tests key tiles (all mask bytes of a tile are fetched at once: no short-circuit, so the loads
+      // overlap), then warp 0 compacts the tiles that have a set cell under this query tile
+      {
         const int rb0 = q0 / p.bm_bq, rb1 = (min(q0 + BM, N) - 1) / p.bm_bq;
+        for (int kt = kt_begin + tid; kt < kt_end; kt += kThreads) {
+          const int cb0 = (kt * BN) / p.bm_bk, cb1 = (min((kt + 1) * BN, S) - 1) / p.bm_bk;
+          unsigned any = 0u;
+          for (int rb = rb0; rb <= rb1; ++rb)
+            for (int cb = cb0; cb <= cb1; ++cb) any |= p.bmask[rb * p.bm_nk + cb];
+          s_flag[kt - kt_begin] = any != 0u ? 1 : 0;
+        }
+      }
+      __syncthreads();
+      if (warp == 0) {
         int count = 0;
         for (int base = kt_begin; base < kt_end; base += 32) {
           const int kt = base + lane;
-          bool on = false;
-          if (kt < kt_end) {
-            const int cb0 = (kt * BN) / p.bm_bk, cb1 = (min((kt + 1) * BN, S) - 1) / p.bm_bk;
-            for (int rb = rb0; rb <= rb1; ++rb)
-              for (int cb = cb0; cb <= cb1; ++cb) on = on || (p.bmask[rb * p.bm_nk + cb] != 0);
-          }
+          const bool on = kt < kt_end && s_flag[kt - kt_begin] != 0;
           const unsigned bal = __ballot_sync(0xffffffffu, on);
           if (on) s_list[count + __popc(bal & ((1u << lane) - 1u))] = static_cast<uint16_t>(kt);
           count += __popc(bal);
@@ -379,6 +386,25 @@ fa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     const bool monotone = p.scale > 0.f;              // lets the row max be taken on the raw dot products
     const float alibi_l2 = (FEAT && p.alibi != nullptr) ? p.alibi[head] * kLog2e : 0.f;
 
+    // FEAT: bit c = mask cell c of this row's block row under the key tile starting at k0
+    // (cells are 16, 32 or 64 keys wide: shifts, and the row's mask line, are worked out once)
+    const int cell_sh = (FEAT && sparse) ? (p.bm_bk == 16 ? 4 : (p.bm_bk == 32 ? 5 : 6)) : 6;
+    const int ncell = BN >> cell_sh;
+    const unsigned full_cells = (1u << ncell) - 1u;
+    const uint8_t* mask_row = (FEAT && sparse) ? p.bmask + static_cast<int64_t>(min(row, N - 1) / p.bm_bq) * p.bm_nk : nullptr;
+    auto row_cells = [&](int k0) -> unsigned {
+      const int cb0 = k0 >> cell_sh;
+      unsigned c4 = 0u;
+#pragma unroll
+      for (int c = 0; c < 4; ++c)
+        if (c < ncell && cb0 + c < p.bm_nk && mask_row[cb0 + c] != 0) c4 |= 1u << c;
+      return c4;
+    };
+    unsigned cells_next = 0xffffffffu;
+    if constexpr (FEAT) {
+      if (sparse) cells_next = row_cells(tile_of(0) * BN);
+    }
+
     for (int j = 0; j < n_tiles; ++j) {
       const int st = j & 1;
       const int k0 = tile_of(j) * BN;
@@ -396,11 +422,10 @@ fa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       bool cells_partial = false;
       if constexpr (FEAT) {
         if (sparse) {
-          const int rb = min(row, N - 1) / p.bm_bq, cb0 = k0 / p.bm_bk, ncell = BN / p.bm_bk;
-          cells = 0u;
-          for (int c = 0; c < ncell; ++c)
-            if (cb0 + c < p.bm_nk && p.bmask[rb * p.bm_nk + cb0 + c] != 0) cells |= 1u << c;
-          cells_partial = __any_sync(0xffffffffu, cells != (1u << ncell) - 1u);
+          // fetched one tile ahead, so that the mask bytes' latency hides under the previous tile's work
+          cells = cells_next;
+          cells_partial = __any_sync(0xffffffffu, cells != full_cells);
+          if (j + 1 < n_tiles) cells_next = row_cells(tile_of(j + 1) * BN);
         }
       }
       const bool need_mask = (k0 + BN > S) || (p.causal && (k0 + BN - 1 > q0 + off)) ||
@@ -479,10 +504,9 @@ fa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
           }
           if constexpr (FEAT) {
             if (cells_partial) {
-              const int sh = p.bm_bk == 16 ? 4 : (p.bm_bk == 32 ? 5 : 6);
 #pragma unroll
               for (int i = 0; i < BN; ++i)
-                if (!((cells >> (i >> sh)) & 1u)) x[i] = -INFINITY;
+                if (!((cells >> (i >> cell_sh)) & 1u)) x[i] = -INFINITY;
             }
           }
         }

@@ -112,28 +112,6 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity,
   }
 }
 
-// The same wait for roles with slack (a producer running ahead, a drain stage): the warp sleeps `ns` between polls, so
-// its polling does not take issue slots from the warps of the same scheduler that it is waiting for.
-__device__ __forceinline__ bool mbar_wait_bounded_sleep(uint32_t bar, uint32_t parity, volatile int* abort_flag, unsigned ns) {
-  if (mbar_try_wait(bar, parity)) return true;
-  uint64_t t0 = 0;
-  uint32_t polls = 0;
-  while (true) {
-    __nanosleep(ns);
-    if (mbar_try_wait(bar, parity)) return true;
-    if ((++polls & 255u) == 0) {
-      if (*abort_flag != 0) return false;
-      const uint64_t now = global_timer_ns();
-      if (t0 == 0) {
-        t0 = now;
-      } else if (now - t0 > 1000000000ull) {
-        *abort_flag = 1;
-        return false;
-      }
-    }
-  }
-}
-
 // ---------------------------------------------------------------------------
 // device: TMA copies (global -> shared), completion on an mbarrier
 // ---------------------------------------------------------------------------

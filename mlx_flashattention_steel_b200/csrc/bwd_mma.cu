@@ -61,6 +61,39 @@ __global__ void __launch_bounds__(256) bwd_preprocess_kernel(const BwdParams p, 
   for (int e = 0; e < PER; ++e) dq[lane + 32 * e] = 0.f;
 }
 
+// The same with 16-byte accesses: D / 8 lanes per row, each with 8 elements of O and dO and 8 accumulator words to
+// clear (one warp per row left every lane with 4 bytes per load and ran at 2.8 TB/s).  Needs 16-byte aligned rows.
+template <typename T, int D>
+__global__ void __launch_bounds__(256) bwd_preprocess_vec_kernel(const BwdParams p, long long total_rows) {
+  constexpr int LPR = D / 8;                                   // lanes per row: 8 or 16
+  const long long t = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  const long long row = t / LPR;
+  const int c = static_cast<int>(t % LPR);
+  const bool live = row < total_rows;                          // whole rows share a warp: the shuffles below stay legal
+  float acc = 0.f;
+  if (live) {
+    const int i = static_cast<int>(row % p.N);
+    const int h = static_cast<int>((row / p.N) % p.Hq);
+    const long long b = row / (static_cast<long long>(p.N) * p.Hq);
+    const T* o = reinterpret_cast<const T*>(p.o) + b * p.o_bs + h * p.o_hs + static_cast<int64_t>(i) * p.o_rs + c * 8;
+    const T* dout = reinterpret_cast<const T*>(p.dout) + row * D + c * 8;
+    const uint4 ow = *reinterpret_cast<const uint4*>(o), dw = *reinterpret_cast<const uint4*>(dout);
+    const uint32_t ou[4] = {ow.x, ow.y, ow.z, ow.w}, du[4] = {dw.x, dw.y, dw.z, dw.w};
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const float2 of = Elem<T>::unpack(ou[e]), df = Elem<T>::unpack(du[e]);
+      acc = fmaf(of.x, df.x, acc);
+      acc = fmaf(of.y, df.y, acc);
+    }
+    float4* dq = reinterpret_cast<float4*>(p.dq_acc + row * D + c * 8);
+    dq[0] = make_float4(0.f, 0.f, 0.f, 0.f);
+    dq[1] = make_float4(0.f, 0.f, 0.f, 0.f);
+  }
+#pragma unroll
+  for (int sft = LPR / 2; sft > 0; sft >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, sft);
+  if (live && c == 0) p.delta[row] = acc;
+}
+
 // ---------------------------------------------------------------------------
 // 3. dQ accumulator -> dtype
 // ---------------------------------------------------------------------------
@@ -329,8 +362,15 @@ template <typename T, int D>
 cudaError_t launch_t(const BwdParams& p, int dtype, bool varlen, int nbatch, int max_k, bool allow_sm100, cudaStream_t stream) {
   const int total_rows = p.B * p.Hq * p.N;
   {
-    const int blocks = (total_rows + 7) / 8;
-    bwd_preprocess_kernel<T, D><<<blocks, 256, 0, stream>>>(p, total_rows);
+    const bool rows16 = reinterpret_cast<uintptr_t>(p.o) % 16 == 0 && reinterpret_cast<uintptr_t>(p.dout) % 16 == 0 &&
+                        p.o_rs % 8 == 0 && p.o_hs % 8 == 0 && p.o_bs % 8 == 0;
+    if (rows16) {
+      const long long threads = static_cast<long long>(total_rows) * (D / 8);
+      bwd_preprocess_vec_kernel<T, D><<<static_cast<unsigned>((threads + 255) / 256), 256, 0, stream>>>(p, total_rows);
+    } else {
+      const int blocks = (total_rows + 7) / 8;
+      bwd_preprocess_kernel<T, D><<<blocks, 256, 0, stream>>>(p, total_rows);
+    }
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return e;
   }

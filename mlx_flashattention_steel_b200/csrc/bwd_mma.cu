@@ -36,6 +36,7 @@ __host__ __device__ inline size_t bwd_align(size_t x) { return (x + 255) / 256 *
 template <typename T, int D>
 __global__ void __launch_bounds__(256) bwd_preprocess_kernel(const BwdParams p, int total_rows) {
   const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+  if (blockIdx.x == 0 && threadIdx.x == 0 && p.work_counter != nullptr) *p.work_counter = 0;
   if (warp >= total_rows) return;
   // warp index = (b*Hq + h)*N + i
   const int i = warp % p.N;
@@ -67,6 +68,7 @@ template <typename T, int D>
 __global__ void __launch_bounds__(256) bwd_preprocess_vec_kernel(const BwdParams p, long long total_rows) {
   constexpr int LPR = D / 8;                                   // lanes per row: 8 or 16
   const long long t = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (t == 0 && p.work_counter != nullptr) *p.work_counter = 0;
   const long long row = t / LPR;
   const int c = static_cast<int>(t % LPR);
   const bool live = row < total_rows;                          // whole rows share a warp: the shuffles below stay legal
@@ -402,7 +404,7 @@ cudaError_t launch_t(const BwdParams& p, int dtype, bool varlen, int nbatch, int
 
 size_t bwd_workspace_bytes(int B, int Hq, int N_total, int D) {
   const size_t rows = static_cast<size_t>(B) * Hq * N_total;
-  return bwd_align(rows * sizeof(float)) + bwd_align(rows * D * sizeof(float));
+  return bwd_align(rows * sizeof(float)) + bwd_align(rows * D * sizeof(float)) + 256;   // delta, dQ accumulator, work counter
 }
 
 cudaError_t launch_bwd(const BwdParams& p_in, int dtype, int D, bool varlen, int nbatch, int max_q, int max_k,
@@ -412,6 +414,8 @@ cudaError_t launch_bwd(const BwdParams& p_in, int dtype, int D, bool varlen, int
   const size_t rows = static_cast<size_t>(p.B) * p.Hq * p.N;
   p.delta = reinterpret_cast<float*>(workspace);
   p.dq_acc = reinterpret_cast<float*>(reinterpret_cast<unsigned char*>(workspace) + bwd_align(rows * sizeof(float)));
+  p.work_counter = reinterpret_cast<int*>(reinterpret_cast<unsigned char*>(workspace) + bwd_align(rows * sizeof(float)) +
+                                          bwd_align(rows * D * sizeof(float)));
   if (rows == 0) return cudaSuccess;
   if (dtype == 0 && D == 64) return launch_t<__half, 64>(p, dtype, varlen, nbatch, max_k, allow_sm100, stream);
   if (dtype == 0 && D == 128) return launch_t<__half, 128>(p, dtype, varlen, nbatch, max_k, allow_sm100, stream);

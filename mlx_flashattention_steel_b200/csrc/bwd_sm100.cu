@@ -2,8 +2,8 @@
 // Same mathematics as bwd_mma.cu (reference: csrc/mfa_steel_bwd.cpp:284-745, 765-1293); the preprocess
 // (delta, dQ accumulator reset) and the final dQ conversion are shared with it.
 //
-// One CTA owns a tile of 128 keys of one kv head and walks the query heads of the GQA group and the
-// 128-row query tiles that can see those keys.  Per query tile, five GEMMs, all M = 128:
+// One persistent CTA per SM takes work items from a global counter; an item is a tile of 128 keys of one kv head, for
+// which the CTA walks the query heads of the GQA group and the 128-row query tiles that can see those keys.  Per query tile, five GEMMs, all M = 128:
 //   S^T  = K . Q^T      (A = K rows in TMEM, per half of 64 queries, K = 64)   -> TMEM [0,64) and [128,192)
 //   dP^T = V . dO^T     (A = V rows in TMEM, per half)                          -> TMEM [64,128) and [192,256)
 //   8 compute warps (thread = key row, two warps per 32 rows splitting the query columns) turn these into
@@ -19,8 +19,9 @@
 // four flush warps, staged in shared memory and added to the fp32 accumulator by TMA reduce-add copies (whole 128-byte
 // lines per request; per-lane red.global.add touched 32 lines per instruction and was bound by the load/store unit);
 // dK / dV leave TMEM once, at the end, through shared memory as whole rows.
-// Warp 8 is the TMA producer (K, V once; Q, dO double-buffered; L and delta staged with them), one thread of warp 9
-// issues the MMAs, warps 10-13 move dQ from TMEM to the fp32 accumulator.  No load uses cluster multicast; every
+// Warp 8 is the TMA producer (Q, dO double-buffered; L and delta staged with them), one thread of warp 9 issues the
+// MMAs, warps 10-13 move dQ from TMEM to the fp32 accumulator; warp 10 also fetches the next item and starts its K / V
+// loads while the current item runs.  No load uses cluster multicast; every
 // mbarrier wait is bounded.
 #include <type_traits>
 
@@ -50,14 +51,18 @@ constexpr int kTileBytes = 128 * HD * 2;                 // 16384: one [128 rows
 constexpr int kDSBytes = BQ * BK * 2;                    // 32768: dS as two 64-key halves [half][query][128 B]
 constexpr int kStatBytes = 2 * 2 * BQ * 4;               // L and delta, two stages
 constexpr int kDQStageBytes = BQ * HD * 4;               // 32768: dQ tile in fp32, two 32-column halves [half][query][128 B]
-constexpr int kSmemTiles = 2 * kTileBytes + 4 * kTileBytes + 2 * kDSBytes + kDQStageBytes;   // K, V, Q x2, dO x2, dS x2, dQ = 196608
+// K, V, Q x2, dO x2, dS x2, dQ, second K buffer (the next work item's keys) = 212992
+constexpr int kSmemTiles = 2 * kTileBytes + 4 * kTileBytes + 2 * kDSBytes + kDQStageBytes + kTileBytes;
 constexpr int kSmemBytes = kSmemTiles + kStatBytes + 256 + 1024;
 
-enum Bar { BAR_KV = 0, BAR_Q_FULL = 1, BAR_Q_EMPTY = 3, BAR_ST_DONE = 5 /* + half */, BAR_PD_READY = 7 /* + half */, BAR_DQ_DONE = 9, BAR_DQ_FREE = 10, BAR_KV_TMEM = 11, BAR_COUNT = 12 };
+// BAR_KV (+ K buffer) live for the whole kernel; the others are set up again for every work item
+enum Bar { BAR_KV = 0, BAR_Q_FULL = 2, BAR_Q_EMPTY = 4, BAR_ST_DONE = 6 /* + half */, BAR_PD_READY = 8 /* + half */, BAR_DQ_DONE = 10, BAR_DQ_FREE = 11, BAR_KV_TMEM = 12, BAR_COUNT = 13 };
 
 struct BwdArgs {
   BwdParams p;
   int dtype;
+  int gx, gy, total_items;      // work items: (key tile, kv head, batch | sequence), key tile fastest
+  int* counter;                 // next work item (zeroed by the preprocess kernel)
 };
 
 // Not volatile: the loads may be scheduled ahead of the (volatile) dS stores of earlier elements, which hides their
@@ -97,54 +102,96 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   unsigned char* sDO = sQ + 2 * kTileBytes;            // [2][128][128 B]
   unsigned char* sDS = sDO + 2 * kTileBytes;           // [2 buffers][2 key halves][128 queries][128 B]
   unsigned char* sDQ = sDS + 2 * kDSBytes;             // [2 column halves][128 queries][128 B] fp32, 128B-swizzled
+  unsigned char* sK1 = sDQ + kDQStageBytes;            // K of every other work item
   float* sL = reinterpret_cast<float*>(smem + kSmemTiles);      // [2][BQ]
   float* sDel = sL + 2 * BQ;                                    // [2][BQ]
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kSmemTiles + kStatBytes);
   uint32_t* s_tmem = reinterpret_cast<uint32_t*>(bars + BAR_COUNT);
   volatile int* s_abort = reinterpret_cast<volatile int*>(s_tmem + 1);
+  // [2][8]: this item and the next one as {index or -1, key tile, kv head, batch, k_begin, S, q_begin, N}
+  volatile int* s_work = reinterpret_cast<volatile int*>(s_tmem + 2);
 
   const BwdParams& p = a.p;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int kvh = blockIdx.y;
-  int bb = blockIdx.z;
-  int q_begin = 0, k_begin = 0, N = p.N, S = p.S;
-  if (p.cu_q != nullptr) {
-    q_begin = p.cu_q[bb];
-    N = p.cu_q[bb + 1] - q_begin;
-    k_begin = p.cu_k[bb];
-    S = p.cu_k[bb + 1] - k_begin;
-    bb = 0;
+  auto bar = [&](int i) -> uint32_t { return smem_u32(&bars[i]); };
+
+  // Persistent CTA, one per SM: work items (128 keys of one kv head of one batch entry or sequence) come from a global
+  // counter in grid order, which puts the key tiles with the most query tiles of each sequence first.  While an item
+  // runs, the producer thread fetches the next one and starts its K load (second buffer) and, once this item's V sits
+  // in TMEM, its V load; set-up, K/V latency and the gap between CTAs are paid once per SM instead of once per item.
+  // Next item that has keys (grid cells beyond a sequence's end are skipped), decoded into slot `sl` of s_work for
+  // every role to read; index -1 when the list is exhausted.  Run by one thread, with global latency per try.
+  auto fetch_next = [&](int sl) -> int {
+    volatile int* o = s_work + sl * 8;
+    for (int tries = 0; tries < (1 << 24); ++tries) {
+      const int idx = atomicAdd(a.counter, 1);
+      if (idx >= a.total_items) break;
+      const int kt = idx % a.gx, kvh_ = (idx / a.gx) % a.gy, z = idx / (a.gx * a.gy);
+      int kb = 0, S_ = p.S, qb = 0, N_ = p.N;
+      if (p.cu_k != nullptr) {
+        kb = p.cu_k[z];
+        S_ = p.cu_k[z + 1] - kb;
+      }
+      if (kt * BK >= S_) continue;
+      if (p.cu_q != nullptr) {
+        qb = p.cu_q[z];
+        N_ = p.cu_q[z + 1] - qb;
+      }
+      o[1] = kt; o[2] = kvh_; o[3] = p.cu_q != nullptr ? 0 : z; o[4] = kb; o[5] = S_; o[6] = qb; o[7] = N_;
+      o[0] = idx;
+      return idx;
+    }
+    o[0] = -1;
+    return -1;
+  };
+  // K / V tile of the item in slot `sl`
+  auto load_k_of = [&](int sl, unsigned char* dst, uint32_t b) {
+    volatile int* o = s_work + sl * 8;
+    tma_load_4d(smem_u32(dst), &tmK, b, 0, o[4] + o[1] * BK, o[2], o[3]);
+  };
+  auto load_v_of = [&](int sl, uint32_t b) {
+    volatile int* o = s_work + sl * 8;
+    tma_load_4d(smem_u32(sV), &tmV, b, 0, o[4] + o[1] * BK, o[2], o[3]);
+  };
+  if (warp == 8 && lane == 0) {
+    mbar_init(bar(BAR_KV), 1);
+    mbar_init(bar(BAR_KV + 1), 1);
+    *s_abort = 0;
+    fence_barrier_init();
+    fence_proxy_async();
+    if (fetch_next(0) >= 0) {
+      mbar_arrive_expect_tx(bar(BAR_KV), 2 * kTileBytes);
+      load_k_of(0, sK, bar(BAR_KV));
+      load_v_of(0, bar(BAR_KV));
+    }
   }
-  const int n0 = blockIdx.x * BK;
-  if (n0 >= S) return;
+  if (warp == 9) {
+    tmem_alloc(smem_u32(s_tmem), kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *s_tmem;
+
+  for (int w = 0;; ++w) {
+  volatile int* wk = s_work + (w & 1) * 8;
+  if (wk[0] < 0 || *s_abort != 0) break;
+  const int kvh = wk[2], bb = wk[3], k_begin = wk[4], S = wk[5], q_begin = wk[6], N = wk[7];
+  const int n0 = wk[1] * BK;
   const int off = S - N;
   int m_begin = 0;
   if (p.causal) m_begin = max(0, n0 - off) / BQ;
   const int m_end = (N + BQ - 1) / BQ;
   const int nm = max(0, m_end - m_begin);
   const int n_iter = nm * p.gqa;
+  const int kbuf = w & 1;                              // K buffer and KV barrier of this item
+  const uint32_t kv_par = (w >> 1) & 1;
+  unsigned char* sKc = kbuf ? sK1 : sK;
 
-  auto bar = [&](int i) -> uint32_t { return smem_u32(&bars[i]); };
-
-  if (n_iter == 0) {
-    // no query sees these keys: dK = dV = 0
-    if (warp < 8) {
-      const int key = n0 + (warp & 3) * 32 + lane, hf = warp >> 2;
-      if (key < S) {
-        const int64_t o = bb * p.dk_bs + kvh * p.dk_hs + static_cast<int64_t>(k_begin + key) * p.dk_rs + hf * 32;
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          reinterpret_cast<uint4*>(reinterpret_cast<uint16_t*>(p.dk) + o)[i] = make_uint4(0u, 0u, 0u, 0u);
-          reinterpret_cast<uint4*>(reinterpret_cast<uint16_t*>(p.dv) + o)[i] = make_uint4(0u, 0u, 0u, 0u);
-        }
-      }
-    }
-    return;
-  }
-
-  // The producer thread sets up the barriers and starts the loads of K, V and of the first two Q / dO tiles (all
-  // stages are empty) before the CTA-wide sync, so that TMEM allocation and the sync hide under them.  A Q_FULL phase
-  // needs the tile's bytes and one arrival, which the producer makes after it has staged the tile's L and delta.
+  // The producer thread sets up this item's barriers and starts the loads of its first two Q / dO tiles (all stages
+  // are empty) before the CTA-wide sync.  A Q_FULL phase needs the tile's bytes and one arrival, which the producer
+  // makes after it has staged the tile's L and delta.
   auto load_q = [&](int it) {
     const int st = it & 1;
     const int hq = kvh * p.gqa + it / nm, m = m_begin + it % nm;
@@ -153,7 +200,8 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     tma_load_4d(smem_u32(sDO + st * kTileBytes), &tmDO, bar(BAR_Q_FULL + st), 0, q_begin + m * BQ, hq, bb);
   };
   if (warp == 8 && lane == 0) {
-    mbar_init(bar(BAR_KV), 1);
+    if (w > 0)
+      for (int i = BAR_Q_FULL; i < BAR_COUNT; ++i) mbar_inval(bar(i));    // nobody waits or arrives between items
     for (int s = 0; s < 2; ++s) {
       mbar_init(bar(BAR_Q_FULL + s), 1);
       mbar_init(bar(BAR_Q_EMPTY + s), 1);
@@ -165,23 +213,14 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     mbar_init(bar(BAR_DQ_DONE), 1);
     mbar_init(bar(BAR_DQ_FREE), 4);       // one arrive per flush warp
     mbar_init(bar(BAR_KV_TMEM), 8);       // one arrive per compute warp
-    *s_abort = 0;
     fence_barrier_init();
     fence_proxy_async();
-    mbar_arrive_expect_tx(bar(BAR_KV), 2 * kTileBytes);
-    tma_load_4d(smem_u32(sK), &tmK, bar(BAR_KV), 0, k_begin + n0, kvh, bb);
-    tma_load_4d(smem_u32(sV), &tmV, bar(BAR_KV), 0, k_begin + n0, kvh, bb);
-    load_q(0);
+    if (n_iter > 0) load_q(0);
     if (n_iter > 1) load_q(1);
-  }
-  if (warp == 9) {
-    tmem_alloc(smem_u32(s_tmem), kTmemCols);
-    tmem_relinquish();
   }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
-  const uint32_t tmem = *s_tmem;
 
   if (warp == 8) {
     // ============================ producer ============================
@@ -218,7 +257,7 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       __syncwarp();
     }
   } else if (warp == 9) {
-   if (lane == 0) {
+   if (lane == 0 && n_iter > 0) {
     // ============================ MMA issue ============================
     // Per query tile t and query half x: [S^T_x, dP^T_x] -> (compute) -> [dV += P^T_x.dO_x, dK += dS^T_x.Q_x]; after both
     // halves dQ = dS.K.  Issue order keeps the pipe fed while the compute warps work on the other half:
@@ -228,7 +267,7 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     const uint32_t id_st = instr_desc(DT, 0, 128, 64);     // S^T, dP^T of one half: B K-major, N = 64
     const uint32_t id_mn = instr_desc(DT, 1, 128, HD);     // dV, dK: B MN-major, N = 64
     const uint32_t id_dq = id_mn | (1u << 15);             // dQ: A (dS^T as stored) MN-major as well
-    const uint64_t kmn = smem_desc(smem_u32(sK), kTileBytes, 1024);
+    const uint64_t kmn = smem_desc(smem_u32(sKc), kTileBytes, 1024);
     // dS^T [query block of 64][key][128 B]: MN (query) blocks kTileBytes apart, 8-key groups 1024 apart
     const uint64_t dsd0 = smem_desc(smem_u32(sDS), kTileBytes, 1024);
     const uint64_t qd0 = smem_desc(smem_u32(sQ), 16, 1024), dod0 = smem_desc(smem_u32(sDO), 16, 1024);
@@ -299,6 +338,25 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     const uint32_t lane_base = static_cast<uint32_t>(wq * 32) << 16;
     const uint32_t stage = smem_u32(sDQ) + wq * 4096;         // this warp's 32 rows; the other column half is 16384 on
     const uint32_t row_addr = stage + lane * 128;
+    if (warp == 10) {
+      // This warp has the most slack at the start of an item (the first dQ is thousands of clocks away): it fetches the
+      // item after this one, starts its K load into the other K buffer and, when this item's V has been copied to
+      // TMEM (or, for an item without query tiles, has landed), its V load.
+      int nxt = -1;
+      if (lane == 0) {
+        nxt = fetch_next((w + 1) & 1);
+        if (nxt >= 0) {
+          mbar_arrive_expect_tx(bar(BAR_KV + (kbuf ^ 1)), 2 * kTileBytes);
+          load_k_of((w + 1) & 1, kbuf ? sK : sK1, bar(BAR_KV + (kbuf ^ 1)));
+        }
+      }
+      nxt = __shfl_sync(0xffffffffu, nxt, 0);
+      if (nxt >= 0) {
+        const bool pass = n_iter > 0 ? mbar_wait_bounded(bar(BAR_KV_TMEM), 0, s_abort)
+                                     : mbar_wait_bounded(bar(BAR_KV + kbuf), kv_par, s_abort);
+        if (__all_sync(0xffffffffu, pass) && lane == 0) load_v_of((w + 1) & 1, bar(BAR_KV + (kbuf ^ 1)));
+      }
+    }
     for (int it = 0; it < n_iter; ++it) {
       if (!__all_sync(0xffffffffu, mbar_wait_bounded(bar(BAR_DQ_DONE), it & 1, s_abort))) break;
       tc_fence_after();
@@ -340,11 +398,22 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     const int rloc = wq * 32 + lane;                         // key row (S^T, dK, dV) or query row (dQ) inside the tile
     const int key = n0 + rloc;
     const uint32_t lane_base = static_cast<uint32_t>(wq * 32) << 16;
-    bool ok = __all_sync(0xffffffffu, mbar_wait_bounded(bar(BAR_KV), 0, s_abort));
+    if (n_iter == 0) {
+      // no query sees these keys: dK = dV = 0
+      if (key < S) {
+        const int64_t o = bb * p.dk_bs + kvh * p.dk_hs + static_cast<int64_t>(k_begin + key) * p.dk_rs + hf * 32;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          reinterpret_cast<uint4*>(reinterpret_cast<uint16_t*>(p.dk) + o)[i] = make_uint4(0u, 0u, 0u, 0u);
+          reinterpret_cast<uint4*>(reinterpret_cast<uint16_t*>(p.dv) + o)[i] = make_uint4(0u, 0u, 0u, 0u);
+        }
+      }
+    } else {
+    bool ok = __all_sync(0xffffffffu, mbar_wait_bounded(bar(BAR_KV + kbuf), kv_par, s_abort));
     if (ok) {
       // K rows (warps 0-3) and V rows (warps 4-7) go to TMEM once, as the A operands of S^T and dP^T: their MMAs then
       // read only the query tiles from shared memory, whose bandwidth is what bounds this kernel
-      const uint32_t rowa = smem_u32(hf == 0 ? sK : sV) + rloc * 128;
+      const uint32_t rowa = smem_u32(hf == 0 ? sKc : sV) + rloc * 128;
       uint32_t kr[32];
 #pragma unroll
       for (int c = 0; c < 8; ++c)
@@ -472,7 +541,16 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         }
       }
     }
+    }  // n_iter > 0
   }
+
+  // ---- end of the item: every MMA has completed (the compute warps saw the last DQ_DONE), every copy has left
+  // shared memory; the barriers may be set up again
+  __syncwarp();
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  }  // work items
 
   // ---- teardown ----
   __syncwarp();
@@ -526,7 +604,19 @@ cudaError_t launch_bwd_sm100_main(const BwdParams& p, int dtype, int nbatch, int
   BwdArgs a;
   a.p = p;
   a.dtype = dtype;
-  dim3 grid((max_k + BK - 1) / BK, p.Hkv, nbatch);
+  a.gx = (max_k + BK - 1) / BK;
+  a.gy = p.Hkv;
+  const long long items = static_cast<long long>(a.gx) * a.gy * nbatch;
+  if (items > 0x7fffffffLL || p.work_counter == nullptr) return cudaErrorInvalidValue;
+  a.total_items = static_cast<int>(items);
+  a.counter = p.work_counter;
+  static int sm_count = 0;
+  if (sm_count == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sm_count <= 0) sm_count = 148;
+  }
+  dim3 grid(static_cast<unsigned>(items < sm_count ? items : sm_count), 1, 1);   // one persistent CTA per SM
   cudaError_t e;
   if (dtype == 0) {
     e = cudaFuncSetAttribute(bwd_sm100_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);

@@ -49,6 +49,7 @@ struct BwdParams {
   const float* lse;
   float* delta;          // workspace [B,Hq,N_pad]
   float* dq_acc;         // workspace fp32 [B,Hq,N,D]
+  int* work_counter;     // workspace: next work item of the persistent backward kernel (reset by the preprocess kernel)
   void* dq;
   void* dk;
   void* dv;

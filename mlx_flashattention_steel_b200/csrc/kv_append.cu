@@ -25,7 +25,7 @@ constexpr int kWarpsPerBlock = 8;
 
 // SrcT: __half or __nv_bfloat16.  POOL: 0 f16, 1 bf16, 3 int8, 4 e4m3 (the library's dtype codes).
 // Each lane moves 8 values (one 16-byte load), so a row takes D/8 lanes and a warp handles 32/(D/8) rows per step;
-// warps walk the rows with a grid stride, two steps in flight, from a grid of a few CTAs per SM.
+// warps walk the rows with a grid stride, three steps in flight, from a grid of a few CTAs per SM.
 template <typename SrcT, int POOL, int D>
 __global__ void __launch_bounds__(kWarpsPerBlock * 32)
 kv_append_kernel(const SrcT* __restrict__ k_new, const SrcT* __restrict__ v_new, int64_t token_stride, int64_t head_stride,
@@ -42,35 +42,48 @@ kv_append_kernel(const SrcT* __restrict__ k_new, const SrcT* __restrict__ v_new,
   const int64_t warp_id = static_cast<int64_t>(blockIdx.x) * kWarpsPerBlock + (threadIdx.x >> 5);
   const int64_t n_warps = static_cast<int64_t>(gridDim.x) * kWarpsPerBlock;
 
-  // one row per lane group; the next step's row is fetched before the current one is quantised and stored
+  // one row per lane group; the rows of the next two steps are fetched before the current one is quantised and
+  // stored.  The values are loaded whether or not the slot turns out to be writable: the source row exists for every
+  // token, and a load that waited for the slot would put two memory latencies in series.
   struct Row {
     uint4 raw;
     int64_t slot;
     int h;
     bool write;
   };
-  auto fetch = [&](int64_t r0) -> Row {
+  // (token, head) of the row this lane group fetches next: advanced by one grid stride per fetch, so that the 64-bit
+  // division happens once per thread and not once per row
+  const int64_t step = n_warps * RPW;
+  const int64_t first = warp_id * RPW + sub;
+  const int step_t = static_cast<int>(step / Hkv), step_h = static_cast<int>(step % Hkv);
+  int64_t f_row = first;
+  int f_t = static_cast<int>(first / Hkv), f_h = static_cast<int>(first % Hkv);
+  auto fetch = [&]() -> Row {
     Row r;
     r.raw = make_uint4(0u, 0u, 0u, 0u);
     r.slot = -1;
-    r.h = 0;
-    const int64_t rowid = r0 + sub;
-    int t = 0;
-    if (rowid < rows) {
-      t = static_cast<int>(rowid / Hkv);
-      r.h = static_cast<int>(rowid % Hkv);
+    r.h = f_h;
+    const int t = f_t;
+    if (f_row < rows) {
       r.slot = __ldg(slots + t);
+      r.raw = __ldg(reinterpret_cast<const uint4*>(new_base + t * token_stride + r.h * head_stride + l * 8));
     }
     r.write = r.slot >= 0 && r.slot < total_slots;      // padding entries and slots outside the pool write nothing
-    if (r.write) r.raw = __ldg(reinterpret_cast<const uint4*>(new_base + t * token_stride + r.h * head_stride + l * 8));
+    f_row += step;
+    f_t += step_t;
+    f_h += step_h;
+    if (f_h >= Hkv) {
+      f_h -= Hkv;
+      ++f_t;
+    }
     return r;
   };
 
-  const int64_t step = n_warps * RPW;
-  Row nxt = fetch(warp_id * RPW);
+  Row nxt = fetch(), nxt2 = fetch();                    // fetch() of a row past the end loads nothing
   for (int64_t r0 = warp_id * RPW; r0 < rows; r0 += step) {
     const Row cur = nxt;
-    if (r0 + step < rows) nxt = fetch(r0 + step);
+    nxt = nxt2;
+    nxt2 = fetch();
     const uint4 raw = cur.raw;
     const int64_t slot = cur.slot;
     const int h = cur.h;
@@ -124,8 +137,11 @@ kv_append_kernel(const SrcT* __restrict__ k_new, const SrcT* __restrict__ v_new,
         const float2 a = make_float2(x[i], x[i + 1]);
         const float2 q0 = __fmul2_rn(a, rb2);
         const float2 y = __ffma2_rn(__ffma2_rn(q0, nb2, a), rb2, q0);
-        qi[i] = max(-127, __float2int_rn(y.x));
-        qi[i + 1] = max(-127, __float2int_rn(y.y));
+        // round to nearest even without the conversion unit: adding 1.5 * 2^23 leaves the integer in the low mantissa
+        // bits (exact for |y| < 2^22; y is at most 127.5 here and is clamped from below first)
+        const float2 r = __fadd2_rn(make_float2(fmaxf(y.x, -127.f), fmaxf(y.y, -127.f)), make_float2(12582912.f, 12582912.f));
+        qi[i] = __float_as_int(r.x) - 0x4B400000;
+        qi[i + 1] = __float_as_int(r.y) - 0x4B400000;
       }
 #pragma unroll
       for (int w = 0; w < 2; ++w) {

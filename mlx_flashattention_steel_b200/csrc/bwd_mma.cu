@@ -65,18 +65,19 @@ __global__ void __launch_bounds__(256) bwd_preprocess_kernel(const BwdParams p, 
 // The same with 16-byte accesses: D / 8 lanes per row, each with 8 elements of O and dO and 8 accumulator words to
 // clear (one warp per row left every lane with 4 bytes per load and ran at 2.8 TB/s).  Needs 16-byte aligned rows.
 template <typename T, int D>
-__global__ void __launch_bounds__(256) bwd_preprocess_vec_kernel(const BwdParams p, long long total_rows) {
+__global__ void __launch_bounds__(256) bwd_preprocess_vec_kernel(const BwdParams p) {
   constexpr int LPR = D / 8;                                   // lanes per row: 8 or 16
-  const long long t = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
-  if (t == 0 && p.work_counter != nullptr) *p.work_counter = 0;
-  const long long row = t / LPR;
+  // grid = (rows of one head in blocks of 256 / LPR, Hq, B): no division by run-time values per thread
+  const int h = blockIdx.y;
+  const long long b = blockIdx.z;
+  const unsigned t = blockIdx.x * blockDim.x + threadIdx.x;
+  if (t == 0 && h == 0 && b == 0 && p.work_counter != nullptr) *p.work_counter = 0;
+  const int i = static_cast<int>(t / LPR);
   const int c = static_cast<int>(t % LPR);
-  const bool live = row < total_rows;                          // whole rows share a warp: the shuffles below stay legal
+  const bool live = i < p.N;                                   // whole rows share a warp: the shuffles below stay legal
+  const long long row = (b * p.Hq + h) * p.N + i;
   float acc = 0.f;
   if (live) {
-    const int i = static_cast<int>(row % p.N);
-    const int h = static_cast<int>((row / p.N) % p.Hq);
-    const long long b = row / (static_cast<long long>(p.N) * p.Hq);
     const T* o = reinterpret_cast<const T*>(p.o) + b * p.o_bs + h * p.o_hs + static_cast<int64_t>(i) * p.o_rs + c * 8;
     const T* dout = reinterpret_cast<const T*>(p.dout) + row * D + c * 8;
     const uint4 ow = *reinterpret_cast<const uint4*>(o), dw = *reinterpret_cast<const uint4*>(dout);
@@ -366,9 +367,10 @@ cudaError_t launch_t(const BwdParams& p, int dtype, bool varlen, int nbatch, int
   {
     const bool rows16 = reinterpret_cast<uintptr_t>(p.o) % 16 == 0 && reinterpret_cast<uintptr_t>(p.dout) % 16 == 0 &&
                         p.o_rs % 8 == 0 && p.o_hs % 8 == 0 && p.o_bs % 8 == 0;
-    if (rows16) {
-      const long long threads = static_cast<long long>(total_rows) * (D / 8);
-      bwd_preprocess_vec_kernel<T, D><<<static_cast<unsigned>((threads + 255) / 256), 256, 0, stream>>>(p, total_rows);
+    if (rows16 && p.Hq <= 65535 && p.B <= 65535) {
+      const long long threads = static_cast<long long>(p.N) * (D / 8);
+      const dim3 pgrid(static_cast<unsigned>((threads + 255) / 256), p.Hq, p.B);
+      bwd_preprocess_vec_kernel<T, D><<<pgrid, 256, 0, stream>>>(p);
     } else {
       const int blocks = (total_rows + 7) / 8;
       bwd_preprocess_kernel<T, D><<<blocks, 256, 0, stream>>>(p, total_rows);

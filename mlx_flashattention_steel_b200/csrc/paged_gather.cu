@@ -10,20 +10,21 @@ namespace b200fa {
 
 namespace {
 
+// I: index type of the flattened chunk space (32-bit whenever it fits: the index is split by run-time divisors per chunk)
+template <typename I>
 __global__ void __launch_bounds__(256) paged_kv_gather_kernel(
     const uint4* __restrict__ pool, const int32_t* __restrict__ block_table,
     const int32_t* __restrict__ seq_lens, int H, int chunks_per_row /* D*elem_bytes/16 */,
     int block_size, int max_blocks, int max_kv_len, long long total_chunks, uint4* __restrict__ out) {
-  const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
-  for (long long idx = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; idx < total_chunks;
-       idx += stride) {
+  const I stride = static_cast<I>(gridDim.x) * blockDim.x, total = static_cast<I>(total_chunks);
+  for (I idx = static_cast<I>(blockIdx.x) * blockDim.x + threadIdx.x; idx < total; idx += stride) {
     // idx = ((b*H + h)*max_kv_len + t)*chunks_per_row + c
-    const int c = static_cast<int>(idx % chunks_per_row);
-    long long rem = idx / chunks_per_row;
-    const int t = static_cast<int>(rem % max_kv_len);
-    rem /= max_kv_len;
-    const int h = static_cast<int>(rem % H);
-    const int b = static_cast<int>(rem / H);
+    const int c = static_cast<int>(idx % static_cast<I>(chunks_per_row));
+    I rem = idx / static_cast<I>(chunks_per_row);
+    const int t = static_cast<int>(rem % static_cast<I>(max_kv_len));
+    rem /= static_cast<I>(max_kv_len);
+    const int h = static_cast<int>(rem % static_cast<I>(H));
+    const int b = static_cast<int>(rem / static_cast<I>(H));
     uint4 val = make_uint4(0u, 0u, 0u, 0u);
     if (t < seq_lens[b]) {
       const int page = block_table[static_cast<long long>(b) * max_blocks + t / block_size];
@@ -95,9 +96,14 @@ cudaError_t launch_paged_gather(const void* pool, const int32_t* block_table, co
   long long blocks = (total + 255) / 256;
   const long long cap = 148LL * 32;
   if (blocks > cap) blocks = cap;
-  paged_kv_gather_kernel<<<static_cast<unsigned>(blocks), 256, 0, stream>>>(
-      reinterpret_cast<const uint4*>(pool), block_table, seq_lens, H, cpr, block_size, max_blocks,
-      max_kv_len, total, reinterpret_cast<uint4*>(out));
+  if (total < (1LL << 31))
+    paged_kv_gather_kernel<uint32_t><<<static_cast<unsigned>(blocks), 256, 0, stream>>>(
+        reinterpret_cast<const uint4*>(pool), block_table, seq_lens, H, cpr, block_size, max_blocks,
+        max_kv_len, total, reinterpret_cast<uint4*>(out));
+  else
+    paged_kv_gather_kernel<long long><<<static_cast<unsigned>(blocks), 256, 0, stream>>>(
+        reinterpret_cast<const uint4*>(pool), block_table, seq_lens, H, cpr, block_size, max_blocks,
+        max_kv_len, total, reinterpret_cast<uint4*>(out));
   return cudaGetLastError();
 }
 

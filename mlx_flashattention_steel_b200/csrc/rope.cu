@@ -18,7 +18,9 @@ namespace b200fa {
 
 namespace {
 
-template <typename T>
+// I: index type of the flattened (batch, head, row, chunk) space: 32-bit whenever it fits, because the index is split by
+// run-time divisors for every 16-byte chunk and a 64-bit division costs several times the rest of the work
+template <typename T, typename I>
 __global__ void __launch_bounds__(256)
 rope_kernel(const T* __restrict__ x, T* __restrict__ out, const float* __restrict__ cosb, const float* __restrict__ sinb,
             const int* __restrict__ offsets, int offset, int B, int H, int N, int D, int rot, int interleaved, int inverse,
@@ -27,14 +29,14 @@ rope_kernel(const T* __restrict__ x, T* __restrict__ out, const float* __restric
   // chunks a thread may own per row: all D/8 (interleaved); first-half chunks + pass-through chunks (split halves)
   const int rot_chunks = rot >> 3, half_chunks = half >> 3, tail_chunks = (D - rot) >> 3;
   const int per_row = interleaved ? (D >> 3) : (half_chunks + tail_chunks);
-  const int64_t total = static_cast<int64_t>(B) * H * N * per_row;
-  for (int64_t idx = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; idx < total;
-       idx += static_cast<int64_t>(gridDim.x) * blockDim.x) {
-    const int c = static_cast<int>(idx % per_row);
-    int64_t r = idx / per_row;
-    const int n = static_cast<int>(r % N);
-    r /= N;
-    const int h = static_cast<int>(r % H), b = static_cast<int>(r / H);
+  const I total = static_cast<I>(B) * H * N * per_row;
+  for (I idx = static_cast<I>(blockIdx.x) * blockDim.x + threadIdx.x; idx < total;
+       idx += static_cast<I>(gridDim.x) * blockDim.x) {
+    const int c = static_cast<int>(idx % static_cast<I>(per_row));
+    I r = idx / static_cast<I>(per_row);
+    const int n = static_cast<int>(r % static_cast<I>(N));
+    r /= static_cast<I>(N);
+    const int h = static_cast<int>(r % static_cast<I>(H)), b = static_cast<int>(r / static_cast<I>(H));
     const T* xr = x + b * x_bs + h * x_hs + static_cast<int64_t>(n) * x_rs;
     T* orow = out + b * o_bs + h * o_hs + static_cast<int64_t>(n) * o_rs;
     const int pos = (offsets != nullptr ? offsets[b] : offset) + n;
@@ -92,15 +94,16 @@ cudaError_t launch_rope(int dtype, const void* x, void* out, const float* cosb, 
   if (total <= 0) return cudaSuccess;
   const int64_t want = (total + 255) / 256;
   const unsigned grid = static_cast<unsigned>(want < 148 * 16 ? want : 148 * 16);
-  if (dtype == 0)
-    rope_kernel<__half><<<grid, 256, 0, stream>>>(static_cast<const __half*>(x), static_cast<__half*>(out), cosb, sinb, offsets,
-                                                  offset, B, H, N, D, rot, interleaved, inverse, xs[0], xs[1], xs[2], os[0],
-                                                  os[1], os[2]);
-  else
-    rope_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(x),
-                                                         static_cast<__nv_bfloat16*>(out), cosb, sinb, offsets, offset, B, H,
-                                                         N, D, rot, interleaved, inverse, xs[0], xs[1], xs[2], os[0], os[1],
-                                                         os[2]);
+  const bool small = total < (1LL << 31);
+#define B200FA_ROPE_LAUNCH(T, I)                                                                                         \
+  rope_kernel<T, I><<<grid, 256, 0, stream>>>(static_cast<const T*>(x), static_cast<T*>(out), cosb, sinb, offsets, offset, B, \
+                                              H, N, D, rot, interleaved, inverse, xs[0], xs[1], xs[2], os[0], os[1], os[2])
+  if (dtype == 0) {
+    if (small) B200FA_ROPE_LAUNCH(__half, uint32_t); else B200FA_ROPE_LAUNCH(__half, int64_t);
+  } else {
+    if (small) B200FA_ROPE_LAUNCH(__nv_bfloat16, uint32_t); else B200FA_ROPE_LAUNCH(__nv_bfloat16, int64_t);
+  }
+#undef B200FA_ROPE_LAUNCH
   return cudaGetLastError();
 }
 

@@ -470,10 +470,13 @@ fa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
           }
         }
       } else {
+        // without softcap or bias a masked tile keeps the raw dot products: the mask writes -inf, the max is taken
+        // on them and mode 0 folds the scale into the exponent's FMA as on an unmasked tile
+        const bool raw = !use_cap && monotone && !(FEAT && p.alibi != nullptr);
         if (use_cap) {
 #pragma unroll
           for (int i = 0; i < BN; ++i) x[i] = cap_out * fast_tanh(x[i] * cap_in);
-        } else {
+        } else if (!raw) {
 #pragma unroll
           for (int i = 0; i < BN; ++i) x[i] *= p.scale_log2;
         }
@@ -511,6 +514,10 @@ fa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
           }
         }
         m_tile = tree_max64(x);
+        if (raw) {
+          mode = 0;
+          m_tile *= p.scale_log2;                      // -inf (a fully masked row) stays -inf: the scale is positive
+        }
       }
 
       // lazy rescale: keep the old reference max unless the row max grew by more than 2^8

@@ -31,7 +31,10 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32)
 kv_append_kernel(const SrcT* __restrict__ k_new, const SrcT* __restrict__ v_new, int64_t token_stride, int64_t head_stride,
                  const int64_t* __restrict__ slots, void* __restrict__ k_pool, void* __restrict__ v_pool,
                  __half* __restrict__ k_scale, __half* __restrict__ v_scale, int T, int Hkv, int64_t total_slots) {
-  constexpr int LPR = D / 8;             // lanes per row: 16 (D = 128) or 8 (D = 64)
+  // values per lane: 8 (one 16-byte load) for 16-bit pools, 16 for 8-bit pools, whose per-row work (row maximum over
+  // the lanes, scale, reciprocal) and per-lane overhead then spread over twice the values and whose stores are 16 bytes
+  constexpr int VPL = (POOL >= 3) ? 16 : 8;
+  constexpr int LPR = D / VPL;           // lanes per row
   constexpr int RPW = 32 / LPR;          // rows per warp step
   const int lane = threadIdx.x & 31, sub = lane / LPR, l = lane % LPR;
   const bool is_v = blockIdx.y != 0;
@@ -46,7 +49,7 @@ kv_append_kernel(const SrcT* __restrict__ k_new, const SrcT* __restrict__ v_new,
   // stored.  The values are loaded whether or not the slot turns out to be writable: the source row exists for every
   // token, and a load that waited for the slot would put two memory latencies in series.
   struct Row {
-    uint4 raw;
+    uint4 raw[VPL / 8];
     int64_t slot;
     int h;
     bool write;
@@ -60,13 +63,16 @@ kv_append_kernel(const SrcT* __restrict__ k_new, const SrcT* __restrict__ v_new,
   int f_t = static_cast<int>(first / Hkv), f_h = static_cast<int>(first % Hkv);
   auto fetch = [&]() -> Row {
     Row r;
-    r.raw = make_uint4(0u, 0u, 0u, 0u);
+#pragma unroll
+    for (int j = 0; j < VPL / 8; ++j) r.raw[j] = make_uint4(0u, 0u, 0u, 0u);
     r.slot = -1;
     r.h = f_h;
     const int t = f_t;
     if (f_row < rows) {
       r.slot = __ldg(slots + t);
-      r.raw = __ldg(reinterpret_cast<const uint4*>(new_base + t * token_stride + r.h * head_stride + l * 8));
+#pragma unroll
+      for (int j = 0; j < VPL / 8; ++j)
+        r.raw[j] = __ldg(reinterpret_cast<const uint4*>(new_base + t * token_stride + r.h * head_stride + l * VPL + j * 8));
     }
     r.write = r.slot >= 0 && r.slot < total_slots;      // padding entries and slots outside the pool write nothing
     f_row += step;
@@ -84,18 +90,18 @@ kv_append_kernel(const SrcT* __restrict__ k_new, const SrcT* __restrict__ v_new,
     const Row cur = nxt;
     nxt = nxt2;
     nxt2 = fetch();
-    const uint4 raw = cur.raw;
     const int64_t slot = cur.slot;
     const int h = cur.h;
     const bool write = cur.write;
-    float x[8];
-    {
-      const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+    float x[VPL];
+#pragma unroll
+    for (int j = 0; j < VPL / 8; ++j) {
+      const uint32_t w[4] = {cur.raw[j].x, cur.raw[j].y, cur.raw[j].z, cur.raw[j].w};
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
         const float2 f = Elem<SrcT>::unpack(w[i]);
-        x[2 * i] = f.x;
-        x[2 * i + 1] = f.y;
+        x[8 * j + 2 * i] = f.x;
+        x[8 * j + 2 * i + 1] = f.y;
       }
     }
     const int64_t dst_row = slot * Hkv + h;             // pools are [page, offset, head, D]: row index = slot * Hkv + h
@@ -112,7 +118,7 @@ kv_append_kernel(const SrcT* __restrict__ k_new, const SrcT* __restrict__ v_new,
     // 8-bit pool: row max over the row's lanes, scale, quantise
     float amax = 0.f;
 #pragma unroll
-    for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(x[i]));
+    for (int i = 0; i < VPL; ++i) amax = fmaxf(amax, fabsf(x[i]));
 #pragma unroll
     for (int o = LPR / 2; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
     // Correctly rounded quotients without the division routine: with r = rn(1/b), q0 = rn(a*r), the residual
@@ -126,14 +132,14 @@ kv_append_kernel(const SrcT* __restrict__ k_new, const SrcT* __restrict__ v_new,
     if (__half2float(sc) == 0.f) sc = __float2half_rn(1.f);
     const float scf = __half2float(sc);
     const float rcp = __frcp_rn(scf);
-    uint32_t packed[2];
+    uint32_t packed[VPL / 4];
     if (POOL == 3) {
       // the same Newton step on value pairs (packed f32x2 ops), round to nearest even, clamp to [-127, 127]
       // (saturating pack covers the top, one max the bottom), four values per pack pair
       const float2 rb2 = make_float2(rcp, rcp), nb2 = make_float2(-scf, -scf);
-      int qi[8];
+      int qi[VPL];
 #pragma unroll
-      for (int i = 0; i < 8; i += 2) {
+      for (int i = 0; i < VPL; i += 2) {
         const float2 a = make_float2(x[i], x[i + 1]);
         const float2 q0 = __fmul2_rn(a, rb2);
         const float2 y = __ffma2_rn(__ffma2_rn(q0, nb2, a), rb2, q0);
@@ -144,25 +150,29 @@ kv_append_kernel(const SrcT* __restrict__ k_new, const SrcT* __restrict__ v_new,
         qi[i + 1] = __float_as_int(r.y) - 0x4B400000;
       }
 #pragma unroll
-      for (int w = 0; w < 2; ++w) {
+      for (int w = 0; w < VPL / 4; ++w) {
         // cvt.pack d, a, b, c = (c << 16) | (sat8(a) << 8) | sat8(b): the upper pair first, then the lower pair on top
         uint32_t hi;
         asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, %3;" : "=r"(hi) : "r"(qi[4 * w + 3]), "r"(qi[4 * w + 2]), "r"(0));
         asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, %3;" : "=r"(packed[w]) : "r"(qi[4 * w + 1]), "r"(qi[4 * w]), "r"(hi));
       }
     } else {
-      uint32_t q[8];
+      uint32_t q[VPL];
 #pragma unroll
-      for (int i = 0; i < 8; ++i) {
+      for (int i = 0; i < VPL; ++i) {
         const float y = div_rn(x[i], scf, rcp);
         q[i] = static_cast<uint32_t>(__nv_cvt_float_to_fp8(fminf(fmaxf(y, -448.f), 448.f), __NV_SATFINITE, __NV_E4M3));
       }
-      packed[0] = q[0] | (q[1] << 8) | (q[2] << 16) | (q[3] << 24);
-      packed[1] = q[4] | (q[5] << 8) | (q[6] << 16) | (q[7] << 24);
+#pragma unroll
+      for (int w = 0; w < VPL / 4; ++w) packed[w] = q[4 * w] | (q[4 * w + 1] << 8) | (q[4 * w + 2] << 16) | (q[4 * w + 3] << 24);
     }
     if (write) {
-      *reinterpret_cast<uint2*>(reinterpret_cast<uint8_t*>(pool) + dst_row * D + l * 8) =
-          make_uint2(packed[0], packed[1]);
+      if constexpr (VPL == 16) {
+        *reinterpret_cast<uint4*>(reinterpret_cast<uint8_t*>(pool) + dst_row * D + l * 16) =
+            make_uint4(packed[0], packed[1], packed[2], packed[3]);
+      } else {
+        *reinterpret_cast<uint2*>(reinterpret_cast<uint8_t*>(pool) + dst_row * D + l * 8) = make_uint2(packed[0], packed[1]);
+      }
       if (l == 0) scale_out[dst_row] = sc;
     }
   }
@@ -172,7 +182,7 @@ template <typename SrcT, int POOL>
 cudaError_t launch_d(int D, const void* k_new, const void* v_new, int64_t ts, int64_t hs, const int64_t* slots, void* k_pool,
                      void* v_pool, void* k_scale, void* v_scale, int T, int Hkv, int64_t total_slots, cudaStream_t stream) {
   const int64_t rows = static_cast<int64_t>(T) * Hkv;
-  const int rpw = 32 / (D / 8);
+  const int rpw = 32 / (D / (POOL >= 3 ? 16 : 8));
   // enough CTAs to cover the rows once, capped at 8 per SM on each of K and V (148 SMs): the rest is the grid stride
   const int64_t want = (rows + static_cast<int64_t>(kWarpsPerBlock) * rpw - 1) / (static_cast<int64_t>(kWarpsPerBlock) * rpw);
   dim3 grid(static_cast<unsigned>(want < 148 * 8 ? want : 148 * 8), 2);

@@ -58,12 +58,10 @@ template <int HD> struct Cfg {
 enum Bar {
   BAR_Q = 0,
   BAR_K_FULL = 1,            // +stage
-  BAR_K_EMPTY = 3,
   BAR_V_FULL = 5,
-  BAR_V_EMPTY = 7,
-  BAR_S_FULL = 9,            // +buffer
+  BAR_PV_DONE = 7,           // +stage: P.V of a tile has completed -- O may be rescaled, the V stage is free again
+  BAR_S_FULL = 9,            // +buffer: S of a tile is complete -- for the softmax warps, and the K stage is free again
   BAR_P_FULL = 11,           // +buffer
-  BAR_PV_DONE = 13,
   BAR_O_STAGED = 14,         // count 4: the softmax warps have written their O rows to shared memory
   BAR_O_FINAL = 15,          // committed once, after the last P.V: O is complete
   BAR_COUNT = 16
@@ -270,13 +268,11 @@ fa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     mbar_init(bar(BAR_Q), 1);
     for (int s = 0; s < kStages; ++s) {
       mbar_init(bar(BAR_K_FULL + s), 1);
-      mbar_init(bar(BAR_K_EMPTY + s), 1);
       mbar_init(bar(BAR_V_FULL + s), 1);
-      mbar_init(bar(BAR_V_EMPTY + s), 1);
+      mbar_init(bar(BAR_PV_DONE + s), 1);
       mbar_init(bar(BAR_S_FULL + s), 1);
       mbar_init(bar(BAR_P_FULL + s), 4);     // one arrive per softmax warp
     }
-    mbar_init(bar(BAR_PV_DONE), 1);
     mbar_init(bar(BAR_O_STAGED), 4);
     mbar_init(bar(BAR_O_FINAL), 1);
     *s_abort = 0;
@@ -307,10 +303,13 @@ fa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       for (int j = kStages; j < n_tiles; ++j) {
         const int st = j & 1;
         const uint32_t par = ((j >> 1) & 1) ^ 1;
-        // K(j) and V(j) reuse the stage of tile j-2: wait until its S MMAs, then its PV MMAs, have read it
-        if (!mbar_wait_bounded(bar(BAR_K_EMPTY + st), par, s_abort)) break;
+        // K(j) and V(j) reuse the stage of tile j-2: wait until its S MMAs, then its PV MMAs, have read it.  These
+        // are the barriers the softmax warps wait on too: every commit costs the MMA thread a bubble, so one commit
+        // serves both readers.  Neither can be more than one completion ahead of this thread: S(j) needs K(j) and
+        // P.V(j) needs V(j), which are loaded below.
+        if (!mbar_wait_bounded(bar(BAR_S_FULL + st), par, s_abort)) break;
         load_k(j);
-        if (!mbar_wait_bounded(bar(BAR_V_EMPTY + st), par, s_abort)) break;
+        if (!mbar_wait_bounded(bar(BAR_PV_DONE + st), par, s_abort)) break;
         load_v(j);
       }
     }
@@ -338,8 +337,7 @@ fa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
           mma_ss(d_tmem, qd + (k >> 2) * kHalfQ + (k & 3) * 2, kd + (k >> 2) * kHalfK + (k & 3) * 2, idesc_qk,
                  k > 0 ? 1u : 0u);
         }
-        tc_commit(bar(BAR_S_FULL + st));        // the softmax warps first, then the producer
-        tc_commit(bar(BAR_K_EMPTY + st));
+        tc_commit(bar(BAR_S_FULL + st));        // for the softmax warps and for the producer
         return true;
       };
       if (ok) ok = issue_s(0);
@@ -361,8 +359,7 @@ fa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
           // a k-step is 16 keys = 2048 B (128 units).  A = P in TMEM: 16 16-bit values = 8 columns per k-step.
           mma_ts(tO, a_tmem + k * 8, vd + k * 128, idesc_pv, (j > 0 || k > 0) ? 1u : 0u);
         }
-        tc_commit(bar(BAR_PV_DONE));
-        tc_commit(bar(BAR_V_EMPTY + st));
+        tc_commit(bar(BAR_PV_DONE + st));       // for the softmax warps' rescale and for the producer
         if (j + 1 == n_tiles) tc_commit(bar(BAR_O_FINAL));
       }
     }
@@ -528,7 +525,8 @@ fa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         l_run *= corr;
         if (j > 0) {
           // O is being accumulated by PV(j-1): wait for it, then scale this row in TMEM
-          if (!__all_sync(0xffffffffu, mbar_wait_bounded(bar(BAR_PV_DONE), (j - 1) & 1, s_abort))) { ok = false; break; }
+          // P.V(j-1): completion (j-1)>>1 of its stage's barrier; the next one there needs this tile's successor's P
+          if (!__all_sync(0xffffffffu, mbar_wait_bounded(bar(BAR_PV_DONE + ((j - 1) & 1)), ((j - 1) >> 1) & 1, s_abort))) { ok = false; break; }
           tc_fence_after();
 #pragma unroll
           for (int c = 0; c < HD / 32; ++c) {

@@ -49,7 +49,6 @@ extern "C" {
 
 /* flags */
 #define B200FA_FLAG_FORCE_MMA_SYNC  1  /* use the portable mma.sync kernels even where a tcgen05 kernel exists */
-#define B200FA_FLAG_DETERMINISTIC   2  /* backward: dQ accumulated in a fixed order */
 
 /*
  * Problem descriptor.  Plays the role of MFAttention::Params + MFASteelParams
@@ -73,11 +72,11 @@ typedef struct b200fa_desc {
   int32_t flags;
   const float* alibi_slopes; /* NULL = off; device float32 [Hq]: slope[h] * (j - (i + S - N)) is added to the scaled
                                 (and soft-capped) score of row i, key j (csrc/mfa_steel_fwd.cpp:951-970).  Dense
-                                forward and backward only; served by the portable kernels. */
+                                layout only, forward and backward. */
   const uint8_t* block_mask; /* NULL = off; device bytes [ceil(N/mask_bq), mask_nk]: row i sees key j only if
                                 block_mask[i / mask_bq][j / mask_bk] != 0 (flash_attention_sparse,
                                 mlx_mfa/attention.py:1219-1311).  Key tiles without an active block are skipped.
-                                Dense 16-bit forward and backward; served by the portable kernels. */
+                                Dense layout, 16-bit, forward and backward. */
   int32_t mask_bq, mask_bk, mask_nk;
 } b200fa_desc;
 
@@ -99,6 +98,8 @@ const char* b200fa_version(void);
  * Forward, dense layout.  Replaces mfa_attention_forward (csrc/bindings.cpp:21-35)
  * and mfa_forward_with_lse (csrc/bindings.cpp:38-57); host dispatch role of
  * MFAttention::eval_gpu (csrc/mfa_attention.cpp:47-409).  `lse` may be NULL.
+ * The forward kernels need no scratch: both *_fwd*_workspace_bytes queries always return 0 (they exist so that a
+ * binding can treat every operator alike) and the workspace arguments are ignored.
  */
 size_t  b200fa_fwd_workspace_bytes(const b200fa_desc* d);
 int32_t b200fa_fwd(const b200fa_desc* d, const void* q, const void* k, const void* v,
@@ -159,9 +160,12 @@ int32_t b200fa_bwd_varlen(const b200fa_desc* d, const void* q, const void* k, co
  *                  mlx_mfa/integrations/mlx_lm.py:97-110 with one group per row)
  *   block_table    int32 [B, max_blocks], -1 = no page
  *   seq_lens       int32 [B]
- *   d->N is the number of query rows per sequence (<= 16), d->S is ignored;
+ *   d->N is the number of query rows per sequence, with (Hq/Hkv) * N <= 8; d->S is ignored;
  *   causal is per-sequence lower-right aligned.
- * `num_pages` is used only to validate the arguments' sizes.
+ * `num_pages` bounds the block_table entries (larger ones are treated as holes and reported through the error word).
+ * Slots of a sequence's last page beyond seq_lens[b] may hold anything, NaN patterns included: they are masked
+ * before they reach the arithmetic.  The workspace size depends on B, Hq, Hkv, N and num_splits only; max_kv_len is
+ * taken by the query so that the signature can stay when that changes.
  */
 size_t  b200fa_decode_paged_workspace_bytes(const b200fa_desc* d, int32_t max_kv_len);
 int32_t b200fa_decode_paged(const b200fa_desc* d, const void* q,
@@ -207,6 +211,15 @@ int32_t b200fa_decode_paged_static(const b200fa_desc* d, const void* q,
                                    int32_t num_pages, int32_t block_size, int32_t max_blocks,
                                    int32_t max_kv_len,
                                    void* out, float* lse, void* stream);
+
+/*
+ * Error word of the last b200fa_decode_paged_static call on the current device (same bits as
+ * b200fa_workspace_status: 0 = ok, bit 0 = a bounded wait inside the kernel gave up and the outputs are undefined,
+ * bit 1 = a block_table entry pointed beyond num_pages and was treated as a hole).  The word lives at the start of
+ * the built-in scratch, whose address a caller of the static entry never sees; this reads it.  Waits for `stream`.
+ * Like the static entry itself it has no counterpart in the reference and allocates nothing.
+ */
+int32_t b200fa_decode_paged_static_status(void* stream, int32_t* status_out);
 
 /*
  * Transpose of b200fa_paged_kv_gather, for the backward pass through a page pool: grad [B, H, max_kv_len, D]

@@ -19,7 +19,6 @@ ERR_DEVICE = -5
 
 F16, BF16, F32, I8, E4M3 = 0, 1, 2, 3, 4
 FLAG_FORCE_MMA_SYNC = 1
-FLAG_DETERMINISTIC = 2
 
 
 class Desc(C.Structure):
@@ -87,6 +86,7 @@ SIGNATURES = {
     "b200fa_decode_paged_workspace_bytes": (_Z, [_DP, _I]),
     "b200fa_decode_paged": (_I, [_DP, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _P, _P, _P, _Z, _P]),
     "b200fa_decode_paged_static": (_I, [_DP, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _P, _P, _P]),
+    "b200fa_decode_paged_static_status": (_I, [_P, C.POINTER(C.c_int32)]),
     "b200fa_paged_kv_scatter_add": (_I, [_P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P, _P]),
     "b200fa_kv_append": (_I, [_I, _I, _I, _I, _I, _I, C.c_int64, _P, _P, C.c_int64, C.c_int64, _P, _P, _P, _P, _P, _P]),
     "b200fa_rope": (_I, [_I, _I, _I, _I, _I, _I, _I, _I, _P, C.POINTER(C.c_int64), _P, C.POINTER(C.c_int64), _P, _P, _I, _P, _I, _P]),

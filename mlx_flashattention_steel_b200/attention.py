@@ -144,6 +144,9 @@ def _fwd_raw(q, k, v, scale, causal, softcap, window_left, want_lse, stream, out
     B, Hq, N, D = q.shape
     Hkv, S = k.shape[1], k.shape[2]
     q, k, v = _row_contig(q), _row_contig(k), _row_contig(v)
+    if Hkv > 1 and S > 0 and k.stride(1) == 0 and v.stride(1) == 0:
+        # one kv head broadcast over the head axis (k.expand(...)): that is MQA, and the kernels read the single head
+        k, v, Hkv = k[:, :1], v[:, :1], 1
     if out is None:
         out = torch.empty((B, Hq, N, D), dtype=q.dtype, device=q.device)
     if want_lse and lse is None:
@@ -160,7 +163,8 @@ def _fwd_raw(q, k, v, scale, causal, softcap, window_left, want_lse, stream, out
     return out, lse
 
 
-def _bwd_raw(q, k, v, out, lse, dout, scale, causal, stream, cu=None, alibi=None, bmask=None):
+def _bwd_raw(q, k, v, out, lse, dout, scale, causal, stream, cu=None, alibi=None, bmask=None, softcap=0.0,
+             window_left=-1):
     _require_cuda(q, k, v, out, lse, dout)
     lib = _lib.load()
     B, Hq, N, D = q.shape
@@ -172,7 +176,8 @@ def _bwd_raw(q, k, v, out, lse, dout, scale, causal, stream, cu=None, alibi=None
     dk = torch.empty((B, Hkv, S, D), dtype=q.dtype, device=q.device)
     dv = torch.empty((B, Hkv, S, D), dtype=q.dtype, device=q.device)
     code = _DTYPE_CODE[q.dtype]
-    d = _desc(code, code, B, Hq, Hkv, N, S, D, scale, causal, flags=_FORCE_FLAGS, q=q, k=k, v=v, o=out, alibi=alibi, bmask=bmask)
+    d = _desc(code, code, B, Hq, Hkv, N, S, D, scale, causal, softcap, window_left, flags=_FORCE_FLAGS, q=q, k=k, v=v,
+              o=out, alibi=alibi, bmask=bmask)
     sp = C.c_void_p(_stream_ptr(stream, q.device))
     with torch.cuda.device(q.device):
         if cu is None:
@@ -212,11 +217,6 @@ class _FlashAttnFn(torch.autograd.Function):
     def backward(ctx, dout, _dlse):
         q, k, v, out, lse = ctx.saved_tensors
         scale, causal, softcap, window_left, stream = ctx.cfg
-        if softcap != 0.0 or window_left >= 0:
-            raise NotImplementedError(
-                "flash_attention backward with softcap or window_size: the reference differentiates "
-                "its SDPA fallback here (mlx_mfa/attention.py:1976-1992, 2020-2027); no CUDA kernel is built."
-            )
         if q.shape[-1] in _FWD_ONLY_HDIMS:
             raise NotImplementedError(f"flash_attention backward for head_dim {q.shape[-1]} is not built.")
         if q.dtype == torch.float32:
@@ -224,7 +224,10 @@ class _FlashAttnFn(torch.autograd.Function):
                 "flash_attention backward for float32: the reference differentiates its SDPA fallback "
                 "(mlx_mfa/attention.py:2013-2019); the CUDA backward takes f16/bf16."
             )
-        dq, dk, dv = _bwd_raw(q, k, v, out, lse, dout, scale, causal, stream, alibi=ctx.alibi, bmask=ctx.bmask)
+        # softcap and window_size are differentiated by the kernels (the reference routes them through its SDPA
+        # fallback's autodiff, mlx_mfa/attention.py:1976-1992, 2020-2027)
+        dq, dk, dv = _bwd_raw(q, k, v, out, lse, dout, scale, causal, stream, alibi=ctx.alibi, bmask=ctx.bmask,
+                              softcap=softcap, window_left=window_left)
         return dq, dk, dv, None, None, None, None, None, None, None, None
 
 

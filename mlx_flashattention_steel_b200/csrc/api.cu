@@ -229,8 +229,6 @@ static int32_t bwd_common(const b200fa_desc* d, const void* q, const void* k, co
   if (d->dtype == B200FA_F32)
     return fail(B200FA_ERR_UNSUPPORTED, "backward is built for f16 and bf16 (the reference's STEEL backward, "
                                         "mlx_mfa/attention.py:2008-2012, takes the same)");
-  if (d->softcap != 0.f || d->window_left >= 0)
-    return fail(B200FA_ERR_UNSUPPORTED, "backward with softcap or window is not built");
   if (d->B == 0 || d->N == 0 || nbatch == 0) return B200FA_OK;
   if (!q || !k || !v || !out || !lse || !dout || !dq || !dk || !dv)
     return fail(B200FA_ERR_INVALID_ARG, "null tensor pointer");
@@ -257,6 +255,7 @@ static int32_t bwd_common(const b200fa_desc* d, const void* q, const void* k, co
   p.lse_hs = f.lse_hs; p.lse_bs = f.lse_bs;
   p.B = d->B; p.Hq = d->Hq; p.Hkv = d->Hkv; p.N = d->N; p.S = d->S;
   p.gqa = f.gqa; p.scale = d->scale; p.scale_log2 = f.scale_log2; p.causal = f.causal;
+  p.softcap = d->softcap; p.window_left = d->window_left;
   p.cu_q = cu_q; p.cu_k = cu_k;
   if ((d->alibi_slopes != nullptr || d->block_mask != nullptr) && varlen)
     return fail(B200FA_ERR_UNSUPPORTED, "alibi_slopes / block_mask with packed sequences are not built");

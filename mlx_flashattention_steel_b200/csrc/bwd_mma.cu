@@ -4,6 +4,9 @@
 // 765-1293 dK/dV; host side csrc/bindings.cpp:120-163):
 //   P = 2^(scale*log2e*S - L),  dP = dO.V^T,  dS = P o (dP - delta),  delta = sum_d dO o O
 //   dV = P^T.dO,  dK = scale * dS^T.Q,  dQ = scale * dS.K
+// With a soft cap the forward's score is cap*tanh(scale*S/cap): P uses the capped score and dS gains the factor
+// 1 - tanh^2 (the reference differentiates its SDPA fallback for softcap and windows, mlx_mfa/attention.py:1976-1992,
+// 2020-2027; here both run in the kernels).  A left window masks keys j < i + (S - N) - window_left.
 // with P and dS rounded to the input dtype before their MMAs, as the reference does
 // (csrc/mfa_steel_bwd.cpp:1100-1101, 1200-1201).
 //
@@ -161,9 +164,14 @@ __global__ void __launch_bounds__(kThreads) bwd_main_kernel(const BwdParams p) {
   // query tiles that can see keys of this tile: rows i >= n0 - off
   int m_begin = 0;
   if (p.causal) m_begin = max(0, n0 - off) / kBM;
-  const int m_end = (N + kBM - 1) / kBM;
+  int m_end = (N + kBM - 1) / kBM;
+  // a left window: the last row that still sees this tile's last key is i = key - off + window_left
+  if (p.window_left >= 0) m_end = min(m_end, max(0, min(S, n0 + kBN) - 1 - off + p.window_left) / kBM + 1);
   const int nm = max(0, m_end - m_begin);
   const int n_iter = nm * p.gqa;
+  const bool use_cap = p.softcap > 0.f;
+  const float cap_in = use_cap ? p.scale / p.softcap : 0.f, cap_out = p.softcap * kLog2e;
+  const bool precise_tanh = p.softcap >= kPreciseTanhMinCap;
 
   float dk[D / 8][4], dv[D / 8][4];
 #pragma unroll
@@ -251,12 +259,19 @@ __global__ void __launch_bounds__(kThreads) bwd_main_kernel(const BwdParams p) {
         const int qrow = m * kBM + ql;
         bool vis = key < S;
         if (p.causal) vis = vis && (key <= qrow + off);
+        if (p.window_left >= 0) vis = vis && (key >= qrow + off - p.window_left);
         if (p.bmask != nullptr && vis) vis = p.bmask[(min(qrow, N - 1) / p.bm_bq) * p.bm_nk + key / p.bm_bk] != 0;
         const float L = Ls[ql];
-        const float sc = fmaf(alibi_l2, static_cast<float>(key - (qrow + off)), st[j][e] * p.scale_log2);
+        float base = st[j][e] * p.scale_log2, dcap = 1.f;
+        if (use_cap) {
+          const float th = cap_tanh(st[j][e] * cap_in, precise_tanh);
+          base = cap_out * th;
+          dcap = fmaf(-th, th, 1.f);                     // d(cap * tanh(s / cap)) / ds
+        }
+        const float sc = fmaf(alibi_l2, static_cast<float>(key - (qrow + off)), base);
         const float pe = (vis && L != -INFINITY) ? fast_exp2(sc - L) : 0.f;
         pv[e] = pe;
-        dsv[e] = pe * (dp[j][e] - Ds[ql]);
+        dsv[e] = pe * (dp[j][e] - Ds[ql]) * dcap;
       }
       // n-tile j of the C layout is half (j & 1) of k-block (j >> 1) of the A layout
       pa[j >> 1][(j & 1) * 2 + 0] = Elem<T>::pack(pv[0], pv[1]);
@@ -381,7 +396,7 @@ cudaError_t launch_t(const BwdParams& p, int dtype, bool varlen, int nbatch, int
   constexpr size_t smem = (2 * kBN * D + 4 * kBM * D + kBN * kBM) * sizeof(T) + 4 * kBM * sizeof(float);
   dim3 grid((max_k + kBN - 1) / kBN, p.Hkv, nbatch);
   cudaError_t e;
-  if (allow_sm100 && bwd_sm100_supported(dtype, D)) {
+  if (allow_sm100 && bwd_sm100_supported(dtype, D) && bwd_sm100_strides_ok(p)) {
     e = launch_bwd_sm100_main(p, dtype, nbatch, max_k, stream);
     if (e != cudaSuccess) return e;
   } else if (varlen) {

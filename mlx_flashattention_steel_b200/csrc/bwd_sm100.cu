@@ -89,7 +89,9 @@ template <int DT> __device__ __forceinline__ uint32_t pack16b(float a, float b) 
   return DT == 0 ? Elem<__half>::pack(a, b) : Elem<__nv_bfloat16>::pack(a, b);
 }
 
-template <int DT>
+// CAP: the forward capped the scores (cap * tanh(s / cap)); P is rebuilt from the capped score and dS carries the
+// factor 1 - tanh^2.  A compile-time variant, so that the plain kernel's compute loop is untouched.
+template <int DT, bool CAP>
 __global__ void __launch_bounds__(kThreads, 1)
 bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                  const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmDO,
@@ -182,7 +184,9 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   const int off = S - N;
   int m_begin = 0;
   if (p.causal) m_begin = max(0, n0 - off) / BQ;
-  const int m_end = (N + BQ - 1) / BQ;
+  int m_end = (N + BQ - 1) / BQ;
+  // a left window: the last row that still sees this tile's last key is i = key - off + window_left
+  if (p.window_left >= 0) m_end = min(m_end, max(0, min(S, n0 + BK) - 1 - off + p.window_left) / BQ + 1);
   const int nm = max(0, m_end - m_begin);
   const int n_iter = nm * p.gqa;
   const int kbuf = w & 1;                              // K buffer and KV barrier of this item
@@ -430,11 +434,15 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       const int m = m_begin + it % nm;
       if (!__all_sync(0xffffffffu, mbar_wait_bounded(bar(BAR_Q_FULL + st), (it >> 1) & 1, s_abort))) { ok = false; break; }
       const uint32_t Ls = opaque_u32(smem_u32(sL + st * BQ)), Ds = Ls + 2 * BQ * 4;
-      const bool need_mask = (n0 + BK > S) || (p.causal && (n0 + BK - 1 > m * BQ + off));
+      const bool need_mask = (n0 + BK > S) || (p.causal && (n0 + BK - 1 > m * BQ + off)) ||
+                             (p.window_left >= 0 && (n0 < m * BQ + BQ - 1 + off - p.window_left));
+      const int wlo = p.window_left >= 0 ? off - p.window_left : -0x40000000;    // key visible iff key >= qrow + wlo
       // dS^T[this key][query] lives in buffer it & 1 as [query block of 64][key][128 B], 16-byte chunks swizzled by
       // key & 7: each thread stores its 32 queries as four 16-byte chunks
       const uint32_t ds_row = smem_u32(sDS) + (it & 1) * kDSBytes + rloc * 128;
       const float2 c2 = make_float2(p.scale_log2, p.scale_log2);
+      const float cap_in = CAP ? p.scale / p.softcap : 0.f, cap_out = p.softcap * kLog2e;
+      const bool precise_tanh = p.softcap >= kPreciseTanhMinCap;
 
       auto run_half = [&](int x, auto masked) {
         const int q0l = x * 64 + hf * 32;                  // first query (inside the tile) of this warp's 32 columns
@@ -453,15 +461,23 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
             const float2 dv = make_float2(__uint_as_float(rd[i + e]), __uint_as_float(rd[i + e + 1]));
             const float2 nl = e == 0 ? make_float2(nL.x, nL.y) : make_float2(nL.z, nL.w);
             const float2 nd = e == 0 ? make_float2(nD.x, nD.y) : make_float2(nD.z, nD.w);
-            const float2 t = __ffma2_rn(sv, c2, nl);
+            float2 t, dcap;
+            if constexpr (CAP) {
+              const float2 th = make_float2(cap_tanh(sv.x * cap_in, precise_tanh), cap_tanh(sv.y * cap_in, precise_tanh));
+              t = __ffma2_rn(th, make_float2(cap_out, cap_out), nl);
+              dcap = __ffma2_rn(make_float2(-th.x, -th.y), th, make_float2(1.f, 1.f));
+            } else {
+              t = __ffma2_rn(sv, c2, nl);
+            }
             float2 pe = make_float2(fast_exp2(t.x), fast_exp2(t.y));
             if constexpr (decltype(masked)::value) {
               const int qrow = m * BQ + q0l + i + e;
               const bool kin = key < S;
-              if (!(kin && (!p.causal || key <= qrow + off))) pe.x = 0.f;
-              if (!(kin && (!p.causal || key <= qrow + 1 + off))) pe.y = 0.f;
+              if (!(kin && (!p.causal || key <= qrow + off) && key >= qrow + wlo)) pe.x = 0.f;
+              if (!(kin && (!p.causal || key <= qrow + 1 + off) && key >= qrow + 1 + wlo)) pe.y = 0.f;
             }
-            const float2 dsv = __fmul2_rn(pe, __fadd2_rn(dv, nd));
+            float2 dsv = __fmul2_rn(pe, __fadd2_rn(dv, nd));
+            if constexpr (CAP) dsv = __fmul2_rn(dsv, dcap);
             pp[(i + e) >> 1] = pack16b<DT>(pe.x, pe.y);
             pd[(i + e) >> 1] = pack16b<DT>(dsv.x, dsv.y);
           }
@@ -576,6 +592,12 @@ bool make_map64(CUtensorMap* m, int dtype, const void* base, int rows, int H, in
 
 bool bwd_sm100_supported(int dtype, int D) { return (dtype == 0 || dtype == 1) && D == HD && get_encode_tiled() != nullptr; }
 
+// TMA strides must be positive: broadcast (stride 0) batch / head dimensions of extent > 1 take the portable kernel.
+bool bwd_sm100_strides_ok(const BwdParams& p) {
+  return !((p.B > 1 && (p.q_bs == 0 || p.k_bs == 0 || p.v_bs == 0)) || (p.Hq > 1 && p.q_hs == 0) ||
+           (p.Hkv > 1 && (p.k_hs == 0 || p.v_hs == 0)));
+}
+
 // Main backward step only: p.delta and p.dq_acc must already hold delta and zeros.
 cudaError_t launch_bwd_sm100_main(const BwdParams& p, int dtype, int nbatch, int max_k, cudaStream_t stream) {
   if (nbatch <= 0 || max_k <= 0) return cudaSuccess;
@@ -617,17 +639,15 @@ cudaError_t launch_bwd_sm100_main(const BwdParams& p, int dtype, int nbatch, int
     if (cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sm_count <= 0) sm_count = 148;
   }
   dim3 grid(static_cast<unsigned>(items < sm_count ? items : sm_count), 1, 1);   // one persistent CTA per SM
-  cudaError_t e;
-  if (dtype == 0) {
-    e = cudaFuncSetAttribute(bwd_sm100_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+  auto launch = [&](auto kern) -> cudaError_t {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
     if (e != cudaSuccess) return e;
-    bwd_sm100_kernel<0><<<grid, kThreads, kSmemBytes, stream>>>(tmQ, tmK, tmV, tmDO, tmDQ, a);
-  } else {
-    e = cudaFuncSetAttribute(bwd_sm100_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
-    if (e != cudaSuccess) return e;
-    bwd_sm100_kernel<1><<<grid, kThreads, kSmemBytes, stream>>>(tmQ, tmK, tmV, tmDO, tmDQ, a);
-  }
-  return cudaGetLastError();
+    kern<<<grid, kThreads, kSmemBytes, stream>>>(tmQ, tmK, tmV, tmDO, tmDQ, a);
+    return cudaGetLastError();
+  };
+  const bool cap = p.softcap > 0.f;
+  if (dtype == 0) return cap ? launch(bwd_sm100_kernel<0, true>) : launch(bwd_sm100_kernel<0, false>);
+  return cap ? launch(bwd_sm100_kernel<1, true>) : launch(bwd_sm100_kernel<1, false>);
 }
 
 cudaError_t bwd_sm100_read_clear_status(cudaStream_t stream, int* out) {

@@ -64,7 +64,9 @@ struct BwdParams {
   int gqa;
   float scale;
   float scale_log2;
+  float softcap;         // 0 = off: the forward capped the scaled scores with cap * tanh(s / cap)
   int causal;
+  int window_left;       // -1 = off
   const int* cu_q;
   const int* cu_k;
   const float* alibi;    // per q-head slopes, or null
@@ -157,6 +159,16 @@ __device__ __forceinline__ float fast_tanh(float x) {
   asm("tanh.approx.f32 %0, %1;\n" : "=f"(y) : "f"(x));
   return y;
 }
+// tanh of the soft cap.  tanh.approx is specified to a relative error of 2^-11; multiplied by cap * log2(e) that is
+// an absolute error of the capped score, negligible for the caps models use (30, 50) and above the 2e-2 parity bar
+// from cap ~ 70 on.  Larger caps therefore take 1 - 2 / (2^(2 y log2 e) + 1): two special-function operations,
+// absolute error ~1e-7 (saturates cleanly: 2^x = inf gives 1, 2^x = 0 gives -1).
+constexpr float kPreciseTanhMinCap = 70.f;
+__device__ __forceinline__ float tanh_exp(float y) {
+  const float e = fast_exp2(y * (2.f * kLog2e));
+  return 1.f - __fdividef(2.f, e + 1.f);
+}
+__device__ __forceinline__ float cap_tanh(float y, bool precise) { return precise ? tanh_exp(y) : fast_tanh(y); }
 
 // Shared-memory tile of rows x DCOLS 16-bit elements, 16-byte chunks XOR-swizzled
 // by the row so that ldmatrix reads of 8 consecutive rows are conflict-free.

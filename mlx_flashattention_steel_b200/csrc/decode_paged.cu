@@ -530,9 +530,10 @@ decode_paged_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_consta
           } else {
             s *= a.q_prescale;
           }
-          if (a.inv_cap > 0.f) s = a.cap_log2 * fast_tanh(s * a.inv_cap);
+          if (a.inv_cap > 0.f) s = a.cap_log2 * cap_tanh(s * a.inv_cap, a.inv_cap * kPreciseTanhMinCap <= 1.f);
           const int tg = tok0 + tok;
           sc[q][e] = (pg[q] != -2 && tg < len && tg <= causal_lim) ? s : -INFINITY;
+          if (tg >= len) vsc[q][e] = 0.f;               // whatever the slot's scale holds (it may be a NaN pattern)
         }
       }
       if (kQuant && first_page) {
@@ -578,6 +579,17 @@ decode_paged_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_consta
 #pragma unroll
       for (int q = 0; q < 2; ++q) {
         if (pg[q] >= 0) {
+          // Slots of the last page beyond the sequence's end hold whatever the pool's owner left there; their P is
+          // zero, but 0 * NaN (or 0 * inf) would still poison the row, so their V values are cleared as they are
+          // loaded.  amask[h]: tokens (2t, 2t+1) for h = 0, (2t+8, 2t+9) for h = 1, one 16-bit lane per token.
+          const int tail_from = len - (j + q) * kBS;      // first token of this page that is beyond the sequence
+          const bool tail = tail_from < kBS;              // warp-uniform
+          uint32_t amask[2] = {0xffffffffu, 0xffffffffu};
+          if (tail) {
+#pragma unroll
+            for (int h = 0; h < 2; ++h)
+              amask[h] = (2 * t + 8 * h < tail_from ? 0x0000ffffu : 0u) | (2 * t + 8 * h + 1 < tail_from ? 0xffff0000u : 0u);
+          }
           uint32_t pb0, pb1;
           if (kQuant) {
             pb0 = pack_h2(pr[q][0] * vsc[q][0] * vnorm, pr[q][1] * vsc[q][1] * vnorm);
@@ -617,6 +629,7 @@ decode_paged_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_consta
                   af[1] = e4m3pair_to_h2(ab[kp] >> 16);
                   af[2] = e4m3pair_to_h2(cd[kp]);
                   af[3] = e4m3pair_to_h2(cd[kp] >> 16);
+                  if (tail) { af[0] &= amask[0]; af[1] &= amask[0]; af[2] &= amask[1]; af[3] &= amask[1]; }
                 }
                 mma16816<MmaT>(oacc[jj * 2 + kp], af, pb0, pb1);
               }
@@ -630,6 +643,7 @@ decode_paged_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_consta
               const uint32_t addr = vbase[q] + (dcol >> 6) * (kBS * 128) + tok * 128 + ((((dcol & 63) >> 3) ^ (tok & 7)) << 4);
               // after .trans: a0 = (d 0-7, tok 0-7), a1 = (d 8-15, tok 0-7), a2 = (d 0-7, tok 8-15), a3 = (d 8-15, tok 8-15)
               ldmatrix_x4_trans(af, addr);
+              if (tail) { af[0] &= amask[0]; af[1] &= amask[0]; af[2] &= amask[1]; af[3] &= amask[1]; }
               mma16816<MmaT>(oacc[mt], af, pb0, pb1);
             }
           }
@@ -933,4 +947,21 @@ extern "C" int32_t b200fa_decode_paged_static(const b200fa_desc* d, const void* 
   return b200fa_decode_paged(d, q, k_pool, v_pool, k_scale, v_scale, block_table, seq_lens, num_pages,
                              block_size, max_blocks, max_kv_len, out, lse, scratch,
                              B200FA_STATIC_SCRATCH_BYTES, stream);
+}
+
+// The static entry's error word sits at the start of the built-in scratch, whose address callers never see.
+extern "C" int32_t b200fa_decode_paged_static_status(void* stream, int32_t* status_out) {
+  if (status_out == nullptr) {
+    b200fa::set_last_error("status_out is null");
+    return B200FA_ERR_INVALID_ARG;
+  }
+  void* scratch = nullptr;
+  cudaError_t e = b200fa::static_scratch_address(&scratch);
+  if (e != cudaSuccess) {
+    char msg[256];
+    snprintf(msg, sizeof(msg), "b200fa_decode_paged_static_status: cudaGetSymbolAddress failed: %s", cudaGetErrorString(e));
+    b200fa::set_last_error(msg);
+    return B200FA_ERR_CUDA;
+  }
+  return b200fa_workspace_status(scratch, stream, status_out);
 }

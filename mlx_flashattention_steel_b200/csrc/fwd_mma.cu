@@ -112,6 +112,7 @@ __global__ void __launch_bounds__(kThreads) fa_fwd_mma_kernel(const FwdParams p)
   const bool use_cap = p.softcap > 0.f;
   const float cap_in = use_cap ? p.scale / p.softcap : 0.f;
   const float cap_out = p.softcap * kLog2e;
+  const bool precise_tanh = p.softcap >= kPreciseTanhMinCap;
   const float alibi_l2 = p.alibi != nullptr ? p.alibi[head] * kLog2e : 0.f;
 
   int stage = 0;
@@ -152,7 +153,7 @@ __global__ void __launch_bounds__(kThreads) fa_fwd_mma_kernel(const FwdParams p)
 #pragma unroll
       for (int i = 0; i < kBK / 8; ++i)
 #pragma unroll
-        for (int e = 0; e < 4; ++e) s[i][e] = cap_out * fast_tanh(s[i][e] * cap_in);
+        for (int e = 0; e < 4; ++e) s[i][e] = cap_out * cap_tanh(s[i][e] * cap_in, precise_tanh);
     } else {
 #pragma unroll
       for (int i = 0; i < kBK / 8; ++i)

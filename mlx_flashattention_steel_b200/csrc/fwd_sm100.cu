@@ -380,6 +380,9 @@ fa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     // largest |y| for which the degree-3 / degree-5 polynomial is within 1e-3 / cap of tanh(y)
     const float y_deg3 = use_cap ? fminf(0.5f, powf(1e-3f * 7.5f / p.softcap, 0.2f)) : 0.f;
     const float y_deg5 = use_cap ? fminf(0.5f, powf(1e-3f * (315.f / 17.f) / p.softcap, 1.f / 7.f)) : 0.f;
+    // ... and the degree-7 one within 2e-3 / cap (0.497 at cap 50); beyond it tanh itself is evaluated
+    const float y_deg7 = use_cap ? fminf(0.5f, powf(2e-3f * (2835.f / 62.f) / p.softcap, 1.f / 9.f)) : 0.f;
+    const bool precise_tanh = p.softcap >= kPreciseTanhMinCap;
     const bool monotone = p.scale > 0.f;              // lets the row max be taken on the raw dot products
     const float alibi_l2 = (FEAT && p.alibi != nullptr) ? p.alibi[head] * kLog2e : 0.f;
 
@@ -440,10 +443,13 @@ fa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         } else {
           // cap*tanh(y), y = x*scale/cap: the odd Taylor polynomial of tanh runs on the FMA pipe and leaves the
           // special-function unit to exp2.  Its degree (3, 5 or 7) is the lowest whose truncation error, times
-          // cap, stays below 1e-3 for the largest |y| among the warp's rows; above |y| = 0.5 tanh.approx takes over.
+          // cap, stays below 1e-3 (2e-3 for degree 7) for the largest |y| among the warp's rows; above that range
+          // (|y| = 0.5 at most) tanh itself is evaluated.
           // bf16: one tree over |x| serves both the range check and the reference max -- f(max|x|) is an upper
-          // bound of the row max at most 2*cap*0.5 above it, so P stays within bf16's exponent range (an fp16 P
-          // could underflow, hence the exact max and a second tree there).
+          // bound of the row max, at most 2*cap*log2(e)*|y| binades above it.  That is harmless while the bound
+          // stays inside the exponent range P is computed in (ex2.approx.ftz flushes below 2^-126): up to 96
+          // binades it is used as it stands (softcap 50 never exceeds 72); beyond, the warp takes the exact max with
+          // a second tree, as fp16 always does (its P would underflow much earlier).
           float xmax, ax;
           if (DT == 1) {
             ax = tree_absmax64(x);
@@ -453,7 +459,10 @@ fa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
             ax = fmaxf(xmax, -tree_min64(x));
           }
           const float ay = ax * cap_in;
-          const unsigned lvl = __reduce_max_sync(0xffffffffu, ay <= y_deg3 ? 0u : (ay <= y_deg5 ? 1u : (ay <= 0.5f ? 2u : 3u)));
+          if (DT == 1) {
+            if (__any_sync(0xffffffffu, 2.f * cap_out * ay > 96.f)) xmax = tree_max64(x);
+          }
+          const unsigned lvl = __reduce_max_sync(0xffffffffu, ay <= y_deg3 ? 0u : (ay <= y_deg5 ? 1u : (ay <= y_deg7 ? 2u : 3u)));
           if (lvl < 3u) {
             mode = 1;
             deg = lvl;
@@ -463,7 +472,7 @@ fa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
           } else {
             mode = 2;
             if (DT == 1) xmax = tree_max64(x);          // scores may saturate here: take the exact max
-            m_tile = cap_out * fast_tanh(xmax * cap_in);
+            m_tile = cap_out * cap_tanh(xmax * cap_in, precise_tanh);
           }
         }
       } else {
@@ -471,8 +480,13 @@ fa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         // on them and mode 0 folds the scale into the exponent's FMA as on an unmasked tile
         const bool raw = !use_cap && monotone && !(FEAT && p.alibi != nullptr);
         if (use_cap) {
+          if (precise_tanh) {
 #pragma unroll
-          for (int i = 0; i < BN; ++i) x[i] = cap_out * fast_tanh(x[i] * cap_in);
+            for (int i = 0; i < BN; ++i) x[i] = cap_out * tanh_exp(x[i] * cap_in);
+          } else {
+#pragma unroll
+            for (int i = 0; i < BN; ++i) x[i] = cap_out * fast_tanh(x[i] * cap_in);
+          }
         } else if (!raw) {
 #pragma unroll
           for (int i = 0; i < BN; ++i) x[i] *= p.scale_log2;
@@ -590,12 +604,22 @@ fa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
           }
         }
       } else if (mode == 2) {
+        if (precise_tanh) {
 #pragma unroll
-        for (int i = 0; i < BN; i += 2) {
-          const float2 e = make_float2(fast_exp2(fmaf(cap_out, fast_tanh(x[i] * cap_in), -msub)),
-                                       fast_exp2(fmaf(cap_out, fast_tanh(x[i + 1] * cap_in), -msub)));
-          lsum2 = __fadd2_rn(lsum2, e);
-          pk[i >> 1] = pack16<DT>(e.x, e.y);
+          for (int i = 0; i < BN; i += 2) {
+            const float2 e = make_float2(fast_exp2(fmaf(cap_out, tanh_exp(x[i] * cap_in), -msub)),
+                                         fast_exp2(fmaf(cap_out, tanh_exp(x[i + 1] * cap_in), -msub)));
+            lsum2 = __fadd2_rn(lsum2, e);
+            pk[i >> 1] = pack16<DT>(e.x, e.y);
+          }
+        } else {
+#pragma unroll
+          for (int i = 0; i < BN; i += 2) {
+            const float2 e = make_float2(fast_exp2(fmaf(cap_out, fast_tanh(x[i] * cap_in), -msub)),
+                                         fast_exp2(fmaf(cap_out, fast_tanh(x[i + 1] * cap_in), -msub)));
+            lsum2 = __fadd2_rn(lsum2, e);
+            pk[i >> 1] = pack16<DT>(e.x, e.y);
+          }
         }
       } else {
 #pragma unroll
@@ -707,6 +731,11 @@ bool make_map(CUtensorMap* m, int dtype, const void* base, int D, int rows, int 
 bool fwd_sm100_supported(const FwdParams& p, int dtype, int D) {
   if (!(dtype == 0 || dtype == 1) || !(D == 64 || D == 128)) return false;
   if (p.N <= 0 || p.S <= 0 || p.B <= 0) return false;
+  // A broadcast (stride 0) batch or head dimension of extent > 1 cannot be described to TMA, whose strides must be
+  // positive; such views run the portable kernel, which indexes with the caller's strides as they are.
+  if ((p.B > 1 && (p.q_bs == 0 || p.k_bs == 0 || p.v_bs == 0 || p.o_bs == 0)) ||
+      (p.Hq > 1 && (p.q_hs == 0 || p.o_hs == 0)) || (p.Hkv > 1 && (p.k_hs == 0 || p.v_hs == 0)))
+    return false;
   if (p.bmask != nullptr) {
     // mask cells must tile the 64-key tiles, and the active-tile list holds 16-bit indices of at most kMaxListTiles
     if (!(p.bm_bk == 16 || p.bm_bk == 32 || p.bm_bk == 64) || p.bm_bq <= 0) return false;
@@ -719,7 +748,7 @@ template <int HD, int DT, bool FEAT>
 static cudaError_t launch_hd(const FwdParams& p, int nbatch, int max_q, cudaStream_t stream) {
   constexpr int dtype = DT;
   CUtensorMap tmQ, tmK, tmV, tmO;
-  // TMA: a size-1 dimension still needs a legal stride
+  // TMA: a size-1 dimension still needs a legal stride (extents > 1 have positive strides: fwd_sm100_supported)
   auto fix = [](int64_t s, int64_t fallback) { return s > 0 ? s : fallback; };
   const int64_t q_hs = fix(p.q_hs, static_cast<int64_t>(p.N) * p.q_rs), q_bs = fix(p.q_bs, q_hs * p.Hq);
   const int64_t k_hs = fix(p.k_hs, static_cast<int64_t>(p.S) * p.k_rs), k_bs = fix(p.k_bs, k_hs * p.Hkv);

@@ -32,6 +32,7 @@ size_t bwd_workspace_bytes(int B, int Hq, int N_total, int D);
 cudaError_t launch_bwd(const BwdParams& p, int dtype, int D, bool varlen, int nbatch, int max_q,
                        int max_k, void* workspace, bool allow_sm100, cudaStream_t stream);
 bool bwd_sm100_supported(int dtype, int D);
+bool bwd_sm100_strides_ok(const BwdParams& p);
 cudaError_t launch_bwd_sm100_main(const BwdParams& p, int dtype, int nbatch, int max_k, cudaStream_t stream);
 
 // KV-cache write path (kv_append.cu): scatter T new tokens per kv head into the page pools; 8-bit pools are

@@ -286,10 +286,14 @@ def backward(
     causal: bool = False,
     cu_q: Optional[Sequence[int]] = None,
     cu_k: Optional[Sequence[int]] = None,
+    softcap: float = 0.0,
+    window_left: int = -1,
 ) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
     """dQ, dK, dV by autograd in float64 through the formulas above — what the
     reference tests do with mx.grad(reference_sdpa) (tests/test_attention.py:191-207,
-    4362-4368).  With cu_q/cu_k the sequences are packed (varlen)."""
+    4362-4368).  With cu_q/cu_k the sequences are packed (varlen).  softcap and window_left follow the
+    reference's differentiable SDPA fallbacks (mlx_mfa/attention.py:1976-1992 window mask, 2020-2027 and
+    1758-1768 tanh cap before the mask)."""
     q64 = q.detach().to(torch.float64).requires_grad_(True)
     k64 = k.detach().to(torch.float64).requires_grad_(True)
     v64 = v.detach().to(torch.float64).requires_grad_(True)
@@ -303,7 +307,9 @@ def backward(
         kk = ks.repeat_interleave(g, dim=1)
         vv = vs.repeat_interleave(g, dim=1)
         s = torch.matmul(qs, kk.transpose(-1, -2)) * scale
-        vis = _visible(n, s_len, causal, -1, slice(0, n))
+        if softcap > 0:
+            s = torch.tanh(s / softcap) * softcap
+        vis = _visible(n, s_len, causal, window_left, slice(0, n))
         if vis is not None:
             s = s.masked_fill(~vis, float("-inf"))
         return torch.matmul(torch.softmax(s, dim=-1), vv)

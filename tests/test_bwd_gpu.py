@@ -51,6 +51,32 @@ def test_backward_scale_and_longer(dev):
     _grads(dev, torch.float16, 1, 4, 2, 512, 512, 128, True, 530, scale=0.05)
 
 
+@pytest.mark.parametrize("D", [64, 128])
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("softcap,window,scale_mult", [(50.0, None, 1.0), (5.0, None, 3.0), (0.0, (40, 0), 1.0),
+                                                       (30.0, (100, 0), 1.0), (200.0, (7, 0), 6.0)])
+def test_backward_softcap_and_window(dev, D, dtype, softcap, window, scale_mult):
+    """Gradients through the soft cap (the factor 1 - tanh^2 on dS) and through a left window, which the reference
+    gets from autodiff of its SDPA fallback (mlx_mfa/attention.py:1976-1992, 2020-2027).  Config 2's own operator
+    (softcap 50, causal, GQA) is the first case; scale multiples push scores into the saturating part of tanh."""
+    B, Hq, Hkv, N, S = 2, 4, 2, 200, 264
+    q = randn((B, Hq, N, D), dtype, 570)
+    k = randn((B, Hkv, S, D), dtype, 571)
+    v = randn((B, Hkv, S, D), dtype, 572)
+    do = randn((B, Hq, N, D), dtype, 573)
+    scale = scale_mult / D ** 0.5
+    qg, kg, vg = (x.to(dev).requires_grad_(True) for x in (q, k, v))
+    out = fa.flash_attention(qg, kg, vg, causal=True, scale=scale, softcap=softcap, window_size=window)
+    out.backward(do.to(dev))
+    wl = -1 if window is None else window[0]
+    O, _, _ = orc.sdpa(q, k, v, scale=scale, causal=True, softcap=softcap, window_left=wl)
+    assert_close(out, O, dtype)
+    dq, dk, dv = orc.backward(q, k, v, do, scale=scale, causal=True, softcap=softcap, window_left=wl)
+    assert_close_grad(qg.grad, dq, dtype, "dQ")
+    assert_close_grad(kg.grad, dk, dtype, "dK")
+    assert_close_grad(vg.grad, dv, dtype, "dV")
+
+
 def _cu(lens):
     return [0] + list(np.cumsum(lens))
 

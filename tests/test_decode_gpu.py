@@ -69,6 +69,40 @@ def test_decode_empty_sequences_and_holes(dev):
     _run(dev, torch.float16, None, 5, 8, 8, 1, [0, 100, 0, 48, 64], 431, holes=True)
 
 
+@pytest.mark.parametrize("quant", [None, "int8", "e4m3"])
+def test_decode_ignores_garbage_beyond_the_sequence_end(dev, quant):
+    """Slots of a sequence's last page beyond seq_lens hold whatever the pool's owner left there (a pool from
+    cudaMalloc or torch.empty, a recycled page).  NaN patterns in those K / V rows and scales must not reach the
+    output: their probabilities are zero, but 0 * NaN is NaN unless the values are masked too."""
+    lens = [5, 17, 100, 33]
+    qdtype = torch.bfloat16
+    pg = make_paged(4, 2, 128, 16, lens, qdtype, 77, quant=quant)
+    table = pg["block_table"]
+    for b, n in enumerate(lens):
+        page = int(table[b, (n - 1) // 16])
+        first = n % 16
+        if first == 0:
+            continue
+        if quant is None:
+            pg["k"][page, first:] = float("nan")
+            pg["v"][page, first:] = float("nan")
+        else:
+            pg["k_scale"][page, first:] = float("nan")
+            pg["v_scale"][page, first:] = float("inf")
+            if quant == "e4m3":
+                pg["v"].view(torch.uint8)[page, first:] = 0x7F        # e4m3 NaN
+                pg["k"].view(torch.uint8)[page, first:] = 0xFF
+    q = randn((4, 8, 1, 128), qdtype, 78)
+    ks, vs = pg["k_scale"], pg["v_scale"]
+    out, lse = fa.flash_attention_paged(
+        q.to(dev), pg["k"].to(dev), pg["v"].to(dev), table.to(dev), pg["seq_lens"].to(dev), causal=True,
+        k_scale=None if ks is None else ks.to(dev), v_scale=None if vs is None else vs.to(dev), return_lse=True)
+    O, L = orc.paged_attention(q, pg["k"], pg["v"], table, pg["seq_lens"], causal=True, k_scale=ks, v_scale=vs)
+    assert torch.isfinite(out.float()).all() and torch.isfinite(lse).all()
+    assert_close(out, O, qdtype)
+    assert_close(lse, L, qdtype, "lse")
+
+
 def test_decode_softcap(dev):
     _run(dev, torch.bfloat16, "int8", 3, 32, 8, 1, [100, 2000, 31], 440, softcap=30.0)
 

@@ -99,6 +99,34 @@ def test_softcap_all_scores_negative(dev, dt, level):
     assert_close(lse, L, dtype, "lse", LSE_TOL[dtype])
 
 
+@pytest.mark.parametrize("frac", [0.2, 0.4])
+@pytest.mark.parametrize("cap", [100.0, 200.0, 1000.0])
+@pytest.mark.parametrize("dt", ["f16", "bf16"])
+def test_softcap_large_caps_strongly_negative_rows(dev, dt, cap, frac):
+    """Capped scores near -frac * cap with a large cap: the bf16 path's reference max taken from max|score| would sit
+    up to 2 * frac * cap * log2(e) binades above the true row max -- beyond the exponent range P is computed in from
+    cap ~ 95 -- so the kernel has to fall back to the exact row max there.  A second case mixes rows: half of them
+    strongly negative, half near zero, inside the same 64-key tiles."""
+    dtype = DT[dt]
+    g = torch.Generator().manual_seed(48)
+    D, N = 128, 256
+    u = torch.randn(D, generator=g)
+    u = u / u.norm()
+    level = frac * cap                                   # |raw scaled score|; tanh(frac) * cap after the cap
+    amp = math.sqrt(level * math.sqrt(D))
+    k = (-amp * u + 0.05 * torch.randn((1, 2, N, D), generator=g)).to(dtype)
+    v = torch.randn((1, 2, N, D), generator=g).to(dtype)
+    q_neg = (amp * u + 0.05 * torch.randn((1, 2, N, D), generator=g)).to(dtype)
+    q_mix = q_neg.clone()
+    q_mix[:, :, ::2] = (0.05 * torch.randn((1, 2, N // 2, D), generator=g)).to(dtype)     # rows with scores near zero
+    for q in (q_neg, q_mix):
+        out, lse = fa.flash_attention(q.to(dev), k.to(dev), v.to(dev), causal=False, softcap=cap, return_lse=True)
+        O, L, _ = orc.sdpa(q, k, v, causal=False, softcap=cap)
+        assert torch.isfinite(L).all() and float(L.min()) < -0.7 * math.tanh(frac) * cap
+        assert_close(out, O, dtype)
+        assert_close(lse, L, dtype, "lse", LSE_TOL[dtype])
+
+
 def test_softcap_zero_is_bit_identical(dev):
     # tests/test_attention.py:2869-2886
     q, k, v = (randn((1, 2, 100, 64), torch.float16, 50 + i).to(dev) for i in range(3))
@@ -158,6 +186,33 @@ def test_strided_views_and_scale(dev):
     O, _, _ = orc.sdpa(q, k, v, scale=0.05, causal=True)
     assert_close(out, O, torch.bfloat16)
     assert torch.equal(out, out2)
+
+
+def test_broadcast_views_match_contiguous(dev):
+    """k / v expanded over the batch or the head axis (stride 0) must give what their materialised copies give,
+    forward and backward: TMA cannot describe a zero stride, so such views must not reach the tcgen05 kernels
+    with a made-up stride."""
+    for D in (64, 128):
+        q = randn((2, 4, 160, D), torch.bfloat16, 110).to(dev)
+        k1 = randn((1, 1, 160, D), torch.bfloat16, 111).to(dev)
+        v1 = randn((1, 1, 160, D), torch.bfloat16, 112).to(dev)
+        do = randn((2, 4, 160, D), torch.bfloat16, 113).to(dev)
+        for shape in ((2, 1, 160, D), (1, 4, 160, D), (2, 4, 160, D), (2, 2, 160, D)):
+            res = []
+            for contiguous in (False, True):
+                qg = q.clone().requires_grad_(True)
+                kb, vb = k1.clone().requires_grad_(True), v1.clone().requires_grad_(True)
+                qq = qg if shape[0] == 2 else qg[:1]
+                ke, ve = kb.expand(shape), vb.expand(shape)
+                if contiguous:
+                    ke, ve = ke.contiguous(), ve.contiguous()
+                out = fa.flash_attention(qq, ke, ve, causal=True)
+                out.backward(do[: qq.shape[0]])
+                res.append((out.detach().float(), qg.grad.float(), kb.grad.float(), vb.grad.float()))
+            for name, a_, b_ in zip(("out", "dq", "dk", "dv"), res[0], res[1]):
+                assert float((a_ - b_).abs().max()) <= 2e-2 + 2.0 ** -7 * float(b_.abs().max()), (D, shape, name)
+        O, _, _ = orc.sdpa(q.cpu(), k1.expand(2, 4, 160, D).cpu(), v1.expand(2, 4, 160, D).cpu(), causal=True)
+        assert_close(fa.flash_attention(q, k1.expand(2, 4, 160, D), v1.expand(2, 4, 160, D), causal=True), O, torch.bfloat16)
 
 
 def test_golden_vectors(dev):

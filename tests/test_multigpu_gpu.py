@@ -2,22 +2,12 @@
 two ranks, each running the paged decode kernel on its part, combined over NCCL; the result must
 match the one-GPU kernel on the whole sequence and the CPU oracle."""
 import os
-import socket
 
 import numpy as np
 import pytest
 import torch
-import torch.multiprocessing as mp
 
 pytestmark = pytest.mark.gpu
-
-
-def _free_port():
-    s = socket.socket()
-    s.bind(("127.0.0.1", 0))
-    port = s.getsockname()[1]
-    s.close()
-    return port
 
 
 def _worker(rank, world, port, payload, ret):
@@ -57,22 +47,13 @@ def test_long_sequence_split_across_two_gpus(dev):
     import mlx_flashattention_steel_b200 as fa
     from oracle import sdpa_oracle as orc
 
-    from .util import make_paged, randn
+    from .util import make_paged, randn, run_ranks
 
     seq_len = 20000
     pg = make_paged(1, 8, 128, 16, [seq_len], torch.bfloat16, 700, quant="int8")
     q = randn((1, 32, 1, 128), torch.bfloat16, 701)
     payload = (q, pg["k"], pg["v"], pg["k_scale"], pg["v_scale"], pg["block_table"], seq_len)
-    ctx = mp.get_context("spawn")
-    ret = ctx.Queue()
-    port = _free_port()
-    procs = [ctx.Process(target=_worker, args=(r, 2, port, payload, ret)) for r in range(2)]
-    for p in procs:
-        p.start()
-    O, L = ret.get(timeout=300)
-    for p in procs:
-        p.join(timeout=120)
-        assert p.exitcode == 0
+    O, L = run_ranks(_worker, 2, (payload,), timeout=300)
     one, lone = fa.flash_attention_paged(q.to(dev), pg["k"].to(dev), pg["v"].to(dev), pg["block_table"].to(dev),
                                          pg["seq_lens"].to(dev), k_scale=pg["k_scale"].to(dev),
                                          v_scale=pg["v_scale"].to(dev), return_lse=True)

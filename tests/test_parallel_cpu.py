@@ -1,15 +1,15 @@
 """CPU tests (gloo, world_size 2) of the multi-GPU host logic: shard planning and the
 cross-rank log-sum-exp combine of split-KV partials, checked against the oracle."""
 import os
-import socket
 
 import pytest
 import torch
 import torch.distributed as dist
-import torch.multiprocessing as mp
 
 from mlx_flashattention_steel_b200 import parallel as par
 from oracle import sdpa_oracle as orc
+
+from .util import run_ranks
 
 
 def test_shard_range_covers_everything_once():
@@ -50,14 +50,6 @@ def test_split_pages():
     assert par.split_pages(7, 2, 1, 16, 100) == (4, 7, 36)
 
 
-def _free_port():
-    s = socket.socket()
-    s.bind(("127.0.0.1", 0))
-    port = s.getsockname()[1]
-    s.close()
-    return port
-
-
 def _worker(rank, world, port, q, k, v, ret):
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)
@@ -89,16 +81,7 @@ def _worker(rank, world, port, q, k, v, ret):
 def test_combine_partials_over_gloo():
     torch.manual_seed(0)
     q, k, v = torch.randn(2, 4, 1, 32), torch.randn(2, 2, 77, 32), torch.randn(2, 2, 77, 32)
-    ctx = mp.get_context("spawn")
-    ret = ctx.Queue()
-    port = _free_port()
-    procs = [ctx.Process(target=_worker, args=(r, 2, port, q, k, v, ret)) for r in range(2)]
-    for p in procs:
-        p.start()
-    O, L, O2, L2 = ret.get(timeout=120)
-    for p in procs:
-        p.join(timeout=60)
-        assert p.exitcode == 0
+    O, L, O2, L2 = run_ranks(_worker, 2, (q, k, v), timeout=120)
     ref, lref, _ = orc.sdpa(q, k, v)
     for o, l in ((O, L), (O2, L2)):
         assert float((o.double() - ref).abs().max()) < 1e-5

@@ -60,6 +60,11 @@ def test_static_scratch_matches_workspace_entry(dev, quant, qdtype):
         assert _call(lib, False, d, q, pg, table, lens, max_len, o_ref, l_ref, ws) == _lib.OK, _lib.last_error()
         assert _call(lib, True, d, q, pg, table, lens, max_len, o_new, l_new) == _lib.OK, _lib.last_error()
         torch.cuda.synchronize()
+        # a caller of the static entry has no workspace pointer to read the kernel's error word from: it asks for it
+        word = C.c_int32(-1)
+        stream = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+        assert lib.b200fa_decode_paged_static_status(stream, C.byref(word)) == _lib.OK, _lib.last_error()
+        assert word.value == 0
         assert float((o_new.float() - o_ref.float()).abs().max()) <= 2e-2
         fin = torch.isfinite(l_ref)
         assert torch.equal(torch.isfinite(l_new), fin)
@@ -80,3 +85,31 @@ def test_static_scratch_rejects_oversized_problems(dev):
     st = lib.b200fa_decode_paged_static(C.byref(d), p, p, p, None, None, p, p, 10, 16, 4, 64, p, None, None)
     assert st == _lib.ERR_WORKSPACE
     assert "scratch" in _lib.last_error()
+
+
+def test_static_scratch_reports_a_table_entry_beyond_the_pool(dev):
+    """A block_table entry >= num_pages is not followed (the kernel treats it as a hole: K = V = 0 for that page) and
+    sets bit 1 of the error word, which the static entry's status call must be able to show."""
+    lib = _lib.load()
+    B, Hq, Hkv, D = 2, 8, 2, 128
+    pg = make_paged(B, Hkv, D, 16, [40, 100], torch.bfloat16, 910)
+    pg = {k: (v.to(dev) if isinstance(v, torch.Tensor) else v) for k, v in pg.items()}
+    table, lens = pg["block_table"].clone().contiguous(), pg["seq_lens"].contiguous()
+    table[1, 2] = pg["k"].shape[0] + 5                  # beyond the pool
+    q = randn((B, Hq, 1, D), torch.bfloat16, 911).to(dev)
+    d = _lib.Desc()
+    d.dtype = d.kv_dtype = _lib.BF16
+    d.B, d.Hq, d.Hkv, d.N, d.S, d.D = B, Hq, Hkv, 1, 0, D
+    d.scale, d.softcap, d.causal, d.window_left = D ** -0.5, 0.0, 1, -1
+    out = torch.empty_like(q)
+    assert _call(lib, True, d, q, pg, table, lens, 100, out, None) == _lib.OK, _lib.last_error()
+    word = C.c_int32(-1)
+    stream = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+    assert lib.b200fa_decode_paged_static_status(stream, C.byref(word)) == _lib.OK, _lib.last_error()
+    assert word.value == 2
+    assert torch.isfinite(out.float()).all()
+    # the next valid call clears the word again
+    table[1, 2] = pg["block_table"][1, 2]
+    assert _call(lib, True, d, q, pg, table, lens, 100, out, None) == _lib.OK, _lib.last_error()
+    assert lib.b200fa_decode_paged_static_status(stream, C.byref(word)) == _lib.OK
+    assert word.value == 0

@@ -39,14 +39,22 @@ def assert_close(got, ref, dtype, what="out", tol=None):
 ULP = {torch.float16: 2.0 ** -10, torch.bfloat16: 2.0 ** -7}
 
 
+def grad_bound(ref, dtype):
+    """Element-wise bound for a 16-bit gradient: 2e-2 absolute, widened only where one rounding of the result to its
+    storage type is itself a sizeable part of that (half a unit in the last place at the reference value, plus 1e-2
+    for the arithmetic): gradients summed over a GQA group reach |x| >= 8, where bf16's half-ulp alone is 0.03."""
+    return torch.clamp(0.5 * ULP[dtype] * ref.abs() + 1e-2, min=TOL[dtype])
+
+
 def assert_close_grad(got, ref, dtype, what):
-    """Gradients summed over a GQA group reach magnitudes where a single rounding to the
-    16-bit output type exceeds 2e-2 (bf16 at |x| >= 4 has ulp 0.03).  The bound is therefore
-    2e-2 absolute plus one unit in the last place of the output dtype at the reference value."""
     a = got.detach().double().cpu()
     b = ref.detach().double().cpu()
-    excess = ((a - b).abs() - (TOL[dtype] + ULP[dtype] * b.abs())).max()
-    assert float(excess) <= 0, f"{what}: exceeds 2e-2 + 1 ulp by {float(excess):.3e}; max-abs {float((a - b).abs().max()):.3e}"
+    err = (a - b).abs()
+    excess = float((err - grad_bound(b, dtype)).max())
+    beyond = float((err > TOL[dtype]).double().mean())
+    assert excess <= 0, (f"{what}: exceeds max(2e-2, 0.5 ulp + 1e-2) by {excess:.3e}; plain max-abs {float(err.max()):.3e}, "
+                         f"share of elements beyond 2e-2: {beyond:.2e}, max |ref| {float(b.abs().max()):.2f}")
+    return float(err.max()), beyond
 
 
 def make_paged(B, Hkv, D, block_size, lens, dtype, seed, quant=None, spare_pages=3, holes=False):
@@ -87,3 +95,54 @@ def make_paged(B, Hkv, D, block_size, lens, dtype, seed, quant=None, spare_pages
             out[name] = qx
             out[name + "_scale"] = sc
     return out
+
+
+def free_port():
+    import socket
+
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    port = s.getsockname()[1]
+    s.close()
+    return port
+
+
+def run_ranks(worker, world, args, timeout=300):
+    """Spawns `world` processes running worker(rank, world, port, *args, ret) and returns what rank 0 puts on `ret`.
+    A rank that dies before reporting fails the test at once (its exit code is polled while waiting), and no child
+    outlives the call: whatever is still alive at the end is terminated, then killed, so that a surviving rank cannot
+    stay blocked in a collective on its device."""
+    import queue
+    import time
+
+    import torch.multiprocessing as mp
+
+    ctx = mp.get_context("spawn")
+    ret = ctx.Queue()
+    port = free_port()
+    procs = [ctx.Process(target=worker, args=(r, world, port, *args, ret)) for r in range(world)]
+    try:
+        for p in procs:
+            p.start()
+        deadline = time.time() + timeout
+        result = None
+        while result is None:
+            try:
+                result = ret.get(timeout=1.0)
+            except queue.Empty:
+                dead = [p.exitcode for p in procs if p.exitcode not in (None, 0)]
+                assert not dead, f"a rank exited with code {dead} before reporting"
+                assert time.time() < deadline, f"no result from the ranks within {timeout} s"
+        for p in procs:
+            p.join(timeout=120)
+            assert p.exitcode == 0, f"rank exit code {p.exitcode}"
+        return result
+    finally:
+        for p in procs:
+            if p.is_alive():
+                p.terminate()
+        for p in procs:
+            p.join(timeout=10)
+            if p.is_alive():
+                p.kill()
+                p.join(timeout=10)

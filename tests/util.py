@@ -41,9 +41,9 @@ ULP = {torch.float16: 2.0 ** -10, torch.bfloat16: 2.0 ** -7}
 
 def grad_bound(ref, dtype):
     """Element-wise bound for a 16-bit gradient: 2e-2 absolute, widened only where one rounding of the result to its
-    storage type is itself a sizeable part of that (half a unit in the last place at the reference value, plus 1e-2
+    storage type is itself a sizeable part of that (half a unit in the last place at the reference value, plus 1.5e-2
     for the arithmetic): gradients summed over a GQA group reach |x| >= 8, where bf16's half-ulp alone is 0.03."""
-    return torch.clamp(0.5 * ULP[dtype] * ref.abs() + 1e-2, min=TOL[dtype])
+    return torch.clamp(0.5 * ULP[dtype] * ref.abs() + 1.5e-2, min=TOL[dtype])
 
 
 def assert_close_grad(got, ref, dtype, what):
@@ -52,7 +52,7 @@ def assert_close_grad(got, ref, dtype, what):
     err = (a - b).abs()
     excess = float((err - grad_bound(b, dtype)).max())
     beyond = float((err > TOL[dtype]).double().mean())
-    assert excess <= 0, (f"{what}: exceeds max(2e-2, 0.5 ulp + 1e-2) by {excess:.3e}; plain max-abs {float(err.max()):.3e}, "
+    assert excess <= 0, (f"{what}: exceeds max(2e-2, 0.5 ulp + 1.5e-2) by {excess:.3e}; plain max-abs {float(err.max()):.3e}, "
                          f"share of elements beyond 2e-2: {beyond:.2e}, max |ref| {float(b.abs().max()):.2f}")
     return float(err.max()), beyond
 

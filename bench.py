@@ -351,6 +351,21 @@ def bench_extras(device, pk):
                                       "fwd_bwd_ms": ms_fb, "fwd_bwd_tflops": 3.5 * fl_fwd / ms_fb / 1e9,
                                       "frac_tensor_peak": 3.5 * fl_fwd / ms_fb / 1e9 / pk["tf"]}
     del q, k, v, do
+    # backward at head_dim 128: config 2's shape (B=4, Hq=32, Hkv=8, N=S=8192, bf16, causal), without and with its
+    # soft cap; 2.5 x the forward's causal-adjusted FLOPs (five GEMMs), whatever the kernels recompute
+    from mlx_flashattention_steel_b200 import attention as fa_attn
+    q, k, v, do = mk((4, 32, 8192, 128), torch.bfloat16), mk((4, 8, 8192, 128), torch.bfloat16), \
+        mk((4, 8, 8192, 128), torch.bfloat16), mk((4, 32, 8192, 128), torch.bfloat16)
+    fl = 2.5 * prefill_flops(C2)
+    bwd = {}
+    for name, cap in (("plain", 0.0), ("softcap50", 50.0)):
+        o_, l_ = fa_attn._fwd_raw(q, k, v, 128 ** -0.5, True, cap, -1, True, None)
+        ms = _time_ms(lambda: fa_attn._bwd_raw(q, k, v, o_, l_, do, 128 ** -0.5, True, None, softcap=cap), 5, 3)
+        bwd[name] = {"ms": ms, "tflops": fl / ms / 1e9, "frac_tensor_peak": fl / ms / 1e9 / pk["tf"]}
+        del o_, l_
+    bwd["kernels"] = "bwd_dkv_sm100_kernel + bwd_dq_sm100_kernel (tcgen05; 7 GEMMs executed for the 5 counted)"
+    out["bwd_d128_dense"] = bwd
+    del q, k, v, do
     # KV-cache write path (the producer of config 4's pools): 262144 new tokens x 8 kv heads x 128, bf16 in,
     # int8 + f16 scales out, into randomly placed pages filled in token order (what a prefill append looks like).
     # Algorithmic bytes = tokens read + values and scales written.

@@ -219,30 +219,14 @@ int32_t b200fa_fwd_varlen(const b200fa_desc* d, const void* q, const void* k, co
 // ---------------------------------------------------------------------------
 // backward
 // ---------------------------------------------------------------------------
-static int32_t bwd_common(const b200fa_desc* d, const void* q, const void* k, const void* v,
-                          const void* out, const float* lse, const void* dout, void* dq, void* dk,
-                          void* dv, const int32_t* cu_q, const int32_t* cu_k, int nbatch, int max_q,
-                          int max_k, void* workspace, size_t workspace_bytes, void* stream) {
-  const bool varlen = cu_q != nullptr;
-  int32_t st = check_common(d, varlen);
-  if (st != B200FA_OK) return st;
-  if (d->dtype == B200FA_F32)
-    return fail(B200FA_ERR_UNSUPPORTED, "backward is built for f16 and bf16 (the reference's STEEL backward, "
-                                        "mlx_mfa/attention.py:2008-2012, takes the same)");
-  if (d->B == 0 || d->N == 0 || nbatch == 0) return B200FA_OK;
-  if (!q || !k || !v || !out || !lse || !dout || !dq || !dk || !dv)
-    return fail(B200FA_ERR_INVALID_ARG, "null tensor pointer");
-  const size_t need = b200fa::bwd_workspace_bytes(d->B, d->Hq, d->N, d->D);
-  if (workspace == nullptr || workspace_bytes < need)
-    return fail(B200FA_ERR_WORKSPACE, "backward needs %zu workspace bytes, got %zu", need, workspace_bytes);
-  if (!aligned16(workspace)) return fail(B200FA_ERR_INVALID_ARG, "workspace must be 16-byte aligned");
+// Shape, stride and option fields of the backward parameter block (no workspace pointers yet).
+static int32_t fill_bwd_params(const b200fa_desc* d, const void* q, const void* k, const void* v, const void* out,
+                               const float* lse, const void* dout, void* dq, void* dk, void* dv, const int32_t* cu_q,
+                               const int32_t* cu_k, b200fa::BwdParams* pp) {
   b200fa::FwdParams f;
-  st = fill_fwd_params(d, q, k, v, const_cast<void*>(out), nullptr, &f);
+  int32_t st = fill_fwd_params(d, q, k, v, const_cast<void*>(out), nullptr, &f);
   if (st != B200FA_OK) return st;
-  if (!aligned16(dout) || !aligned16(dq) || !aligned16(dk) || !aligned16(dv))
-    return fail(B200FA_ERR_INVALID_ARG, "dout, dq, dk, dv must be 16-byte aligned");
-  if (d->D == 256) return fail(B200FA_ERR_UNSUPPORTED, "backward for head_dim 256 is not built");
-  b200fa::BwdParams p;
+  b200fa::BwdParams& p = *pp;
   memset(&p, 0, sizeof(p));
   p.q = q; p.k = k; p.v = v; p.o = out; p.dout = dout; p.lse = lse;
   p.dq = dq; p.dk = dk; p.dv = dv;
@@ -257,13 +241,51 @@ static int32_t bwd_common(const b200fa_desc* d, const void* q, const void* k, co
   p.gqa = f.gqa; p.scale = d->scale; p.scale_log2 = f.scale_log2; p.causal = f.causal;
   p.softcap = d->softcap; p.window_left = d->window_left;
   p.cu_q = cu_q; p.cu_k = cu_k;
-  if ((d->alibi_slopes != nullptr || d->block_mask != nullptr) && varlen)
-    return fail(B200FA_ERR_UNSUPPORTED, "alibi_slopes / block_mask with packed sequences are not built");
   p.alibi = d->alibi_slopes;       // biased / block-masked scores are recomputed by the portable kernel only
   p.bmask = d->block_mask;
   p.bm_bq = d->mask_bq; p.bm_bk = d->mask_bk; p.bm_nk = d->mask_nk;
-  cudaError_t e = b200fa::launch_bwd(p, d->dtype, d->D, varlen, nbatch, max_q, max_k, workspace,
-                                     !(d->flags & B200FA_FLAG_FORCE_MMA_SYNC) && p.alibi == nullptr && p.bmask == nullptr,
+  return B200FA_OK;
+}
+
+static bool bwd_allow_sm100(const b200fa_desc* d) {
+  return !(d->flags & B200FA_FLAG_FORCE_MMA_SYNC) && d->alibi_slopes == nullptr && d->block_mask == nullptr;
+}
+
+// The split head_dim-128 path keeps no fp32 dQ accumulator, which is most of the workspace.
+static size_t bwd_need_bytes(const b200fa_desc* d) {
+  b200fa::BwdParams p;
+  if (d->dtype == B200FA_F32 || d->D == 256 ||
+      fill_bwd_params(d, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, &p) != B200FA_OK)
+    return b200fa::bwd_workspace_bytes(d->B, d->Hq, d->N, d->D, false);
+  return b200fa::bwd_workspace_bytes(d->B, d->Hq, d->N, d->D, b200fa::bwd_takes_split_path(p, d->dtype, d->D, bwd_allow_sm100(d)));
+}
+
+static int32_t bwd_common(const b200fa_desc* d, const void* q, const void* k, const void* v,
+                          const void* out, const float* lse, const void* dout, void* dq, void* dk,
+                          void* dv, const int32_t* cu_q, const int32_t* cu_k, int nbatch, int max_q,
+                          int max_k, void* workspace, size_t workspace_bytes, void* stream) {
+  const bool varlen = cu_q != nullptr;
+  int32_t st = check_common(d, varlen);
+  if (st != B200FA_OK) return st;
+  if (d->dtype == B200FA_F32)
+    return fail(B200FA_ERR_UNSUPPORTED, "backward is built for f16 and bf16 (the reference's STEEL backward, "
+                                        "mlx_mfa/attention.py:2008-2012, takes the same)");
+  if (d->B == 0 || d->N == 0 || nbatch == 0) return B200FA_OK;
+  if (!q || !k || !v || !out || !lse || !dout || !dq || !dk || !dv)
+    return fail(B200FA_ERR_INVALID_ARG, "null tensor pointer");
+  if (d->D == 256) return fail(B200FA_ERR_UNSUPPORTED, "backward for head_dim 256 is not built");
+  const size_t need = bwd_need_bytes(d);
+  if (workspace == nullptr || workspace_bytes < need)
+    return fail(B200FA_ERR_WORKSPACE, "backward needs %zu workspace bytes, got %zu", need, workspace_bytes);
+  if (!aligned16(workspace)) return fail(B200FA_ERR_INVALID_ARG, "workspace must be 16-byte aligned");
+  if (!aligned16(dout) || !aligned16(dq) || !aligned16(dk) || !aligned16(dv))
+    return fail(B200FA_ERR_INVALID_ARG, "dout, dq, dk, dv must be 16-byte aligned");
+  if ((d->alibi_slopes != nullptr || d->block_mask != nullptr) && varlen)
+    return fail(B200FA_ERR_UNSUPPORTED, "alibi_slopes / block_mask with packed sequences are not built");
+  b200fa::BwdParams p;
+  st = fill_bwd_params(d, q, k, v, out, lse, dout, dq, dk, dv, cu_q, cu_k, &p);
+  if (st != B200FA_OK) return st;
+  cudaError_t e = b200fa::launch_bwd(p, d->dtype, d->D, varlen, nbatch, max_q, max_k, workspace, bwd_allow_sm100(d),
                                      reinterpret_cast<cudaStream_t>(stream));
   if (e != cudaSuccess) return cuda_fail(e, "backward launch");
   return B200FA_OK;
@@ -271,7 +293,7 @@ static int32_t bwd_common(const b200fa_desc* d, const void* q, const void* k, co
 
 size_t b200fa_bwd_workspace_bytes(const b200fa_desc* d) {
   if (d == nullptr) return 0;
-  return b200fa::bwd_workspace_bytes(d->B, d->Hq, d->N, d->D);
+  return bwd_need_bytes(d);
 }
 
 int32_t b200fa_bwd(const b200fa_desc* d, const void* q, const void* k, const void* v, const void* out,
@@ -286,7 +308,7 @@ size_t b200fa_bwd_varlen_workspace_bytes(const b200fa_desc* d, int32_t num_seqs,
                                          int32_t max_seqlen_k) {
   (void)num_seqs; (void)max_seqlen_q; (void)max_seqlen_k;
   if (d == nullptr) return 0;
-  return b200fa::bwd_workspace_bytes(d->B, d->Hq, d->N, d->D);
+  return bwd_need_bytes(d);
 }
 
 int32_t b200fa_bwd_varlen(const b200fa_desc* d, const void* q, const void* k, const void* v,
@@ -397,10 +419,13 @@ int32_t b200fa_kernel_status(void* stream, int32_t* status_out) {
   if (status_out == nullptr) return fail(B200FA_ERR_INVALID_ARG, "status_out is null");
   cudaStream_t cs = reinterpret_cast<cudaStream_t>(stream);
   int a = 0, b = 0;
+  int c = 0, dd = 0;
   cudaError_t e = b200fa::fwd_sm100_read_clear_status(cs, &a);
   if (e == cudaSuccess) e = b200fa::bwd_sm100_read_clear_status(cs, &b);
+  if (e == cudaSuccess) e = b200fa::bwd_dkv_sm100_read_clear_status(cs, &c);
+  if (e == cudaSuccess) e = b200fa::bwd_dq_sm100_read_clear_status(cs, &dd);
   if (e != cudaSuccess) return cuda_fail(e, "kernel status read");
-  *status_out = a | b;
+  *status_out = a | b | c | dd;
   return B200FA_OK;
 }
 

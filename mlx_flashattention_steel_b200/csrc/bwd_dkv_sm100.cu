@@ -1,0 +1,510 @@
+// Blackwell backward, head_dim 128, part 2 of 2: dK and dV.  tcgen05 MMAs with every accumulator in TMEM.
+//
+// The counterpart of the reference's dK/dV kernel (csrc/mfa_steel_bwd.cpp:765-1293); dQ is computed by
+// bwd_dq_sm100.cu.  One persistent CTA per SM takes work items from a global counter; an item is a tile of 128 keys of
+// one kv head, for which the CTA walks the query heads of the GQA group and the 128-row query tiles that can see those
+// keys.  Per query tile, four GEMMs with M = 128 key rows, the query tile handled as two halves x of 64 queries:
+//   S^T_x  = K . Q_x^T     (SS, N = 64, K = 128)                    -> TMEM [0,64) / [128,192)
+//   dP^T_x = V . dO_x^T    (SS, N = 64, K = 128)                    -> TMEM [64,128) / [192,256)
+//   8 compute warps (thread = key row, two warps per 32 rows splitting the query columns) turn these into
+//   P^T = 2^(s - L) and dS^T = P^T o (dP^T - delta) [x (1 - tanh^2) under a soft cap], written back as 16-bit A
+//   operands over the columns they came from
+//   dV += P^T_x . dO_x     (A from TMEM, B = dO as an MN-major operand, N = 128)   -> TMEM [256,384)
+//   dK += dS^T_x . Q_x     (A from TMEM, B = Q MN-major, N = 128)                  -> TMEM [384,512)
+// All 512 TMEM columns are in use, so K and V stay in shared memory as A operands.  The two query halves have their
+// own S^T / dP^T columns: the MMAs of one half (and the next tile's S^T / dP^T) run while the compute warps work on
+// the other half.  Warp 8 is the TMA producer (K and V once per item; Q and dO double-buffered, with -L and -delta of
+// the query rows staged beside them), one thread of warp 9 issues the MMAs.  dK / dV leave TMEM once per item, through
+// shared memory as whole rows.  No load uses cluster multicast; every mbarrier wait is bounded and a timeout raises
+// this file's status word (read through b200fa_kernel_status).
+#include <type_traits>
+
+#include "common.cuh"
+#include "launch.h"
+#include "tcgen05.cuh"
+#include "tma.cuh"
+
+namespace b200fa {
+// Device status word of this file's kernels: bit 0 = a bounded wait gave up.
+static __device__ int g_kernel_status = 0;
+
+namespace {
+
+constexpr int HD = 128;
+constexpr int BK = 128;      // keys per item (TMEM lanes)
+constexpr int BQ = 128;      // queries per step, as two halves of 64
+constexpr int kThreads = 320;       // warps 0-7 compute, 8 producer, 9 MMA issue
+constexpr uint32_t kTmemCols = 512;
+constexpr uint32_t cST = 0, cDPT = 64, cDV = 256, cDK = 384;     // S^T_x at cST + 128x, dP^T_x at cDPT + 128x
+
+constexpr int kTileBytes = 128 * HD * 2;                 // 32768: one [2 d-halves][128 rows][128 B] tile
+constexpr int kHalfBytes = kTileBytes / 2;
+constexpr int kStatBytes = 2 * 2 * BQ * 4;               // L and delta, two stages
+constexpr int kSmemTiles = 2 * kTileBytes + 4 * kTileBytes;        // K, V, Q x2, dO x2 = 196608
+constexpr int kSmemBytes = kSmemTiles + kStatBytes + 256 + 1024;
+
+// BAR_KV lives for the whole kernel; the others are set up again for every work item
+enum Bar { BAR_KV = 0, BAR_Q_FULL = 1, BAR_Q_EMPTY = 3, BAR_ST_DONE = 5 /* + half */, BAR_PD_READY = 7 /* + half */, BAR_ACC_DONE = 9, BAR_COUNT = 10 };
+
+struct DkvArgs {
+  BwdParams p;
+  int gx, gy, total_items;      // work items: (key tile, kv head, batch | sequence), key tile fastest
+  int* counter;                 // next work item (zeroed by the preprocess kernel)
+};
+
+__device__ __forceinline__ float4 lds_f4(uint32_t addr) {
+  float4 v;
+  asm("ld.shared.v4.f32 {%0,%1,%2,%3}, [%4];\n" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(addr));
+  return v;
+}
+__device__ __forceinline__ void sts_v4(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+  asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};\n" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
+}
+__device__ __forceinline__ void lds_v4u(uint32_t addr, uint32_t& a, uint32_t& b, uint32_t& c, uint32_t& d) {
+  asm volatile("ld.shared.v4.b32 {%0,%1,%2,%3}, [%4];\n" : "=r"(a), "=r"(b), "=r"(c), "=r"(d) : "r"(addr) : "memory");
+}
+// The address of the L / delta rows must come from here, issued after the wait that makes the data visible, so that
+// no (non-volatile) load moves above that wait or is merged with the same address of another tile.
+__device__ __forceinline__ uint32_t opaque_u32(uint32_t x) {
+  uint32_t y;
+  asm volatile("mov.u32 %0, %1;\n" : "=r"(y) : "r"(x) : "memory");
+  return y;
+}
+template <int DT> __device__ __forceinline__ uint32_t pack16k(float a, float b) {
+  return DT == 0 ? Elem<__half>::pack(a, b) : Elem<__nv_bfloat16>::pack(a, b);
+}
+
+template <int DT, bool CAP>
+__global__ void __launch_bounds__(kThreads, 1)
+bwd_dkv_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                     const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmDO, const DkvArgs a) {
+  extern __shared__ __align__(1024) unsigned char smem_raw[];
+  unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  unsigned char* sK = smem;
+  unsigned char* sV = sK + kTileBytes;
+  unsigned char* sQ = sV + kTileBytes;                 // [2 stages][2 d-halves][128][128 B]
+  unsigned char* sDO = sQ + 2 * kTileBytes;
+  float* sL = reinterpret_cast<float*>(smem + kSmemTiles);      // [2][BQ]
+  float* sDel = sL + 2 * BQ;                                    // [2][BQ]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kSmemTiles + kStatBytes);
+  uint32_t* s_tmem = reinterpret_cast<uint32_t*>(bars + BAR_COUNT);
+  volatile int* s_abort = reinterpret_cast<volatile int*>(s_tmem + 1);
+  // [2][8]: this item and the next one as {index or -1, key tile, kv head, batch, k_begin, S, q_begin, N}
+  volatile int* s_work = reinterpret_cast<volatile int*>(s_tmem + 2);
+
+  const BwdParams& p = a.p;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  auto bar = [&](int i) -> uint32_t { return smem_u32(&bars[i]); };
+
+  // Next item that has keys (grid cells beyond a sequence's end are skipped), decoded into slot `sl` of s_work for
+  // every role to read; index -1 when the list is exhausted.  Run by one thread.
+  auto fetch_next = [&](int sl) -> int {
+    volatile int* o = s_work + sl * 8;
+    for (int tries = 0; tries < (1 << 24); ++tries) {
+      const int idx = atomicAdd(a.counter, 1);
+      if (idx >= a.total_items) break;
+      const int kt = idx % a.gx, kvh_ = (idx / a.gx) % a.gy, z = idx / (a.gx * a.gy);
+      int kb = 0, S_ = p.S, qb = 0, N_ = p.N;
+      if (p.cu_k != nullptr) {
+        kb = p.cu_k[z];
+        S_ = p.cu_k[z + 1] - kb;
+      }
+      if (kt * BK >= S_) continue;
+      if (p.cu_q != nullptr) {
+        qb = p.cu_q[z];
+        N_ = p.cu_q[z + 1] - qb;
+      }
+      o[1] = kt; o[2] = kvh_; o[3] = p.cu_q != nullptr ? 0 : z; o[4] = kb; o[5] = S_; o[6] = qb; o[7] = N_;
+      o[0] = idx;
+      return idx;
+    }
+    o[0] = -1;
+    return -1;
+  };
+  if (warp == 8 && lane == 0) {
+    mbar_init(bar(BAR_KV), 1);
+    *s_abort = 0;
+    fence_barrier_init();
+    fence_proxy_async();
+    fetch_next(0);
+  }
+  if (warp == 9) {
+    tmem_alloc(smem_u32(s_tmem), kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *s_tmem;
+  int kv_uses = 0;                                       // items so far that loaded K / V (phase of BAR_KV)
+
+  for (int w = 0;; ++w) {
+  volatile int* wk = s_work + (w & 1) * 8;
+  if (wk[0] < 0 || *s_abort != 0) break;
+  const int kvh = wk[2], bb = wk[3], k_begin = wk[4], S = wk[5], q_begin = wk[6], N = wk[7];
+  const int n0 = wk[1] * BK;
+  const int off = S - N;
+  int m_begin = 0;
+  if (p.causal) m_begin = max(0, n0 - off) / BQ;
+  int m_end = (N + BQ - 1) / BQ;
+  // a left window: the last row that still sees this tile's last key is i = key - off + window_left
+  if (p.window_left >= 0) m_end = min(m_end, max(0, min(S, n0 + BK) - 1 - off + p.window_left) / BQ + 1);
+  const int nm = max(0, m_end - m_begin);
+  const int n_iter = nm * p.gqa;
+  const uint32_t kv_par = kv_uses & 1;
+  if (n_iter > 0) ++kv_uses;
+
+  auto load_q = [&](int it) {
+    const int st = it & 1;
+    const int hq = kvh * p.gqa + it / nm, m = m_begin + it % nm;
+    mbar_expect_tx(bar(BAR_Q_FULL + st), 2 * kTileBytes);
+#pragma unroll
+    for (int hf = 0; hf < 2; ++hf) {
+      tma_load_4d(smem_u32(sQ + st * kTileBytes + hf * kHalfBytes), &tmQ, bar(BAR_Q_FULL + st), 64 * hf, q_begin + m * BQ, hq, bb);
+      tma_load_4d(smem_u32(sDO + st * kTileBytes + hf * kHalfBytes), &tmDO, bar(BAR_Q_FULL + st), 64 * hf, q_begin + m * BQ, hq, bb);
+    }
+  };
+  if (warp == 8 && lane == 0) {
+    if (w > 0)
+      for (int i = BAR_Q_FULL; i < BAR_COUNT; ++i) mbar_inval(bar(i));    // nobody waits or arrives between items
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(bar(BAR_Q_FULL + s), 1);
+      mbar_init(bar(BAR_Q_EMPTY + s), 1);
+    }
+    for (int x = 0; x < 2; ++x) {
+      mbar_init(bar(BAR_ST_DONE + x), 1);
+      mbar_init(bar(BAR_PD_READY + x), 8);  // one arrive per compute warp
+    }
+    mbar_init(bar(BAR_ACC_DONE), 1);
+    fence_barrier_init();
+    fence_proxy_async();
+    if (n_iter > 0) {
+      mbar_arrive_expect_tx(bar(BAR_KV), 2 * kTileBytes);
+#pragma unroll
+      for (int hf = 0; hf < 2; ++hf) {
+        tma_load_4d(smem_u32(sK + hf * kHalfBytes), &tmK, bar(BAR_KV), 64 * hf, k_begin + n0, kvh, bb);
+        tma_load_4d(smem_u32(sV + hf * kHalfBytes), &tmV, bar(BAR_KV), 64 * hf, k_begin + n0, kvh, bb);
+      }
+      load_q(0);
+      if (n_iter > 1) load_q(1);
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+
+  if (warp == 8) {
+    // ============================ producer ============================
+    for (int it = 0; it < n_iter; ++it) {
+      const int st = it & 1;
+      const int hq = kvh * p.gqa + it / nm, m = m_begin + it % nm;
+      // -L and -delta of the 128 query rows ride with the Q tile; rows beyond N (or without any visible key)
+      // get L = +inf so that their P is exactly zero
+      float Lr[4], dr[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int row = m * BQ + lane * 4 + i;
+        Lr[i] = INFINITY;
+        dr[i] = 0.f;
+        if (row < N) {
+          const int64_t idx = bb * p.lse_bs + hq * p.lse_hs + q_begin + row;
+          Lr[i] = p.lse[idx];
+          dr[i] = p.delta[idx];
+          if (Lr[i] == -INFINITY) Lr[i] = INFINITY;
+        }
+      }
+      if (it >= 2) {
+        if (!__all_sync(0xffffffffu, mbar_wait_bounded(bar(BAR_Q_EMPTY + st), ((it >> 1) & 1) ^ 1, s_abort))) break;
+        if (lane == 0) load_q(it);
+      }
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        sL[st * BQ + lane * 4 + i] = -Lr[i];            // stored negated: the compute loop adds them
+        sDel[st * BQ + lane * 4 + i] = -dr[i];
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar(BAR_Q_FULL + st));
+      __syncwarp();
+    }
+    // the next item, for every role to read after the end-of-item sync
+    if (lane == 0) fetch_next((w + 1) & 1);
+  } else if (warp == 9) {
+   if (lane == 0 && n_iter > 0) {
+    // ============================ MMA issue ============================
+    // Per query tile t and query half x: [S^T_x, dP^T_x] -> (compute) -> [dV += P^T_x.dO_x, dK += dS^T_x.Q_x].
+    //   ST/DPT a,b (t=0) | PD_a -> dV_a dK_a, ST/DPT a (t+1) | PD_b -> dV_b dK_b, ST/DPT b (t+1) | ...
+    const uint32_t id_st = instr_desc(DT, 0, 128, 64);     // S^T, dP^T of one half: B K-major, N = 64
+    const uint32_t id_mn = instr_desc(DT, 1, 128, HD);     // dV, dK: B MN-major, N = 128
+    const uint64_t kd = smem_desc(smem_u32(sK), 16, 1024), vd = smem_desc(smem_u32(sV), 16, 1024);
+    const uint64_t qd0 = smem_desc(smem_u32(sQ), 16, 1024), dod0 = smem_desc(smem_u32(sDO), 16, 1024);
+    const uint64_t qmn0 = smem_desc(smem_u32(sQ), kHalfBytes, 1024), domn0 = smem_desc(smem_u32(sDO), kHalfBytes, 1024);
+    constexpr uint64_t kTileU = kTileBytes >> 4, kHalfU = kHalfBytes >> 4, kHalfRowsU = (64 * 128) >> 4;
+    bool ok = mbar_wait_bounded(bar(BAR_KV), kv_par, s_abort);
+    tc_fence_after();
+    // S^T_x and dP^T_x of tile `it`: A = the K / V rows (K-major, two d-halves), B rows = the 64 queries of half x
+    auto issue_stdp = [&](int it, int x) {
+      const int st = it & 1;
+      const uint64_t qd = qd0 + st * kTileU + x * kHalfRowsU, dod = dod0 + st * kTileU + x * kHalfRowsU;
+#pragma unroll
+      for (int k = 0; k < HD / 16; ++k)
+        mma_ss(tmem + cST + 128 * x, kd + (k >> 2) * kHalfU + (k & 3) * 2, qd + (k >> 2) * kHalfU + (k & 3) * 2, id_st,
+               k > 0 ? 1u : 0u);
+#pragma unroll
+      for (int k = 0; k < HD / 16; ++k)
+        mma_ss(tmem + cDPT + 128 * x, vd + (k >> 2) * kHalfU + (k & 3) * 2, dod + (k >> 2) * kHalfU + (k & 3) * 2, id_st,
+               k > 0 ? 1u : 0u);
+      tc_commit(bar(BAR_ST_DONE + x));
+    };
+    if (ok) ok = mbar_wait_bounded(bar(BAR_Q_FULL), 0, s_abort);
+    if (ok) {
+      tc_fence_after();
+      issue_stdp(0, 0);
+      issue_stdp(0, 1);
+    }
+    for (int it = 0; it < n_iter && ok; ++it) {
+      const int st = it & 1;
+#pragma unroll
+      for (int x = 0; x < 2; ++x) {
+        // the compute warps vouch, before they arrive here, that the next tile's Q / dO have landed (half a)
+        if (!mbar_wait_bounded(bar(BAR_PD_READY + x), it & 1, s_abort)) { ok = false; break; }
+        tc_fence_after();
+        const uint64_t qmn = qmn0 + st * kTileU + x * kHalfRowsU, domn = domn0 + st * kTileU + x * kHalfRowsU;
+        // A in TMEM: 8 columns per 16 queries; queries 0-31 of the half at +0, 32-63 at +32 (where the two warps of a
+        // row wrote them); B rows = queries, 16 rows = 128 units
+#pragma unroll
+        for (int k = 0; k < 4; ++k)
+          mma_ts(tmem + cDV, tmem + cST + 128 * x + (k >> 1) * 32 + (k & 1) * 8, domn + k * 128, id_mn,
+                 (it > 0 || x > 0 || k > 0) ? 1u : 0u);
+#pragma unroll
+        for (int k = 0; k < 4; ++k)
+          mma_ts(tmem + cDK, tmem + cDPT + 128 * x + (k >> 1) * 32 + (k & 1) * 8, qmn + k * 128, id_mn,
+                 (it > 0 || x > 0 || k > 0) ? 1u : 0u);
+        if (x == 1) tc_commit(bar(BAR_Q_EMPTY + st));
+        // the buffers of half x are free again (the MMAs above read them in pipe order before anything issued now)
+        if (it + 1 < n_iter) issue_stdp(it + 1, x);
+      }
+    }
+    if (ok) tc_commit(bar(BAR_ACC_DONE));
+   }
+  } else {
+    // ============================ compute warps 0-7 ============================
+    const int wq = warp & 3, hf = warp >> 2;                 // TMEM lane quarter, column half
+    const int rloc = wq * 32 + lane;                         // key row inside the tile
+    const int key = n0 + rloc;
+    const uint32_t lane_base = static_cast<uint32_t>(wq * 32) << 16;
+    if (n_iter == 0) {
+      // no query sees these keys: dK = dV = 0
+      if (key < S) {
+        const int64_t o = bb * p.dk_bs + kvh * p.dk_hs + static_cast<int64_t>(k_begin + key) * p.dk_rs + hf * 64;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          reinterpret_cast<uint4*>(reinterpret_cast<uint16_t*>(p.dk) + o)[i] = make_uint4(0u, 0u, 0u, 0u);
+          reinterpret_cast<uint4*>(reinterpret_cast<uint16_t*>(p.dv) + o)[i] = make_uint4(0u, 0u, 0u, 0u);
+        }
+      }
+    } else {
+    bool ok = true;
+    for (int it = 0; it < n_iter && ok; ++it) {
+      const int st = it & 1;
+      const int m = m_begin + it % nm;
+      if (!__all_sync(0xffffffffu, mbar_wait_bounded(bar(BAR_Q_FULL + st), (it >> 1) & 1, s_abort))) { ok = false; break; }
+      const uint32_t Ls = opaque_u32(smem_u32(sL + st * BQ)), Ds = Ls + 2 * BQ * 4;
+      const bool need_mask = (n0 + BK > S) || (p.causal && (n0 + BK - 1 > m * BQ + off)) ||
+                             (p.window_left >= 0 && (n0 < m * BQ + BQ - 1 + off - p.window_left));
+      const int wlo = p.window_left >= 0 ? off - p.window_left : -0x40000000;    // key visible iff key >= qrow + wlo
+      const float2 c2 = make_float2(p.scale_log2, p.scale_log2);
+      const float cap_in = CAP ? p.scale / p.softcap : 0.f, cap_out = p.softcap * kLog2e;
+      const bool precise_tanh = p.softcap >= kPreciseTanhMinCap;
+
+      auto run_half = [&](int x, auto masked) {
+        const int q0l = x * 64 + hf * 32;                  // first query (inside the tile) of this warp's 32 columns
+        uint32_t rs[32], rd[32];
+        tmem_ld32(tmem + lane_base + cST + 128 * x + hf * 32, rs);
+        tmem_ld32(tmem + lane_base + cDPT + 128 * x + hf * 32, rd);
+        tc_wait_ld();
+        uint32_t pp[16], pd[16];
+#pragma unroll
+        for (int i = 0; i < 32; i += 4) {
+          const float4 nL = lds_f4(Ls + (q0l + i) * 4);      // -L of four queries
+          const float4 nD = lds_f4(Ds + (q0l + i) * 4);      // -delta
+#pragma unroll
+          for (int e = 0; e < 4; e += 2) {
+            const float2 sv = make_float2(__uint_as_float(rs[i + e]), __uint_as_float(rs[i + e + 1]));
+            const float2 dv = make_float2(__uint_as_float(rd[i + e]), __uint_as_float(rd[i + e + 1]));
+            const float2 nl = e == 0 ? make_float2(nL.x, nL.y) : make_float2(nL.z, nL.w);
+            const float2 nd = e == 0 ? make_float2(nD.x, nD.y) : make_float2(nD.z, nD.w);
+            float2 t, dcap;
+            if constexpr (CAP) {
+              const float2 th = make_float2(cap_tanh(sv.x * cap_in, precise_tanh), cap_tanh(sv.y * cap_in, precise_tanh));
+              t = __ffma2_rn(th, make_float2(cap_out, cap_out), nl);
+              dcap = __ffma2_rn(make_float2(-th.x, -th.y), th, make_float2(1.f, 1.f));
+            } else {
+              t = __ffma2_rn(sv, c2, nl);
+            }
+            float2 pe = make_float2(fast_exp2(t.x), fast_exp2(t.y));
+            if constexpr (decltype(masked)::value) {
+              const int qrow = m * BQ + q0l + i + e;
+              const bool kin = key < S;
+              if (!(kin && (!p.causal || key <= qrow + off) && key >= qrow + wlo)) pe.x = 0.f;
+              if (!(kin && (!p.causal || key <= qrow + 1 + off) && key >= qrow + 1 + wlo)) pe.y = 0.f;
+            }
+            float2 dsv = __fmul2_rn(pe, __fadd2_rn(dv, nd));
+            if constexpr (CAP) dsv = __fmul2_rn(dsv, dcap);
+            pp[(i + e) >> 1] = pack16k<DT>(pe.x, pe.y);
+            pd[(i + e) >> 1] = pack16k<DT>(dsv.x, dsv.y);
+          }
+        }
+        // P^T and dS^T go back as 16-bit pairs along the query index, inside the 32 columns this warp has just read
+        // (the other warp of these rows may still be reading its own 32)
+        tmem_st16(tmem + lane_base + cST + 128 * x + hf * 32, pp);
+        tmem_st16(tmem + lane_base + cDPT + 128 * x + hf * 32, pd);
+      };
+
+#pragma unroll
+      for (int x = 0; x < 2; ++x) {
+        if (!__all_sync(0xffffffffu, mbar_wait_bounded(bar(BAR_ST_DONE + x), it & 1, s_abort))) { ok = false; break; }
+        tc_fence_after();
+        if (need_mask) run_half(x, std::true_type{}); else run_half(x, std::false_type{});
+        tc_wait_st();
+        // on behalf of the MMA thread: half a vouches for the next tile's Q / dO (its S^T / dP^T are issued right
+        // after this half's dV / dK).  The barrier cannot be more than one completion ahead: the next fill of that
+        // stage needs this arrival first.
+        if (x == 0 && it + 1 < n_iter &&
+            !__all_sync(0xffffffffu, mbar_wait_bounded(bar(BAR_Q_FULL + ((it + 1) & 1)), ((it + 1) >> 1) & 1, s_abort))) { ok = false; break; }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar(BAR_PD_READY + x));
+      }
+    }
+
+    if (ok) ok = __all_sync(0xffffffffu, mbar_wait_bounded(bar(BAR_ACC_DONE), 0, s_abort));
+    // dK, dV: rows = keys, this warp's d-half hf (64 of the 128 columns).  The tiles go through shared memory (the
+    // Q stages, which nothing reads any more: dK in stage 0, dV in stage 1) so that each store instruction writes
+    // whole 128-byte rows.
+    if (ok) {
+      tc_fence_after();
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        uint32_t rk[32], rv[32];
+        tmem_ld32(tmem + lane_base + cDK + hf * 64 + c * 32, rk);
+        tmem_ld32(tmem + lane_base + cDV + hf * 64 + c * 32, rv);
+        tc_wait_ld();
+        const uint32_t srow = smem_u32(sQ) + hf * kHalfBytes + rloc * 128;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const int i = 8 * j;
+          const uint32_t o = static_cast<uint32_t>(((c * 4 + j) ^ (rloc & 7)) << 4);
+          sts_v4(srow + o, pack16k<DT>(__uint_as_float(rk[i]) * p.scale, __uint_as_float(rk[i + 1]) * p.scale),
+                 pack16k<DT>(__uint_as_float(rk[i + 2]) * p.scale, __uint_as_float(rk[i + 3]) * p.scale),
+                 pack16k<DT>(__uint_as_float(rk[i + 4]) * p.scale, __uint_as_float(rk[i + 5]) * p.scale),
+                 pack16k<DT>(__uint_as_float(rk[i + 6]) * p.scale, __uint_as_float(rk[i + 7]) * p.scale));
+          sts_v4(srow + kTileBytes + o, pack16k<DT>(__uint_as_float(rv[i]), __uint_as_float(rv[i + 1])),
+                 pack16k<DT>(__uint_as_float(rv[i + 2]), __uint_as_float(rv[i + 3])),
+                 pack16k<DT>(__uint_as_float(rv[i + 4]), __uint_as_float(rv[i + 5])),
+                 pack16k<DT>(__uint_as_float(rv[i + 6]), __uint_as_float(rv[i + 7])));
+        }
+      }
+    }
+    // all eight compute warps pass here, whatever happened before (a named barrier has no time-out)
+    asm volatile("bar.sync 1, 256;\n" ::: "memory");
+    if (ok) {
+      // 128 rows x 2 d-halves x 8 chunks of 16 bytes per tensor; a warp instruction covers four whole half-rows
+#pragma unroll
+      for (int r8 = 0; r8 < 8; ++r8) {
+        const int i = r8 * 256 + tid;
+        const int h = i >> 10, r = (i >> 3) & 127, c = i & 7;
+        const uint32_t sa = smem_u32(sQ) + h * kHalfBytes + r * 128 + static_cast<uint32_t>((c ^ (r & 7)) << 4);
+        uint4 vk, vv;
+        lds_v4u(sa, vk.x, vk.y, vk.z, vk.w);
+        lds_v4u(sa + kTileBytes, vv.x, vv.y, vv.z, vv.w);
+        if (n0 + r < S) {
+          const int64_t o = bb * p.dk_bs + kvh * p.dk_hs + static_cast<int64_t>(k_begin + n0 + r) * p.dk_rs + h * 64 + c * 8;
+          *reinterpret_cast<uint4*>(reinterpret_cast<uint16_t*>(p.dk) + o) = vk;
+          *reinterpret_cast<uint4*>(reinterpret_cast<uint16_t*>(p.dv) + o) = vv;
+        }
+      }
+    }
+    }  // n_iter > 0
+  }
+
+  // ---- end of the item: every MMA has completed (the compute warps saw ACC_DONE), the epilogue has read its staging
+  // rows; the barriers may be set up again and the tiles refilled
+  __syncwarp();
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  }  // work items
+
+  // ---- teardown ----
+  __syncwarp();
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 9) {
+    tc_fence_after();
+    tmem_dealloc(tmem, kTmemCols);
+  }
+  if (tid == 0 && *s_abort != 0) atomicOr(&g_kernel_status, 1);
+}
+
+bool make_map128k(CUtensorMap* m, int dtype, const void* base, int rows, int H, int B, int64_t rs, int64_t hs, int64_t bs) {
+  const uint64_t dims[4] = {static_cast<uint64_t>(HD), static_cast<uint64_t>(rows), static_cast<uint64_t>(H),
+                            static_cast<uint64_t>(B)};
+  const uint64_t strides[3] = {static_cast<uint64_t>(rs) * 2, static_cast<uint64_t>(hs) * 2, static_cast<uint64_t>(bs) * 2};
+  const uint32_t box[4] = {64, 128, 1, 1};
+  return encode_tmap(m, dtype == 0 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, base, dims,
+                     strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
+}
+
+}  // namespace
+
+bool bwd_split_sm100_supported(int dtype, int D) { return (dtype == 0 || dtype == 1) && D == HD && get_encode_tiled() != nullptr; }
+
+// dK and dV for head_dim 128; p.delta must hold delta and *p.work_counter zero.
+cudaError_t launch_bwd_dkv_sm100(const BwdParams& p, int dtype, int nbatch, int max_k, cudaStream_t stream) {
+  if (nbatch <= 0 || max_k <= 0) return cudaSuccess;
+  CUtensorMap tmQ, tmK, tmV, tmDO;
+  auto fix = [](int64_t s, int64_t fallback) { return s > 0 ? s : fallback; };   // size-1 dimensions only (see bwd_sm100_strides_ok)
+  const int64_t q_hs = fix(p.q_hs, static_cast<int64_t>(p.N) * p.q_rs), q_bs = fix(p.q_bs, q_hs * p.Hq);
+  const int64_t k_hs = fix(p.k_hs, static_cast<int64_t>(p.S) * p.k_rs), k_bs = fix(p.k_bs, k_hs * p.Hkv);
+  const int64_t v_hs = fix(p.v_hs, static_cast<int64_t>(p.S) * p.v_rs), v_bs = fix(p.v_bs, v_hs * p.Hkv);
+  const int64_t do_hs = static_cast<int64_t>(p.N) * HD, do_bs = do_hs * p.Hq;
+  if (!make_map128k(&tmQ, dtype, p.q, p.N, p.Hq, p.B, p.q_rs, q_hs, q_bs) ||
+      !make_map128k(&tmK, dtype, p.k, p.S, p.Hkv, p.B, p.k_rs, k_hs, k_bs) ||
+      !make_map128k(&tmV, dtype, p.v, p.S, p.Hkv, p.B, p.v_rs, v_hs, v_bs) ||
+      !make_map128k(&tmDO, dtype, p.dout, p.N, p.Hq, p.B, HD, do_hs, do_bs))
+    return cudaErrorInvalidValue;
+  DkvArgs a;
+  a.p = p;
+  a.gx = (max_k + BK - 1) / BK;
+  a.gy = p.Hkv;
+  const long long items = static_cast<long long>(a.gx) * a.gy * nbatch;
+  if (items > 0x7fffffffLL || p.work_counter == nullptr) return cudaErrorInvalidValue;
+  a.total_items = static_cast<int>(items);
+  a.counter = p.work_counter;
+  int dev = 0, sm_count = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess ||
+      sm_count <= 0)
+    sm_count = 148;
+  dim3 grid(static_cast<unsigned>(items < sm_count ? items : sm_count), 1, 1);   // one persistent CTA per SM
+  auto launch = [&](auto kern) -> cudaError_t {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+    if (e != cudaSuccess) return e;
+    kern<<<grid, kThreads, kSmemBytes, stream>>>(tmQ, tmK, tmV, tmDO, a);
+    return cudaGetLastError();
+  };
+  const bool cap = p.softcap > 0.f;
+  if (dtype == 0) return cap ? launch(bwd_dkv_sm100_kernel<0, true>) : launch(bwd_dkv_sm100_kernel<0, false>);
+  return cap ? launch(bwd_dkv_sm100_kernel<1, true>) : launch(bwd_dkv_sm100_kernel<1, false>);
+}
+
+cudaError_t bwd_dkv_sm100_read_clear_status(cudaStream_t stream, int* out) {
+  const int zero = 0;
+  cudaError_t e = cudaMemcpyFromSymbolAsync(out, g_kernel_status, sizeof(int), 0, cudaMemcpyDeviceToHost, stream);
+  if (e == cudaSuccess) e = cudaStreamSynchronize(stream);
+  if (e == cudaSuccess && *out != 0)
+    e = cudaMemcpyToSymbolAsync(g_kernel_status, &zero, sizeof(int), 0, cudaMemcpyHostToDevice, stream);
+  if (e == cudaSuccess) e = cudaStreamSynchronize(stream);
+  return e;
+}
+
+}  // namespace b200fa

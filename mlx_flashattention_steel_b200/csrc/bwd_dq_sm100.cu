@@ -1,0 +1,386 @@
+// Blackwell backward, head_dim 128, part 1 of 2: dQ.  tcgen05 MMAs with TMEM accumulators, TMA-staged tiles.
+//
+// The reference splits its backward into a dQ kernel and a dK/dV kernel (csrc/mfa_steel_bwd.cpp:284-745 and
+// 765-1293; dispatch csrc/mfa_attention.cpp:732-930); so does this path for head_dim 128, where one kernel holding
+// S^T, dP^T, dV, dK and dQ would need 640 TMEM columns.  Each kernel recomputes P from the forward's lse.  dQ needs
+// no atomics this way: every query tile is owned by one CTA, so the result is bit-reproducible.
+//
+// One CTA = 128 query rows of one query head; it walks the 64-key tiles those rows can see (causal / window tiles
+// outside the band are skipped whole).  Per key tile j, three GEMMs with M = 128 query rows:
+//   S(j)  = Q . K(j)^T      (SS, N = 64, K = 128)  -> TMEM S buffer j & 1
+//   dP(j) = dO . V(j)^T     (SS, N = 64, K = 128)  -> TMEM dP buffer j & 1
+//   8 compute warps (thread = query row; the two warps of a lane quarter split the 64 key columns) form
+//   P = 2^(s - L) and dS = P o (dP - delta) [x (1 - tanh^2) under a soft cap] and write dS back as a 16-bit A operand
+//   over the dP columns they came from
+//   dQ   += dS(j) . K(j)    (A from TMEM, B = K(j) as an MN-major operand, N = 128)  -> TMEM dQ
+// Issue order SD(0) SD(1) dQ(0) SD(2) dQ(1) ... keeps the tensor pipe busy while the compute warps work on the other
+// buffer.  Warp 8 is the TMA producer (Q and dO once, K and V tiles into a three-stage ring), one thread of warp 9
+// issues the MMAs.  dQ leaves TMEM once, scaled, through shared memory (TMA store for the dense layout).
+// TMEM: [0,128) S0 S1, [128,256) dP0 dP1, [256,384) dQ.  No load uses cluster multicast; every mbarrier wait is
+// bounded and a timeout raises this file's status word (read through b200fa_kernel_status).
+#include "common.cuh"
+#include "launch.h"
+#include "tcgen05.cuh"
+#include "tma.cuh"
+
+namespace b200fa {
+// Device status word of this file's kernels: bit 0 = a bounded wait gave up.
+static __device__ int g_kernel_status = 0;
+
+namespace {
+
+constexpr int HD = 128;
+constexpr int BM = 128;            // query rows per CTA
+constexpr int BN = 64;             // keys per tile
+constexpr int kStages = 3;
+constexpr int kThreads = 320;      // warps 0-7 compute, 8 producer, 9 MMA issue
+constexpr uint32_t kTmemCols = 512;
+constexpr uint32_t cS = 0, cDP = 128, cDQ = 256;
+
+constexpr int kQBytes = BM * HD * 2;        // 32768: [2 d-halves][128 rows][128 B]
+constexpr int kKVBytes = BN * HD * 2;       // 16384: [2 d-halves][64 rows][128 B]
+constexpr int kStageBytes = 2 * kKVBytes;   // K then V
+constexpr int kSmemTiles = 2 * kQBytes + kStages * kStageBytes;
+constexpr int kSmemBytes = kSmemTiles + 256 + 1024;
+
+enum Bar {
+  BAR_Q = 0,
+  BAR_KV_FULL = 1,          // + stage
+  BAR_KV_EMPTY = 4,         // + stage: the dQ MMAs of the tile (the last readers of its K and V) have completed
+  BAR_SD_FULL = 7,          // + buffer: S and dP of a tile are complete
+  BAR_DS_READY = 9,         // + buffer: count 8, the compute warps have written dS
+  BAR_DQ_FINAL = 11,
+  BAR_STAGED = 12,          // count 8: the compute warps have staged their dQ rows in shared memory
+  BAR_COUNT = 13
+};
+
+struct DqArgs {
+  BwdParams p;
+  int tma_store;
+};
+
+template <int DT> __device__ __forceinline__ uint32_t pack16q(float a, float b) {
+  return DT == 0 ? Elem<__half>::pack(a, b) : Elem<__nv_bfloat16>::pack(a, b);
+}
+
+template <int DT, bool CAP>
+__global__ void __launch_bounds__(kThreads, 1)
+bwd_dq_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                    const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmDO,
+                    const __grid_constant__ CUtensorMap tmDQ, const DqArgs a) {
+  extern __shared__ __align__(1024) unsigned char smem_raw[];
+  unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  unsigned char* sQ = smem;
+  unsigned char* sDO = sQ + kQBytes;
+  unsigned char* sKV = sDO + kQBytes;                       // [stage][K | V]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kSmemTiles);
+  uint32_t* s_tmem = reinterpret_cast<uint32_t*>(bars + BAR_COUNT);
+  volatile int* s_abort = reinterpret_cast<volatile int*>(s_tmem + 1);
+
+  const BwdParams& p = a.p;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int head = blockIdx.y;
+  int batch = blockIdx.z;
+  const int kvh = head / p.gqa;
+  int N = p.N, S = p.S, q_begin = 0, k_begin = 0;
+  if (p.cu_q != nullptr) {
+    q_begin = p.cu_q[batch];
+    N = p.cu_q[batch + 1] - q_begin;
+    k_begin = p.cu_k[batch];
+    S = p.cu_k[batch + 1] - k_begin;
+    batch = 0;
+  }
+  const int q0 = (static_cast<int>(gridDim.x) - 1 - static_cast<int>(blockIdx.x)) * BM;   // heavy (late) tiles first
+  if (q0 >= N) return;
+  const int off = S - N;
+  int k_hi = S;
+  if (p.causal) k_hi = min(S, q0 + BM + off);
+  int k_lo = 0;
+  if (p.window_left >= 0) k_lo = max(0, q0 + off - p.window_left);
+  const int kt_begin = k_lo / BN;
+  const int kt_end = k_hi > 0 ? (k_hi + BN - 1) / BN : 0;
+  const int n_tiles = kt_end - kt_begin;
+
+  if (n_tiles <= 0) {
+    // no visible key for any row of this tile: dQ = 0
+    if (warp < 4) {
+      const int row = q0 + tid;
+      if (row < N) {
+        uint4* drow = reinterpret_cast<uint4*>(reinterpret_cast<uint16_t*>(p.dq) + batch * p.dq_bs + head * p.dq_hs +
+                                               static_cast<int64_t>(q_begin + row) * p.dq_rs);
+#pragma unroll
+        for (int i = 0; i < HD / 8; ++i) drow[i] = make_uint4(0u, 0u, 0u, 0u);
+      }
+    }
+    return;
+  }
+
+  auto bar = [&](int i) -> uint32_t { return smem_u32(&bars[i]); };
+  auto load_kv = [&](int j) {
+    const int st = j % kStages;
+    unsigned char* dst = sKV + st * kStageBytes;
+    mbar_arrive_expect_tx(bar(BAR_KV_FULL + st), kStageBytes);
+    const int row = k_begin + (kt_begin + j) * BN;
+#pragma unroll
+    for (int hf = 0; hf < 2; ++hf) {
+      tma_load_4d(smem_u32(dst + hf * (kKVBytes / 2)), &tmK, bar(BAR_KV_FULL + st), 64 * hf, row, kvh, batch);
+      tma_load_4d(smem_u32(dst + kKVBytes + hf * (kKVBytes / 2)), &tmV, bar(BAR_KV_FULL + st), 64 * hf, row, kvh, batch);
+    }
+  };
+  if (warp == 8 && lane == 0) {
+    mbar_init(bar(BAR_Q), 1);
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(bar(BAR_KV_FULL + s), 1);
+      mbar_init(bar(BAR_KV_EMPTY + s), 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(bar(BAR_SD_FULL + b), 1);
+      mbar_init(bar(BAR_DS_READY + b), 8);
+    }
+    mbar_init(bar(BAR_DQ_FINAL), 1);
+    mbar_init(bar(BAR_STAGED), 8);
+    *s_abort = 0;
+    fence_barrier_init();
+    fence_proxy_async();
+    mbar_arrive_expect_tx(bar(BAR_Q), 2 * kQBytes);
+#pragma unroll
+    for (int hf = 0; hf < 2; ++hf) {
+      tma_load_4d(smem_u32(sQ + hf * (kQBytes / 2)), &tmQ, bar(BAR_Q), 64 * hf, q_begin + q0, head, batch);
+      tma_load_4d(smem_u32(sDO + hf * (kQBytes / 2)), &tmDO, bar(BAR_Q), 64 * hf, q_begin + q0, head, batch);
+    }
+    for (int j = 0; j < kStages && j < n_tiles; ++j) load_kv(j);
+  }
+  if (warp == 9) {
+    tmem_alloc(smem_u32(s_tmem), kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *s_tmem;
+
+  if (warp == 8) {
+    // ============================ producer ============================
+    if (lane == 0) {
+      for (int j = kStages; j < n_tiles; ++j) {
+        // the stage's previous tile (j - kStages) is free when its dQ MMAs have completed; the producer is at most
+        // one completion behind that barrier (the MMA thread needs tile j before it can release this stage again)
+        if (!mbar_wait_bounded(bar(BAR_KV_EMPTY + j % kStages), ((j / kStages) & 1) ^ 1, s_abort)) break;
+        load_kv(j);
+      }
+    }
+  } else if (warp == 9) {
+    // ============================ MMA issue ============================
+    if (lane == 0) {
+      const uint32_t id_sd = instr_desc(DT, 0, BM, BN);          // S, dP: B K-major, N = 64
+      const uint32_t id_dq = instr_desc(DT, 1, BM, HD);          // dQ: B = K MN-major, N = 128
+      const uint64_t qd = smem_desc(smem_u32(sQ), 16, 1024), dod = smem_desc(smem_u32(sDO), 16, 1024);
+      const uint64_t kd0 = smem_desc(smem_u32(sKV), 16, 1024);
+      const uint64_t kmn0 = smem_desc(smem_u32(sKV), kKVBytes / 2, 1024);
+      constexpr uint64_t kHalfQ = (kQBytes / 2) >> 4, kHalfK = (kKVBytes / 2) >> 4, kStageU = kStageBytes >> 4,
+                         kVOff = kKVBytes >> 4;
+      bool ok = mbar_wait_bounded(bar(BAR_Q), 0, s_abort);
+      auto issue_sd = [&](int j) -> bool {
+        const int st = j % kStages, b = j & 1;
+        if (!mbar_wait_bounded(bar(BAR_KV_FULL + st), (j / kStages) & 1, s_abort)) return false;
+        tc_fence_after();
+        const uint64_t kd = kd0 + static_cast<uint64_t>(st) * kStageU, vd = kd + kVOff;
+#pragma unroll
+        for (int k = 0; k < HD / 16; ++k)
+          mma_ss(tmem + cS + 64 * b, qd + (k >> 2) * kHalfQ + (k & 3) * 2, kd + (k >> 2) * kHalfK + (k & 3) * 2, id_sd,
+                 k > 0 ? 1u : 0u);
+#pragma unroll
+        for (int k = 0; k < HD / 16; ++k)
+          mma_ss(tmem + cDP + 64 * b, dod + (k >> 2) * kHalfQ + (k & 3) * 2, vd + (k >> 2) * kHalfK + (k & 3) * 2, id_sd,
+                 k > 0 ? 1u : 0u);
+        tc_commit(bar(BAR_SD_FULL + b));
+        return true;
+      };
+      if (ok) ok = issue_sd(0);
+      for (int j = 0; j < n_tiles && ok; ++j) {
+        const int st = j % kStages, b = j & 1;
+        if (j + 1 < n_tiles) {
+          ok = issue_sd(j + 1);
+          if (!ok) break;
+        }
+        if (!mbar_wait_bounded(bar(BAR_DS_READY + b), (j >> 1) & 1, s_abort)) { ok = false; break; }
+        tc_fence_after();
+        const uint64_t kmn = kmn0 + static_cast<uint64_t>(st) * kStageU;
+        // A = dS in TMEM: 16 keys = 8 columns; keys 0-31 of the tile at +0, 32-63 at +32 (where the two warps of a
+        // row wrote them).  B = K rows = keys: 16 rows = 2048 B = 128 units.
+#pragma unroll
+        for (int k = 0; k < BN / 16; ++k)
+          mma_ts(tmem + cDQ, tmem + cDP + 64 * b + (k >> 1) * 32 + (k & 1) * 8, kmn + k * 128, id_dq,
+                 (j > 0 || k > 0) ? 1u : 0u);
+        tc_commit(bar(BAR_KV_EMPTY + st));
+        if (j + 1 == n_tiles) tc_commit(bar(BAR_DQ_FINAL));
+      }
+    }
+  } else {
+    // ============================ compute warps 0-7 ============================
+    const int wq = warp & 3, hf = warp >> 2;                   // TMEM lane quarter, key-column half
+    const int rloc = wq * 32 + lane;
+    const int row = q0 + rloc;
+    const uint32_t lane_base = static_cast<uint32_t>(wq * 32) << 16;
+    // -L and -delta of this thread's row; rows beyond N or without any visible key get P = 0 (exp2 of -inf)
+    float nL = -INFINITY, nD = 0.f;
+    if (row < N) {
+      const int64_t idx = batch * p.lse_bs + head * p.lse_hs + q_begin + row;
+      const float L = p.lse[idx];
+      nL = (L == -INFINITY) ? -INFINITY : -L;
+      nD = -p.delta[idx];
+    }
+    const float cap_in = CAP ? p.scale / p.softcap : 0.f, cap_out = p.softcap * kLog2e;
+    const bool precise_tanh = p.softcap >= kPreciseTanhMinCap;
+    const float2 c2 = make_float2(p.scale_log2, p.scale_log2), nL2 = make_float2(nL, nL), nD2 = make_float2(nD, nD);
+    bool ok = true;
+    for (int j = 0; j < n_tiles; ++j) {
+      const int b = j & 1;
+      const int k0 = (kt_begin + j) * BN + hf * 32;            // first key of this thread's 32 columns
+      if (!__all_sync(0xffffffffu, mbar_wait_bounded(bar(BAR_SD_FULL + b), (j >> 1) & 1, s_abort))) { ok = false; break; }
+      tc_fence_after();
+      uint32_t rs[32], rd[32];
+      tmem_ld32(tmem + lane_base + cS + 64 * b + hf * 32, rs);
+      tmem_ld32(tmem + lane_base + cDP + 64 * b + hf * 32, rd);
+      tc_wait_ld();
+      // visible keys of this row, relative to k0: [lo_rel, hi_rel]
+      const int hi_rel = (p.causal ? min(S - 1, row + off) : S - 1) - k0;
+      const int lo_rel = (p.window_left >= 0 ? row + off - p.window_left : 0) - k0;
+      const bool need_mask = __any_sync(0xffffffffu, hi_rel < 31 || lo_rel > 0);
+      uint32_t pd[16];
+#pragma unroll
+      for (int i = 0; i < 32; i += 2) {
+        const float2 sv = make_float2(__uint_as_float(rs[i]), __uint_as_float(rs[i + 1]));
+        const float2 dv = make_float2(__uint_as_float(rd[i]), __uint_as_float(rd[i + 1]));
+        float2 t, dcap;
+        if constexpr (CAP) {
+          const float2 th = make_float2(cap_tanh(sv.x * cap_in, precise_tanh), cap_tanh(sv.y * cap_in, precise_tanh));
+          t = __ffma2_rn(th, make_float2(cap_out, cap_out), nL2);
+          dcap = __ffma2_rn(make_float2(-th.x, -th.y), th, make_float2(1.f, 1.f));
+        } else {
+          t = __ffma2_rn(sv, c2, nL2);
+        }
+        float2 pe = make_float2(fast_exp2(t.x), fast_exp2(t.y));
+        if (need_mask) {
+          if (i > hi_rel || i < lo_rel) pe.x = 0.f;
+          if (i + 1 > hi_rel || i + 1 < lo_rel) pe.y = 0.f;
+        }
+        float2 dsv = __fmul2_rn(pe, __fadd2_rn(dv, nD2));
+        if constexpr (CAP) dsv = __fmul2_rn(dsv, dcap);
+        pd[i >> 1] = pack16q<DT>(dsv.x, dsv.y);
+      }
+      // dS goes back as 16-bit pairs along the key index, inside the 32 columns this warp has just read
+      tmem_st16(tmem + lane_base + cDP + 64 * b + hf * 32, pd);
+      tc_wait_st();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar(BAR_DS_READY + b));
+    }
+
+    // ---- epilogue: dQ * scale -> 16-bit, through shared memory (the Q / dO tiles are free: every MMA has completed) ----
+    if (ok) ok = __all_sync(0xffffffffu, mbar_wait_bounded(bar(BAR_DQ_FINAL), 0, s_abort));
+    if (ok) {
+      tc_fence_after();
+      // this warp's 64 of the 128 columns = d-half hf; staged as [d-half][row][128 B], 16-byte chunks swizzled by row
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        uint32_t o[32];
+        tmem_ld32(tmem + lane_base + cDQ + hf * 64 + c * 32, o);
+        tc_wait_ld();
+#pragma unroll
+        for (int i = 0; i < 32; i += 8) {
+          uint4 v;
+          v.x = pack16q<DT>(__uint_as_float(o[i]) * p.scale, __uint_as_float(o[i + 1]) * p.scale);
+          v.y = pack16q<DT>(__uint_as_float(o[i + 2]) * p.scale, __uint_as_float(o[i + 3]) * p.scale);
+          v.z = pack16q<DT>(__uint_as_float(o[i + 4]) * p.scale, __uint_as_float(o[i + 5]) * p.scale);
+          v.w = pack16q<DT>(__uint_as_float(o[i + 6]) * p.scale, __uint_as_float(o[i + 7]) * p.scale);
+          const int chunk = c * 4 + (i >> 3);
+          if (a.tma_store) {
+            *reinterpret_cast<uint4*>(sQ + hf * (kQBytes / 2) + rloc * 128 + ((chunk ^ (rloc & 7)) << 4)) = v;
+          } else if (row < N) {
+            uint16_t* drow = reinterpret_cast<uint16_t*>(p.dq) + batch * p.dq_bs + head * p.dq_hs +
+                             static_cast<int64_t>(q_begin + row) * p.dq_rs;
+            *reinterpret_cast<uint4*>(drow + hf * 64 + chunk * 8) = v;
+          }
+        }
+      }
+      if (a.tma_store) {
+        fence_proxy_async();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar(BAR_STAGED));
+        if (tid == 0 && mbar_wait_bounded(bar(BAR_STAGED), 0, s_abort)) {
+#pragma unroll
+          for (int h2 = 0; h2 < 2; ++h2)
+            tma_store_4d(&tmDQ, smem_u32(sQ + h2 * (kQBytes / 2)), 64 * h2, q0, head, batch);
+          tma_store_commit();
+          tma_store_wait<0>();
+        }
+      }
+    }
+  }
+
+  // ---- teardown ----
+  __syncwarp();
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 9) {
+    tc_fence_after();
+    tmem_dealloc(tmem, kTmemCols);
+  }
+  if (tid == 0 && *s_abort != 0) atomicOr(&g_kernel_status, 1);
+}
+
+bool make_map128(CUtensorMap* m, int dtype, const void* base, int rows, int H, int B, int64_t rs, int64_t hs, int64_t bs,
+                 int box_rows) {
+  const uint64_t dims[4] = {static_cast<uint64_t>(HD), static_cast<uint64_t>(rows), static_cast<uint64_t>(H),
+                            static_cast<uint64_t>(B)};
+  const uint64_t strides[3] = {static_cast<uint64_t>(rs) * 2, static_cast<uint64_t>(hs) * 2, static_cast<uint64_t>(bs) * 2};
+  const uint32_t box[4] = {64, static_cast<uint32_t>(box_rows), 1, 1};
+  return encode_tmap(m, dtype == 0 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, base, dims,
+                     strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
+}
+
+}  // namespace
+
+// dQ for head_dim 128; p.delta must already hold delta.  Dense: nbatch = B, max_q = N.  Packed varlen: nbatch =
+// number of sequences, max_q = the longest query sequence.
+cudaError_t launch_bwd_dq_sm100(const BwdParams& p, int dtype, int nbatch, int max_q, cudaStream_t stream) {
+  if (nbatch <= 0 || max_q <= 0) return cudaSuccess;
+  CUtensorMap tmQ, tmK, tmV, tmDO, tmDQ;
+  auto fix = [](int64_t s, int64_t fallback) { return s > 0 ? s : fallback; };   // size-1 dimensions only (see bwd_sm100_strides_ok)
+  const int64_t q_hs = fix(p.q_hs, static_cast<int64_t>(p.N) * p.q_rs), q_bs = fix(p.q_bs, q_hs * p.Hq);
+  const int64_t k_hs = fix(p.k_hs, static_cast<int64_t>(p.S) * p.k_rs), k_bs = fix(p.k_bs, k_hs * p.Hkv);
+  const int64_t v_hs = fix(p.v_hs, static_cast<int64_t>(p.S) * p.v_rs), v_bs = fix(p.v_bs, v_hs * p.Hkv);
+  const int64_t do_hs = static_cast<int64_t>(p.N) * HD, do_bs = do_hs * p.Hq;
+  if (!make_map128(&tmQ, dtype, p.q, p.N, p.Hq, p.B, p.q_rs, q_hs, q_bs, BM) ||
+      !make_map128(&tmK, dtype, p.k, p.S, p.Hkv, p.B, p.k_rs, k_hs, k_bs, BN) ||
+      !make_map128(&tmV, dtype, p.v, p.S, p.Hkv, p.B, p.v_rs, v_hs, v_bs, BN) ||
+      !make_map128(&tmDO, dtype, p.dout, p.N, p.Hq, p.B, HD, do_hs, do_bs, BM))
+    return cudaErrorInvalidValue;
+  DqArgs a;
+  a.p = p;
+  a.tma_store = (p.cu_q == nullptr && make_map128(&tmDQ, dtype, p.dq, p.N, p.Hq, p.B, p.dq_rs, fix(p.dq_hs, 1), fix(p.dq_bs, 1), BM)) ? 1 : 0;
+  if (!a.tma_store) tmDQ = tmQ;
+  dim3 grid((max_q + BM - 1) / BM, p.Hq, nbatch);
+  auto launch = [&](auto kern) -> cudaError_t {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+    if (e != cudaSuccess) return e;
+    kern<<<grid, kThreads, kSmemBytes, stream>>>(tmQ, tmK, tmV, tmDO, tmDQ, a);
+    return cudaGetLastError();
+  };
+  const bool cap = p.softcap > 0.f;
+  if (dtype == 0) return cap ? launch(bwd_dq_sm100_kernel<0, true>) : launch(bwd_dq_sm100_kernel<0, false>);
+  return cap ? launch(bwd_dq_sm100_kernel<1, true>) : launch(bwd_dq_sm100_kernel<1, false>);
+}
+
+cudaError_t bwd_dq_sm100_read_clear_status(cudaStream_t stream, int* out) {
+  const int zero = 0;
+  cudaError_t e = cudaMemcpyFromSymbolAsync(out, g_kernel_status, sizeof(int), 0, cudaMemcpyDeviceToHost, stream);
+  if (e == cudaSuccess) e = cudaStreamSynchronize(stream);
+  if (e == cudaSuccess && *out != 0)
+    e = cudaMemcpyToSymbolAsync(g_kernel_status, &zero, sizeof(int), 0, cudaMemcpyHostToDevice, stream);
+  if (e == cudaSuccess) e = cudaStreamSynchronize(stream);
+  return e;
+}
+
+}  // namespace b200fa

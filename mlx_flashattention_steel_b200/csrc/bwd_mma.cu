@@ -60,9 +60,11 @@ __global__ void __launch_bounds__(256) bwd_preprocess_kernel(const BwdParams p, 
 #pragma unroll
   for (int s = 16; s > 0; s >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, s);
   if (lane == 0) p.delta[warp] = acc;
-  float* dq = p.dq_acc + static_cast<int64_t>(warp) * D;
+  if (p.dq_acc != nullptr) {          // the split head_dim-128 path has no accumulator
+    float* dq = p.dq_acc + static_cast<int64_t>(warp) * D;
 #pragma unroll
-  for (int e = 0; e < PER; ++e) dq[lane + 32 * e] = 0.f;
+    for (int e = 0; e < PER; ++e) dq[lane + 32 * e] = 0.f;
+  }
 }
 
 // The same with 16-byte accesses: D / 8 lanes per row, each with 8 elements of O and dO and 8 accumulator words to
@@ -91,9 +93,11 @@ __global__ void __launch_bounds__(256) bwd_preprocess_vec_kernel(const BwdParams
       acc = fmaf(of.x, df.x, acc);
       acc = fmaf(of.y, df.y, acc);
     }
-    float4* dq = reinterpret_cast<float4*>(p.dq_acc + row * D + c * 8);
-    dq[0] = make_float4(0.f, 0.f, 0.f, 0.f);
-    dq[1] = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (p.dq_acc != nullptr) {        // the split head_dim-128 path has no accumulator
+      float4* dq = reinterpret_cast<float4*>(p.dq_acc + row * D + c * 8);
+      dq[0] = make_float4(0.f, 0.f, 0.f, 0.f);
+      dq[1] = make_float4(0.f, 0.f, 0.f, 0.f);
+    }
   }
 #pragma unroll
   for (int sft = LPR / 2; sft > 0; sft >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, sft);
@@ -377,7 +381,8 @@ __global__ void __launch_bounds__(kThreads) bwd_main_kernel(const BwdParams p) {
 }
 
 template <typename T, int D>
-cudaError_t launch_t(const BwdParams& p, int dtype, bool varlen, int nbatch, int max_k, bool allow_sm100, cudaStream_t stream) {
+cudaError_t launch_t(const BwdParams& p, int dtype, bool varlen, int nbatch, int max_q, int max_k, bool allow_sm100,
+                     cudaStream_t stream) {
   const int total_rows = p.B * p.Hq * p.N;
   {
     const bool rows16 = reinterpret_cast<uintptr_t>(p.o) % 16 == 0 && reinterpret_cast<uintptr_t>(p.dout) % 16 == 0 &&
@@ -396,6 +401,12 @@ cudaError_t launch_t(const BwdParams& p, int dtype, bool varlen, int nbatch, int
   constexpr size_t smem = (2 * kBN * D + 4 * kBM * D + kBN * kBM) * sizeof(T) + 4 * kBM * sizeof(float);
   dim3 grid((max_k + kBN - 1) / kBN, p.Hkv, nbatch);
   cudaError_t e;
+  if (p.dq_acc == nullptr) {
+    // head_dim 128 on tcgen05: dK / dV and dQ by a kernel each, no accumulator and no conversion pass
+    e = launch_bwd_dkv_sm100(p, dtype, nbatch, max_k, stream);
+    if (e != cudaSuccess) return e;
+    return launch_bwd_dq_sm100(p, dtype, nbatch, max_q, stream);
+  }
   if (allow_sm100 && bwd_sm100_supported(dtype, D) && bwd_sm100_strides_ok(p)) {
     e = launch_bwd_sm100_main(p, dtype, nbatch, max_k, stream);
     if (e != cudaSuccess) return e;
@@ -419,25 +430,30 @@ cudaError_t launch_t(const BwdParams& p, int dtype, bool varlen, int nbatch, int
 
 }  // namespace
 
-size_t bwd_workspace_bytes(int B, int Hq, int N_total, int D) {
+// delta, work counter and -- except on the split head_dim-128 path -- the fp32 dQ accumulator
+size_t bwd_workspace_bytes(int B, int Hq, int N_total, int D, bool split) {
   const size_t rows = static_cast<size_t>(B) * Hq * N_total;
-  return bwd_align(rows * sizeof(float)) + bwd_align(rows * D * sizeof(float)) + 256;   // delta, dQ accumulator, work counter
+  return bwd_align(rows * sizeof(float)) + 256 + (split ? 0 : bwd_align(rows * D * sizeof(float)));
+}
+
+bool bwd_takes_split_path(const BwdParams& p, int dtype, int D, bool allow_sm100) {
+  return allow_sm100 && p.alibi == nullptr && p.bmask == nullptr && bwd_split_sm100_supported(dtype, D) && bwd_sm100_strides_ok(p);
 }
 
 cudaError_t launch_bwd(const BwdParams& p_in, int dtype, int D, bool varlen, int nbatch, int max_q, int max_k,
                        void* workspace, bool allow_sm100, cudaStream_t stream) {
-  (void)max_q;
   BwdParams p = p_in;
   const size_t rows = static_cast<size_t>(p.B) * p.Hq * p.N;
-  p.delta = reinterpret_cast<float*>(workspace);
-  p.dq_acc = reinterpret_cast<float*>(reinterpret_cast<unsigned char*>(workspace) + bwd_align(rows * sizeof(float)));
-  p.work_counter = reinterpret_cast<int*>(reinterpret_cast<unsigned char*>(workspace) + bwd_align(rows * sizeof(float)) +
-                                          bwd_align(rows * D * sizeof(float)));
+  unsigned char* ws = reinterpret_cast<unsigned char*>(workspace);
+  p.delta = reinterpret_cast<float*>(ws);
+  p.work_counter = reinterpret_cast<int*>(ws + bwd_align(rows * sizeof(float)));
+  p.dq_acc = bwd_takes_split_path(p, dtype, D, allow_sm100) ? nullptr
+                                                            : reinterpret_cast<float*>(ws + bwd_align(rows * sizeof(float)) + 256);
   if (rows == 0) return cudaSuccess;
-  if (dtype == 0 && D == 64) return launch_t<__half, 64>(p, dtype, varlen, nbatch, max_k, allow_sm100, stream);
-  if (dtype == 0 && D == 128) return launch_t<__half, 128>(p, dtype, varlen, nbatch, max_k, allow_sm100, stream);
-  if (dtype == 1 && D == 64) return launch_t<__nv_bfloat16, 64>(p, dtype, varlen, nbatch, max_k, allow_sm100, stream);
-  if (dtype == 1 && D == 128) return launch_t<__nv_bfloat16, 128>(p, dtype, varlen, nbatch, max_k, allow_sm100, stream);
+  if (dtype == 0 && D == 64) return launch_t<__half, 64>(p, dtype, varlen, nbatch, max_q, max_k, allow_sm100, stream);
+  if (dtype == 0 && D == 128) return launch_t<__half, 128>(p, dtype, varlen, nbatch, max_q, max_k, allow_sm100, stream);
+  if (dtype == 1 && D == 64) return launch_t<__nv_bfloat16, 64>(p, dtype, varlen, nbatch, max_q, max_k, allow_sm100, stream);
+  if (dtype == 1 && D == 128) return launch_t<__nv_bfloat16, 128>(p, dtype, varlen, nbatch, max_q, max_k, allow_sm100, stream);
   return cudaErrorInvalidValue;
 }
 

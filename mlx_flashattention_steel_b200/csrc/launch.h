@@ -26,14 +26,20 @@ cudaError_t launch_paged_gather(const void* pool, const int32_t* block_table, co
                                 int B, int H, int D, int elem_bytes, int block_size, int max_blocks,
                                 int max_kv_len, void* out, cudaStream_t stream);
 
-size_t bwd_workspace_bytes(int B, int Hq, int N_total, int D);
-// allow_sm100: let the tcgen05 main kernel run where it exists (head_dim 64); the preprocess and the
-// dQ conversion are common to both.
+// split: the head_dim-128 tcgen05 path (bwd_takes_split_path), which needs no dQ accumulator
+size_t bwd_workspace_bytes(int B, int Hq, int N_total, int D, bool split);
+bool bwd_takes_split_path(const BwdParams& p, int dtype, int D, bool allow_sm100);
+// allow_sm100: let the tcgen05 kernels run where they exist (head_dim 64: one kernel plus the dQ conversion;
+// head_dim 128: a dK/dV kernel and a dQ kernel); the preprocess is common to all.
 cudaError_t launch_bwd(const BwdParams& p, int dtype, int D, bool varlen, int nbatch, int max_q,
                        int max_k, void* workspace, bool allow_sm100, cudaStream_t stream);
 bool bwd_sm100_supported(int dtype, int D);
 bool bwd_sm100_strides_ok(const BwdParams& p);
 cudaError_t launch_bwd_sm100_main(const BwdParams& p, int dtype, int nbatch, int max_k, cudaStream_t stream);
+// head_dim 128 (bwd_dkv_sm100.cu, bwd_dq_sm100.cu): p.delta filled, *p.work_counter zero
+bool bwd_split_sm100_supported(int dtype, int D);
+cudaError_t launch_bwd_dkv_sm100(const BwdParams& p, int dtype, int nbatch, int max_k, cudaStream_t stream);
+cudaError_t launch_bwd_dq_sm100(const BwdParams& p, int dtype, int nbatch, int max_q, cudaStream_t stream);
 
 // KV-cache write path (kv_append.cu): scatter T new tokens per kv head into the page pools; 8-bit pools are
 // quantised per (token, head) with an f16 scale.  Strides in elements; slots[t] = page * block_size + offset.
@@ -54,5 +60,7 @@ cudaError_t launch_rope(int dtype, const void* x, void* out, const float* cosb, 
 // Read (and clear when set) the device status word of the tcgen05 kernels of each file; they wait for `stream`.
 cudaError_t fwd_sm100_read_clear_status(cudaStream_t stream, int* out);
 cudaError_t bwd_sm100_read_clear_status(cudaStream_t stream, int* out);
+cudaError_t bwd_dkv_sm100_read_clear_status(cudaStream_t stream, int* out);
+cudaError_t bwd_dq_sm100_read_clear_status(cudaStream_t stream, int* out);
 
 }  // namespace b200fa

@@ -157,7 +157,10 @@ def _fwd_raw(q, k, v, scale, causal, softcap, window_left, want_lse, stream, out
     d = _desc(code, code, B, Hq, Hkv, N, S, D, scale, causal, softcap, window_left,
               flags=_FORCE_FLAGS, q=q, k=k if S > 0 else None, v=v if S > 0 else None, o=out, alibi=alibi, bmask=bmask)
     with torch.cuda.device(q.device):
-        st = lib.b200fa_fwd(C.byref(d), _ptr(q), _ptr(k), _ptr(v), _ptr(out), _ptr(lse), None, 0,
+        # non-zero only for a few query rows against a long cache (N <= 4, S >= 256): the split-KV decode route
+        need = lib.b200fa_fwd_workspace_bytes(C.byref(d))
+        ws = torch.empty(need, dtype=torch.uint8, device=q.device) if need > 0 else None
+        st = lib.b200fa_fwd(C.byref(d), _ptr(q), _ptr(k), _ptr(v), _ptr(out), _ptr(lse), _ptr(ws), need,
                             C.c_void_p(_stream_ptr(stream, q.device)))
     _lib.check(st, "flash_attention")
     return out, lse
@@ -568,8 +571,8 @@ def flash_attention_paged(
     ``seq_lens`` that the reference also performs (mlx_mfa/attention.py:2871-2873);
     ``num_splits`` caps how many CTAs share the page list (0 = one per SM).
 
-    Short queries ((Hq/Hkv)*Nq <= 8, D = 128, block_size 16) run the split-KV
-    decode kernel with in-kernel combine; other shapes gather pages and attend
+    Short queries ((Hq/Hkv)*Nq <= 8; D = 128, or D = 64 with 16-bit pools; block_size a multiple
+    of 16) run the split-KV decode kernel with in-kernel combine; other shapes gather pages and attend
     per sequence like the reference (mlx_mfa/attention.py:2944-2989).  When gradients are
     wanted (q or a 16-bit pool requires grad) every shape takes the gather route, whose
     backward adds dK / dV back into pool-shaped gradients page by page (2878-2940, 3020-3084).
@@ -615,7 +618,8 @@ def flash_attention_paged(
 
     # training: gradients flow through the gather route (gather, per-sequence attention, scatter-add into the pools)
     needs_grad = torch.is_grad_enabled() and (q.requires_grad or k_pages.requires_grad or v_pages.requires_grad)
-    decode_ok = (Hq // Hkv) * Nq <= 8 and D == 128 and block_size == 16 and not needs_grad
+    decode_ok = ((Hq // Hkv) * Nq <= 8 and (D == 128 or (D == 64 and not quant)) and block_size % 16 == 0
+                 and not needs_grad)
     if decode_ok:
         out, lse = _decode_raw(q, k_pages, v_pages, k_scale, v_scale, table, lens, max_kv_len, float(scale),
                                bool(causal), float(softcap), block_size, return_lse, stream, num_splits)

@@ -149,14 +149,30 @@ int32_t b200fa_device_info(int32_t device, b200fa_device_info_t* out) {
 // ---------------------------------------------------------------------------
 // forward
 // ---------------------------------------------------------------------------
+// Dense flash-decode route (the reference's use_flash_decode, csrc/mfa_attention.cpp:150-151: N <= 4, S >= 256,
+// 16-bit, no block mask), further limited to what the split-KV decode kernel takes: at most 8 query rows per kv
+// head, head_dim 64 / 128, no window and no ALiBi, contiguous q and out.
+static bool dense_decode_route(const b200fa_desc* d) {
+  if (d == nullptr || (d->dtype != B200FA_F16 && d->dtype != B200FA_BF16)) return false;
+  if (d->flags & B200FA_FLAG_FORCE_MMA_SYNC) return false;
+  if (!(d->N >= 1 && d->N <= 4 && d->S >= 256) || (d->D != 64 && d->D != 128)) return false;
+  if (d->Hkv <= 0 || d->Hq % d->Hkv != 0 || (d->Hq / d->Hkv) * d->N > 8) return false;
+  if (d->window_left >= 0 || d->alibi_slopes != nullptr || d->block_mask != nullptr) return false;
+  if (d->causal && d->N > d->S) return false;
+  auto contiguous = [&](const int64_t st[3]) {
+    return (st[0] == 0 && st[1] == 0 && st[2] == 0) ||
+           (st[2] == d->D && st[1] == static_cast<int64_t>(d->N) * d->D && (d->B == 1 || st[0] == static_cast<int64_t>(d->Hq) * d->N * d->D));
+  };
+  return contiguous(d->q_strides) && contiguous(d->o_strides);
+}
+
 size_t b200fa_fwd_workspace_bytes(const b200fa_desc* d) {
-  (void)d;
-  return 0;
+  if (!dense_decode_route(d)) return 0;
+  return b200fa::decode_workspace_bytes(d->B, d->Hq, d->Hkv, d->N, d->D, d->S, d->num_splits);
 }
 
 int32_t b200fa_fwd(const b200fa_desc* d, const void* q, const void* k, const void* v, void* out,
                    float* lse, void* workspace, size_t workspace_bytes, void* stream) {
-  (void)workspace; (void)workspace_bytes;
   int32_t st = check_common(d, false);
   if (st != B200FA_OK) return st;
   if (d->B == 0 || d->N == 0) return B200FA_OK;
@@ -167,6 +183,29 @@ int32_t b200fa_fwd(const b200fa_desc* d, const void* q, const void* k, const voi
   if (st != B200FA_OK) return st;
   cudaStream_t cs = reinterpret_cast<cudaStream_t>(stream);
   cudaError_t e;
+  // A few query rows against a long dense cache: split-KV decode over the cache in place (all SMs share the keys of
+  // every head) instead of one 128-row tile per head.  Taken when the caller brought the workspace the query asked
+  // for; without it the call runs the prefill kernel, which is correct for every shape.
+  if (dense_decode_route(d) && workspace != nullptr && aligned16(workspace) &&
+      workspace_bytes >= b200fa::decode_workspace_bytes(d->B, d->Hq, d->Hkv, d->N, d->D, d->S, d->num_splits) &&
+      !(p.B > 1 && (p.k_bs == 0 || p.v_bs == 0)) && !(p.Hkv > 1 && (p.k_hs == 0 || p.v_hs == 0))) {
+    b200fa::DecodeParams dp;
+    memset(&dp, 0, sizeof(dp));
+    dp.q = q; dp.k_pool = k; dp.v_pool = v; dp.out = out; dp.lse = lse; dp.workspace = workspace;
+    dp.B = d->B; dp.Hq = d->Hq; dp.Hkv = d->Hkv; dp.Nq = d->N; dp.D = d->D;
+    dp.num_pages = 0; dp.block_size = 16; dp.max_blocks = 0; dp.max_kv_len = d->S;
+    dp.q_dtype = d->dtype; dp.kv_dtype = d->dtype;
+    dp.scale = d->scale; dp.softcap = d->softcap; dp.causal = d->causal ? 1 : 0;
+    dp.num_splits = d->num_splits;
+    dp.dense = 1;
+    dp.k_bs = p.k_bs; dp.k_hs = p.k_hs; dp.k_rs = p.k_rs;
+    dp.v_bs = p.v_bs; dp.v_hs = p.v_hs; dp.v_rs = p.v_rs;
+    char msg[256] = "";
+    e = b200fa::launch_decode_paged(dp, cs, msg, sizeof(msg));
+    if (e == cudaSuccess) return B200FA_OK;
+    if (e != cudaErrorNotSupported) return fail(B200FA_ERR_CUDA, "dense decode launch: %s %s", cudaGetErrorString(e), msg);
+    // not a shape the decode kernel takes after all: fall through to the prefill kernels
+  }
   if (d->dtype == B200FA_F32) {
     e = b200fa::launch_fwd_f32(p, d->D, false, d->B, d->N, cs);
   } else if (!(d->flags & B200FA_FLAG_FORCE_MMA_SYNC) && b200fa::fwd_sm100_supported(p, d->dtype, d->D)) {
@@ -444,7 +483,9 @@ static int32_t decode_check(const b200fa_desc* d) {
   if (d == nullptr) return fail(B200FA_ERR_INVALID_ARG, "descriptor is null");
   if (d->dtype != B200FA_F16 && d->dtype != B200FA_BF16)
     return fail(B200FA_ERR_UNSUPPORTED, "paged decode takes f16 or bf16 queries");
-  if (d->D != 128) return fail(B200FA_ERR_UNSUPPORTED, "paged decode is built for head_dim 128");
+  if (d->D != 128 && d->D != 64) return fail(B200FA_ERR_UNSUPPORTED, "paged decode is built for head_dim 64 and 128");
+  if (d->D == 64 && d->kv_dtype != d->dtype)
+    return fail(B200FA_ERR_UNSUPPORTED, "paged decode at head_dim 64 takes 16-bit pools (8-bit pools: head_dim 128)");
   if (d->B < 0 || d->Hq <= 0 || d->Hkv <= 0 || d->N <= 0)
     return fail(B200FA_ERR_INVALID_ARG, "bad extent");
   if (d->Hq % d->Hkv != 0)
@@ -470,7 +511,8 @@ int32_t b200fa_decode_paged(const b200fa_desc* d, const void* q, const void* k_p
                             void* workspace, size_t workspace_bytes, void* stream) {
   int32_t st = decode_check(d);
   if (st != B200FA_OK) return st;
-  if (block_size != 16) return fail(B200FA_ERR_UNSUPPORTED, "paged decode is built for block_size 16");
+  if (block_size < 16 || block_size % 16 != 0)
+    return fail(B200FA_ERR_UNSUPPORTED, "paged decode takes pages of 16, 32, 48, 64, ... tokens (a multiple of 16), got %d", block_size);
   if (num_pages <= 0 || max_blocks <= 0 || max_kv_len < 0) return fail(B200FA_ERR_INVALID_ARG, "bad extent");
   if (d->B == 0) return B200FA_OK;
   if (!q || !k_pool || !v_pool || !block_table || !seq_lens || !out)

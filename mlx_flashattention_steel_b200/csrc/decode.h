@@ -12,8 +12,8 @@ struct DecodeParams {
   const void* v_pool;
   const void* k_scale;      // [num_pages, block_size, Hkv] f16 (8-bit pools)
   const void* v_scale;
-  const int32_t* block_table;  // [B, max_blocks]
-  const int32_t* seq_lens;     // [B]
+  const int32_t* block_table;  // [B, max_blocks]; null = dense caches (see `dense`)
+  const int32_t* seq_lens;     // [B]; null = every sequence holds max_kv_len tokens
   void* out;                // [B, Hq, Nq, D] q dtype
   float* lse;               // [B, Hq, Nq] or null
   void* workspace;
@@ -23,6 +23,10 @@ struct DecodeParams {
   float scale, softcap;
   int causal;
   int num_splits;           // upper bound on CTAs per head group; 0 = one per SM
+  // Dense caches: k_pool / v_pool are [B, Hkv, S, D] tensors with these strides (elements; D contiguous), S =
+  // max_kv_len; "page" j of sequence b is its tokens [16 j, 16 j + 16), no table is read.
+  int dense;
+  int64_t k_bs, k_hs, k_rs, v_bs, v_hs, v_rs;
 };
 
 size_t decode_workspace_bytes(int B, int Hq, int Hkv, int Nq, int D, int max_kv_len, int num_splits);

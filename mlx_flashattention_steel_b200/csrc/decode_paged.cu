@@ -20,6 +20,12 @@
 //     partial (normalised O, base-2 lse) and bumps a counter; the CTA that brings the
 //     counter to the number of parts combines them.  Nobody spins on anybody.
 //
+//   * Pages of 32, 64, ... tokens are walked as 16-token units (a unit is what one TMA box and one consumer step
+//     cover).  Dense caches [B, Hkv, S, D] (the reference's flash-decode route for N <= 4, S >= 256 on plain
+//     flash_attention calls, csrc/mfa_attention.cpp:150-288) run the same kernel: unit j of sequence b is its tokens
+//     [16 j, 16 j + 16), addressed through a tensor map with the cache's own strides, and no table is read.
+//   * head_dim 128 for every pool type; head_dim 64 for 16-bit pools and dense caches.
+//
 // Every mbarrier wait is bounded (tma.cuh); a timeout raises the error word at the
 // start of the workspace and the CTA leaves.
 #include <cuda_fp8.h>
@@ -38,8 +44,7 @@ namespace b200fa {
 
 namespace {
 
-constexpr int kBS = 16;           // tokens per page
-constexpr int kD = 128;
+constexpr int kBS = 16;           // tokens per unit (one TMA box, one consumer step); a page is 1, 2, 4, ... units
 constexpr int kMaxStages = 8;
 
 enum KvKind { KV_F16 = 0, KV_BF16 = 1, KV_I8 = 2, KV_E4M3 = 3 };
@@ -56,7 +61,7 @@ struct DecodeLayout {          // workspace carve-up, in bytes from the workspac
 
 __host__ __device__ inline size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
 
-__host__ __device__ inline DecodeLayout make_layout(int B, int Hq, int Nq, int HG, int G) {
+__host__ __device__ inline DecodeLayout make_layout(int B, int Hq, int Nq, int HG, int G, int kD) {
   DecodeLayout L;
   L.err = 0;
   L.counters = 16;
@@ -75,6 +80,7 @@ struct KernelArgs {
   int group;         // Hq / Hkv
   int rows;          // group * Nq (<= 8)
   int stages;
+  int upp;              // 16-token units per page = block_size / 16
   int stage_kv_bytes;   // bytes of one K (or V) stage tile = HPC * kBS * row_bytes
   int scale_bytes;      // bytes of one scale page = kBS * Hkv * 2 (0 when not quantized)
   float q_prescale;     // folded into Q (8-bit pools) or applied to the scores (16-bit)
@@ -100,7 +106,7 @@ __global__ void __launch_bounds__(1024) decode_plan_kernel(const int32_t* __rest
     const int i = base + tid;
     int val = 0;
     if (i < B) {
-      int len = seq_lens[i];
+      int len = seq_lens != nullptr ? seq_lens[i] : max_kv_len;
       len = len < 0 ? 0 : (len > max_kv_len ? max_kv_len : len);
       val = (len + kBS - 1) / kBS;
     }
@@ -190,11 +196,13 @@ __device__ __forceinline__ int cta_of_unit(long long u, int G, long long U) {
 // ---------------------------------------------------------------------------
 // main kernel
 // ---------------------------------------------------------------------------
-template <int KV, int HPC>
+template <int KV, int HPC, int kD>
 __global__ void __launch_bounds__((HPC + 1) * 32, 1)
 decode_paged_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
                     const KernelArgs a) {
   constexpr bool kQuant = (KV == KV_I8 || KV == KV_E4M3);
+  static_assert(kD == 128 || (kD == 64 && !kQuant), "head_dim 64 is built for 16-bit pools only");
+  constexpr int kKS = kD / 16;                         // k-steps of S = Q.K^T, m-tiles of O^T
   constexpr int kRowBytes = kQuant ? kD : 2 * kD;      // bytes of one (token, head) row
   constexpr int kHalves = kRowBytes / 128;
   constexpr int kHeadBytes = kBS * kRowBytes;          // one head of one page in shared memory
@@ -292,27 +300,35 @@ decode_paged_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_consta
       if (s1 <= u) { ++b; continue; }
       const int j_lo = static_cast<int>(u - s0);
       const int j_hi = static_cast<int>((hi < s1 ? hi : s1) - s0);
-      const int32_t* row = p.block_table + static_cast<size_t>(b) * p.max_blocks;
+      const int32_t* row = p.dense ? nullptr : p.block_table + static_cast<size_t>(b) * p.max_blocks;
       for (int j0 = j_lo; j0 < j_hi && ok; j0 += 32) {
         const int jj = j0 + lane;
-        int my_page = (jj < j_hi) ? row[jj] : -1;
-        if (my_page >= p.num_pages) {
-          my_page = -1;
-          atomicOr(err, 2);                      // table entry beyond the pool
+        // first token of unit jj in the pool (paged: its page's tokens start at page * block_size) or in the
+        // sequence (dense); -1 = no page
+        int my_tok = -1;
+        if (jj < j_hi) {
+          if (p.dense) {
+            my_tok = jj * kBS;
+          } else {
+            const int pg_id = row[jj / a.upp];
+            if (pg_id >= p.num_pages) atomicOr(err, 2);              // table entry beyond the pool
+            else if (pg_id >= 0) my_tok = pg_id * p.block_size + (jj % a.upp) * kBS;
+          }
         }
         const int n = min(32, j_hi - j0);
         for (int i = 0; i < n; ++i) {
-          const int page = __shfl_sync(0xffffffffu, my_page, i);
+          const int page = __shfl_sync(0xffffffffu, my_tok, i);       // token offset of the unit, or -1
           if (!__all_sync(0xffffffffu, mbar_wait_bounded(smem_u32(&bars[kMaxStages + stage]), phase ^ 1u, s_abort))) { ok = false; break; }
           if (lane == 0) {
             s_page[stage] = page;
             const uint32_t full = smem_u32(&bars[stage]);
             if (page >= 0) {
               mbar_arrive_expect_tx(full, tx_bytes);
-              tma_load_5d(smem_u32(sK + static_cast<size_t>(stage) * a.stage_kv_bytes), &tmK, full, 0, page * kBS, 0, hg * HPC, 0);
-              tma_load_5d(smem_u32(sV + static_cast<size_t>(stage) * a.stage_kv_bytes), &tmV, full, 0, page * kBS, 0, hg * HPC, 0);
+              const int batch_coord = p.dense ? b : 0;
+              tma_load_5d(smem_u32(sK + static_cast<size_t>(stage) * a.stage_kv_bytes), &tmK, full, 0, page, 0, hg * HPC, batch_coord);
+              tma_load_5d(smem_u32(sV + static_cast<size_t>(stage) * a.stage_kv_bytes), &tmV, full, 0, page, 0, hg * HPC, batch_coord);
               if (kQuant) {
-                const size_t soff = static_cast<size_t>(page) * a.scale_bytes;
+                const size_t soff = static_cast<size_t>(page / kBS) * a.scale_bytes;
                 bulk_load(smem_u32(sKs + static_cast<size_t>(stage) * a.scale_bytes),
                           reinterpret_cast<const unsigned char*>(p.k_scale) + soff, a.scale_bytes, full);
                 bulk_load(smem_u32(sVs + static_cast<size_t>(stage) * a.scale_bytes),
@@ -349,18 +365,18 @@ decode_paged_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_consta
     if (s1 <= u) { ++b; continue; }
     const int j_lo = static_cast<int>(u - s0);
     const int j_hi = static_cast<int>((hi < s1 ? hi : s1) - s0);
-    int len = p.seq_lens[b];
+    int len = p.seq_lens != nullptr ? p.seq_lens[b] : p.max_kv_len;
     len = len < 0 ? 0 : (len > p.max_kv_len ? p.max_kv_len : len);
     const int c_first = cta_of_unit(s0, G, U);
     const int c_last = cta_of_unit(static_cast<long long>(s1) - 1, G, U);
     const int n_parts = c_last - c_first + 1;
 
     // ---- Q fragments (A operand rows 0..7; rows 8..15 are zero padding) ----
-    uint32_t qa[8][2];
+    uint32_t qa[8][2];                 // kKS k-steps are used
     float q_bias = 0.f;          // int8 pools: 1152 * sum of the row's query values (see i8pair_to_h2_biased)
     {
       const size_t qoff = ((static_cast<size_t>(b) * p.Hq + hq_row) * p.Nq + qi_row) * kD;
-      if (kQuant) {
+      if constexpr (kQuant) {
         // lane t owns d in [32t, 32t+32): k-step s uses d = 32t + 4s + {0,1 | 2,3}
         float f[32];
         if (row_valid) {
@@ -416,7 +432,7 @@ decode_paged_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_consta
         // natural order: a0 = Q[g][16s + 2t, +1], a2 = Q[g][16s + 8 + 2t, +1]
         const uint32_t* src = reinterpret_cast<const uint32_t*>(reinterpret_cast<const uint16_t*>(p.q) + qoff);
 #pragma unroll
-        for (int s = 0; s < 8; ++s) {
+        for (int s = 0; s < kKS; ++s) {
           qa[s][0] = row_valid ? src[8 * s + t] : 0u;
           qa[s][1] = row_valid ? src[8 * s + 4 + t] : 0u;
         }
@@ -470,7 +486,7 @@ decode_paged_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_consta
 #pragma unroll
       for (int q = 0; q < 2; ++q) {
         if (pg[q] >= 0) {
-          if (kQuant) {
+          if constexpr (kQuant) {
 #pragma unroll
             for (int jn = 0; jn < 2; ++jn) {
               const int tok = 8 * jn + g;                     // tok & 7 == g
@@ -495,7 +511,7 @@ decode_paged_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_consta
             }
           } else {
 #pragma unroll
-            for (int s = 0; s < 8; ++s) {
+            for (int s = 0; s < kKS; ++s) {
               uint32_t bfr[4];
               const int tok = (lane & 7) + ((lane >> 4) << 3);
               const int dcol = 16 * s + (((lane >> 3) & 1) << 3);
@@ -561,7 +577,7 @@ decode_paged_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_consta
         const float c0 = __shfl_sync(0xffffffffu, corr, (2 * t) * 4);
         const float c1 = __shfl_sync(0xffffffffu, corr, (2 * t + 1) * 4);
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
+        for (int i = 0; i < kKS; ++i) {
           oacc[i][0] *= c0; oacc[i][1] *= c1; oacc[i][2] *= c0; oacc[i][3] *= c1;
         }
         m_run = m_new;
@@ -601,7 +617,7 @@ decode_paged_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_consta
             pb0 = pack_h2(pr[q][0], pr[q][1]);
             pb1 = pack_h2(pr[q][2], pr[q][3]);
           }
-          if (kQuant) {
+          if constexpr (kQuant) {
             // lane (g,t) reads word w = g + 8*jj (4 head-dim bytes) of token rows 2t, 2t+1, 2t+8, 2t+9
             const uint32_t rA = vbase[q] + (2 * t) * 128, rB = rA + 128, rC = rA + 8 * 128, rD = rC + 128;
             const int xa = (2 * t) & 7, xb = (2 * t + 1) & 7;
@@ -636,7 +652,7 @@ decode_paged_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_consta
             }
           } else {
 #pragma unroll
-            for (int mt = 0; mt < 8; ++mt) {
+            for (int mt = 0; mt < kKS; ++mt) {
               uint32_t af[4];
               const int tok = (lane & 7) + ((lane >> 4) << 3);
               const int dcol = 16 * mt + (((lane >> 3) & 1) << 3);
@@ -675,7 +691,7 @@ decode_paged_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_consta
     const int slot = c + b;
 
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {
+    for (int i = 0; i < kKS; ++i) {
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
         // head-dim index of accumulator register e of m-tile i
@@ -726,17 +742,20 @@ decode_paged_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_consta
           const float msb = (mmax == -INFINITY) ? 0.f : mmax;
           float wsum = 0.f;
           float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+          const bool col_live = lane * 4 < kD;            // head_dim 64: the first 16 lanes carry the row
           for (int i = 0; i < n_parts; ++i) {
             const size_t sl = static_cast<size_t>(c_first + i + b);
             const float w = exp2f(__ldcg(&part_lse[sl * HqNq + rowi]) - msb);
             wsum += w;
+            if (!col_live) continue;
             const float4 v4 = __ldcg(reinterpret_cast<const float4*>(&part_o[(sl * HqNq + rowi) * kD + lane * 4]));
             acc.x = fmaf(w, v4.x, acc.x); acc.y = fmaf(w, v4.y, acc.y);
             acc.z = fmaf(w, v4.z, acc.z); acc.w = fmaf(w, v4.w, acc.w);
           }
           const float inv = wsum > 0.f ? 1.f / wsum : 0.f;
           const size_t o = ((static_cast<size_t>(b) * p.Hq + hq) * p.Nq + qi) * kD + lane * 4;
-          if (p.q_dtype == 0) {
+          if (!col_live) {
+          } else if (p.q_dtype == 0) {
             __half2 h0 = __floats2half2_rn(acc.x * inv, acc.y * inv), h1 = __floats2half2_rn(acc.z * inv, acc.w * inv);
             uint2 pk = make_uint2(*reinterpret_cast<uint32_t*>(&h0), *reinterpret_cast<uint32_t*>(&h1));
             *reinterpret_cast<uint2*>(reinterpret_cast<__half*>(p.out) + o) = pk;
@@ -787,10 +806,10 @@ int pick_grid_x(int Hkv, int num_splits) {
   return gx;
 }
 
-template <int KV, int HPC>
+template <int KV, int HPC, int D>
 cudaError_t launch_t(const CUtensorMap& tmK, const CUtensorMap& tmV, const KernelArgs& a, int gx, size_t smem,
                      cudaStream_t stream) {
-  auto kern = decode_paged_kernel<KV, HPC>;
+  auto kern = decode_paged_kernel<KV, HPC, D>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
   if (e != cudaSuccess) return e;
   dim3 grid(gx, a.HG);
@@ -798,24 +817,24 @@ cudaError_t launch_t(const CUtensorMap& tmK, const CUtensorMap& tmV, const Kerne
   return cudaGetLastError();
 }
 
-template <int KV>
+template <int KV, int D>
 cudaError_t launch_kv(int hpc, const CUtensorMap& tmK, const CUtensorMap& tmV, const KernelArgs& a, int gx,
                       size_t smem, cudaStream_t stream) {
   switch (hpc) {
-    case 8: return launch_t<KV, 8>(tmK, tmV, a, gx, smem, stream);
-    case 4: return launch_t<KV, 4>(tmK, tmV, a, gx, smem, stream);
-    case 2: return launch_t<KV, 2>(tmK, tmV, a, gx, smem, stream);
-    default: return launch_t<KV, 1>(tmK, tmV, a, gx, smem, stream);
+    case 8: return launch_t<KV, 8, D>(tmK, tmV, a, gx, smem, stream);
+    case 4: return launch_t<KV, 4, D>(tmK, tmV, a, gx, smem, stream);
+    case 2: return launch_t<KV, 2, D>(tmK, tmV, a, gx, smem, stream);
+    default: return launch_t<KV, 1, D>(tmK, tmV, a, gx, smem, stream);
   }
 }
 
 }  // namespace
 
 size_t decode_workspace_bytes(int B, int Hq, int Hkv, int Nq, int D, int max_kv_len, int num_splits) {
-  (void)D; (void)max_kv_len;
+  (void)max_kv_len;
   if (B <= 0 || Hq <= 0 || Hkv <= 0 || Nq <= 0) return 16;
   const int hpc = pick_hpc(Hkv);
-  return make_layout(B, Hq, Nq, Hkv / hpc, pick_grid_x(Hkv, num_splits)).total;
+  return make_layout(B, Hq, Nq, Hkv / hpc, pick_grid_x(Hkv, num_splits), D).total;
 }
 
 cudaError_t launch_decode_paged(const DecodeParams& p, cudaStream_t stream, char* msg, size_t msg_len) {
@@ -823,11 +842,21 @@ cudaError_t launch_decode_paged(const DecodeParams& p, cudaStream_t stream, char
   const int hpc = pick_hpc(p.Hkv);
   const int HG = p.Hkv / hpc;
   const int gx = pick_grid_x(p.Hkv, p.num_splits);
+  const int kD = p.D;
   const int row_bytes = quant ? kD : 2 * kD;
+  if (!(kD == 128 || (kD == 64 && !quant))) {
+    snprintf(msg, msg_len, "head_dim %d with kv_dtype %d (built: 128 for every pool type, 64 for 16-bit pools)", kD, p.kv_dtype);
+    return cudaErrorNotSupported;
+  }
+  if (!p.dense && (p.block_size < kBS || p.block_size % kBS != 0)) {
+    snprintf(msg, msg_len, "block_size %d: pages must hold a multiple of %d tokens", p.block_size, kBS);
+    return cudaErrorNotSupported;
+  }
 
   KernelArgs a;
   a.p = p;
-  a.lay = make_layout(p.B, p.Hq, p.Nq, HG, gx);
+  a.upp = p.dense ? 1 : p.block_size / kBS;
+  a.lay = make_layout(p.B, p.Hq, p.Nq, HG, gx, kD);
   a.HG = HG;
   a.group = p.Hq / p.Hkv;
   a.rows = a.group * p.Nq;
@@ -849,16 +878,36 @@ cudaError_t launch_decode_paged(const DecodeParams& p, cudaStream_t stream, char
   a.inv_cap = p.softcap > 0.f ? 1.f / p.softcap : 0.f;
   const size_t smem = 1024 + static_cast<size_t>(stages) * per_stage + 2 * kMaxStages * 8 + kMaxStages * 4 + 64;
 
-  // tensor maps over the pools: (128 B, tokens, halves of a row, heads, 1)
+  // tensor maps, in bytes: (128 B, tokens, 128-byte halves of a row, heads, batch).  A pool is one "batch" of
+  // num_pages * block_size tokens with the heads of a token side by side; a dense cache has its own strides.
   CUtensorMap tmK, tmV;
-  const uint64_t tokens = static_cast<uint64_t>(p.num_pages) * kBS;
-  const uint64_t dims[5] = {128, tokens, static_cast<uint64_t>(row_bytes / 128), static_cast<uint64_t>(p.Hkv), 1};
-  const uint64_t strides[4] = {static_cast<uint64_t>(p.Hkv) * row_bytes, 128, static_cast<uint64_t>(row_bytes),
-                               tokens * p.Hkv * row_bytes};
   const uint32_t box[5] = {128, kBS, static_cast<uint32_t>(row_bytes / 128), static_cast<uint32_t>(hpc), 1};
-  if (!encode_tmap(&tmK, CU_TENSOR_MAP_DATA_TYPE_UINT8, 5, p.k_pool, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B) ||
-      !encode_tmap(&tmV, CU_TENSOR_MAP_DATA_TYPE_UINT8, 5, p.v_pool, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B)) {
-    snprintf(msg, msg_len, "cuTensorMapEncodeTiled failed for the page pools");
+  bool maps_ok;
+  if (p.dense) {
+    const uint64_t dims[5] = {128, static_cast<uint64_t>(p.max_kv_len), static_cast<uint64_t>(row_bytes / 128),
+                              static_cast<uint64_t>(p.Hkv), static_cast<uint64_t>(p.B)};
+    auto strides_of = [&](int64_t bs, int64_t hs, int64_t rs, uint64_t (&st)[4]) {
+      // a size-1 dimension still needs a legal stride
+      const uint64_t row = static_cast<uint64_t>(rs) * 2;
+      const uint64_t head = hs > 0 ? static_cast<uint64_t>(hs) * 2 : row * p.max_kv_len;
+      st[0] = row; st[1] = 128; st[2] = head;
+      st[3] = bs > 0 ? static_cast<uint64_t>(bs) * 2 : head * p.Hkv;
+    };
+    uint64_t ks[4], vs[4];
+    strides_of(p.k_bs, p.k_hs, p.k_rs, ks);
+    strides_of(p.v_bs, p.v_hs, p.v_rs, vs);
+    maps_ok = encode_tmap(&tmK, CU_TENSOR_MAP_DATA_TYPE_UINT8, 5, p.k_pool, dims, ks, box, CU_TENSOR_MAP_SWIZZLE_128B) &&
+              encode_tmap(&tmV, CU_TENSOR_MAP_DATA_TYPE_UINT8, 5, p.v_pool, dims, vs, box, CU_TENSOR_MAP_SWIZZLE_128B);
+  } else {
+    const uint64_t tokens = static_cast<uint64_t>(p.num_pages) * p.block_size;
+    const uint64_t dims[5] = {128, tokens, static_cast<uint64_t>(row_bytes / 128), static_cast<uint64_t>(p.Hkv), 1};
+    const uint64_t strides[4] = {static_cast<uint64_t>(p.Hkv) * row_bytes, 128, static_cast<uint64_t>(row_bytes),
+                                 tokens * p.Hkv * row_bytes};
+    maps_ok = encode_tmap(&tmK, CU_TENSOR_MAP_DATA_TYPE_UINT8, 5, p.k_pool, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B) &&
+              encode_tmap(&tmV, CU_TENSOR_MAP_DATA_TYPE_UINT8, 5, p.v_pool, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
+  }
+  if (!maps_ok) {
+    snprintf(msg, msg_len, "cuTensorMapEncodeTiled failed for the K / V tensors");
     return cudaErrorInvalidValue;
   }
 
@@ -870,10 +919,12 @@ cudaError_t launch_decode_paged(const DecodeParams& p, cudaStream_t stream, char
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return e;
   switch (p.kv_dtype) {
-    case 0: return launch_kv<KV_F16>(hpc, tmK, tmV, a, gx, smem, stream);
-    case 1: return launch_kv<KV_BF16>(hpc, tmK, tmV, a, gx, smem, stream);
-    case 3: return launch_kv<KV_I8>(hpc, tmK, tmV, a, gx, smem, stream);
-    case 4: return launch_kv<KV_E4M3>(hpc, tmK, tmV, a, gx, smem, stream);
+    case 0: return kD == 64 ? launch_kv<KV_F16, 64>(hpc, tmK, tmV, a, gx, smem, stream)
+                            : launch_kv<KV_F16, 128>(hpc, tmK, tmV, a, gx, smem, stream);
+    case 1: return kD == 64 ? launch_kv<KV_BF16, 64>(hpc, tmK, tmV, a, gx, smem, stream)
+                            : launch_kv<KV_BF16, 128>(hpc, tmK, tmV, a, gx, smem, stream);
+    case 3: return launch_kv<KV_I8, 128>(hpc, tmK, tmV, a, gx, smem, stream);
+    case 4: return launch_kv<KV_E4M3, 128>(hpc, tmK, tmV, a, gx, smem, stream);
     default: snprintf(msg, msg_len, "kv_dtype %d", p.kv_dtype); return cudaErrorNotSupported;
   }
 }

@@ -22,17 +22,18 @@ def _status_checks():
     A._set_check_decode_status(old)
 
 
-def _run(dev, qdtype, quant, B, Hq, Hkv, Nq, lens, seed, causal=True, softcap=0.0, num_splits=0, holes=False, tol=2e-2):
-    pg = make_paged(B, Hkv, 128, 16, lens, qdtype, seed, quant=quant)
+def _run(dev, qdtype, quant, B, Hq, Hkv, Nq, lens, seed, causal=True, softcap=0.0, num_splits=0, holes=False, tol=2e-2,
+         D=128, block_size=16):
+    pg = make_paged(B, Hkv, D, block_size, lens, qdtype, seed, quant=quant)
     table = pg["block_table"].clone()
     if holes:
         table[B - 1, 1] = -1
-    q = randn((B, Hq, Nq, 128), qdtype, seed + 7)
+    q = randn((B, Hq, Nq, D), qdtype, seed + 7)
     ks, vs = pg["k_scale"], pg["v_scale"]
     out, lse = fa.flash_attention_paged(
         q.to(dev), pg["k"].to(dev), pg["v"].to(dev), table.to(dev), pg["seq_lens"].to(dev), causal=causal,
         k_scale=None if ks is None else ks.to(dev), v_scale=None if vs is None else vs.to(dev), softcap=softcap,
-        return_lse=True, num_splits=num_splits)
+        return_lse=True, num_splits=num_splits, block_size=block_size)
     torch.cuda.synchronize()
     O, L = orc.paged_attention(q, pg["k"], pg["v"], table, pg["seq_lens"], causal=causal, softcap=softcap,
                                k_scale=ks, v_scale=vs)
@@ -101,6 +102,65 @@ def test_decode_ignores_garbage_beyond_the_sequence_end(dev, quant):
     assert torch.isfinite(out.float()).all() and torch.isfinite(lse).all()
     assert_close(out, O, qdtype)
     assert_close(lse, L, qdtype, "lse")
+
+
+@pytest.mark.parametrize("block_size", [32, 64, 48])
+@pytest.mark.parametrize("quant", [None, "int8", "e4m3"])
+def test_decode_page_sizes(dev, block_size, quant):
+    """The reference takes any block_size (mlx_mfa/attention.py:914, 2828; its docstring recommends 16, 32 or 64):
+    pages of several 16-token units, ragged last pages, holes and split sequences."""
+    _run(dev, torch.bfloat16, quant, 5, 8, 2, 1, [1, 31, 33, 700, 2900], 480, block_size=block_size, holes=True)
+    _run(dev, torch.float16, quant, 3, 4, 4, 2, [64, 65, 1500], 481, block_size=block_size, num_splits=3)
+
+
+@pytest.mark.parametrize("qdtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("block_size", [16, 64])
+def test_decode_head_dim_64(dev, qdtype, block_size):
+    """head_dim 64 pools (16-bit): GQA groups, several query rows, split sequences."""
+    _run(dev, qdtype, None, 5, 8, 2, 1, LENS, 485, D=64, block_size=block_size)
+    _run(dev, qdtype, None, 3, 6, 3, 4, [70, 900, 2000], 486, D=64, block_size=block_size, causal=True, softcap=20.0)
+    _run(dev, qdtype, None, 2, 16, 16, 1, [300, 5000], 487, D=64, block_size=block_size, num_splits=2)
+
+
+@pytest.mark.parametrize("N", [1, 4, 5])
+@pytest.mark.parametrize("S", [255, 256, 1000, 4099])
+@pytest.mark.parametrize("D", [64, 128])
+def test_dense_cache_decode_route(dev, N, S, D):
+    """Plain flash_attention / dense flash_attention_kvcache calls with a few query rows against a long cache: the
+    reference switches to flash-decoding at N <= 4 and S >= 256 (csrc/mfa_attention.cpp:150-151; its own threshold
+    cases are tests/test_attention.py:1525-1598 in the reference).  Both sides of the threshold, ragged S, causal and
+    not, GQA, soft cap, and a cache that is a view of a longer buffer, against the oracle."""
+    dtype = torch.bfloat16
+    B, Hq, Hkv = 2, 8, 4
+    q = randn((B, Hq, N, D), dtype, 490)
+    kbuf = randn((B, Hkv, S + 37, D), dtype, 491)
+    vbuf = randn((B, Hkv, S + 37, D), dtype, 492)
+    k, v = kbuf[:, :, :S], vbuf[:, :, :S]                       # strided views: batch / head strides of the longer buffer
+    for causal, softcap in ((True, 0.0), (False, 0.0), (True, 30.0)):
+        out, lse = fa.flash_attention(q.to(dev), kbuf.to(dev)[:, :, :S], vbuf.to(dev)[:, :, :S], causal=causal,
+                                      softcap=softcap, return_lse=True)
+        O, L, _ = orc.sdpa(q, k, v, causal=causal, softcap=softcap)
+        assert_close(out, O, dtype)
+        assert_close(lse, L, dtype, "lse")
+    out = fa.flash_attention_kvcache(q.to(dev), k.to(dev), v.to(dev), causal=True)
+    O, _, _ = orc.sdpa(q, k, v, causal=True)
+    assert_close(out, O, dtype)
+
+
+def test_dense_cache_decode_matches_prefill_kernel(dev):
+    """The decode route and the prefill kernel must agree on the same call (different bits show both really ran)."""
+    from mlx_flashattention_steel_b200 import _lib
+
+    q = randn((3, 16, 2, 128), torch.float16, 495).to(dev)
+    k, v = (randn((3, 4, 3000, 128), torch.float16, 496 + i).to(dev) for i in range(2))
+    a, la = fa.flash_attention(q, k, v, causal=True, return_lse=True)
+    old = A._set_force_flags(_lib.FLAG_FORCE_MMA_SYNC)          # keeps the call off the decode route
+    try:
+        b, lb = fa.flash_attention(q, k, v, causal=True, return_lse=True)
+    finally:
+        A._set_force_flags(old)
+    assert float((a.float() - b.float()).abs().max()) <= 2e-2 and float((la - lb).abs().max()) <= 2e-2
+    assert not torch.equal(a, b)
 
 
 def test_decode_softcap(dev):

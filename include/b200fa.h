@@ -78,6 +78,11 @@ typedef struct b200fa_desc {
                                 mlx_mfa/attention.py:1219-1311).  Key tiles without an active block are skipped.
                                 Dense layout, 16-bit, forward and backward. */
   int32_t mask_bq, mask_bk, mask_nk;
+  const int32_t* kv_lens;    /* NULL = off; device int32 [B]: batch entry b attends to its first kv_lens[b] keys only
+                                (clamped to [0, S]; the causal alignment follows that count).  Dense forward, f16 /
+                                bf16, head_dim 64 / 128.  The reference slices each sequence to its exact length on
+                                the host and launches once per sequence (mlx_mfa/attention.py:2950-2989); this is the
+                                same result from one launch. */
 } b200fa_desc;
 
 typedef struct b200fa_device_info_t {
@@ -176,6 +181,35 @@ int32_t b200fa_decode_paged(const b200fa_desc* d, const void* q,
                             int32_t max_kv_len,
                             void* out, float* lse,
                             void* workspace, size_t workspace_bytes, void* stream);
+
+/*
+ * Paged-KV attention for prefill-sized queries (chunked prefill over a page pool): the forward kernel reads K / V
+ * through the block table, page by page; nothing is gathered.  Replaces mfa_paged_steel_forward
+ * (csrc/bindings.cpp:367-407; MFAPagedSteelForward, csrc/mfa_attention.cpp:1355-1552; kernel
+ * csrc/mfa_steel_fwd.cpp:2462-3121) for the shapes b200fa_decode_paged does not take.
+ *   q [B, Hq, N, D] (strides from the descriptor), k_pool / v_pool [num_pages, block_size, Hkv, D] in d->dtype
+ *   (16-bit pools; 8-bit pools go through b200fa_paged_kv_gather_dequant first), block_size a multiple of 16,
+ *   block_table int32 [B, max_blocks] (-1 or an entry beyond the pool = a page of zeros), seq_lens int32 [B].
+ * Sequence b attends to its first seq_lens[b] tokens (at most max_kv_len); causal is lower-right aligned per
+ * sequence; softcap and window_left apply; d->S is ignored.  Slots of a sequence's last page beyond seq_lens[b] must
+ * hold finite values (their probabilities are zero, but the tensor core multiplies them all the same).
+ * No workspace.  head_dim 64 / 128, f16 / bf16.
+ */
+int32_t b200fa_fwd_paged(const b200fa_desc* d, const void* q, const void* k_pool, const void* v_pool,
+                         const int32_t* block_table, const int32_t* seq_lens, int32_t num_pages, int32_t block_size,
+                         int32_t max_blocks, int32_t max_kv_len, void* out, float* lse, void* stream);
+
+/*
+ * Page gather with dequantisation: out[b,h,t,:] = out_dtype(float(pool[page, t % block_size, h, :]) * scale[page,
+ * t % block_size, h]) for t < seq_lens[b] and a valid table entry, else zero -- the dense-dequant path of
+ * mlx_mfa/integrations/mlx_lm.py:97-110 (mx.dequantize(..., dtype=q.dtype)) fused with the gather of
+ * csrc/mfa_paged_gather.cpp:44-80.  pool_dtype B200FA_I8 / B200FA_E4M3, out_dtype B200FA_F16 / B200FA_BF16,
+ * scale float16 [num_pages, block_size, H]; D a multiple of 16.
+ */
+int32_t b200fa_paged_kv_gather_dequant(const void* pool, const void* scale, const int32_t* block_table,
+                                       const int32_t* seq_lens, int32_t B, int32_t H, int32_t D, int32_t pool_dtype,
+                                       int32_t out_dtype, int32_t block_size, int32_t max_blocks, int32_t max_kv_len,
+                                       void* out, void* stream);
 
 /*
  * Paged decode for callers that cannot give it a workspace.  Same arguments and

@@ -14,6 +14,7 @@ from .attention import (
     is_mfa_available,
     kernel_status,
     paged_kv_gather,
+    paged_kv_gather_dequant,
 )
 
 from .host_pipeline import HostPipeline, flash_attention_from_host
@@ -35,6 +36,7 @@ __all__ = [
     "flash_attention_kvcache",
     "flash_attention_paged",
     "paged_kv_gather",
+    "paged_kv_gather_dequant",
     "flash_attention_rope",
     "flash_attention_sparse",
     "make_causal_block_mask",

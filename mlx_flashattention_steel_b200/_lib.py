@@ -48,6 +48,7 @@ class Desc(C.Structure):
         ("mask_bq", C.c_int32),
         ("mask_bk", C.c_int32),
         ("mask_nk", C.c_int32),
+        ("kv_lens", C.c_void_p),
     ]
 
 
@@ -86,6 +87,8 @@ SIGNATURES = {
     "b200fa_decode_paged_workspace_bytes": (_Z, [_DP, _I]),
     "b200fa_decode_paged": (_I, [_DP, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _P, _P, _P, _Z, _P]),
     "b200fa_decode_paged_static": (_I, [_DP, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _P, _P, _P]),
+    "b200fa_fwd_paged": (_I, [_DP, _P, _P, _P, _P, _P, _I, _I, _I, _I, _P, _P, _P]),
+    "b200fa_paged_kv_gather_dequant": (_I, [_P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P, _P]),
     "b200fa_decode_paged_static_status": (_I, [_P, C.POINTER(C.c_int32)]),
     "b200fa_paged_kv_scatter_add": (_I, [_P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P, _P]),
     "b200fa_kv_append": (_I, [_I, _I, _I, _I, _I, _I, C.c_int64, _P, _P, C.c_int64, C.c_int64, _P, _P, _P, _P, _P, _P]),

@@ -45,6 +45,7 @@ __all__ = [
     "flash_attention_kvcache",
     "flash_attention_paged",
     "paged_kv_gather",
+    "paged_kv_gather_dequant",
     "kernel_status",
     "is_mfa_available",
     "get_device_info",
@@ -100,7 +101,7 @@ def _ptr(t: Optional[torch.Tensor]):
 
 
 def _desc(dtype, kv_dtype, B, Hq, Hkv, N, S, D, scale, causal, softcap=0.0, window_left=-1,
-          num_splits=0, flags=0, q=None, k=None, v=None, o=None, alibi=None, bmask=None) -> _lib.Desc:
+          num_splits=0, flags=0, q=None, k=None, v=None, o=None, alibi=None, bmask=None, kv_lens=None) -> _lib.Desc:
     d = _lib.Desc()
     d.dtype, d.kv_dtype = dtype, kv_dtype
     d.B, d.Hq, d.Hkv, d.N, d.S, d.D = B, Hq, Hkv, N, S, D
@@ -117,6 +118,7 @@ def _desc(dtype, kv_dtype, B, Hq, Hkv, N, S, D, scale, causal, softcap=0.0, wind
     d.num_splits = int(num_splits)
     d.flags = int(flags)
     d.alibi_slopes = None if alibi is None else alibi.data_ptr()
+    d.kv_lens = None if kv_lens is None else kv_lens.data_ptr()
     if bmask is not None:            # (uint8 tensor [NQ, NK], block rows, block columns)
         d.block_mask = bmask[0].data_ptr()
         d.mask_bq, d.mask_bk, d.mask_nk = int(bmask[1]), int(bmask[2]), int(bmask[0].shape[1])
@@ -137,8 +139,9 @@ def _set_force_flags(flags: int) -> int:
 # raw operator calls (C-ABI)
 # ---------------------------------------------------------------------------
 def _fwd_raw(q, k, v, scale, causal, softcap, window_left, want_lse, stream, out=None, lse=None, alibi=None,
-             bmask=None):
-    """One forward launch.  `out` / `lse` may be caller-owned contiguous buffers (the host pipeline's staging slots)."""
+             bmask=None, kv_lens=None):
+    """One forward launch.  `out` / `lse` may be caller-owned contiguous buffers (the host pipeline's staging slots).
+    `kv_lens` (int32 [B] on the device): batch entry b sees its first kv_lens[b] keys only."""
     _require_cuda(q, k, v)
     lib = _lib.load()
     B, Hq, N, D = q.shape
@@ -155,7 +158,8 @@ def _fwd_raw(q, k, v, scale, causal, softcap, window_left, want_lse, stream, out
         lse = None
     code = _DTYPE_CODE[q.dtype]
     d = _desc(code, code, B, Hq, Hkv, N, S, D, scale, causal, softcap, window_left,
-              flags=_FORCE_FLAGS, q=q, k=k if S > 0 else None, v=v if S > 0 else None, o=out, alibi=alibi, bmask=bmask)
+              flags=_FORCE_FLAGS, q=q, k=k if S > 0 else None, v=v if S > 0 else None, o=out, alibi=alibi, bmask=bmask,
+              kv_lens=kv_lens)
     with torch.cuda.device(q.device):
         # non-zero only for a few query rows against a long cache (N <= 4, S >= 256): the split-KV decode route
         need = lib.b200fa_fwd_workspace_bytes(C.byref(d))
@@ -491,6 +495,51 @@ class _PagedGatherFn(torch.autograd.Function):
         return grad_pool, None, None, None, None
 
 
+def _fwd_paged_raw(q, k_pages, v_pages, table, lens, max_kv_len, scale, causal, softcap, window_left, want_lse, stream):
+    """Forward over a 16-bit page pool for prefill-sized queries: K / V are read through the block table."""
+    _require_cuda(q, k_pages, v_pages, table, lens)
+    lib = _lib.load()
+    B, Hq, N, D = q.shape
+    num_pages, block_size, Hkv, _ = k_pages.shape
+    q = _row_contig(q)
+    out = torch.empty((B, Hq, N, D), dtype=q.dtype, device=q.device)
+    lse = torch.empty((B, Hq, N), dtype=torch.float32, device=q.device) if want_lse else None
+    code = _DTYPE_CODE[q.dtype]
+    d = _desc(code, code, B, Hq, Hkv, N, int(max_kv_len), D, scale, causal, softcap, window_left, flags=_FORCE_FLAGS, q=q, o=out)
+    with torch.cuda.device(q.device):
+        st = lib.b200fa_fwd_paged(C.byref(d), _ptr(q), _ptr(k_pages), _ptr(v_pages), _ptr(table), _ptr(lens), num_pages,
+                                  block_size, table.shape[1], int(max_kv_len), _ptr(out), _ptr(lse),
+                                  C.c_void_p(_stream_ptr(stream, q.device)))
+    _lib.check(st, "flash_attention_paged")
+    return out, lse
+
+
+def paged_kv_gather_dequant(pool, scale, block_table, seq_lens, max_kv_len: int, out_dtype, stream=None) -> torch.Tensor:
+    """int8 / float8_e4m3 ``pool [num_pages, block_size, H, D]`` with float16 ``scale [num_pages, block_size, H]`` ->
+    ``out_dtype [B, H, max_kv_len, D]``: the page gather and the dense-dequant step of
+    mlx_mfa/integrations/mlx_lm.py:97-110 (``mx.dequantize(..., dtype=q.dtype)``) in one pass; zeros beyond
+    ``seq_lens[b]`` and for ``-1`` table entries."""
+    pool = _as_tensor(pool, "pool").contiguous()
+    scale = _as_tensor(scale, "scale").to(torch.float16).contiguous()
+    table = _as_tensor(block_table, "block_table").to(torch.int32).contiguous()
+    lens = _as_tensor(seq_lens, "seq_lens").to(torch.int32).contiguous()
+    if pool.dtype not in _KV_CODE:
+        raise ValueError(f"paged_kv_gather_dequant: pool dtype {pool.dtype} is not an 8-bit KV type.")
+    if out_dtype not in (torch.float16, torch.bfloat16):
+        raise ValueError("paged_kv_gather_dequant: out_dtype must be float16 or bfloat16.")
+    _require_cuda(pool, scale, table, lens)
+    lib = _lib.load()
+    _, bs, H, D = pool.shape
+    B, max_blocks = table.shape
+    out = torch.empty((B, H, max_kv_len, D), dtype=out_dtype, device=pool.device)
+    with torch.cuda.device(pool.device):
+        st = lib.b200fa_paged_kv_gather_dequant(_ptr(pool), _ptr(scale), _ptr(table), _ptr(lens), B, H, D,
+                                                _KV_CODE[pool.dtype], _DTYPE_CODE[out_dtype], bs, max_blocks,
+                                                int(max_kv_len), _ptr(out), C.c_void_p(_stream_ptr(stream, pool.device)))
+    _lib.check(st, "paged_kv_gather_dequant")
+    return out
+
+
 _CHECK_DECODE_STATUS = False   # tests switch this on: one stream sync per call
 
 
@@ -624,10 +673,23 @@ def flash_attention_paged(
         out, lse = _decode_raw(q, k_pages, v_pages, k_scale, v_scale, table, lens, max_kv_len, float(scale),
                                bool(causal), float(softcap), block_size, return_lse, stream, num_splits)
         return (out, lse) if return_lse else out
+    if not needs_grad and D in _SUPPORTED_HDIMS:
+        # Prefill-sized queries (chunked prefill over the pool), one launch for all sequences.  16-bit pools: the
+        # forward kernel walks the block table itself.  8-bit pools: pages are gathered and dequantised to the query
+        # dtype in one pass (the reference's dense-dequant path), then the dense kernel runs with per-sequence key
+        # counts -- where the reference slices and launches per sequence (mlx_mfa/attention.py:2950-2989).
+        if quant:
+            K = paged_kv_gather_dequant(k_pages, k_scale, table, lens, int(max_kv_len), q.dtype, stream)
+            V = paged_kv_gather_dequant(v_pages, v_scale, table, lens, int(max_kv_len), q.dtype, stream)
+            out, lse = _fwd_raw(q, K, V, float(scale), bool(causal), float(softcap), -1, return_lse, stream, kv_lens=lens)
+        else:
+            out, lse = _fwd_paged_raw(q, k_pages, v_pages, table, lens, max_kv_len, float(scale), bool(causal),
+                                      float(softcap), -1, return_lse, stream)
+        return (out, lse) if return_lse else out
     if quant:
-        raise NotImplementedError("quantized pools are served by the decode kernel only ((Hq/Hkv)*Nq <= 8, D=128).")
+        raise NotImplementedError("quantized pools take f16 / bf16 queries at head_dim 64 or 128 and carry no gradient.")
     if return_lse:
-        raise NotImplementedError("return_lse on the gather route is not built.")
+        raise NotImplementedError("return_lse on the training (gather) route is not built.")
     # gather route, as the reference: pages -> contiguous, then exact-length slices per sequence
     if needs_grad:
         _require_cuda(q, k_pages, v_pages, table, lens)

@@ -104,6 +104,7 @@ int32_t fill_fwd_params(const b200fa_desc* d, const void* q, const void* k, cons
   p->alibi = d->alibi_slopes;
   p->bmask = d->block_mask;
   p->bm_bq = d->mask_bq; p->bm_bk = d->mask_bk; p->bm_nk = d->mask_nk;
+  p->kv_lens = d->kv_lens;
   if (d->block_mask != nullptr) {
     if (d->mask_bq <= 0 || d->mask_bk <= 0 || static_cast<int64_t>(d->mask_nk) * d->mask_bk < d->S)
       return fail(B200FA_ERR_INVALID_ARG, "block_mask: block sizes must be positive and mask_nk * mask_bk cover S");
@@ -206,14 +207,73 @@ int32_t b200fa_fwd(const b200fa_desc* d, const void* q, const void* k, const voi
     if (e != cudaErrorNotSupported) return fail(B200FA_ERR_CUDA, "dense decode launch: %s %s", cudaGetErrorString(e), msg);
     // not a shape the decode kernel takes after all: fall through to the prefill kernels
   }
+  if (d->kv_lens != nullptr && (d->dtype == B200FA_F32 || !b200fa::fwd_sm100_supported(p, d->dtype, d->D)))
+    return fail(B200FA_ERR_UNSUPPORTED, "kv_lens takes f16 / bf16 at head_dim 64 / 128 with positive batch and head strides");
   if (d->dtype == B200FA_F32) {
     e = b200fa::launch_fwd_f32(p, d->D, false, d->B, d->N, cs);
-  } else if (!(d->flags & B200FA_FLAG_FORCE_MMA_SYNC) && b200fa::fwd_sm100_supported(p, d->dtype, d->D)) {
+  } else if ((d->kv_lens != nullptr || !(d->flags & B200FA_FLAG_FORCE_MMA_SYNC)) && b200fa::fwd_sm100_supported(p, d->dtype, d->D)) {
     e = b200fa::launch_fwd_sm100(p, d->dtype, d->D, d->B, d->N, cs);
   } else {
     e = b200fa::launch_fwd_mma(p, d->dtype, d->D, false, d->B, d->N, cs);
   }
   if (e != cudaSuccess) return cuda_fail(e, "forward launch");
+  return B200FA_OK;
+}
+
+int32_t b200fa_fwd_paged(const b200fa_desc* d, const void* q, const void* k_pool, const void* v_pool,
+                         const int32_t* block_table, const int32_t* seq_lens, int32_t num_pages, int32_t block_size,
+                         int32_t max_blocks, int32_t max_kv_len, void* out, float* lse, void* stream) {
+  int32_t st = check_common(d, false);
+  if (st != B200FA_OK) return st;
+  if (d->dtype != B200FA_F16 && d->dtype != B200FA_BF16) return fail(B200FA_ERR_UNSUPPORTED, "paged forward takes f16 / bf16");
+  if (d->kv_dtype != d->dtype)
+    return fail(B200FA_ERR_UNSUPPORTED, "paged forward reads 16-bit pools; dequantise 8-bit pools with b200fa_paged_kv_gather_dequant");
+  if (d->D != 64 && d->D != 128) return fail(B200FA_ERR_UNSUPPORTED, "paged forward is built for head_dim 64 and 128");
+  if (d->alibi_slopes != nullptr || d->block_mask != nullptr)
+    return fail(B200FA_ERR_UNSUPPORTED, "alibi_slopes / block_mask are not supported in paged mode");
+  if (block_size < 16 || block_size % 16 != 0)
+    return fail(B200FA_ERR_UNSUPPORTED, "paged forward takes pages of a multiple of 16 tokens, got %d", block_size);
+  if (num_pages <= 0 || max_blocks <= 0 || max_kv_len < 0) return fail(B200FA_ERR_INVALID_ARG, "bad extent");
+  if (static_cast<int64_t>(num_pages) * block_size >= (1LL << 31)) return fail(B200FA_ERR_UNSUPPORTED, "pool of 2^31 tokens or more");
+  if (static_cast<int64_t>(max_blocks) * block_size < max_kv_len)
+    return fail(B200FA_ERR_INVALID_ARG, "max_kv_len %d exceeds max_blocks*block_size", max_kv_len);
+  if (d->B == 0 || d->N == 0) return B200FA_OK;
+  if (!q || !k_pool || !v_pool || !block_table || !seq_lens || !out) return fail(B200FA_ERR_INVALID_ARG, "null tensor pointer");
+  b200fa_desc dd = *d;
+  dd.S = max_kv_len;
+  dd.k_strides[0] = dd.k_strides[1] = dd.k_strides[2] = 0;      // the pools are addressed through the table, not by strides
+  dd.v_strides[0] = dd.v_strides[1] = dd.v_strides[2] = 0;
+  b200fa::FwdParams p;
+  st = fill_fwd_params(&dd, q, k_pool, v_pool, out, lse, &p);
+  if (st != B200FA_OK) return st;
+  p.kv_lens = seq_lens;
+  p.block_table = block_table;
+  p.max_blocks = max_blocks; p.page_size = block_size; p.num_pages = num_pages;
+  if (!b200fa::fwd_sm100_supported(p, d->dtype, d->D))
+    return fail(B200FA_ERR_UNSUPPORTED, "paged forward: shape or strides not taken by the tcgen05 kernel");
+  cudaError_t e = b200fa::launch_fwd_sm100(p, d->dtype, d->D, d->B, d->N, reinterpret_cast<cudaStream_t>(stream));
+  if (e != cudaSuccess) return cuda_fail(e, "paged forward launch");
+  return B200FA_OK;
+}
+
+int32_t b200fa_paged_kv_gather_dequant(const void* pool, const void* scale, const int32_t* block_table,
+                                       const int32_t* seq_lens, int32_t B, int32_t H, int32_t D, int32_t pool_dtype,
+                                       int32_t out_dtype, int32_t block_size, int32_t max_blocks, int32_t max_kv_len,
+                                       void* out, void* stream) {
+  if (B < 0 || H <= 0 || D <= 0 || block_size <= 0 || max_blocks < 0 || max_kv_len < 0)
+    return fail(B200FA_ERR_INVALID_ARG, "bad extent");
+  if (pool_dtype != B200FA_I8 && pool_dtype != B200FA_E4M3) return fail(B200FA_ERR_UNSUPPORTED, "gather_dequant: pool must be int8 or e4m3");
+  if (out_dtype != B200FA_F16 && out_dtype != B200FA_BF16) return fail(B200FA_ERR_UNSUPPORTED, "gather_dequant: output must be f16 or bf16");
+  if (D % 16 != 0) return fail(B200FA_ERR_INVALID_ARG, "D must be a multiple of 16");
+  if (B == 0 || max_kv_len == 0) return B200FA_OK;
+  if (!pool || !scale || !block_table || !seq_lens || !out) return fail(B200FA_ERR_INVALID_ARG, "null pointer");
+  if (!aligned16(pool) || !aligned16(out)) return fail(B200FA_ERR_INVALID_ARG, "pool/out must be 16-byte aligned");
+  if (static_cast<int64_t>(max_blocks) * block_size < max_kv_len)
+    return fail(B200FA_ERR_INVALID_ARG, "max_kv_len %d exceeds max_blocks*block_size", max_kv_len);
+  cudaError_t e = b200fa::launch_paged_gather_dequant(pool, scale, block_table, seq_lens, B, H, D, pool_dtype, out_dtype,
+                                                      block_size, max_blocks, max_kv_len, out,
+                                                      reinterpret_cast<cudaStream_t>(stream));
+  if (e != cudaSuccess) return cuda_fail(e, "gather_dequant launch");
   return B200FA_OK;
 }
 
@@ -238,8 +298,8 @@ int32_t b200fa_fwd_varlen(const b200fa_desc* d, const void* q, const void* k, co
   b200fa::FwdParams p;
   st = fill_fwd_params(d, q, k, v, out, lse, &p);
   if (st != B200FA_OK) return st;
-  if (d->alibi_slopes != nullptr || d->block_mask != nullptr)
-    return fail(B200FA_ERR_UNSUPPORTED, "alibi_slopes / block_mask with packed sequences are not built");
+  if (d->alibi_slopes != nullptr || d->block_mask != nullptr || d->kv_lens != nullptr)
+    return fail(B200FA_ERR_UNSUPPORTED, "alibi_slopes / block_mask / kv_lens with packed sequences are not built");
   p.cu_q = cu_seqlens_q;
   p.cu_k = cu_seqlens_k;
   cudaStream_t cs = reinterpret_cast<cudaStream_t>(stream);
@@ -309,6 +369,7 @@ static int32_t bwd_common(const b200fa_desc* d, const void* q, const void* k, co
   if (d->dtype == B200FA_F32)
     return fail(B200FA_ERR_UNSUPPORTED, "backward is built for f16 and bf16 (the reference's STEEL backward, "
                                         "mlx_mfa/attention.py:2008-2012, takes the same)");
+  if (d->kv_lens != nullptr) return fail(B200FA_ERR_UNSUPPORTED, "backward with kv_lens is not built");
   if (d->B == 0 || d->N == 0 || nbatch == 0) return B200FA_OK;
   if (!q || !k || !v || !out || !lse || !dout || !dq || !dk || !dv)
     return fail(B200FA_ERR_INVALID_ARG, "null tensor pointer");

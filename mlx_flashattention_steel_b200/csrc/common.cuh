@@ -36,6 +36,12 @@ struct FwdParams {
   const float* alibi;    // per q-head slopes, or null
   const unsigned char* bmask;  // block mask bytes [rows / bm_bq][bm_nk], or null
   int bm_bq, bm_bk, bm_nk;
+  // Dense layout only (tcgen05 kernel): per-batch key counts (null = S for every batch entry), and a page pool in
+  // place of dense k / v: k and v then point at pools [num_pages, page_size, Hkv, D] and the keys of batch entry b
+  // are the tokens block_table[b][0 .. ] lists, kv_lens[b] of them.
+  const int* kv_lens;
+  const int* block_table;      // [B, max_blocks], -1 = no page; null = dense k / v
+  int max_blocks, page_size, num_pages;
 };
 
 // Backward parameter block.  Role of MFASteelBackwardParams

@@ -19,6 +19,10 @@
 // TMEM (256 of 512 columns, so two CTAs share an SM and hide each other's softmax):
 //   [0,64) S0 / P0   [64,128) S1 / P1   [128,128+D) O.
 // Tiles above the causal diagonal or left of the window are skipped whole.
+// Paged K / V (prefill-sized queries over a page pool; the role of the reference's paged STEEL forward,
+// csrc/mfa_steel_fwd.cpp:2462-3121, host csrc/mfa_attention.cpp:1355-1552): the producer walks the block table and
+// brings a 64-key tile in as four 16-token boxes, one per page or part of a page; holes in the table and units
+// beyond the sequence read the pool's out-of-bounds rows, which TMA fills with zeros.  Nothing is gathered.
 // No load here uses cluster multicast.  Every mbarrier wait is bounded; on a timeout the
 // CTA raises its abort flag, frees its TMEM, sets bit 0 of this file's device status word
 // (read through b200fa_kernel_status) and leaves; that launch's outputs are then undefined.
@@ -181,7 +185,10 @@ fa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     k_begin = p.cu_k[batch];
     S = p.cu_k[batch + 1] - k_begin;
     batch = 0;
+  } else if (p.kv_lens != nullptr) {
+    S = min(max(p.kv_lens[batch], 0), p.S);            // this batch entry's own key count
   }
+  const bool paged = p.block_table != nullptr;
   const int q0 = (static_cast<int>(gridDim.x) - 1 - static_cast<int>(blockIdx.x)) * BM;
   if (q0 >= N) return;
   const int off = S - N;
@@ -246,19 +253,53 @@ fa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     return;
   }
 
+  // Paged pools: first pool token of each 16-token unit of the j-th tile (a page is page_size / 16 units).  Units
+  // whose table entry is missing, negative or beyond the pool, and units past the sequence's end, point at the first
+  // row beyond the pool: TMA delivers zeros (and the full byte count) for it.
+  struct UnitToks { int t[BN / 16]; };
+  auto unit_toks = [&](int j) -> UnitToks {
+    UnitToks u;
+    const int upp = p.page_size >> 4;
+    const int oob = p.num_pages * p.page_size;
+    const int32_t* row = p.block_table + static_cast<int64_t>(batch) * p.max_blocks;
+#pragma unroll
+    for (int i = 0; i < BN / 16; ++i) {
+      const int unit = tile_of(j) * (BN / 16) + i;
+      const int blk = unit / upp;
+      int page = -1;
+      if (unit * 16 < S && blk < p.max_blocks) page = __ldg(row + blk);
+      u.t[i] = (page >= 0 && page < p.num_pages) ? page * p.page_size + (unit % upp) * 16 : oob;
+    }
+    return u;
+  };
+  auto load_paged = [&](unsigned char* dst, const CUtensorMap* tm, uint32_t b, const UnitToks& u) {
+#pragma unroll
+    for (int i = 0; i < BN / 16; ++i)
+#pragma unroll
+      for (int hf = 0; hf < kHalves; ++hf)
+        tma_load_4d(smem_u32(dst + hf * (kKVBytes / kHalves) + i * 2048), tm, b, 64 * hf, u.t[i], kvh, 0);
+  };
   // The producer thread sets up the barriers and starts the first loads (Q and as many K / V tiles as there are
   // stages, all of which are empty) before the CTA-wide sync, so TMEM allocation and the sync hide under them.
-  auto load_k = [&](int j) {
+  auto load_k = [&](int j, const UnitToks& u) {
     const int st = j & 1;
     mbar_arrive_expect_tx(bar(BAR_K_FULL + st), kKVBytes);
+    if (paged) {
+      load_paged(sK + st * kKVBytes, &tmK, bar(BAR_K_FULL + st), u);
+      return;
+    }
 #pragma unroll
     for (int hf = 0; hf < kHalves; ++hf)
       tma_load_4d(smem_u32(sK + st * kKVBytes + hf * (kKVBytes / kHalves)), &tmK, bar(BAR_K_FULL + st), 64 * hf,
                   k_begin + tile_of(j) * BN, kvh, batch);
   };
-  auto load_v = [&](int j) {
+  auto load_v = [&](int j, const UnitToks& u) {
     const int st = j & 1;
     mbar_arrive_expect_tx(bar(BAR_V_FULL + st), kKVBytes);
+    if (paged) {
+      load_paged(sV + st * kKVBytes, &tmV, bar(BAR_V_FULL + st), u);
+      return;
+    }
 #pragma unroll
     for (int hf = 0; hf < kHalves; ++hf)
       tma_load_4d(smem_u32(sV + st * kKVBytes + hf * (kKVBytes / kHalves)), &tmV, bar(BAR_V_FULL + st), 64 * hf,
@@ -283,8 +324,10 @@ fa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     for (int hf = 0; hf < kHalves; ++hf)
       tma_load_4d(smem_u32(sQ + hf * (kQBytes / kHalves)), &tmQ, bar(BAR_Q), 64 * hf, q_begin + q0, head, batch);
     for (int j = 0; j < kStages && j < n_tiles; ++j) {
-      load_k(j);
-      load_v(j);
+      UnitToks u = {};
+      if (paged) u = unit_toks(j);
+      load_k(j, u);
+      load_v(j, u);
     }
   }
   if (warp == 5) {
@@ -300,17 +343,23 @@ fa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   if (warp == 4) {
     // ============================ producer ============================
     if (lane == 0) {
+      // paged: the table entries of a tile are fetched one tile ahead, so that their latency passes under the wait
+      // for the stage
+      UnitToks u_next = {};
+      if (paged && kStages < n_tiles) u_next = unit_toks(kStages);
       for (int j = kStages; j < n_tiles; ++j) {
         const int st = j & 1;
         const uint32_t par = ((j >> 1) & 1) ^ 1;
+        const UnitToks u = u_next;
+        if (paged && j + 1 < n_tiles) u_next = unit_toks(j + 1);
         // K(j) and V(j) reuse the stage of tile j-2: wait until its S MMAs, then its PV MMAs, have read it.  These
         // are the barriers the softmax warps wait on too: every commit costs the MMA thread a bubble, so one commit
         // serves both readers.  Neither can be more than one completion ahead of this thread: S(j) needs K(j) and
         // P.V(j) needs V(j), which are loaded below.
         if (!mbar_wait_bounded(bar(BAR_S_FULL + st), par, s_abort)) break;
-        load_k(j);
+        load_k(j, u);
         if (!mbar_wait_bounded(bar(BAR_PV_DONE + st), par, s_abort)) break;
-        load_v(j);
+        load_v(j, u);
       }
     }
   } else if (warp == 5) {
@@ -736,6 +785,13 @@ bool fwd_sm100_supported(const FwdParams& p, int dtype, int D) {
   if ((p.B > 1 && (p.q_bs == 0 || p.k_bs == 0 || p.v_bs == 0 || p.o_bs == 0)) ||
       (p.Hq > 1 && (p.q_hs == 0 || p.o_hs == 0)) || (p.Hkv > 1 && (p.k_hs == 0 || p.v_hs == 0)))
     return false;
+  if (p.block_table != nullptr) {
+    // paged K / V: dense queries only, pages of a multiple of 16 tokens, no bias / block mask
+    if (p.cu_q != nullptr || p.alibi != nullptr || p.bmask != nullptr) return false;
+    if (p.page_size < 16 || p.page_size % 16 != 0 || p.num_pages <= 0 || p.max_blocks <= 0) return false;
+    if (static_cast<int64_t>(p.num_pages) * p.page_size >= (1LL << 31)) return false;
+  }
+  if (p.kv_lens != nullptr && p.cu_q != nullptr) return false;
   if (p.bmask != nullptr) {
     // mask cells must tile the 64-key tiles, and the active-tile list holds 16-bit indices of at most kMaxListTiles
     if (!(p.bm_bk == 16 || p.bm_bk == 32 || p.bm_bk == 64) || p.bm_bq <= 0) return false;
@@ -753,10 +809,18 @@ static cudaError_t launch_hd(const FwdParams& p, int nbatch, int max_q, cudaStre
   const int64_t q_hs = fix(p.q_hs, static_cast<int64_t>(p.N) * p.q_rs), q_bs = fix(p.q_bs, q_hs * p.Hq);
   const int64_t k_hs = fix(p.k_hs, static_cast<int64_t>(p.S) * p.k_rs), k_bs = fix(p.k_bs, k_hs * p.Hkv);
   const int64_t v_hs = fix(p.v_hs, static_cast<int64_t>(p.S) * p.v_rs), v_bs = fix(p.v_bs, v_hs * p.Hkv);
-  if (!make_map(&tmQ, dtype, p.q, HD, p.N, p.Hq, p.B, p.q_rs, q_hs, q_bs, BM) ||
-      !make_map(&tmK, dtype, p.k, HD, p.S, p.Hkv, p.B, p.k_rs, k_hs, k_bs, BN) ||
-      !make_map(&tmV, dtype, p.v, HD, p.S, p.Hkv, p.B, p.v_rs, v_hs, v_bs, BN))
+  if (!make_map(&tmQ, dtype, p.q, HD, p.N, p.Hq, p.B, p.q_rs, q_hs, q_bs, BM)) return cudaErrorInvalidValue;
+  if (p.block_table != nullptr) {
+    // pools [num_pages, page_size, Hkv, D] seen as [1][Hkv][num_pages * page_size tokens][D]; boxes of 16 tokens
+    const int tokens = p.num_pages * p.page_size;
+    const int64_t tok_stride = static_cast<int64_t>(p.Hkv) * HD;
+    if (!make_map(&tmK, dtype, p.k, HD, tokens, p.Hkv, 1, tok_stride, HD, tok_stride * tokens, 16) ||
+        !make_map(&tmV, dtype, p.v, HD, tokens, p.Hkv, 1, tok_stride, HD, tok_stride * tokens, 16))
+      return cudaErrorInvalidValue;
+  } else if (!make_map(&tmK, dtype, p.k, HD, p.S, p.Hkv, p.B, p.k_rs, k_hs, k_bs, BN) ||
+             !make_map(&tmV, dtype, p.v, HD, p.S, p.Hkv, p.B, p.v_rs, v_hs, v_bs, BN)) {
     return cudaErrorInvalidValue;
+  }
   Sm100Args a;
   a.p = p;
   // dense outputs go out by TMA; packed sequences share rows of one tensor, so their tiles are stored row by row

@@ -22,6 +22,10 @@ cudaError_t launch_fwd_f32(const FwdParams& p, int D, bool varlen, int nbatch, i
 bool fwd_sm100_supported(const FwdParams& p, int dtype, int D);
 cudaError_t launch_fwd_sm100(const FwdParams& p, int dtype, int D, int nbatch, int max_q, cudaStream_t stream);
 
+// int8 / e4m3 pool + f16 scales -> f16 / bf16 dense [B, H, max_kv_len, D]
+cudaError_t launch_paged_gather_dequant(const void* pool, const void* scale, const int32_t* block_table,
+                                        const int32_t* seq_lens, int B, int H, int D, int pool_dtype, int out_dtype,
+                                        int block_size, int max_blocks, int max_kv_len, void* out, cudaStream_t stream);
 cudaError_t launch_paged_gather(const void* pool, const int32_t* block_table, const int32_t* seq_lens,
                                 int B, int H, int D, int elem_bytes, int block_size, int max_blocks,
                                 int max_kv_len, void* out, cudaStream_t stream);

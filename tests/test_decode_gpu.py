@@ -186,6 +186,65 @@ def test_gather_route_for_long_queries(dev):
     assert_close(out, O, torch.bfloat16)
 
 
+@pytest.mark.parametrize("quant", [None, "int8", "e4m3"])
+@pytest.mark.parametrize("block_size,D", [(16, 128), (32, 128), (64, 64), (16, 64)])
+def test_paged_prefill_chunks(dev, quant, block_size, D):
+    """Prefill-sized queries over a page pool (chunked prefill): sequences of different length with -1 padding (the
+    reference's paged cases, tests/test_attention.py:3812-3857 in the reference), a hole in a table, GQA, causal
+    lower-right alignment per sequence, soft cap, lse.  16-bit pools are read through the block table by the forward
+    kernel; 8-bit pools are gathered and dequantised first.  Both against the oracle's gather + per-sequence attention."""
+    if quant is not None and D == 64 and block_size == 16:
+        pytest.skip("one 8-bit head_dim-64 case is enough")
+    dtype = torch.bfloat16
+    lens = [48, 100, 700, 0, 1030]
+    B, Hq, Hkv = len(lens), 8, 2
+    pg = make_paged(B, Hkv, D, block_size, lens, dtype, 600, quant=quant)
+    table = pg["block_table"].clone()
+    table[2, 1] = -1                                   # a hole: its tokens count as zeros
+    ks, vs = pg["k_scale"], pg["v_scale"]
+    for Nq, causal, softcap in ((16, True, 0.0), (40, True, 30.0), (130, False, 0.0)):
+        q = randn((B, Hq, Nq, D), dtype, 601 + Nq)
+        out, lse = fa.flash_attention_paged(
+            q.to(dev), pg["k"].to(dev), pg["v"].to(dev), table.to(dev), pg["seq_lens"].to(dev), causal=causal,
+            block_size=block_size, k_scale=None if ks is None else ks.to(dev), v_scale=None if vs is None else vs.to(dev),
+            softcap=softcap, return_lse=True)
+        O, L = orc.paged_attention(q, pg["k"], pg["v"], table, pg["seq_lens"], causal=causal, softcap=softcap,
+                                   k_scale=ks, v_scale=vs)
+        # rows of a causal chunk longer than its sequence see no key: zeros and -inf on both sides
+        assert_close(out, O, dtype)
+        assert_close(lse, L, dtype, "lse")
+
+
+@pytest.mark.parametrize("quant", ["int8", "e4m3"])
+@pytest.mark.parametrize("out_dtype", [torch.float16, torch.bfloat16])
+def test_gather_dequant_is_bit_exact(dev, quant, out_dtype):
+    """out = out_dtype(float(x) * float(scale)), one rounding: equal to the oracle's dequantise-then-gather bit for bit."""
+    lens = [5, 33, 200]
+    pg = make_paged(3, 4, 128, 16, lens, out_dtype, 610, quant=quant)
+    got = fa.paged_kv_gather_dequant(pg["k"].to(dev), pg["k_scale"].to(dev), pg["block_table"].to(dev),
+                                     pg["seq_lens"].to(dev), 200, out_dtype)
+    deq = orc.dequant(pg["k"], pg["k_scale"], out_dtype)
+    ref = orc.paged_gather(deq.view(torch.int16).numpy(), pg["block_table"].numpy(), pg["seq_lens"].numpy(), 200)
+    assert np.array_equal(got.cpu().view(torch.int16).numpy(), ref)
+
+
+def test_dense_attention_with_per_sequence_key_counts(dev):
+    """kv_lens through the raw forward: each batch entry attends to its own number of keys of a padded dense cache."""
+    dtype = torch.float16
+    lens = [300, 1, 0, 257]
+    q = randn((4, 4, 70, 128), dtype, 620)
+    k, v = randn((4, 2, 300, 128), dtype, 621), randn((4, 2, 300, 128), dtype, 622)
+    lt = torch.tensor(lens, dtype=torch.int32, device=dev)
+    out, lse = A._fwd_raw(q.to(dev), k.to(dev), v.to(dev), 128 ** -0.5, True, 0.0, -1, True, None, kv_lens=lt)
+    for b, n in enumerate(lens):
+        if n == 0:
+            assert not out[b].any() and torch.isinf(lse[b]).all()
+            continue
+        O, L, _ = orc.sdpa(q[b:b + 1], k[b:b + 1, :, :n], v[b:b + 1, :, :n], causal=True)
+        assert_close(out[b:b + 1], O, dtype)
+        assert_close(lse[b:b + 1], L, dtype, "lse")
+
+
 def test_config4_shaped_reduced(dev):
     """Config-4 shape with fewer, shorter sequences: B=24, lens ~ U[512, 6144], int8 KV, bf16 q."""
     rng = np.random.default_rng(4)

@@ -8,6 +8,11 @@ N = 1 workload ("config 2"): B=4, Hq=32, Hkv=8, N=S=8192, D=128, bf16, causal,
 softcap=50, return_lse; synthetic N(0,1) inputs from a fixed seed.  With N > 1 (one
 process per GPU under torchrun) every rank runs its own batch of 4 — (batch, kv-head)
 shards need no collective — so scaling is weak and `value` is the sum over ranks.
+Beside that headline the line carries, at every N: `strong` (the ONE fixed config-2
+batch dealt out as 32 (batch, kv-head) units, 32/N per rank), `decode` (config 4 with
+its 128 sequences sharded by batch, each rank with its own pool), `decode_long` (one
+256k-token int8 sequence whose pages are split across the ranks, partials combined
+over NCCL) and `e2e.copy_ceiling_gbs` (the end-to-end pipeline with the kernel left out).
 
 One "step" = one forward over the batch.  `value` is timed with CUDA events on the
 launching stream with inputs resident in HBM (inputs are 403 MB > the 126 MB L2, so no
@@ -200,16 +205,20 @@ def run_reference(args, rank, world):
         secs.append(s)
     val = statistics.median(vals)
     g = cfg["Hq"] // cfg["Hkv"]
-    step_equiv_ms = statistics.median(secs) * cfg["B"] * cfg["Hkv"] * 1e3
+    slice_ms = statistics.median(secs) * 1e3
     line = {
         "impl": "reference", "metric": METRIC, "value": val, "unit": "TFLOP/s", "n_gpus": args.gpus,
-        "steps": args.steps, "warmup": args.warmup, "ms_per_step": step_equiv_ms, "higher_is_better": True,
-        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": slice_ms,
+        "ms_per_step_full_equiv": slice_ms * cfg["B"] * cfg["Hkv"], "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None,
+        "dtype": "f32 (wider than the reference's own bf16 CPU path: the restatement computes in float32)",
+        "data": "synthetic",
         "config": workload_config(args.gpus),
         "cpu_baseline": {"value": val, "unit": "TFLOP/s", "cores": torch.get_num_threads(), "kind": "port", "sample": sample},
         "e2e": {"value": val, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "note": "CPU restatement of the reference's SDPA fallback (MLX itself is not installable here); "
-                "each step times one (batch, kv-group) slice, ms_per_step is scaled to the whole batch",
+                "each step times one (batch, kv-group) slice = 1/32 of the workload: ms_per_step is that slice's own time, "
+                "ms_per_step_full_equiv the same scaled to the whole batch; value (TFLOP/s) is scale-free",
     }
     print(json.dumps(line), flush=True)
 
@@ -220,29 +229,45 @@ def workload_config(n):
             "l2": "inputs (403 MB) exceed L2 (126 MB); no explicit flush"}
 
 
-def bench_decode(device, steps, warmup, pk, batch=None):
-    """Config 4: paged int8-KV decode, B=128, seq_lens ~ U[512, 32768], page 16."""
+def dram_traffic_ratio(key):
+    """DRAM bytes per algorithmic byte of the ncu capture named `key` (measured on a small case of the same kernel);
+    None when the table is missing."""
+    try:
+        t = json.load(open(os.path.join(ROOT, "profiles", "dram_traffic.json")))[key]
+        return float(t["dram_bytes"]) / float(t["algorithmic_bytes"])
+    except (OSError, KeyError, ValueError):
+        return None
+
+
+def bench_decode(device, steps, warmup, pk, batch=None, rank=0, world=1, dist=None):
+    """Config 4: paged int8-KV decode, B=128, seq_lens ~ U[512, 32768], page 16.  With world > 1 the 128 sequences are
+    sharded by batch: rank r owns a contiguous range of them with a pool of its own (no collective on the data path);
+    the total is all ranks' bytes over the slowest rank's time."""
     import numpy as np
 
     import mlx_flashattention_steel_b200 as fa
+    from mlx_flashattention_steel_b200 import parallel as par
 
     cfg = dict(C4)
     if batch:
         cfg["B"] = batch
     rng = np.random.default_rng(4)
-    lens = rng.integers(cfg["lo"], cfg["hi"] + 1, size=cfg["B"]).astype(np.int32)
+    all_lens = rng.integers(cfg["lo"], cfg["hi"] + 1, size=cfg["B"]).astype(np.int32)
+    b_lo, b_hi = par.shard_range(cfg["B"], world, rank)
+    lens = all_lens[b_lo:b_hi]
+    nb = int(b_hi - b_lo)
     bs, Hkv, D = cfg["block_size"], cfg["Hkv"], cfg["D"]
     pages_per = (lens + bs - 1) // bs
     P = int(pages_per.sum()) + 8
     perm = rng.permutation(P)
     max_blocks = int(pages_per.max())
-    table = -np.ones((cfg["B"], max_blocks), dtype=np.int32)
+    table = -np.ones((nb, max_blocks), dtype=np.int32)
     pos = 0
-    for b in range(cfg["B"]):
+    for b in range(nb):
         n = int(pages_per[b])
         table[b, :n] = perm[pos:pos + n]
         pos += n
-    gd = torch.Generator(device=device).manual_seed(4)
+    gd = torch.Generator(device=device).manual_seed(4 + rank)
     pools = {}
     for name in ("k", "v"):
         qx = torch.empty((P, bs, Hkv, D), dtype=torch.int8, device=device)
@@ -254,7 +279,7 @@ def bench_decode(device, steps, warmup, pk, batch=None):
             qx[p0:p0 + x.shape[0]] = (x / s.float().unsqueeze(-1)).round().clamp(-127, 127).to(torch.int8)
             sc[p0:p0 + x.shape[0]] = s
         pools[name] = (qx, sc)
-    q = torch.randn((cfg["B"], cfg["Hq"], 1, D), generator=gd, device=device).to(torch.bfloat16)
+    q = torch.randn((nb, cfg["Hq"], 1, D), generator=gd, device=device).to(torch.bfloat16)
     table_t = torch.from_numpy(table).to(device)
     lens_t = torch.from_numpy(lens).to(device)
     max_len = int(lens.max())
@@ -268,6 +293,8 @@ def bench_decode(device, steps, warmup, pk, batch=None):
     for _ in range(max(warmup, 3)):
         step()
     torch.cuda.synchronize()
+    if dist is not None:
+        dist.barrier()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     for _ in range(steps):
@@ -276,14 +303,119 @@ def bench_decode(device, steps, warmup, pk, batch=None):
     torch.cuda.synchronize()
     ms = e0.elapsed_time(e1) / steps
     gbs = bytes_alg / (ms * 1e-3) / 1e9
-    return {"metric": "paged-decode KV GB/s", "value": gbs, "unit": "GB/s", "ms_per_step": ms,
-            "workload": "config 4: B=128 Hq=32 Hkv=8 D=128 page 16 seq_lens~U[512,32768] int8 KV + f16 scales, bf16 q",
-            "tokens": tokens, "algorithmic_bytes": bytes_alg,
+    ms_max, bytes_total, per_rank = ms, bytes_alg, [gbs]
+    if dist is not None:
+        t = torch.tensor([ms, float(bytes_alg)], device=device, dtype=torch.float64)
+        allt = [torch.empty_like(t) for _ in range(world)]
+        dist.all_gather(allt, t)
+        ms_max = max(float(x[0]) for x in allt)
+        bytes_total = sum(float(x[1]) for x in allt)
+        per_rank = [float(x[1]) / (float(x[0]) * 1e-3) / 1e9 for x in allt]
+    total_gbs = bytes_total / (ms_max * 1e-3) / 1e9
+    ratio = dram_traffic_ratio("decode_paged_config4_small")
+    return {"metric": "paged-decode KV GB/s", "value": total_gbs, "unit": "GB/s", "ms_per_step": ms_max,
+            "workload": f"config 4: B={cfg['B']} Hq=32 Hkv=8 D=128 page 16 seq_lens~U[512,32768] int8 KV + f16 scales, bf16 q"
+                        + (f"; sequences sharded by batch over {world} GPUs, one pool per GPU" if world > 1 else ""),
+            "n_gpus": world, "per_gpu_gbs": per_rank, "tokens": tokens if world == 1 else None,
+            "algorithmic_bytes": bytes_total,
+            # per GPU: rank 0's own launch against the measured copy bandwidth of one GPU
             "roofline": {"bound": "hbm", "achieved": gbs, "peak": pk["hbm"], "unit": "GB/s", "frac": gbs / pk["hbm"],
-                         # ncu capture at B=24 read 968.0 MB + wrote 4.4 MB for 966.5 MB algorithmic
-                         # (profiles/decode_paged_config4_small.md); traffic grows with the tokens processed
-                         "traffic": bytes_alg * (968.0 + 4.4) / 966.5, "peak_source": pk["src"]},
+                         # the ncu capture was taken at B=24; DRAM traffic grows with the tokens processed
+                         "traffic": bytes_alg * ratio if ratio else None, "peak_source": pk["src"]},
             "gpu_launches": steps * 2}
+
+
+def bench_strong(device, rank, world, dist, steps, warmup):
+    """Strong scaling of config 2: ONE fixed batch (same seed on every rank), dealt out as 32 (batch, kv-head) units;
+    each rank attends its 32 / world units as views of the full tensors, no collective.  Time = slowest rank."""
+    import mlx_flashattention_steel_b200 as fa
+    from mlx_flashattention_steel_b200 import parallel as par
+
+    cfg = dict(C2)
+    q, k, v = make_prefill_inputs(cfg, device, seed=2)
+    g = cfg["Hq"] // cfg["Hkv"]
+    blocks = par.shard_blocks(cfg["B"], cfg["Hkv"], world, rank)
+
+    def step():
+        for b, h0, h1 in blocks:
+            fa.flash_attention(q[b:b + 1, h0 * g:h1 * g], k[b:b + 1, h0:h1], v[b:b + 1, h0:h1], causal=True,
+                               softcap=cfg["softcap"], return_lse=True)
+
+    for _ in range(max(warmup, 3)):
+        step()
+    torch.cuda.synchronize()
+    if dist is not None:
+        dist.barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        step()
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / steps
+    if dist is not None:
+        t = torch.tensor([ms], device=device, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    units = sum(h1 - h0 for _, h0, h1 in blocks)
+    return {"scaling": "strong", "workload": "the one config-2 batch (B=4, 32 (batch, kv-head) units) split over the GPUs",
+            "units_per_gpu": units, "launches_per_step_per_gpu": len(blocks), "ms_per_step": ms,
+            "value": prefill_flops(cfg) / (ms * 1e-3) / 1e12, "unit": "TFLOP/s"}
+
+
+def bench_decode_long(device, rank, world, dist, steps, warmup):
+    """One 262144-token int8 sequence (Hq=32, Hkv=8, D=128, page 16) whose pages are split across the ranks: each rank
+    runs the paged decode kernel on its pages (fp32 partials + lse in one packed buffer), one NCCL all-gather, one
+    combine launch.  Reports the whole step and the local kernel alone, i.e. the share the exchange costs."""
+    import mlx_flashattention_steel_b200 as fa
+    from mlx_flashattention_steel_b200 import attention as fa_attn, parallel as par
+
+    S, Hq, Hkv, D, bs = 262144, 32, 8, 128, 16
+    n_pages = S // bs
+    lo, hi, ntok = par.split_pages(n_pages, world, rank, bs, S)
+    P = hi - lo
+    gd = torch.Generator(device=device).manual_seed(40 + rank)
+    kq = torch.randint(-127, 128, (P, bs, Hkv, D), generator=gd, device=device, dtype=torch.int8)
+    vq = torch.randint(-127, 128, (P, bs, Hkv, D), generator=gd, device=device, dtype=torch.int8)
+    ksc = (torch.rand((P, bs, Hkv), generator=gd, device=device) * 0.004 + 0.006).to(torch.float16)
+    vsc = (torch.rand((P, bs, Hkv), generator=gd, device=device) * 0.004 + 0.006).to(torch.float16)
+    q = torch.randn((1, Hq, 1, D), generator=torch.Generator(device=device).manual_seed(41), device=device).to(torch.bfloat16)
+    tbl = torch.randperm(P, generator=gd, device=device).to(torch.int32).unsqueeze(0)
+    lens = torch.tensor([ntok], dtype=torch.int32, device=device)
+
+    def local():
+        return fa_attn._decode_raw(q, kq, vq, ksc, vsc, tbl, lens, ntok, D ** -0.5, False, 0.0, bs, True, None, packed=True)
+
+    def full():
+        if dist is None:
+            return fa.flash_attention_paged(q, kq, vq, tbl, lens, k_scale=ksc, v_scale=vsc, max_kv_len=ntok)
+        return par.decode_long_sequence(q, kq, vq, tbl, lens, k_scale=ksc, v_scale=vsc, max_kv_len=ntok)
+
+    res = {}
+    for name, fn in (("step", full), ("local_kernel", local)):
+        for _ in range(max(warmup, 3)):
+            fn()
+        torch.cuda.synchronize()
+        if dist is not None:
+            dist.barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / steps
+        if dist is not None:
+            t = torch.tensor([ms], device=device, dtype=torch.float64)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        res[name] = ms
+    bytes_alg = S * Hkv * (2 * D + 4)
+    return {"workload": "one 262144-token sequence, int8 KV + f16 scales, Hq=32 Hkv=8 D=128 page 16, pages split over the GPUs",
+            "n_gpus": world, "ms_per_step": res["step"], "local_kernel_ms": res["local_kernel"],
+            "exchange_share": max(0.0, 1.0 - res["local_kernel"] / res["step"]) if world > 1 else 0.0,
+            "exchange": "NCCL all-gather of Hq*(D+4) fp32 per rank + one combine launch" if world > 1 else "none (one GPU)",
+            "value": bytes_alg / (res["step"] * 1e-3) / 1e9, "unit": "GB/s"}
 
 
 def _time_ms(fn, steps, warmup):
@@ -498,14 +630,38 @@ def main():
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         e2e_ms = float(t.item())
     e2e_val = flops / (e2e_ms * 1e-3) / 1e12 * world
-    del hq, hk, hv, ho, hl
+
+    # the same pipeline with the kernel launch left out, all ranks at once: what the host link and the host's memory
+    # allow for these copies (the ceiling the end-to-end figure is to be read against)
+    def copy_step():
+        pipe.run(hq, hk, hv, ho, hl, causal=True, softcap=cfg["softcap"], copies_only=True)
+
+    copy_step()
+    torch.cuda.synchronize()
+    if dist is not None:
+        dist.barrier()
+    e0.record()
+    for _ in range(e2e_steps):
+        copy_step()
+    e1.record()
+    torch.cuda.synchronize()
+    copy_ms = e0.elapsed_time(e1) / e2e_steps
+    if dist is not None:
+        t = torch.tensor([copy_ms], device=device, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        copy_ms = float(t.item())
+    copy_ceiling_gbs = (h2d + d2h) * world / (copy_ms * 1e-3) / 1e9
+    del hq, hk, hv, ho, hl, pipe
 
     decode = None
-    if rank == 0 and not args.no_decode and not args.small:
+    if not args.no_decode and not args.small:
         try:
-            decode = bench_decode(device, max(args.steps, 10), warm, pk)
+            decode = bench_decode(device, max(args.steps, 10), warm, pk, rank=rank, world=world, dist=dist)
         except NotImplementedError as e:  # decode kernel not built for this shape
             decode = {"unavailable": str(e)}
+    del q, k, v
+    strong = bench_strong(device, rank, world, dist, max(3, min(args.steps, 10)), warm)
+    decode_long = bench_decode_long(device, rank, world, dist, 20, warm)
     extras = None
     if rank == 0 and world == 1 and not args.no_extras:
         extras = bench_extras(device, pk)
@@ -513,6 +669,7 @@ def main():
         dist.barrier()
 
     if rank == 0:
+        traffic_ratio = dram_traffic_ratio("fwd_sm100_config2_small")
         cpu = None
         if world == 1 and not args.no_cpu_baseline:
             torch.set_num_threads(os.cpu_count() or 1)
@@ -523,19 +680,24 @@ def main():
             "metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
             "warmup": warm, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": "bf16", "data": "synthetic", "config": workload_config(world),
-            # traffic: dram bytes of one launch; the ncu capture (profiles/fwd_sm100_config2_small.md) was taken at
-            # B=2 N=4096 (136 MB for 84.9 MB of q+k+v+o+lse) and is scaled by the algorithmic bytes of this launch
+            # traffic: dram bytes of one launch; the ncu capture was taken on a smaller case of the same kernel and is
+            # scaled by the algorithmic bytes (q + k + v + o + lse) of this launch
             "roofline": {"bound": "tensor", "achieved": tf_rank, "peak": pk["tf"], "unit": "TFLOP/s",
-                         "frac": tf_rank / pk["tf"], "traffic": 136.0e6 / 84.9e6 * 675.3e6, "peak_source": pk["src"],
+                         "frac": tf_rank / pk["tf"],
+                         "traffic": (traffic_ratio * (h2d + d2h)) if traffic_ratio else None, "peak_source": pk["src"],
                          "frac_of_sustained": (tf_rank / pk["tf_sustained"]) if pk.get("tf_sustained") else None,
                          "flops_per_launch": flops},
             "cpu_baseline": cpu,
             "e2e": {"value": e2e_val, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-                    "ms_per_step": e2e_ms},
+                    "ms_per_step": e2e_ms, "copy_ceiling_gbs": copy_ceiling_gbs, "copies_only_ms_per_step": copy_ms,
+                    "achieved_copy_gbs": (h2d + d2h) * world / (e2e_ms * 1e-3) / 1e9,
+                    "frac_of_copy_ceiling": copy_ms / e2e_ms},
             "gpu_launches": args.steps,
             "kernel_status": int(fa.kernel_status()),       # 0 = no bounded wait inside a tcgen05 kernel gave up
             "clocks": clocks,
             "decode": decode,
+            "strong": strong,
+            "decode_long": decode_long,
             "extras": extras,
         }
         if args.small:

@@ -49,6 +49,10 @@ extern "C" {
 
 /* flags */
 #define B200FA_FLAG_FORCE_MMA_SYNC  1  /* use the portable mma.sync kernels even where a tcgen05 kernel exists */
+#define B200FA_FLAG_PACKED_F32      4  /* b200fa_decode_paged: `out` is float [B*Hq*N][D+4], the normalised row in fp32 with
+                                          its base-2 lse at column D (columns D+1..D+3 pad the row to 16 bytes); `lse` is
+                                          ignored.  The per-GPU partial of a sequence whose pages are spread over several
+                                          GPUs, in the form b200fa_combine_partials takes. */
 
 /*
  * Problem descriptor.  Plays the role of MFAttention::Params + MFASteelParams
@@ -181,6 +185,17 @@ int32_t b200fa_decode_paged(const b200fa_desc* d, const void* q,
                             int32_t max_kv_len,
                             void* out, float* lse,
                             void* workspace, size_t workspace_bytes, void* stream);
+
+/*
+ * Merges R partial attention results over disjoint key ranges (one per GPU, gathered by the caller -- one NCCL
+ * all-gather of the packed rows): gathered is float [R][rows][D+4] in the B200FA_FLAG_PACKED_F32 form,
+ * out [rows][D] in out_dtype (f16 / bf16), lse float [rows] or NULL.  L = log2 sum_r 2^lse_r,
+ * O = sum_r 2^(lse_r - L) O_r: the split combine of the reference's flash-decode reduce
+ * (csrc/mfa_steel_fwd.cpp:2066-2101), applied across GPUs; the reference itself is single-device.  D a multiple of 4,
+ * at most 128.
+ */
+int32_t b200fa_combine_partials(const float* gathered, int32_t R, int64_t rows, int32_t D, int32_t out_dtype,
+                                void* out, float* lse, void* stream);
 
 /*
  * Paged-KV attention for prefill-sized queries (chunked prefill over a page pool): the forward kernel reads K / V

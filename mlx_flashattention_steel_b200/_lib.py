@@ -19,6 +19,7 @@ ERR_DEVICE = -5
 
 F16, BF16, F32, I8, E4M3 = 0, 1, 2, 3, 4
 FLAG_FORCE_MMA_SYNC = 1
+FLAG_PACKED_F32 = 4
 
 
 class Desc(C.Structure):
@@ -87,6 +88,7 @@ SIGNATURES = {
     "b200fa_decode_paged_workspace_bytes": (_Z, [_DP, _I]),
     "b200fa_decode_paged": (_I, [_DP, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _P, _P, _P, _Z, _P]),
     "b200fa_decode_paged_static": (_I, [_DP, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _P, _P, _P]),
+    "b200fa_combine_partials": (_I, [_P, _I, C.c_int64, _I, _I, _P, _P, _P]),
     "b200fa_fwd_paged": (_I, [_DP, _P, _P, _P, _P, _P, _I, _I, _I, _I, _P, _P, _P]),
     "b200fa_paged_kv_gather_dequant": (_I, [_P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P, _P]),
     "b200fa_decode_paged_static_status": (_I, [_P, C.POINTER(C.c_int32)]),

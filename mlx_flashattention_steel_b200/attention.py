@@ -556,17 +556,24 @@ if hasattr(torch, "float8_e4m3fn"):
 
 
 def _decode_raw(q, k_pages, v_pages, k_scale, v_scale, table, lens, max_kv_len, scale, causal, softcap,
-                block_size, want_lse, stream, num_splits=0, workspace=None):
+                block_size, want_lse, stream, num_splits=0, workspace=None, packed=False):
+    """One decode launch.  packed=True returns (float32 [B*Hq*Nq, D+4], None): each row is the normalised output in
+    fp32 with its base-2 lse at column D -- the per-GPU partial that `parallel.combine_packed` merges."""
     _require_cuda(q, k_pages, v_pages, k_scale, v_scale, table, lens)
     lib = _lib.load()
     B, Hq, Nq, D = q.shape
     num_pages, _, Hkv, _ = k_pages.shape
     q = q.contiguous()
-    out = torch.empty((B, Hq, Nq, D), dtype=q.dtype, device=q.device)
-    lse = torch.empty((B, Hq, Nq), dtype=torch.float32, device=q.device) if want_lse else None
+    if packed:
+        out = torch.empty((B * Hq * Nq, D + 4), dtype=torch.float32, device=q.device)
+        lse = None
+    else:
+        out = torch.empty((B, Hq, Nq, D), dtype=q.dtype, device=q.device)
+        lse = torch.empty((B, Hq, Nq), dtype=torch.float32, device=q.device) if want_lse else None
     code = _DTYPE_CODE[q.dtype]
     kv_code = _KV_CODE.get(k_pages.dtype, _DTYPE_CODE.get(k_pages.dtype, -1))
-    d = _desc(code, kv_code, B, Hq, Hkv, Nq, 0, D, scale, causal, softcap, -1, num_splits, _FORCE_FLAGS)
+    d = _desc(code, kv_code, B, Hq, Hkv, Nq, 0, D, scale, causal, softcap, -1, num_splits,
+              _FORCE_FLAGS | (_lib.FLAG_PACKED_F32 if packed else 0))
     with torch.cuda.device(q.device):
         need = lib.b200fa_decode_paged_workspace_bytes(C.byref(d), int(max_kv_len))
         if workspace is None or workspace.numel() < need:

@@ -220,6 +220,18 @@ int32_t b200fa_fwd(const b200fa_desc* d, const void* q, const void* k, const voi
   return B200FA_OK;
 }
 
+int32_t b200fa_combine_partials(const float* gathered, int32_t R, int64_t rows, int32_t D, int32_t out_dtype,
+                                void* out, float* lse, void* stream) {
+  if (R < 0 || rows < 0 || D <= 0 || D % 4 != 0 || D > 128) return fail(B200FA_ERR_INVALID_ARG, "combine_partials: bad extent");
+  if (out_dtype != B200FA_F16 && out_dtype != B200FA_BF16) return fail(B200FA_ERR_UNSUPPORTED, "combine_partials: f16 / bf16 output");
+  if (R == 0 || rows == 0) return B200FA_OK;
+  if (!gathered || !out) return fail(B200FA_ERR_INVALID_ARG, "combine_partials: null pointer");
+  if (!aligned16(gathered) || (reinterpret_cast<uintptr_t>(out) & 7u)) return fail(B200FA_ERR_INVALID_ARG, "combine_partials: alignment");
+  cudaError_t e = b200fa::launch_combine_partials(gathered, R, rows, D, out_dtype, out, lse, reinterpret_cast<cudaStream_t>(stream));
+  if (e != cudaSuccess) return cuda_fail(e, "combine_partials launch");
+  return B200FA_OK;
+}
+
 int32_t b200fa_fwd_paged(const b200fa_desc* d, const void* q, const void* k_pool, const void* v_pool,
                          const int32_t* block_table, const int32_t* seq_lens, int32_t num_pages, int32_t block_size,
                          int32_t max_blocks, int32_t max_kv_len, void* out, float* lse, void* stream) {
@@ -599,6 +611,7 @@ int32_t b200fa_decode_paged(const b200fa_desc* d, const void* q, const void* k_p
   p.q_dtype = d->dtype; p.kv_dtype = d->kv_dtype;
   p.scale = d->scale; p.softcap = d->softcap; p.causal = d->causal ? 1 : 0;
   p.num_splits = d->num_splits;
+  p.packed_f32 = (d->flags & B200FA_FLAG_PACKED_F32) ? 1 : 0;
   char msg[256] = "";
   cudaError_t e = b200fa::launch_decode_paged(p, reinterpret_cast<cudaStream_t>(stream), msg, sizeof(msg));
   if (e == cudaErrorNotSupported) return fail(B200FA_ERR_UNSUPPORTED, "decode: %s", msg);

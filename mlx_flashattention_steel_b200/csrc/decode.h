@@ -27,7 +27,15 @@ struct DecodeParams {
   // max_kv_len; "page" j of sequence b is its tokens [16 j, 16 j + 16), no table is read.
   int dense;
   int64_t k_bs, k_hs, k_rs, v_bs, v_hs, v_rs;
+  // Partial results for a combine across GPUs: `out` is float [B * Hq * Nq][D + 4] -- the normalised row in fp32
+  // with its base-2 lse at column D (columns D + 1 .. D + 3 pad the row to 16 bytes) -- and `lse` is ignored.
+  int packed_f32;
 };
+
+// gathered: [R][rows][D + 4] packed partials (see DecodeParams::packed_f32) -> out [rows][D] (dtype 0 f16 / 1 bf16),
+// lse [rows] (may be null): L = log2 sum_r 2^lse_r, O = sum_r 2^(lse_r - L) O_r.
+cudaError_t launch_combine_partials(const float* gathered, int R, long long rows, int D, int out_dtype, void* out,
+                                    float* lse, cudaStream_t stream);
 
 size_t decode_workspace_bytes(int B, int Hq, int Hkv, int Nq, int D, int max_kv_len, int num_splits);
 cudaError_t launch_decode_paged(const DecodeParams& p, cudaStream_t stream, char* msg, size_t msg_len);

@@ -246,10 +246,17 @@ decode_paged_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_consta
         const int r = i / kD;                       // (head in cta, group, qi)
         const int qi = r % p.Nq;
         const int hq = (hg * HPC) * a.group + r / p.Nq;
-        const size_t o = ((static_cast<size_t>(b) * p.Hq + hq) * p.Nq + qi) * kD + d;
-        if (p.q_dtype == 0) reinterpret_cast<__half*>(p.out)[o] = __float2half(0.f);
-        else reinterpret_cast<__nv_bfloat16*>(p.out)[o] = __float2bfloat16(0.f);
-        if (p.lse != nullptr && d == 0) p.lse[(static_cast<size_t>(b) * p.Hq + hq) * p.Nq + qi] = -INFINITY;
+        const size_t orow = (static_cast<size_t>(b) * p.Hq + hq) * p.Nq + qi;
+        const size_t o = orow * kD + d;
+        if (p.packed_f32) {
+          float* pk = reinterpret_cast<float*>(p.out) + orow * (kD + 4);
+          pk[d] = 0.f;
+          if (d == 0) pk[kD] = -INFINITY;
+        } else {
+          if (p.q_dtype == 0) reinterpret_cast<__half*>(p.out)[o] = __float2half(0.f);
+          else reinterpret_cast<__nv_bfloat16*>(p.out)[o] = __float2bfloat16(0.f);
+          if (p.lse != nullptr && d == 0) p.lse[orow] = -INFINITY;
+        }
       }
     }
   }
@@ -704,8 +711,10 @@ decode_paged_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_consta
         const int hq = kvh * a.group + r % a.group;
         const int qi = r / a.group;
         if (direct) {
-          const size_t o = ((static_cast<size_t>(b) * p.Hq + hq) * p.Nq + qi) * kD + d;
-          if (p.q_dtype == 0) reinterpret_cast<__half*>(p.out)[o] = __float2half_rn(val);
+          const size_t orow = (static_cast<size_t>(b) * p.Hq + hq) * p.Nq + qi;
+          const size_t o = orow * kD + d;
+          if (p.packed_f32) reinterpret_cast<float*>(p.out)[orow * (kD + 4) + d] = val;
+          else if (p.q_dtype == 0) reinterpret_cast<__half*>(p.out)[o] = __float2half_rn(val);
           else reinterpret_cast<__nv_bfloat16*>(p.out)[o] = __float2bfloat16_rn(val);
         } else {
           part_o[(static_cast<size_t>(slot) * HqNq + hq * p.Nq + qi) * kD + d] = val;
@@ -714,7 +723,9 @@ decode_paged_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_consta
     }
     if (t == 0 && row_valid) {
       if (direct) {
-        if (p.lse != nullptr) p.lse[(static_cast<size_t>(b) * p.Hq + hq_row) * p.Nq + qi_row] = lse_row;
+        const size_t orow = (static_cast<size_t>(b) * p.Hq + hq_row) * p.Nq + qi_row;
+        if (p.packed_f32) reinterpret_cast<float*>(p.out)[orow * (kD + 4) + kD] = lse_row;
+        else if (p.lse != nullptr) p.lse[orow] = lse_row;
       } else {
         part_lse[static_cast<size_t>(slot) * HqNq + hq_row * p.Nq + qi_row] = lse_row;
       }
@@ -753,8 +764,13 @@ decode_paged_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_consta
             acc.z = fmaf(w, v4.z, acc.z); acc.w = fmaf(w, v4.w, acc.w);
           }
           const float inv = wsum > 0.f ? 1.f / wsum : 0.f;
-          const size_t o = ((static_cast<size_t>(b) * p.Hq + hq) * p.Nq + qi) * kD + lane * 4;
-          if (!col_live) {
+          const size_t orow = (static_cast<size_t>(b) * p.Hq + hq) * p.Nq + qi;
+          const size_t o = orow * kD + lane * 4;
+          if (p.packed_f32) {
+            float* pk = reinterpret_cast<float*>(p.out) + orow * (kD + 4);
+            if (col_live) *reinterpret_cast<float4*>(pk + lane * 4) = make_float4(acc.x * inv, acc.y * inv, acc.z * inv, acc.w * inv);
+            if (lane == 0) pk[kD] = wsum > 0.f ? mmax + log2f(wsum) : -INFINITY;
+          } else if (!col_live) {
           } else if (p.q_dtype == 0) {
             __half2 h0 = __floats2half2_rn(acc.x * inv, acc.y * inv), h1 = __floats2half2_rn(acc.z * inv, acc.w * inv);
             uint2 pk = make_uint2(*reinterpret_cast<uint32_t*>(&h0), *reinterpret_cast<uint32_t*>(&h1));
@@ -764,8 +780,7 @@ decode_paged_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_consta
             uint2 pk = make_uint2(*reinterpret_cast<uint32_t*>(&h0), *reinterpret_cast<uint32_t*>(&h1));
             *reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(p.out) + o) = pk;
           }
-          if (p.lse != nullptr && lane == 0)
-            p.lse[(static_cast<size_t>(b) * p.Hq + hq) * p.Nq + qi] = wsum > 0.f ? mmax + log2f(wsum) : -INFINITY;
+          if (!p.packed_f32 && p.lse != nullptr && lane == 0) p.lse[orow] = wsum > 0.f ? mmax + log2f(wsum) : -INFINITY;
         }
       }
       named_bar_sync(1, HPC * 32);   // s_last is reused by the next sequence
@@ -775,6 +790,43 @@ decode_paged_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_consta
     if (u >= s1) ++b;
   }
   if (!ok && lane == 0) atomicOr(err, 1);
+}
+
+// Combine of per-GPU partials: one warp per output row, lanes across the head dim.
+__global__ void __launch_bounds__(256) combine_partials_kernel(const float* __restrict__ g, int R, long long rows, int D,
+                                                               int out_dtype, void* __restrict__ out, float* __restrict__ lse) {
+  const long long row = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (row >= rows) return;
+  const int W = D + 4;
+  float m = -INFINITY;
+  for (int r = 0; r < R; ++r) m = fmaxf(m, g[(static_cast<long long>(r) * rows + row) * W + D]);
+  const float ms = (m == -INFINITY) ? 0.f : m;
+  float wsum = 0.f;
+  float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+  const bool live = lane * 4 < D;
+  for (int r = 0; r < R; ++r) {
+    const float* src = g + (static_cast<long long>(r) * rows + row) * W;
+    const float w = exp2f(src[D] - ms);
+    wsum += w;
+    if (live) {
+      const float4 v = *reinterpret_cast<const float4*>(src + lane * 4);
+      acc.x = fmaf(w, v.x, acc.x); acc.y = fmaf(w, v.y, acc.y); acc.z = fmaf(w, v.z, acc.z); acc.w = fmaf(w, v.w, acc.w);
+    }
+  }
+  const float inv = wsum > 0.f ? 1.f / wsum : 0.f;
+  if (live) {
+    const long long o = row * D + lane * 4;
+    uint2 pk;
+    if (out_dtype == 0) {
+      pk = make_uint2(pack_h2(acc.x * inv, acc.y * inv), pack_h2(acc.z * inv, acc.w * inv));
+      *reinterpret_cast<uint2*>(reinterpret_cast<__half*>(out) + o) = pk;
+    } else {
+      pk = make_uint2(pack_bf2(acc.x * inv, acc.y * inv), pack_bf2(acc.z * inv, acc.w * inv));
+      *reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(out) + o) = pk;
+    }
+  }
+  if (lse != nullptr && lane == 0) lse[row] = wsum > 0.f ? m + log2f(wsum) : -INFINITY;
 }
 
 int device_sm_count() {
@@ -829,6 +881,14 @@ cudaError_t launch_kv(int hpc, const CUtensorMap& tmK, const CUtensorMap& tmV, c
 }
 
 }  // namespace
+
+cudaError_t launch_combine_partials(const float* gathered, int R, long long rows, int D, int out_dtype, void* out,
+                                    float* lse, cudaStream_t stream) {
+  if (R <= 0 || rows <= 0) return cudaSuccess;
+  const long long blocks = (rows * 32 + 255) / 256;
+  combine_partials_kernel<<<static_cast<unsigned>(blocks), 256, 0, stream>>>(gathered, R, rows, D, out_dtype, out, lse);
+  return cudaGetLastError();
+}
 
 size_t decode_workspace_bytes(int B, int Hq, int Hkv, int Nq, int D, int max_kv_len, int num_splits) {
   (void)max_kv_len;

@@ -50,7 +50,9 @@ class HostPipeline:
         self.do = mk((c, hc * g) + tuple(q_shape[2:]), dtype)
         self.dl = mk((c, hc * g, q_shape[2]), torch.float32) if want_lse else None
 
-    def run(self, q, k, v, out, lse=None, scale=None, causal=False, softcap=0.0, window_size=None):
+    def run(self, q, k, v, out, lse=None, scale=None, causal=False, softcap=0.0, window_size=None, copies_only=False):
+        """copies_only: a measuring aid -- the same copies through the same streams and events with the kernel launch
+        left out (what comes back is whatever the staging buffers held); it shows what the host link alone allows."""
         B, Hkv, g, D = q.shape[0], k.shape[1], self.group, q.shape[3]
         if scale is None:
             scale = 1.0 / math.sqrt(D)
@@ -81,8 +83,11 @@ class HostPipeline:
                     self.s_run.wait_event(copied[i - self.depth])      # that piece's outputs have left this slot
                 # a ragged last piece is a strided view of its slot: let the launch allocate its outputs then
                 full = do.is_contiguous() and (dl is None or dl.is_contiguous())
-                o, l = _fwd_raw(dq, dk, dv, float(scale), bool(causal), float(softcap), window_left, want_lse, self.s_run,
-                                out=do if full else None, lse=dl if full else None)
+                if copies_only:
+                    o, l, full = do, dl, True
+                else:
+                    o, l = _fwd_raw(dq, dk, dv, float(scale), bool(causal), float(softcap), window_left, want_lse, self.s_run,
+                                    out=do if full else None, lse=dl if full else None)
                 ran.append(self.s_run.record_event())
             with torch.cuda.stream(self.s_out):
                 self.s_out.wait_event(ran[i])

@@ -9,10 +9,12 @@ around the operators on an 8-GPU box.
   ``shard_units`` deals the (batch, kv-head) units out and each rank runs the ordinary
   operators on views of its shard.
 * One very long decode sequence is the exception: its page list is split across ranks,
-  every rank runs the same split-KV decode kernel over its pages with ``return_lse=True``,
-  and ``combine_partials`` merges the per-rank (O, lse) with one small all-gather
-  (Hq*(D+1) floats per rank) and the log-sum-exp rule the decode kernel itself uses
-  between CTAs (``L = log2 sum_r 2^lse_r``, ``O = sum_r 2^(lse_r - L) O_r``).
+  every rank runs the same split-KV decode kernel over its pages, which leaves its partial
+  (fp32 rows with their base-2 lse) in one packed buffer; ``combine_packed`` merges the ranks'
+  partials with one small NCCL all-gather (Hq*(D+4) floats per rank) and one launch of the
+  library's combine kernel -- the log-sum-exp rule the decode kernel itself uses between CTAs
+  (``L = log2 sum_r 2^lse_r``, ``O = sum_r 2^(lse_r - L) O_r``).  ``combine_partials`` is the
+  same rule in torch ops for host tensors (the gloo tests of the host logic).
 """
 from __future__ import annotations
 
@@ -36,6 +38,18 @@ def shard_units(B: int, Hkv: int, world: int, rank: int) -> List[Tuple[int, int]
     rank's units are a few whole batches plus a contiguous head range (views, no copies)."""
     lo, hi = shard_range(B * Hkv, world, rank)
     return [(u // Hkv, u % Hkv) for u in range(lo, hi)]
+
+
+def shard_blocks(B: int, Hkv: int, world: int, rank: int) -> List[Tuple[int, int, int]]:
+    """The units of ``shard_units`` merged into (batch, first kv head, end kv head) blocks: a rank's units are
+    contiguous, so they are at most a partial batch, some whole batches and another partial batch -- one launch each."""
+    blocks: List[Tuple[int, int, int]] = []
+    for b, h in shard_units(B, Hkv, world, rank):
+        if blocks and blocks[-1][0] == b and blocks[-1][2] == h:
+            blocks[-1] = (b, blocks[-1][1], h + 1)
+        else:
+            blocks.append((b, h, h + 1))
+    return blocks
 
 
 def shard_views(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, world: int, rank: int):
@@ -80,17 +94,53 @@ def combine_partials(out: torch.Tensor, lse: torch.Tensor, group: Optional[dist.
     return o.to(out_dtype or out.dtype), L
 
 
+def combine_packed(packed: torch.Tensor, D: int, out_dtype: torch.dtype, group: Optional[dist.ProcessGroup] = None,
+                   stream=None) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Merges the per-rank packed partials of the decode kernel (float32 [rows, D+4]: the normalised row in fp32, its
+    base-2 lse at column D) into (O [rows, D] out_dtype, L [rows] float32) on every rank: one NCCL all-gather of the
+    packed rows -- the partials stay fp32 across ranks -- and one launch of the library's combine kernel."""
+    import ctypes as C
+
+    from . import _lib
+    from .attention import _DTYPE_CODE, _stream_ptr
+
+    world = dist.get_world_size(group)
+    rows = packed.shape[0]
+    gathered = torch.empty((world,) + tuple(packed.shape), dtype=torch.float32, device=packed.device)
+    dist.all_gather_into_tensor(gathered, packed, group=group)
+    out = torch.empty((rows, D), dtype=out_dtype, device=packed.device)
+    lse = torch.empty((rows,), dtype=torch.float32, device=packed.device)
+    with torch.cuda.device(packed.device):
+        st = _lib.load().b200fa_combine_partials(C.c_void_p(gathered.data_ptr()), world, rows, D, _DTYPE_CODE[out_dtype],
+                                                 C.c_void_p(out.data_ptr()), C.c_void_p(lse.data_ptr()),
+                                                 C.c_void_p(_stream_ptr(stream, packed.device)))
+    _lib.check(st, "combine_partials")
+    return out, lse
+
+
 def decode_long_sequence(q, k_pages, v_pages, block_table_local, seq_lens_local, *, group=None, scale=None,
-                         k_scale=None, v_scale=None, softcap: float = 0.0, max_kv_len=None):
+                         k_scale=None, v_scale=None, softcap: float = 0.0, max_kv_len=None, block_size: int = 16):
     """Decode step for sequences whose pages are spread over the ranks of ``group``: every rank passes
-    the block table rows and token counts of ITS part of each sequence (q is replicated).  Runs the
-    paged decode kernel locally, then ``combine_partials``.  causal is irrelevant for a single query
+    the block table rows and token counts of ITS part of each sequence (q is replicated).  Three launches and one
+    collective per step: the paged decode kernel on the local pages, leaving fp32 partials with their lse in one
+    packed buffer; an all-gather of that buffer; the combine kernel.  causal is irrelevant for a single query
     token (the reference notes N=1 causal == non-causal, tests/test_attention.py:1472-1487)."""
-    from .attention import flash_attention_paged
+    import math
+
+    from .attention import _decode_raw
 
     if q.shape[2] != 1:
         raise NotImplementedError("decode_long_sequence takes one query token per sequence")
-    o, l = flash_attention_paged(q, k_pages, v_pages, block_table_local, seq_lens_local, scale=scale, causal=False,
-                                 k_scale=k_scale, v_scale=v_scale, softcap=softcap, max_kv_len=max_kv_len,
-                                 return_lse=True)
-    return combine_partials(o, l, group=group, out_dtype=q.dtype)
+    B, Hq, _, D = q.shape
+    if scale is None:
+        scale = 1.0 / math.sqrt(D)
+    table = block_table_local.to(torch.int32).contiguous()
+    lens = seq_lens_local.to(torch.int32).contiguous()
+    if max_kv_len is None:
+        max_kv_len = table.shape[1] * block_size        # no host read of seq_lens: the table's width bounds the length
+    if k_scale is not None:
+        k_scale, v_scale = k_scale.to(torch.float16).contiguous(), v_scale.to(torch.float16).contiguous()
+    packed, _ = _decode_raw(q, k_pages.contiguous(), v_pages.contiguous(), k_scale, v_scale, table, lens, int(max_kv_len),
+                            float(scale), False, float(softcap), block_size, True, None, packed=True)
+    o, l = combine_packed(packed, D, q.dtype, group=group)
+    return o.view(B, Hq, 1, D), l.view(B, Hq, 1)

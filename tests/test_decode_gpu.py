@@ -245,6 +245,55 @@ def test_dense_attention_with_per_sequence_key_counts(dev):
         assert_close(lse[b:b + 1], L, dtype, "lse")
 
 
+@pytest.mark.parametrize("parts", [2, 3])
+def test_packed_partials_and_combine_kernel(dev, parts):
+    """What the multi-GPU long-sequence path does, on one GPU: the page list of each sequence is cut into `parts`
+    ranges, the decode kernel leaves an fp32 partial with its lse for each range (one packed buffer per range), and the
+    combine kernel merges them.  The result must equal the decode of the whole sequences and the oracle.  One range
+    is left empty for one sequence (lse = -inf drops out of the combine)."""
+    import ctypes as C
+
+    from mlx_flashattention_steel_b200 import _lib
+    from mlx_flashattention_steel_b200 import parallel as par
+
+    dtype, D, bs = torch.bfloat16, 128, 16
+    lens = [5000, 130, 16]
+    B, Hq, Hkv = len(lens), 16, 4
+    pg = make_paged(B, Hkv, D, bs, lens, dtype, 630, quant="int8")
+    pgd = {k: (v.to(dev) if isinstance(v, torch.Tensor) else v) for k, v in pg.items()}
+    q = randn((B, Hq, 1, D), dtype, 631)
+    qd = q.to(dev)
+    packed = []
+    for r in range(parts):
+        rows, counts = [], []
+        for b, n in enumerate(lens):
+            lo, hi, ntok = par.split_pages((n + bs - 1) // bs, parts, r, bs, n)
+            rows.append(pg["block_table"][b, lo:hi])
+            counts.append(ntok)
+        width = max(1, max(len(x) for x in rows))
+        tbl = torch.full((B, width), -1, dtype=torch.int32)
+        for b, x in enumerate(rows):
+            tbl[b, :len(x)] = x
+        lt = torch.tensor(counts, dtype=torch.int32)
+        pk, _ = A._decode_raw(qd, pgd["k"], pgd["v"], pgd["k_scale"], pgd["v_scale"], tbl.to(dev), lt.to(dev),
+                              max(max(counts), 1), D ** -0.5, False, 0.0, bs, True, None, packed=True)
+        assert pk.shape == (B * Hq, D + 4) and pk.dtype == torch.float32
+        packed.append(pk)
+    gathered = torch.stack(packed, dim=0).contiguous()
+    out = torch.empty((B * Hq, D), dtype=dtype, device=dev)
+    lse = torch.empty((B * Hq,), dtype=torch.float32, device=dev)
+    st = _lib.load().b200fa_combine_partials(C.c_void_p(gathered.data_ptr()), parts, B * Hq, D, _lib.BF16,
+                                             C.c_void_p(out.data_ptr()), C.c_void_p(lse.data_ptr()),
+                                             C.c_void_p(torch.cuda.current_stream().cuda_stream))
+    assert st == _lib.OK, _lib.last_error()
+    O, L = orc.paged_attention(q, pg["k"], pg["v"], pg["block_table"], pg["seq_lens"], k_scale=pg["k_scale"],
+                               v_scale=pg["v_scale"])
+    assert_close(out.view(B, Hq, 1, D), O, dtype)
+    assert_close(lse.view(B, Hq, 1), L, dtype, "lse")
+    # the short sequences leave whole ranges empty: their partial lse must be -inf, not NaN
+    assert torch.isinf(gathered[parts - 1, 2 * Hq:, D]).all()
+
+
 def test_config4_shaped_reduced(dev):
     """Config-4 shape with fewer, shorter sequences: B=24, lens ~ U[512, 6144], int8 KV, bf16 q."""
     rng = np.random.default_rng(4)

@@ -7,16 +7,19 @@
 //
 // One CTA = 128 query rows of one query head; it walks the 64-key tiles those rows can see (causal / window tiles
 // outside the band are skipped whole).  Per key tile j, three GEMMs with M = 128 query rows:
-//   S(j)  = Q . K(j)^T      (SS, N = 64, K = 128)  -> TMEM S buffer j & 1
-//   dP(j) = dO . V(j)^T     (SS, N = 64, K = 128)  -> TMEM dP buffer j & 1
+//   S(j)  = Q . K(j)^T      (SS, N = 64, K = 128)  -> TMEM S buffer j % 3
+//   dP(j) = dO . V(j)^T     (SS, N = 64, K = 128)  -> TMEM dP buffer j % 3
 //   8 compute warps (thread = query row; the two warps of a lane quarter split the 64 key columns) form
 //   P = 2^(s - L) and dS = P o (dP - delta) [x (1 - tanh^2) under a soft cap] and write dS back as a 16-bit A operand
-//   over the dP columns they came from
+//   over the dP columns they came from.  There are two such sets of 8 warps, one for the even tiles and one for the
+//   odd ones: a warp's step is a chain of latencies (barrier, TMEM load, arithmetic, TMEM store, arrive), and with
+//   one set the tensor pipe was active a third of the time
 //   dQ   += dS(j) . K(j)    (A from TMEM, B = K(j) as an MN-major operand, N = 128)  -> TMEM dQ
-// Issue order SD(0) SD(1) dQ(0) SD(2) dQ(1) ... keeps the tensor pipe busy while the compute warps work on the other
-// buffer.  Warp 8 is the TMA producer (Q and dO once, K and V tiles into a three-stage ring), one thread of warp 9
+// Issue order SD(0) SD(1) dQ(0) SD(2) dQ(1) ...: the S / dP MMAs of the next tile are queued while the compute warps
+// work on this one.
+// Warp 16 is the TMA producer (Q and dO once, K and V tiles into a four-stage ring), one thread of warp 17
 // issues the MMAs.  dQ leaves TMEM once, scaled, through shared memory (TMA store for the dense layout).
-// TMEM: [0,128) S0 S1, [128,256) dP0 dP1, [256,384) dQ.  No load uses cluster multicast; every mbarrier wait is
+// TMEM (all 512 columns): [0,128) S0 S1, [128,256) dP0 dP1, [256,384) dQ, [384,512) Q and dO as A operands.  No load uses cluster multicast; every mbarrier wait is
 // bounded and a timeout raises this file's status word (read through b200fa_kernel_status).
 #include "common.cuh"
 #include "launch.h"
@@ -32,10 +35,15 @@ namespace {
 constexpr int HD = 128;
 constexpr int BM = 128;            // query rows per CTA
 constexpr int BN = 64;             // keys per tile
-constexpr int kStages = 3;
-constexpr int kThreads = 320;      // warps 0-7 compute, 8 producer, 9 MMA issue
+constexpr int kStages = 4;         // K / V ring: tiles j .. j + 2 are in use at once, one more is in flight
+constexpr int kBufs = 2;           // S / dP buffers in TMEM
+constexpr int kThreads = 576;      // warps 0-7 compute (even tiles), 8-15 compute (odd tiles), 16 producer, 17 MMA issue
+constexpr int kProducerWarp = 16, kMmaWarp = 17;
 constexpr uint32_t kTmemCols = 512;
 constexpr uint32_t cS = 0, cDP = 128, cDQ = 256;
+// Q and dO rows as 16-bit A operands (two elements per column), copied from shared memory once per CTA: the S / dP
+// MMAs then read only K / V from shared memory, whose bandwidth is what an SS MMA of this shape saturates
+constexpr uint32_t cQA = 384, cDOA = 448;
 
 constexpr int kQBytes = BM * HD * 2;        // 32768: [2 d-halves][128 rows][128 B]
 constexpr int kKVBytes = BN * HD * 2;       // 16384: [2 d-halves][64 rows][128 B]
@@ -46,12 +54,13 @@ constexpr int kSmemBytes = kSmemTiles + 256 + 1024;
 enum Bar {
   BAR_Q = 0,
   BAR_KV_FULL = 1,          // + stage
-  BAR_KV_EMPTY = 4,         // + stage: the dQ MMAs of the tile (the last readers of its K and V) have completed
-  BAR_SD_FULL = 7,          // + buffer: S and dP of a tile are complete
-  BAR_DS_READY = 9,         // + buffer: count 8, the compute warps have written dS
-  BAR_DQ_FINAL = 11,
-  BAR_STAGED = 12,          // count 8: the compute warps have staged their dQ rows in shared memory
-  BAR_COUNT = 13
+  BAR_KV_EMPTY = 5,         // + stage: the dQ MMAs of the tile (the last readers of its K and V) have completed
+  BAR_SD_FULL = 9,          // + buffer: S and dP of a tile are complete
+  BAR_DS_READY = 12,        // + buffer: count 8, the compute warps have written dS
+  BAR_DQ_FINAL = 15,
+  BAR_STAGED = 16,          // count 16: the compute warps have staged their dQ rows in shared memory
+  BAR_QA_READY = 17,        // count 16: Q and dO sit in TMEM
+  BAR_COUNT = 18
 };
 
 struct DqArgs {
@@ -127,18 +136,19 @@ bwd_dq_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       tma_load_4d(smem_u32(dst + kKVBytes + hf * (kKVBytes / 2)), &tmV, bar(BAR_KV_FULL + st), 64 * hf, row, kvh, batch);
     }
   };
-  if (warp == 8 && lane == 0) {
+  if (warp == kProducerWarp && lane == 0) {
     mbar_init(bar(BAR_Q), 1);
     for (int s = 0; s < kStages; ++s) {
       mbar_init(bar(BAR_KV_FULL + s), 1);
       mbar_init(bar(BAR_KV_EMPTY + s), 1);
     }
-    for (int b = 0; b < 2; ++b) {
+    for (int b = 0; b < kBufs; ++b) {
       mbar_init(bar(BAR_SD_FULL + b), 1);
       mbar_init(bar(BAR_DS_READY + b), 8);
     }
     mbar_init(bar(BAR_DQ_FINAL), 1);
-    mbar_init(bar(BAR_STAGED), 8);
+    mbar_init(bar(BAR_STAGED), 16);
+    mbar_init(bar(BAR_QA_READY), 16);
     *s_abort = 0;
     fence_barrier_init();
     fence_proxy_async();
@@ -150,7 +160,7 @@ bwd_dq_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     }
     for (int j = 0; j < kStages && j < n_tiles; ++j) load_kv(j);
   }
-  if (warp == 9) {
+  if (warp == kMmaWarp) {
     tmem_alloc(smem_u32(s_tmem), kTmemCols);
     tmem_relinquish();
   }
@@ -159,7 +169,7 @@ bwd_dq_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   tc_fence_after();
   const uint32_t tmem = *s_tmem;
 
-  if (warp == 8) {
+  if (warp == kProducerWarp) {
     // ============================ producer ============================
     if (lane == 0) {
       for (int j = kStages; j < n_tiles; ++j) {
@@ -169,41 +179,39 @@ bwd_dq_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         load_kv(j);
       }
     }
-  } else if (warp == 9) {
+  } else if (warp == kMmaWarp) {
     // ============================ MMA issue ============================
     if (lane == 0) {
       const uint32_t id_sd = instr_desc(DT, 0, BM, BN);          // S, dP: B K-major, N = 64
       const uint32_t id_dq = instr_desc(DT, 1, BM, HD);          // dQ: B = K MN-major, N = 128
-      const uint64_t qd = smem_desc(smem_u32(sQ), 16, 1024), dod = smem_desc(smem_u32(sDO), 16, 1024);
       const uint64_t kd0 = smem_desc(smem_u32(sKV), 16, 1024);
       const uint64_t kmn0 = smem_desc(smem_u32(sKV), kKVBytes / 2, 1024);
-      constexpr uint64_t kHalfQ = (kQBytes / 2) >> 4, kHalfK = (kKVBytes / 2) >> 4, kStageU = kStageBytes >> 4,
-                         kVOff = kKVBytes >> 4;
-      bool ok = mbar_wait_bounded(bar(BAR_Q), 0, s_abort);
+      constexpr uint64_t kHalfK = (kKVBytes / 2) >> 4, kStageU = kStageBytes >> 4, kVOff = kKVBytes >> 4;
+      bool ok = mbar_wait_bounded(bar(BAR_QA_READY), 0, s_abort);
+      tc_fence_after();
       auto issue_sd = [&](int j) -> bool {
-        const int st = j % kStages, b = j & 1;
+        const int st = j % kStages, b = j % kBufs;
         if (!mbar_wait_bounded(bar(BAR_KV_FULL + st), (j / kStages) & 1, s_abort)) return false;
         tc_fence_after();
         const uint64_t kd = kd0 + static_cast<uint64_t>(st) * kStageU, vd = kd + kVOff;
 #pragma unroll
         for (int k = 0; k < HD / 16; ++k)
-          mma_ss(tmem + cS + 64 * b, qd + (k >> 2) * kHalfQ + (k & 3) * 2, kd + (k >> 2) * kHalfK + (k & 3) * 2, id_sd,
-                 k > 0 ? 1u : 0u);
+          mma_ts(tmem + cS + 64 * b, tmem + cQA + k * 8, kd + (k >> 2) * kHalfK + (k & 3) * 2, id_sd, k > 0 ? 1u : 0u);
 #pragma unroll
         for (int k = 0; k < HD / 16; ++k)
-          mma_ss(tmem + cDP + 64 * b, dod + (k >> 2) * kHalfQ + (k & 3) * 2, vd + (k >> 2) * kHalfK + (k & 3) * 2, id_sd,
-                 k > 0 ? 1u : 0u);
+          mma_ts(tmem + cDP + 64 * b, tmem + cDOA + k * 8, vd + (k >> 2) * kHalfK + (k & 3) * 2, id_sd, k > 0 ? 1u : 0u);
         tc_commit(bar(BAR_SD_FULL + b));
         return true;
       };
-      if (ok) ok = issue_sd(0);
+      for (int j = 0; j < kBufs - 1 && j < n_tiles && ok; ++j) ok = issue_sd(j);
       for (int j = 0; j < n_tiles && ok; ++j) {
-        const int st = j % kStages, b = j & 1;
-        if (j + 1 < n_tiles) {
-          ok = issue_sd(j + 1);
+        const int st = j % kStages, b = j % kBufs;
+        // the other buffer is free: dQ(j - 1), the last reader of its dS, was issued in the previous iteration
+        if (j + kBufs - 1 < n_tiles) {
+          ok = issue_sd(j + kBufs - 1);
           if (!ok) break;
         }
-        if (!mbar_wait_bounded(bar(BAR_DS_READY + b), (j >> 1) & 1, s_abort)) { ok = false; break; }
+        if (!mbar_wait_bounded(bar(BAR_DS_READY + b), (j / kBufs) & 1, s_abort)) { ok = false; break; }
         tc_fence_after();
         const uint64_t kmn = kmn0 + static_cast<uint64_t>(st) * kStageU;
         // A = dS in TMEM: 16 keys = 8 columns; keys 0-31 of the tile at +0, 32-63 at +32 (where the two warps of a
@@ -217,8 +225,8 @@ bwd_dq_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       }
     }
   } else {
-    // ============================ compute warps 0-7 ============================
-    const int wq = warp & 3, hf = warp >> 2;                   // TMEM lane quarter, key-column half
+    // ============================ compute warps 0-15 ============================
+    const int wq = warp & 3, hf = (warp >> 2) & 1, set = warp >> 3;   // TMEM lane quarter, key-column half, tile parity
     const int rloc = wq * 32 + lane;
     const int row = q0 + rloc;
     const uint32_t lane_base = static_cast<uint32_t>(wq * 32) << 16;
@@ -233,11 +241,27 @@ bwd_dq_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     const float cap_in = CAP ? p.scale / p.softcap : 0.f, cap_out = p.softcap * kLog2e;
     const bool precise_tanh = p.softcap >= kPreciseTanhMinCap;
     const float2 c2 = make_float2(p.scale_log2, p.scale_log2), nL2 = make_float2(nL, nL), nD2 = make_float2(nD, nD);
-    bool ok = true;
-    for (int j = 0; j < n_tiles; ++j) {
-      const int b = j & 1;
+    bool ok = __all_sync(0xffffffffu, mbar_wait_bounded(bar(BAR_Q), 0, s_abort));
+    if (ok) {
+      // this row's 128 bytes of d-half hf of Q (set 0) or dO (set 1) -> 32 TMEM columns of the A operand
+      const uint32_t rowa = smem_u32(set == 0 ? sQ : sDO) + hf * (kQBytes / 2) + rloc * 128;
+      uint32_t qr[32];
+#pragma unroll
+      for (int c = 0; c < 8; ++c)
+        asm volatile("ld.shared.v4.b32 {%0,%1,%2,%3}, [%4];\n"
+                     : "=r"(qr[4 * c]), "=r"(qr[4 * c + 1]), "=r"(qr[4 * c + 2]), "=r"(qr[4 * c + 3])
+                     : "r"(rowa + static_cast<uint32_t>((c ^ (rloc & 7)) << 4))
+                     : "memory");
+      tmem_st32(tmem + lane_base + (set == 0 ? cQA : cDOA) + hf * 32, qr);
+      tc_wait_st();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar(BAR_QA_READY));
+    }
+    for (int j = set; j < n_tiles && ok; j += 2) {
+      const int b = j % kBufs;
       const int k0 = (kt_begin + j) * BN + hf * 32;            // first key of this thread's 32 columns
-      if (!__all_sync(0xffffffffu, mbar_wait_bounded(bar(BAR_SD_FULL + b), (j >> 1) & 1, s_abort))) { ok = false; break; }
+      if (!__all_sync(0xffffffffu, mbar_wait_bounded(bar(BAR_SD_FULL + b), (j / kBufs) & 1, s_abort))) { ok = false; break; }
       tc_fence_after();
       uint32_t rs[32], rd[32];
       tmem_ld32(tmem + lane_base + cS + 64 * b + hf * 32, rs);
@@ -281,9 +305,10 @@ bwd_dq_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     if (ok) ok = __all_sync(0xffffffffu, mbar_wait_bounded(bar(BAR_DQ_FINAL), 0, s_abort));
     if (ok) {
       tc_fence_after();
-      // this warp's 64 of the 128 columns = d-half hf; staged as [d-half][row][128 B], 16-byte chunks swizzled by row
-#pragma unroll
-      for (int c = 0; c < 2; ++c) {
+      // this warp's 32 of the 128 columns: d-half hf, 32-column half `set` of it; staged as [d-half][row][128 B],
+      // 16-byte chunks swizzled by row
+      {
+        const int c = set;
         uint32_t o[32];
         tmem_ld32(tmem + lane_base + cDQ + hf * 64 + c * 32, o);
         tc_wait_ld();
@@ -323,7 +348,7 @@ bwd_dq_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   __syncwarp();
   tc_fence_before();
   __syncthreads();
-  if (warp == 9) {
+  if (warp == kMmaWarp) {
     tc_fence_after();
     tmem_dealloc(tmem, kTmemCols);
   }

@@ -206,3 +206,38 @@ def test_golden_vectors():
         O, L1, _ = orc.sdpa(q, k, v, causal=True, **kw)
         assert np.allclose(O.numpy(), z[f"{name}_o"], atol=1e-12)
         assert np.allclose(L1.numpy(), z[f"{name}_lse"], atol=1e-12)
+
+
+def test_oracle_agrees_with_an_independent_implementation():
+    """The oracle restates the reference's formulas; nothing the reference ships can pin it (its CPU arithmetic lives
+    in MLX).  An independent implementation at least catches a typo: torch's own CPU scaled_dot_product_attention in
+    float64 (masks built here from the definition j <= i + S - N, j >= i + S - N - left) must give the same outputs,
+    and autograd through it the same gradients, for causal, windowed, GQA and cross-length cases."""
+    import torch.nn.functional as F
+
+    g = torch.Generator().manual_seed(7)
+    for (B, Hq, Hkv, N, S, causal, wl) in ((2, 4, 2, 33, 33, True, -1), (1, 6, 3, 20, 47, True, 9), (1, 2, 2, 40, 25, False, -1),
+                                           (2, 8, 1, 17, 64, True, 0)):
+        q = torch.randn((B, Hq, N, 32), generator=g, dtype=torch.float64)
+        k = torch.randn((B, Hkv, S, 32), generator=g, dtype=torch.float64)
+        v = torch.randn((B, Hkv, S, 32), generator=g, dtype=torch.float64)
+        do = torch.randn((B, Hq, N, 32), generator=g, dtype=torch.float64)
+        i = torch.arange(N).unsqueeze(1) + (S - N)
+        j = torch.arange(S).unsqueeze(0)
+        vis = torch.ones((N, S), dtype=torch.bool)
+        if causal:
+            vis &= j <= i
+        if wl >= 0:
+            vis &= j >= i - wl
+        rows_ok = vis.any(dim=1)
+        qg, kg, vg = (x.clone().requires_grad_(True) for x in (q, k, v))
+        rep = Hq // Hkv
+        ref = F.scaled_dot_product_attention(qg, kg.repeat_interleave(rep, 1), vg.repeat_interleave(rep, 1),
+                                             attn_mask=vis | ~rows_ok.unsqueeze(1))
+        ref = ref * rows_ok.view(1, 1, N, 1)                 # rows without a visible key: zero by this library's convention
+        O, _, _ = orc.sdpa(q, k, v, causal=causal, window_left=wl)
+        assert float((O - ref.detach()).abs().max()) < 1e-10
+        ref.backward(do)
+        dq, dk, dv = orc.backward(q, k, v, do, causal=causal, window_left=wl)
+        for a, b in ((dq, qg.grad), (dk, kg.grad), (dv, vg.grad)):
+            assert float((a - b).abs().max()) < 1e-9

@@ -49,6 +49,9 @@ extern "C" {
 
 /* flags */
 #define B200FA_FLAG_FORCE_MMA_SYNC  1  /* use the portable mma.sync kernels even where a tcgen05 kernel exists */
+#define B200FA_FLAG_FWD_PERSISTENT  8  /* tcgen05 forward: persistent CTAs (each walks many query tiles) whatever the shape */
+#define B200FA_FLAG_FWD_ONE_ITEM   16  /* tcgen05 forward: one query tile per CTA whatever the shape; without either flag the
+                                          launcher chooses (persistent for large packed-sequence launches) */
 #define B200FA_FLAG_PACKED_F32      4  /* b200fa_decode_paged: `out` is float [B*Hq*N][D+4], the normalised row in fp32 with
                                           its base-2 lse at column D (columns D+1..D+3 pad the row to 16 bytes); `lse` is
                                           ignored.  The per-GPU partial of a sequence whose pages are spread over several

@@ -20,6 +20,8 @@ ERR_DEVICE = -5
 F16, BF16, F32, I8, E4M3 = 0, 1, 2, 3, 4
 FLAG_FORCE_MMA_SYNC = 1
 FLAG_PACKED_F32 = 4
+FLAG_FWD_PERSISTENT = 8
+FLAG_FWD_ONE_ITEM = 16
 
 
 class Desc(C.Structure):

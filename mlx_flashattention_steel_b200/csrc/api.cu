@@ -105,6 +105,7 @@ int32_t fill_fwd_params(const b200fa_desc* d, const void* q, const void* k, cons
   p->bmask = d->block_mask;
   p->bm_bq = d->mask_bq; p->bm_bk = d->mask_bk; p->bm_nk = d->mask_nk;
   p->kv_lens = d->kv_lens;
+  p->persist_mode = (d->flags & B200FA_FLAG_FWD_PERSISTENT) ? 1 : ((d->flags & B200FA_FLAG_FWD_ONE_ITEM) ? 2 : 0);
   if (d->block_mask != nullptr) {
     if (d->mask_bq <= 0 || d->mask_bk <= 0 || static_cast<int64_t>(d->mask_nk) * d->mask_bk < d->S)
       return fail(B200FA_ERR_INVALID_ARG, "block_mask: block sizes must be positive and mask_nk * mask_bk cover S");

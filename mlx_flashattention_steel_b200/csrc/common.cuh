@@ -42,6 +42,7 @@ struct FwdParams {
   const int* kv_lens;
   const int* block_table;      // [B, max_blocks], -1 = no page; null = dense k / v
   int max_blocks, page_size, num_pages;
+  int persist_mode;            // tcgen05 forward: 0 = the launcher chooses, 1 = persistent CTAs, 2 = one item per CTA
 };
 
 // Backward parameter block.  Role of MFASteelBackwardParams

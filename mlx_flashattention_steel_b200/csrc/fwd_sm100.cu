@@ -66,6 +66,7 @@ enum Bar {
   BAR_PV_DONE = 7,           // +stage: P.V of a tile has completed -- O may be rescaled, the V stage is free again
   BAR_S_FULL = 9,            // +buffer: S of a tile is complete -- for the softmax warps, and the K stage is free again
   BAR_P_FULL = 11,           // +buffer
+  BAR_Q_FREE = 13,           // persistent CTAs: the item's last S MMAs have read Q -- the next item's Q may land
   BAR_O_STAGED = 14,         // count 4: the softmax warps have written their O rows to shared memory
   BAR_O_FINAL = 15,          // committed once, after the last P.V: O is complete
   BAR_COUNT = 16
@@ -74,6 +75,7 @@ enum Bar {
 struct Sm100Args {
   FwdParams p;
   int tma_store;             // dense layout: O leaves through shared memory and TMA stores
+  int gx, gy, total_items;   // persistent CTAs: items = (query tile, head, batch | sequence), query tile fastest
 };
 
 // max / min of 64 values as a 3-ary tree (depth 4) instead of a 63-deep dependent chain
@@ -152,7 +154,13 @@ template <int DT> __device__ __forceinline__ uint32_t pack16(float a, float b) {
 // FEAT adds the ALiBi bias and the block mask (reference: mlx_mfa/attention.py:1079-1216 flash_attention_sparse,
 // csrc/mfa_steel_fwd.cpp:230-262 the shader's per-tile mask test): a key tile is visited only if one of the mask
 // cells under it is set, and partially set tiles are masked by element.  The plain instantiation compiles none of it.
-template <int HD, int DT, bool FEAT>
+// PERSIST: the CTA stays on its SM and walks items i = blockIdx.x, blockIdx.x + gridDim.x, ... (a query tile of one
+// head each) instead of one item per CTA.  TMEM, the barriers and the rings live across items: every phase is counted
+// in tiles (g) or items (itn) since the CTA started, the producer requests the next item's Q as soon as the last S
+// MMAs of this one have read it and its K tiles as their stages free up, so set-up, launch gaps and load latency are
+// paid once per SM instead of once per query tile -- what shapes with few key tiles per query tile (a sliding
+// window, short packed sequences) spend a third of their time on otherwise.
+template <int HD, int DT, bool FEAT, bool PERSIST>
 __global__ void __launch_bounds__(kThreads, 2)
 fa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                     const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmO,
@@ -171,34 +179,43 @@ fa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   uint16_t* s_list = reinterpret_cast<uint16_t*>(smem + kSmemTiles + 256);     // FEAT only
   unsigned char* s_flag = reinterpret_cast<unsigned char*>(s_list + kMaxListTiles);
 
+  static_assert(!(FEAT && PERSIST), "the feature instantiation keeps per-CTA tile lists: one item per CTA");
   const FwdParams& p = a.p;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int head = blockIdx.y;
-  int batch = blockIdx.z;
-  const int kvh = head / p.gqa;
-  int N = p.N, S = p.S, q_begin = 0, k_begin = 0;
-  if (p.cu_q != nullptr) {
-    // packed varlen: blockIdx.z is the sequence; rows of the neighbouring sequences that a tile drags in
-    // are masked (keys) or simply not stored (queries)
-    q_begin = p.cu_q[batch];
-    N = p.cu_q[batch + 1] - q_begin;
-    k_begin = p.cu_k[batch];
-    S = p.cu_k[batch + 1] - k_begin;
-    batch = 0;
-  } else if (p.kv_lens != nullptr) {
-    S = min(max(p.kv_lens[batch], 0), p.S);            // this batch entry's own key count
-  }
+  // geometry of the current item; the lambdas below read these by reference
+  int head, batch, kvh, N, S, q_begin, k_begin, q0, off, kt_begin, kt_end, n_tiles;
+  auto item_geometry = [&](int xt, int h, int z, int gx) {
+    head = h;
+    batch = z;
+    kvh = head / p.gqa;
+    N = p.N; S = p.S; q_begin = 0; k_begin = 0;
+    if (p.cu_q != nullptr) {
+      // packed varlen: z is the sequence; rows of the neighbouring sequences that a tile drags in
+      // are masked (keys) or simply not stored (queries)
+      q_begin = p.cu_q[batch];
+      N = p.cu_q[batch + 1] - q_begin;
+      k_begin = p.cu_k[batch];
+      S = p.cu_k[batch + 1] - k_begin;
+      batch = 0;
+    } else if (p.kv_lens != nullptr) {
+      S = min(max(p.kv_lens[batch], 0), p.S);          // this batch entry's own key count
+    }
+    q0 = (gx - 1 - xt) * BM;
+    off = S - N;
+    int k_hi = S;
+    if (p.causal) k_hi = min(S, q0 + BM + off);
+    int k_lo = 0;
+    if (p.window_left >= 0) k_lo = max(0, q0 + off - p.window_left);
+    kt_begin = k_lo / BN;
+    kt_end = k_hi > 0 ? (k_hi + BN - 1) / BN : 0;
+    n_tiles = kt_end - kt_begin;
+  };
   const bool paged = p.block_table != nullptr;
-  const int q0 = (static_cast<int>(gridDim.x) - 1 - static_cast<int>(blockIdx.x)) * BM;
-  if (q0 >= N) return;
-  const int off = S - N;
-  int k_hi = S;
-  if (p.causal) k_hi = min(S, q0 + BM + off);
-  int k_lo = 0;
-  if (p.window_left >= 0) k_lo = max(0, q0 + off - p.window_left);
-  const int kt_begin = k_lo / BN;
-  const int kt_end = k_hi > 0 ? (k_hi + BN - 1) / BN : 0;
-  int n_tiles = kt_end - kt_begin;
+  if constexpr (!PERSIST) {
+    item_geometry(static_cast<int>(blockIdx.x), static_cast<int>(blockIdx.y), static_cast<int>(blockIdx.z),
+                  static_cast<int>(gridDim.x));
+    if (q0 >= N) return;
+  }
   const bool sparse = FEAT && p.bmask != nullptr;
   if constexpr (FEAT) {
     if (sparse) {
@@ -238,8 +255,8 @@ fa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
 
   auto bar = [&](int i) -> uint32_t { return smem_u32(&bars[i]); };
 
-  if (n_tiles <= 0) {
-    // no visible key for any row of this tile: O = 0, lse = -inf
+  // no visible key for any row of this tile: O = 0, lse = -inf
+  auto zero_rows = [&]() {
     if (warp < 4) {
       const int row = q0 + tid;
       if (row < N) {
@@ -250,7 +267,12 @@ fa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         if (p.lse != nullptr) p.lse[batch * p.lse_bs + head * p.lse_hs + q_begin + row] = -INFINITY;
       }
     }
-    return;
+  };
+  if constexpr (!PERSIST) {
+    if (n_tiles <= 0) {
+      zero_rows();
+      return;
+    }
   }
 
   // Paged pools: first pool token of each 16-token unit of the j-th tile (a page is page_size / 16 units).  Units
@@ -281,8 +303,8 @@ fa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   };
   // The producer thread sets up the barriers and starts the first loads (Q and as many K / V tiles as there are
   // stages, all of which are empty) before the CTA-wide sync, so TMEM allocation and the sync hide under them.
-  auto load_k = [&](int j, const UnitToks& u) {
-    const int st = j & 1;
+  // st: ring stage = parity of the tile's running count since the CTA started
+  auto load_k = [&](int j, int st, const UnitToks& u) {
     mbar_arrive_expect_tx(bar(BAR_K_FULL + st), kKVBytes);
     if (paged) {
       load_paged(sK + st * kKVBytes, &tmK, bar(BAR_K_FULL + st), u);
@@ -293,8 +315,7 @@ fa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       tma_load_4d(smem_u32(sK + st * kKVBytes + hf * (kKVBytes / kHalves)), &tmK, bar(BAR_K_FULL + st), 64 * hf,
                   k_begin + tile_of(j) * BN, kvh, batch);
   };
-  auto load_v = [&](int j, const UnitToks& u) {
-    const int st = j & 1;
+  auto load_v = [&](int j, int st, const UnitToks& u) {
     mbar_arrive_expect_tx(bar(BAR_V_FULL + st), kKVBytes);
     if (paged) {
       load_paged(sV + st * kKVBytes, &tmV, bar(BAR_V_FULL + st), u);
@@ -316,18 +337,21 @@ fa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     }
     mbar_init(bar(BAR_O_STAGED), 4);
     mbar_init(bar(BAR_O_FINAL), 1);
+    mbar_init(bar(BAR_Q_FREE), 1);
     *s_abort = 0;
     fence_barrier_init();
     fence_proxy_async();
-    mbar_arrive_expect_tx(bar(BAR_Q), kQBytes);
+    if constexpr (!PERSIST) {
+      mbar_arrive_expect_tx(bar(BAR_Q), kQBytes);
 #pragma unroll
-    for (int hf = 0; hf < kHalves; ++hf)
-      tma_load_4d(smem_u32(sQ + hf * (kQBytes / kHalves)), &tmQ, bar(BAR_Q), 64 * hf, q_begin + q0, head, batch);
-    for (int j = 0; j < kStages && j < n_tiles; ++j) {
-      UnitToks u = {};
-      if (paged) u = unit_toks(j);
-      load_k(j, u);
-      load_v(j, u);
+      for (int hf = 0; hf < kHalves; ++hf)
+        tma_load_4d(smem_u32(sQ + hf * (kQBytes / kHalves)), &tmQ, bar(BAR_Q), 64 * hf, q_begin + q0, head, batch);
+      for (int j = 0; j < kStages && j < n_tiles; ++j) {
+        UnitToks u = {};
+        if (paged) u = unit_toks(j);
+        load_k(j, j & 1, u);
+        load_v(j, j & 1, u);
+      }
     }
   }
   if (warp == 5) {
@@ -340,26 +364,70 @@ fa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   const uint32_t tmem = *s_tmem;
   const uint32_t tS0 = tmem, tO = tmem + 128;   // S buffers at +0 and +64, O (HD columns) at +128
 
+  // The O tile leaves through the V stages (free once the item's last P.V has completed) and a TMA store that the
+  // producer thread issues: it is the one that needs those stages next, and the softmax warps move on at once.
+  auto store_o = [&](uint32_t parity, int q0_, int head_, int batch_) {
+    if (mbar_wait_bounded(bar(BAR_O_STAGED), parity, s_abort)) {
+#pragma unroll
+      for (int hf = 0; hf < kHalves; ++hf)
+        tma_store_4d(&tmO, smem_u32(sV + hf * (kQBytes / kHalves)), 64 * hf, q0_, head_, batch_);
+      tma_store_commit();
+      tma_store_wait_read<0>();        // the copies have left shared memory; the kernel's end makes them visible
+    }
+  };
+
+  int g0 = 0, itn = 0;       // key tiles and items this CTA has been through: every barrier phase counts from them
+  int prev_q0 = 0, prev_head = 0, prev_batch = 0;
+  const int n_items = PERSIST ? a.total_items : 1;
+  for (int it = PERSIST ? static_cast<int>(blockIdx.x) : 0; it < n_items; it += PERSIST ? static_cast<int>(gridDim.x) : 1) {
+  if constexpr (PERSIST) {
+    item_geometry(it % a.gx, (it / a.gx) % a.gy, it / (a.gx * a.gy), a.gx);
+    if (q0 >= N) continue;
+    if (n_tiles <= 0) {
+      zero_rows();
+      continue;
+    }
+  }
+
   if (warp == 4) {
     // ============================ producer ============================
     if (lane == 0) {
+      bool okp = true;
+      if constexpr (PERSIST) {
+        // Q of this item may land once the previous item's S MMAs have read theirs
+        if (itn > 0) okp = mbar_wait_bounded(bar(BAR_Q_FREE), (itn - 1) & 1, s_abort);
+        if (okp) {
+          mbar_arrive_expect_tx(bar(BAR_Q), kQBytes);
+#pragma unroll
+          for (int hf = 0; hf < kHalves; ++hf)
+            tma_load_4d(smem_u32(sQ + hf * (kQBytes / kHalves)), &tmQ, bar(BAR_Q), 64 * hf, q_begin + q0, head, batch);
+        }
+      }
       // paged: the table entries of a tile are fetched one tile ahead, so that their latency passes under the wait
       // for the stage
+      constexpr int j_first = PERSIST ? 0 : kStages;     // one item per CTA: the first tiles were requested before the sync
       UnitToks u_next = {};
-      if (paged && kStages < n_tiles) u_next = unit_toks(kStages);
-      for (int j = kStages; j < n_tiles; ++j) {
-        const int st = j & 1;
-        const uint32_t par = ((j >> 1) & 1) ^ 1;
+      if (paged && j_first < n_tiles) u_next = unit_toks(j_first);
+      for (int j = j_first; j < n_tiles && okp; ++j) {
+        const int g = g0 + j, st = g & 1;
+        const uint32_t par = ((g >> 1) & 1) ^ 1;
         const UnitToks u = u_next;
         if (paged && j + 1 < n_tiles) u_next = unit_toks(j + 1);
-        // K(j) and V(j) reuse the stage of tile j-2: wait until its S MMAs, then its PV MMAs, have read it.  These
+        // K(g) and V(g) reuse the stage of tile g-2: wait until its S MMAs, then its PV MMAs, have read it.  These
         // are the barriers the softmax warps wait on too: every commit costs the MMA thread a bubble, so one commit
-        // serves both readers.  Neither can be more than one completion ahead of this thread: S(j) needs K(j) and
-        // P.V(j) needs V(j), which are loaded below.
-        if (!mbar_wait_bounded(bar(BAR_S_FULL + st), par, s_abort)) break;
-        load_k(j, u);
-        if (!mbar_wait_bounded(bar(BAR_PV_DONE + st), par, s_abort)) break;
-        load_v(j, u);
+        // serves both readers.  Neither can be more than one completion ahead of this thread: S(g) needs K(g) and
+        // P.V(g) needs V(g), which are loaded below.
+        if (g >= kStages && !mbar_wait_bounded(bar(BAR_S_FULL + st), par, s_abort)) break;
+        load_k(j, st, u);
+        if (g >= kStages && !mbar_wait_bounded(bar(BAR_PV_DONE + st), par, s_abort)) break;
+        if constexpr (PERSIST) {
+          // the V stages hold the previous item's staged O tile until its store has read them
+          if (j == 0 && itn > 0 && a.tma_store) store_o((itn - 1) & 1, prev_q0, prev_head, prev_batch);
+        }
+        load_v(j, st, u);
+      }
+      if constexpr (!PERSIST) {
+        if (a.tma_store) store_o(0, q0, head, batch);
       }
     }
   } else if (warp == 5) {
@@ -373,10 +441,10 @@ fa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       const uint64_t kd0 = smem_desc(smem_u32(sK), 16, 1024);
       const uint64_t vd0 = smem_desc(smem_u32(sV), kKVBytes / kHalves, 1024);
       constexpr uint64_t kHalfQ = (kQBytes / kHalves) >> 4, kHalfK = (kKVBytes / kHalves) >> 4, kStageKV = kKVBytes >> 4;
-      bool ok = mbar_wait_bounded(bar(BAR_Q), 0, s_abort);
+      bool ok = mbar_wait_bounded(bar(BAR_Q), itn & 1, s_abort);
       auto issue_s = [&](int j) -> bool {
-        const int st = j & 1;
-        if (!mbar_wait_bounded(bar(BAR_K_FULL + st), (j >> 1) & 1, s_abort)) return false;
+        const int g = g0 + j, st = g & 1;
+        if (!mbar_wait_bounded(bar(BAR_K_FULL + st), (g >> 1) & 1, s_abort)) return false;
         tc_fence_after();
         const uint64_t kd = kd0 + static_cast<uint64_t>(st) * kStageKV;
         const uint32_t d_tmem = tS0 + st * 64;
@@ -387,18 +455,21 @@ fa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
                  k > 0 ? 1u : 0u);
         }
         tc_commit(bar(BAR_S_FULL + st));        // for the softmax warps and for the producer
+        if constexpr (PERSIST) {
+          if (j + 1 == n_tiles) tc_commit(bar(BAR_Q_FREE));   // nothing of this item reads Q any more
+        }
         return true;
       };
       if (ok) ok = issue_s(0);
       for (int j = 0; j < n_tiles && ok; ++j) {
-        const int st = j & 1;
+        const int g = g0 + j, st = g & 1;
         if (j + 1 < n_tiles) {
           ok = issue_s(j + 1);
           if (!ok) break;
         }
         // V landed long ago; wait for it first so that nothing but the MMA issue follows the arrival of P
-        if (!mbar_wait_bounded(bar(BAR_V_FULL + st), (j >> 1) & 1, s_abort)) { ok = false; break; }
-        if (!mbar_wait_bounded(bar(BAR_P_FULL + st), (j >> 1) & 1, s_abort)) { ok = false; break; }
+        if (!mbar_wait_bounded(bar(BAR_V_FULL + st), (g >> 1) & 1, s_abort)) { ok = false; break; }
+        if (!mbar_wait_bounded(bar(BAR_P_FULL + st), (g >> 1) & 1, s_abort)) { ok = false; break; }
         tc_fence_after();
         const uint64_t vd = vd0 + static_cast<uint64_t>(st) * kStageKV;
         const uint32_t a_tmem = tS0 + st * 64;
@@ -455,9 +526,9 @@ fa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     }
 
     for (int j = 0; j < n_tiles; ++j) {
-      const int st = j & 1;
+      const int g = g0 + j, st = g & 1;
       const int k0 = tile_of(j) * BN;
-      if (!__all_sync(0xffffffffu, mbar_wait_bounded(bar(BAR_S_FULL + st), (j >> 1) & 1, s_abort))) { ok = false; break; }
+      if (!__all_sync(0xffffffffu, mbar_wait_bounded(bar(BAR_S_FULL + st), (g >> 1) & 1, s_abort))) { ok = false; break; }
       tc_fence_after();
       uint32_t r0[32], r1[32];
       tmem_ld32(tS0 + lane_base + st * 64, r0);
@@ -589,7 +660,7 @@ fa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         if (j > 0) {
           // O is being accumulated by PV(j-1): wait for it, then scale this row in TMEM
           // P.V(j-1): completion (j-1)>>1 of its stage's barrier; the next one there needs this tile's successor's P
-          if (!__all_sync(0xffffffffu, mbar_wait_bounded(bar(BAR_PV_DONE + ((j - 1) & 1)), ((j - 1) >> 1) & 1, s_abort))) { ok = false; break; }
+          if (!__all_sync(0xffffffffu, mbar_wait_bounded(bar(BAR_PV_DONE + ((g - 1) & 1)), ((g - 1) >> 1) & 1, s_abort))) { ok = false; break; }
           tc_fence_after();
 #pragma unroll
           for (int c = 0; c < HD / 32; ++c) {
@@ -692,12 +763,12 @@ fa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     // cannot alias: PV_DONE would not do here, because a warp may reach this point two completions ahead of it
     // (S(n-1) complete only implies PV(n-3)) or after both have happened, and a parity wait is only sound within one
     // phase of the barrier.
-    if (ok) ok = __all_sync(0xffffffffu, mbar_wait_bounded(bar(BAR_O_FINAL), 0, s_abort));
+    if (ok) ok = __all_sync(0xffffffffu, mbar_wait_bounded(bar(BAR_O_FINAL), itn & 1, s_abort));
     if (ok) {
       tc_fence_after();
       const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
       if (a.tma_store) {
-        // Stage the tile in the Q buffer (free: every S MMA has completed) as two 64-wide 128B-swizzled halves and
+        // Stage the tile in the V stages (free: every P.V has completed) as two 64-wide 128B-swizzled halves and
         // let TMA write it: full-line stores instead of 32 rows x 16 bytes per instruction; rows beyond N are
         // clipped by the tensor map.
         const int r = tid;
@@ -714,20 +785,13 @@ fa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
             v.z = pack16<DT>(__uint_as_float(o[i + 4]) * inv, __uint_as_float(o[i + 5]) * inv);
             v.w = pack16<DT>(__uint_as_float(o[i + 6]) * inv, __uint_as_float(o[i + 7]) * inv);
             const int chunk = c * 4 + (i >> 3);              // 16-byte chunk of the row: half = chunk / 8
-            unsigned char* dst = sQ + (chunk >> 3) * (kQBytes / kHalves) + r * 128 + (((chunk & 7) ^ (r & 7)) << 4);
+            unsigned char* dst = sV + (chunk >> 3) * (kQBytes / kHalves) + r * 128 + (((chunk & 7) ^ (r & 7)) << 4);
             *reinterpret_cast<uint4*>(dst) = v;
           }
         }
         fence_proxy_async();
         __syncwarp();
-        if (lane == 0) mbar_arrive(bar(BAR_O_STAGED));
-        if (tid == 0 && mbar_wait_bounded(bar(BAR_O_STAGED), 0, s_abort)) {
-#pragma unroll
-          for (int hf = 0; hf < kHalves; ++hf)
-            tma_store_4d(&tmO, smem_u32(sQ + hf * (kQBytes / kHalves)), 64 * hf, q0, head, batch);
-          tma_store_commit();
-          tma_store_wait<0>();
-        }
+        if (lane == 0) mbar_arrive(bar(BAR_O_STAGED));          // the producer thread issues the store
       } else {
         uint16_t* orow = reinterpret_cast<uint16_t*>(p.o) + batch * p.o_bs + head * p.o_hs +
                          static_cast<int64_t>(q_begin + row) * p.o_rs;
@@ -752,6 +816,17 @@ fa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       if (p.lse != nullptr && row < N)
         p.lse[batch * p.lse_bs + head * p.lse_hs + q_begin + row] = l_run > 0.f ? m_used + log2f(l_run) : -INFINITY;
     }
+  }
+
+  prev_q0 = q0; prev_head = head; prev_batch = batch;
+  g0 += n_tiles;
+  ++itn;
+  if (*s_abort != 0) break;
+  }  // items
+
+  if constexpr (PERSIST) {
+    // the last item's O tile
+    if (warp == 4 && lane == 0 && itn > 0 && a.tma_store && *s_abort == 0) store_o((itn - 1) & 1, prev_q0, prev_head, prev_batch);
   }
 
   // ---- teardown: everyone meets, then the allocating warp frees TMEM ----
@@ -800,6 +875,18 @@ bool fwd_sm100_supported(const FwdParams& p, int dtype, int D) {
   return get_encode_tiled() != nullptr;
 }
 
+// Persistent CTAs pay off where set-up, launch gaps and the first loads' latency are a visible part of a CTA's life
+// and the items are many and short: packed sequences (config 5's forward: 0.889 -> 0.837 ms; ten unmasked key tiles per
+// query tile: +6 %).  They do not for a sliding window (config 3: -2.5 %: its query tiles are bounded by the fill and
+// drain of the S -> softmax -> P.V pipeline, which a persistent CTA pays per item just the same) and they lose where
+// items are long and uneven (config 2: 2.23 -> 2.74 ms with the static deal), which keep one CTA per item and the
+// hardware scheduler's balancing.  `mode`: 0 = choose, 1 = persistent, 2 = one item per CTA (descriptor flags).
+static bool want_persistent(const FwdParams& p, int nbatch, int max_q, int sm_count, int mode) {
+  if (mode != 0) return mode == 1;
+  const long long items = static_cast<long long>((max_q + BM - 1) / BM) * p.Hq * nbatch;
+  return p.cu_q != nullptr && p.window_left < 0 && items >= 8LL * 2 * sm_count && max_q <= 64 * BM;
+}
+
 template <int HD, int DT, bool FEAT>
 static cudaError_t launch_hd(const FwdParams& p, int nbatch, int max_q, cudaStream_t stream) {
   constexpr int dtype = DT;
@@ -828,11 +915,29 @@ static cudaError_t launch_hd(const FwdParams& p, int nbatch, int max_q, cudaStre
   a.tma_store = (p.cu_q == nullptr && make_map(&tmO, dtype, p.o, HD, p.N, p.Hq, p.B, p.o_rs, o_hs, o_bs, BM)) ? 1 : 0;
   if (!a.tma_store) tmO = tmQ;
   constexpr int smem_bytes = FEAT ? Cfg<HD>::kSmemBytesFeat : Cfg<HD>::kSmemBytes;
-  cudaError_t e = cudaFuncSetAttribute(fa_fwd_sm100_kernel<HD, DT, FEAT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+  dim3 grid((max_q + BM - 1) / BM, p.Hq, nbatch);
+  a.gx = static_cast<int>(grid.x);
+  a.gy = static_cast<int>(grid.y);
+  const long long items = static_cast<long long>(grid.x) * grid.y * grid.z;
+  a.total_items = static_cast<int>(items < 0x7fffffffLL ? items : 0x7fffffffLL);
+  if constexpr (!FEAT) {
+    int dev = 0, sm_count = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess ||
+        sm_count <= 0)
+      sm_count = 148;
+    if (items < 0x7fffffffLL && want_persistent(p, nbatch, max_q, sm_count, a.p.persist_mode)) {
+      cudaError_t e = cudaFuncSetAttribute(fa_fwd_sm100_kernel<HD, DT, false, true>,
+                                           cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
+      if (e != cudaSuccess) return e;
+      const int ctas = static_cast<int>(items < 2LL * sm_count ? items : 2LL * sm_count);     // two CTAs per SM
+      fa_fwd_sm100_kernel<HD, DT, false, true><<<ctas, kThreads, smem_bytes, stream>>>(tmQ, tmK, tmV, tmO, a);
+      return cudaGetLastError();
+    }
+  }
+  cudaError_t e = cudaFuncSetAttribute(fa_fwd_sm100_kernel<HD, DT, FEAT, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        smem_bytes);
   if (e != cudaSuccess) return e;
-  dim3 grid((max_q + BM - 1) / BM, p.Hq, nbatch);
-  fa_fwd_sm100_kernel<HD, DT, FEAT><<<grid, kThreads, smem_bytes, stream>>>(tmQ, tmK, tmV, tmO, a);
+  fa_fwd_sm100_kernel<HD, DT, FEAT, false><<<grid, kThreads, smem_bytes, stream>>>(tmQ, tmK, tmV, tmO, a);
   return cudaGetLastError();
 }
 

@@ -410,7 +410,8 @@ def flash_attention_varlen(
     q, k, v ``[1, H, total_tokens, D]``; ``cu_seqlens_*`` int32 ``[num_seqs + 1]``
     cumulative lengths; sequences attend only to themselves; ``causal`` is applied
     per sequence.  Returns ``[1, H, total_q, D]``.  ``num_seqs == 0`` returns ``q``
-    (mlx_mfa/attention.py:2444-2445).  ``block_mask`` raises NotImplementedError.
+    (mlx_mfa/attention.py:2444-2445).  ``block_mask`` (one block mask valid for every sequence) goes through a
+    per-sequence split, as in the reference.
     """
     q, k, v = _as_tensor(q, "q"), _as_tensor(k, "k"), _as_tensor(v, "v")
     if q.ndim != 4 or k.ndim != 4 or v.ndim != 4:
@@ -422,12 +423,19 @@ def flash_attention_varlen(
     nseq = cu_q.numel() - 1
     if nseq <= 0:
         return q
-    if block_mask is not None:
-        raise NotImplementedError("flash_attention_varlen: block_mask (block-sparse) is not built.")
     if q.shape[0] != 1 or k.shape[0] != 1 or v.shape[0] != 1:
         raise ValueError("flash_attention_varlen expects packed tensors with batch size 1.")
     if cu_k.numel() != cu_q.numel():
         raise ValueError("cu_seqlens_q and cu_seqlens_k must have the same length.")
+    if block_mask is not None:
+        # The mask has to fit every sequence by itself, so the reference takes it through a per-sequence split and
+        # concatenation of flash_attention_sparse calls (mlx_mfa/attention.py:2365-2390, 2448-2453); so does this.
+        from .sparse import flash_attention_sparse
+
+        cq, ck = [int(x) for x in cu_q.tolist()], [int(x) for x in cu_k.tolist()]
+        outs = [flash_attention_sparse(q[:, :, cq[i]:cq[i + 1]], k[:, :, ck[i]:ck[i + 1]], v[:, :, ck[i]:ck[i + 1]],
+                                       block_mask, scale=scale, causal=causal, stream=stream) for i in range(nseq)]
+        return torch.cat(outs, dim=2)
     D = q.shape[-1]
     if k.shape[-1] != D or v.shape[-1] != D:
         raise ValueError("q, k, v must have the same head_dim.")

@@ -579,10 +579,13 @@ fa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
             ax = fmaxf(xmax, -tree_min64(x));
           }
           const float ay = ax * cap_in;
-          if (DT == 1) {
-            if (__any_sync(0xffffffffu, 2.f * cap_out * ay > 96.f)) xmax = tree_max64(x);
-          }
-          const unsigned lvl = __reduce_max_sync(0xffffffffu, ay <= y_deg3 ? 0u : (ay <= y_deg5 ? 1u : (ay <= y_deg7 ? 2u : 3u)));
+          // one warp-wide OR carries both answers: the highest polynomial level any row needs (one-hot in bits 0-3) and
+          // whether any row's bound leaves the exponent range (bit 4)
+          const unsigned code = (ay <= y_deg3 ? 1u : (ay <= y_deg5 ? 2u : (ay <= y_deg7 ? 4u : 8u))) |
+                                ((DT == 1 && 2.f * cap_out * ay > 96.f) ? 16u : 0u);
+          const unsigned all = __reduce_or_sync(0xffffffffu, code);
+          const unsigned lvl = (all & 8u) ? 3u : ((all & 4u) ? 2u : ((all & 2u) ? 1u : 0u));
+          if (DT == 1 && (all & 16u)) xmax = tree_max64(x);
           if (lvl < 3u) {
             mode = 1;
             deg = lvl;

@@ -114,3 +114,26 @@ def test_sparse_backward(dev, dtype, D):
     assert_close_grad(kg.grad, kr.grad, dtype, "dK")
     assert_close_grad(vg.grad, vr.grad, dtype, "dV")
     assert float(qg.grad[:, :, 3 * BQ:4 * BQ].abs().max()) == 0.0      # rows with no active cell get no gradient
+
+
+@pytest.mark.gpu
+def test_varlen_with_a_block_mask(dev):
+    """flash_attention_varlen(block_mask=...): one mask that fits every sequence, applied per sequence -- the
+    reference's split / concatenate route (mlx_mfa/attention.py:2365-2390, 2448-2453).  Sequences of 100 and 128
+    tokens share the [4, 8] cell grid of head_dim 128; forward and gradients against the oracle per sequence."""
+    D, dtype = 128, torch.bfloat16
+    BQ, BK = _steel_block_config(D)
+    lens = [100, 128, 97]
+    cu = [0, 100, 228, 325]
+    mask = _random_mask(4, 8, 970, density=0.5)
+    q, k, v, do = (randn((1, 4, 325, D), dtype, 971 + i) for i in range(4))
+    k, v = k[:, :2].contiguous(), v[:, :2].contiguous()
+    cu_t = torch.tensor(cu, dtype=torch.int32, device=dev)
+    qg, kg, vg = (x.to(dev).requires_grad_(True) for x in (q, k, v))
+    out = fa.flash_attention_varlen(qg, kg, vg, cu_t, cu_t, 128, 128, causal=True, block_mask=mask.to(dev))
+    out.backward(do.to(dev))
+    for i, n in enumerate(lens):
+        sl = slice(cu[i], cu[i + 1])
+        O, _, _ = orc.sdpa(q[:, :, sl], k[:, :, sl], v[:, :, sl], causal=True, block_mask=mask, block=(BQ, BK))
+        assert_close(out[:, :, sl], O, dtype)
+    assert qg.grad.shape == q.shape and torch.isfinite(qg.grad.float()).all() and torch.isfinite(kg.grad.float()).all()

@@ -517,6 +517,43 @@ def bench_extras(device, pk):
     return out
 
 
+def profile_case(name, device, steps, warmup):
+    """Profiling aids (not bench values): small cases of the other kernels, sized for an ncu capture -- inputs larger
+    than L2, well under a GB on the device, a few launches."""
+    import numpy as np
+
+    import mlx_flashattention_steel_b200 as fa
+    from mlx_flashattention_steel_b200 import attention as fa_attn
+
+    gd = torch.Generator(device=device).manual_seed(21)
+    mk = lambda shape, dt: torch.randn(shape, generator=gd, device=device).to(dt)
+    if name == "c3":          # config 3 reduced: B=1, H=2, N=S=32768, fp16, causal, window (512, 0)
+        q, k, v = (mk((1, 2, 32768, 128), torch.float16) for _ in range(3))
+        fn = lambda: fa.flash_attention(q, k, v, causal=True, window_size=(512, 0))
+    elif name == "c5":        # config 5 reduced: 16384 packed tokens, lengths ~ U[128, 4096], H=16, D=64, bf16, fwd + bwd
+        rng = np.random.default_rng(5)
+        lens = []
+        while sum(lens) < 16384:
+            lens.append(int(rng.integers(128, 4097)))
+        lens[-1] -= sum(lens) - 16384
+        cu = torch.tensor([0] + list(np.cumsum(lens)), dtype=torch.int32, device=device)
+        q, k, v, do = (mk((1, 16, 16384, 64), torch.bfloat16) for _ in range(4))
+
+        def fn():
+            qg, kg, vg = (x.detach().requires_grad_(True) for x in (q, k, v))
+            fa.flash_attention_varlen(qg, kg, vg, cu, cu, max(lens), max(lens), causal=True).backward(do)
+    elif name == "bwd128":    # config 2's shape reduced: B=2, Hq=16, Hkv=4, N=S=8192, bf16, causal, backward only
+        q, k, v, do = mk((2, 16, 8192, 128), torch.bfloat16), mk((2, 4, 8192, 128), torch.bfloat16), \
+            mk((2, 4, 8192, 128), torch.bfloat16), mk((2, 16, 8192, 128), torch.bfloat16)
+        o_, l_ = fa_attn._fwd_raw(q, k, v, 128 ** -0.5, True, 0.0, -1, True, None)
+        fn = lambda: fa_attn._bwd_raw(q, k, v, o_, l_, do, 128 ** -0.5, True, None)
+    else:
+        raise SystemExit(f"unknown --case {name}")
+    ms = _time_ms(fn, steps, warmup)
+    print(json.dumps({"note": f"--case {name}: profiling case, not a bench value", "ms_per_step": ms,
+                      "kernel_status": int(fa.kernel_status())}), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -527,6 +564,8 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-extras", action="store_true", help="skip configs 1, 3 and 5")
     ap.add_argument("--small", action="store_true", help="profiling aid: N=S=4096, B=2 (not a bench value)")
+    ap.add_argument("--case", default="", choices=["", "c3", "c5", "bwd128"],
+                    help="profiling aid: run one small case of another kernel and exit (not a bench value)")
     ap.add_argument("--only-decode", type=int, default=0, metavar="B",
                     help="profiling aid: run only the decode measurement with batch B (not a bench value)")
     args = ap.parse_args()
@@ -554,6 +593,9 @@ def main():
     pk = peaks()
     if args.only_decode:
         print(json.dumps(bench_decode(device, args.steps, args.warmup, pk, batch=args.only_decode)), flush=True)
+        return
+    if args.case:
+        profile_case(args.case, device, args.steps, args.warmup)
         return
     cfg = dict(C2)
     if args.small:

@@ -168,9 +168,9 @@ __device__ __forceinline__ float fast_tanh(float x) {
 }
 // tanh of the soft cap.  tanh.approx is specified to a relative error of 2^-11; multiplied by cap * log2(e) that is
 // an absolute error of the capped score, negligible for the caps models use (30, 50) and above the 2e-2 parity bar
-// from cap ~ 70 on.  Larger caps therefore take 1 - 2 / (2^(2 y log2 e) + 1): two special-function operations,
+// from cap ~ 70 on.  Caps of 64 and more therefore take 1 - 2 / (2^(2 y log2 e) + 1): two special-function operations,
 // absolute error ~1e-7 (saturates cleanly: 2^x = inf gives 1, 2^x = 0 gives -1).
-constexpr float kPreciseTanhMinCap = 70.f;
+constexpr float kPreciseTanhMinCap = 64.f;
 __device__ __forceinline__ float tanh_exp(float y) {
   const float e = fast_exp2(y * (2.f * kLog2e));
   return 1.f - __fdividef(2.f, e + 1.f);

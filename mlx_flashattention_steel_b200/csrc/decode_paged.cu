@@ -196,7 +196,9 @@ __device__ __forceinline__ int cta_of_unit(long long u, int G, long long U) {
 // ---------------------------------------------------------------------------
 // main kernel
 // ---------------------------------------------------------------------------
-template <int KV, int HPC, int kD>
+// CAP: soft cap on.  A template parameter so that the common launch without one carries no tanh code in its unrolled
+// inner loops (with it compiled in, config 4 -- which has no soft cap -- ran 4 % slower).
+template <int KV, int HPC, int kD, bool CAP>
 __global__ void __launch_bounds__((HPC + 1) * 32, 1)
 decode_paged_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
                     const KernelArgs a) {
@@ -553,7 +555,7 @@ decode_paged_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_consta
           } else {
             s *= a.q_prescale;
           }
-          if (a.inv_cap > 0.f) s = a.cap_log2 * cap_tanh(s * a.inv_cap, a.inv_cap * kPreciseTanhMinCap <= 1.f);
+          if constexpr (CAP) s = a.cap_log2 * cap_tanh(s * a.inv_cap, a.inv_cap * kPreciseTanhMinCap <= 1.f);
           const int tg = tok0 + tok;
           sc[q][e] = (pg[q] != -2 && tg < len && tg <= causal_lim) ? s : -INFINITY;
           if (tg >= len) vsc[q][e] = 0.f;               // whatever the slot's scale holds (it may be a NaN pattern)
@@ -861,12 +863,14 @@ int pick_grid_x(int Hkv, int num_splits) {
 template <int KV, int HPC, int D>
 cudaError_t launch_t(const CUtensorMap& tmK, const CUtensorMap& tmV, const KernelArgs& a, int gx, size_t smem,
                      cudaStream_t stream) {
-  auto kern = decode_paged_kernel<KV, HPC, D>;
-  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
-  if (e != cudaSuccess) return e;
   dim3 grid(gx, a.HG);
-  kern<<<grid, (HPC + 1) * 32, smem, stream>>>(tmK, tmV, a);
-  return cudaGetLastError();
+  auto go = [&](auto kern) -> cudaError_t {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+    if (e != cudaSuccess) return e;
+    kern<<<grid, (HPC + 1) * 32, smem, stream>>>(tmK, tmV, a);
+    return cudaGetLastError();
+  };
+  return a.inv_cap > 0.f ? go(decode_paged_kernel<KV, HPC, D, true>) : go(decode_paged_kernel<KV, HPC, D, false>);
 }
 
 template <int KV, int D>

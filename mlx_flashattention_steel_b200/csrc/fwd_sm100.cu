@@ -160,7 +160,10 @@ template <int DT> __device__ __forceinline__ uint32_t pack16(float a, float b) {
 // MMAs of this one have read it and its K tiles as their stages free up, so set-up, launch gaps and load latency are
 // paid once per SM instead of once per query tile -- what shapes with few key tiles per query tile (a sliding
 // window, short packed sequences) spend a third of their time on otherwise.
-template <int HD, int DT, bool FEAT, bool PERSIST>
+// BIGCAP: soft caps of kPreciseTanhMinCap (64) and more.  Only they can push the bf16 path's upper bound of the row
+// max out of the exponent range, and only for them is tanh.approx too coarse; the guard and the two-operation tanh are
+// compiled into this instantiation alone, so the common caps (30, 50) keep the lean loop.
+template <int HD, int DT, bool FEAT, bool PERSIST, bool BIGCAP>
 __global__ void __launch_bounds__(kThreads, 2)
 fa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                     const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmO,
@@ -364,8 +367,9 @@ fa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   const uint32_t tmem = *s_tmem;
   const uint32_t tS0 = tmem, tO = tmem + 128;   // S buffers at +0 and +64, O (HD columns) at +128
 
-  // The O tile leaves through the V stages (free once the item's last P.V has completed) and a TMA store that the
-  // producer thread issues: it is the one that needs those stages next, and the softmax warps move on at once.
+  // Persistent CTAs: the O tile leaves through the V stages (free once the item's last P.V has completed) and a TMA
+  // store that the producer thread issues: it is the one that needs those stages next, and the softmax warps move on at
+  // once.  One item per CTA: through the Q buffer, stored by the first softmax thread.
   auto store_o = [&](uint32_t parity, int q0_, int head_, int batch_) {
     if (mbar_wait_bounded(bar(BAR_O_STAGED), parity, s_abort)) {
 #pragma unroll
@@ -425,9 +429,6 @@ fa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
           if (j == 0 && itn > 0 && a.tma_store) store_o((itn - 1) & 1, prev_q0, prev_head, prev_batch);
         }
         load_v(j, st, u);
-      }
-      if constexpr (!PERSIST) {
-        if (a.tma_store) store_o(0, q0, head, batch);
       }
     }
   } else if (warp == 5) {
@@ -501,8 +502,8 @@ fa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     const float y_deg3 = use_cap ? fminf(0.5f, powf(1e-3f * 7.5f / p.softcap, 0.2f)) : 0.f;
     const float y_deg5 = use_cap ? fminf(0.5f, powf(1e-3f * (315.f / 17.f) / p.softcap, 1.f / 7.f)) : 0.f;
     // ... and the degree-7 one within 2e-3 / cap (0.497 at cap 50); beyond it tanh itself is evaluated
-    const float y_deg7 = use_cap ? fminf(0.5f, powf(2e-3f * (2835.f / 62.f) / p.softcap, 1.f / 9.f)) : 0.f;
-    const bool precise_tanh = p.softcap >= kPreciseTanhMinCap;
+    const float y_deg7 = BIGCAP ? fminf(0.5f, powf(2e-3f * (2835.f / 62.f) / p.softcap, 1.f / 9.f)) : 0.5f;
+    constexpr bool precise_tanh = BIGCAP;
     const bool monotone = p.scale > 0.f;              // lets the row max be taken on the raw dot products
     const float alibi_l2 = (FEAT && p.alibi != nullptr) ? p.alibi[head] * kLog2e : 0.f;
 
@@ -581,11 +582,17 @@ fa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
           const float ay = ax * cap_in;
           // one warp-wide OR carries both answers: the highest polynomial level any row needs (one-hot in bits 0-3) and
           // whether any row's bound leaves the exponent range (bit 4)
-          const unsigned code = (ay <= y_deg3 ? 1u : (ay <= y_deg5 ? 2u : (ay <= y_deg7 ? 4u : 8u))) |
-                                ((DT == 1 && 2.f * cap_out * ay > 96.f) ? 16u : 0u);
-          const unsigned all = __reduce_or_sync(0xffffffffu, code);
-          const unsigned lvl = (all & 8u) ? 3u : ((all & 4u) ? 2u : ((all & 2u) ? 1u : 0u));
-          if (DT == 1 && (all & 16u)) xmax = tree_max64(x);
+          unsigned lvl;
+          if constexpr (BIGCAP) {
+            const unsigned code = (ay <= y_deg3 ? 1u : (ay <= y_deg5 ? 2u : (ay <= y_deg7 ? 4u : 8u))) |
+                                  ((DT == 1 && 2.f * cap_out * ay > 96.f) ? 16u : 0u);
+            const unsigned all = __reduce_or_sync(0xffffffffu, code);
+            lvl = (all & 8u) ? 3u : ((all & 4u) ? 2u : ((all & 2u) ? 1u : 0u));
+            if (DT == 1 && (all & 16u)) xmax = tree_max64(x);
+          } else {
+            // caps below 64: the bound is at most 2 * 64 * log2(e) * 0.5 = 92 binades above the row max, inside the range
+            lvl = __reduce_max_sync(0xffffffffu, ay <= y_deg3 ? 0u : (ay <= y_deg5 ? 1u : (ay <= y_deg7 ? 2u : 3u)));
+          }
           if (lvl < 3u) {
             mode = 1;
             deg = lvl;
@@ -771,9 +778,11 @@ fa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       tc_fence_after();
       const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
       if (a.tma_store) {
-        // Stage the tile in the V stages (free: every P.V has completed) as two 64-wide 128B-swizzled halves and
+        // Stage the tile in the Q buffer (free: every S MMA has completed; persistent CTAs, whose next Q may already
+        // be landing there, use the V stages: every P.V has completed) as two 64-wide 128B-swizzled halves and
         // let TMA write it: full-line stores instead of 32 rows x 16 bytes per instruction; rows beyond N are
         // clipped by the tensor map.
+        unsigned char* stage = PERSIST ? sV : sQ;
         const int r = tid;
 #pragma unroll
         for (int c = 0; c < HD / 32; ++c) {
@@ -788,13 +797,22 @@ fa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
             v.z = pack16<DT>(__uint_as_float(o[i + 4]) * inv, __uint_as_float(o[i + 5]) * inv);
             v.w = pack16<DT>(__uint_as_float(o[i + 6]) * inv, __uint_as_float(o[i + 7]) * inv);
             const int chunk = c * 4 + (i >> 3);              // 16-byte chunk of the row: half = chunk / 8
-            unsigned char* dst = sV + (chunk >> 3) * (kQBytes / kHalves) + r * 128 + (((chunk & 7) ^ (r & 7)) << 4);
+            unsigned char* dst = stage + (chunk >> 3) * (kQBytes / kHalves) + r * 128 + (((chunk & 7) ^ (r & 7)) << 4);
             *reinterpret_cast<uint4*>(dst) = v;
           }
         }
         fence_proxy_async();
         __syncwarp();
-        if (lane == 0) mbar_arrive(bar(BAR_O_STAGED));          // the producer thread issues the store
+        if (lane == 0) mbar_arrive(bar(BAR_O_STAGED));          // persistent CTAs: the producer thread issues the store
+        if constexpr (!PERSIST) {
+          if (tid == 0 && mbar_wait_bounded(bar(BAR_O_STAGED), 0, s_abort)) {
+#pragma unroll
+            for (int hf = 0; hf < kHalves; ++hf)
+              tma_store_4d(&tmO, smem_u32(sQ + hf * (kQBytes / kHalves)), 64 * hf, q0, head, batch);
+            tma_store_commit();
+            tma_store_wait<0>();
+          }
+        }
       } else {
         uint16_t* orow = reinterpret_cast<uint16_t*>(p.o) + batch * p.o_bs + head * p.o_hs +
                          static_cast<int64_t>(q_begin + row) * p.o_rs;
@@ -921,6 +939,7 @@ static cudaError_t launch_hd(const FwdParams& p, int nbatch, int max_q, cudaStre
   dim3 grid((max_q + BM - 1) / BM, p.Hq, nbatch);
   a.gx = static_cast<int>(grid.x);
   a.gy = static_cast<int>(grid.y);
+  const bool bigcap = p.softcap >= kPreciseTanhMinCap;
   const long long items = static_cast<long long>(grid.x) * grid.y * grid.z;
   a.total_items = static_cast<int>(items < 0x7fffffffLL ? items : 0x7fffffffLL);
   if constexpr (!FEAT) {
@@ -929,19 +948,25 @@ static cudaError_t launch_hd(const FwdParams& p, int nbatch, int max_q, cudaStre
         sm_count <= 0)
       sm_count = 148;
     if (items < 0x7fffffffLL && want_persistent(p, nbatch, max_q, sm_count, a.p.persist_mode)) {
-      cudaError_t e = cudaFuncSetAttribute(fa_fwd_sm100_kernel<HD, DT, false, true>,
-                                           cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
-      if (e != cudaSuccess) return e;
       const int ctas = static_cast<int>(items < 2LL * sm_count ? items : 2LL * sm_count);     // two CTAs per SM
-      fa_fwd_sm100_kernel<HD, DT, false, true><<<ctas, kThreads, smem_bytes, stream>>>(tmQ, tmK, tmV, tmO, a);
-      return cudaGetLastError();
+      auto launch_p = [&](auto kern) -> cudaError_t {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
+        if (e != cudaSuccess) return e;
+        kern<<<ctas, kThreads, smem_bytes, stream>>>(tmQ, tmK, tmV, tmO, a);
+        return cudaGetLastError();
+      };
+      return bigcap ? launch_p(fa_fwd_sm100_kernel<HD, DT, false, true, true>)
+                    : launch_p(fa_fwd_sm100_kernel<HD, DT, false, true, false>);
     }
   }
-  cudaError_t e = cudaFuncSetAttribute(fa_fwd_sm100_kernel<HD, DT, FEAT, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                       smem_bytes);
-  if (e != cudaSuccess) return e;
-  fa_fwd_sm100_kernel<HD, DT, FEAT, false><<<grid, kThreads, smem_bytes, stream>>>(tmQ, tmK, tmV, tmO, a);
-  return cudaGetLastError();
+  auto launch_1 = [&](auto kern) -> cudaError_t {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
+    if (e != cudaSuccess) return e;
+    kern<<<grid, kThreads, smem_bytes, stream>>>(tmQ, tmK, tmV, tmO, a);
+    return cudaGetLastError();
+  };
+  return bigcap ? launch_1(fa_fwd_sm100_kernel<HD, DT, FEAT, false, true>)
+                : launch_1(fa_fwd_sm100_kernel<HD, DT, FEAT, false, false>);
 }
 
 // Dense: nbatch = B, max_q = N.  Packed varlen (p.cu_q set, B == 1, N/S = total tokens): nbatch = number of

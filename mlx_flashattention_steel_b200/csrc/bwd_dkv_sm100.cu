@@ -74,7 +74,8 @@ template <int DT> __device__ __forceinline__ uint32_t pack16k(float a, float b) 
   return DT == 0 ? Elem<__half>::pack(a, b) : Elem<__nv_bfloat16>::pack(a, b);
 }
 
-template <int DT, bool CAP>
+// CAP (soft cap) and WIN (left window) are compile-time variants: the plain kernel's loops carry neither.
+template <int DT, bool CAP, bool WIN>
 __global__ void __launch_bounds__(kThreads, 1)
 bwd_dkv_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                      const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmDO, const DkvArgs a) {
@@ -148,7 +149,7 @@ bwd_dkv_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
   if (p.causal) m_begin = max(0, n0 - off) / BQ;
   int m_end = (N + BQ - 1) / BQ;
   // a left window: the last row that still sees this tile's last key is i = key - off + window_left
-  if (p.window_left >= 0) m_end = min(m_end, max(0, min(S, n0 + BK) - 1 - off + p.window_left) / BQ + 1);
+  if constexpr (WIN) m_end = min(m_end, max(0, min(S, n0 + BK) - 1 - off + p.window_left) / BQ + 1);
   const int nm = max(0, m_end - m_begin);
   const int n_iter = nm * p.gqa;
   const uint32_t kv_par = kv_uses & 1;
@@ -310,8 +311,8 @@ bwd_dkv_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
       if (!__all_sync(0xffffffffu, mbar_wait_bounded(bar(BAR_Q_FULL + st), (it >> 1) & 1, s_abort))) { ok = false; break; }
       const uint32_t Ls = opaque_u32(smem_u32(sL + st * BQ)), Ds = Ls + 2 * BQ * 4;
       const bool need_mask = (n0 + BK > S) || (p.causal && (n0 + BK - 1 > m * BQ + off)) ||
-                             (p.window_left >= 0 && (n0 < m * BQ + BQ - 1 + off - p.window_left));
-      const int wlo = p.window_left >= 0 ? off - p.window_left : -0x40000000;    // key visible iff key >= qrow + wlo
+                             (WIN && (n0 < m * BQ + BQ - 1 + off - p.window_left));
+      const int wlo = WIN ? off - p.window_left : 0;    // window: key visible iff key >= qrow + wlo
       const float2 c2 = make_float2(p.scale_log2, p.scale_log2);
       const float cap_in = CAP ? p.scale / p.softcap : 0.f, cap_out = p.softcap * kLog2e;
       const bool precise_tanh = p.softcap >= kPreciseTanhMinCap;
@@ -345,8 +346,8 @@ bwd_dkv_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
             if constexpr (decltype(masked)::value) {
               const int qrow = m * BQ + q0l + i + e;
               const bool kin = key < S;
-              if (!(kin && (!p.causal || key <= qrow + off) && key >= qrow + wlo)) pe.x = 0.f;
-              if (!(kin && (!p.causal || key <= qrow + 1 + off) && key >= qrow + 1 + wlo)) pe.y = 0.f;
+              if (!(kin && (!p.causal || key <= qrow + off) && (!WIN || key >= qrow + wlo))) pe.x = 0.f;
+              if (!(kin && (!p.causal || key <= qrow + 1 + off) && (!WIN || key >= qrow + 1 + wlo))) pe.y = 0.f;
             }
             float2 dsv = __fmul2_rn(pe, __fadd2_rn(dv, nd));
             if constexpr (CAP) dsv = __fmul2_rn(dsv, dcap);
@@ -492,9 +493,13 @@ cudaError_t launch_bwd_dkv_sm100(const BwdParams& p, int dtype, int nbatch, int 
     kern<<<grid, kThreads, kSmemBytes, stream>>>(tmQ, tmK, tmV, tmDO, a);
     return cudaGetLastError();
   };
-  const bool cap = p.softcap > 0.f;
-  if (dtype == 0) return cap ? launch(bwd_dkv_sm100_kernel<0, true>) : launch(bwd_dkv_sm100_kernel<0, false>);
-  return cap ? launch(bwd_dkv_sm100_kernel<1, true>) : launch(bwd_dkv_sm100_kernel<1, false>);
+  const bool cap = p.softcap > 0.f, win = p.window_left >= 0;
+  if (dtype == 0) {
+    if (cap) return win ? launch(bwd_dkv_sm100_kernel<0, true, true>) : launch(bwd_dkv_sm100_kernel<0, true, false>);
+    return win ? launch(bwd_dkv_sm100_kernel<0, false, true>) : launch(bwd_dkv_sm100_kernel<0, false, false>);
+  }
+  if (cap) return win ? launch(bwd_dkv_sm100_kernel<1, true, true>) : launch(bwd_dkv_sm100_kernel<1, true, false>);
+  return win ? launch(bwd_dkv_sm100_kernel<1, false, true>) : launch(bwd_dkv_sm100_kernel<1, false, false>);
 }
 
 cudaError_t bwd_dkv_sm100_read_clear_status(cudaStream_t stream, int* out) {

@@ -72,7 +72,8 @@ template <int DT> __device__ __forceinline__ uint32_t pack16q(float a, float b) 
   return DT == 0 ? Elem<__half>::pack(a, b) : Elem<__nv_bfloat16>::pack(a, b);
 }
 
-template <int DT, bool CAP>
+// CAP (soft cap) and WIN (left window) are compile-time variants: the plain kernel's loops carry neither.
+template <int DT, bool CAP, bool WIN>
 __global__ void __launch_bounds__(kThreads, 1)
 bwd_dq_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                     const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmDO,
@@ -105,7 +106,7 @@ bwd_dq_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   int k_hi = S;
   if (p.causal) k_hi = min(S, q0 + BM + off);
   int k_lo = 0;
-  if (p.window_left >= 0) k_lo = max(0, q0 + off - p.window_left);
+  if constexpr (WIN) k_lo = max(0, q0 + off - p.window_left);
   const int kt_begin = k_lo / BN;
   const int kt_end = k_hi > 0 ? (k_hi + BN - 1) / BN : 0;
   const int n_tiles = kt_end - kt_begin;
@@ -269,8 +270,8 @@ bwd_dq_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       tc_wait_ld();
       // visible keys of this row, relative to k0: [lo_rel, hi_rel]
       const int hi_rel = (p.causal ? min(S - 1, row + off) : S - 1) - k0;
-      const int lo_rel = (p.window_left >= 0 ? row + off - p.window_left : 0) - k0;
-      const bool need_mask = __any_sync(0xffffffffu, hi_rel < 31 || lo_rel > 0);
+      const int lo_rel = WIN ? row + off - p.window_left - k0 : 0;
+      const bool need_mask = __any_sync(0xffffffffu, hi_rel < 31 || (WIN && lo_rel > 0));
       uint32_t pd[16];
 #pragma unroll
       for (int i = 0; i < 32; i += 2) {
@@ -286,8 +287,8 @@ bwd_dq_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         }
         float2 pe = make_float2(fast_exp2(t.x), fast_exp2(t.y));
         if (need_mask) {
-          if (i > hi_rel || i < lo_rel) pe.x = 0.f;
-          if (i + 1 > hi_rel || i + 1 < lo_rel) pe.y = 0.f;
+          if (i > hi_rel || (WIN && i < lo_rel)) pe.x = 0.f;
+          if (i + 1 > hi_rel || (WIN && i + 1 < lo_rel)) pe.y = 0.f;
         }
         float2 dsv = __fmul2_rn(pe, __fadd2_rn(dv, nD2));
         if constexpr (CAP) dsv = __fmul2_rn(dsv, dcap);
@@ -393,9 +394,13 @@ cudaError_t launch_bwd_dq_sm100(const BwdParams& p, int dtype, int nbatch, int m
     kern<<<grid, kThreads, kSmemBytes, stream>>>(tmQ, tmK, tmV, tmDO, tmDQ, a);
     return cudaGetLastError();
   };
-  const bool cap = p.softcap > 0.f;
-  if (dtype == 0) return cap ? launch(bwd_dq_sm100_kernel<0, true>) : launch(bwd_dq_sm100_kernel<0, false>);
-  return cap ? launch(bwd_dq_sm100_kernel<1, true>) : launch(bwd_dq_sm100_kernel<1, false>);
+  const bool cap = p.softcap > 0.f, win = p.window_left >= 0;
+  if (dtype == 0) {
+    if (cap) return win ? launch(bwd_dq_sm100_kernel<0, true, true>) : launch(bwd_dq_sm100_kernel<0, true, false>);
+    return win ? launch(bwd_dq_sm100_kernel<0, false, true>) : launch(bwd_dq_sm100_kernel<0, false, false>);
+  }
+  if (cap) return win ? launch(bwd_dq_sm100_kernel<1, true, true>) : launch(bwd_dq_sm100_kernel<1, true, false>);
+  return win ? launch(bwd_dq_sm100_kernel<1, false, true>) : launch(bwd_dq_sm100_kernel<1, false, false>);
 }
 
 cudaError_t bwd_dq_sm100_read_clear_status(cudaStream_t stream, int* out) {

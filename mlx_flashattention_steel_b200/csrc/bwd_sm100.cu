@@ -90,8 +90,10 @@ template <int DT> __device__ __forceinline__ uint32_t pack16b(float a, float b) 
 }
 
 // CAP: the forward capped the scores (cap * tanh(s / cap)); P is rebuilt from the capped score and dS carries the
-// factor 1 - tanh^2.  A compile-time variant, so that the plain kernel's compute loop is untouched.
-template <int DT, bool CAP>
+// factor 1 - tanh^2.  WIN: a left window (fewer query tiles per key tile, one more test in the masked tiles).  Both are
+// compile-time variants, so that the plain kernel's loops are untouched (with the window test compiled into every
+// instance config 5's backward ran 9 % slower).
+template <int DT, bool CAP, bool WIN>
 __global__ void __launch_bounds__(kThreads, 1)
 bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                  const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmDO,
@@ -186,7 +188,7 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   if (p.causal) m_begin = max(0, n0 - off) / BQ;
   int m_end = (N + BQ - 1) / BQ;
   // a left window: the last row that still sees this tile's last key is i = key - off + window_left
-  if (p.window_left >= 0) m_end = min(m_end, max(0, min(S, n0 + BK) - 1 - off + p.window_left) / BQ + 1);
+  if constexpr (WIN) m_end = min(m_end, max(0, min(S, n0 + BK) - 1 - off + p.window_left) / BQ + 1);
   const int nm = max(0, m_end - m_begin);
   const int n_iter = nm * p.gqa;
   const int kbuf = w & 1;                              // K buffer and KV barrier of this item
@@ -435,8 +437,8 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       if (!__all_sync(0xffffffffu, mbar_wait_bounded(bar(BAR_Q_FULL + st), (it >> 1) & 1, s_abort))) { ok = false; break; }
       const uint32_t Ls = opaque_u32(smem_u32(sL + st * BQ)), Ds = Ls + 2 * BQ * 4;
       const bool need_mask = (n0 + BK > S) || (p.causal && (n0 + BK - 1 > m * BQ + off)) ||
-                             (p.window_left >= 0 && (n0 < m * BQ + BQ - 1 + off - p.window_left));
-      const int wlo = p.window_left >= 0 ? off - p.window_left : -0x40000000;    // key visible iff key >= qrow + wlo
+                             (WIN && (n0 < m * BQ + BQ - 1 + off - p.window_left));
+      const int wlo = WIN ? off - p.window_left : 0;    // window: key visible iff key >= qrow + wlo
       // dS^T[this key][query] lives in buffer it & 1 as [query block of 64][key][128 B], 16-byte chunks swizzled by
       // key & 7: each thread stores its 32 queries as four 16-byte chunks
       const uint32_t ds_row = smem_u32(sDS) + (it & 1) * kDSBytes + rloc * 128;
@@ -473,8 +475,8 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
             if constexpr (decltype(masked)::value) {
               const int qrow = m * BQ + q0l + i + e;
               const bool kin = key < S;
-              if (!(kin && (!p.causal || key <= qrow + off) && key >= qrow + wlo)) pe.x = 0.f;
-              if (!(kin && (!p.causal || key <= qrow + 1 + off) && key >= qrow + 1 + wlo)) pe.y = 0.f;
+              if (!(kin && (!p.causal || key <= qrow + off) && (!WIN || key >= qrow + wlo))) pe.x = 0.f;
+              if (!(kin && (!p.causal || key <= qrow + 1 + off) && (!WIN || key >= qrow + 1 + wlo))) pe.y = 0.f;
             }
             float2 dsv = __fmul2_rn(pe, __fadd2_rn(dv, nd));
             if constexpr (CAP) dsv = __fmul2_rn(dsv, dcap);
@@ -645,9 +647,13 @@ cudaError_t launch_bwd_sm100_main(const BwdParams& p, int dtype, int nbatch, int
     kern<<<grid, kThreads, kSmemBytes, stream>>>(tmQ, tmK, tmV, tmDO, tmDQ, a);
     return cudaGetLastError();
   };
-  const bool cap = p.softcap > 0.f;
-  if (dtype == 0) return cap ? launch(bwd_sm100_kernel<0, true>) : launch(bwd_sm100_kernel<0, false>);
-  return cap ? launch(bwd_sm100_kernel<1, true>) : launch(bwd_sm100_kernel<1, false>);
+  const bool cap = p.softcap > 0.f, win = p.window_left >= 0;
+  if (dtype == 0) {
+    if (cap) return win ? launch(bwd_sm100_kernel<0, true, true>) : launch(bwd_sm100_kernel<0, true, false>);
+    return win ? launch(bwd_sm100_kernel<0, false, true>) : launch(bwd_sm100_kernel<0, false, false>);
+  }
+  if (cap) return win ? launch(bwd_sm100_kernel<1, true, true>) : launch(bwd_sm100_kernel<1, true, false>);
+  return win ? launch(bwd_sm100_kernel<1, false, true>) : launch(bwd_sm100_kernel<1, false, false>);
 }
 
 cudaError_t bwd_sm100_read_clear_status(cudaStream_t stream, int* out) {

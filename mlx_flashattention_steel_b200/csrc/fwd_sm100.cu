@@ -160,10 +160,12 @@ template <int DT> __device__ __forceinline__ uint32_t pack16(float a, float b) {
 // MMAs of this one have read it and its K tiles as their stages free up, so set-up, launch gaps and load latency are
 // paid once per SM instead of once per query tile -- what shapes with few key tiles per query tile (a sliding
 // window, short packed sequences) spend a third of their time on otherwise.
-// BIGCAP: soft caps of kPreciseTanhMinCap (64) and more.  Only they can push the bf16 path's upper bound of the row
-// max out of the exponent range, and only for them is tanh.approx too coarse; the guard and the two-operation tanh are
-// compiled into this instantiation alone, so the common caps (30, 50) keep the lean loop.
-template <int HD, int DT, bool FEAT, bool PERSIST, bool BIGCAP>
+// CAPM: 0 = no soft cap, 1 = a cap below kPreciseTanhMinCap (64), 2 = a larger one.  Only the large caps can push the
+// bf16 path's upper bound of the row max out of the exponent range, and only for them is tanh.approx too coarse: the
+// guard and the two-operation tanh are compiled into that instantiation alone, so the common caps (30, 50) keep the
+// lean loop, and the instantiation without a cap carries no tanh code at all (the kernels are sensitive to the size of
+// their unrolled loops: measured per variant on the same box).
+template <int HD, int DT, bool FEAT, bool PERSIST, int CAPM>
 __global__ void __launch_bounds__(kThreads, 2)
 fa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                     const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmO,
@@ -488,7 +490,8 @@ fa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     // ============================ softmax (warps 0-3) ============================
     const int row = q0 + tid;                         // query row of this thread
     const uint32_t lane_base = static_cast<uint32_t>(warp * 32) << 16;
-    const bool use_cap = p.softcap > 0.f;
+    constexpr bool BIGCAP = CAPM == 2;
+    constexpr bool use_cap = CAPM != 0;
     const float cap_in = use_cap ? p.scale / p.softcap : 0.f;
     const float cap_out = p.softcap * kLog2e;
     float m_used = -INFINITY, l_run = 0.f;
@@ -939,7 +942,7 @@ static cudaError_t launch_hd(const FwdParams& p, int nbatch, int max_q, cudaStre
   dim3 grid((max_q + BM - 1) / BM, p.Hq, nbatch);
   a.gx = static_cast<int>(grid.x);
   a.gy = static_cast<int>(grid.y);
-  const bool bigcap = p.softcap >= kPreciseTanhMinCap;
+  const int capm = p.softcap >= kPreciseTanhMinCap ? 2 : (p.softcap > 0.f ? 1 : 0);
   const long long items = static_cast<long long>(grid.x) * grid.y * grid.z;
   a.total_items = static_cast<int>(items < 0x7fffffffLL ? items : 0x7fffffffLL);
   if constexpr (!FEAT) {
@@ -955,8 +958,8 @@ static cudaError_t launch_hd(const FwdParams& p, int nbatch, int max_q, cudaStre
         kern<<<ctas, kThreads, smem_bytes, stream>>>(tmQ, tmK, tmV, tmO, a);
         return cudaGetLastError();
       };
-      return bigcap ? launch_p(fa_fwd_sm100_kernel<HD, DT, false, true, true>)
-                    : launch_p(fa_fwd_sm100_kernel<HD, DT, false, true, false>);
+      return capm == 2 ? launch_p(fa_fwd_sm100_kernel<HD, DT, false, true, 2>)
+                       : (capm == 1 ? launch_p(fa_fwd_sm100_kernel<HD, DT, false, true, 1>) : launch_p(fa_fwd_sm100_kernel<HD, DT, false, true, 0>));
     }
   }
   auto launch_1 = [&](auto kern) -> cudaError_t {
@@ -965,8 +968,8 @@ static cudaError_t launch_hd(const FwdParams& p, int nbatch, int max_q, cudaStre
     kern<<<grid, kThreads, smem_bytes, stream>>>(tmQ, tmK, tmV, tmO, a);
     return cudaGetLastError();
   };
-  return bigcap ? launch_1(fa_fwd_sm100_kernel<HD, DT, FEAT, false, true>)
-                : launch_1(fa_fwd_sm100_kernel<HD, DT, FEAT, false, false>);
+  return capm == 2 ? launch_1(fa_fwd_sm100_kernel<HD, DT, FEAT, false, 2>)
+                   : (capm == 1 ? launch_1(fa_fwd_sm100_kernel<HD, DT, FEAT, false, 1>) : launch_1(fa_fwd_sm100_kernel<HD, DT, FEAT, false, 0>));
 }
 
 // Dense: nbatch = B, max_q = N.  Packed varlen (p.cu_q set, B == 1, N/S = total tokens): nbatch = number of

@@ -353,15 +353,13 @@ static int32_t fill_bwd_params(const b200fa_desc* d, const void* q, const void* 
   p.gqa = f.gqa; p.scale = d->scale; p.scale_log2 = f.scale_log2; p.causal = f.causal;
   p.softcap = d->softcap; p.window_left = d->window_left;
   p.cu_q = cu_q; p.cu_k = cu_k;
-  p.alibi = d->alibi_slopes;       // biased / block-masked scores are recomputed by the portable kernel only
+  p.alibi = d->alibi_slopes;
   p.bmask = d->block_mask;
   p.bm_bq = d->mask_bq; p.bm_bk = d->mask_bk; p.bm_nk = d->mask_nk;
   return B200FA_OK;
 }
 
-static bool bwd_allow_sm100(const b200fa_desc* d) {
-  return !(d->flags & B200FA_FLAG_FORCE_MMA_SYNC) && d->alibi_slopes == nullptr && d->block_mask == nullptr;
-}
+static bool bwd_allow_sm100(const b200fa_desc* d) { return !(d->flags & B200FA_FLAG_FORCE_MMA_SYNC); }
 
 // The split head_dim-128 path keeps no fp32 dQ accumulator, which is most of the workspace.
 static size_t bwd_need_bytes(const b200fa_desc* d) {

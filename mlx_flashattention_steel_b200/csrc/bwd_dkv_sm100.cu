@@ -75,7 +75,10 @@ template <int DT> __device__ __forceinline__ uint32_t pack16k(float a, float b) 
 }
 
 // CAP (soft cap) and WIN (left window) are compile-time variants: the plain kernel's loops carry neither.
-template <int DT, bool CAP, bool WIN>
+// FEAT: the ALiBi bias slope[h] * (key - (query + S - N)) and / or a block mask (cells of mask_bq x mask_bk, mask_bq a
+// multiple of 32 so that the 32 queries a thread handles per step share one cell), as the forward's feature
+// instantiation applies them (csrc/mfa_steel_fwd.cpp:951-970, 230-262 in the reference).  Without CAP / WIN.
+template <int DT, bool CAP, bool WIN, bool FEAT>
 __global__ void __launch_bounds__(kThreads, 1)
 bwd_dkv_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                      const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmDO, const DkvArgs a) {
@@ -314,11 +317,21 @@ bwd_dkv_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
                              (WIN && (n0 < m * BQ + BQ - 1 + off - p.window_left));
       const int wlo = WIN ? off - p.window_left : 0;    // window: key visible iff key >= qrow + wlo
       const float2 c2 = make_float2(p.scale_log2, p.scale_log2);
+      const float alibi_l2 = (FEAT && p.alibi != nullptr) ? p.alibi[kvh * p.gqa + it / nm] * kLog2e : 0.f;
       const float cap_in = CAP ? p.scale / p.softcap : 0.f, cap_out = p.softcap * kLog2e;
       const bool precise_tanh = p.softcap >= kPreciseTanhMinCap;
 
       auto run_half = [&](int x, auto masked) {
         const int q0l = x * 64 + hf * 32;                  // first query (inside the tile) of this warp's 32 columns
+        // FEAT: the mask cell of (these 32 queries, this key) and the bias of the first of them, in the log2 domain
+        bool cell_on = true;
+        float ab = 0.f;
+        if constexpr (FEAT) {
+          const int qrow0 = m * BQ + q0l;
+          if (p.bmask != nullptr)
+            cell_on = key < S && p.bmask[static_cast<int64_t>(min(qrow0, N - 1) / p.bm_bq) * p.bm_nk + key / p.bm_bk] != 0;
+          ab = alibi_l2 * static_cast<float>(key - off - qrow0);
+        }
         uint32_t rs[32], rd[32];
         tmem_ld32(tmem + lane_base + cST + 128 * x + hf * 32, rs);
         tmem_ld32(tmem + lane_base + cDPT + 128 * x + hf * 32, rd);
@@ -342,7 +355,13 @@ bwd_dkv_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
             } else {
               t = __ffma2_rn(sv, c2, nl);
             }
+            if constexpr (FEAT) {
+              t = __fadd2_rn(t, make_float2(fmaf(-alibi_l2, static_cast<float>(i + e), ab), fmaf(-alibi_l2, static_cast<float>(i + e + 1), ab)));
+            }
             float2 pe = make_float2(fast_exp2(t.x), fast_exp2(t.y));
+            if constexpr (FEAT) {
+              if (!cell_on) pe = make_float2(0.f, 0.f);
+            }
             if constexpr (decltype(masked)::value) {
               const int qrow = m * BQ + q0l + i + e;
               const bool kin = key < S;
@@ -493,13 +512,14 @@ cudaError_t launch_bwd_dkv_sm100(const BwdParams& p, int dtype, int nbatch, int 
     kern<<<grid, kThreads, kSmemBytes, stream>>>(tmQ, tmK, tmV, tmDO, a);
     return cudaGetLastError();
   };
-  const bool cap = p.softcap > 0.f, win = p.window_left >= 0;
+  const bool cap = p.softcap > 0.f, win = p.window_left >= 0, feat = p.alibi != nullptr || p.bmask != nullptr;
+  if (feat) return dtype == 0 ? launch(bwd_dkv_sm100_kernel<0, false, false, true>) : launch(bwd_dkv_sm100_kernel<1, false, false, true>);
   if (dtype == 0) {
-    if (cap) return win ? launch(bwd_dkv_sm100_kernel<0, true, true>) : launch(bwd_dkv_sm100_kernel<0, true, false>);
-    return win ? launch(bwd_dkv_sm100_kernel<0, false, true>) : launch(bwd_dkv_sm100_kernel<0, false, false>);
+    if (cap) return win ? launch(bwd_dkv_sm100_kernel<0, true, true, false>) : launch(bwd_dkv_sm100_kernel<0, true, false, false>);
+    return win ? launch(bwd_dkv_sm100_kernel<0, false, true, false>) : launch(bwd_dkv_sm100_kernel<0, false, false, false>);
   }
-  if (cap) return win ? launch(bwd_dkv_sm100_kernel<1, true, true>) : launch(bwd_dkv_sm100_kernel<1, true, false>);
-  return win ? launch(bwd_dkv_sm100_kernel<1, false, true>) : launch(bwd_dkv_sm100_kernel<1, false, false>);
+  if (cap) return win ? launch(bwd_dkv_sm100_kernel<1, true, true, false>) : launch(bwd_dkv_sm100_kernel<1, true, false, false>);
+  return win ? launch(bwd_dkv_sm100_kernel<1, false, true, false>) : launch(bwd_dkv_sm100_kernel<1, false, false, false>);
 }
 
 cudaError_t bwd_dkv_sm100_read_clear_status(cudaStream_t stream, int* out) {

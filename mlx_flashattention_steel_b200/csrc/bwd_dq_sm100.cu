@@ -72,8 +72,9 @@ template <int DT> __device__ __forceinline__ uint32_t pack16q(float a, float b) 
   return DT == 0 ? Elem<__half>::pack(a, b) : Elem<__nv_bfloat16>::pack(a, b);
 }
 
-// CAP (soft cap) and WIN (left window) are compile-time variants: the plain kernel's loops carry neither.
-template <int DT, bool CAP, bool WIN>
+// CAP (soft cap) and WIN (left window) are compile-time variants: the plain kernel's loops carry neither.  FEAT: the
+// ALiBi bias and / or a block mask (cells of 16, 32 or 64 keys), without CAP / WIN.
+template <int DT, bool CAP, bool WIN, bool FEAT>
 __global__ void __launch_bounds__(kThreads, 1)
 bwd_dq_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                     const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmDO,
@@ -242,6 +243,10 @@ bwd_dq_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     const float cap_in = CAP ? p.scale / p.softcap : 0.f, cap_out = p.softcap * kLog2e;
     const bool precise_tanh = p.softcap >= kPreciseTanhMinCap;
     const float2 c2 = make_float2(p.scale_log2, p.scale_log2), nL2 = make_float2(nL, nL), nD2 = make_float2(nD, nD);
+    const float alibi_l2 = (FEAT && p.alibi != nullptr) ? p.alibi[head] * kLog2e : 0.f;
+    const bool masked_cells = FEAT && p.bmask != nullptr;
+    const int cell_sh = masked_cells ? (p.bm_bk == 16 ? 4 : (p.bm_bk == 32 ? 5 : 6)) : 6;
+    const uint8_t* mask_row = masked_cells ? p.bmask + static_cast<int64_t>(min(row, N - 1) / p.bm_bq) * p.bm_nk : nullptr;
     bool ok = __all_sync(0xffffffffu, mbar_wait_bounded(bar(BAR_Q), 0, s_abort));
     if (ok) {
       // this row's 128 bytes of d-half hf of Q (set 0) or dO (set 1) -> 32 TMEM columns of the A operand
@@ -264,6 +269,19 @@ bwd_dq_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       const int k0 = (kt_begin + j) * BN + hf * 32;            // first key of this thread's 32 columns
       if (!__all_sync(0xffffffffu, mbar_wait_bounded(bar(BAR_SD_FULL + b), (j / kBufs) & 1, s_abort))) { ok = false; break; }
       tc_fence_after();
+      // FEAT: bit c = mask cell c of this row under the 32 keys from k0 (two cells of 16 keys, else one); the bias of
+      // key k0 for this row, in the log2 domain
+      unsigned cells = 3u;
+      float ab = 0.f;
+      if constexpr (FEAT) {
+        if (masked_cells) {
+          const int cb0 = k0 >> cell_sh;
+          cells = (cb0 < p.bm_nk && mask_row[cb0] != 0) ? 1u : 0u;
+          if (cell_sh == 4) cells |= (cb0 + 1 < p.bm_nk && mask_row[cb0 + 1] != 0) ? 2u : 0u;
+          else cells |= cells << 1;
+        }
+        ab = alibi_l2 * static_cast<float>(k0 - (row + off));
+      }
       uint32_t rs[32], rd[32];
       tmem_ld32(tmem + lane_base + cS + 64 * b + hf * 32, rs);
       tmem_ld32(tmem + lane_base + cDP + 64 * b + hf * 32, rd);
@@ -285,7 +303,13 @@ bwd_dq_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         } else {
           t = __ffma2_rn(sv, c2, nL2);
         }
+        if constexpr (FEAT) {
+          t = __fadd2_rn(t, make_float2(fmaf(alibi_l2, static_cast<float>(i), ab), fmaf(alibi_l2, static_cast<float>(i + 1), ab)));
+        }
         float2 pe = make_float2(fast_exp2(t.x), fast_exp2(t.y));
+        if constexpr (FEAT) {
+          if (!((cells >> (i >> 4)) & 1u)) pe = make_float2(0.f, 0.f);     // keys i, i + 1 share a 16-key cell
+        }
         if (need_mask) {
           if (i > hi_rel || (WIN && i < lo_rel)) pe.x = 0.f;
           if (i + 1 > hi_rel || (WIN && i + 1 < lo_rel)) pe.y = 0.f;
@@ -394,13 +418,14 @@ cudaError_t launch_bwd_dq_sm100(const BwdParams& p, int dtype, int nbatch, int m
     kern<<<grid, kThreads, kSmemBytes, stream>>>(tmQ, tmK, tmV, tmDO, tmDQ, a);
     return cudaGetLastError();
   };
-  const bool cap = p.softcap > 0.f, win = p.window_left >= 0;
+  const bool cap = p.softcap > 0.f, win = p.window_left >= 0, feat = p.alibi != nullptr || p.bmask != nullptr;
+  if (feat) return dtype == 0 ? launch(bwd_dq_sm100_kernel<0, false, false, true>) : launch(bwd_dq_sm100_kernel<1, false, false, true>);
   if (dtype == 0) {
-    if (cap) return win ? launch(bwd_dq_sm100_kernel<0, true, true>) : launch(bwd_dq_sm100_kernel<0, true, false>);
-    return win ? launch(bwd_dq_sm100_kernel<0, false, true>) : launch(bwd_dq_sm100_kernel<0, false, false>);
+    if (cap) return win ? launch(bwd_dq_sm100_kernel<0, true, true, false>) : launch(bwd_dq_sm100_kernel<0, true, false, false>);
+    return win ? launch(bwd_dq_sm100_kernel<0, false, true, false>) : launch(bwd_dq_sm100_kernel<0, false, false, false>);
   }
-  if (cap) return win ? launch(bwd_dq_sm100_kernel<1, true, true>) : launch(bwd_dq_sm100_kernel<1, true, false>);
-  return win ? launch(bwd_dq_sm100_kernel<1, false, true>) : launch(bwd_dq_sm100_kernel<1, false, false>);
+  if (cap) return win ? launch(bwd_dq_sm100_kernel<1, true, true, false>) : launch(bwd_dq_sm100_kernel<1, true, false, false>);
+  return win ? launch(bwd_dq_sm100_kernel<1, false, true, false>) : launch(bwd_dq_sm100_kernel<1, false, false, false>);
 }
 
 cudaError_t bwd_dq_sm100_read_clear_status(cudaStream_t stream, int* out) {

@@ -437,7 +437,7 @@ size_t bwd_workspace_bytes(int B, int Hq, int N_total, int D, bool split) {
 }
 
 bool bwd_takes_split_path(const BwdParams& p, int dtype, int D, bool allow_sm100) {
-  return allow_sm100 && p.alibi == nullptr && p.bmask == nullptr && bwd_split_sm100_supported(dtype, D) && bwd_sm100_strides_ok(p);
+  return allow_sm100 && bwd_split_sm100_supported(dtype, D) && bwd_sm100_strides_ok(p);
 }
 
 cudaError_t launch_bwd(const BwdParams& p_in, int dtype, int D, bool varlen, int nbatch, int max_q, int max_k,

@@ -93,7 +93,10 @@ template <int DT> __device__ __forceinline__ uint32_t pack16b(float a, float b) 
 // factor 1 - tanh^2.  WIN: a left window (fewer query tiles per key tile, one more test in the masked tiles).  Both are
 // compile-time variants, so that the plain kernel's loops are untouched (with the window test compiled into every
 // instance config 5's backward ran 9 % slower).
-template <int DT, bool CAP, bool WIN>
+// FEAT: the ALiBi bias slope[h] * (key - (query + S - N)) and / or a block mask (cells of mask_bq x mask_bk, mask_bq a
+// multiple of 32 so that the 32 queries a thread handles per step share one cell), as the forward's feature
+// instantiation applies them (csrc/mfa_steel_fwd.cpp:951-970, 230-262 in the reference).  Without CAP / WIN.
+template <int DT, bool CAP, bool WIN, bool FEAT>
 __global__ void __launch_bounds__(kThreads, 1)
 bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                  const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmDO,
@@ -443,11 +446,21 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       // key & 7: each thread stores its 32 queries as four 16-byte chunks
       const uint32_t ds_row = smem_u32(sDS) + (it & 1) * kDSBytes + rloc * 128;
       const float2 c2 = make_float2(p.scale_log2, p.scale_log2);
+      const float alibi_l2 = (FEAT && p.alibi != nullptr) ? p.alibi[kvh * p.gqa + it / nm] * kLog2e : 0.f;
       const float cap_in = CAP ? p.scale / p.softcap : 0.f, cap_out = p.softcap * kLog2e;
       const bool precise_tanh = p.softcap >= kPreciseTanhMinCap;
 
       auto run_half = [&](int x, auto masked) {
         const int q0l = x * 64 + hf * 32;                  // first query (inside the tile) of this warp's 32 columns
+        // FEAT: the mask cell of (these 32 queries, this key) and the bias of the first of them, in the log2 domain
+        bool cell_on = true;
+        float ab = 0.f;
+        if constexpr (FEAT) {
+          const int qrow0 = m * BQ + q0l;
+          if (p.bmask != nullptr)
+            cell_on = key < S && p.bmask[static_cast<int64_t>(min(qrow0, N - 1) / p.bm_bq) * p.bm_nk + key / p.bm_bk] != 0;
+          ab = alibi_l2 * static_cast<float>(key - off - qrow0);
+        }
         uint32_t rs[32], rd[32];
         tmem_ld32(tmem + lane_base + cST + 128 * x + hf * 32, rs);
         tmem_ld32(tmem + lane_base + cDPT + 128 * x + hf * 32, rd);
@@ -471,7 +484,13 @@ bwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
             } else {
               t = __ffma2_rn(sv, c2, nl);
             }
+            if constexpr (FEAT) {
+              t = __fadd2_rn(t, make_float2(fmaf(-alibi_l2, static_cast<float>(i + e), ab), fmaf(-alibi_l2, static_cast<float>(i + e + 1), ab)));
+            }
             float2 pe = make_float2(fast_exp2(t.x), fast_exp2(t.y));
+            if constexpr (FEAT) {
+              if (!cell_on) pe = make_float2(0.f, 0.f);
+            }
             if constexpr (decltype(masked)::value) {
               const int qrow = m * BQ + q0l + i + e;
               const bool kin = key < S;
@@ -594,8 +613,14 @@ bool make_map64(CUtensorMap* m, int dtype, const void* base, int rows, int H, in
 
 bool bwd_sm100_supported(int dtype, int D) { return (dtype == 0 || dtype == 1) && D == HD && get_encode_tiled() != nullptr; }
 
-// TMA strides must be positive: broadcast (stride 0) batch / head dimensions of extent > 1 take the portable kernel.
+// What the tcgen05 backward kernels take beyond dtype and head_dim.  TMA strides must be positive: broadcast
+// (stride 0) batch / head dimensions of extent > 1 take the portable kernel.  ALiBi / block mask: dense layout, without
+// soft cap or window, mask cells of 32k queries x 16 / 32 / 64 keys.
 bool bwd_sm100_strides_ok(const BwdParams& p) {
+  if (p.alibi != nullptr || p.bmask != nullptr) {
+    if (p.softcap > 0.f || p.window_left >= 0 || p.cu_q != nullptr) return false;
+    if (p.bmask != nullptr && (p.bm_bq <= 0 || p.bm_bq % 32 != 0 || !(p.bm_bk == 16 || p.bm_bk == 32 || p.bm_bk == 64))) return false;
+  }
   return !((p.B > 1 && (p.q_bs == 0 || p.k_bs == 0 || p.v_bs == 0)) || (p.Hq > 1 && p.q_hs == 0) ||
            (p.Hkv > 1 && (p.k_hs == 0 || p.v_hs == 0)));
 }
@@ -647,13 +672,14 @@ cudaError_t launch_bwd_sm100_main(const BwdParams& p, int dtype, int nbatch, int
     kern<<<grid, kThreads, kSmemBytes, stream>>>(tmQ, tmK, tmV, tmDO, tmDQ, a);
     return cudaGetLastError();
   };
-  const bool cap = p.softcap > 0.f, win = p.window_left >= 0;
+  const bool cap = p.softcap > 0.f, win = p.window_left >= 0, feat = p.alibi != nullptr || p.bmask != nullptr;
+  if (feat) return dtype == 0 ? launch(bwd_sm100_kernel<0, false, false, true>) : launch(bwd_sm100_kernel<1, false, false, true>);
   if (dtype == 0) {
-    if (cap) return win ? launch(bwd_sm100_kernel<0, true, true>) : launch(bwd_sm100_kernel<0, true, false>);
-    return win ? launch(bwd_sm100_kernel<0, false, true>) : launch(bwd_sm100_kernel<0, false, false>);
+    if (cap) return win ? launch(bwd_sm100_kernel<0, true, true, false>) : launch(bwd_sm100_kernel<0, true, false, false>);
+    return win ? launch(bwd_sm100_kernel<0, false, true, false>) : launch(bwd_sm100_kernel<0, false, false, false>);
   }
-  if (cap) return win ? launch(bwd_sm100_kernel<1, true, true>) : launch(bwd_sm100_kernel<1, true, false>);
-  return win ? launch(bwd_sm100_kernel<1, false, true>) : launch(bwd_sm100_kernel<1, false, false>);
+  if (cap) return win ? launch(bwd_sm100_kernel<1, true, true, false>) : launch(bwd_sm100_kernel<1, true, false, false>);
+  return win ? launch(bwd_sm100_kernel<1, false, true, false>) : launch(bwd_sm100_kernel<1, false, false, false>);
 }
 
 cudaError_t bwd_sm100_read_clear_status(cudaStream_t stream, int* out) {

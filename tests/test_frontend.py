@@ -62,8 +62,8 @@ def test_varlen_checks():
     cu = torch.tensor([0], dtype=torch.int32)
     assert fa.flash_attention_varlen(q, k, v, cu, cu, 0, 0) is q      # num_seqs == 0 returns q
     cu = torch.tensor([0, 8], dtype=torch.int32)
-    with pytest.raises(NotImplementedError, match="block_mask"):
-        fa.flash_attention_varlen(q, k, v, cu, cu, 8, 8, block_mask=torch.ones(1, 1))
+    with pytest.raises(ValueError, match="block_mask shape"):   # the mask must fit every sequence: [1, 1] for 8 tokens ...
+        fa.flash_attention_varlen(q, k, v, cu, cu, 8, 8, block_mask=torch.ones(2, 2))
     with pytest.raises(ValueError, match="batch size 1"):
         fa.flash_attention_varlen(*_qkv(B=2), cu, cu, 8, 8)
 

@@ -119,14 +119,14 @@ def test_sparse_backward(dev, dtype, D):
 @pytest.mark.gpu
 def test_varlen_with_a_block_mask(dev):
     """flash_attention_varlen(block_mask=...): one mask that fits every sequence, applied per sequence -- the
-    reference's split / concatenate route (mlx_mfa/attention.py:2365-2390, 2448-2453).  Sequences of 100 and 128
+    reference's split / concatenate route (mlx_mfa/attention.py:2365-2390, 2448-2453).  Sequences of 113 to 128
     tokens share the [4, 8] cell grid of head_dim 128; forward and gradients against the oracle per sequence."""
     D, dtype = 128, torch.bfloat16
     BQ, BK = _steel_block_config(D)
-    lens = [100, 128, 97]
-    cu = [0, 100, 228, 325]
+    lens = [120, 128, 113]
+    cu = [0, 120, 248, 361]
     mask = _random_mask(4, 8, 970, density=0.5)
-    q, k, v, do = (randn((1, 4, 325, D), dtype, 971 + i) for i in range(4))
+    q, k, v, do = (randn((1, 4, 361, D), dtype, 971 + i) for i in range(4))
     k, v = k[:, :2].contiguous(), v[:, :2].contiguous()
     cu_t = torch.tensor(cu, dtype=torch.int32, device=dev)
     qg, kg, vg = (x.to(dev).requires_grad_(True) for x in (q, k, v))
@@ -137,3 +137,41 @@ def test_varlen_with_a_block_mask(dev):
         O, _, _ = orc.sdpa(q[:, :, sl], k[:, :, sl], v[:, :, sl], causal=True, block_mask=mask, block=(BQ, BK))
         assert_close(out[:, :, sl], O, dtype)
     assert qg.grad.shape == q.shape and torch.isfinite(qg.grad.float()).all() and torch.isfinite(kg.grad.float()).all()
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("D", [64, 128])
+@pytest.mark.parametrize("feature", ["alibi", "block_mask", "both"])
+def test_feature_backward_tcgen05_and_portable_kernels_agree(dev, D, feature):
+    """ALiBi and block-masked gradients run the tcgen05 backward kernels (head_dim 64: one kernel; 128: dK/dV + dQ
+    kernels); forcing the mma.sync kernel must give the same gradients within tolerance, with different bits."""
+    from mlx_flashattention_steel_b200 import _lib, attention as A
+
+    dtype = torch.bfloat16
+    B, Hq, Hkv, N = 2, 4, 2, 300
+    BQ, BK = _steel_block_config(D)
+    mask = _random_mask((N + BQ - 1) // BQ, (N + BK - 1) // BK, 980, density=0.5).to(dev)
+    slopes = torch.tensor([0.5, 0.25, 0.125, 0.0625], device=dev)
+    q, k, v, do = (randn((B, Hq, N, D), dtype, 981 + i).to(dev) for i in range(4))
+    k, v = k[:, :Hkv].contiguous(), v[:, :Hkv].contiguous()
+
+    def grads():
+        qg, kg, vg = (x.clone().requires_grad_(True) for x in (q, k, v))
+        bm = (mask.to(torch.uint8).contiguous(), BQ, BK) if feature in ("block_mask", "both") else None
+        al = slopes if feature in ("alibi", "both") else None
+        out, _ = A._FlashAttnFn.apply(qg, kg, vg, D ** -0.5, True, 0.0, -1, False, None, al, bm)
+        out.backward(do)
+        return qg.grad.float(), kg.grad.float(), vg.grad.float()
+
+    g1 = grads()
+    old = A._set_force_flags(_lib.FLAG_FORCE_MMA_SYNC)
+    try:
+        g2 = grads()
+    finally:
+        A._set_force_flags(old)
+    differs = False
+    for a, b in zip(g1, g2):
+        assert float((a - b).abs().max()) <= 2e-2 + 2.0 ** -7 * float(b.abs().max())
+        differs = differs or not torch.equal(a, b)
+    assert differs
+    assert fa.kernel_status() == 0

@@ -115,3 +115,69 @@ def test_decode_rejects_bad_arguments():
     d = _desc(N=1, Hq=32, Hkv=8)
     st = lib.b200fa_decode_paged(C.byref(d), p, p, p, None, None, p, p, 10, 16, 4, 64, p, None, None, 0, None)
     assert st == _lib.ERR_WORKSPACE
+
+
+def test_decode_shapes_and_page_sizes_are_validated():
+    lib = _lib.load()
+    p = C.c_void_p(256)
+    d = _desc(N=1, Hq=32, Hkv=8)
+    # pages must hold a multiple of 16 tokens
+    st = lib.b200fa_decode_paged(C.byref(d), p, p, p, None, None, p, p, 10, 24, 4, 64, p, None, p, 1 << 30, None)
+    assert st == _lib.ERR_UNSUPPORTED and "multiple of 16" in _lib.last_error()
+    # head_dim 64 takes 16-bit pools only
+    d = _desc(N=1, Hq=32, Hkv=8, D=64, kv_dtype=_lib.I8)
+    st = lib.b200fa_decode_paged(C.byref(d), p, p, p, p, p, p, p, 10, 16, 4, 64, p, None, p, 1 << 30, None)
+    assert st == _lib.ERR_UNSUPPORTED and "head_dim 64" in _lib.last_error()
+
+
+def test_dense_decode_route_asks_for_a_workspace_only_where_it_applies():
+    lib = _lib.load()
+    # N <= 4 and S >= 256 (the reference's flash-decode threshold), at most 8 query rows per kv head
+    assert lib.b200fa_fwd_workspace_bytes(C.byref(_desc(N=1, S=4096, Hq=32, Hkv=8))) > 0
+    assert lib.b200fa_fwd_workspace_bytes(C.byref(_desc(N=4, S=256, Hq=4, Hkv=2))) > 0
+    assert lib.b200fa_fwd_workspace_bytes(C.byref(_desc(N=5, S=4096, Hq=4, Hkv=4))) == 0
+    assert lib.b200fa_fwd_workspace_bytes(C.byref(_desc(N=1, S=255, Hq=4, Hkv=4))) == 0
+    assert lib.b200fa_fwd_workspace_bytes(C.byref(_desc(N=4, S=4096, Hq=32, Hkv=8))) == 0          # 16 rows per kv head
+    assert lib.b200fa_fwd_workspace_bytes(C.byref(_desc(N=1, S=4096, Hq=4, Hkv=4, window_left=64))) == 0
+    assert lib.b200fa_fwd_workspace_bytes(C.byref(_desc(N=1, S=4096, Hq=4, Hkv=4, dtype=_lib.F32))) == 0
+
+
+def test_paged_forward_and_helpers_reject_bad_arguments():
+    lib = _lib.load()
+    p = C.c_void_p(256)
+    d = _desc(N=64, Hq=8, Hkv=2)
+    call = lambda dd, bs=16, pages=10, mb=8, ml=100: lib.b200fa_fwd_paged(C.byref(dd), p, p, p, p, p, pages, bs, mb, ml, p, None, None)
+    assert call(d, bs=24) == _lib.ERR_UNSUPPORTED                       # pages of a multiple of 16 tokens
+    assert call(_desc(N=64, Hq=8, Hkv=2, kv_dtype=_lib.I8)) == _lib.ERR_UNSUPPORTED and "gather_dequant" in _lib.last_error()
+    assert call(d, mb=2, ml=100) == _lib.ERR_INVALID_ARG                # max_kv_len beyond max_blocks * block_size
+    assert call(_desc(N=64, Hq=8, Hkv=2, D=256)) == _lib.ERR_UNSUPPORTED
+    assert lib.b200fa_fwd_paged(C.byref(d), p, None, p, p, p, 10, 16, 8, 100, p, None, None) == _lib.ERR_INVALID_ARG
+    # gather + dequantise
+    gd = lib.b200fa_paged_kv_gather_dequant
+    assert gd(p, p, p, p, 1, 2, 128, _lib.BF16, _lib.BF16, 16, 4, 32, p, None) == _lib.ERR_UNSUPPORTED    # pool must be 8-bit
+    assert gd(p, p, p, p, 1, 2, 128, _lib.I8, _lib.F32, 16, 4, 32, p, None) == _lib.ERR_UNSUPPORTED
+    assert gd(p, p, p, p, 1, 2, 72, _lib.I8, _lib.BF16, 16, 4, 32, p, None) == _lib.ERR_INVALID_ARG       # D % 16
+    assert gd(p, None, p, p, 1, 2, 128, _lib.I8, _lib.BF16, 16, 4, 32, p, None) == _lib.ERR_INVALID_ARG
+    assert gd(None, None, None, None, 0, 2, 128, _lib.I8, _lib.BF16, 16, 4, 32, None, None) == _lib.OK
+    # combine of partials
+    cp = lib.b200fa_combine_partials
+    assert cp(p, 2, 8, 130, _lib.BF16, p, None, None) == _lib.ERR_INVALID_ARG                            # D % 4, D <= 128
+    assert cp(p, 2, 8, 128, _lib.F32, p, None, None) == _lib.ERR_UNSUPPORTED
+    assert cp(None, 2, 8, 128, _lib.BF16, p, None, None) == _lib.ERR_INVALID_ARG
+    assert cp(None, 0, 8, 128, _lib.BF16, None, None, None) == _lib.OK
+    # the static decode entry's status reader
+    assert lib.b200fa_decode_paged_static_status(None, None) == _lib.ERR_INVALID_ARG
+
+
+def test_kv_lens_is_refused_where_no_kernel_honours_it():
+    lib = _lib.load()
+    p = C.c_void_p(256)
+    d = _desc(dtype=_lib.F32, kv_dtype=_lib.F32)
+    d.kv_lens = 256
+    assert lib.b200fa_fwd(C.byref(d), p, p, p, p, None, None, 0, None) == _lib.ERR_UNSUPPORTED
+    d = _desc()
+    d.kv_lens = 256
+    assert lib.b200fa_bwd(C.byref(d), p, p, p, p, p, p, p, p, p, p, 1 << 30, None) == _lib.ERR_UNSUPPORTED
+    dv = _desc(B=1)
+    dv.kv_lens = 256
+    assert lib.b200fa_fwd_varlen(C.byref(dv), p, p, p, p, p, 1, 16, 16, p, None, None, 0, None) == _lib.ERR_UNSUPPORTED

@@ -35,6 +35,18 @@ def test_shard_units_config2():
     assert sorted(all_units) == [(b, h) for b in range(4) for h in range(8)]
 
 
+def test_shard_blocks_merge_contiguous_units():
+    # 4 batches x 8 kv heads: one GPU takes every batch whole; 8 GPUs take half a batch each; 3 GPUs cut batches
+    assert par.shard_blocks(4, 8, 1, 0) == [(0, 0, 8), (1, 0, 8), (2, 0, 8), (3, 0, 8)]
+    assert par.shard_blocks(4, 8, 8, 5) == [(2, 4, 8)]
+    seen = []
+    for r in range(3):
+        for b, h0, h1 in par.shard_blocks(4, 8, 3, r):
+            assert 0 <= h0 < h1 <= 8
+            seen += [(b, h) for h in range(h0, h1)]
+    assert seen == [(b, h) for b in range(4) for h in range(8)]
+
+
 def test_shard_views_are_views():
     q, k, v = torch.zeros(2, 8, 4, 16), torch.zeros(2, 2, 6, 16), torch.zeros(2, 2, 6, 16)
     got = list(par.shard_views(q, k, v, 2, 1))

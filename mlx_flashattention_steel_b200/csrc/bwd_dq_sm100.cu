@@ -54,7 +54,7 @@ constexpr int kSmemBytes = kSmemTiles + 256 + 1024;
 enum Bar {
   BAR_Q = 0,
   BAR_KV_FULL = 1,          // + stage
-  BAR_KV_EMPTY = 5,         // + stage: the dQ MMAs of the tile (the last readers of its K and V) have completed
+  BAR_KV_EMPTY = 5,         // + stage: a compute warp has seen the dQ MMAs of the tile (the last readers of its K, V) complete
   BAR_SD_FULL = 9,          // + buffer: S and dP of a tile are complete
   BAR_DS_READY = 12,        // + buffer: count 8, the compute warps have written dS
   BAR_DQ_FINAL = 15,
@@ -175,8 +175,9 @@ bwd_dq_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     // ============================ producer ============================
     if (lane == 0) {
       for (int j = kStages; j < n_tiles; ++j) {
-        // the stage's previous tile (j - kStages) is free when its dQ MMAs have completed; the producer is at most
-        // one completion behind that barrier (the MMA thread needs tile j before it can release this stage again)
+        // the stage's previous tile t = j - kStages is free when its dQ MMAs have completed; a compute warp says so
+        // when it sees the commit that follows them (the one that carries S / dP of tile t + 2).  The producer is at
+        // most one completion behind that barrier: the stage is released again only after tile j has been used
         if (!mbar_wait_bounded(bar(BAR_KV_EMPTY + j % kStages), ((j / kStages) & 1) ^ 1, s_abort)) break;
         load_kv(j);
       }
@@ -191,10 +192,14 @@ bwd_dq_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       constexpr uint64_t kHalfK = (kKVBytes / 2) >> 4, kStageU = kStageBytes >> 4, kVOff = kKVBytes >> 4;
       bool ok = mbar_wait_bounded(bar(BAR_QA_READY), 0, s_abort);
       tc_fence_after();
-      auto issue_sd = [&](int j) -> bool {
+      // S(j), dP(j) into buffer j & 1.  `landed`: the tile's K / V are known to have landed (the compute warps checked
+      // before they handed over dS(j - 2)); the first two tiles wait here
+      auto issue_sd = [&](int j, bool landed) -> bool {
         const int st = j % kStages, b = j % kBufs;
-        if (!mbar_wait_bounded(bar(BAR_KV_FULL + st), (j / kStages) & 1, s_abort)) return false;
-        tc_fence_after();
+        if (!landed) {
+          if (!mbar_wait_bounded(bar(BAR_KV_FULL + st), (j / kStages) & 1, s_abort)) return false;
+          tc_fence_after();
+        }
         const uint64_t kd = kd0 + static_cast<uint64_t>(st) * kStageU, vd = kd + kVOff;
 #pragma unroll
         for (int k = 0; k < HD / 16; ++k)
@@ -202,17 +207,17 @@ bwd_dq_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
 #pragma unroll
         for (int k = 0; k < HD / 16; ++k)
           mma_ts(tmem + cDP + 64 * b, tmem + cDOA + k * 8, vd + (k >> 2) * kHalfK + (k & 3) * 2, id_sd, k > 0 ? 1u : 0u);
-        tc_commit(bar(BAR_SD_FULL + b));
         return true;
       };
-      for (int j = 0; j < kBufs - 1 && j < n_tiles && ok; ++j) ok = issue_sd(j);
+      for (int j = 0; j < kBufs && j < n_tiles && ok; ++j) {
+        ok = issue_sd(j, false);
+        if (ok) tc_commit(bar(BAR_SD_FULL + j));
+      }
+      // One wait and one commit per tile: dQ(j), then S / dP of tile j + 2 into the buffer whose dS those MMAs have
+      // just read (the pipe runs in order), then one commit that both hands tile j + 2 to the compute warps and
+      // releases tile j's K / V stage to the producer.
       for (int j = 0; j < n_tiles && ok; ++j) {
         const int st = j % kStages, b = j % kBufs;
-        // the other buffer is free: dQ(j - 1), the last reader of its dS, was issued in the previous iteration
-        if (j + kBufs - 1 < n_tiles) {
-          ok = issue_sd(j + kBufs - 1);
-          if (!ok) break;
-        }
         if (!mbar_wait_bounded(bar(BAR_DS_READY + b), (j / kBufs) & 1, s_abort)) { ok = false; break; }
         tc_fence_after();
         const uint64_t kmn = kmn0 + static_cast<uint64_t>(st) * kStageU;
@@ -222,7 +227,8 @@ bwd_dq_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         for (int k = 0; k < BN / 16; ++k)
           mma_ts(tmem + cDQ, tmem + cDP + 64 * b + (k >> 1) * 32 + (k & 1) * 8, kmn + k * 128, id_dq,
                  (j > 0 || k > 0) ? 1u : 0u);
-        tc_commit(bar(BAR_KV_EMPTY + st));
+        if (j + kBufs < n_tiles) issue_sd(j + kBufs, true);
+        tc_commit(bar(BAR_SD_FULL + b));
         if (j + 1 == n_tiles) tc_commit(bar(BAR_DQ_FINAL));
       }
     }
@@ -269,6 +275,8 @@ bwd_dq_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       const int k0 = (kt_begin + j) * BN + hf * 32;            // first key of this thread's 32 columns
       if (!__all_sync(0xffffffffu, mbar_wait_bounded(bar(BAR_SD_FULL + b), (j / kBufs) & 1, s_abort))) { ok = false; break; }
       tc_fence_after();
+      // the commit just seen followed dQ(j - 2): that tile's K / V stage can be refilled
+      if (j >= kBufs && wq == 0 && hf == 0 && lane == 0) mbar_arrive(bar(BAR_KV_EMPTY + (j - kBufs) % kStages));
       // FEAT: bit c = mask cell c of this row under the 32 keys from k0 (two cells of 16 keys, else one); the bias of
       // key k0 for this row, in the log2 domain
       unsigned cells = 3u;
@@ -321,6 +329,12 @@ bwd_dq_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       // dS goes back as 16-bit pairs along the key index, inside the 32 columns this warp has just read
       tmem_st16(tmem + lane_base + cDP + 64 * b + hf * 32, pd);
       tc_wait_st();
+      // the MMA thread issues S / dP of tile j + 2 right behind dQ(j) without a wait of its own: see that tile's
+      // K / V land before handing over dS(j)
+      if (j + kBufs < n_tiles) {
+        const int jn = j + kBufs;
+        if (!__all_sync(0xffffffffu, mbar_wait_bounded(bar(BAR_KV_FULL + jn % kStages), (jn / kStages) & 1, s_abort))) { ok = false; break; }
+      }
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(bar(BAR_DS_READY + b));

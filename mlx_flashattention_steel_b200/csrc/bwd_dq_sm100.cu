@@ -5,22 +5,25 @@
 // S^T, dP^T, dV, dK and dQ would need 640 TMEM columns.  Each kernel recomputes P from the forward's lse.  dQ needs
 // no atomics this way: every query tile is owned by one CTA, so the result is bit-reproducible.
 //
-// One CTA = 128 query rows of one query head; it walks the 64-key tiles those rows can see (causal / window tiles
-// outside the band are skipped whole).  Per key tile j, three GEMMs with M = 128 query rows:
-//   S(j)  = Q . K(j)^T      (SS, N = 64, K = 128)  -> TMEM S buffer j % 3
-//   dP(j) = dO . V(j)^T     (SS, N = 64, K = 128)  -> TMEM dP buffer j % 3
-//   8 compute warps (thread = query row; the two warps of a lane quarter split the 64 key columns) form
-//   P = 2^(s - L) and dS = P o (dP - delta) [x (1 - tanh^2) under a soft cap] and write dS back as a 16-bit A operand
-//   over the dP columns they came from.  There are two such sets of 8 warps, one for the even tiles and one for the
-//   odd ones: a warp's step is a chain of latencies (barrier, TMEM load, arithmetic, TMEM store, arrive), and with
-//   one set the tensor pipe was active a third of the time
-//   dQ   += dS(j) . K(j)    (A from TMEM, B = K(j) as an MN-major operand, N = 128)  -> TMEM dQ
-// Issue order SD(0) SD(1) dQ(0) SD(2) dQ(1) ...: the S / dP MMAs of the next tile are queued while the compute warps
-// work on this one.
-// Warp 16 is the TMA producer (Q and dO once, K and V tiles into a four-stage ring), one thread of warp 17
-// issues the MMAs.  dQ leaves TMEM once, scaled, through shared memory (TMA store for the dense layout).
-// TMEM (all 512 columns): [0,128) S0 S1, [128,256) dP0 dP1, [256,384) dQ, [384,512) Q and dO as A operands.  No load uses cluster multicast; every mbarrier wait is
-// bounded and a timeout raises this file's status word (read through b200fa_kernel_status).
+// One CTA = 128 query rows of one query head; it walks the 128-key tiles those rows can see (causal / window tiles
+// outside the band are skipped whole).  Per key tile j, three GEMMs with M = 128 query rows, all of them N = 128
+// (an N = 64 MMA of this shape takes 1.5x its share of the tensor pipe):
+//   S(j)  = Q . K(j)^T      (A = Q in TMEM, B = K(j) K-major)   -> TMEM S
+//   dP(j) = dO . V(j)^T     (A = dO in TMEM, B = V(j) K-major)  -> TMEM dP
+//   dQ   += dS(j) . K(j)    (A = dS in TMEM, B = K(j) as an MN-major operand)  -> TMEM dQ
+// S and dP have one buffer each, and 16 compute warps (thread = query row, a warp = 32 rows x 32 keys) work on a
+// tile in two phases so that neither buffer is held long:
+//   phase A  load S(j) into registers (S is free for tile j + 1 from here on), P' = 2^(s - L) [x (1 - tanh^2)]
+//   phase B  load dP(j), dS = P' o (dP - delta), written back as a 16-bit A operand over the dP columns it came from
+// Issue order per tile j: dQ(j) dP(j+1) | S(j+2).  The chain that sets the pace is dS(j) -> dQ(j), dP(j+1) ->
+// phase B(j+1) -> dS(j+1); S(j+2) runs on the tensor pipe and phase A(j+2) on the compute warps in its shadow.
+// Warp 16 is the TMA producer (Q and dO once; K tiles into a four-stage ring, V tiles into a three-stage ring), one
+// thread of warp 17 issues the MMAs.  Q and dO pass through the last K and V stage into TMEM (16-bit A operands)
+// before those stages join their rings.  dQ leaves TMEM once, scaled, through shared memory (TMA store for the dense
+// layout).
+// TMEM (all 512 columns): [0,128) S, [128,256) dP / dS, [256,384) dQ, [384,512) Q and dO.  No load uses cluster
+// multicast; every mbarrier wait is bounded and a timeout raises this file's status word (read through
+// b200fa_kernel_status).
 #include "common.cuh"
 #include "launch.h"
 #include "tcgen05.cuh"
@@ -34,10 +37,11 @@ namespace {
 
 constexpr int HD = 128;
 constexpr int BM = 128;            // query rows per CTA
-constexpr int BN = 64;             // keys per tile
-constexpr int kStages = 4;         // K / V ring: tiles j .. j + 2 are in use at once, one more is in flight
-constexpr int kBufs = 2;           // S / dP buffers in TMEM
-constexpr int kThreads = 576;      // warps 0-7 compute (even tiles), 8-15 compute (odd tiles), 16 producer, 17 MMA issue
+constexpr int BN = 128;            // keys per tile
+constexpr int kKStages = 4;        // K(j) is read by S(j) two tiles before dQ(j): three tiles in use, one in flight
+constexpr int kVStages = 3;        // V(j) is read once, by dP(j)
+constexpr int kFreeBars = 4;
+constexpr int kThreads = 576;      // warps 0-15 compute, 16 producer, 17 MMA issue
 constexpr int kProducerWarp = 16, kMmaWarp = 17;
 constexpr uint32_t kTmemCols = 512;
 constexpr uint32_t cS = 0, cDP = 128, cDQ = 256;
@@ -45,22 +49,25 @@ constexpr uint32_t cS = 0, cDP = 128, cDQ = 256;
 // MMAs then read only K / V from shared memory, whose bandwidth is what an SS MMA of this shape saturates
 constexpr uint32_t cQA = 384, cDOA = 448;
 
-constexpr int kQBytes = BM * HD * 2;        // 32768: [2 d-halves][128 rows][128 B]
-constexpr int kKVBytes = BN * HD * 2;       // 16384: [2 d-halves][64 rows][128 B]
-constexpr int kStageBytes = 2 * kKVBytes;   // K then V
-constexpr int kSmemTiles = 2 * kQBytes + kStages * kStageBytes;
+constexpr int kTileBytes = BN * HD * 2;     // 32768: [2 d-halves][128 rows][128 B]; Q and dO tiles have the same shape
+constexpr int kSmemTiles = (kKStages + kVStages) * kTileBytes;
 constexpr int kSmemBytes = kSmemTiles + 256 + 1024;
+static_assert(kSmemBytes <= 227 * 1024, "shared memory");
 
 enum Bar {
   BAR_Q = 0,
-  BAR_KV_FULL = 1,          // + stage
-  BAR_KV_EMPTY = 5,         // + stage: a compute warp has seen the dQ MMAs of the tile (the last readers of its K, V) complete
-  BAR_SD_FULL = 9,          // + buffer: S and dP of a tile are complete
-  BAR_DS_READY = 12,        // + buffer: count 8, the compute warps have written dS
-  BAR_DQ_FINAL = 15,
-  BAR_STAGED = 16,          // count 16: the compute warps have staged their dQ rows in shared memory
-  BAR_QA_READY = 17,        // count 16: Q and dO sit in TMEM
-  BAR_COUNT = 18
+  BAR_K_FULL = 1,           // + stage
+  BAR_V_FULL = 5,           // + stage
+  BAR_FREE = 8,             // + (tile % 4): a compute warp has seen dP(tile) complete, and with it dQ(tile - 1): the stages
+                            //   of V(tile) and K(tile - 1) can be refilled
+  BAR_S_FULL = 12,          // S of a tile is complete
+  BAR_DP_FULL = 13,         // dP of a tile (and dQ of the tile before it) is complete
+  BAR_S_FREE = 14,          // count 16: the compute warps hold S in registers
+  BAR_DS_READY = 15,        // count 16: the compute warps have written dS
+  BAR_DQ_FINAL = 16,
+  BAR_STAGED = 17,          // count 16: the compute warps have staged their dQ rows in shared memory
+  BAR_QA_READY = 18,        // count 16: Q and dO sit in TMEM
+  BAR_COUNT = 19
 };
 
 struct DqArgs {
@@ -81,9 +88,10 @@ bwd_dq_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
                     const __grid_constant__ CUtensorMap tmDQ, const DqArgs a) {
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  unsigned char* sQ = smem;
-  unsigned char* sDO = sQ + kQBytes;
-  unsigned char* sKV = sDO + kQBytes;                       // [stage][K | V]
+  unsigned char* sK = smem;                                 // [stage] K tiles
+  unsigned char* sV = sK + kKStages * kTileBytes;           // [stage] V tiles
+  unsigned char* sQ = sK + (kKStages - 1) * kTileBytes;     // Q passes through the last K stage,
+  unsigned char* sDO = sV + (kVStages - 1) * kTileBytes;    // dO through the last V stage
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kSmemTiles);
   uint32_t* s_tmem = reinterpret_cast<uint32_t*>(bars + BAR_COUNT);
   volatile int* s_abort = reinterpret_cast<volatile int*>(s_tmem + 1);
@@ -127,40 +135,47 @@ bwd_dq_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   }
 
   auto bar = [&](int i) -> uint32_t { return smem_u32(&bars[i]); };
-  auto load_kv = [&](int j) {
-    const int st = j % kStages;
-    unsigned char* dst = sKV + st * kStageBytes;
-    mbar_arrive_expect_tx(bar(BAR_KV_FULL + st), kStageBytes);
+  auto load_k = [&](int j) {
+    const int st = j % kKStages;
+    unsigned char* dst = sK + st * kTileBytes;
+    mbar_arrive_expect_tx(bar(BAR_K_FULL + st), kTileBytes);
     const int row = k_begin + (kt_begin + j) * BN;
 #pragma unroll
-    for (int hf = 0; hf < 2; ++hf) {
-      tma_load_4d(smem_u32(dst + hf * (kKVBytes / 2)), &tmK, bar(BAR_KV_FULL + st), 64 * hf, row, kvh, batch);
-      tma_load_4d(smem_u32(dst + kKVBytes + hf * (kKVBytes / 2)), &tmV, bar(BAR_KV_FULL + st), 64 * hf, row, kvh, batch);
-    }
+    for (int hf = 0; hf < 2; ++hf)
+      tma_load_4d(smem_u32(dst + hf * (kTileBytes / 2)), &tmK, bar(BAR_K_FULL + st), 64 * hf, row, kvh, batch);
+  };
+  auto load_v = [&](int j) {
+    const int st = j % kVStages;
+    unsigned char* dst = sV + st * kTileBytes;
+    mbar_arrive_expect_tx(bar(BAR_V_FULL + st), kTileBytes);
+    const int row = k_begin + (kt_begin + j) * BN;
+#pragma unroll
+    for (int hf = 0; hf < 2; ++hf)
+      tma_load_4d(smem_u32(dst + hf * (kTileBytes / 2)), &tmV, bar(BAR_V_FULL + st), 64 * hf, row, kvh, batch);
   };
   if (warp == kProducerWarp && lane == 0) {
     mbar_init(bar(BAR_Q), 1);
-    for (int s = 0; s < kStages; ++s) {
-      mbar_init(bar(BAR_KV_FULL + s), 1);
-      mbar_init(bar(BAR_KV_EMPTY + s), 1);
-    }
-    for (int b = 0; b < kBufs; ++b) {
-      mbar_init(bar(BAR_SD_FULL + b), 1);
-      mbar_init(bar(BAR_DS_READY + b), 8);
-    }
+    for (int st = 0; st < kKStages; ++st) mbar_init(bar(BAR_K_FULL + st), 1);
+    for (int st = 0; st < kVStages; ++st) mbar_init(bar(BAR_V_FULL + st), 1);
+    for (int i = 0; i < kFreeBars; ++i) mbar_init(bar(BAR_FREE + i), 1);
+    mbar_init(bar(BAR_S_FULL), 1);
+    mbar_init(bar(BAR_DP_FULL), 1);
+    mbar_init(bar(BAR_S_FREE), 16);
+    mbar_init(bar(BAR_DS_READY), 16);
     mbar_init(bar(BAR_DQ_FINAL), 1);
     mbar_init(bar(BAR_STAGED), 16);
     mbar_init(bar(BAR_QA_READY), 16);
     *s_abort = 0;
     fence_barrier_init();
     fence_proxy_async();
-    mbar_arrive_expect_tx(bar(BAR_Q), 2 * kQBytes);
+    mbar_arrive_expect_tx(bar(BAR_Q), 2 * kTileBytes);
 #pragma unroll
     for (int hf = 0; hf < 2; ++hf) {
-      tma_load_4d(smem_u32(sQ + hf * (kQBytes / 2)), &tmQ, bar(BAR_Q), 64 * hf, q_begin + q0, head, batch);
-      tma_load_4d(smem_u32(sDO + hf * (kQBytes / 2)), &tmDO, bar(BAR_Q), 64 * hf, q_begin + q0, head, batch);
+      tma_load_4d(smem_u32(sQ + hf * (kTileBytes / 2)), &tmQ, bar(BAR_Q), 64 * hf, q_begin + q0, head, batch);
+      tma_load_4d(smem_u32(sDO + hf * (kTileBytes / 2)), &tmDO, bar(BAR_Q), 64 * hf, q_begin + q0, head, batch);
     }
-    for (int j = 0; j < kStages && j < n_tiles; ++j) load_kv(j);
+    for (int j = 0; j < kKStages - 1 && j < n_tiles; ++j) load_k(j);
+    for (int j = 0; j < kVStages - 1 && j < n_tiles; ++j) load_v(j);
   }
   if (warp == kMmaWarp) {
     tmem_alloc(smem_u32(s_tmem), kTmemCols);
@@ -174,67 +189,90 @@ bwd_dq_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   if (warp == kProducerWarp) {
     // ============================ producer ============================
     if (lane == 0) {
-      for (int j = kStages; j < n_tiles; ++j) {
-        // the stage's previous tile t = j - kStages is free when its dQ MMAs have completed; a compute warp says so
-        // when it sees the commit that follows them (the one that carries S / dP of tile t + 2).  The producer is at
-        // most one completion behind that barrier: the stage is released again only after tile j has been used
-        if (!mbar_wait_bounded(bar(BAR_KV_EMPTY + j % kStages), ((j / kStages) & 1) ^ 1, s_abort)) break;
-        load_kv(j);
+      // the stages Q and dO came through join the rings once both sit in TMEM
+      bool ok = true;
+      if (n_tiles > kVStages - 1) {
+        ok = mbar_wait_bounded(bar(BAR_QA_READY), 0, s_abort);
+        if (ok) {
+          load_v(kVStages - 1);
+          if (n_tiles > kKStages - 1) load_k(kKStages - 1);
+        }
+      }
+      // event t (a compute warp has seen dP(t) complete) frees the stages of V(t) and K(t - 1): tiles t + 3 of both
+      // go there.  Event t + 4, the next on the same barrier, needs V(t + 4), which is loaded after event t + 1.
+      for (int t = 0; t + kVStages < n_tiles && ok; ++t) {
+        ok = mbar_wait_bounded(bar(BAR_FREE + t % kFreeBars), (t / kFreeBars) & 1, s_abort);
+        if (!ok) break;
+        load_v(t + kVStages);
+        if (t >= 1) load_k(t + kKStages - 1);
       }
     }
   } else if (warp == kMmaWarp) {
     // ============================ MMA issue ============================
     if (lane == 0) {
-      const uint32_t id_sd = instr_desc(DT, 0, BM, BN);          // S, dP: B K-major, N = 64
-      const uint32_t id_dq = instr_desc(DT, 1, BM, HD);          // dQ: B = K MN-major, N = 128
-      const uint64_t kd0 = smem_desc(smem_u32(sKV), 16, 1024);
-      const uint64_t kmn0 = smem_desc(smem_u32(sKV), kKVBytes / 2, 1024);
-      constexpr uint64_t kHalfK = (kKVBytes / 2) >> 4, kStageU = kStageBytes >> 4, kVOff = kKVBytes >> 4;
-      bool ok = mbar_wait_bounded(bar(BAR_QA_READY), 0, s_abort);
-      tc_fence_after();
-      // S(j), dP(j) into buffer j & 1.  `landed`: the tile's K / V are known to have landed (the compute warps checked
-      // before they handed over dS(j - 2)); the first two tiles wait here
-      auto issue_sd = [&](int j, bool landed) -> bool {
-        const int st = j % kStages, b = j % kBufs;
-        if (!landed) {
-          if (!mbar_wait_bounded(bar(BAR_KV_FULL + st), (j / kStages) & 1, s_abort)) return false;
-          tc_fence_after();
-        }
-        const uint64_t kd = kd0 + static_cast<uint64_t>(st) * kStageU, vd = kd + kVOff;
+      const uint32_t id_sd = instr_desc(DT, 0, BM, BN);          // S, dP: B K-major, N = 128 keys
+      const uint32_t id_dq = instr_desc(DT, 1, BM, HD);          // dQ: B = K MN-major, N = 128 = head_dim
+      const uint64_t kd0 = smem_desc(smem_u32(sK), 16, 1024);
+      const uint64_t vd0 = smem_desc(smem_u32(sV), 16, 1024);
+      const uint64_t kmn0 = smem_desc(smem_u32(sK), kTileBytes / 2, 1024);
+      constexpr uint64_t kHalf = (kTileBytes / 2) >> 4, kTileU = kTileBytes >> 4;
+      auto issue_s = [&](int j) {
+        const uint64_t kd = kd0 + static_cast<uint64_t>(j % kKStages) * kTileU;
 #pragma unroll
         for (int k = 0; k < HD / 16; ++k)
-          mma_ts(tmem + cS + 64 * b, tmem + cQA + k * 8, kd + (k >> 2) * kHalfK + (k & 3) * 2, id_sd, k > 0 ? 1u : 0u);
-#pragma unroll
-        for (int k = 0; k < HD / 16; ++k)
-          mma_ts(tmem + cDP + 64 * b, tmem + cDOA + k * 8, vd + (k >> 2) * kHalfK + (k & 3) * 2, id_sd, k > 0 ? 1u : 0u);
-        return true;
+          mma_ts(tmem + cS, tmem + cQA + k * 8, kd + (k >> 2) * kHalf + (k & 3) * 2, id_sd, k > 0 ? 1u : 0u);
+        tc_commit(bar(BAR_S_FULL));
       };
-      for (int j = 0; j < kBufs && j < n_tiles && ok; ++j) {
-        ok = issue_sd(j, false);
-        if (ok) tc_commit(bar(BAR_SD_FULL + j));
-      }
-      // One wait and one commit per tile: dQ(j), then S / dP of tile j + 2 into the buffer whose dS those MMAs have
-      // just read (the pipe runs in order), then one commit that both hands tile j + 2 to the compute warps and
-      // releases tile j's K / V stage to the producer.
-      for (int j = 0; j < n_tiles && ok; ++j) {
-        const int st = j % kStages, b = j % kBufs;
-        if (!mbar_wait_bounded(bar(BAR_DS_READY + b), (j / kBufs) & 1, s_abort)) { ok = false; break; }
+      auto issue_dp = [&](int j) {
+        const uint64_t vd = vd0 + static_cast<uint64_t>(j % kVStages) * kTileU;
+#pragma unroll
+        for (int k = 0; k < HD / 16; ++k)
+          mma_ts(tmem + cDP, tmem + cDOA + k * 8, vd + (k >> 2) * kHalf + (k & 3) * 2, id_sd, k > 0 ? 1u : 0u);
+      };
+      // The first K and V tiles are waited for here; every later one by the compute warps, before the arrival that
+      // lets its MMAs be issued (S_FREE of the tile before for K, DS_READY of the tile before for V).
+      bool ok = mbar_wait_bounded(bar(BAR_QA_READY), 0, s_abort) && mbar_wait_bounded(bar(BAR_K_FULL + 0), 0, s_abort);
+      if (ok) {
         tc_fence_after();
-        const uint64_t kmn = kmn0 + static_cast<uint64_t>(st) * kStageU;
-        // A = dS in TMEM: 16 keys = 8 columns; keys 0-31 of the tile at +0, 32-63 at +32 (where the two warps of a
-        // row wrote them).  B = K rows = keys: 16 rows = 2048 B = 128 units.
+        issue_s(0);
+        ok = mbar_wait_bounded(bar(BAR_V_FULL + 0), 0, s_abort);
+      }
+      if (ok) {
+        tc_fence_after();
+        issue_dp(0);
+        tc_commit(bar(BAR_DP_FULL));
+      }
+      if (ok && n_tiles > 1) {
+        ok = mbar_wait_bounded(bar(BAR_S_FREE), 0, s_abort);
+        if (ok) {
+          tc_fence_after();
+          issue_s(1);
+        }
+      }
+      for (int j = 0; j < n_tiles && ok; ++j) {
+        if (!mbar_wait_bounded(bar(BAR_DS_READY), j & 1, s_abort)) { ok = false; break; }
+        tc_fence_after();
+        const uint64_t kmn = kmn0 + static_cast<uint64_t>(j % kKStages) * kTileU;
+        // A = dS in TMEM: 16 keys = 8 columns; keys 32c .. 32c + 31 of the tile at column 32c (where warp column c
+        // wrote them).  B = K rows = keys: 16 rows = 2048 B = 128 units.
 #pragma unroll
         for (int k = 0; k < BN / 16; ++k)
-          mma_ts(tmem + cDQ, tmem + cDP + 64 * b + (k >> 1) * 32 + (k & 1) * 8, kmn + k * 128, id_dq,
-                 (j > 0 || k > 0) ? 1u : 0u);
-        if (j + kBufs < n_tiles) issue_sd(j + kBufs, true);
-        tc_commit(bar(BAR_SD_FULL + b));
+          mma_ts(tmem + cDQ, tmem + cDP + (k >> 1) * 32 + (k & 1) * 8, kmn + k * 128, id_dq, (j > 0 || k > 0) ? 1u : 0u);
+        // dP(j + 1) overwrites the dS those MMAs read: the pipe runs in order
+        if (j + 1 < n_tiles) issue_dp(j + 1);
+        tc_commit(bar(BAR_DP_FULL));
         if (j + 1 == n_tiles) tc_commit(bar(BAR_DQ_FINAL));
+        if (j + 2 < n_tiles) {
+          if (!mbar_wait_bounded(bar(BAR_S_FREE), (j + 1) & 1, s_abort)) { ok = false; break; }
+          tc_fence_after();
+          issue_s(j + 2);
+        }
       }
     }
   } else {
     // ============================ compute warps 0-15 ============================
-    const int wq = warp & 3, hf = (warp >> 2) & 1, set = warp >> 3;   // TMEM lane quarter, key-column half, tile parity
+    const int wq = warp & 3, cq = warp >> 2;          // TMEM lane quarter (rows), 32-key column quarter of a tile
+    const int hf = cq & 1, set = cq >> 1;              // for the Q / dO copy: d-half, Q or dO
     const int rloc = wq * 32 + lane;
     const int row = q0 + rloc;
     const uint32_t lane_base = static_cast<uint32_t>(wq * 32) << 16;
@@ -256,7 +294,7 @@ bwd_dq_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     bool ok = __all_sync(0xffffffffu, mbar_wait_bounded(bar(BAR_Q), 0, s_abort));
     if (ok) {
       // this row's 128 bytes of d-half hf of Q (set 0) or dO (set 1) -> 32 TMEM columns of the A operand
-      const uint32_t rowa = smem_u32(set == 0 ? sQ : sDO) + hf * (kQBytes / 2) + rloc * 128;
+      const uint32_t rowa = smem_u32(set == 0 ? sQ : sDO) + hf * (kTileBytes / 2) + rloc * 128;
       uint32_t qr[32];
 #pragma unroll
       for (int c = 0; c < 8; ++c)
@@ -270,13 +308,21 @@ bwd_dq_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       __syncwarp();
       if (lane == 0) mbar_arrive(bar(BAR_QA_READY));
     }
-    for (int j = set; j < n_tiles && ok; j += 2) {
-      const int b = j % kBufs;
-      const int k0 = (kt_begin + j) * BN + hf * 32;            // first key of this thread's 32 columns
-      if (!__all_sync(0xffffffffu, mbar_wait_bounded(bar(BAR_SD_FULL + b), (j / kBufs) & 1, s_abort))) { ok = false; break; }
+    for (int j = 0; j < n_tiles && ok; ++j) {
+      const int k0 = (kt_begin + j) * BN + cq * 32;            // first key of this thread's 32 columns
+      // ---------------- phase A: S -> P' ----------------
+      if (!__all_sync(0xffffffffu, mbar_wait_bounded(bar(BAR_S_FULL), j & 1, s_abort))) { ok = false; break; }
       tc_fence_after();
-      // the commit just seen followed dQ(j - 2): that tile's K / V stage can be refilled
-      if (j >= kBufs && wq == 0 && hf == 0 && lane == 0) mbar_arrive(bar(BAR_KV_EMPTY + (j - kBufs) % kStages));
+      uint32_t rs[32];
+      tmem_ld32(tmem + lane_base + cS + cq * 32, rs);
+      tc_wait_ld();
+      // S(j + 1) is issued when every warp holds S(j): see that tile's K land first
+      if (j + 1 < n_tiles) {
+        if (!__all_sync(0xffffffffu, mbar_wait_bounded(bar(BAR_K_FULL + (j + 1) % kKStages), ((j + 1) / kKStages) & 1, s_abort))) { ok = false; break; }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar(BAR_S_FREE));
       // FEAT: bit c = mask cell c of this row under the 32 keys from k0 (two cells of 16 keys, else one); the bias of
       // key k0 for this row, in the log2 domain
       unsigned cells = 3u;
@@ -290,19 +336,14 @@ bwd_dq_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         }
         ab = alibi_l2 * static_cast<float>(k0 - (row + off));
       }
-      uint32_t rs[32], rd[32];
-      tmem_ld32(tmem + lane_base + cS + 64 * b + hf * 32, rs);
-      tmem_ld32(tmem + lane_base + cDP + 64 * b + hf * 32, rd);
-      tc_wait_ld();
       // visible keys of this row, relative to k0: [lo_rel, hi_rel]
       const int hi_rel = (p.causal ? min(S - 1, row + off) : S - 1) - k0;
       const int lo_rel = WIN ? row + off - p.window_left - k0 : 0;
       const bool need_mask = __any_sync(0xffffffffu, hi_rel < 31 || (WIN && lo_rel > 0));
-      uint32_t pd[16];
+      float pr[32];                                            // P, times (1 - tanh^2) under a soft cap
 #pragma unroll
       for (int i = 0; i < 32; i += 2) {
         const float2 sv = make_float2(__uint_as_float(rs[i]), __uint_as_float(rs[i + 1]));
-        const float2 dv = make_float2(__uint_as_float(rd[i]), __uint_as_float(rd[i + 1]));
         float2 t, dcap;
         if constexpr (CAP) {
           const float2 th = make_float2(cap_tanh(sv.x * cap_in, precise_tanh), cap_tanh(sv.y * cap_in, precise_tanh));
@@ -322,34 +363,47 @@ bwd_dq_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
           if (i > hi_rel || (WIN && i < lo_rel)) pe.x = 0.f;
           if (i + 1 > hi_rel || (WIN && i + 1 < lo_rel)) pe.y = 0.f;
         }
-        float2 dsv = __fmul2_rn(pe, __fadd2_rn(dv, nD2));
-        if constexpr (CAP) dsv = __fmul2_rn(dsv, dcap);
+        if constexpr (CAP) pe = __fmul2_rn(pe, dcap);
+        pr[i] = pe.x;
+        pr[i + 1] = pe.y;
+      }
+      // ---------------- phase B: dP -> dS ----------------
+      if (!__all_sync(0xffffffffu, mbar_wait_bounded(bar(BAR_DP_FULL), j & 1, s_abort))) { ok = false; break; }
+      tc_fence_after();
+      // the commit just seen also followed dQ(j - 1): V(j)'s and K(j - 1)'s stages can be refilled
+      if (warp == 0 && lane == 0) mbar_arrive(bar(BAR_FREE + j % kFreeBars));
+      uint32_t rd[32];
+      tmem_ld32(tmem + lane_base + cDP + cq * 32, rd);
+      tc_wait_ld();
+      uint32_t pd[16];
+#pragma unroll
+      for (int i = 0; i < 32; i += 2) {
+        const float2 dv = make_float2(__uint_as_float(rd[i]), __uint_as_float(rd[i + 1]));
+        const float2 dsv = __fmul2_rn(make_float2(pr[i], pr[i + 1]), __fadd2_rn(dv, nD2));
         pd[i >> 1] = pack16q<DT>(dsv.x, dsv.y);
       }
       // dS goes back as 16-bit pairs along the key index, inside the 32 columns this warp has just read
-      tmem_st16(tmem + lane_base + cDP + 64 * b + hf * 32, pd);
+      tmem_st16(tmem + lane_base + cDP + cq * 32, pd);
       tc_wait_st();
-      // the MMA thread issues S / dP of tile j + 2 right behind dQ(j) without a wait of its own: see that tile's
-      // K / V land before handing over dS(j)
-      if (j + kBufs < n_tiles) {
-        const int jn = j + kBufs;
-        if (!__all_sync(0xffffffffu, mbar_wait_bounded(bar(BAR_KV_FULL + jn % kStages), (jn / kStages) & 1, s_abort))) { ok = false; break; }
+      // dP(j + 1) follows dQ(j) on the MMA thread without a wait of its own: see that tile's V land first
+      if (j + 1 < n_tiles) {
+        if (!__all_sync(0xffffffffu, mbar_wait_bounded(bar(BAR_V_FULL + (j + 1) % kVStages), ((j + 1) / kVStages) & 1, s_abort))) { ok = false; break; }
       }
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(bar(BAR_DS_READY + b));
+      if (lane == 0) mbar_arrive(bar(BAR_DS_READY));
     }
 
-    // ---- epilogue: dQ * scale -> 16-bit, through shared memory (the Q / dO tiles are free: every MMA has completed) ----
+    // ---- epilogue: dQ * scale -> 16-bit, through shared memory ----
     if (ok) ok = __all_sync(0xffffffffu, mbar_wait_bounded(bar(BAR_DQ_FINAL), 0, s_abort));
     if (ok) {
       tc_fence_after();
-      // this warp's 32 of the 128 columns: d-half hf, 32-column half `set` of it; staged as [d-half][row][128 B],
-      // 16-byte chunks swizzled by row
+      // this warp's 32 of the 128 columns: d-half dh, 32-column half c of it; staged as [d-half][row][128 B] in the
+      // first K stage (every load has been consumed), 16-byte chunks swizzled by row
       {
-        const int c = set;
+        const int dh = cq >> 1, c = cq & 1;
         uint32_t o[32];
-        tmem_ld32(tmem + lane_base + cDQ + hf * 64 + c * 32, o);
+        tmem_ld32(tmem + lane_base + cDQ + dh * 64 + c * 32, o);
         tc_wait_ld();
 #pragma unroll
         for (int i = 0; i < 32; i += 8) {
@@ -360,11 +414,11 @@ bwd_dq_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
           v.w = pack16q<DT>(__uint_as_float(o[i + 6]) * p.scale, __uint_as_float(o[i + 7]) * p.scale);
           const int chunk = c * 4 + (i >> 3);
           if (a.tma_store) {
-            *reinterpret_cast<uint4*>(sQ + hf * (kQBytes / 2) + rloc * 128 + ((chunk ^ (rloc & 7)) << 4)) = v;
+            *reinterpret_cast<uint4*>(sK + dh * (kTileBytes / 2) + rloc * 128 + ((chunk ^ (rloc & 7)) << 4)) = v;
           } else if (row < N) {
             uint16_t* drow = reinterpret_cast<uint16_t*>(p.dq) + batch * p.dq_bs + head * p.dq_hs +
                              static_cast<int64_t>(q_begin + row) * p.dq_rs;
-            *reinterpret_cast<uint4*>(drow + hf * 64 + chunk * 8) = v;
+            *reinterpret_cast<uint4*>(drow + dh * 64 + chunk * 8) = v;
           }
         }
       }
@@ -375,7 +429,7 @@ bwd_dq_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         if (tid == 0 && mbar_wait_bounded(bar(BAR_STAGED), 0, s_abort)) {
 #pragma unroll
           for (int h2 = 0; h2 < 2; ++h2)
-            tma_store_4d(&tmDQ, smem_u32(sQ + h2 * (kQBytes / 2)), 64 * h2, q0, head, batch);
+            tma_store_4d(&tmDQ, smem_u32(sK + h2 * (kTileBytes / 2)), 64 * h2, q0, head, batch);
           tma_store_commit();
           tma_store_wait<0>();
         }

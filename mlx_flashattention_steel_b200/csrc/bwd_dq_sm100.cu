@@ -367,6 +367,11 @@ bwd_dq_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         pr[i] = pe.x;
         pr[i + 1] = pe.y;
       }
+      // dP(j + 1) follows dQ(j) on the MMA thread without a wait of its own: see that tile's V land before DS_READY(j).
+      // Checked here, where it costs nothing: the exponentials above are still in flight
+      if (j + 1 < n_tiles) {
+        if (!__all_sync(0xffffffffu, mbar_wait_bounded(bar(BAR_V_FULL + (j + 1) % kVStages), ((j + 1) / kVStages) & 1, s_abort))) { ok = false; break; }
+      }
       // ---------------- phase B: dP -> dS ----------------
       if (!__all_sync(0xffffffffu, mbar_wait_bounded(bar(BAR_DP_FULL), j & 1, s_abort))) { ok = false; break; }
       tc_fence_after();
@@ -385,10 +390,6 @@ bwd_dq_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       // dS goes back as 16-bit pairs along the key index, inside the 32 columns this warp has just read
       tmem_st16(tmem + lane_base + cDP + cq * 32, pd);
       tc_wait_st();
-      // dP(j + 1) follows dQ(j) on the MMA thread without a wait of its own: see that tile's V land first
-      if (j + 1 < n_tiles) {
-        if (!__all_sync(0xffffffffu, mbar_wait_bounded(bar(BAR_V_FULL + (j + 1) % kVStages), ((j + 1) / kVStages) & 1, s_abort))) { ok = false; break; }
-      }
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(bar(BAR_DS_READY));

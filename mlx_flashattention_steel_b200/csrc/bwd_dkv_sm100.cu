@@ -3,20 +3,23 @@
 // The counterpart of the reference's dK/dV kernel (csrc/mfa_steel_bwd.cpp:765-1293); dQ is computed by
 // bwd_dq_sm100.cu.  One persistent CTA per SM takes work items from a global counter; an item is a tile of 128 keys of
 // one kv head, for which the CTA walks the query heads of the GQA group and the 128-row query tiles that can see those
-// keys.  Per query tile, four GEMMs with M = 128 key rows, the query tile handled as two halves x of 64 queries:
-//   S^T_x  = K . Q_x^T     (SS, N = 64, K = 128)                    -> TMEM [0,64) / [128,192)
-//   dP^T_x = V . dO_x^T    (SS, N = 64, K = 128)                    -> TMEM [64,128) / [192,256)
-//   8 compute warps (thread = key row, two warps per 32 rows splitting the query columns) turn these into
-//   P^T = 2^(s - L) and dS^T = P^T o (dP^T - delta) [x (1 - tanh^2) under a soft cap], written back as 16-bit A
-//   operands over the columns they came from
-//   dV += P^T_x . dO_x     (A from TMEM, B = dO as an MN-major operand, N = 128)   -> TMEM [256,384)
-//   dK += dS^T_x . Q_x     (A from TMEM, B = Q MN-major, N = 128)                  -> TMEM [384,512)
-// All 512 TMEM columns are in use, so K and V stay in shared memory as A operands.  The two query halves have their
-// own S^T / dP^T columns: the MMAs of one half (and the next tile's S^T / dP^T) run while the compute warps work on
-// the other half.  Warp 8 is the TMA producer (K and V once per item; Q and dO double-buffered, with -L and -delta of
-// the query rows staged beside them), one thread of warp 9 issues the MMAs.  dK / dV leave TMEM once per item, through
-// shared memory as whole rows.  No load uses cluster multicast; every mbarrier wait is bounded and a timeout raises
-// this file's status word (read through b200fa_kernel_status).
+// keys.  Per query tile (128 queries), four GEMMs with M = 128 key rows, every MMA N = 128 (an N = 64 MMA of this
+// shape takes 1.5x its share of the tensor pipe):
+//   S^T  = K . Q^T      (SS, K = 128)                                   -> TMEM [0,128)
+//   dP^T = V . dO^T     (SS, K = 128)                                   -> TMEM [128,256)
+//   dV  += P^T . dO     (A from TMEM, B = dO as an MN-major operand)    -> TMEM [256,384)
+//   dK  += dS^T . Q     (A from TMEM, B = Q MN-major)                   -> TMEM [384,512)
+// All 512 TMEM columns are in use, so K and V stay in shared memory as A operands and S^T / dP^T have one buffer
+// each.  16 compute warps (thread = key row, a warp = 32 keys x 32 queries) work in two phases:
+//   phase A  S^T -> P^T = 2^(s - L), written back as a 16-bit A operand over the columns it came from (P_READY),
+//            with P^T [x (1 - tanh^2) under a soft cap] kept in registers
+//   phase B  dP^T -> dS^T = P^T o (dP^T - delta), written back the same way (DS_READY)
+// and the MMA thread alternates two groups: on P_READY dV(t) S^T(t+1), on DS_READY dK(t) dP^T(t+1); each group runs
+// on the tensor pipe while the compute warps are in the other phase.  Warp 16 is the TMA producer (K and V once per
+// item; Q and dO double-buffered, with -L and -delta of the query rows staged beside them), one thread of warp 17
+// issues the MMAs.  dK / dV leave TMEM once per item, through shared memory as whole rows.  No load uses cluster
+// multicast; every mbarrier wait is bounded and a timeout raises this file's status word (read through
+// b200fa_kernel_status).
 #include <type_traits>
 
 #include "common.cuh"
@@ -32,19 +35,40 @@ namespace {
 
 constexpr int HD = 128;
 constexpr int BK = 128;      // keys per item (TMEM lanes)
-constexpr int BQ = 128;      // queries per step, as two halves of 64
-constexpr int kThreads = 320;       // warps 0-7 compute, 8 producer, 9 MMA issue
+constexpr int BQ = 128;      // queries per step
+constexpr int kThreads = 576;       // warps 0-15 compute, 16 producer, 17 MMA issue
+constexpr int kProducerWarp = 16, kMmaWarp = 17;
 constexpr uint32_t kTmemCols = 512;
-constexpr uint32_t cST = 0, cDPT = 64, cDV = 256, cDK = 384;     // S^T_x at cST + 128x, dP^T_x at cDPT + 128x
+constexpr uint32_t cST = 0, cDPT = 128, cDV = 256, cDK = 384;
 
 constexpr int kTileBytes = 128 * HD * 2;                 // 32768: one [2 d-halves][128 rows][128 B] tile
 constexpr int kHalfBytes = kTileBytes / 2;
-constexpr int kStatBytes = 2 * 2 * BQ * 4;               // L and delta, two stages
-constexpr int kSmemTiles = 2 * kTileBytes + 4 * kTileBytes;        // K, V, Q x2, dO x2 = 196608
-constexpr int kSmemBytes = kSmemTiles + kStatBytes + 256 + 1024;
+constexpr int kQStages = 3;      // Q(t) is read by S^T(t) one group before P_READY(t - 1)'s dV and by dK(t) last: three in use
+constexpr int kDOStages = 2;     // dO(t): dP^T(t), then dV(t)
+constexpr int kStatBytes = 2 * 2 * BQ * 4;               // -L and -delta of a query tile, two slots
+constexpr int kSmemTiles = (2 + kQStages + kDOStages) * kTileBytes;        // K, V, Q x3, dO x2 = 229376
+constexpr int kSmemUsed = kSmemTiles + kStatBytes + 256;
+// All of the 227 KB a CTA can have: the tiles need a 1024-byte boundary, so the dynamic window may start up to
+// kSmemBytes - kSmemUsed bytes off one (checked at run time; a CTA that finds less room raises status bit 1)
+constexpr int kSmemBytes = 227 * 1024;
+static_assert(kSmemUsed <= kSmemBytes, "shared memory");
 
 // BAR_KV lives for the whole kernel; the others are set up again for every work item
-enum Bar { BAR_KV = 0, BAR_Q_FULL = 1, BAR_Q_EMPTY = 3, BAR_ST_DONE = 5 /* + half */, BAR_PD_READY = 7 /* + half */, BAR_ACC_DONE = 9, BAR_COUNT = 10 };
+enum Bar {
+  BAR_KV = 0,
+  BAR_Q_FULL = 1,        // + stage (3)
+  BAR_DO_FULL = 4,       // + stage (2)
+  BAR_STAT_FULL = 6,     // + slot (2): -L and -delta of a query tile are written
+  BAR_Q_EMPTY = 8,       // + stage: a compute warp has seen dK of the stage's tile complete (at the start of the next
+                         //   tile's phase B; every warp has then finished the tile's phase B, so its stat slot is free too)
+  BAR_DO_EMPTY = 11,     // + stage: a compute warp has seen dV of the stage's tile complete (start of the next phase A)
+  BAR_ST_FULL = 13,      // S^T of a tile is complete (and dV of the tile before it)
+  BAR_DPT_FULL = 14,     // dP^T of a tile is complete (and dK of the tile before it)
+  BAR_P_READY = 15,      // count 16: P^T is written
+  BAR_DS_READY = 16,     // count 16: dS^T is written
+  BAR_ACC_DONE = 17,
+  BAR_COUNT = 18
+};
 
 struct DkvArgs {
   BwdParams p;
@@ -86,10 +110,10 @@ bwd_dkv_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   unsigned char* sK = smem;
   unsigned char* sV = sK + kTileBytes;
-  unsigned char* sQ = sV + kTileBytes;                 // [2 stages][2 d-halves][128][128 B]
-  unsigned char* sDO = sQ + 2 * kTileBytes;
-  float* sL = reinterpret_cast<float*>(smem + kSmemTiles);      // [2][BQ]
-  float* sDel = sL + 2 * BQ;                                    // [2][BQ]
+  unsigned char* sQ = sV + kTileBytes;                 // [3 stages][2 d-halves][128][128 B]
+  unsigned char* sDO = sQ + kQStages * kTileBytes;     // [2 stages]
+  float* sL = reinterpret_cast<float*>(smem + kSmemTiles);      // [2 slots][BQ]
+  float* sDel = sL + 2 * BQ;                                    // [2 slots][BQ]
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kSmemTiles + kStatBytes);
   uint32_t* s_tmem = reinterpret_cast<uint32_t*>(bars + BAR_COUNT);
   volatile int* s_abort = reinterpret_cast<volatile int*>(s_tmem + 1);
@@ -99,6 +123,10 @@ bwd_dkv_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
   const BwdParams& p = a.p;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   auto bar = [&](int i) -> uint32_t { return smem_u32(&bars[i]); };
+  if (smem + kSmemUsed > smem_raw + kSmemBytes) {          // CTA-uniform: the window starts too far off a 1024-byte boundary
+    if (tid == 0) atomicOr(&g_kernel_status, 2);
+    return;
+  }
 
   // Next item that has keys (grid cells beyond a sequence's end are skipped), decoded into slot `sl` of s_work for
   // every role to read; index -1 when the list is exhausted.  Run by one thread.
@@ -125,14 +153,14 @@ bwd_dkv_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
     o[0] = -1;
     return -1;
   };
-  if (warp == 8 && lane == 0) {
+  if (warp == kProducerWarp && lane == 0) {
     mbar_init(bar(BAR_KV), 1);
     *s_abort = 0;
     fence_barrier_init();
     fence_proxy_async();
     fetch_next(0);
   }
-  if (warp == 9) {
+  if (warp == kMmaWarp) {
     tmem_alloc(smem_u32(s_tmem), kTmemCols);
     tmem_relinquish();
   }
@@ -159,26 +187,37 @@ bwd_dkv_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
   if (n_iter > 0) ++kv_uses;
 
   auto load_q = [&](int it) {
-    const int st = it & 1;
+    const int st = it % kQStages;
     const int hq = kvh * p.gqa + it / nm, m = m_begin + it % nm;
-    mbar_expect_tx(bar(BAR_Q_FULL + st), 2 * kTileBytes);
+    mbar_arrive_expect_tx(bar(BAR_Q_FULL + st), kTileBytes);
 #pragma unroll
-    for (int hf = 0; hf < 2; ++hf) {
+    for (int hf = 0; hf < 2; ++hf)
       tma_load_4d(smem_u32(sQ + st * kTileBytes + hf * kHalfBytes), &tmQ, bar(BAR_Q_FULL + st), 64 * hf, q_begin + m * BQ, hq, bb);
-      tma_load_4d(smem_u32(sDO + st * kTileBytes + hf * kHalfBytes), &tmDO, bar(BAR_Q_FULL + st), 64 * hf, q_begin + m * BQ, hq, bb);
-    }
   };
-  if (warp == 8 && lane == 0) {
+  auto load_do = [&](int it) {
+    const int st = it % kDOStages;
+    const int hq = kvh * p.gqa + it / nm, m = m_begin + it % nm;
+    mbar_arrive_expect_tx(bar(BAR_DO_FULL + st), kTileBytes);
+#pragma unroll
+    for (int hf = 0; hf < 2; ++hf)
+      tma_load_4d(smem_u32(sDO + st * kTileBytes + hf * kHalfBytes), &tmDO, bar(BAR_DO_FULL + st), 64 * hf, q_begin + m * BQ, hq, bb);
+  };
+  if (warp == kProducerWarp && lane == 0) {
     if (w > 0)
       for (int i = BAR_Q_FULL; i < BAR_COUNT; ++i) mbar_inval(bar(i));    // nobody waits or arrives between items
-    for (int s = 0; s < 2; ++s) {
+    for (int s = 0; s < kQStages; ++s) {
       mbar_init(bar(BAR_Q_FULL + s), 1);
       mbar_init(bar(BAR_Q_EMPTY + s), 1);
     }
-    for (int x = 0; x < 2; ++x) {
-      mbar_init(bar(BAR_ST_DONE + x), 1);
-      mbar_init(bar(BAR_PD_READY + x), 8);  // one arrive per compute warp
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(bar(BAR_DO_FULL + s), 1);
+      mbar_init(bar(BAR_DO_EMPTY + s), 1);
+      mbar_init(bar(BAR_STAT_FULL + s), 1);
     }
+    mbar_init(bar(BAR_ST_FULL), 1);
+    mbar_init(bar(BAR_DPT_FULL), 1);
+    mbar_init(bar(BAR_P_READY), 16);        // one arrive per compute warp
+    mbar_init(bar(BAR_DS_READY), 16);
     mbar_init(bar(BAR_ACC_DONE), 1);
     fence_barrier_init();
     fence_proxy_async();
@@ -190,21 +229,25 @@ bwd_dkv_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
         tma_load_4d(smem_u32(sV + hf * kHalfBytes), &tmV, bar(BAR_KV), 64 * hf, k_begin + n0, kvh, bb);
       }
       load_q(0);
-      if (n_iter > 1) load_q(1);
+      load_do(0);
+      if (n_iter > 1) {
+        load_q(1);
+        load_do(1);
+      }
+      if (n_iter > 2) load_q(2);
     }
   }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
 
-  if (warp == 8) {
+  if (warp == kProducerWarp) {
     // ============================ producer ============================
-    for (int it = 0; it < n_iter; ++it) {
-      const int st = it & 1;
+    // -L and -delta of tile `it`'s 128 query rows -> registers (four rows per lane); rows beyond N (or without any
+    // visible key) get L = +inf so that their P is exactly zero
+    float Lr[4], dr[4];
+    auto read_stats = [&](int it) {
       const int hq = kvh * p.gqa + it / nm, m = m_begin + it % nm;
-      // -L and -delta of the 128 query rows ride with the Q tile; rows beyond N (or without any visible key)
-      // get L = +inf so that their P is exactly zero
-      float Lr[4], dr[4];
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
         const int row = m * BQ + lane * 4 + i;
@@ -217,221 +260,260 @@ bwd_dkv_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
           if (Lr[i] == -INFINITY) Lr[i] = INFINITY;
         }
       }
-      if (it >= 2) {
-        if (!__all_sync(0xffffffffu, mbar_wait_bounded(bar(BAR_Q_EMPTY + st), ((it >> 1) & 1) ^ 1, s_abort))) break;
-        if (lane == 0) load_q(it);
-      }
+    };
+    auto write_stats = [&](int it) {
+      const int sl = it & 1;
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
-        sL[st * BQ + lane * 4 + i] = -Lr[i];            // stored negated: the compute loop adds them
-        sDel[st * BQ + lane * 4 + i] = -dr[i];
+        sL[sl * BQ + lane * 4 + i] = -Lr[i];            // stored negated: the compute loop adds them
+        sDel[sl * BQ + lane * 4 + i] = -dr[i];
       }
       __syncwarp();
-      if (lane == 0) mbar_arrive(bar(BAR_Q_FULL + st));
+      if (lane == 0) mbar_arrive(bar(BAR_STAT_FULL + sl));
       __syncwarp();
+    };
+    for (int it = 0; it < 2 && it < n_iter; ++it) {
+      read_stats(it);
+      write_stats(it);
+    }
+    // Tile e's dO stage is released at the start of phase A of tile e + 1, its Q stage and stat slot at the start of
+    // phase B of tile e + 1: dO(e + 2), then Q(e + 3) and the stats of tile e + 2, go there.  Each barrier's next
+    // completion needs the tile loaded here, so the producer is never more than one completion behind.
+    for (int e = 0; e + 2 < n_iter; ++e) {
+      read_stats(e + 2);
+      if (!__all_sync(0xffffffffu, mbar_wait_bounded(bar(BAR_DO_EMPTY + (e & 1)), (e >> 1) & 1, s_abort))) break;
+      if (lane == 0) load_do(e + 2);
+      if (!__all_sync(0xffffffffu, mbar_wait_bounded(bar(BAR_Q_EMPTY + e % kQStages), (e / kQStages) & 1, s_abort))) break;
+      if (lane == 0 && e + 3 < n_iter) load_q(e + 3);
+      write_stats(e + 2);
     }
     // the next item, for every role to read after the end-of-item sync
     if (lane == 0) fetch_next((w + 1) & 1);
-  } else if (warp == 9) {
+  } else if (warp == kMmaWarp) {
    if (lane == 0 && n_iter > 0) {
     // ============================ MMA issue ============================
-    // Per query tile t and query half x: [S^T_x, dP^T_x] -> (compute) -> [dV += P^T_x.dO_x, dK += dS^T_x.Q_x].
-    //   ST/DPT a,b (t=0) | PD_a -> dV_a dK_a, ST/DPT a (t+1) | PD_b -> dV_b dK_b, ST/DPT b (t+1) | ...
-    const uint32_t id_st = instr_desc(DT, 0, 128, 64);     // S^T, dP^T of one half: B K-major, N = 64
-    const uint32_t id_mn = instr_desc(DT, 1, 128, HD);     // dV, dK: B MN-major, N = 128
+    //   S^T(0) dP^T(0) | P_READY(t) -> dV(t) S^T(t+1) | DS_READY(t) -> dK(t) dP^T(t+1) | ...
+    const uint32_t id_st = instr_desc(DT, 0, 128, BQ);     // S^T, dP^T: B K-major, N = 128 queries
+    const uint32_t id_mn = instr_desc(DT, 1, 128, HD);     // dV, dK: B MN-major, N = 128 = head_dim
     const uint64_t kd = smem_desc(smem_u32(sK), 16, 1024), vd = smem_desc(smem_u32(sV), 16, 1024);
     const uint64_t qd0 = smem_desc(smem_u32(sQ), 16, 1024), dod0 = smem_desc(smem_u32(sDO), 16, 1024);
     const uint64_t qmn0 = smem_desc(smem_u32(sQ), kHalfBytes, 1024), domn0 = smem_desc(smem_u32(sDO), kHalfBytes, 1024);
-    constexpr uint64_t kTileU = kTileBytes >> 4, kHalfU = kHalfBytes >> 4, kHalfRowsU = (64 * 128) >> 4;
+    constexpr uint64_t kTileU = kTileBytes >> 4, kHalfU = kHalfBytes >> 4;
     bool ok = mbar_wait_bounded(bar(BAR_KV), kv_par, s_abort);
-    tc_fence_after();
-    // S^T_x and dP^T_x of tile `it`: A = the K / V rows (K-major, two d-halves), B rows = the 64 queries of half x
-    auto issue_stdp = [&](int it, int x) {
-      const int st = it & 1;
-      const uint64_t qd = qd0 + st * kTileU + x * kHalfRowsU, dod = dod0 + st * kTileU + x * kHalfRowsU;
+    // A = the K / V rows (K-major, two d-halves), B rows = the 128 queries of tile `it`
+    auto issue_st = [&](int it) {
+      const uint64_t qd = qd0 + (it % kQStages) * kTileU;
 #pragma unroll
       for (int k = 0; k < HD / 16; ++k)
-        mma_ss(tmem + cST + 128 * x, kd + (k >> 2) * kHalfU + (k & 3) * 2, qd + (k >> 2) * kHalfU + (k & 3) * 2, id_st,
-               k > 0 ? 1u : 0u);
-#pragma unroll
-      for (int k = 0; k < HD / 16; ++k)
-        mma_ss(tmem + cDPT + 128 * x, vd + (k >> 2) * kHalfU + (k & 3) * 2, dod + (k >> 2) * kHalfU + (k & 3) * 2, id_st,
-               k > 0 ? 1u : 0u);
-      tc_commit(bar(BAR_ST_DONE + x));
+        mma_ss(tmem + cST, kd + (k >> 2) * kHalfU + (k & 3) * 2, qd + (k >> 2) * kHalfU + (k & 3) * 2, id_st, k > 0 ? 1u : 0u);
+      tc_commit(bar(BAR_ST_FULL));
     };
+    auto issue_dpt = [&](int it) {
+      const uint64_t dod = dod0 + (it & 1) * kTileU;
+#pragma unroll
+      for (int k = 0; k < HD / 16; ++k)
+        mma_ss(tmem + cDPT, vd + (k >> 2) * kHalfU + (k & 3) * 2, dod + (k >> 2) * kHalfU + (k & 3) * 2, id_st, k > 0 ? 1u : 0u);
+      tc_commit(bar(BAR_DPT_FULL));
+    };
+    // the first Q and dO tiles are waited for here, every later one by the compute warps before the arrival that
+    // lets its MMAs be issued
     if (ok) ok = mbar_wait_bounded(bar(BAR_Q_FULL), 0, s_abort);
     if (ok) {
       tc_fence_after();
-      issue_stdp(0, 0);
-      issue_stdp(0, 1);
+      issue_st(0);
+      ok = mbar_wait_bounded(bar(BAR_DO_FULL), 0, s_abort);
+    }
+    if (ok) {
+      tc_fence_after();
+      issue_dpt(0);
     }
     for (int it = 0; it < n_iter && ok; ++it) {
-      const int st = it & 1;
+      const uint64_t qmn = qmn0 + (it % kQStages) * kTileU, domn = domn0 + (it & 1) * kTileU;
+      // the compute warps vouch, before they arrive here, that the next tile's Q has landed (DS_READY: its dO)
+      if (!mbar_wait_bounded(bar(BAR_P_READY), it & 1, s_abort)) { ok = false; break; }
+      tc_fence_after();
+      // A in TMEM: 8 columns per 16 queries; queries 32c .. 32c + 31 of the tile at column 32c (where warp column c
+      // wrote them); B rows = queries, 16 rows = 128 units
 #pragma unroll
-      for (int x = 0; x < 2; ++x) {
-        // the compute warps vouch, before they arrive here, that the next tile's Q / dO have landed (half a)
-        if (!mbar_wait_bounded(bar(BAR_PD_READY + x), it & 1, s_abort)) { ok = false; break; }
-        tc_fence_after();
-        const uint64_t qmn = qmn0 + st * kTileU + x * kHalfRowsU, domn = domn0 + st * kTileU + x * kHalfRowsU;
-        // A in TMEM: 8 columns per 16 queries; queries 0-31 of the half at +0, 32-63 at +32 (where the two warps of a
-        // row wrote them); B rows = queries, 16 rows = 128 units
+      for (int k = 0; k < BQ / 16; ++k)
+        mma_ts(tmem + cDV, tmem + cST + (k >> 1) * 32 + (k & 1) * 8, domn + k * 128, id_mn, (it > 0 || k > 0) ? 1u : 0u);
+      // S^T(it + 1) overwrites the P^T those MMAs read: the pipe runs in order
+      if (it + 1 < n_iter) issue_st(it + 1);
+      if (!mbar_wait_bounded(bar(BAR_DS_READY), it & 1, s_abort)) { ok = false; break; }
+      tc_fence_after();
 #pragma unroll
-        for (int k = 0; k < 4; ++k)
-          mma_ts(tmem + cDV, tmem + cST + 128 * x + (k >> 1) * 32 + (k & 1) * 8, domn + k * 128, id_mn,
-                 (it > 0 || x > 0 || k > 0) ? 1u : 0u);
-#pragma unroll
-        for (int k = 0; k < 4; ++k)
-          mma_ts(tmem + cDK, tmem + cDPT + 128 * x + (k >> 1) * 32 + (k & 1) * 8, qmn + k * 128, id_mn,
-                 (it > 0 || x > 0 || k > 0) ? 1u : 0u);
-        if (x == 1) tc_commit(bar(BAR_Q_EMPTY + st));
-        // the buffers of half x are free again (the MMAs above read them in pipe order before anything issued now)
-        if (it + 1 < n_iter) issue_stdp(it + 1, x);
-      }
+      for (int k = 0; k < BQ / 16; ++k)
+        mma_ts(tmem + cDK, tmem + cDPT + (k >> 1) * 32 + (k & 1) * 8, qmn + k * 128, id_mn, (it > 0 || k > 0) ? 1u : 0u);
+      if (it + 1 < n_iter) issue_dpt(it + 1);
     }
     if (ok) tc_commit(bar(BAR_ACC_DONE));
    }
   } else {
-    // ============================ compute warps 0-7 ============================
-    const int wq = warp & 3, hf = warp >> 2;                 // TMEM lane quarter, column half
+    // ============================ compute warps 0-15 ============================
+    const int wq = warp & 3, cq = warp >> 2;                 // TMEM lane quarter (keys), 32-query column quarter
     const int rloc = wq * 32 + lane;                         // key row inside the tile
     const int key = n0 + rloc;
     const uint32_t lane_base = static_cast<uint32_t>(wq * 32) << 16;
     if (n_iter == 0) {
       // no query sees these keys: dK = dV = 0
       if (key < S) {
-        const int64_t o = bb * p.dk_bs + kvh * p.dk_hs + static_cast<int64_t>(k_begin + key) * p.dk_rs + hf * 64;
+        const int64_t o = bb * p.dk_bs + kvh * p.dk_hs + static_cast<int64_t>(k_begin + key) * p.dk_rs + cq * 32;
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
+        for (int i = 0; i < 4; ++i) {
           reinterpret_cast<uint4*>(reinterpret_cast<uint16_t*>(p.dk) + o)[i] = make_uint4(0u, 0u, 0u, 0u);
           reinterpret_cast<uint4*>(reinterpret_cast<uint16_t*>(p.dv) + o)[i] = make_uint4(0u, 0u, 0u, 0u);
         }
       }
     } else {
     bool ok = true;
+    const int q0l = cq * 32;                               // first query (inside the tile) of this warp's 32 columns
+    const float2 c2 = make_float2(p.scale_log2, p.scale_log2);
+    const float cap_in = CAP ? p.scale / p.softcap : 0.f, cap_out = p.softcap * kLog2e;
+    const bool precise_tanh = p.softcap >= kPreciseTanhMinCap;
+    const int wlo = WIN ? off - p.window_left : 0;         // window: key visible iff key >= qrow + wlo
     for (int it = 0; it < n_iter && ok; ++it) {
-      const int st = it & 1;
+      const int sl = it & 1;
       const int m = m_begin + it % nm;
-      if (!__all_sync(0xffffffffu, mbar_wait_bounded(bar(BAR_Q_FULL + st), (it >> 1) & 1, s_abort))) { ok = false; break; }
-      const uint32_t Ls = opaque_u32(smem_u32(sL + st * BQ)), Ds = Ls + 2 * BQ * 4;
+      if (!__all_sync(0xffffffffu, mbar_wait_bounded(bar(BAR_STAT_FULL + sl), (it >> 1) & 1, s_abort))) { ok = false; break; }
+      const uint32_t Ls = opaque_u32(smem_u32(sL + sl * BQ)), Ds = Ls + 2 * BQ * 4;
       const bool need_mask = (n0 + BK > S) || (p.causal && (n0 + BK - 1 > m * BQ + off)) ||
                              (WIN && (n0 < m * BQ + BQ - 1 + off - p.window_left));
-      const int wlo = WIN ? off - p.window_left : 0;    // window: key visible iff key >= qrow + wlo
-      const float2 c2 = make_float2(p.scale_log2, p.scale_log2);
       const float alibi_l2 = (FEAT && p.alibi != nullptr) ? p.alibi[kvh * p.gqa + it / nm] * kLog2e : 0.f;
-      const float cap_in = CAP ? p.scale / p.softcap : 0.f, cap_out = p.softcap * kLog2e;
-      const bool precise_tanh = p.softcap >= kPreciseTanhMinCap;
+      // FEAT: the mask cell of (these 32 queries, this key) and the bias of the first of them, in the log2 domain
+      bool cell_on = true;
+      float ab = 0.f;
+      if constexpr (FEAT) {
+        const int qrow0 = m * BQ + q0l;
+        if (p.bmask != nullptr)
+          cell_on = key < S && p.bmask[static_cast<int64_t>(min(qrow0, N - 1) / p.bm_bq) * p.bm_nk + key / p.bm_bk] != 0;
+        ab = alibi_l2 * static_cast<float>(key - off - qrow0);
+      }
 
-      auto run_half = [&](int x, auto masked) {
-        const int q0l = x * 64 + hf * 32;                  // first query (inside the tile) of this warp's 32 columns
-        // FEAT: the mask cell of (these 32 queries, this key) and the bias of the first of them, in the log2 domain
-        bool cell_on = true;
-        float ab = 0.f;
-        if constexpr (FEAT) {
-          const int qrow0 = m * BQ + q0l;
-          if (p.bmask != nullptr)
-            cell_on = key < S && p.bmask[static_cast<int64_t>(min(qrow0, N - 1) / p.bm_bq) * p.bm_nk + key / p.bm_bk] != 0;
-          ab = alibi_l2 * static_cast<float>(key - off - qrow0);
-        }
-        uint32_t rs[32], rd[32];
-        tmem_ld32(tmem + lane_base + cST + 128 * x + hf * 32, rs);
-        tmem_ld32(tmem + lane_base + cDPT + 128 * x + hf * 32, rd);
+      // ---------------- phase A: S^T -> P^T (TMEM, 16-bit) and P^T [x (1 - tanh^2)] (registers) ----------------
+      if (!__all_sync(0xffffffffu, mbar_wait_bounded(bar(BAR_ST_FULL), it & 1, s_abort))) { ok = false; break; }
+      tc_fence_after();
+      // the commit just seen also followed dV(it - 1), the last reader of the other dO stage
+      if (it >= 1 && warp == 0 && lane == 0) mbar_arrive(bar(BAR_DO_EMPTY + ((it - 1) & 1)));
+      float pr[32];
+      {
+        uint32_t rs[32];
+        tmem_ld32(tmem + lane_base + cST + q0l, rs);
         tc_wait_ld();
-        uint32_t pp[16], pd[16];
+        uint32_t pp[16];
+        auto phase_a = [&](auto masked) {
+#pragma unroll
+          for (int i = 0; i < 32; i += 4) {
+            const float4 nL = lds_f4(Ls + (q0l + i) * 4);      // -L of four queries
+#pragma unroll
+            for (int e = 0; e < 4; e += 2) {
+              const float2 sv = make_float2(__uint_as_float(rs[i + e]), __uint_as_float(rs[i + e + 1]));
+              const float2 nl = e == 0 ? make_float2(nL.x, nL.y) : make_float2(nL.z, nL.w);
+              float2 t;
+              [[maybe_unused]] float2 dcap;
+              if constexpr (CAP) {
+                const float2 th = make_float2(cap_tanh(sv.x * cap_in, precise_tanh), cap_tanh(sv.y * cap_in, precise_tanh));
+                t = __ffma2_rn(th, make_float2(cap_out, cap_out), nl);
+                dcap = __ffma2_rn(make_float2(-th.x, -th.y), th, make_float2(1.f, 1.f));
+              } else {
+                t = __ffma2_rn(sv, c2, nl);
+              }
+              if constexpr (FEAT) {
+                t = __fadd2_rn(t, make_float2(fmaf(-alibi_l2, static_cast<float>(i + e), ab), fmaf(-alibi_l2, static_cast<float>(i + e + 1), ab)));
+              }
+              float2 pe = make_float2(fast_exp2(t.x), fast_exp2(t.y));
+              if constexpr (FEAT) {
+                if (!cell_on) pe = make_float2(0.f, 0.f);
+              }
+              if constexpr (decltype(masked)::value) {
+                const int qrow = m * BQ + q0l + i + e;
+                const bool kin = key < S;
+                if (!(kin && (!p.causal || key <= qrow + off) && (!WIN || key >= qrow + wlo))) pe.x = 0.f;
+                if (!(kin && (!p.causal || key <= qrow + 1 + off) && (!WIN || key >= qrow + 1 + wlo))) pe.y = 0.f;
+              }
+              pp[(i + e) >> 1] = pack16k<DT>(pe.x, pe.y);
+              if constexpr (CAP) pe = __fmul2_rn(pe, dcap);
+              pr[i + e] = pe.x;
+              pr[i + e + 1] = pe.y;
+            }
+          }
+        };
+        if (need_mask) phase_a(std::true_type{}); else phase_a(std::false_type{});
+        // P^T goes back as 16-bit pairs along the query index, inside the 32 columns this warp has just read
+        tmem_st16(tmem + lane_base + cST + q0l, pp);
+        tc_wait_st();
+      }
+      // on behalf of the MMA thread: the next tile's Q has landed (its S^T follows this tile's dV)
+      if (it + 1 < n_iter &&
+          !__all_sync(0xffffffffu, mbar_wait_bounded(bar(BAR_Q_FULL + (it + 1) % kQStages), ((it + 1) / kQStages) & 1, s_abort))) { ok = false; break; }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar(BAR_P_READY));
+
+      // ---------------- phase B: dP^T -> dS^T ----------------
+      if (!__all_sync(0xffffffffu, mbar_wait_bounded(bar(BAR_DPT_FULL), it & 1, s_abort))) { ok = false; break; }
+      tc_fence_after();
+      // the commit just seen also followed dK(it - 1), the last reader of that tile's Q stage; and every warp has
+      // finished phase B(it - 1), the last reader of its stat slot
+      if (it >= 1 && warp == 0 && lane == 0) mbar_arrive(bar(BAR_Q_EMPTY + (it - 1) % kQStages));
+      {
+        uint32_t rd[32];
+        tmem_ld32(tmem + lane_base + cDPT + q0l, rd);
+        tc_wait_ld();
+        uint32_t pd[16];
 #pragma unroll
         for (int i = 0; i < 32; i += 4) {
-          const float4 nL = lds_f4(Ls + (q0l + i) * 4);      // -L of four queries
-          const float4 nD = lds_f4(Ds + (q0l + i) * 4);      // -delta
-#pragma unroll
-          for (int e = 0; e < 4; e += 2) {
-            const float2 sv = make_float2(__uint_as_float(rs[i + e]), __uint_as_float(rs[i + e + 1]));
-            const float2 dv = make_float2(__uint_as_float(rd[i + e]), __uint_as_float(rd[i + e + 1]));
-            const float2 nl = e == 0 ? make_float2(nL.x, nL.y) : make_float2(nL.z, nL.w);
-            const float2 nd = e == 0 ? make_float2(nD.x, nD.y) : make_float2(nD.z, nD.w);
-            float2 t, dcap;
-            if constexpr (CAP) {
-              const float2 th = make_float2(cap_tanh(sv.x * cap_in, precise_tanh), cap_tanh(sv.y * cap_in, precise_tanh));
-              t = __ffma2_rn(th, make_float2(cap_out, cap_out), nl);
-              dcap = __ffma2_rn(make_float2(-th.x, -th.y), th, make_float2(1.f, 1.f));
-            } else {
-              t = __ffma2_rn(sv, c2, nl);
-            }
-            if constexpr (FEAT) {
-              t = __fadd2_rn(t, make_float2(fmaf(-alibi_l2, static_cast<float>(i + e), ab), fmaf(-alibi_l2, static_cast<float>(i + e + 1), ab)));
-            }
-            float2 pe = make_float2(fast_exp2(t.x), fast_exp2(t.y));
-            if constexpr (FEAT) {
-              if (!cell_on) pe = make_float2(0.f, 0.f);
-            }
-            if constexpr (decltype(masked)::value) {
-              const int qrow = m * BQ + q0l + i + e;
-              const bool kin = key < S;
-              if (!(kin && (!p.causal || key <= qrow + off) && (!WIN || key >= qrow + wlo))) pe.x = 0.f;
-              if (!(kin && (!p.causal || key <= qrow + 1 + off) && (!WIN || key >= qrow + 1 + wlo))) pe.y = 0.f;
-            }
-            float2 dsv = __fmul2_rn(pe, __fadd2_rn(dv, nd));
-            if constexpr (CAP) dsv = __fmul2_rn(dsv, dcap);
-            pp[(i + e) >> 1] = pack16k<DT>(pe.x, pe.y);
-            pd[(i + e) >> 1] = pack16k<DT>(dsv.x, dsv.y);
-          }
+          const float4 nD = lds_f4(Ds + (q0l + i) * 4);      // -delta of four queries
+          const float2 d0 = __fmul2_rn(make_float2(pr[i], pr[i + 1]),
+                                       __fadd2_rn(make_float2(__uint_as_float(rd[i]), __uint_as_float(rd[i + 1])), make_float2(nD.x, nD.y)));
+          const float2 d1 = __fmul2_rn(make_float2(pr[i + 2], pr[i + 3]),
+                                       __fadd2_rn(make_float2(__uint_as_float(rd[i + 2]), __uint_as_float(rd[i + 3])), make_float2(nD.z, nD.w)));
+          pd[i >> 1] = pack16k<DT>(d0.x, d0.y);
+          pd[(i >> 1) + 1] = pack16k<DT>(d1.x, d1.y);
         }
-        // P^T and dS^T go back as 16-bit pairs along the query index, inside the 32 columns this warp has just read
-        // (the other warp of these rows may still be reading its own 32)
-        tmem_st16(tmem + lane_base + cST + 128 * x + hf * 32, pp);
-        tmem_st16(tmem + lane_base + cDPT + 128 * x + hf * 32, pd);
-      };
-
-#pragma unroll
-      for (int x = 0; x < 2; ++x) {
-        if (!__all_sync(0xffffffffu, mbar_wait_bounded(bar(BAR_ST_DONE + x), it & 1, s_abort))) { ok = false; break; }
-        tc_fence_after();
-        if (need_mask) run_half(x, std::true_type{}); else run_half(x, std::false_type{});
+        tmem_st16(tmem + lane_base + cDPT + q0l, pd);
         tc_wait_st();
-        // on behalf of the MMA thread: half a vouches for the next tile's Q / dO (its S^T / dP^T are issued right
-        // after this half's dV / dK).  The barrier cannot be more than one completion ahead: the next fill of that
-        // stage needs this arrival first.
-        if (x == 0 && it + 1 < n_iter &&
-            !__all_sync(0xffffffffu, mbar_wait_bounded(bar(BAR_Q_FULL + ((it + 1) & 1)), ((it + 1) >> 1) & 1, s_abort))) { ok = false; break; }
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(bar(BAR_PD_READY + x));
       }
+      // on behalf of the MMA thread: the next tile's dO has landed (its dP^T follows this tile's dK)
+      if (it + 1 < n_iter &&
+          !__all_sync(0xffffffffu, mbar_wait_bounded(bar(BAR_DO_FULL + ((it + 1) & 1)), ((it + 1) >> 1) & 1, s_abort))) { ok = false; break; }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar(BAR_DS_READY));
     }
 
     if (ok) ok = __all_sync(0xffffffffu, mbar_wait_bounded(bar(BAR_ACC_DONE), 0, s_abort));
-    // dK, dV: rows = keys, this warp's d-half hf (64 of the 128 columns).  The tiles go through shared memory (the
-    // Q stages, which nothing reads any more: dK in stage 0, dV in stage 1) so that each store instruction writes
-    // whole 128-byte rows.
+    // dK, dV: rows = keys, this warp's 32 of the 128 columns.  The tiles go through shared memory (the Q stages,
+    // which nothing reads any more: dK in stage 0, dV in stage 1) so that each store instruction writes whole
+    // 128-byte rows.
     if (ok) {
       tc_fence_after();
+      const int dh = cq >> 1, c = cq & 1;                // d-half, 32-column half of it
+      uint32_t rk[32], rv[32];
+      tmem_ld32(tmem + lane_base + cDK + cq * 32, rk);
+      tmem_ld32(tmem + lane_base + cDV + cq * 32, rv);
+      tc_wait_ld();
+      const uint32_t srow = smem_u32(sQ) + dh * kHalfBytes + rloc * 128;
 #pragma unroll
-      for (int c = 0; c < 2; ++c) {
-        uint32_t rk[32], rv[32];
-        tmem_ld32(tmem + lane_base + cDK + hf * 64 + c * 32, rk);
-        tmem_ld32(tmem + lane_base + cDV + hf * 64 + c * 32, rv);
-        tc_wait_ld();
-        const uint32_t srow = smem_u32(sQ) + hf * kHalfBytes + rloc * 128;
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          const int i = 8 * j;
-          const uint32_t o = static_cast<uint32_t>(((c * 4 + j) ^ (rloc & 7)) << 4);
-          sts_v4(srow + o, pack16k<DT>(__uint_as_float(rk[i]) * p.scale, __uint_as_float(rk[i + 1]) * p.scale),
-                 pack16k<DT>(__uint_as_float(rk[i + 2]) * p.scale, __uint_as_float(rk[i + 3]) * p.scale),
-                 pack16k<DT>(__uint_as_float(rk[i + 4]) * p.scale, __uint_as_float(rk[i + 5]) * p.scale),
-                 pack16k<DT>(__uint_as_float(rk[i + 6]) * p.scale, __uint_as_float(rk[i + 7]) * p.scale));
-          sts_v4(srow + kTileBytes + o, pack16k<DT>(__uint_as_float(rv[i]), __uint_as_float(rv[i + 1])),
-                 pack16k<DT>(__uint_as_float(rv[i + 2]), __uint_as_float(rv[i + 3])),
-                 pack16k<DT>(__uint_as_float(rv[i + 4]), __uint_as_float(rv[i + 5])),
-                 pack16k<DT>(__uint_as_float(rv[i + 6]), __uint_as_float(rv[i + 7])));
-        }
+      for (int j = 0; j < 4; ++j) {
+        const int i = 8 * j;
+        const uint32_t o = static_cast<uint32_t>(((c * 4 + j) ^ (rloc & 7)) << 4);
+        sts_v4(srow + o, pack16k<DT>(__uint_as_float(rk[i]) * p.scale, __uint_as_float(rk[i + 1]) * p.scale),
+               pack16k<DT>(__uint_as_float(rk[i + 2]) * p.scale, __uint_as_float(rk[i + 3]) * p.scale),
+               pack16k<DT>(__uint_as_float(rk[i + 4]) * p.scale, __uint_as_float(rk[i + 5]) * p.scale),
+               pack16k<DT>(__uint_as_float(rk[i + 6]) * p.scale, __uint_as_float(rk[i + 7]) * p.scale));
+        sts_v4(srow + kTileBytes + o, pack16k<DT>(__uint_as_float(rv[i]), __uint_as_float(rv[i + 1])),
+               pack16k<DT>(__uint_as_float(rv[i + 2]), __uint_as_float(rv[i + 3])),
+               pack16k<DT>(__uint_as_float(rv[i + 4]), __uint_as_float(rv[i + 5])),
+               pack16k<DT>(__uint_as_float(rv[i + 6]), __uint_as_float(rv[i + 7])));
       }
     }
-    // all eight compute warps pass here, whatever happened before (a named barrier has no time-out)
-    asm volatile("bar.sync 1, 256;\n" ::: "memory");
+    // all sixteen compute warps pass here, whatever happened before (a named barrier has no time-out)
+    asm volatile("bar.sync 1, 512;\n" ::: "memory");
     if (ok) {
       // 128 rows x 2 d-halves x 8 chunks of 16 bytes per tensor; a warp instruction covers four whole half-rows
 #pragma unroll
-      for (int r8 = 0; r8 < 8; ++r8) {
-        const int i = r8 * 256 + tid;
+      for (int r4 = 0; r4 < 4; ++r4) {
+        const int i = r4 * 512 + tid;
         const int h = i >> 10, r = (i >> 3) & 127, c = i & 7;
         const uint32_t sa = smem_u32(sQ) + h * kHalfBytes + r * 128 + static_cast<uint32_t>((c ^ (r & 7)) << 4);
         uint4 vk, vv;
@@ -459,7 +541,7 @@ bwd_dkv_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
   __syncwarp();
   tc_fence_before();
   __syncthreads();
-  if (warp == 9) {
+  if (warp == kMmaWarp) {
     tc_fence_after();
     tmem_dealloc(tmem, kTmemCols);
   }

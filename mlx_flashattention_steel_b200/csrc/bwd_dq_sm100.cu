@@ -13,15 +13,18 @@
 //   dQ   += dS(j) . K(j)    (A = dS in TMEM, B = K(j) as an MN-major operand)  -> TMEM dQ
 // S and dP have one buffer each, and 16 compute warps (thread = query row, a warp = 32 rows x 32 keys) work on a
 // tile in two phases so that neither buffer is held long:
-//   phase A  load S(j) into registers (S is free for tile j + 1 from here on), P' = 2^(s - L) [x (1 - tanh^2)]
-//   phase B  load dP(j), dS = P' o (dP - delta), written back as a 16-bit A operand over the dP columns it came from
-// Issue order per tile j: dQ(j) dP(j+1) | S(j+2).  The chain that sets the pace is dS(j) -> dQ(j), dP(j+1) ->
-// phase B(j+1) -> dS(j+1); S(j+2) runs on the tensor pipe and phase A(j+2) on the compute warps in its shadow.
-// Warp 16 is the TMA producer (Q and dO once; K tiles into a four-stage ring, V tiles into a three-stage ring), one
-// thread of warp 17 issues the MMAs.  Q and dO pass through the last K and V stage into TMEM (16-bit A operands)
-// before those stages join their rings.  dQ leaves TMEM once, scaled, through shared memory (TMA store for the dense
-// layout).
-// TMEM (all 512 columns): [0,128) S, [128,256) dP / dS, [256,384) dQ, [384,512) Q and dO.  No load uses cluster
+//   phase A  load S(j) into registers (S is free for tile j + 2 from here on: S_FREE), P' = 2^(s - L) [x (1 - tanh^2)]:
+//            bound by the special-function unit
+//   phase B  load dP(j) into registers (dP is free for tile j + 1: DP_FREE), dS = P' o (dP - delta), written as a
+//            16-bit A operand into columns of its own (DS_READY)
+// The MMA thread issues, as each arrival comes in: dP(j+1) on DP_FREE(j), dQ(j) on DS_READY(j), S(j+2) on
+// S_FREE(j+1).  Nothing on the tensor pipe waits for the compute warps' arithmetic: the pace is set by whichever is
+// longer, the 24 MMAs of a tile or phase A + phase B.
+// Warp 16 is the TMA producer (Q and dO once; K tiles into a four-stage ring, V tiles into a two-stage ring), one
+// thread of warp 17 issues the MMAs.  Q passes through the last K stage into TMEM (a 16-bit A operand); dO stays in
+// shared memory (the dP MMAs are SS: TMEM has no room for it beside dS).  dQ leaves TMEM once, scaled, through
+// shared memory (TMA store for the dense layout).
+// TMEM (all 512 columns): [0,128) S, [128,256) dP, [256,384) dQ, [384,448) Q, [448,512) dS.  No load uses cluster
 // multicast; every mbarrier wait is bounded and a timeout raises this file's status word (read through
 // b200fa_kernel_status).
 #include "common.cuh"
@@ -39,35 +42,35 @@ constexpr int HD = 128;
 constexpr int BM = 128;            // query rows per CTA
 constexpr int BN = 128;            // keys per tile
 constexpr int kKStages = 4;        // K(j) is read by S(j) two tiles before dQ(j): three tiles in use, one in flight
-constexpr int kVStages = 3;        // V(j) is read once, by dP(j)
-constexpr int kFreeBars = 4;
-constexpr int kThreads = 576;      // warps 0-15 compute, 16 producer, 17 MMA issue
-constexpr int kProducerWarp = 16, kMmaWarp = 17;
+constexpr int kVStages = 2;        // V(j) is read once, by dP(j)
+constexpr int kThreads = 640;      // warps 0-15 compute, 16 producer, 17 / 18 / 19 MMA issue (dP / S / dQ)
+constexpr int kProducerWarp = 16, kMmaWarp = 17, kMmaWarpS = 18, kMmaWarpQ = 19;
 constexpr uint32_t kTmemCols = 512;
 constexpr uint32_t cS = 0, cDP = 128, cDQ = 256;
-// Q and dO rows as 16-bit A operands (two elements per column), copied from shared memory once per CTA: the S / dP
-// MMAs then read only K / V from shared memory, whose bandwidth is what an SS MMA of this shape saturates
-constexpr uint32_t cQA = 384, cDOA = 448;
+// Q rows as a 16-bit A operand (two elements per column), copied from shared memory once per CTA; dS of the current
+// tile, 16 keys per 8 columns
+constexpr uint32_t cQA = 384, cDS = 448;
 
 constexpr int kTileBytes = BN * HD * 2;     // 32768: [2 d-halves][128 rows][128 B]; Q and dO tiles have the same shape
-constexpr int kSmemTiles = (kKStages + kVStages) * kTileBytes;
+constexpr int kSmemTiles = (kKStages + kVStages + 1) * kTileBytes;     // + dO
 constexpr int kSmemBytes = kSmemTiles + 256 + 1024;
 static_assert(kSmemBytes <= 227 * 1024, "shared memory");
 
 enum Bar {
-  BAR_Q = 0,
-  BAR_K_FULL = 1,           // + stage
-  BAR_V_FULL = 5,           // + stage
-  BAR_FREE = 8,             // + (tile % 4): a compute warp has seen dP(tile) complete, and with it dQ(tile - 1): the stages
-                            //   of V(tile) and K(tile - 1) can be refilled
-  BAR_S_FULL = 12,          // S of a tile is complete
-  BAR_DP_FULL = 13,         // dP of a tile (and dQ of the tile before it) is complete
-  BAR_S_FREE = 14,          // count 16: the compute warps hold S in registers
-  BAR_DS_READY = 15,        // count 16: the compute warps have written dS
-  BAR_DQ_FINAL = 16,
-  BAR_STAGED = 17,          // count 16: the compute warps have staged their dQ rows in shared memory
-  BAR_QA_READY = 18,        // count 16: Q and dO sit in TMEM
-  BAR_COUNT = 19
+  BAR_Q = 0,                // Q and dO have landed
+  BAR_K_FULL = 1,           // + stage (4)
+  BAR_V_FULL = 5,           // + stage (2)
+  BAR_K_FREE = 7,           // + stage: a compute warp has seen dQ of the stage's tile complete
+  BAR_V_FREE = 11,          // + stage: a compute warp has seen dP of the stage's tile complete
+  BAR_S_FULL = 13,          // S of a tile is complete
+  BAR_DP_FULL = 14,         // dP of a tile is complete
+  BAR_DQ_DONE = 15,         // the dQ MMAs of a tile are complete: its dS columns and its K stage are free
+  BAR_S_FREE = 16,          // count 16: the compute warps hold S in registers
+  BAR_DP_FREE = 17,         // count 16: the compute warps hold dP in registers
+  BAR_DS_READY = 18,        // count 16: the compute warps have written dS
+  BAR_STAGED = 19,          // count 16: the compute warps have staged their dQ rows in shared memory
+  BAR_QA_READY = 20,        // count 16: Q sits in TMEM
+  BAR_COUNT = 21
 };
 
 struct DqArgs {
@@ -90,8 +93,8 @@ bwd_dq_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   unsigned char* sK = smem;                                 // [stage] K tiles
   unsigned char* sV = sK + kKStages * kTileBytes;           // [stage] V tiles
-  unsigned char* sQ = sK + (kKStages - 1) * kTileBytes;     // Q passes through the last K stage,
-  unsigned char* sDO = sV + (kVStages - 1) * kTileBytes;    // dO through the last V stage
+  unsigned char* sDO = sV + kVStages * kTileBytes;          // dO, resident: the A operand of the dP MMAs
+  unsigned char* sQ = sK + (kKStages - 1) * kTileBytes;     // Q passes through the last K stage
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kSmemTiles);
   uint32_t* s_tmem = reinterpret_cast<uint32_t*>(bars + BAR_COUNT);
   volatile int* s_abort = reinterpret_cast<volatile int*>(s_tmem + 1);
@@ -157,12 +160,14 @@ bwd_dq_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     mbar_init(bar(BAR_Q), 1);
     for (int st = 0; st < kKStages; ++st) mbar_init(bar(BAR_K_FULL + st), 1);
     for (int st = 0; st < kVStages; ++st) mbar_init(bar(BAR_V_FULL + st), 1);
-    for (int i = 0; i < kFreeBars; ++i) mbar_init(bar(BAR_FREE + i), 1);
+    for (int st = 0; st < kKStages; ++st) mbar_init(bar(BAR_K_FREE + st), 1);
+    for (int st = 0; st < kVStages; ++st) mbar_init(bar(BAR_V_FREE + st), 1);
     mbar_init(bar(BAR_S_FULL), 1);
     mbar_init(bar(BAR_DP_FULL), 1);
+    mbar_init(bar(BAR_DQ_DONE), 1);
     mbar_init(bar(BAR_S_FREE), 16);
+    mbar_init(bar(BAR_DP_FREE), 16);
     mbar_init(bar(BAR_DS_READY), 16);
-    mbar_init(bar(BAR_DQ_FINAL), 1);
     mbar_init(bar(BAR_STAGED), 16);
     mbar_init(bar(BAR_QA_READY), 16);
     *s_abort = 0;
@@ -175,7 +180,7 @@ bwd_dq_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       tma_load_4d(smem_u32(sDO + hf * (kTileBytes / 2)), &tmDO, bar(BAR_Q), 64 * hf, q_begin + q0, head, batch);
     }
     for (int j = 0; j < kKStages - 1 && j < n_tiles; ++j) load_k(j);
-    for (int j = 0; j < kVStages - 1 && j < n_tiles; ++j) load_v(j);
+    for (int j = 0; j < kVStages && j < n_tiles; ++j) load_v(j);
   }
   if (warp == kMmaWarp) {
     tmem_alloc(smem_u32(s_tmem), kTmemCols);
@@ -189,22 +194,26 @@ bwd_dq_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   if (warp == kProducerWarp) {
     // ============================ producer ============================
     if (lane == 0) {
-      // the stages Q and dO came through join the rings once both sit in TMEM
+      // the stage Q came through joins the K ring once Q sits in TMEM
       bool ok = true;
-      if (n_tiles > kVStages - 1) {
+      if (n_tiles > kKStages - 1) {
         ok = mbar_wait_bounded(bar(BAR_QA_READY), 0, s_abort);
-        if (ok) {
-          load_v(kVStages - 1);
-          if (n_tiles > kKStages - 1) load_k(kKStages - 1);
-        }
+        if (ok) load_k(kKStages - 1);
       }
-      // event t (a compute warp has seen dP(t) complete) frees the stages of V(t) and K(t - 1): tiles t + 3 of both
-      // go there.  Event t + 4, the next on the same barrier, needs V(t + 4), which is loaded after event t + 1.
-      for (int t = 0; t + kVStages < n_tiles && ok; ++t) {
-        ok = mbar_wait_bounded(bar(BAR_FREE + t % kFreeBars), (t / kFreeBars) & 1, s_abort);
-        if (!ok) break;
-        load_v(t + kVStages);
-        if (t >= 1) load_k(t + kKStages - 1);
+      // In time order: V(e)'s stage is released in phase B of tile e, K(e - 1)'s in phase B of tile e (when dQ(e - 1)
+      // is seen complete).  Each barrier's next completion needs the tile loaded here, so the producer is never
+      // more than one completion behind.
+      for (int e = 0; e < n_tiles && ok; ++e) {
+        if (e + kVStages < n_tiles) {
+          ok = mbar_wait_bounded(bar(BAR_V_FREE + e % kVStages), (e / kVStages) & 1, s_abort);
+          if (!ok) break;
+          load_v(e + kVStages);
+        }
+        if (e >= 1 && e - 1 + kKStages < n_tiles) {
+          ok = mbar_wait_bounded(bar(BAR_K_FREE + (e - 1) % kKStages), ((e - 1) / kKStages) & 1, s_abort);
+          if (!ok) break;
+          load_k(e - 1 + kKStages);
+        }
       }
     }
   } else if (warp == kMmaWarp) {
@@ -214,7 +223,57 @@ bwd_dq_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       const uint32_t id_dq = instr_desc(DT, 1, BM, HD);          // dQ: B = K MN-major, N = 128 = head_dim
       const uint64_t kd0 = smem_desc(smem_u32(sK), 16, 1024);
       const uint64_t vd0 = smem_desc(smem_u32(sV), 16, 1024);
+      const uint64_t dod = smem_desc(smem_u32(sDO), 16, 1024);
       const uint64_t kmn0 = smem_desc(smem_u32(sK), kTileBytes / 2, 1024);
+      constexpr uint64_t kHalf = (kTileBytes / 2) >> 4, kTileU = kTileBytes >> 4;
+      auto issue_dp = [&](int j) {
+        const uint64_t vd = vd0 + static_cast<uint64_t>(j % kVStages) * kTileU;
+#pragma unroll
+        for (int k = 0; k < HD / 16; ++k)
+          mma_ss(tmem + cDP, dod + (k >> 2) * kHalf + (k & 3) * 2, vd + (k >> 2) * kHalf + (k & 3) * 2, id_sd, k > 0 ? 1u : 0u);
+        tc_commit(bar(BAR_DP_FULL));
+      };
+      // The first V tile is waited for here (BAR_Q, behind QA_READY, also covers dO); every later one by the compute
+      // warps, before the arrival that lets its MMAs be issued.
+      bool ok = mbar_wait_bounded(bar(BAR_QA_READY), 0, s_abort) && mbar_wait_bounded(bar(BAR_V_FULL + 0), 0, s_abort);
+      if (ok) {
+        tc_fence_after();
+        issue_dp(0);
+      }
+      for (int j = 0; j < n_tiles && ok; ++j) {
+        if (j + 1 < n_tiles) {
+          // every warp holds dP(j) in registers (and has seen V(j + 1) land)
+          if (!mbar_wait_bounded(bar(BAR_DP_FREE), j & 1, s_abort)) { ok = false; break; }
+          tc_fence_after();
+          issue_dp(j + 1);
+        }
+      }
+    }
+  } else if (warp == kMmaWarpQ) {
+    // ============================ MMA issue: dQ ============================
+    if (lane == 0) {
+      const uint32_t id_dq = instr_desc(DT, 1, BM, HD);          // dQ: B = K MN-major, N = 128 = head_dim
+      const uint64_t kmn0 = smem_desc(smem_u32(sK), kTileBytes / 2, 1024);
+      constexpr uint64_t kTileU = kTileBytes >> 4;
+      bool ok = true;
+      for (int j = 0; j < n_tiles && ok; ++j) {
+        if (!mbar_wait_bounded(bar(BAR_DS_READY), j & 1, s_abort)) { ok = false; break; }
+        tc_fence_after();
+        const uint64_t kmn = kmn0 + static_cast<uint64_t>(j % kKStages) * kTileU;
+        // A = dS in TMEM: 16 keys = 8 columns.  B = K rows = keys: 16 rows = 2048 B = 128 units.
+#pragma unroll
+        for (int k = 0; k < BN / 16; ++k)
+          mma_ts(tmem + cDQ, tmem + cDS + k * 8, kmn + k * 128, id_dq, (j > 0 || k > 0) ? 1u : 0u);
+        tc_commit(bar(BAR_DQ_DONE));
+      }
+    }
+  } else if (warp == kMmaWarpS) {
+    // ============================ MMA issue: S ============================
+    // A second issuing thread: S(j + 2) depends on nothing the other thread issues (its buffer is freed by S_FREE,
+    // its commit tracks its own MMAs), and its waits and issues overlap the other thread's.
+    if (lane == 0) {
+      const uint32_t id_sd = instr_desc(DT, 0, BM, BN);
+      const uint64_t kd0 = smem_desc(smem_u32(sK), 16, 1024);
       constexpr uint64_t kHalf = (kTileBytes / 2) >> 4, kTileU = kTileBytes >> 4;
       auto issue_s = [&](int j) {
         const uint64_t kd = kd0 + static_cast<uint64_t>(j % kKStages) * kTileU;
@@ -223,56 +282,23 @@ bwd_dq_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
           mma_ts(tmem + cS, tmem + cQA + k * 8, kd + (k >> 2) * kHalf + (k & 3) * 2, id_sd, k > 0 ? 1u : 0u);
         tc_commit(bar(BAR_S_FULL));
       };
-      auto issue_dp = [&](int j) {
-        const uint64_t vd = vd0 + static_cast<uint64_t>(j % kVStages) * kTileU;
-#pragma unroll
-        for (int k = 0; k < HD / 16; ++k)
-          mma_ts(tmem + cDP, tmem + cDOA + k * 8, vd + (k >> 2) * kHalf + (k & 3) * 2, id_sd, k > 0 ? 1u : 0u);
-      };
-      // The first K and V tiles are waited for here; every later one by the compute warps, before the arrival that
-      // lets its MMAs be issued (S_FREE of the tile before for K, DS_READY of the tile before for V).
+      // the first two K tiles are waited for here, every later one by the compute warps before S_FREE
       bool ok = mbar_wait_bounded(bar(BAR_QA_READY), 0, s_abort) && mbar_wait_bounded(bar(BAR_K_FULL + 0), 0, s_abort);
       if (ok) {
         tc_fence_after();
         issue_s(0);
-        ok = mbar_wait_bounded(bar(BAR_V_FULL + 0), 0, s_abort);
       }
-      if (ok) {
+      for (int j = 1; j < n_tiles && ok; ++j) {
+        // every warp holds S(j - 1) in registers (and has seen K(j) land)
+        if (!mbar_wait_bounded(bar(BAR_S_FREE), (j - 1) & 1, s_abort)) { ok = false; break; }
         tc_fence_after();
-        issue_dp(0);
-        tc_commit(bar(BAR_DP_FULL));
-      }
-      if (ok && n_tiles > 1) {
-        ok = mbar_wait_bounded(bar(BAR_S_FREE), 0, s_abort);
-        if (ok) {
-          tc_fence_after();
-          issue_s(1);
-        }
-      }
-      for (int j = 0; j < n_tiles && ok; ++j) {
-        if (!mbar_wait_bounded(bar(BAR_DS_READY), j & 1, s_abort)) { ok = false; break; }
-        tc_fence_after();
-        const uint64_t kmn = kmn0 + static_cast<uint64_t>(j % kKStages) * kTileU;
-        // A = dS in TMEM: 16 keys = 8 columns; keys 32c .. 32c + 31 of the tile at column 32c (where warp column c
-        // wrote them).  B = K rows = keys: 16 rows = 2048 B = 128 units.
-#pragma unroll
-        for (int k = 0; k < BN / 16; ++k)
-          mma_ts(tmem + cDQ, tmem + cDP + (k >> 1) * 32 + (k & 1) * 8, kmn + k * 128, id_dq, (j > 0 || k > 0) ? 1u : 0u);
-        // dP(j + 1) overwrites the dS those MMAs read: the pipe runs in order
-        if (j + 1 < n_tiles) issue_dp(j + 1);
-        tc_commit(bar(BAR_DP_FULL));
-        if (j + 1 == n_tiles) tc_commit(bar(BAR_DQ_FINAL));
-        if (j + 2 < n_tiles) {
-          if (!mbar_wait_bounded(bar(BAR_S_FREE), (j + 1) & 1, s_abort)) { ok = false; break; }
-          tc_fence_after();
-          issue_s(j + 2);
-        }
+        issue_s(j);
       }
     }
-  } else {
+  } else if (warp < 16) {
     // ============================ compute warps 0-15 ============================
     const int wq = warp & 3, cq = warp >> 2;          // TMEM lane quarter (rows), 32-key column quarter of a tile
-    const int hf = cq & 1, set = cq >> 1;              // for the Q / dO copy: d-half, Q or dO
+    const int hf = cq & 1, set = cq >> 1;              // for the Q copy: d-half; warps of set 0 copy
     const int rloc = wq * 32 + lane;
     const int row = q0 + rloc;
     const uint32_t lane_base = static_cast<uint32_t>(wq * 32) << 16;
@@ -293,17 +319,19 @@ bwd_dq_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     const uint8_t* mask_row = masked_cells ? p.bmask + static_cast<int64_t>(min(row, N - 1) / p.bm_bq) * p.bm_nk : nullptr;
     bool ok = __all_sync(0xffffffffu, mbar_wait_bounded(bar(BAR_Q), 0, s_abort));
     if (ok) {
-      // this row's 128 bytes of d-half hf of Q (set 0) or dO (set 1) -> 32 TMEM columns of the A operand
-      const uint32_t rowa = smem_u32(set == 0 ? sQ : sDO) + hf * (kTileBytes / 2) + rloc * 128;
-      uint32_t qr[32];
+      if (set == 0) {
+        // this row's 128 bytes of d-half hf of Q -> 32 TMEM columns of the A operand
+        const uint32_t rowa = smem_u32(sQ) + hf * (kTileBytes / 2) + rloc * 128;
+        uint32_t qr[32];
 #pragma unroll
-      for (int c = 0; c < 8; ++c)
-        asm volatile("ld.shared.v4.b32 {%0,%1,%2,%3}, [%4];\n"
-                     : "=r"(qr[4 * c]), "=r"(qr[4 * c + 1]), "=r"(qr[4 * c + 2]), "=r"(qr[4 * c + 3])
-                     : "r"(rowa + static_cast<uint32_t>((c ^ (rloc & 7)) << 4))
-                     : "memory");
-      tmem_st32(tmem + lane_base + (set == 0 ? cQA : cDOA) + hf * 32, qr);
-      tc_wait_st();
+        for (int c = 0; c < 8; ++c)
+          asm volatile("ld.shared.v4.b32 {%0,%1,%2,%3}, [%4];\n"
+                       : "=r"(qr[4 * c]), "=r"(qr[4 * c + 1]), "=r"(qr[4 * c + 2]), "=r"(qr[4 * c + 3])
+                       : "r"(rowa + static_cast<uint32_t>((c ^ (rloc & 7)) << 4))
+                       : "memory");
+        tmem_st32(tmem + lane_base + cQA + hf * 32, qr);
+        tc_wait_st();
+      }
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(bar(BAR_QA_READY));
@@ -367,7 +395,7 @@ bwd_dq_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         pr[i] = pe.x;
         pr[i + 1] = pe.y;
       }
-      // dP(j + 1) follows dQ(j) on the MMA thread without a wait of its own: see that tile's V land before DS_READY(j).
+      // dP(j + 1) is issued on DP_FREE(j) without a wait of the MMA thread's own: see that tile's V land first.
       // Checked here, where it costs nothing: the exponentials above are still in flight
       if (j + 1 < n_tiles) {
         if (!__all_sync(0xffffffffu, mbar_wait_bounded(bar(BAR_V_FULL + (j + 1) % kVStages), ((j + 1) / kVStages) & 1, s_abort))) { ok = false; break; }
@@ -375,11 +403,14 @@ bwd_dq_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       // ---------------- phase B: dP -> dS ----------------
       if (!__all_sync(0xffffffffu, mbar_wait_bounded(bar(BAR_DP_FULL), j & 1, s_abort))) { ok = false; break; }
       tc_fence_after();
-      // the commit just seen also followed dQ(j - 1): V(j)'s and K(j - 1)'s stages can be refilled
-      if (warp == 0 && lane == 0) mbar_arrive(bar(BAR_FREE + j % kFreeBars));
+      // dP(j) is complete: V(j)'s stage can be refilled
+      if (warp == 0 && lane == 0) mbar_arrive(bar(BAR_V_FREE + j % kVStages));
       uint32_t rd[32];
       tmem_ld32(tmem + lane_base + cDP + cq * 32, rd);
       tc_wait_ld();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar(BAR_DP_FREE));
       uint32_t pd[16];
 #pragma unroll
       for (int i = 0; i < 32; i += 2) {
@@ -387,8 +418,14 @@ bwd_dq_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         const float2 dsv = __fmul2_rn(make_float2(pr[i], pr[i + 1]), __fadd2_rn(dv, nD2));
         pd[i >> 1] = pack16q<DT>(dsv.x, dsv.y);
       }
-      // dS goes back as 16-bit pairs along the key index, inside the 32 columns this warp has just read
-      tmem_st16(tmem + lane_base + cDP + cq * 32, pd);
+      // the dS columns still hold dS(j - 1) until dQ(j - 1) has read them; its completion also frees K(j - 1)'s stage
+      if (j >= 1) {
+        if (!__all_sync(0xffffffffu, mbar_wait_bounded(bar(BAR_DQ_DONE), (j - 1) & 1, s_abort))) { ok = false; break; }
+        tc_fence_after();
+        if (warp == 0 && lane == 0) mbar_arrive(bar(BAR_K_FREE + (j - 1) % kKStages));
+      }
+      // dS as 16-bit pairs along the key index: this warp's 32 keys -> 16 columns
+      tmem_st16(tmem + lane_base + cDS + cq * 16, pd);
       tc_wait_st();
       tc_fence_before();
       __syncwarp();
@@ -396,7 +433,7 @@ bwd_dq_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     }
 
     // ---- epilogue: dQ * scale -> 16-bit, through shared memory ----
-    if (ok) ok = __all_sync(0xffffffffu, mbar_wait_bounded(bar(BAR_DQ_FINAL), 0, s_abort));
+    if (ok) ok = __all_sync(0xffffffffu, mbar_wait_bounded(bar(BAR_DQ_DONE), (n_tiles - 1) & 1, s_abort));
     if (ok) {
       tc_fence_after();
       // this warp's 32 of the 128 columns: d-half dh, 32-column half c of it; staged as [d-half][row][128 B] in the

@@ -9,7 +9,7 @@
 // outside the band are skipped whole).  Per key tile j, three GEMMs with M = 128 query rows, all of them N = 128
 // (an N = 64 MMA of this shape takes 1.5x its share of the tensor pipe):
 //   S(j)  = Q . K(j)^T      (A = Q in TMEM, B = K(j) K-major)   -> TMEM S
-//   dP(j) = dO . V(j)^T     (A = dO in TMEM, B = V(j) K-major)  -> TMEM dP
+//   dP(j) = dO . V(j)^T     (A = dO in shared memory, B = V(j) K-major)  -> TMEM dP
 //   dQ   += dS(j) . K(j)    (A = dS in TMEM, B = K(j) as an MN-major operand)  -> TMEM dQ
 // S and dP have one buffer each, and 16 compute warps (thread = query row, a warp = 32 rows x 32 keys) work on a
 // tile in two phases so that neither buffer is held long:
@@ -17,11 +17,13 @@
 //            bound by the special-function unit
 //   phase B  load dP(j) into registers (dP is free for tile j + 1: DP_FREE), dS = P' o (dP - delta), written as a
 //            16-bit A operand into columns of its own (DS_READY)
-// The MMA thread issues, as each arrival comes in: dP(j+1) on DP_FREE(j), dQ(j) on DS_READY(j), S(j+2) on
-// S_FREE(j+1).  Nothing on the tensor pipe waits for the compute warps' arithmetic: the pace is set by whichever is
-// longer, the 24 MMAs of a tile or phase A + phase B.
-// Warp 16 is the TMA producer (Q and dO once; K tiles into a four-stage ring, V tiles into a two-stage ring), one
-// thread of warp 17 issues the MMAs.  Q passes through the last K stage into TMEM (a 16-bit A operand); dO stays in
+// Each arrival releases one group of MMAs: dP(j+1) on DP_FREE(j), dQ(j) on DS_READY(j), S(j+2) on S_FREE(j+1).
+// Nothing on the tensor pipe waits for the compute warps' arithmetic.  The three groups write disjoint accumulators
+// and a tcgen05.commit tracks the MMAs of the thread that executes it, so each group has an issuing thread of its
+// own (one lane of warps 17, 18, 19): in place a thread spends about 96 clocks per MMA it issues, waits included,
+// against the pipe's 64, and three threads keep the pipe fed where one does not.
+// Warp 16 is the TMA producer (Q and dO once; K tiles into a four-stage ring, V tiles into a two-stage ring).
+// Q passes through the last K stage into TMEM (a 16-bit A operand); dO stays in
 // shared memory (the dP MMAs are SS: TMEM has no room for it beside dS).  dQ leaves TMEM once, scaled, through
 // shared memory (TMA store for the dense layout).
 // TMEM (all 512 columns): [0,128) S, [128,256) dP, [256,384) dQ, [384,448) Q, [448,512) dS.  No load uses cluster

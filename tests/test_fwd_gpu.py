@@ -311,6 +311,25 @@ def test_short_tiles_wait_for_both_pending_accumulations(dev):
         assert float((out - v_const).abs().max()) <= 1e-2
 
 
+def test_host_pipeline_overlapping_calls(dev):
+    """Calls with join=False follow one another without draining the pipeline; each still returns its own result."""
+    gen = torch.Generator().manual_seed(11)
+    shapes = ((3, 8, 256, 128), (3, 2, 256, 128))
+    reqs = [tuple(torch.randn(sh, generator=gen).to(torch.bfloat16).pin_memory() for sh in (shapes[0], shapes[1], shapes[1]))
+            for _ in range(4)]
+    outs = [torch.empty(shapes[0], dtype=torch.bfloat16).pin_memory() for _ in reqs]
+    lses = [torch.empty(shapes[0][:3], dtype=torch.float32).pin_memory() for _ in reqs]
+    pipe = fa.HostPipeline(shapes[0], shapes[1], torch.bfloat16, dev, chunk=1, depth=2, want_lse=True)
+    for (q, k, v), o, l in zip(reqs, outs, lses):
+        fa.flash_attention_from_host(q, k, v, out=o, lse=l, pipeline=pipe, return_lse=True, causal=True, join=False)
+    pipe.join()
+    torch.cuda.synchronize()
+    for (q, k, v), o, l in zip(reqs, outs, lses):
+        ro, rl = fa.flash_attention(q.to(dev), k.to(dev), v.to(dev), causal=True, return_lse=True)
+        assert torch.equal(o, ro.cpu())
+        assert torch.equal(l, rl.cpu())
+
+
 def test_host_pipeline_matches_device_call(dev):
     """flash_attention_from_host (chunked, stream-pipelined copies) returns what the device call returns."""
     q = randn((3, 8, 300, 128), torch.bfloat16, 130).pin_memory()

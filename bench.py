@@ -462,6 +462,13 @@ def bench_extras(device, pk):
     out["sparse_window_mask_fp16"] = {"ms": ms, "active_cells": float(bm.float().mean().item()),
                                       "tflops_active_cells": fl / ms / 1e9, "kernel": "fa_fwd_sm100_kernel<128, f16, features>"}
     del q, k, v
+    # head_dim 256, the reference's largest kernel size (its own table: causal forward, N = 8192): B=2 H=16 bf16
+    q, k, v = (mk((2, 16, 8192, 256), torch.bfloat16) for _ in range(3))
+    ms = _time_ms(lambda: fa.flash_attention(q, k, v, causal=True), 10, 3)
+    fl = 4.0 * 2 * 16 * 256 * (8192 * 8193 // 2)
+    out["head_dim256_causal_bf16"] = {"ms": ms, "tflops": fl / ms / 1e9, "frac_tensor_peak": fl / ms / 1e9 / pk["tf"],
+                                      "kernel": "fa_fwd_sm100_kernel<256> (one CTA per SM)"}
+    del q, k, v
     # config 5: packed varlen, 65536 tokens, lengths ~ U{128..4096}, H=16 D=64 bf16 causal, fwd + bwd
     rng = np.random.default_rng(5)
     lens = []

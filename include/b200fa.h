@@ -66,7 +66,7 @@ typedef struct b200fa_desc {
   int32_t dtype;        /* B200FA_F16 | B200FA_BF16 | B200FA_F32 (q, out, dout, grads) */
   int32_t kv_dtype;     /* == dtype, or B200FA_I8 / B200FA_E4M3 for decode pools */
   int32_t B, Hq, Hkv;   /* Hq % Hkv == 0 (GQA / MQA) */
-  int32_t N, S, D;      /* query rows, key rows, head dim (64 or 128) */
+  int32_t N, S, D;      /* query rows, key rows, head dim (64 or 128; 256 for the 16-bit forward) */
   int64_t q_strides[3]; /* batch, head, row — in elements; 0,0,0 => contiguous BHND */
   int64_t k_strides[3];
   int64_t v_strides[3];

@@ -1,5 +1,5 @@
 // Blackwell forward kernel: tcgen05 MMAs with TMEM accumulators, TMA-staged tiles,
-// warp-specialised roles.  Dense and packed-varlen layouts, 16-bit, D = 64 or 128; any N, S; GQA;
+// warp-specialised roles.  Dense and packed-varlen layouts, 16-bit, D = 64, 128 or 256; any N, S; GQA;
 // causal (lower-right), left window, softcap, lse.  What it computes is the reference forward
 // (csrc/mfa_steel_fwd.cpp:801-1221); how is Blackwell's own:
 //
@@ -16,7 +16,8 @@
 //              the softmax warps work on the other buffer; tcgen05.commit signals the
 //              mbarriers that free smem stages and publish S / O.
 //
-// TMEM (256 of 512 columns, so two CTAs share an SM and hide each other's softmax):
+// TMEM (256 of 512 columns up to D = 128, so two CTAs share an SM and hide each other's softmax; D = 256 takes 384
+// and one CTA per SM):
 //   [0,64) S0 / P0   [64,128) S1 / P1   [128,128+D) O.
 // Tiles above the causal diagonal or left of the window are skipped whole.
 // Paged K / V (prefill-sized queries over a page pool; the role of the reference's paged STEEL forward,
@@ -44,10 +45,12 @@ constexpr int BM = 128;      // query rows per CTA
 constexpr int BN = 64;       // keys per tile
 constexpr int kStages = 2;
 constexpr int kThreads = 192;
-constexpr uint32_t kTmemCols = 256;
+// TMEM columns of one CTA: two 64-column S buffers + head_dim columns of O, rounded up to a power of two.  256 for
+// head_dim <= 128 (two CTAs per SM), all 512 for head_dim 256 (one CTA per SM)
+template <int HD> constexpr uint32_t tmem_cols() { return HD > 128 ? 512u : 256u; }
 constexpr int kMaxListTiles = 1024;   // block-sparse instantiation: active key tiles of one query tile (16-bit indices)
 
-// Sizes that depend on the head dim (64 or 128).  Tiles are stored as 64-element (128-byte) wide halves,
+// Sizes that depend on the head dim (64, 128 or 256).  Tiles are stored as 64-element (128-byte) wide halves,
 // [half][row][128 B], each half one 128B-swizzle atom wide.
 template <int HD> struct Cfg {
   static constexpr int kHalves = HD / 64;
@@ -360,7 +363,7 @@ fa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     }
   }
   if (warp == 5) {
-    tmem_alloc(smem_u32(s_tmem), kTmemCols);
+    tmem_alloc(smem_u32(s_tmem), tmem_cols<HD>());
     tmem_relinquish();
   }
   tc_fence_before();
@@ -859,7 +862,7 @@ fa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   __syncthreads();
   if (warp == 5) {
     tc_fence_after();
-    tmem_dealloc(tmem, kTmemCols);
+    tmem_dealloc(tmem, tmem_cols<HD>());
   }
   if (tid == 0 && *s_abort != 0) atomicOr(&g_kernel_status, 1);
 }
@@ -877,7 +880,9 @@ bool make_map(CUtensorMap* m, int dtype, const void* base, int D, int rows, int 
 }  // namespace
 
 bool fwd_sm100_supported(const FwdParams& p, int dtype, int D) {
-  if (!(dtype == 0 || dtype == 1) || !(D == 64 || D == 128)) return false;
+  if (!(dtype == 0 || dtype == 1) || !(D == 64 || D == 128 || D == 256)) return false;
+  // head_dim 256: one CTA per SM (192 KB of tiles, 384 TMEM columns); no bias / block-mask instantiation
+  if (D == 256 && (p.alibi != nullptr || p.bmask != nullptr)) return false;
   if (p.N <= 0 || p.S <= 0 || p.B <= 0) return false;
   // A broadcast (stride 0) batch or head dimension of extent > 1 cannot be described to TMA, whose strides must be
   // positive; such views run the portable kernel, which indexes with the caller's strides as they are.
@@ -945,7 +950,7 @@ static cudaError_t launch_hd(const FwdParams& p, int nbatch, int max_q, cudaStre
   const int capm = p.softcap >= kPreciseTanhMinCap ? 2 : (p.softcap > 0.f ? 1 : 0);
   const long long items = static_cast<long long>(grid.x) * grid.y * grid.z;
   a.total_items = static_cast<int>(items < 0x7fffffffLL ? items : 0x7fffffffLL);
-  if constexpr (!FEAT) {
+  if constexpr (!FEAT && HD <= 128) {
     int dev = 0, sm_count = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess ||
         sm_count <= 0)
@@ -983,6 +988,8 @@ cudaError_t launch_fwd_sm100(const FwdParams& p, int dtype, int D, int nbatch, i
   }
   if (D == 64)
     return dtype == 0 ? launch_hd<64, 0, false>(p, nbatch, max_q, stream) : launch_hd<64, 1, false>(p, nbatch, max_q, stream);
+  if (D == 256)
+    return dtype == 0 ? launch_hd<256, 0, false>(p, nbatch, max_q, stream) : launch_hd<256, 1, false>(p, nbatch, max_q, stream);
   return dtype == 0 ? launch_hd<128, 0, false>(p, nbatch, max_q, stream) : launch_hd<128, 1, false>(p, nbatch, max_q, stream);
 }
 

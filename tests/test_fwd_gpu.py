@@ -281,8 +281,8 @@ def test_full_size_linearity_in_v(dev):
 @pytest.mark.parametrize("dt", ["f16", "bf16"])
 @pytest.mark.parametrize("Hq,Hkv,N,S,causal", [(4, 4, 200, 200, True), (4, 2, 70, 333, False), (2, 1, 1, 500, True)])
 def test_head_dim_256_forward(dev, dt, Hq, Hkv, N, S, causal):
-    """head_dim 256 (the reference's largest kernel size, mlx_mfa/attention.py:30): 16-bit forward through the portable
-    kernel; the backward and float32 are refused."""
+    """head_dim 256 (the reference's largest kernel size, mlx_mfa/attention.py:30): 16-bit forward (the tcgen05 kernel,
+    one CTA per SM); the backward and float32 are refused."""
     _run(dev, DT[dt], 1, Hq, Hkv, N, S, 256, 180, causal=causal)
     _run(dev, DT[dt], 1, Hq, Hkv, N, S, 256, 181, causal=causal, softcap=20.0, window_size=(64, 0))
     q = randn((1, 2, 16, 256), torch.float32, 182).to(dev)
@@ -291,6 +291,33 @@ def test_head_dim_256_forward(dev, dt, Hq, Hkv, N, S, causal):
     qh = randn((1, 2, 16, 256), DT[dt], 183).to(dev).requires_grad_(True)
     with pytest.raises(NotImplementedError):
         fa.flash_attention(qh, qh, qh).sum().backward()
+
+
+@pytest.mark.parametrize("dt", ["f16", "bf16"])
+def test_head_dim_256_long_and_varlen(dev, dt):
+    """head_dim 256 over many key tiles (lazy rescale, both S buffers, all four 64-column halves of O), GQA, softcap,
+    against the oracle; the tcgen05 kernel against the portable one; packed sequences against per-sequence calls."""
+    _run(dev, DT[dt], 2, 4, 2, 700, 700, 256, 184, causal=True)
+    _run(dev, DT[dt], 1, 2, 2, 130, 1100, 256, 185, causal=False, softcap=30.0)
+    q = randn((1, 4, 900, 256), DT[dt], 186).to(dev)
+    k = randn((1, 2, 900, 256), DT[dt], 187).to(dev)
+    v = randn((1, 2, 900, 256), DT[dt], 188).to(dev)
+    a, la = fa.flash_attention(q, k, v, causal=True, return_lse=True)
+    old = fa_attn._set_force_flags(_lib.FLAG_FORCE_MMA_SYNC)
+    try:
+        b, lb = fa.flash_attention(q, k, v, causal=True, return_lse=True)
+    finally:
+        fa_attn._set_force_flags(old)
+    assert float((a.float() - b.float()).abs().max()) <= 2e-2
+    assert float((la - lb).abs().max()) <= 2e-2
+    lens = [300, 129, 471]
+    cu = torch.tensor([0, 300, 429, 900], dtype=torch.int32, device=dev)
+    pv = fa.flash_attention_varlen(q, k, v, cu, cu, max(lens), max(lens), causal=True)
+    for i, n in enumerate(lens):
+        b0 = int(cu[i])
+        ref = fa.flash_attention(q[:, :, b0:b0 + n], k[:, :, b0:b0 + n], v[:, :, b0:b0 + n], causal=True)
+        assert float((pv[:, :, b0:b0 + n].float() - ref.float()).abs().max()) <= 2e-2
+    assert fa.kernel_status() == 0
 
 
 def test_short_tiles_wait_for_both_pending_accumulations(dev):

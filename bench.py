@@ -658,53 +658,46 @@ def main():
     # host->device copy, the kernel and the device->host copy of neighbouring chunks overlap
     pipe = fa.HostPipeline(hq.shape, hk.shape, hq.dtype, device, chunk=1, depth=3, want_lse=True)
 
-    # consecutive steps are a stream of requests: join=False lets step i + 1's copies in run beside step i's copies
-    # out (every step still copies its inputs in and its result out); the pipeline is joined before the closing event
-    def e2e_step():
-        fa.flash_attention_from_host(hq, hk, hv, out=ho, lse=hl, pipeline=pipe, return_lse=True, causal=True,
-                                     softcap=cfg["softcap"], join=False)
-
+    # Consecutive steps are a stream of requests.  With join=False step i + 1's copies in run beside step i's copies out
+    # (every step still copies all of its inputs in and its result out; the pipeline is joined before the closing
+    # event); with join=True every call drains before the next.  Overlapping wins while the host link has duplex
+    # headroom (one or two GPUs here); with more GPUs sharing the host's memory system it can lose, so both are timed
+    # and the faster one (by the slowest rank) is the figure reported; the other rides along in the same object.
     e2e_steps = max(3, min(args.steps, 10))
-    for _ in range(2):
-        e2e_step()
-    pipe.join()
-    torch.cuda.synchronize()
-    if dist is not None:
-        dist.barrier()
-    e0.record()
-    for _ in range(e2e_steps):
-        e2e_step()
-    pipe.join()
-    e1.record()
-    torch.cuda.synchronize()
-    e2e_ms = e0.elapsed_time(e1) / e2e_steps
-    if dist is not None:
-        t = torch.tensor([e2e_ms], device=device, dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        e2e_ms = float(t.item())
+
+    def timed(step_fn):
+        for _ in range(2):
+            step_fn()
+        pipe.join()
+        torch.cuda.synchronize()
+        if dist is not None:
+            dist.barrier()
+        e0.record()
+        for _ in range(e2e_steps):
+            step_fn()
+        pipe.join()
+        e1.record()
+        torch.cuda.synchronize()
+        ms_ = e0.elapsed_time(e1) / e2e_steps
+        if dist is not None:
+            t = torch.tensor([ms_], device=device, dtype=torch.float64)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms_ = float(t.item())
+        return ms_
+
+    def e2e_step(join):
+        return lambda: fa.flash_attention_from_host(hq, hk, hv, out=ho, lse=hl, pipeline=pipe, return_lse=True,
+                                                    causal=True, softcap=cfg["softcap"], join=join)
+
+    e2e_by_mode = {"overlapped calls": timed(e2e_step(False)), "joined calls": timed(e2e_step(True))}
+    e2e_mode = min(e2e_by_mode, key=e2e_by_mode.get)
+    e2e_ms = e2e_by_mode[e2e_mode]
     e2e_val = flops / (e2e_ms * 1e-3) / 1e12 * world
 
-    # the same pipeline with the kernel launch left out, all ranks at once: what the host link and the host's memory
-    # allow for these copies (the ceiling the end-to-end figure is to be read against)
-    def copy_step():
-        pipe.run(hq, hk, hv, ho, hl, causal=True, softcap=cfg["softcap"], copies_only=True, join=False)
-
-    copy_step()
-    pipe.join()
-    torch.cuda.synchronize()
-    if dist is not None:
-        dist.barrier()
-    e0.record()
-    for _ in range(e2e_steps):
-        copy_step()
-    pipe.join()
-    e1.record()
-    torch.cuda.synchronize()
-    copy_ms = e0.elapsed_time(e1) / e2e_steps
-    if dist is not None:
-        t = torch.tensor([copy_ms], device=device, dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        copy_ms = float(t.item())
+    # the same pipeline, in the same mode, with the kernel launch left out, all ranks at once: what the host link and
+    # the host's memory allow for these copies (the ceiling the end-to-end figure is to be read against)
+    copy_ms = timed(lambda: pipe.run(hq, hk, hv, ho, hl, causal=True, softcap=cfg["softcap"], copies_only=True,
+                                     join=(e2e_mode == "joined calls")))
     copy_ceiling_gbs = (h2d + d2h) * world / (copy_ms * 1e-3) / 1e9
     del hq, hk, hv, ho, hl, pipe
 
@@ -746,7 +739,8 @@ def main():
             "e2e": {"value": e2e_val, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                     "ms_per_step": e2e_ms, "copy_ceiling_gbs": copy_ceiling_gbs, "copies_only_ms_per_step": copy_ms,
                     "achieved_copy_gbs": (h2d + d2h) * world / (e2e_ms * 1e-3) / 1e9,
-                    "frac_of_copy_ceiling": copy_ms / e2e_ms},
+                    "frac_of_copy_ceiling": copy_ms / e2e_ms, "mode": e2e_mode,
+                    "ms_per_step_by_mode": e2e_by_mode},
             "gpu_launches": args.steps,
             "kernel_status": int(fa.kernel_status()),       # 0 = no bounded wait inside a tcgen05 kernel gave up
             "clocks": clocks,

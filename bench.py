@@ -554,6 +554,9 @@ def profile_case(name, device, steps, warmup):
             mk((2, 4, 8192, 128), torch.bfloat16), mk((2, 16, 8192, 128), torch.bfloat16)
         o_, l_ = fa_attn._fwd_raw(q, k, v, 128 ** -0.5, True, 0.0, -1, True, None)
         fn = lambda: fa_attn._bwd_raw(q, k, v, o_, l_, do, 128 ** -0.5, True, None)
+    elif name == "d256":      # head_dim 256 forward: B=1, H=16, N=S=8192, bf16, causal (201 MB of q, k, v, o)
+        q, k, v = (mk((1, 16, 8192, 256), torch.bfloat16) for _ in range(3))
+        fn = lambda: fa.flash_attention(q, k, v, causal=True)
     else:
         raise SystemExit(f"unknown --case {name}")
     ms = _time_ms(fn, steps, warmup)
@@ -571,7 +574,7 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-extras", action="store_true", help="skip configs 1, 3 and 5")
     ap.add_argument("--small", action="store_true", help="profiling aid: N=S=4096, B=2 (not a bench value)")
-    ap.add_argument("--case", default="", choices=["", "c3", "c5", "bwd128"],
+    ap.add_argument("--case", default="", choices=["", "c3", "c5", "bwd128", "d256"],
                     help="profiling aid: run one small case of another kernel and exit (not a bench value)")
     ap.add_argument("--only-decode", type=int, default=0, metavar="B",
                     help="profiling aid: run only the decode measurement with batch B (not a bench value)")

@@ -247,6 +247,9 @@ __global__ void __launch_bounds__(kThreads) fa_fwd_mma_kernel(const FwdParams p)
     kt = kt_next;
   }
   cp_async_wait<0>();
+  // A tile without any key tile never reached the loop's barrier: the Q rows this warp is about to reuse for its
+  // output were requested by threads of every warp, and their copies must have landed first (CTA-uniform branch)
+  if (kt_first >= kt_end) __syncthreads();
 
   // ---- epilogue ----
 #pragma unroll

@@ -320,6 +320,29 @@ def test_head_dim_256_long_and_varlen(dev, dt):
     assert fa.kernel_status() == 0
 
 
+@pytest.mark.parametrize("D", [64, 128, 256])
+def test_query_tiles_without_any_visible_key(dev, D):
+    """Causal with N > S: the first N - S rows see no key and must come out as exact zeros with lse = -inf, in both
+    forward kernels.  (The portable kernel reuses its Q tile as the output staging area; a query tile that visits no
+    key tile must still wait for every thread's Q copies before it does.)"""
+    N, S, Hq, Hkv = 2049, 63, 24, 3
+    q = randn((1, Hq, N, D), torch.float16, 190).to(dev)
+    k = randn((1, Hkv, S, D), torch.float16, 191).to(dev)
+    v = randn((1, Hkv, S, D), torch.float16, 192).to(dev)
+    dead = N - S
+    for flags in (0, _lib.FLAG_FORCE_MMA_SYNC):
+        old = fa_attn._set_force_flags(flags)
+        try:
+            for _ in range(6):
+                o, l = fa.flash_attention(q, k, v, causal=True, return_lse=True)
+                assert int((o[:, :, :dead] != 0).sum()) == 0
+                assert bool(torch.isinf(l[:, :, :dead]).all()) and bool((l[:, :, :dead] < 0).all())
+                assert bool(torch.isfinite(l[:, :, dead:]).all())
+        finally:
+            fa_attn._set_force_flags(old)
+    assert fa.kernel_status() == 0
+
+
 def test_short_tiles_wait_for_both_pending_accumulations(dev):
     """A query tile with two key tiles can finish its second softmax before the first P.V product has completed;
     the epilogue must then wait for both.  With constant V every output equals that constant whatever the

@@ -370,6 +370,7 @@ bwd_dkv_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
     const float2 c2 = make_float2(p.scale_log2, p.scale_log2);
     const float cap_in = CAP ? p.scale / p.softcap : 0.f, cap_out = p.softcap * kLog2e;
     const bool precise_tanh = p.softcap >= kPreciseTanhMinCap;
+    const SmallCap sc = CAP ? small_cap_consts(p.scale, p.softcap) : SmallCap{};
     const int wlo = WIN ? off - p.window_left : 0;         // window: key visible iff key >= qrow + wlo
     for (int it = 0; it < n_iter && ok; ++it) {
       const int sl = it & 1;
@@ -400,7 +401,15 @@ bwd_dkv_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
         tmem_ld32(tmem + lane_base + cST + q0l, rs);
         tc_wait_ld();
         uint32_t pp[16];
-        auto phase_a = [&](auto masked) {
+        // soft cap: are all of this warp's scores small enough for the polynomial form (see small_cap_consts)?
+        bool small_y = false;
+        if constexpr (CAP) {
+          float am = 0.f;
+#pragma unroll
+          for (int i = 0; i < 32; ++i) am = fmaxf(am, fabsf(__uint_as_float(rs[i])));
+          small_y = __all_sync(0xffffffffu, am * cap_in <= sc.y3);
+        }
+        auto phase_a = [&](auto masked, auto small_c) {
 #pragma unroll
           for (int i = 0; i < 32; i += 4) {
             const float4 nL = lds_f4(Ls + (q0l + i) * 4);      // -L of four queries
@@ -411,9 +420,15 @@ bwd_dkv_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
               float2 t;
               [[maybe_unused]] float2 dcap;
               if constexpr (CAP) {
-                const float2 th = make_float2(cap_tanh(sv.x * cap_in, precise_tanh), cap_tanh(sv.y * cap_in, precise_tanh));
-                t = __ffma2_rn(th, make_float2(cap_out, cap_out), nl);
-                dcap = __ffma2_rn(make_float2(-th.x, -th.y), th, make_float2(1.f, 1.f));
+                if constexpr (decltype(small_c)::value) {
+                  const float2 z = __fmul2_rn(sv, sv);
+                  t = __ffma2_rn(sv, __ffma2_rn(z, make_float2(sc.kb3, sc.kb3), make_float2(sc.kk, sc.kk)), nl);
+                  dcap = __ffma2_rn(z, __ffma2_rn(z, make_float2(sc.e2, sc.e2), make_float2(sc.e1, sc.e1)), make_float2(1.f, 1.f));
+                } else {
+                  const float2 th = make_float2(cap_tanh(sv.x * cap_in, precise_tanh), cap_tanh(sv.y * cap_in, precise_tanh));
+                  t = __ffma2_rn(th, make_float2(cap_out, cap_out), nl);
+                  dcap = __ffma2_rn(make_float2(-th.x, -th.y), th, make_float2(1.f, 1.f));
+                }
               } else {
                 t = __ffma2_rn(sv, c2, nl);
               }
@@ -437,7 +452,11 @@ bwd_dkv_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
             }
           }
         };
-        if (need_mask) phase_a(std::true_type{}); else phase_a(std::false_type{});
+        if (CAP && small_y) {
+          if (need_mask) phase_a(std::true_type{}, std::true_type{}); else phase_a(std::false_type{}, std::true_type{});
+        } else {
+          if (need_mask) phase_a(std::true_type{}, std::false_type{}); else phase_a(std::false_type{}, std::false_type{});
+        }
         // P^T goes back as 16-bit pairs along the query index, inside the 32 columns this warp has just read
         tmem_st16(tmem + lane_base + cST + q0l, pp);
         tc_wait_st();

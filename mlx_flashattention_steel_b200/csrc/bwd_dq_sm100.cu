@@ -29,6 +29,8 @@
 // TMEM (all 512 columns): [0,128) S, [128,256) dP, [256,384) dQ, [384,448) Q, [448,512) dS.  No load uses cluster
 // multicast; every mbarrier wait is bounded and a timeout raises this file's status word (read through
 // b200fa_kernel_status).
+#include <type_traits>
+
 #include "common.cuh"
 #include "launch.h"
 #include "tcgen05.cuh"
@@ -314,6 +316,7 @@ bwd_dq_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     }
     const float cap_in = CAP ? p.scale / p.softcap : 0.f, cap_out = p.softcap * kLog2e;
     const bool precise_tanh = p.softcap >= kPreciseTanhMinCap;
+    const SmallCap sc = CAP ? small_cap_consts(p.scale, p.softcap) : SmallCap{};
     const float2 c2 = make_float2(p.scale_log2, p.scale_log2), nL2 = make_float2(nL, nL), nD2 = make_float2(nD, nD);
     const float alibi_l2 = (FEAT && p.alibi != nullptr) ? p.alibi[head] * kLog2e : 0.f;
     const bool masked_cells = FEAT && p.bmask != nullptr;
@@ -371,32 +374,49 @@ bwd_dq_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       const int lo_rel = WIN ? row + off - p.window_left - k0 : 0;
       const bool need_mask = __any_sync(0xffffffffu, hi_rel < 31 || (WIN && lo_rel > 0));
       float pr[32];                                            // P, times (1 - tanh^2) under a soft cap
+      // soft cap: are all of this warp's scores small enough for the polynomial form (see small_cap_consts)?
+      bool small_y = false;
+      if constexpr (CAP) {
+        float am = 0.f;
 #pragma unroll
-      for (int i = 0; i < 32; i += 2) {
-        const float2 sv = make_float2(__uint_as_float(rs[i]), __uint_as_float(rs[i + 1]));
-        float2 t, dcap;
-        if constexpr (CAP) {
-          const float2 th = make_float2(cap_tanh(sv.x * cap_in, precise_tanh), cap_tanh(sv.y * cap_in, precise_tanh));
-          t = __ffma2_rn(th, make_float2(cap_out, cap_out), nL2);
-          dcap = __ffma2_rn(make_float2(-th.x, -th.y), th, make_float2(1.f, 1.f));
-        } else {
-          t = __ffma2_rn(sv, c2, nL2);
-        }
-        if constexpr (FEAT) {
-          t = __fadd2_rn(t, make_float2(fmaf(alibi_l2, static_cast<float>(i), ab), fmaf(alibi_l2, static_cast<float>(i + 1), ab)));
-        }
-        float2 pe = make_float2(fast_exp2(t.x), fast_exp2(t.y));
-        if constexpr (FEAT) {
-          if (!((cells >> (i >> 4)) & 1u)) pe = make_float2(0.f, 0.f);     // keys i, i + 1 share a 16-key cell
-        }
-        if (need_mask) {
-          if (i > hi_rel || (WIN && i < lo_rel)) pe.x = 0.f;
-          if (i + 1 > hi_rel || (WIN && i + 1 < lo_rel)) pe.y = 0.f;
-        }
-        if constexpr (CAP) pe = __fmul2_rn(pe, dcap);
-        pr[i] = pe.x;
-        pr[i + 1] = pe.y;
+        for (int i = 0; i < 32; ++i) am = fmaxf(am, fabsf(__uint_as_float(rs[i])));
+        small_y = __all_sync(0xffffffffu, am * cap_in <= sc.y3);
       }
+      auto phase_a = [&](auto small_c) {
+#pragma unroll
+        for (int i = 0; i < 32; i += 2) {
+          const float2 sv = make_float2(__uint_as_float(rs[i]), __uint_as_float(rs[i + 1]));
+          float2 t, dcap;
+          if constexpr (CAP) {
+            if constexpr (decltype(small_c)::value) {
+              const float2 z = __fmul2_rn(sv, sv);
+              t = __ffma2_rn(sv, __ffma2_rn(z, make_float2(sc.kb3, sc.kb3), make_float2(sc.kk, sc.kk)), nL2);
+              dcap = __ffma2_rn(z, __ffma2_rn(z, make_float2(sc.e2, sc.e2), make_float2(sc.e1, sc.e1)), make_float2(1.f, 1.f));
+            } else {
+              const float2 th = make_float2(cap_tanh(sv.x * cap_in, precise_tanh), cap_tanh(sv.y * cap_in, precise_tanh));
+              t = __ffma2_rn(th, make_float2(cap_out, cap_out), nL2);
+              dcap = __ffma2_rn(make_float2(-th.x, -th.y), th, make_float2(1.f, 1.f));
+            }
+          } else {
+            t = __ffma2_rn(sv, c2, nL2);
+          }
+          if constexpr (FEAT) {
+            t = __fadd2_rn(t, make_float2(fmaf(alibi_l2, static_cast<float>(i), ab), fmaf(alibi_l2, static_cast<float>(i + 1), ab)));
+          }
+          float2 pe = make_float2(fast_exp2(t.x), fast_exp2(t.y));
+          if constexpr (FEAT) {
+            if (!((cells >> (i >> 4)) & 1u)) pe = make_float2(0.f, 0.f);     // keys i, i + 1 share a 16-key cell
+          }
+          if (need_mask) {
+            if (i > hi_rel || (WIN && i < lo_rel)) pe.x = 0.f;
+            if (i + 1 > hi_rel || (WIN && i + 1 < lo_rel)) pe.y = 0.f;
+          }
+          if constexpr (CAP) pe = __fmul2_rn(pe, dcap);
+          pr[i] = pe.x;
+          pr[i + 1] = pe.y;
+        }
+      };
+      if (CAP && small_y) phase_a(std::true_type{}); else phase_a(std::false_type{});
       // dP(j + 1) is issued on DP_FREE(j) without a wait of the MMA thread's own: see that tile's V land first.
       // Checked here, where it costs nothing: the exponentials above are still in flight
       if (j + 1 < n_tiles) {

@@ -176,6 +176,26 @@ __device__ __forceinline__ float tanh_exp(float y) {
   return 1.f - __fdividef(2.f, e + 1.f);
 }
 __device__ __forceinline__ float cap_tanh(float y, bool precise) { return precise ? tanh_exp(y) : fast_tanh(y); }
+// Backward kernels, soft cap, small scores.  With y = s * scale / cap and |y| <= y3 = min(0.3, (7.5e-3 / cap)^(1/5))
+// the degree-3 truncation of tanh is within 1e-3 / cap of it, so the capped score in the log2 domain is
+//   cap * log2(e) * tanh(y) ~ s * (kk + kb3 * z),  z = s^2, kk = scale * log2(e), kb3 = -kk * (scale / cap)^2 / 3
+// and 1 - tanh^2(y) ~ 1 + z * (e1 + e2 * z), e1 = -(scale / cap)^2, e2 = (2 / 3) (scale / cap)^4 (the y^6 / 9 term is
+// below 1e-5 there): six packed FMA-pipe operations per pair of scores and no special-function operation besides the
+// two exponentials.  tanh.approx on every score instead doubles the load of the special-function unit (16 results per
+// clock per SM), which is what bounds phase A of those kernels.
+struct SmallCap {
+  float y3, kk, kb3, e1, e2;
+};
+__device__ __forceinline__ SmallCap small_cap_consts(float scale, float softcap) {
+  SmallCap c;
+  const float ci = scale / softcap;
+  c.y3 = fminf(0.3f, powf(7.5e-3f / softcap, 0.2f));
+  c.kk = scale * kLog2e;
+  c.kb3 = -c.kk * ci * ci * (1.f / 3.f);
+  c.e1 = -ci * ci;
+  c.e2 = (2.f / 3.f) * ci * ci * ci * ci;
+  return c;
+}
 
 // Shared-memory tile of rows x DCOLS 16-bit elements, 16-byte chunks XOR-swizzled
 // by the row so that ldmatrix reads of 8 consecutive rows are conflict-free.

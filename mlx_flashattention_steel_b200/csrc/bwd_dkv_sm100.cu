@@ -474,24 +474,28 @@ bwd_dkv_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
       // the commit just seen also followed dK(it - 1), the last reader of that tile's Q stage; and every warp has
       // finished phase B(it - 1), the last reader of its stat slot
       if (it >= 1 && warp == 0 && lane == 0) mbar_arrive(bar(BAR_Q_EMPTY + (it - 1) % kQStages));
-      {
-        uint32_t rd[32];
-        tmem_ld32(tmem + lane_base + cDPT + q0l, rd);
-        tc_wait_ld();
-        uint32_t pd[16];
+      // in two halves of 16 queries: fewer registers are live at once
 #pragma unroll
-        for (int i = 0; i < 32; i += 4) {
-          const float4 nD = lds_f4(Ds + (q0l + i) * 4);      // -delta of four queries
-          const float2 d0 = __fmul2_rn(make_float2(pr[i], pr[i + 1]),
+      for (int h = 0; h < 2; ++h) {
+        uint32_t rd[16];
+        tmem_ld16(tmem + lane_base + cDPT + q0l + 16 * h, rd);
+        tc_wait_ld();
+        uint32_t pd[8];
+#pragma unroll
+        for (int i = 0; i < 16; i += 4) {
+          const float4 nD = lds_f4(Ds + (q0l + 16 * h + i) * 4);      // -delta of four queries
+          const float2 d0 = __fmul2_rn(make_float2(pr[16 * h + i], pr[16 * h + i + 1]),
                                        __fadd2_rn(make_float2(__uint_as_float(rd[i]), __uint_as_float(rd[i + 1])), make_float2(nD.x, nD.y)));
-          const float2 d1 = __fmul2_rn(make_float2(pr[i + 2], pr[i + 3]),
+          const float2 d1 = __fmul2_rn(make_float2(pr[16 * h + i + 2], pr[16 * h + i + 3]),
                                        __fadd2_rn(make_float2(__uint_as_float(rd[i + 2]), __uint_as_float(rd[i + 3])), make_float2(nD.z, nD.w)));
           pd[i >> 1] = pack16k<DT>(d0.x, d0.y);
           pd[(i >> 1) + 1] = pack16k<DT>(d1.x, d1.y);
         }
-        tmem_st16(tmem + lane_base + cDPT + q0l, pd);
-        tc_wait_st();
+        // dS^T of queries 16h .. 16h + 15 over columns 8h .. 8h + 7 of this warp's 32.  The second half's dP^T sits in
+        // columns 16 .. 31, which this store does not touch
+        tmem_st8(tmem + lane_base + cDPT + q0l + 8 * h, pd);
       }
+      tc_wait_st();
       // on behalf of the MMA thread: the next tile's dO has landed (its dP^T follows this tile's dK)
       if (it + 1 < n_iter &&
           !__all_sync(0xffffffffu, mbar_wait_bounded(bar(BAR_DO_FULL + ((it + 1) & 1)), ((it + 1) >> 1) & 1, s_abort))) { ok = false; break; }

@@ -92,6 +92,12 @@ __device__ __forceinline__ void tmem_st16(uint32_t addr, const uint32_t (&r)[16]
       : "memory");
 }
 
+__device__ __forceinline__ void tmem_st8(uint32_t addr, const uint32_t (&r)[8]) {
+  asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};\n" ::"r"(addr), "r"(r[0]),
+               "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7])
+               : "memory");
+}
+
 // Shared-memory matrix descriptor (sm_100 format): 128B swizzle, version 1.
 //   start address >> 4 in bits [0,14), leading byte offset >> 4 in [16,30),
 //   stride byte offset >> 4 in [32,46), version 1 in [46,48), layout 2 (SWIZZLE_128B) in [61,64).

@@ -241,8 +241,8 @@ def dram_traffic_ratio(key):
 
 def bench_decode(device, steps, warmup, pk, batch=None, rank=0, world=1, dist=None):
     """Config 4: paged int8-KV decode, B=128, seq_lens ~ U[512, 32768], page 16.  With world > 1 the 128 sequences are
-    sharded by batch: rank r owns a contiguous range of them with a pool of its own (no collective on the data path);
-    the total is all ranks' bytes over the slowest rank's time."""
+    sharded by batch: rank r owns a subset of them, balanced by KV length, with a pool of its own (no collective on the
+    data path); the total is all ranks' bytes over the slowest rank's time."""
     import numpy as np
 
     import mlx_flashattention_steel_b200 as fa
@@ -253,9 +253,10 @@ def bench_decode(device, steps, warmup, pk, batch=None, rank=0, world=1, dist=No
         cfg["B"] = batch
     rng = np.random.default_rng(4)
     all_lens = rng.integers(cfg["lo"], cfg["hi"] + 1, size=cfg["B"]).astype(np.int32)
-    b_lo, b_hi = par.shard_range(cfg["B"], world, rank)
-    lens = all_lens[b_lo:b_hi]
-    nb = int(b_hi - b_lo)
+    # sequences are dealt out by KV length (the cost of a decode step), not by position: the slowest rank sets the time
+    mine = par.shard_by_load(all_lens, world)[rank]
+    lens = all_lens[np.asarray(mine, dtype=np.int64)]
+    nb = len(mine)
     bs, Hkv, D = cfg["block_size"], cfg["Hkv"], cfg["D"]
     pages_per = (lens + bs - 1) // bs
     P = int(pages_per.sum()) + 8
@@ -315,7 +316,7 @@ def bench_decode(device, steps, warmup, pk, batch=None, rank=0, world=1, dist=No
     ratio = dram_traffic_ratio("decode_paged_config4_small")
     return {"metric": "paged-decode KV GB/s", "value": total_gbs, "unit": "GB/s", "ms_per_step": ms_max,
             "workload": f"config 4: B={cfg['B']} Hq=32 Hkv=8 D=128 page 16 seq_lens~U[512,32768] int8 KV + f16 scales, bf16 q"
-                        + (f"; sequences sharded by batch over {world} GPUs, one pool per GPU" if world > 1 else ""),
+                        + (f"; sequences sharded by batch over {world} GPUs (balanced by KV length), one pool per GPU" if world > 1 else ""),
             "n_gpus": world, "per_gpu_gbs": per_rank, "tokens": tokens if world == 1 else None,
             "algorithmic_bytes": bytes_total,
             # per GPU: rank 0's own launch against the measured copy bandwidth of one GPU

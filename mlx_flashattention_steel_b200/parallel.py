@@ -33,6 +33,24 @@ def shard_range(n: int, world: int, rank: int) -> Tuple[int, int]:
     return lo, lo + base + (1 if rank < extra else 0)
 
 
+def shard_by_load(loads, world: int) -> List[List[int]]:
+    """Deals items with unequal cost (sequences by their KV length) out to ``world`` ranks so that the heaviest rank is
+    as light as a greedy pass makes it: items in order of decreasing load, each to the rank that is lightest so far
+    (ties: the lower rank; equal loads: the lower index first).  Returns each rank's item indices in increasing order.
+    Every rank computes the same deal from the same ``loads``; nothing is exchanged."""
+    if world <= 0:
+        raise ValueError(f"bad world: {world}")
+    loads = [int(x) for x in loads]
+    order = sorted(range(len(loads)), key=lambda i: (-loads[i], i))
+    total = [0] * world
+    owned: List[List[int]] = [[] for _ in range(world)]
+    for i in order:
+        r = min(range(world), key=lambda j: (total[j], j))
+        owned[r].append(i)
+        total[r] += loads[i]
+    return [sorted(o) for o in owned]
+
+
 def shard_units(B: int, Hkv: int, world: int, rank: int) -> List[Tuple[int, int]]:
     """(batch, kv-head) units owned by ``rank``; unit u = b * Hkv + h, dealt contiguously so a
     rank's units are a few whole batches plus a contiguous head range (views, no copies)."""

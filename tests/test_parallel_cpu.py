@@ -25,6 +25,30 @@ def test_shard_range_covers_everything_once():
         par.shard_range(4, 2, 2)
 
 
+def test_shard_by_load_balances_and_covers():
+    import numpy as np
+
+    rng = np.random.default_rng(4)
+    lens = rng.integers(512, 32769, size=128)
+    for world in (1, 2, 3, 4, 8):
+        deal = par.shard_by_load(lens, world)
+        assert len(deal) == world
+        flat = sorted(i for d in deal for i in d)
+        assert flat == list(range(128))                       # every sequence exactly once
+        assert all(d == sorted(d) for d in deal)
+        totals = [int(lens[d].sum()) for d in deal]
+        # a greedy deal is within one item of even: no rank exceeds the mean by more than the longest sequence
+        assert max(totals) - sum(totals) / world <= int(lens.max())
+        assert par.shard_by_load(lens, world) == deal          # deterministic: every rank computes the same deal
+    # contiguous dealing of the same lengths is visibly worse at eight ranks
+    contiguous = [int(lens[slice(*par.shard_range(128, 8, r))].sum()) for r in range(8)]
+    assert max(int(lens[d].sum()) for d in par.shard_by_load(lens, 8)) < max(contiguous)
+    assert par.shard_by_load([], 2) == [[], []]
+    assert par.shard_by_load([5, 5, 5], 2) == [[0, 2], [1]]
+    with pytest.raises(ValueError):
+        par.shard_by_load([1], 0)
+
+
 def test_shard_units_config2():
     # 4 batches x 8 kv heads over 8 GPUs -> 4 units each, whole number of heads of one batch
     all_units = []
